@@ -1,0 +1,174 @@
+"""GPU decoder: the layer walk of one decode / verify step over the sm_100a kernels.
+
+``DecoderModel.step_rows(M)`` enqueues one forward pass for M rows (M <= 64)
+on the current stream; every kernel reads row positions, request slots and input
+tokens from the device control block, so the enqueued sequence can be captured
+once per M in a CUDA graph and replayed without host writes -- the role of the
+reference's capture walk (src/runtime/capture.cc:1332-1510: gdn_layer / fa_layer /
+mlp / head) with CUDA graphs in place of closed Level Zero command lists.
+
+Launches per dense layer: resid_norm, qkv GEMV, rope_append, attn_decode,
+attn_merge, o GEMV, resid_norm, gate_up GEMV, down GEMV (SiLU*up folded into its
+activation load) = 9; the reference's list has 12 per layer (774 for 64 layers).
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from typing import List, Optional
+
+import torch
+
+from ..ops import lib as K
+from .config import ModelConfig
+from .oracle import rope_tables
+from .weights import ModelWeights, LayerWeights, QLinear
+
+
+@dataclass
+class LinearPlan:
+    ql: QLinear
+    splits: int
+    part: torch.Tensor     # fp32 [splits * max_rows * n] scratch
+
+
+class StepBuffers:
+    """Activations and split-K scratch of one step, sized once for ``max_rows``."""
+
+    def __init__(self, cfg: ModelConfig, max_rows: int, nsplit_attn: int, device):
+        bf, f32 = torch.bfloat16, torch.float32
+        h = cfg.hidden
+        self.max_rows = max_rows
+        self.resid = torch.zeros(max_rows, h, dtype=bf, device=device)
+        self.x = torch.zeros(max_rows, h, dtype=bf, device=device)
+        self.q = torch.zeros(max_rows, cfg.q_dim, dtype=bf, device=device)
+        self.attn_out = torch.zeros(max_rows, cfg.q_dim, dtype=bf, device=device)
+        self.o_part = torch.zeros(max_rows * cfg.n_q_heads * nsplit_attn * cfg.head_dim, dtype=f32, device=device)
+        self.ml_part = torch.zeros(max_rows * cfg.n_q_heads * nsplit_attn * 2, dtype=f32, device=device)
+        self.logits = torch.zeros(max_rows, cfg.vocab, dtype=f32, device=device)
+        self.ncand = K.head_ncand(cfg.vocab)
+        self.cand_val = torch.zeros(max_rows * self.ncand, dtype=f32, device=device)
+        self.cand_idx = torch.zeros(max_rows * self.ncand, dtype=torch.int32, device=device)
+        self.flag = torch.zeros(4, dtype=torch.int32, device=device)
+        self._parts = {}
+        self.device = device
+
+    def part(self, name: str, splits: int, n: int) -> torch.Tensor:
+        key = (name, splits, n)
+        if key not in self._parts:
+            self._parts[key] = torch.zeros(splits * self.max_rows * n, dtype=torch.float32, device=self.device)
+        return self._parts[key]
+
+
+class KVCache:
+    """Paged KV: per layer ``[page][kv_head][16][D]`` for K and for V (bf16 or int8 + fp32 scales)."""
+
+    def __init__(self, cfg: ModelConfig, n_layers: int, num_pages: int, device, kv_dtype: str = "bf16"):
+        self.kv_int8 = kv_dtype == "int8"
+        dt = torch.int8 if self.kv_int8 else torch.bfloat16
+        self.num_pages = num_pages
+        self.k = torch.zeros(n_layers, num_pages, cfg.n_kv_heads, cfg.page_size, cfg.head_dim, dtype=dt, device=device)
+        self.v = torch.zeros_like(self.k)
+        if self.kv_int8:
+            self.k_scale = torch.zeros(n_layers, num_pages, cfg.n_kv_heads, cfg.page_size, dtype=torch.float32, device=device)
+            self.v_scale = torch.zeros_like(self.k_scale)
+        else:
+            self.k_scale = self.v_scale = None
+
+    def layer(self, li: int):
+        ks = self.k_scale[li] if self.kv_int8 else None
+        vs = self.v_scale[li] if self.kv_int8 else None
+        return self.k[li], self.v[li], ks, vs
+
+
+class DecoderModel:
+    def __init__(self, weights: ModelWeights, max_rows: int = 64, max_pos: int = 8192, nsplit_attn: int = 32,
+                 int8_head: bool = False):
+        self.w = weights
+        self.cfg = cfg = weights.cfg
+        self.device = weights.embed.device
+        self.max_rows = max_rows
+        self.nsplit_attn = nsplit_attn
+        self.buf = StepBuffers(cfg, max_rows, nsplit_attn, self.device)
+        cos, sin = rope_tables(cfg.head_dim, cfg.rope_theta, max_pos)
+        self.cos_t, self.sin_t = cos.to(self.device).contiguous(), sin.to(self.device).contiguous()
+        self.max_pos = max_pos
+        self.scale = 1.0 / math.sqrt(cfg.head_dim)
+        self.int8_head = int8_head
+        if int8_head and weights.lm_head_i8 is None:
+            wf = weights.lm_head.float()
+            sc = wf.abs().amax(dim=1).clamp_min(1e-8) / 127.0
+            weights.lm_head_i8 = (torch.round(wf / sc[:, None]).clamp_(-127, 127).to(torch.int8).contiguous(), sc.contiguous())
+        self._splits = {}
+
+    # ------------------------------------------------------------------ pieces
+    def _gemv(self, name: str, ql: QLinear, x: torch.Tensor, m: int, x_mode=0, s_in=1, x_slice=0):
+        key = (ql.n, ql.k)
+        s = self._splits.get(key)
+        if s is None:
+            s = self._splits[key] = K.gemv_splits(ql.n, ql.k)
+        part = self.buf.part(name, s, ql.n)
+        K.gemv_w4(ql.w4b, x, part, m, ql.n, ql.k, s, x_mode=x_mode, s_in=s_in, x_slice=x_slice)
+        return part, s
+
+    def attention_block(self, lw: LayerWeights, li: int, m: int, ctrl, block_table, max_blocks, kv: KVCache):
+        cfg, b = self.cfg, self.buf
+        part, s = self._gemv("qkv", lw.qkv, b.x, m)
+        kc, vc, ks, vs = kv.layer(li)
+        K.rope_append(part, m * cfg.qkv_dim, s, m, ctrl, block_table, max_blocks, self.cos_t, self.sin_t,
+                      cfg.n_q_heads, cfg.n_kv_heads, cfg.head_dim, b.q, kc, vc, ks, vs, kv.kv_int8)
+        K.attn_decode(b.q, kc, vc, block_table, ctrl, b.o_part, b.ml_part, b.attn_out, m, cfg.n_q_heads,
+                      cfg.n_kv_heads, cfg.head_dim, self.nsplit_attn, max_blocks, self.scale, ks, vs, kv.kv_int8)
+        return self._gemv("o", lw.o, b.attn_out, m)
+
+    def ffn_block(self, lw: LayerWeights, m: int):
+        cfg, b = self.cfg, self.buf
+        gu, s_gu = self._gemv("gate_up", lw.gate_up, b.x, m)
+        return self._gemv("down", lw.down, gu, m, x_mode=1, s_in=s_gu, x_slice=m * 2 * cfg.ffn)
+
+    def layers_walk(self, layers: List[LayerWeights], m: int, ctrl, block_table, max_blocks, kv: KVCache,
+                    first_from_embed: bool = True, kv_layer0: int = 0):
+        """Runs ``layers``; returns the (partials, splits) of the last residual branch, not yet folded."""
+        cfg, b = self.cfg, self.buf
+        h = cfg.hidden
+        pend = None
+        for i, lw in enumerate(layers):
+            if pend is None:
+                if first_from_embed:
+                    K.resid_norm(0, m, h, lw.input_norm, cfg.rms_eps, b.resid, b.x, embed=self.w.embed, ctrl=ctrl,
+                                 vocab=cfg.vocab, flag=b.flag)
+                else:   # resid already holds the layer input
+                    K.resid_norm(1, m, h, lw.input_norm, cfg.rms_eps, b.resid, b.x, resid_in=b.resid, splits=0)
+            else:
+                K.resid_norm(1, m, h, lw.input_norm, cfg.rms_eps, b.resid, b.x, resid_in=b.resid, part=pend[0],
+                             part_slice=m * h, splits=pend[1])
+            po, so = self.attention_block(lw, kv_layer0 + i, m, ctrl, block_table, max_blocks, kv)
+            K.resid_norm(1, m, h, lw.post_norm, cfg.rms_eps, b.resid, b.x, resid_in=b.resid, part=po,
+                         part_slice=m * h, splits=so)
+            if lw.gate_up is not None:
+                pend = self.ffn_block(lw, m)
+            else:
+                from . import moe as _moe
+                pend = _moe.moe_block_rows(self, lw, m)
+        return pend
+
+    def head(self, m: int, pend, ctrl, advance: bool, final_norm: Optional[torch.Tensor] = None):
+        cfg, b = self.cfg, self.buf
+        h = cfg.hidden
+        fn = self.w.final_norm if final_norm is None else final_norm
+        K.resid_norm(1, m, h, fn, cfg.rms_eps, b.resid, b.x, resid_in=b.resid, part=pend[0], part_slice=m * h,
+                     splits=pend[1])
+        if self.int8_head:
+            w8, sc = self.w.lm_head_i8
+            K.head_gemv(w8, b.x, b.logits, m, cfg.vocab, h, b.cand_val, b.cand_idx, wscale=sc)
+        else:
+            K.head_gemv(self.w.lm_head, b.x, b.logits, m, cfg.vocab, h, b.cand_val, b.cand_idx)
+        K.argmax_finish(b.cand_val, b.cand_idx, b.ncand, m, ctrl, advance)
+
+    # ------------------------------------------------------------------ whole step
+    def step_rows(self, m: int, ctrl, block_table, max_blocks, kv: KVCache, advance: bool):
+        """One forward pass for the ``m`` rows described by ``ctrl``; the arg-max of each row lands in
+        ``ctrl[out_token]``; with ``advance`` the rows' tokens and positions move on for the next replay."""
+        assert 1 <= m <= self.max_rows
+        pend = self.layers_walk(self.w.layers, m, ctrl, block_table, max_blocks, kv)
+        self.head(m, pend, ctrl, advance)

@@ -1,0 +1,632 @@
+// Element-wise and reduction kernels of the decode / verify step.
+//
+//   resid_norm      split-K fold + residual add + RMSNorm (or embedding gather + RMSNorm)
+//   rope_append     split-K fold of qkv + rotate-half RoPE + paged KV append (bf16 or int8)
+//   attn_decode     paged split-KV flash-decode for M rows (GQA packed per KV head)
+//   attn_merge      merge of the split partials -> bf16 attention output
+//   gemv_bf16       bf16 weight GEMV (lm_head, router), logits + per-CTA arg-max candidates
+//   gemv_i8         int8 weight GEMV with one fp32 scale per row (int8 lm_head)
+//   argmax_finish   deterministic arg-max (ties -> lower id) + control-block advance
+//
+// They stand where the reference has prep.cl, embed_gather.cl, attn.cl (attn_prep),
+// attn_v2.cl, gemv_bf16.cl, gemv_i8w.cl and argmax.cl.  All of them read the row
+// table of the device-resident control block, so a captured CUDA graph replays
+// without host writes (the reference's central idea: docs/04-architecture.md:214-228).
+#include "common.cuh"
+
+using namespace b2;
+
+namespace {
+
+// Control block (int32 words), shared by host and device.
+constexpr int CTRL_N_ROWS = 0;
+constexpr int CTRL_ROW_REQ = 16;     // [64] request slot of each row
+constexpr int CTRL_ROW_POS = 80;     // [64] absolute position of each row
+constexpr int CTRL_CUR_TOKEN = 144;  // [64] input token of each row
+constexpr int CTRL_OUT_TOKEN = 208;  // [64] arg-max of each row
+constexpr int CTRL_OUT_VALUE = 272;  // [64] its logit (float bits)
+constexpr int CTRL_WORDS = 512;
+
+// ------------------------------------------------------------------ resid_norm
+// One CTA per row.  mode 0: r = embed[cur_token[m]];  mode 1: r = resid_in + sum_s part[s].
+// resid_out = bf16(r);  x_out = bf16(resid_out * rsqrt(mean(resid_out^2) + eps) * w).
+struct ResidNormParams {
+  const __nv_bfloat16* embed;
+  const int* ctrl;
+  const __nv_bfloat16* resid_in;
+  const float* part;
+  long long part_slice;
+  int S, H, mode, vocab;
+  const float* w;
+  float eps;
+  __nv_bfloat16* resid_out;
+  __nv_bfloat16* x_out;
+  int* flag;
+};
+
+__global__ void __launch_bounds__(256) resid_norm_kernel(const ResidNormParams p) {
+  extern __shared__ float vals[];
+  __shared__ float red[8];
+  pdl_wait();
+  pdl_launch_dependents();
+  const int m = blockIdx.x, tid = threadIdx.x;
+  const int H2 = p.H >> 1;
+  float ss = 0.f;
+  const __nv_bfloat162* src2;
+  if (p.mode == 0) {
+    int tok = p.ctrl[CTRL_CUR_TOKEN + m];
+    if (tok < 0 || tok >= p.vocab) {  // out-of-vocabulary id: flag it, read row 0
+      if (tid == 0 && p.flag) atomicExch(p.flag, 0xDEAD0001);
+      tok = 0;
+    }
+    src2 = reinterpret_cast<const __nv_bfloat162*>(p.embed + (size_t)tok * p.H);
+  } else {
+    src2 = reinterpret_cast<const __nv_bfloat162*>(p.resid_in + (size_t)m * p.H);
+  }
+  for (int i = tid; i < H2; i += 256) {
+    float2 v = __bfloat1622float2(src2[i]);
+    if (p.mode == 1) {
+      for (int s = 0; s < p.S; ++s) {
+        const float2 a = *reinterpret_cast<const float2*>(p.part + (size_t)s * p.part_slice + (size_t)m * p.H + 2 * i);
+        v.x += a.x;
+        v.y += a.y;
+      }
+    }
+    const __nv_bfloat162 r = __floats2bfloat162_rn(v.x, v.y);
+    reinterpret_cast<__nv_bfloat162*>(p.resid_out + (size_t)m * p.H)[i] = r;
+    const float2 rf = __bfloat1622float2(r);
+    vals[2 * i] = rf.x;
+    vals[2 * i + 1] = rf.y;
+    ss += rf.x * rf.x + rf.y * rf.y;
+  }
+  ss = warp_sum(ss);
+  if ((tid & 31) == 0) red[tid >> 5] = ss;
+  __syncthreads();
+  float tot = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) tot += red[i];
+  const float rinv = rsqrtf(tot / (float)p.H + p.eps);
+  if (p.x_out) {
+    for (int i = tid; i < H2; i += 256) {
+      const float2 wv = *reinterpret_cast<const float2*>(p.w + 2 * i);
+      reinterpret_cast<__nv_bfloat162*>(p.x_out + (size_t)m * p.H)[i] =
+          __floats2bfloat162_rn(vals[2 * i] * rinv * wv.x, vals[2 * i + 1] * rinv * wv.y);
+    }
+  }
+}
+
+// ------------------------------------------------------------------ rope_append
+// One CTA per row.  Folds the qkv split-K slices, applies rotate-half RoPE to q and k,
+// writes q (bf16 [M][q_dim]) and appends k, v to the paged cache at the row's position.
+// Cache layout per layer: [page][kv_head][16][D] (bf16), or int8 with one fp32 scale
+// per (page, kv_head, slot) stored in a side array [page][kv_head][16].
+struct RopeParams {
+  const float* qkv;
+  long long slice;
+  int S;
+  const int* ctrl;
+  const int* block_table;
+  int max_blocks;
+  const float* cos_t;  // [max_pos][D/2]
+  const float* sin_t;
+  int n_q, n_kv, D;
+  __nv_bfloat16* q_out;
+  void* k_cache;
+  void* v_cache;
+  float* k_scale;
+  float* v_scale;
+  int kv_int8;
+};
+
+__global__ void __launch_bounds__(256) rope_append_kernel(const RopeParams p) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int m = blockIdx.x;
+  const int req = p.ctrl[CTRL_ROW_REQ + m], pos = p.ctrl[CTRL_ROW_POS + m];
+  const int D = p.D, Dh = D >> 1;
+  const int q_dim = p.n_q * D, kv_dim = p.n_kv * D, ld = q_dim + 2 * kv_dim;
+  const float* row = p.qkv + (size_t)m * ld;
+  const int page = p.block_table[(size_t)req * p.max_blocks + (pos >> 4)], slot = pos & 15;
+  const int n_pairs = (p.n_q + p.n_kv) * Dh;
+  if (!p.kv_int8) {
+    for (int i = threadIdx.x; i < n_pairs + kv_dim / 2; i += blockDim.x) {
+      if (i < n_pairs) {
+        const int head = i / Dh, j = i % Dh;
+        const int c0 = head * D + j;
+        float x1 = 0.f, x2 = 0.f;
+        for (int s = 0; s < p.S; ++s) {
+          x1 += row[(size_t)s * p.slice + c0];
+          x2 += row[(size_t)s * p.slice + c0 + Dh];
+        }
+        const float c = p.cos_t[(size_t)pos * Dh + j], sn = p.sin_t[(size_t)pos * Dh + j];
+        const float y1 = x1 * c - x2 * sn, y2 = x2 * c + x1 * sn;
+        if (head < p.n_q) {
+          p.q_out[(size_t)m * q_dim + c0] = __float2bfloat16(y1);
+          p.q_out[(size_t)m * q_dim + c0 + Dh] = __float2bfloat16(y2);
+        } else {
+          const int kh = head - p.n_q;
+          __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.k_cache) + (((size_t)page * p.n_kv + kh) * 16 + slot) * D;
+          dst[j] = __float2bfloat16(y1);
+          dst[j + Dh] = __float2bfloat16(y2);
+        }
+      } else {
+        const int e = (i - n_pairs) * 2;  // v element pair
+        const int kh = e / D, j = e % D;
+        float v0 = 0.f, v1 = 0.f;
+        for (int s = 0; s < p.S; ++s) {
+          v0 += row[(size_t)s * p.slice + q_dim + kv_dim + e];
+          v1 += row[(size_t)s * p.slice + q_dim + kv_dim + e + 1];
+        }
+        __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.v_cache) + (((size_t)page * p.n_kv + kh) * 16 + slot) * D;
+        *reinterpret_cast<__nv_bfloat162*>(dst + j) = __floats2bfloat162_rn(v0, v1);
+      }
+    }
+  } else {
+    // int8 KV: one warp per (k|v, kv head); per-(token, head) scale = max|x| / 127.
+    // q is written first by all threads.
+    for (int i = threadIdx.x; i < p.n_q * Dh; i += blockDim.x) {
+      const int head = i / Dh, j = i % Dh, c0 = head * D + j;
+      float x1 = 0.f, x2 = 0.f;
+      for (int s = 0; s < p.S; ++s) {
+        x1 += row[(size_t)s * p.slice + c0];
+        x2 += row[(size_t)s * p.slice + c0 + Dh];
+      }
+      const float c = p.cos_t[(size_t)pos * Dh + j], sn = p.sin_t[(size_t)pos * Dh + j];
+      p.q_out[(size_t)m * q_dim + c0] = __float2bfloat16(x1 * c - x2 * sn);
+      p.q_out[(size_t)m * q_dim + c0 + Dh] = __float2bfloat16(x2 * c + x1 * sn);
+    }
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+    for (int job = warp; job < 2 * p.n_kv; job += nw) {
+      const bool is_v = job >= p.n_kv;
+      const int kh = is_v ? job - p.n_kv : job;
+      // each lane holds D/32 elements (pairs j and j + D/2 for k so the rotation stays in-lane)
+      float vals[8];
+      const int per = D / 32;  // 2 or 4 (D = 64 / 128); up to 8 for D = 256
+      float amax = 0.f;
+      if (!is_v) {
+        for (int u = 0; u < per / 2; ++u) {
+          const int j = lane * (per / 2) + u;
+          const int c0 = q_dim + kh * D + j;
+          float x1 = 0.f, x2 = 0.f;
+          for (int s = 0; s < p.S; ++s) {
+            x1 += row[(size_t)s * p.slice + c0];
+            x2 += row[(size_t)s * p.slice + c0 + Dh];
+          }
+          const float c = p.cos_t[(size_t)pos * Dh + j], sn = p.sin_t[(size_t)pos * Dh + j];
+          vals[2 * u] = x1 * c - x2 * sn;
+          vals[2 * u + 1] = x2 * c + x1 * sn;
+        }
+      } else {
+        for (int u = 0; u < per; ++u) {
+          const int e = q_dim + kv_dim + kh * D + lane * per + u;
+          float v = 0.f;
+          for (int s = 0; s < p.S; ++s) v += row[(size_t)s * p.slice + e];
+          vals[u] = v;
+        }
+      }
+      for (int u = 0; u < per; ++u) amax = fmaxf(amax, fabsf(vals[u]));
+      amax = warp_max(amax);
+      const float sc = amax > 0.f ? amax / 127.f : 1.f, inv = 1.f / sc;
+      int8_t* base = reinterpret_cast<int8_t*>(is_v ? p.v_cache : p.k_cache) + (((size_t)page * p.n_kv + kh) * 16 + slot) * D;
+      if (!is_v) {
+        for (int u = 0; u < per / 2; ++u) {
+          const int j = lane * (per / 2) + u;
+          base[j] = (int8_t)__float2int_rn(vals[2 * u] * inv);
+          base[j + Dh] = (int8_t)__float2int_rn(vals[2 * u + 1] * inv);
+        }
+      } else {
+        for (int u = 0; u < per; ++u) base[lane * per + u] = (int8_t)__float2int_rn(vals[u] * inv);
+      }
+      if (lane == 0) (is_v ? p.v_scale : p.k_scale)[((size_t)page * p.n_kv + kh) * 16 + slot] = sc;
+    }
+  }
+}
+
+// ------------------------------------------------------------------ attn_decode
+// grid (n_kv, nsplit, M), 256 threads.  Each warp takes keys strided by 8 inside the
+// CTA's page range, four keys per iteration; each lane owns D/32 dims of q, k, v for
+// all GQA query heads of the KV head, so K and V rows are read once per group of heads.
+struct AttnDecParams {
+  const __nv_bfloat16* q;  // [M][n_q*D]
+  const void* k_cache;
+  const void* v_cache;
+  const float* k_scale;
+  const float* v_scale;
+  const int* block_table;
+  const int* ctrl;
+  float* o_part;   // [M][n_q][nsplit][D]
+  float* ml_part;  // [M][n_q][nsplit][2]
+  int n_q, n_kv, nsplit, max_blocks;
+  float scale_log2;  // softmax scale * log2(e)
+  int kv_int8;
+};
+
+template <int D, int GQA>
+__global__ void __launch_bounds__(256) attn_decode_kernel(const AttnDecParams p) {
+  constexpr int DL = D / 32;
+  constexpr int KPI = 4;  // keys per iteration per warp
+  __shared__ float sm_o[8][GQA][D];
+  __shared__ float sm_ml[8][GQA][2];
+  pdl_wait();
+  pdl_launch_dependents();
+  const int kh = blockIdx.x, split = blockIdx.y, m = blockIdx.z;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int req = p.ctrl[CTRL_ROW_REQ + m], ctx = p.ctrl[CTRL_ROW_POS + m] + 1;
+  const int total_pages = (ctx + 15) >> 4;
+  const int pps = (total_pages + p.nsplit - 1) / p.nsplit;
+  const int key0 = split * pps * 16, key1 = min(ctx, (split + 1) * pps * 16);
+
+  float qv[GQA][DL];
+#pragma unroll
+  for (int h = 0; h < GQA; ++h) {
+    const __nv_bfloat16* qp = p.q + (size_t)m * p.n_q * D + (size_t)(kh * GQA + h) * D + lane * DL;
+#pragma unroll
+    for (int d = 0; d < DL; ++d) qv[h][d] = __bfloat162float(qp[d]) * p.scale_log2;
+  }
+  float mx[GQA], l[GQA], acc[GQA][DL];
+#pragma unroll
+  for (int h = 0; h < GQA; ++h) {
+    mx[h] = -INFINITY;
+    l[h] = 0.f;
+#pragma unroll
+    for (int d = 0; d < DL; ++d) acc[h][d] = 0.f;
+  }
+  const int* bt = p.block_table + (size_t)req * p.max_blocks;
+
+  for (int kb = key0 + warp * KPI; kb < key1; kb += 8 * KPI) {
+    float kf[KPI][DL], vf[KPI][DL];
+    bool valid[KPI];
+#pragma unroll
+    for (int u = 0; u < KPI; ++u) {
+      const int key = kb + u;
+      valid[u] = key < key1;
+      const int kk = valid[u] ? key : key0;
+      const int page = bt[kk >> 4], slot = kk & 15;
+      const size_t off = (((size_t)page * p.n_kv + kh) * 16 + slot);
+      if (!p.kv_int8) {
+        const __nv_bfloat16* kp = reinterpret_cast<const __nv_bfloat16*>(p.k_cache) + off * D + lane * DL;
+        const __nv_bfloat16* vp = reinterpret_cast<const __nv_bfloat16*>(p.v_cache) + off * D + lane * DL;
+        if constexpr (DL == 4) {
+          const uint2 kr = *reinterpret_cast<const uint2*>(kp), vr = *reinterpret_cast<const uint2*>(vp);
+          kf[u][0] = bf16_lo(kr.x); kf[u][1] = bf16_hi(kr.x); kf[u][2] = bf16_lo(kr.y); kf[u][3] = bf16_hi(kr.y);
+          vf[u][0] = bf16_lo(vr.x); vf[u][1] = bf16_hi(vr.x); vf[u][2] = bf16_lo(vr.y); vf[u][3] = bf16_hi(vr.y);
+        } else {
+#pragma unroll
+          for (int d = 0; d < DL; ++d) {
+            kf[u][d] = __bfloat162float(kp[d]);
+            vf[u][d] = __bfloat162float(vp[d]);
+          }
+        }
+      } else {
+        const int8_t* kp = reinterpret_cast<const int8_t*>(p.k_cache) + off * D + lane * DL;
+        const int8_t* vp = reinterpret_cast<const int8_t*>(p.v_cache) + off * D + lane * DL;
+        const float ks = p.k_scale[off], vs = p.v_scale[off];
+#pragma unroll
+        for (int d = 0; d < DL; ++d) {
+          kf[u][d] = (float)kp[d] * ks;
+          vf[u][d] = (float)vp[d] * vs;
+        }
+      }
+    }
+    float s[GQA][KPI];
+#pragma unroll
+    for (int h = 0; h < GQA; ++h)
+#pragma unroll
+      for (int u = 0; u < KPI; ++u) {
+        float d0 = 0.f;
+#pragma unroll
+        for (int d = 0; d < DL; ++d) d0 = fmaf(qv[h][d], kf[u][d], d0);
+        d0 = warp_sum(d0);
+        s[h][u] = valid[u] ? d0 : -INFINITY;
+      }
+#pragma unroll
+    for (int h = 0; h < GQA; ++h) {
+      float mn = mx[h];
+#pragma unroll
+      for (int u = 0; u < KPI; ++u) mn = fmaxf(mn, s[h][u]);
+      const float corr = exp2f(mx[h] - mn);  // mx = -inf on first pass -> 0
+      l[h] *= corr;
+#pragma unroll
+      for (int d = 0; d < DL; ++d) acc[h][d] *= corr;
+#pragma unroll
+      for (int u = 0; u < KPI; ++u) {
+        const float pe = exp2f(s[h][u] - mn);
+        l[h] += pe;
+#pragma unroll
+        for (int d = 0; d < DL; ++d) acc[h][d] = fmaf(pe, vf[u][d], acc[h][d]);
+      }
+      mx[h] = mn;
+    }
+  }
+  // ---- merge the 8 warps in a fixed order
+#pragma unroll
+  for (int h = 0; h < GQA; ++h) {
+#pragma unroll
+    for (int d = 0; d < DL; ++d) sm_o[warp][h][lane * DL + d] = acc[h][d];
+    if (lane == 0) {
+      sm_ml[warp][h][0] = mx[h];
+      sm_ml[warp][h][1] = l[h];
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < GQA * D; i += 256) {
+    const int h = i / D, d = i % D;
+    float mm = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) mm = fmaxf(mm, sm_ml[w][h][0]);
+    float lt = 0.f, o = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) {
+      const float mw = sm_ml[w][h][0];
+      const float c = (mw == -INFINITY) ? 0.f : exp2f(mw - mm);
+      lt += sm_ml[w][h][1] * c;
+      o += sm_o[w][h][d] * c;
+    }
+    const size_t base = ((size_t)m * p.n_q + kh * GQA + h) * p.nsplit + split;
+    p.o_part[base * D + d] = o;
+    if (d == 0) {
+      p.ml_part[base * 2] = mm;
+      p.ml_part[base * 2 + 1] = lt;
+    }
+  }
+}
+
+// grid (n_q, M), D threads
+__global__ void attn_merge_kernel(const float* o_part, const float* ml_part, __nv_bfloat16* out, int n_q, int nsplit,
+                                  int D) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int h = blockIdx.x, m = blockIdx.y, d = threadIdx.x;
+  const size_t base = ((size_t)m * n_q + h) * nsplit;
+  float mm = -INFINITY;
+  for (int s = 0; s < nsplit; ++s) mm = fmaxf(mm, ml_part[(base + s) * 2]);
+  float lt = 0.f, o = 0.f;
+  for (int s = 0; s < nsplit; ++s) {
+    const float ms = ml_part[(base + s) * 2];
+    const float c = (ms == -INFINITY) ? 0.f : exp2f(ms - mm);
+    lt += ml_part[(base + s) * 2 + 1] * c;
+    o += o_part[(base + s) * D + d] * c;
+  }
+  out[((size_t)m * n_q + h) * D + d] = __float2bfloat16(lt > 0.f ? o / lt : 0.f);
+}
+
+// ------------------------------------------------------------------ gemv_bf16 / gemv_i8 (lm_head, router)
+// 256 threads = 8 warps, each warp owns RW rows; lanes stride K in 16-byte vectors.
+// Writes logits fp32 [M][ldo] and, when cand_val != nullptr, the CTA's best (value, id) per row m.
+template <typename WT>
+struct HeadParams {
+  const WT* w;          // [N][K]
+  const float* wscale;  // int8: [N]
+  const __nv_bfloat16* x;  // [M][K]
+  float* out;
+  int M, N, K, ldo;
+  float* cand_val;  // [M][gridDim.x]
+  int* cand_idx;
+  int n_valid;      // ids >= n_valid never win the arg-max
+};
+
+template <typename WT, int MT>
+__global__ void __launch_bounds__(256) head_gemv_kernel(const HeadParams<WT> p, int m0) {
+  constexpr int RW = 8;                       // rows per warp
+  constexpr int VE = 16 / sizeof(WT);         // weights per 16-byte vector
+  __shared__ float sv[8][MT];
+  __shared__ int si[8][MT];
+  pdl_wait();
+  pdl_launch_dependents();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row0 = (blockIdx.x * 8 + warp) * RW;
+  float best[MT];
+  int besti[MT];
+#pragma unroll
+  for (int m = 0; m < MT; ++m) { best[m] = -INFINITY; besti[m] = 0x7fffffff; }
+  for (int rr = 0; rr < RW; rr += 4) {
+    float acc[4][MT];
+#pragma unroll
+    for (int r = 0; r < 4; ++r)
+#pragma unroll
+      for (int m = 0; m < MT; ++m) acc[r][m] = 0.f;
+    for (int k = lane * VE; k < p.K; k += 32 * VE) {
+      uint4 wv[4];
+#pragma unroll
+      for (int r = 0; r < 4; ++r) {
+        const int n = min(row0 + rr + r, p.N - 1);
+        wv[r] = __ldcs(reinterpret_cast<const uint4*>(p.w + (size_t)n * p.K + k));
+      }
+#pragma unroll
+      for (int m = 0; m < MT; ++m) {
+        const int mm = min(m0 + m, p.M - 1);
+        float xf[VE];
+        const uint4* xp = reinterpret_cast<const uint4*>(p.x + (size_t)mm * p.K + k);
+#pragma unroll
+        for (int v = 0; v < VE / 8; ++v) {
+          const uint4 xv = __ldg(xp + v);
+          xf[8 * v + 0] = bf16_lo(xv.x); xf[8 * v + 1] = bf16_hi(xv.x);
+          xf[8 * v + 2] = bf16_lo(xv.y); xf[8 * v + 3] = bf16_hi(xv.y);
+          xf[8 * v + 4] = bf16_lo(xv.z); xf[8 * v + 5] = bf16_hi(xv.z);
+          xf[8 * v + 6] = bf16_lo(xv.w); xf[8 * v + 7] = bf16_hi(xv.w);
+        }
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+          const uint32_t ww[4] = {wv[r].x, wv[r].y, wv[r].z, wv[r].w};
+          float a = acc[r][m];
+          if constexpr (sizeof(WT) == 2) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              a = fmaf(bf16_lo(ww[j]), xf[2 * j], a);
+              a = fmaf(bf16_hi(ww[j]), xf[2 * j + 1], a);
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              a = fmaf((float)(int8_t)(ww[j] & 0xff), xf[4 * j], a);
+              a = fmaf((float)(int8_t)((ww[j] >> 8) & 0xff), xf[4 * j + 1], a);
+              a = fmaf((float)(int8_t)((ww[j] >> 16) & 0xff), xf[4 * j + 2], a);
+              a = fmaf((float)(int8_t)(ww[j] >> 24), xf[4 * j + 3], a);
+            }
+          }
+          acc[r][m] = a;
+        }
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+      const int n = row0 + rr + r;
+#pragma unroll
+      for (int m = 0; m < MT; ++m) {
+        float v = warp_sum(acc[r][m]);
+        if constexpr (sizeof(WT) == 1) v *= (n < p.N ? p.wscale[n] : 0.f);
+        if (n < p.N && m0 + m < p.M) {
+          if (lane == 0) p.out[(size_t)(m0 + m) * p.ldo + n] = v;
+          if (n < p.n_valid && (v > best[m])) { best[m] = v; besti[m] = n; }  // rows ascend: ties keep the lower id
+        }
+      }
+    }
+  }
+  if (p.cand_val) {
+    if (lane == 0) {
+#pragma unroll
+      for (int m = 0; m < MT; ++m) { sv[warp][m] = best[m]; si[warp][m] = besti[m]; }
+    }
+    __syncthreads();
+    if (threadIdx.x < MT && m0 + threadIdx.x < p.M) {
+      const int m = threadIdx.x;
+      float b = -INFINITY;
+      int bi = 0x7fffffff;
+      for (int w = 0; w < 8; ++w)
+        if (sv[w][m] > b) { b = sv[w][m]; bi = si[w][m]; }
+      p.cand_val[(size_t)(m0 + m) * gridDim.x + blockIdx.x] = b;
+      p.cand_idx[(size_t)(m0 + m) * gridDim.x + blockIdx.x] = bi;
+    }
+  }
+}
+
+// grid M, 256 threads: reduce the candidates; ties -> lower id; write control block.
+__global__ void __launch_bounds__(256) argmax_finish_kernel(const float* cand_val, const int* cand_idx, int ncand,
+                                                            int* ctrl, int advance) {
+  __shared__ float sv[256];
+  __shared__ int si[256];
+  pdl_wait();
+  pdl_launch_dependents();
+  const int m = blockIdx.x, tid = threadIdx.x;
+  float b = -INFINITY;
+  int bi = 0x7fffffff;
+  for (int i = tid; i < ncand; i += 256) {
+    const float v = cand_val[(size_t)m * ncand + i];
+    const int id = cand_idx[(size_t)m * ncand + i];
+    if (v > b || (v == b && id < bi)) { b = v; bi = id; }
+  }
+  sv[tid] = b;
+  si[tid] = bi;
+  __syncthreads();
+  for (int o = 128; o > 0; o >>= 1) {
+    if (tid < o) {
+      const float v = sv[tid + o];
+      const int id = si[tid + o];
+      if (v > sv[tid] || (v == sv[tid] && id < si[tid])) { sv[tid] = v; si[tid] = id; }
+    }
+    __syncthreads();
+  }
+  if (tid == 0) {
+    ctrl[CTRL_OUT_TOKEN + m] = si[0];
+    ctrl[CTRL_OUT_VALUE + m] = __float_as_int(sv[0]);
+    if (advance) {
+      ctrl[CTRL_CUR_TOKEN + m] = si[0];
+      ctrl[CTRL_ROW_POS + m] += 1;
+    }
+  }
+}
+
+}  // namespace
+
+// =================================================================== C entry points
+extern "C" int b2_resid_norm(const void* embed, const int* ctrl, const void* resid_in, const float* part,
+                             long long part_slice, int S, int M, int H, int mode, int vocab, const float* w, float eps,
+                             void* resid_out, void* x_out, int* flag, void* stream) {
+  ResidNormParams p;
+  p.embed = (const __nv_bfloat16*)embed; p.ctrl = ctrl; p.resid_in = (const __nv_bfloat16*)resid_in;
+  p.part = part; p.part_slice = part_slice; p.S = S; p.H = H; p.mode = mode; p.vocab = vocab; p.w = w; p.eps = eps;
+  p.resid_out = (__nv_bfloat16*)resid_out; p.x_out = (__nv_bfloat16*)x_out; p.flag = flag;
+  if (H % 2) return -1;
+  return b2_launch(resid_norm_kernel, dim3(M), dim3(256), (size_t)H * 4, (cudaStream_t)stream, true, p);
+}
+
+extern "C" int b2_rope_append(const float* qkv, long long slice, int S, int M, const int* ctrl, const int* block_table,
+                              int max_blocks, const float* cos_t, const float* sin_t, int n_q, int n_kv, int D,
+                              void* q_out, void* k_cache, void* v_cache, float* k_scale, float* v_scale, int kv_int8,
+                              void* stream) {
+  RopeParams p;
+  p.qkv = qkv; p.slice = slice; p.S = S; p.ctrl = ctrl; p.block_table = block_table; p.max_blocks = max_blocks;
+  p.cos_t = cos_t; p.sin_t = sin_t; p.n_q = n_q; p.n_kv = n_kv; p.D = D; p.q_out = (__nv_bfloat16*)q_out;
+  p.k_cache = k_cache; p.v_cache = v_cache; p.k_scale = k_scale; p.v_scale = v_scale; p.kv_int8 = kv_int8;
+  if (D % 64 || D > 256) return -1;
+  return b2_launch(rope_append_kernel, dim3(M), dim3(256), 0, (cudaStream_t)stream, true, p);
+}
+
+template <int D>
+static int attn_decode_dispatch(int gqa, const AttnDecParams& p, dim3 grid, cudaStream_t st) {
+  switch (gqa) {
+    case 1: return b2_launch(attn_decode_kernel<D, 1>, grid, dim3(256), 0, st, true, p);
+    case 2: return b2_launch(attn_decode_kernel<D, 2>, grid, dim3(256), 0, st, true, p);
+    case 4: return b2_launch(attn_decode_kernel<D, 4>, grid, dim3(256), 0, st, true, p);
+    case 5: return b2_launch(attn_decode_kernel<D, 5>, grid, dim3(256), 0, st, true, p);
+    case 8: return b2_launch(attn_decode_kernel<D, 8>, grid, dim3(256), 0, st, true, p);
+  }
+  return -3;
+}
+
+extern "C" int b2_attn_decode(const void* q, const void* k_cache, const void* v_cache, const float* k_scale,
+                              const float* v_scale, const int* block_table, const int* ctrl, float* o_part,
+                              float* ml_part, void* out, int M, int n_q, int n_kv, int D, int nsplit, int max_blocks,
+                              float scale, int kv_int8, void* stream) {
+  AttnDecParams p;
+  p.q = (const __nv_bfloat16*)q; p.k_cache = k_cache; p.v_cache = v_cache; p.k_scale = k_scale; p.v_scale = v_scale;
+  p.block_table = block_table; p.ctrl = ctrl; p.o_part = o_part; p.ml_part = ml_part;
+  p.n_q = n_q; p.n_kv = n_kv; p.nsplit = nsplit; p.max_blocks = max_blocks;
+  p.scale_log2 = scale * 1.4426950408889634f; p.kv_int8 = kv_int8;
+  dim3 grid(n_kv, nsplit, M);
+  cudaStream_t st = (cudaStream_t)stream;
+  int rc;
+  if (D == 128) rc = attn_decode_dispatch<128>(n_q / n_kv, p, grid, st);
+  else if (D == 64) rc = attn_decode_dispatch<64>(n_q / n_kv, p, grid, st);
+  else return -2;
+  if (rc) return rc;
+  return b2_launch(attn_merge_kernel, dim3(n_q, M), dim3(D), 0, st, true, (const float*)o_part, (const float*)ml_part,
+                   (__nv_bfloat16*)out, n_q, nsplit, D);
+}
+
+template <typename WT>
+static int head_launch(const HeadParams<WT>& p, cudaStream_t st) {
+  const int rows_per_cta = 64;
+  dim3 grid((p.N + rows_per_cta - 1) / rows_per_cta);
+  for (int m0 = 0; m0 < p.M; m0 += 4) {
+    const int mt = min(4, p.M - m0);
+    int rc;
+    if (mt == 1) rc = b2_launch(head_gemv_kernel<WT, 1>, grid, dim3(256), 0, st, true, p, m0);
+    else if (mt == 2) rc = b2_launch(head_gemv_kernel<WT, 2>, grid, dim3(256), 0, st, true, p, m0);
+    else rc = b2_launch(head_gemv_kernel<WT, 4>, grid, dim3(256), 0, st, true, p, m0);
+    if (rc) return rc;
+  }
+  return 0;
+}
+
+// Number of arg-max candidates per row that b2_head_gemv writes (= its grid size).
+extern "C" int b2_head_ncand(int N) { return (N + 63) / 64; }
+
+extern "C" int b2_head_gemv(const void* w, const float* wscale, int w_int8, const void* x, float* out, int M, int N,
+                            int K, int ldo, float* cand_val, int* cand_idx, int n_valid, void* stream) {
+  if (K % (w_int8 ? 16 : 8) != 0) return -1;
+  if (w_int8) {
+    HeadParams<int8_t> p{(const int8_t*)w, wscale, (const __nv_bfloat16*)x, out, M, N, K, ldo, cand_val, cand_idx, n_valid};
+    return head_launch(p, (cudaStream_t)stream);
+  }
+  HeadParams<__nv_bfloat16> p{(const __nv_bfloat16*)w, nullptr, (const __nv_bfloat16*)x, out, M, N, K, ldo, cand_val, cand_idx, n_valid};
+  return head_launch(p, (cudaStream_t)stream);
+}
+
+extern "C" int b2_argmax_finish(const float* cand_val, const int* cand_idx, int ncand, int M, int* ctrl, int advance,
+                                void* stream) {
+  return b2_launch(argmax_finish_kernel, dim3(M), dim3(256), 0, (cudaStream_t)stream, true, cand_val, cand_idx, ncand,
+                   ctrl, advance);
+}
+
+B2_DEFINE_STATUS(decode)

@@ -1,0 +1,164 @@
+"""ctypes bindings of the sm_100a kernel library.
+
+The library exports plain C entry points that take raw device pointers and a
+``cudaStream_t``; the wrappers here pass ``tensor.data_ptr()`` and the current
+torch stream, so the kernels are captured by ``torch.cuda.CUDAGraph`` like any
+other work on that stream.  There is no PyTorch fallback: on a machine with a
+GPU a missing library is an error, never a silent eager path.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from typing import Optional
+
+import torch
+
+from . import build as _build
+
+_lib: Optional[ctypes.CDLL] = None
+_UNITS = ("gemv", "decode", "gemm", "attn", "moe", "comm", "spec")
+
+# Control block layout (int32 words) -- mirrors decode_ops.cu
+CTRL_N_ROWS = 0
+CTRL_ROW_REQ = 16
+CTRL_ROW_POS = 80
+CTRL_CUR_TOKEN = 144
+CTRL_OUT_TOKEN = 208
+CTRL_OUT_VALUE = 272
+CTRL_WORDS = 512
+MAX_ROWS = 64
+
+launch_count = 0    # kernels launched through this module (bench.py reports it)
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def lib() -> ctypes.CDLL:
+    global _lib
+    if _lib is None:
+        path = _build.LIB
+        if not os.path.exists(path) or not _build.is_current():
+            try:
+                path = _build.build()
+            except Exception as e:  # no nvcc on this machine: use the shipped binary if there is one
+                if not os.path.exists(_build.LIB):
+                    raise KernelError(f"kernel library is not built and cannot be built here: {e}") from e
+                path = _build.LIB
+        _lib = ctypes.CDLL(path)
+    return _lib
+
+
+def available() -> bool:
+    return torch.cuda.is_available()
+
+
+def _p(t: Optional[torch.Tensor]):
+    return ctypes.c_void_p(0 if t is None else t.data_ptr())
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _check(rc: int, what: str):
+    global launch_count
+    launch_count += 1
+    if rc != 0:
+        raise KernelError(f"{what} failed with code {rc}")
+
+
+def status() -> dict:
+    """Reads every translation unit's status word; {} when no kernel recorded an error."""
+    out = {}
+    L = lib()
+    for u in _UNITS:
+        fn = getattr(L, f"b2_status_{u}", None)
+        if fn is None:
+            continue
+        buf = (ctypes.c_uint * 4)()
+        rc = fn(buf)
+        if rc != 0:
+            raise KernelError(f"status read failed ({u}): cuda error {rc}")
+        if buf[0]:
+            out[u] = {"code": hex(buf[0]), "detail": buf[1], "count": buf[2]}
+    return out
+
+
+def status_clear():
+    L = lib()
+    for u in _UNITS:
+        fn = getattr(L, f"b2_status_clear_{u}", None)
+        if fn is not None:
+            fn()
+
+
+def check_status():
+    s = status()
+    if s:
+        raise KernelError(f"device kernels reported bounded-wait failures: {s}")
+
+
+# ----------------------------------------------------------------------------- decode ops
+def gemv_splits(n: int, k: int) -> int:
+    return lib().b2_gemv_w4_splits(n, k)
+
+
+def gemv_w4(w4b: torch.Tensor, x: torch.Tensor, out: torch.Tensor, m: int, n: int, k: int, splits: int,
+            x_mode: int = 0, s_in: int = 1, x_slice: int = 0, ldx: Optional[int] = None):
+    """``out[s][m][n]`` fp32 partial sums of ``x @ W^T`` for a W4B weight.
+
+    ``x_mode`` 0: ``x`` is bf16 ``[m][k]``.  ``x_mode`` 1: ``x`` is fp32 ``[s_in][m][2k]``
+    split-K slices of a gate‖up projection (interleave16); the kernel folds them and applies
+    SiLU(gate) * up while staging the activations.
+    """
+    if ldx is None:
+        ldx = k if x_mode == 0 else 2 * k
+    rc = lib().b2_gemv_w4(_p(w4b), _p(x), _p(out), m, n, k, splits, ldx, n, x_mode, s_in,
+                          ctypes.c_longlong(x_slice), _stream())
+    _check(rc, "gemv_w4")
+
+
+def resid_norm(mode: int, m: int, h: int, w: torch.Tensor, eps: float, resid_out: torch.Tensor,
+               x_out: Optional[torch.Tensor], *, embed=None, ctrl=None, vocab=0, resid_in=None, part=None,
+               part_slice=0, splits=0, flag=None):
+    rc = lib().b2_resid_norm(_p(embed), _p(ctrl), _p(resid_in), _p(part), ctypes.c_longlong(part_slice), splits, m, h,
+                             mode, vocab, _p(w), ctypes.c_float(eps), _p(resid_out), _p(x_out), _p(flag), _stream())
+    _check(rc, "resid_norm")
+
+
+def rope_append(qkv_part, slice_elems, splits, m, ctrl, block_table, max_blocks, cos_t, sin_t, n_q, n_kv, d, q_out,
+                k_cache, v_cache, k_scale=None, v_scale=None, kv_int8=False):
+    rc = lib().b2_rope_append(_p(qkv_part), ctypes.c_longlong(slice_elems), splits, m, _p(ctrl), _p(block_table),
+                              max_blocks, _p(cos_t), _p(sin_t), n_q, n_kv, d, _p(q_out), _p(k_cache), _p(v_cache),
+                              _p(k_scale), _p(v_scale), int(kv_int8), _stream())
+    _check(rc, "rope_append")
+
+
+def attn_decode(q, k_cache, v_cache, block_table, ctrl, o_part, ml_part, out, m, n_q, n_kv, d, nsplit, max_blocks,
+                scale, k_scale=None, v_scale=None, kv_int8=False):
+    global launch_count
+    rc = lib().b2_attn_decode(_p(q), _p(k_cache), _p(v_cache), _p(k_scale), _p(v_scale), _p(block_table), _p(ctrl),
+                              _p(o_part), _p(ml_part), _p(out), m, n_q, n_kv, d, nsplit, max_blocks,
+                              ctypes.c_float(scale), int(kv_int8), _stream())
+    launch_count += 1
+    _check(rc, "attn_decode")
+
+
+def head_ncand(n: int) -> int:
+    return lib().b2_head_ncand(n)
+
+
+def head_gemv(w, x, out, m, n, k, cand_val=None, cand_idx=None, n_valid=None, wscale=None):
+    global launch_count
+    rc = lib().b2_head_gemv(_p(w), _p(wscale), int(wscale is not None), _p(x), _p(out), m, n, k, n, _p(cand_val),
+                            _p(cand_idx), n if n_valid is None else n_valid, _stream())
+    launch_count += (m + 3) // 4 - 1
+    _check(rc, "head_gemv")
+
+
+def argmax_finish(cand_val, cand_idx, ncand, m, ctrl, advance: bool):
+    rc = lib().b2_argmax_finish(_p(cand_val), _p(cand_idx), ncand, m, _p(ctrl), int(advance), _stream())
+    _check(rc, "argmax_finish")

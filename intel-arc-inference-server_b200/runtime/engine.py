@@ -1,0 +1,185 @@
+"""Single-GPU engine: sequence slots, paged KV, control block, CUDA-graph replay.
+
+The role of the reference's ``runtime::Engine`` (src/runtime/engine.h:52-690):
+ingest a prompt, replay decode steps, verify draft rows, keep per-sequence
+state in slots.  Here a "captured command list" is a ``torch.cuda.CUDAGraph``
+per (row count, advance) pair; the device control block carries positions and
+tokens from one replay to the next, so plain decode needs no host write between
+steps.  Host-side bookkeeping (sequence lengths, page tables) is deterministic
+from the number of steps, so the host never reads the device to know where a
+sequence is.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+from ..models.config import ModelConfig
+from ..models.decoder import DecoderModel, KVCache
+from ..models.weights import ModelWeights
+from ..ops import lib as K
+from .kv_pool import KvPool
+
+PAGE = 16
+
+
+@dataclass
+class Row:
+    slot: int
+    pos: int
+    token: int
+
+
+class Engine:
+    def __init__(self, weights: ModelWeights, max_seqs: int = 1, max_len: int = 4096, kv_dtype: str = "bf16",
+                 max_rows: int = 64, use_graphs: bool = True, int8_head: bool = False, num_pages: Optional[int] = None,
+                 nsplit_attn: int = 32, prefill_backend: str = "bf16"):
+        self.cfg = cfg = weights.cfg
+        self.device = weights.embed.device
+        self.max_seqs, self.max_len, self.max_rows = max_seqs, max_len, max_rows
+        self.max_blocks = (max_len + PAGE - 1) // PAGE
+        if num_pages is None:
+            num_pages = max_seqs * self.max_blocks + 1
+        self.model = DecoderModel(weights, max_rows=max_rows, max_pos=max_len, nsplit_attn=nsplit_attn,
+                                  int8_head=int8_head)
+        self.kv = KVCache(cfg, cfg.n_layers, num_pages, self.device, kv_dtype)
+        self.kv_dtype = kv_dtype
+        self.pool = KvPool(num_pages, max_seqs, self.max_blocks)
+        self.ctrl = torch.zeros(K.CTRL_WORDS, dtype=torch.int32, device=self.device)
+        self.ctrl_host = torch.zeros(K.CTRL_WORDS, dtype=torch.int32).pin_memory()
+        self.out_host = torch.zeros(K.CTRL_WORDS, dtype=torch.int32).pin_memory()
+        self.block_table = torch.zeros(max_seqs, self.max_blocks, dtype=torch.int32, device=self.device)
+        self.block_table_host = torch.zeros(max_seqs, self.max_blocks, dtype=torch.int32).pin_memory()
+        self.seq_len = [0] * max_seqs
+        self.use_graphs = use_graphs
+        self.graphs: Dict[Tuple[int, bool], torch.cuda.CUDAGraph] = {}
+        self.prefill_backend = prefill_backend
+        self._prefill = None
+        self.steps_replayed = 0
+        self.launches_per_step: Dict[Tuple[int, bool], int] = {}
+
+    # ------------------------------------------------------------------ slots and pages
+    def reset(self, slot: Optional[int] = None):
+        slots = range(self.max_seqs) if slot is None else [slot]
+        for s in slots:
+            self.pool.release(s)
+            self.seq_len[s] = 0
+
+    def truncate(self, slot: int, length: int):
+        """Drop everything after ``length`` positions (rejected draft rows)."""
+        assert length <= self.seq_len[slot]
+        self.seq_len[slot] = length
+        self.pool.truncate(slot, (length + PAGE - 1) // PAGE)
+
+    def _ensure_pages(self, slot: int, upto_len: int):
+        if upto_len > self.max_len:
+            raise ValueError(f"sequence of {upto_len} positions exceeds max_len {self.max_len}")
+        changed = self.pool.ensure(slot, (upto_len + PAGE - 1) // PAGE)
+        if changed:
+            row = self.pool.table(slot)
+            self.block_table_host[slot, : len(row)] = torch.from_numpy(np.asarray(row, dtype=np.int32))
+            self.block_table[slot].copy_(self.block_table_host[slot], non_blocking=True)
+
+    def _write_rows(self, rows: Sequence[Row]):
+        m = len(rows)
+        c = self.ctrl_host
+        c[K.CTRL_N_ROWS] = m
+        for i, r in enumerate(rows):
+            c[K.CTRL_ROW_REQ + i] = r.slot
+            c[K.CTRL_ROW_POS + i] = r.pos
+            c[K.CTRL_CUR_TOKEN + i] = r.token
+        self.ctrl.copy_(c, non_blocking=True)
+
+    # ------------------------------------------------------------------ running a step
+    def _enqueue(self, m: int, advance: bool):
+        self.model.step_rows(m, self.ctrl, self.block_table, self.max_blocks, self.kv, advance)
+
+    def _run(self, m: int, advance: bool):
+        if not self.use_graphs:
+            self._enqueue(m, advance)
+            return
+        key = (m, advance)
+        g = self.graphs.get(key)
+        if g is None:
+            # warm-up outside capture (sets function attributes, allocates split-K scratch), then
+            # restore the control block the warm-up advanced
+            saved = self.ctrl.clone()
+            n0 = K.launch_count
+            self._enqueue(m, advance)
+            self.launches_per_step[key] = K.launch_count - n0
+            torch.cuda.current_stream().synchronize()
+            self.ctrl.copy_(saved)
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                self._enqueue(m, advance)
+            self.ctrl.copy_(saved)
+            self.graphs[key] = g
+        g.replay()
+        self.steps_replayed += 1
+
+    def _read_out(self, m: int) -> List[int]:
+        self.out_host.copy_(self.ctrl, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        return self.out_host[K.CTRL_OUT_TOKEN: K.CTRL_OUT_TOKEN + m].tolist()
+
+    # ------------------------------------------------------------------ public API
+    def forward_rows(self, rows: Sequence[Row], advance: bool = False, read: bool = True):
+        """Run arbitrary rows (verify, batched decode, chunked ingest). KV of each row is appended."""
+        for r in rows:
+            self._ensure_pages(r.slot, r.pos + 1)
+        self._write_rows(rows)
+        self._run(len(rows), advance)
+        for r in rows:
+            self.seq_len[r.slot] = max(self.seq_len[r.slot], r.pos + 1)
+        return self._read_out(len(rows)) if read else None
+
+    def logits(self, m: int) -> torch.Tensor:
+        """fp32 logits of the last step's rows (device tensor view)."""
+        return self.model.buf.logits[:m]
+
+    def prefill(self, slot: int, ids: Sequence[int], chunk: Optional[int] = None) -> int:
+        """Ingest ``ids`` after the slot's current length; returns the greedy next token."""
+        ids = list(ids)
+        if self.prefill_backend != "rows" and len(ids) > self.max_rows:
+            from .prefill import PrefillRunner
+            if self._prefill is None:
+                self._prefill = PrefillRunner(self)
+            return self._prefill.run(slot, ids, chunk)
+        start = self.seq_len[slot]
+        out = None
+        for c0 in range(0, len(ids), self.max_rows):
+            part = ids[c0: c0 + self.max_rows]
+            rows = [Row(slot, start + c0 + i, t) for i, t in enumerate(part)]
+            last = c0 + self.max_rows >= len(ids)
+            out = self.forward_rows(rows, advance=False, read=last)
+        return out[-1]
+
+    def decode_begin(self, slots: Sequence[int], tokens: Sequence[int]):
+        """Arm plain decode: one row per slot, starting with ``tokens`` at each slot's current length."""
+        rows = [Row(s, self.seq_len[s], t) for s, t in zip(slots, tokens)]
+        self._write_rows(rows)
+        self._decode_slots = list(slots)
+
+    def decode_step(self, read: bool = True):
+        """One replay of the armed decode rows; the device advances tokens and positions itself."""
+        slots = self._decode_slots
+        for s in slots:
+            self._ensure_pages(s, self.seq_len[s] + 1)
+        self._run(len(slots), True)
+        for s in slots:
+            self.seq_len[s] += 1
+        return self._read_out(len(slots)) if read else None
+
+    def generate(self, ids: Sequence[int], n_new: int, slot: int = 0) -> List[int]:
+        """Greedy: prefill ``ids`` then ``n_new`` tokens; returns the new tokens."""
+        self.reset(slot)
+        first = self.prefill(slot, ids)
+        out = [first]
+        if n_new > 1:
+            self.decode_begin([slot], [first])
+            for _ in range(n_new - 1):
+                out.append(self.decode_step()[0])
+        return out

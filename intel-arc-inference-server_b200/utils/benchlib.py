@@ -1,0 +1,102 @@
+"""Timed regions of ``bench.py``: decode steps and prefill passes through the public Engine API.
+
+The same measurement style as the reference's ``b70-decode --bench``
+(src/cli/b70_decode.cc:82-90,131-140): ingest a prompt to the wanted depth, then
+time plain decode steps; prefill is timed as whole prompt passes.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..models.config import preset
+from ..models.weights import random_weights
+from ..ops import lib as K
+from ..runtime.engine import Engine, Row
+
+
+def _events():
+    return torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+
+def run_decode_bench(args, barrier) -> dict:
+    cfg = preset(args.model)
+    dev = torch.device("cuda", torch.cuda.current_device())
+    weights = random_weights(cfg, device=dev, seed=0, exact=False)
+    total = args.depth + 2 * (args.steps + args.warmup) + 64
+    eng = Engine(weights, max_seqs=1, max_len=total, kv_dtype=args.kv_cache, int8_head=args.int8_head,
+                 prefill_backend=args.prefill_backend,
+                 nsplit_attn=max(4, min(64, args.depth // 128)))
+    g = torch.Generator().manual_seed(0)
+    ids = torch.randint(0, cfg.vocab, (args.depth,), generator=g).tolist()
+    first = eng.prefill(0, ids)
+    # ---- device-timed: graph replays, tokens and positions advance on the device
+    eng.decode_begin([0], [first])
+    for _ in range(args.warmup):
+        eng.decode_step(read=False)
+    barrier()
+    e0, e1 = _events()
+    n0 = K.launch_count
+    e0.record()
+    for _ in range(args.steps):
+        eng.decode_step(read=False)
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1) / args.steps
+    launches = eng.launches_per_step.get((1, True), 0) * args.steps
+    # ---- end to end: every step the host sends the row (pinned H2D) and reads the token back (D2H)
+    tok = eng._read_out(1)[0]
+    pos = eng.seq_len[0]
+    for _ in range(args.warmup):
+        tok = eng.forward_rows([Row(0, pos, tok)], advance=False, read=True)[0]
+        pos += 1
+    barrier()
+    e0, e1 = _events()
+    e0.record()
+    for _ in range(args.steps):
+        tok = eng.forward_rows([Row(0, pos, tok)], advance=False, read=True)[0]
+        pos += 1
+    e1.record()
+    barrier()
+    e2e_ms = e0.elapsed_time(e1) / args.steps
+    w_bytes = cfg.weight_bytes_per_token(1.0 if args.int8_head else 2.0)
+    kv_bytes = cfg.kv_bytes_per_token(args.kv_cache) * args.depth
+    return {
+        "metric": "decode_tokens_per_s", "baseline": 164.0,
+        "ms_per_step": ms, "tokens_per_step": 1, "e2e_ms_per_step": e2e_ms,
+        "h2d": K.CTRL_WORDS * 4, "d2h": K.CTRL_WORDS * 4, "launches": launches,
+        "config": {"model": cfg.name, "global_batch": 1, "seq_len": args.depth, "parallelism": "replica",
+                   "kv_cache": args.kv_cache, "lm_head": "int8" if args.int8_head else "bf16",
+                   "weights": "W4A16 int4 g64, random init", "l2": "inputs larger than L2 (12.7 GB of weights per step)",
+                   "bytes_per_step": w_bytes + kv_bytes,
+                   "achieved_GBps": (w_bytes + kv_bytes) / (ms / 1e3) / 1e9},
+    }
+
+
+def run_prefill_bench(args, barrier, model: str, backend: str) -> dict:
+    cfg = preset(model)
+    dev = torch.device("cuda", torch.cuda.current_device())
+    weights = random_weights(cfg, device=dev, seed=0, exact=False)
+    n = args.prefill_len
+    eng = Engine(weights, max_seqs=1, max_len=n + 64, kv_dtype="bf16", prefill_backend=backend, use_graphs=False)
+    g = torch.Generator().manual_seed(1)
+    ids_t = torch.randint(0, cfg.vocab, (n,), generator=g, dtype=torch.int32).pin_memory()
+    ids = ids_t.tolist()
+    reps = max(3, min(args.steps, 8))
+    for _ in range(3):
+        eng.reset(0)
+        eng.prefill(0, ids)
+    barrier()
+    e0, e1 = _events()
+    n0 = K.launch_count
+    e0.record()
+    for _ in range(reps):
+        eng.reset(0)
+        eng.prefill(0, ids)       # includes the H2D copy of the ids and the D2H read of the first token
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1) / reps
+    base = 11223.0 if cfg.is_moe else 2800.0
+    return {"ms": ms, "tokens": n, "baseline": base, "launches": (K.launch_count - n0),
+            "e2e_ms": ms, "h2d": n * 4, "d2h": K.CTRL_WORDS * 4,
+            "config": {"model": cfg.name, "global_batch": 1, "seq_len": n, "backend": backend,
+                       "parallelism": "replica", "l2": "weights larger than L2"}}

@@ -1,0 +1,222 @@
+"""Decode-path kernels against plain PyTorch fp32 references of the same op (GPU)."""
+import math
+
+import pytest
+import torch
+
+from b200serve.models.oracle import apply_rope, rope_tables
+from b200serve.models.weights import deinterleave16
+from b200serve.utils import quant as Q
+
+pytestmark = pytest.mark.gpu
+
+
+def K():
+    from b200serve.ops import lib
+    return lib
+
+
+def _ctrl(rows):
+    k = K()
+    c = torch.zeros(k.CTRL_WORDS, dtype=torch.int32)
+    c[k.CTRL_N_ROWS] = len(rows)
+    for i, (req, pos, tok) in enumerate(rows):
+        c[k.CTRL_ROW_REQ + i], c[k.CTRL_ROW_POS + i], c[k.CTRL_CUR_TOKEN + i] = req, pos, tok
+    return c.cuda()
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 256, 256), (1, 5120, 5120), (3, 1408, 256), (8, 512, 704),
+                                     (13, 640, 1024), (33, 384, 2048), (64, 256, 512), (2, 200, 192)])
+def test_gemv_w4_matches_fp32(m, n, k):
+    k_ = K()
+    torch.manual_seed(m * 1000 + n)
+    w = torch.randn(n, k) * 0.02
+    q, s = Q.quantize_rtn(w)
+    w4b = Q.to_w4b(q, s).cuda()
+    wd = Q.dequant(q, s)
+    x = (torch.randn(m, k)).to(torch.bfloat16)
+    splits = k_.gemv_splits(n, k)
+    out = torch.full((splits, m, n), float("nan"), device="cuda")
+    k_.gemv_w4(w4b, x.cuda(), out, m, n, k, splits)
+    torch.cuda.synchronize()
+    k_.check_status()
+    got = out.sum(0).cpu()
+    ref = x.float() @ wd.t()
+    assert torch.isfinite(got).all()
+    assert (got - ref).abs().max() <= 2e-3 * ref.abs().max() + 1e-4
+
+
+def test_gemv_w4_rows_do_not_depend_on_m():
+    """Property R: a row's bits are the same whether it runs alone or among other rows."""
+    k_ = K()
+    torch.manual_seed(7)
+    n, k = 512, 1024
+    w4b = Q.random_w4b(n, k, "cuda", 3)
+    x = torch.randn(40, k, device="cuda").to(torch.bfloat16)
+    s = k_.gemv_splits(n, k)
+    outs = {}
+    for m in (1, 5, 8, 9, 17, 40):
+        o = torch.zeros(s, m, n, device="cuda")
+        k_.gemv_w4(w4b, x[:m].contiguous(), o, m, n, k, s)
+        outs[m] = o.sum(0)
+    torch.cuda.synchronize()
+    for m in (5, 8, 9, 17, 40):
+        assert torch.equal(outs[m][0], outs[1][0])
+        assert torch.equal(outs[40][:m], outs[m])
+
+
+def test_gemv_w4_silu_mul_fold_input():
+    k_ = K()
+    torch.manual_seed(11)
+    m, i_dim, n = 4, 704, 256
+    s_in = 3
+    gu = torch.randn(s_in, m, 2 * i_dim) * 0.5
+    w = torch.randn(n, i_dim) * 0.02
+    q, s = Q.quantize_rtn(w)
+    w4b = Q.to_w4b(q, s).cuda()
+    splits = k_.gemv_splits(n, i_dim)
+    out = torch.zeros(splits, m, n, device="cuda")
+    k_.gemv_w4(w4b, gu.cuda(), out, m, n, i_dim, splits, x_mode=1, s_in=s_in, x_slice=m * 2 * i_dim)
+    torch.cuda.synchronize()
+    g, u = deinterleave16(gu.sum(0))
+    act = (torch.nn.functional.silu(g) * u).to(torch.bfloat16).float()
+    ref = act @ Q.dequant(q, s).t()
+    got = out.sum(0).cpu()
+    assert (got - ref).abs().max() <= 3e-3 * ref.abs().max() + 1e-4
+
+
+def test_resid_norm_embed_and_fold():
+    k_ = K()
+    torch.manual_seed(5)
+    m, h, vocab = 5, 5120, 100
+    embed = (torch.randn(vocab, h) * 0.02).to(torch.bfloat16).cuda()
+    w = (1 + 0.1 * torch.randn(h)).cuda()
+    toks = [3, 99, 0, 42, 7]
+    ctrl = _ctrl([(0, i, t) for i, t in enumerate(toks)])
+    resid = torch.zeros(m, h, dtype=torch.bfloat16, device="cuda")
+    x = torch.zeros_like(resid)
+    k_.resid_norm(0, m, h, w, 1e-6, resid, x, embed=embed, ctrl=ctrl, vocab=vocab)
+    r_ref = embed[toks].float()
+    x_ref = r_ref * torch.rsqrt(r_ref.pow(2).mean(-1, keepdim=True) + 1e-6) * w
+    assert torch.equal(resid, embed[toks])
+    assert (x.float() - x_ref).abs().max() < 2e-2 * x_ref.abs().max()
+    # fold: resid + sum of 3 slices
+    part = torch.randn(3, m, h, device="cuda") * 0.05
+    resid2 = torch.zeros_like(resid)
+    k_.resid_norm(1, m, h, w, 1e-6, resid2, x, resid_in=resid, part=part, part_slice=m * h, splits=3)
+    r2 = (resid.float() + part[0] + part[1] + part[2]).to(torch.bfloat16)
+    assert torch.equal(resid2, r2)
+    x2 = r2.float() * torch.rsqrt(r2.float().pow(2).mean(-1, keepdim=True) + 1e-6) * w
+    assert (x.float() - x2).abs().max() < 1e-2 * x2.abs().max()
+    k_.check_status()
+
+
+@pytest.mark.parametrize("kv_int8", [False, True])
+@pytest.mark.parametrize("n_q,n_kv,d", [(4, 2, 64), (40, 8, 128), (16, 4, 128)])
+def test_rope_append_and_attention(n_q, n_kv, d, kv_int8):
+    """rope_append writes q and the paged cache; attn_decode + merge reproduce softmax attention."""
+    k_ = K()
+    torch.manual_seed(n_q + d)
+    ctx, m = 77, 3                       # 3 verify rows at positions ctx-3 .. ctx-1 of request 1
+    max_blocks, num_pages = 8, 32
+    qkv_dim = (n_q + 2 * n_kv) * d
+    cos, sin = rope_tables(d, 1e6, 256)
+    cos, sin = cos.cuda(), sin.cuda()
+    # scattered pages for request 1
+    table = torch.zeros(2, max_blocks, dtype=torch.int32)
+    pages = [5, 9, 2, 17, 30]
+    table[1, :5] = torch.tensor(pages, dtype=torch.int32)
+    table = table.cuda()
+    dt = torch.int8 if kv_int8 else torch.bfloat16
+    kc = torch.zeros(num_pages, n_kv, 16, d, dtype=dt, device="cuda")
+    vc = torch.zeros_like(kc)
+    ks = torch.zeros(num_pages, n_kv, 16, device="cuda") if kv_int8 else None
+    vs = torch.zeros(num_pages, n_kv, 16, device="cuda") if kv_int8 else None
+    all_qkv = torch.randn(ctx, qkv_dim)
+    q_out = torch.zeros(64, n_q * d, dtype=torch.bfloat16, device="cuda")
+    # append in chunks of up to 64 rows, 2 split-K slices each
+    for c0 in range(0, ctx, 64):
+        rows = list(range(c0, min(ctx, c0 + 64)))
+        sl = torch.stack([all_qkv[rows] * 0.25, all_qkv[rows] * 0.75]).cuda().contiguous()
+        ctrl = _ctrl([(1, p, 0) for p in rows])
+        k_.rope_append(sl, len(rows) * qkv_dim, 2, len(rows), ctrl, table, max_blocks, cos, sin, n_q, n_kv, d,
+                       q_out, kc, vc, ks, vs, kv_int8)
+    torch.cuda.synchronize()
+    pos = torch.arange(ctx)
+    q_ref = apply_rope(all_qkv[:, : n_q * d].reshape(ctx, n_q, d), pos, 1e6)
+    k_ref = apply_rope(all_qkv[:, n_q * d: (n_q + n_kv) * d].reshape(ctx, n_kv, d), pos, 1e6)
+    v_ref = all_qkv[:, (n_q + n_kv) * d:].reshape(ctx, n_kv, d)
+    # cache contents
+    def gather(cache, scale):
+        out = torch.zeros(ctx, n_kv, d)
+        for p in range(ctx):
+            pg = pages[p // 16]
+            row = cache[pg, :, p % 16, :].float().cpu()
+            if scale is not None:
+                row = row * scale[pg, :, p % 16].cpu()[:, None]
+            out[p] = row
+        return out
+    tol = 0.02 if kv_int8 else 0.01
+    assert (gather(kc, ks) - k_ref).abs().max() < tol * k_ref.abs().max()
+    assert (gather(vc, vs) - v_ref).abs().max() < tol * v_ref.abs().max()
+    # attention for the last m rows (their q was written by the last rope_append call)
+    last_rows = list(range(ctx - m, ctx))
+    nrows_last = ctx - (ctx - 1) // 64 * 64
+    qsel = q_out[nrows_last - m: nrows_last].contiguous()
+    assert (qsel.float().cpu().reshape(m, n_q, d) - q_ref[last_rows]).abs().max() < 0.02 * q_ref.abs().max()
+    ctrl = _ctrl([(1, p, 0) for p in last_rows])
+    nsplit = 4
+    o_part = torch.zeros(m * n_q * nsplit * d, device="cuda")
+    ml = torch.zeros(m * n_q * nsplit * 2, device="cuda")
+    out = torch.zeros(m, n_q * d, dtype=torch.bfloat16, device="cuda")
+    k_.attn_decode(qsel, kc, vc, table, ctrl, o_part, ml, out, m, n_q, n_kv, d, nsplit, max_blocks,
+                   1.0 / math.sqrt(d), ks, vs, kv_int8)
+    torch.cuda.synchronize()
+    k_.check_status()
+    g = n_q // n_kv
+    kk = k_ref.repeat_interleave(g, dim=1)
+    vv = v_ref.repeat_interleave(g, dim=1)
+    ref = torch.zeros(m, n_q, d)
+    for i, p in enumerate(last_rows):
+        sc = torch.einsum("hd,shd->hs", q_ref[p], kk[: p + 1]) / math.sqrt(d)
+        ref[i] = torch.einsum("hs,shd->hd", torch.softmax(sc, -1), vv[: p + 1])
+    got = out.float().cpu().reshape(m, n_q, d)
+    assert (got - ref).abs().max() < (0.04 if kv_int8 else 0.02) * ref.abs().max() + 1e-3
+
+
+@pytest.mark.parametrize("int8", [False, True])
+def test_head_gemv_and_argmax(int8):
+    k_ = K()
+    torch.manual_seed(9)
+    m, n, kdim = 6, 1000, 512
+    w = (torch.randn(n, kdim) * 0.05).to(torch.bfloat16)
+    x = torch.randn(m, kdim).to(torch.bfloat16)
+    # force a tie between ids 17 and 600 on row 0: identical weight rows
+    w[600] = w[17]
+    ncand = k_.head_ncand(n)
+    out = torch.zeros(m, n, device="cuda")
+    cv = torch.zeros(m * ncand, device="cuda")
+    ci = torch.zeros(m * ncand, dtype=torch.int32, device="cuda")
+    if int8:
+        sc = w.float().abs().amax(1) / 127
+        w8 = torch.round(w.float() / sc[:, None]).to(torch.int8)
+        k_.head_gemv(w8.cuda(), x.cuda(), out, m, n, kdim, cv, ci, wscale=sc.cuda())
+        ref = x.float() @ (w8.float() * sc[:, None]).t()
+    else:
+        k_.head_gemv(w.cuda(), x.cuda(), out, m, n, kdim, cv, ci)
+        ref = x.float() @ w.float().t()
+    ctrl = _ctrl([(0, 10 + i, 0) for i in range(m)])
+    k_.argmax_finish(cv, ci, ncand, m, ctrl, True)
+    torch.cuda.synchronize()
+    k_.check_status()
+    got = out.cpu()
+    assert (got - ref).abs().max() < 2e-3 * ref.abs().max()
+    c = ctrl.cpu()
+    toks = c[k_.CTRL_OUT_TOKEN: k_.CTRL_OUT_TOKEN + m]
+    # device arg-max of its own logits, ties to the lower id
+    mx = got.max(dim=1, keepdim=True).values
+    idx = torch.where(got == mx, torch.arange(n)[None, :], torch.tensor(n)).min(dim=1).values
+    assert toks.tolist() == idx.tolist()
+    assert got[0, 17] == got[0, 600]
+    assert c[k_.CTRL_CUR_TOKEN: k_.CTRL_CUR_TOKEN + m].tolist() == idx.tolist()
+    assert c[k_.CTRL_ROW_POS: k_.CTRL_ROW_POS + m].tolist() == [11 + i for i in range(m)]
