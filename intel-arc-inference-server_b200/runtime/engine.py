@@ -36,7 +36,7 @@ class Row:
 class Engine:
     def __init__(self, weights: ModelWeights, max_seqs: int = 1, max_len: int = 4096, kv_dtype: str = "bf16",
                  max_rows: int = 64, use_graphs: bool = True, int8_head: bool = False, num_pages: Optional[int] = None,
-                 nsplit_attn: int = 32, prefill_backend: str = "bf16"):
+                 nsplit_attn: int = 32, prefill_backend: str = "rows"):
         self.cfg = cfg = weights.cfg
         self.device = weights.embed.device
         self.max_seqs, self.max_len, self.max_rows = max_seqs, max_len, max_rows
