@@ -44,53 +44,69 @@ struct ResidNormParams {
   int* flag;
 };
 
-__global__ void __launch_bounds__(256) resid_norm_kernel(const ResidNormParams p) {
+// blockDim = H/8 rounded up to a warp (at most 1024): each thread owns 8 consecutive elements per
+// pass, and the S slice loads of a pass are independent, so they are all in flight together.
+__global__ void __launch_bounds__(1024) resid_norm_kernel(const ResidNormParams p) {
   extern __shared__ float vals[];
-  __shared__ float red[8];
+  __shared__ float red[32];
   pdl_wait();
   pdl_launch_dependents();
-  const int m = blockIdx.x, tid = threadIdx.x;
-  const int H2 = p.H >> 1;
+  const int m = blockIdx.x, tid = threadIdx.x, nthr = blockDim.x;
+  const int H8 = p.H >> 3;
   float ss = 0.f;
-  const __nv_bfloat162* src2;
+  const uint4* src;
   if (p.mode == 0) {
     int tok = p.ctrl[CTRL_CUR_TOKEN + m];
     if (tok < 0 || tok >= p.vocab) {  // out-of-vocabulary id: flag it, read row 0
       if (tid == 0 && p.flag) atomicExch(p.flag, 0xDEAD0001);
       tok = 0;
     }
-    src2 = reinterpret_cast<const __nv_bfloat162*>(p.embed + (size_t)tok * p.H);
+    src = reinterpret_cast<const uint4*>(p.embed + (size_t)tok * p.H);
   } else {
-    src2 = reinterpret_cast<const __nv_bfloat162*>(p.resid_in + (size_t)m * p.H);
+    src = reinterpret_cast<const uint4*>(p.resid_in + (size_t)m * p.H);
   }
-  for (int i = tid; i < H2; i += 256) {
-    float2 v = __bfloat1622float2(src2[i]);
+  for (int i = tid; i < H8; i += nthr) {
+    const uint4 rv = src[i];
+    float v[8] = {bf16_lo(rv.x), bf16_hi(rv.x), bf16_lo(rv.y), bf16_hi(rv.y),
+                  bf16_lo(rv.z), bf16_hi(rv.z), bf16_lo(rv.w), bf16_hi(rv.w)};
     if (p.mode == 1) {
+      const float* pp = p.part + (size_t)m * p.H + 8 * i;
+#pragma unroll 4
       for (int s = 0; s < p.S; ++s) {
-        const float2 a = *reinterpret_cast<const float2*>(p.part + (size_t)s * p.part_slice + (size_t)m * p.H + 2 * i);
-        v.x += a.x;
-        v.y += a.y;
+        const float4 a0 = *reinterpret_cast<const float4*>(pp + (size_t)s * p.part_slice);
+        const float4 a1 = *reinterpret_cast<const float4*>(pp + (size_t)s * p.part_slice + 4);
+        v[0] += a0.x; v[1] += a0.y; v[2] += a0.z; v[3] += a0.w;
+        v[4] += a1.x; v[5] += a1.y; v[6] += a1.z; v[7] += a1.w;
       }
     }
-    const __nv_bfloat162 r = __floats2bfloat162_rn(v.x, v.y);
-    reinterpret_cast<__nv_bfloat162*>(p.resid_out + (size_t)m * p.H)[i] = r;
-    const float2 rf = __bfloat1622float2(r);
-    vals[2 * i] = rf.x;
-    vals[2 * i + 1] = rf.y;
-    ss += rf.x * rf.x + rf.y * rf.y;
+    uint4 o;
+    o.x = pack_bf16(v[0], v[1]); o.y = pack_bf16(v[2], v[3]); o.z = pack_bf16(v[4], v[5]); o.w = pack_bf16(v[6], v[7]);
+    reinterpret_cast<uint4*>(p.resid_out + (size_t)m * p.H)[i] = o;
+    const uint32_t ow[4] = {o.x, o.y, o.z, o.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float f0 = bf16_lo(ow[j]), f1 = bf16_hi(ow[j]);
+      vals[8 * i + 2 * j] = f0;
+      vals[8 * i + 2 * j + 1] = f1;
+      ss += f0 * f0 + f1 * f1;
+    }
   }
   ss = warp_sum(ss);
   if ((tid & 31) == 0) red[tid >> 5] = ss;
   __syncthreads();
   float tot = 0.f;
-#pragma unroll
-  for (int i = 0; i < 8; ++i) tot += red[i];
+  for (int i = 0; i < (nthr >> 5); ++i) tot += red[i];
   const float rinv = rsqrtf(tot / (float)p.H + p.eps);
   if (p.x_out) {
-    for (int i = tid; i < H2; i += 256) {
-      const float2 wv = *reinterpret_cast<const float2*>(p.w + 2 * i);
-      reinterpret_cast<__nv_bfloat162*>(p.x_out + (size_t)m * p.H)[i] =
-          __floats2bfloat162_rn(vals[2 * i] * rinv * wv.x, vals[2 * i + 1] * rinv * wv.y);
+    for (int i = tid; i < H8; i += nthr) {
+      const float4 w0 = *reinterpret_cast<const float4*>(p.w + 8 * i), w1 = *reinterpret_cast<const float4*>(p.w + 8 * i + 4);
+      const float* vv = vals + 8 * i;
+      uint4 o;
+      o.x = pack_bf16(vv[0] * rinv * w0.x, vv[1] * rinv * w0.y);
+      o.y = pack_bf16(vv[2] * rinv * w0.z, vv[3] * rinv * w0.w);
+      o.z = pack_bf16(vv[4] * rinv * w1.x, vv[5] * rinv * w1.y);
+      o.w = pack_bf16(vv[6] * rinv * w1.z, vv[7] * rinv * w1.w);
+      reinterpret_cast<uint4*>(p.x_out + (size_t)m * p.H)[i] = o;
     }
   }
 }
@@ -129,12 +145,12 @@ __global__ void __launch_bounds__(256) rope_append_kernel(const RopeParams p) {
   const int page = p.block_table[(size_t)req * p.max_blocks + (pos >> 4)], slot = pos & 15;
   const int n_pairs = (p.n_q + p.n_kv) * Dh;
   if (!p.kv_int8) {
-    for (int i = threadIdx.x; i < n_pairs + kv_dim / 2; i += blockDim.x) {
+    for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < n_pairs + kv_dim / 2; i += gridDim.y * blockDim.x) {
       if (i < n_pairs) {
         const int head = i / Dh, j = i % Dh;
         const int c0 = head * D + j;
         float x1 = 0.f, x2 = 0.f;
-        for (int s = 0; s < p.S; ++s) {
+        _Pragma("unroll 4") for (int s = 0; s < p.S; ++s) {
           x1 += row[(size_t)s * p.slice + c0];
           x2 += row[(size_t)s * p.slice + c0 + Dh];
         }
@@ -153,7 +169,7 @@ __global__ void __launch_bounds__(256) rope_append_kernel(const RopeParams p) {
         const int e = (i - n_pairs) * 2;  // v element pair
         const int kh = e / D, j = e % D;
         float v0 = 0.f, v1 = 0.f;
-        for (int s = 0; s < p.S; ++s) {
+        _Pragma("unroll 4") for (int s = 0; s < p.S; ++s) {
           v0 += row[(size_t)s * p.slice + q_dim + kv_dim + e];
           v1 += row[(size_t)s * p.slice + q_dim + kv_dim + e + 1];
         }
@@ -164,10 +180,10 @@ __global__ void __launch_bounds__(256) rope_append_kernel(const RopeParams p) {
   } else {
     // int8 KV: one warp per (k|v, kv head); per-(token, head) scale = max|x| / 127.
     // q is written first by all threads.
-    for (int i = threadIdx.x; i < p.n_q * Dh; i += blockDim.x) {
+    for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < p.n_q * Dh; i += gridDim.y * blockDim.x) {
       const int head = i / Dh, j = i % Dh, c0 = head * D + j;
       float x1 = 0.f, x2 = 0.f;
-      for (int s = 0; s < p.S; ++s) {
+      _Pragma("unroll 4") for (int s = 0; s < p.S; ++s) {
         x1 += row[(size_t)s * p.slice + c0];
         x2 += row[(size_t)s * p.slice + c0 + Dh];
       }
@@ -176,7 +192,7 @@ __global__ void __launch_bounds__(256) rope_append_kernel(const RopeParams p) {
       p.q_out[(size_t)m * q_dim + c0 + Dh] = __float2bfloat16(x2 * c + x1 * sn);
     }
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
-    for (int job = warp; job < 2 * p.n_kv; job += nw) {
+    for (int job = blockIdx.y * nw + warp; job < 2 * p.n_kv; job += gridDim.y * nw) {
       const bool is_v = job >= p.n_kv;
       const int kh = is_v ? job - p.n_kv : job;
       // each lane holds D/32 elements (pairs j and j + D/2 for k so the rotation stays in-lane)
@@ -188,7 +204,7 @@ __global__ void __launch_bounds__(256) rope_append_kernel(const RopeParams p) {
           const int j = lane * (per / 2) + u;
           const int c0 = q_dim + kh * D + j;
           float x1 = 0.f, x2 = 0.f;
-          for (int s = 0; s < p.S; ++s) {
+          _Pragma("unroll 4") for (int s = 0; s < p.S; ++s) {
             x1 += row[(size_t)s * p.slice + c0];
             x2 += row[(size_t)s * p.slice + c0 + Dh];
           }
@@ -200,7 +216,7 @@ __global__ void __launch_bounds__(256) rope_append_kernel(const RopeParams p) {
         for (int u = 0; u < per; ++u) {
           const int e = q_dim + kv_dim + kh * D + lane * per + u;
           float v = 0.f;
-          for (int s = 0; s < p.S; ++s) v += row[(size_t)s * p.slice + e];
+          _Pragma("unroll 4") for (int s = 0; s < p.S; ++s) v += row[(size_t)s * p.slice + e];
           vals[u] = v;
         }
       }
@@ -546,8 +562,10 @@ extern "C" int b2_resid_norm(const void* embed, const int* ctrl, const void* res
   p.embed = (const __nv_bfloat16*)embed; p.ctrl = ctrl; p.resid_in = (const __nv_bfloat16*)resid_in;
   p.part = part; p.part_slice = part_slice; p.S = S; p.H = H; p.mode = mode; p.vocab = vocab; p.w = w; p.eps = eps;
   p.resid_out = (__nv_bfloat16*)resid_out; p.x_out = (__nv_bfloat16*)x_out; p.flag = flag;
-  if (H % 2) return -1;
-  return b2_launch(resid_norm_kernel, dim3(M), dim3(256), (size_t)H * 4, (cudaStream_t)stream, true, p);
+  if (H % 8) return -1;
+  int threads = ((H / 8 + 31) / 32) * 32;
+  if (threads > 1024) threads = 1024;
+  return b2_launch(resid_norm_kernel, dim3(M), dim3(threads), (size_t)H * 4, (cudaStream_t)stream, true, p);
 }
 
 extern "C" int b2_rope_append(const float* qkv, long long slice, int S, int M, const int* ctrl, const int* block_table,
@@ -559,7 +577,9 @@ extern "C" int b2_rope_append(const float* qkv, long long slice, int S, int M, c
   p.cos_t = cos_t; p.sin_t = sin_t; p.n_q = n_q; p.n_kv = n_kv; p.D = D; p.q_out = (__nv_bfloat16*)q_out;
   p.k_cache = k_cache; p.v_cache = v_cache; p.k_scale = k_scale; p.v_scale = v_scale; p.kv_int8 = kv_int8;
   if (D % 64 || D > 256) return -1;
-  return b2_launch(rope_append_kernel, dim3(M), dim3(256), 0, (cudaStream_t)stream, true, p);
+  const int items = (n_q + n_kv) * (D / 2) + n_kv * D / 2;
+  int gy = kv_int8 ? max((n_q * D / 2 + 255) / 256, (2 * n_kv + 7) / 8) : (items + 255) / 256;
+  return b2_launch(rope_append_kernel, dim3(M, gy), dim3(256), 0, (cudaStream_t)stream, true, p);
 }
 
 template <int D>

@@ -251,10 +251,12 @@ int launch_t(const GemvParams& p, cudaStream_t stream) {
 }  // namespace
 
 // Number of k splits: a function of (N, K) only, so that a row's bits do not depend on M.
+// The grid (N/128 x splits) is sized to one wave of 296 CTA slots (148 SMs x 2 resident CTAs):
+// a second, partly filled wave would cost a full stream latency for a fraction of the work.
 extern "C" int b2_gemv_w4_splits(int N, int K) {
   const int nb = (N + 127) / 128, kg = K / 64;
-  int s = (296 + nb - 1) / nb;          // aim at two CTAs per SM
-  int smax = kg / 8;                    // at least 8 groups (512 k) per split
+  int s = 296 / nb;
+  int smax = kg / 8;  // at least 8 groups (512 k) per split
   if (smax < 1) smax = 1;
   if (s > smax) s = smax;
   if (s > 16) s = 16;

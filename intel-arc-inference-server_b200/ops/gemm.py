@@ -1,0 +1,66 @@
+"""Bindings of the tcgen05 prefill GEMMs (``csrc/gemm_tc.cu``)."""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from . import lib as K
+
+EPI_BF16, EPI_F32, EPI_SILU_MUL, EPI_RESID_ADD = 0, 1, 2, 3
+
+
+def _launch(a, b, c, m, n, k, ldc, i8, epi, resid=None, a_scale=None, b_scale=None, blocks=None, n_experts=0, bn=0):
+    be = br0 = brn = nb = None
+    max_blk = 0
+    if blocks is not None:
+        be, br0, brn, nb, max_blk = blocks
+    rc = K.lib().b2_gemm_tc(K._p(a), K._p(b), K._p(c), m, n, k, ldc, int(i8), epi, K._p(resid), K._p(a_scale),
+                            K._p(b_scale), K._p(be), K._p(br0), K._p(brn), K._p(nb), max_blk, n_experts, bn,
+                            K._stream())
+    K._check(rc, "gemm_tc")
+
+
+def gemm_bf16(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor, epi: int = EPI_BF16,
+              resid: Optional[torch.Tensor] = None, bn: int = 0):
+    """``c = a @ b.T`` with ``a`` ``[M][K]``, ``b`` ``[N][K]`` bf16.  ``epi``: bf16 / fp32 store,
+    SiLU(gate)*up over interleave16 columns (``c`` is ``[M][N/2]``), or ``resid + a b^T`` in bf16."""
+    m, k = a.shape
+    n = b.shape[0]
+    _launch(a, b, c, m, n, k, c.stride(0), False, epi, resid=resid, bn=bn)
+
+
+def gemm_i8(a8, b8, a_scale, b_scale, c, epi: int = EPI_BF16, resid=None, bn: int = 0):
+    """int8 x int8 -> int32 on kind::i8, ``c = (a8 @ b8.T) * a_scale[:, None] * b_scale[None, :]``."""
+    m, k = a8.shape
+    n = b8.shape[0]
+    _launch(a8, b8, c, m, n, k, c.stride(0), True, epi, resid=resid, a_scale=a_scale, b_scale=b_scale, bn=bn)
+
+
+def gemm_grouped_bf16(a, b, c, blocks, epi: int = EPI_BF16, bn: int = 0):
+    """Grouped (MoE) GEMM: ``a`` ``[rows][K]`` expert-sorted rows, ``b`` ``[E][N][K]``; ``blocks`` is
+    ``(blk_expert, blk_row0, blk_rows, n_blk, max_blk)`` device tables of 128-row blocks."""
+    e, n, k = b.shape
+    _launch(a, b, c, a.shape[0], n, k, c.stride(0), False, epi, blocks=blocks, n_experts=e, bn=bn)
+
+
+def dequant_w4b(w4b: torch.Tensor, n: int, k: int, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """W4B -> bf16 ``[n][k]`` with ``bf16_rne((q - 8) * scale)``."""
+    if out is None:
+        out = torch.empty(n, k, dtype=torch.bfloat16, device=w4b.device)
+    rc = K.lib().b2_dequant_w4b(K._p(w4b), K._p(out), n, k, K._stream())
+    K._check(rc, "dequant_w4b")
+    return out
+
+
+def quant_rows_i8(x: torch.Tensor, q: Optional[torch.Tensor] = None, scale: Optional[torch.Tensor] = None):
+    """Per-token symmetric int8: ``scale[m] = max|x[m]| / 127``."""
+    m, k = x.shape
+    if q is None:
+        q = torch.empty(m, k, dtype=torch.int8, device=x.device)
+    if scale is None:
+        scale = torch.empty(m, dtype=torch.float32, device=x.device)
+    rc = K.lib().b2_quant_rows_i8(K._p(x), K._p(q), K._p(scale), m, k, K._stream())
+    K._check(rc, "quant_rows_i8")
+    return q, scale

@@ -1,0 +1,59 @@
+"""Small decode workload for kernel profiling: a few layers of a named shape at a given depth.
+
+    python -m b200serve.utils.profile_decode --model dense-27b --layers 4 --depth 4096 --steps 3
+
+The KV cache is filled with random values up to ``depth`` (no prompt pass), so a
+capture sees only the decode-step kernels.  Runs eagerly (no CUDA graph) so every
+launch appears under its own name in a launch list.
+"""
+from __future__ import annotations
+
+import argparse
+from dataclasses import replace
+
+import torch
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--model", default="dense-27b")
+    ap.add_argument("--layers", type=int, default=4)
+    ap.add_argument("--depth", type=int, default=4096)
+    ap.add_argument("--steps", type=int, default=3)
+    ap.add_argument("--rows", type=int, default=1)
+    ap.add_argument("--kv-cache", default="bf16")
+    ap.add_argument("--graphs", action="store_true")
+    ap.add_argument("--time", action="store_true", help="print CUDA-event ms per step")
+    args = ap.parse_args()
+    from ..models.config import preset
+    from ..models.weights import random_weights
+    from ..runtime.engine import Engine, Row
+    from ..ops import lib as K
+    cfg = replace(preset(args.model), n_layers=args.layers)
+    w = random_weights(cfg, device="cuda", seed=0, exact=False)
+    eng = Engine(w, max_seqs=1, max_len=args.depth + 256, kv_dtype=args.kv_cache, use_graphs=args.graphs,
+                 nsplit_attn=max(4, min(64, args.depth // 128)))
+    if args.kv_cache == "bf16":
+        eng.kv.k.normal_(0, 0.5); eng.kv.v.normal_(0, 0.5)
+    eng._ensure_pages(0, args.depth)
+    eng.seq_len[0] = args.depth
+    m = args.rows
+    def step():
+        p = eng.seq_len[0]
+        return eng.forward_rows([Row(0, p + i, 17 + i) for i in range(m)], advance=False, read=False)
+    for _ in range(2):
+        step(); eng.truncate(0, args.depth)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step(); eng.truncate(0, args.depth)
+    e1.record()
+    torch.cuda.synchronize()
+    K.check_status()
+    if args.time:
+        print(f"ms_per_step {e0.elapsed_time(e1) / args.steps:.4f} layers {args.layers} rows {m}")
+
+
+if __name__ == "__main__":
+    main()

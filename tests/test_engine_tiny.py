@@ -23,7 +23,7 @@ def _to_cuda(w):
     def mv(o):
         if isinstance(o, torch.Tensor):
             return o.cuda()
-        if is_dataclass(o):
+        if is_dataclass(o) and not o.__dataclass_params__.frozen:
             c = copy.copy(o)
             for f in fields(o):
                 if not f.name.startswith("_"):
