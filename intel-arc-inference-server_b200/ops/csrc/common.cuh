@@ -64,27 +64,35 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
+// upper bound (ns) of one hardware-suspended poll; a completed phase wakes the thread at once
+constexpr uint32_t kSuspendHintNs = 20000;
 __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
-      : "r"(bar), "r"(parity)
+      : "r"(bar), "r"(parity), "r"(kSuspendHintNs)
       : "memory");
   return ok != 0;
 }
-// Bounded wait: gives up after kWaitNs of wall time (checked every 64 polls).
-constexpr uint64_t kWaitNs = 2000000000ull;  // 2 s
+// Bounded wait.  mbarrier.try_wait suspends the thread in hardware until the phase completes or a
+// short system time limit passes, so the loop is not a hot spin.  The bound is kept on the SM's own
+// cycle counter (%clock64 costs a few cycles; %globaltimer is a slow read that, taken on every
+// wait, delayed each wake-up by most of a microsecond) and is only consulted after 256 failed
+// polls: about 4e9 cycles, i.e. roughly two seconds at 2 GHz.
+constexpr long long kWaitCycles = 4000000000ll;
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, unsigned int code) {
-  if (mbar_try(bar, parity)) return true;
-  uint64_t t0 = globaltimer_ns();
+#pragma unroll 1
+  for (int i = 0; i < 256; ++i)
+    if (mbar_try(bar, parity)) return true;
+  const long long t0 = clock64();
   for (;;) {
 #pragma unroll 1
-    for (int i = 0; i < 64; ++i)
+    for (int i = 0; i < 256; ++i)
       if (mbar_try(bar, parity)) return true;
-    if (globaltimer_ns() - t0 > kWaitNs) {
+    if (clock64() - t0 > kWaitCycles) {
       record_error(code, (blockIdx.x << 8) | (threadIdx.x >> 5));
       return false;
     }

@@ -272,7 +272,7 @@ __global__ void __launch_bounds__(256) dequant_w4b_kernel(const uint8_t* __restr
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   const uint4 wv = *reinterpret_cast<const uint4*>(blk + warp * 512 + lane * 16);
   const __half* sc = reinterpret_cast<const __half*>(blk + 4096) + warp * 16;
-  const float s_lo = __half2float(sc[g]), s_hi = __half2float(sc[g + 8]);
+  const float s_lo = __half2float(sc[2 * g]), s_hi = __half2float(sc[2 * g + 1]);  // scales are stored as (g, g + 8) pairs
   const uint32_t wa[4] = {wv.x, wv.y, wv.z, wv.w};
 #pragma unroll
   for (int c = 0; c < 4; ++c) {

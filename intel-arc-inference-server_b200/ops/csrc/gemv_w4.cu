@@ -11,15 +11,19 @@
 // griddepcontrol.wait, so under programmatic dependent launch the weights of this
 // linear are already in flight while the previous kernel finishes.  Eight
 // consumer warps each own 16 output rows: they read their 16 bytes per lane,
-// expand nibbles to exact bf16 integers with two logic ops and one subtract, and
-// feed mma.m16n8k16 with the weights as the 16-row operand and up to 8 tokens as
-// the 8-column operand (tokens beyond 8 reuse the dequantised registers, so the
-// weights are read once for any M: weight-stationary).  Group scales are applied
-// in fp32 to the per-group partial sums.  Split-K slices are written separately
-// and summed by the consumer kernel in a fixed order: no atomics, bitwise
-// reproducible, and a row's result does not depend on M (the split count is a
-// function of N and K only) -- the reference's "property R"
-// (src/kernels/gemm_sm.cl:44-50).
+// expand nibbles to the exact bf16 integers 128 + q with one shift and one logic
+// op per pair, and feed mma.m16n8k16 with the weights as the 16-row operand and up
+// to 8 tokens as the 8-column operand (tokens beyond 8 reuse the expanded
+// registers, so the weights are read once for any M: weight-stationary).  The
+// zero point is folded in after the MMAs (sum x (q - 8) = sum x (128 + q) - 136
+// sum x, with the per-group sums of x made once while staging the activations)
+// and group scales are applied in fp32 to the per-group partial sums.  The inner
+// loop is bound by the integer pipe, so everything else is kept off it: explicit
+// 32-bit shared-memory addresses, vector loads of the B operand, paired scales.
+// Split-K slices are written separately and summed by the consumer kernel in a
+// fixed order: no atomics, bitwise reproducible, and a row's result does not
+// depend on M (the split count is a function of N and K only) -- the
+// reference's "property R" (src/kernels/gemm_sm.cl:44-50).
 #include "common.cuh"
 
 using namespace b2;
@@ -30,8 +34,10 @@ constexpr int kBlockBytes = 4352;
 constexpr int kG = 2;  // quantisation groups (W4B blocks) per ring stage
 constexpr int kStages = 8;
 constexpr int kStageBytes = kG * kBlockBytes;
+constexpr int kRingBytes = kStages * kStageBytes;
 constexpr int kConsumerThreads = 256;
 constexpr int kThreads = kConsumerThreads + 32;
+constexpr int kXBudget = 36 * 1024;  // bytes of staged activations per chunk
 
 struct GemvParams {
   const uint8_t* w;  // [nb][KG][4352]
@@ -41,29 +47,102 @@ struct GemvParams {
   int ldx, ldo;
   int x_mode, s_in;
   long long x_slice;  // elements between input slices (x_mode 1)
+  int rows;           // staged token rows (M rounded up to 1, 2, 4, 8, 16, 32, 64)
+  int xcg;            // groups of x staged at a time
 };
 
-template <int T>
-struct Cfg {
-  static constexpr int XC = 2048 / T;           // k elements of x staged at a time
-  static constexpr int XCG = XC / 64;           // groups per x chunk
-  static constexpr int ROWS = 8 * T;            // token rows (padded)
-  static constexpr int STRIDE_W = XC / 2 + 4;   // row stride in 32-bit words (+4: conflict-free B reads)
-  static constexpr int X_BYTES = ROWS * STRIDE_W * 4;
-  static constexpr int SMEM = kStages * kStageBytes + X_BYTES + 256 + 128;
-};
+__host__ __device__ inline int stride_words(int xcg) { return xcg * 32 + 4; }  // +4 words: conflict-free B reads
 
 __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
+__device__ __forceinline__ uint4 lds128(uint32_t a) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
+  return v;
+}
+__device__ __forceinline__ uint32_t lds32(uint32_t a) {
+  uint32_t v;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a));
+  return v;
+}
+__device__ __forceinline__ float2 lds64f(uint32_t a) {
+  float2 v;
+  asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(a));
+  return v;
+}
+__device__ __forceinline__ void sts32(uint32_t a, uint32_t v) {
+  asm volatile("st.shared.u32 [%0], %1;" ::"r"(a), "r"(v) : "memory");
+}
+
+// NG quantisation groups (64 k each, consecutive blocks of one ring stage) of one 16-row tile against
+// T token tiles.  The groups are worked on together and each keeps two accumulators (k16 steps 0, 2
+// and 1, 3), so 2 NG independent MMA chains are in flight instead of one chain of four.
+template <int T, int NG>
+__device__ __forceinline__ void group_mma(float (&acc)[T][4], uint32_t blk_addr, uint32_t w_off, uint32_t sc_off,
+                                          const uint32_t (&x_addr)[T], uint32_t gs_addr) {
+  constexpr uint32_t kMagic = 0x43004300u, kMask = 0x000F000Fu;
+  uint4 wv[NG];
+  uint32_t sc2[NG];
+#pragma unroll
+  for (int q = 0; q < NG; ++q) {
+    wv[q] = lds128(blk_addr + q * kBlockBytes + w_off);
+    sc2[q] = lds32(blk_addr + q * kBlockBytes + sc_off);  // scales of rows g and g + 8 (stored as a pair)
+  }
+  float ag[NG][2][T][4];
+#pragma unroll
+  for (int q = 0; q < NG; ++q)
+#pragma unroll
+    for (int c = 0; c < 2; ++c)
+#pragma unroll
+      for (int tt = 0; tt < T; ++tt) ag[q][c][tt][0] = ag[q][c][tt][1] = ag[q][c][tt][2] = ag[q][c][tt][3] = 0.f;
+#pragma unroll
+  for (int pr = 0; pr < 2; ++pr) {
+    uint4 xb[NG][T];
+#pragma unroll
+    for (int q = 0; q < NG; ++q)
+#pragma unroll
+      for (int tt = 0; tt < T; ++tt) xb[q][tt] = lds128(x_addr[tt] + q * 128 + pr * 16);
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+#pragma unroll
+      for (int q = 0; q < NG; ++q) {
+        const uint32_t w0 = pr ? wv[q].z : wv[q].x, w1 = pr ? wv[q].w : wv[q].y;
+        const uint32_t a0 = ((w0 >> (8 * h)) & kMask) | kMagic;
+        const uint32_t a1 = ((w1 >> (8 * h)) & kMask) | kMagic;
+        const uint32_t a2 = ((w0 >> (8 * h + 4)) & kMask) | kMagic;
+        const uint32_t a3 = ((w1 >> (8 * h + 4)) & kMask) | kMagic;
+#pragma unroll
+        for (int tt = 0; tt < T; ++tt) {
+          const uint32_t b0 = h ? xb[q][tt].z : xb[q][tt].x, b1 = h ? xb[q][tt].w : xb[q][tt].y;
+          mma_bf16_16816(ag[q][h][tt], a0, a1, a2, a3, b0, b1);
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int q = 0; q < NG; ++q) {
+    const __half2 sh = *reinterpret_cast<const __half2*>(&sc2[q]);
+    const float s_lo = __low2float(sh), s_hi = __high2float(sh);
+#pragma unroll
+    for (int tt = 0; tt < T; ++tt) {
+      const float2 sx = lds64f(gs_addr + q * 8 * T * 4 + tt * 32);  // sums of x for tokens 8 tt + 2t, + 1
+      acc[tt][0] = fmaf(s_lo, fmaf(-136.f, sx.x, ag[q][0][tt][0] + ag[q][1][tt][0]), acc[tt][0]);
+      acc[tt][1] = fmaf(s_lo, fmaf(-136.f, sx.y, ag[q][0][tt][1] + ag[q][1][tt][1]), acc[tt][1]);
+      acc[tt][2] = fmaf(s_hi, fmaf(-136.f, sx.x, ag[q][0][tt][2] + ag[q][1][tt][2]), acc[tt][2]);
+      acc[tt][3] = fmaf(s_hi, fmaf(-136.f, sx.y, ag[q][0][tt][3] + ag[q][1][tt][3]), acc[tt][3]);
+    }
+  }
+}
 
 template <int T>
 __global__ void __launch_bounds__(kThreads, (T <= 2 ? 2 : 1)) gemv_w4_kernel(const GemvParams p) {
-  using C = Cfg<T>;
   extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
-  uint8_t* ring = smem;
-  uint32_t* xs = reinterpret_cast<uint32_t*>(smem + kStages * kStageBytes);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes + C::X_BYTES);
-  const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + kStages);
+  const uint32_t smem0 = (smem_u32(smem_raw) + 127u) & ~127u;
+  const uint32_t ring = smem0;
+  const uint32_t bars = smem0 + kRingBytes;               // 16 mbarriers
+  const uint32_t gs0 = bars + 128;                        // float [xcg][8 T] group sums of x
+  const uint32_t xs0 = gs0 + ((p.xcg * 8 * T * 4 + 127) & ~127);  // bf16 rows, permuted per group
+  const uint32_t full0 = bars, empty0 = bars + 8 * kStages;
+  const int strideB = stride_words(p.xcg) * 4;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int nblk = blockIdx.x, split = blockIdx.y;
@@ -94,7 +173,7 @@ __global__ void __launch_bounds__(kThreads, (T <= 2 ? 2 : 1)) gemv_w4_kernel(con
         const int ng = min(kG, ngroups - i * kG);
         const uint32_t bytes = ng * kBlockBytes;
         mbar_expect_tx(full0 + 8 * s, bytes);
-        bulk_g2s(smem_u32(ring + s * kStageBytes), src + (size_t)i * kStageBytes, bytes, full0 + 8 * s);
+        bulk_g2s(ring + s * kStageBytes, src + (size_t)i * kStageBytes, bytes, full0 + 8 * s);
         issued = i + 1;
       }
       if (!ok) {
@@ -115,22 +194,31 @@ __global__ void __launch_bounds__(kThreads, (T <= 2 ? 2 : 1)) gemv_w4_kernel(con
   float acc[T][4];
 #pragma unroll
   for (int i = 0; i < T; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
-
-  const uint32_t kMagic = 0x43004300u, kMask = 0x000F000Fu;
-  const __nv_bfloat162 k136 = __floats2bfloat162_rn(136.f, 136.f);
   bool ok = true;
 
-  for (int c0 = 0; c0 < ngroups; c0 += C::XCG) {
-    const int cg = min(C::XCG, ngroups - c0);  // groups in this chunk
+  // per-thread constant offsets.  A token row beyond the staged rows aliases the last staged row:
+  // column j of the MMA result depends on token j alone, and columns of absent tokens are not stored.
+  const uint32_t w_off = warp * 512 + lane * 16;
+  const uint32_t sc_off = 4096 + (warp * 16 + 2 * g) * 2;
+  uint32_t x_row[T];
+#pragma unroll
+  for (int tt = 0; tt < T; ++tt) x_row[tt] = xs0 + min(tt * 8 + g, p.rows - 1) * strideB + t * 32;
+  const uint32_t gs_t = gs0 + 2 * t * 4;
+
+  const int xvec = p.xcg * 8;  // 16-byte vectors per staged row
+  for (int c0 = 0; c0 < ngroups; c0 += p.xcg) {
+    const int cg = min(p.xcg, ngroups - c0);  // groups in this chunk
     consumer_sync();
-    // ---- stage x[:, k0 : k0 + 64 cg] as bf16 rows
+    // ---- stage x[:, k0 : k0 + 64 cg] as bf16, permuted inside each group
     {
       const int k0 = (gbeg + c0) * 64;
-      const int nvec = cg * 8;  // 16-byte vectors per row
-      for (int v = tid; v < C::ROWS * C::XC / 8; v += kConsumerThreads) {
-        const int row = v / (C::XC / 8), col = v % (C::XC / 8);
+      const int nvec = cg * 8;
+      const int total = p.rows * xvec;  // a multiple of 8; lanes of a warp stay together in groups of 8
+      for (int v0 = 0; v0 < total; v0 += kConsumerThreads) {
+        const int v = v0 + tid;
+        const int row = v / xvec, col = v - row * xvec;
         uint4 val = make_uint4(0, 0, 0, 0);
-        if (row < p.M && col < nvec) {
+        if (v < total && row < p.M && col < nvec) {
           const int k = k0 + col * 8;
           if (p.x_mode == 0) {
             val = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p.x) + (size_t)row * p.ldx + k);
@@ -140,6 +228,7 @@ __global__ void __launch_bounds__(kThreads, (T <= 2 ? 2 : 1)) gemv_w4_kernel(con
             float gsum[8], usum[8];
 #pragma unroll
             for (int i = 0; i < 8; ++i) gsum[i] = usum[i] = 0.f;
+#pragma unroll 4
             for (int s = 0; s < p.s_in; ++s) {
               const float4* gp = reinterpret_cast<const float4*>(base + (size_t)s * p.x_slice);
               const float4 g0 = gp[0], g1 = gp[1], u0 = gp[4], u1 = gp[5];
@@ -154,63 +243,45 @@ __global__ void __launch_bounds__(kThreads, (T <= 2 ? 2 : 1)) gemv_w4_kernel(con
             val.w = pack_bf16(silu(gsum[6]) * usum[6], silu(gsum[7]) * usum[7]);
           }
         }
-        *reinterpret_cast<uint4*>(xs + row * C::STRIDE_W + col * 4) = val;
+        // Word (step, half, t) of a group is stored at t * 8 + step * 2 + half, so that lane (g, t) of
+        // the main loop reads its eight B-operand words of the group with two 16-byte loads.
+        float sum = bf16_lo(val.x) + bf16_hi(val.x) + bf16_lo(val.y) + bf16_hi(val.y) + bf16_lo(val.z) +
+                    bf16_hi(val.z) + bf16_lo(val.w) + bf16_hi(val.w);
+        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+        sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+        sum += __shfl_xor_sync(0xffffffffu, sum, 4);
+        if (v < total) {
+          const int step = (col & 7) >> 1, half = col & 1;
+          const uint32_t dst = xs0 + row * strideB + ((col >> 3) * 32 + step * 2 + half) * 4;
+          sts32(dst, val.x);
+          sts32(dst + 32, val.y);
+          sts32(dst + 64, val.z);
+          sts32(dst + 96, val.w);
+          // sum of the group's 64 activations as rounded to bf16: folds the zero point
+          if ((col & 7) == 0) asm volatile("st.shared.f32 [%0], %1;" ::"r"(gs0 + ((col >> 3) * 8 * T + row) * 4), "f"(sum) : "memory");
+        }
       }
     }
     consumer_sync();
 
-    // ---- consume the ring stages that cover this chunk
-    // (after a failed wait the warp skips the rest of its work but still meets the others at
-    //  the named barrier, so a lost copy costs one bounded wait and never a deadlock)
+    // ---- consume the ring stages that cover this chunk.  After a failed wait the warp skips the rest
+    // of its work but still meets the others at the named barrier, so a lost copy costs one bounded
+    // wait and never a deadlock.
     for (int gi = 0; gi < cg; gi += kG) {
       const int i = (c0 + gi) / kG;  // stage index since kernel start
       const int s = i % kStages;
       if (ok) ok = mbar_wait(full0 + 8 * s, (i / kStages) & 1, ERR_GEMV_FULL_WAIT);
       if (!ok) continue;
-      const uint8_t* st = ring + s * kStageBytes;
-      const int ng = min(kG, cg - gi);
+      const uint32_t st = ring + s * kStageBytes;
+      uint32_t xa[T];
 #pragma unroll
-      for (int q = 0; q < kG; ++q) {
-        if (q < ng) {
-          const uint8_t* blk = st + q * kBlockBytes;
-          const uint4 wv = *reinterpret_cast<const uint4*>(blk + warp * 512 + lane * 16);
-          const __half* sc = reinterpret_cast<const __half*>(blk + 4096) + warp * 16;
-          const float s_lo = __half2float(sc[g]), s_hi = __half2float(sc[g + 8]);
-          float ag[T][4];
+      for (int tt = 0; tt < T; ++tt) xa[tt] = x_row[tt] + gi * 128;
+      if (gi + 1 < cg) group_mma<T, (T <= 2 ? 2 : 1)>(acc, st, w_off, sc_off, xa, gs_t + gi * 8 * T * 4);
+      else group_mma<T, 1>(acc, st, w_off, sc_off, xa, gs_t + gi * 8 * T * 4);
+      if (T > 2 && gi + 1 < cg) {
 #pragma unroll
-          for (int i2 = 0; i2 < T; ++i2) ag[i2][0] = ag[i2][1] = ag[i2][2] = ag[i2][3] = 0.f;
-          const uint32_t* xrow = xs + g * C::STRIDE_W + (gi + q) * 32 + t;
-          const uint32_t wa[2][2] = {{wv.x, wv.y}, {wv.z, wv.w}};
-#pragma unroll
-          for (int pr = 0; pr < 2; ++pr) {
-#pragma unroll
-            for (int h = 0; h < 2; ++h) {
-              uint32_t a[4];
-              a[0] = ((wa[pr][0] >> (8 * h)) & kMask) | kMagic;
-              a[1] = ((wa[pr][1] >> (8 * h)) & kMask) | kMagic;
-              a[2] = ((wa[pr][0] >> (8 * h + 4)) & kMask) | kMagic;
-              a[3] = ((wa[pr][1] >> (8 * h + 4)) & kMask) | kMagic;
-#pragma unroll
-              for (int r = 0; r < 4; ++r) {
-                __nv_bfloat162 v = __hsub2(*reinterpret_cast<__nv_bfloat162*>(&a[r]), k136);
-                a[r] = *reinterpret_cast<uint32_t*>(&v);
-              }
-              const int step = 2 * pr + h;
-#pragma unroll
-              for (int tt = 0; tt < T; ++tt) {
-                const uint32_t* xr = xrow + tt * 8 * C::STRIDE_W + step * 8;
-                mma_bf16_16816(ag[tt], a[0], a[1], a[2], a[3], xr[0], xr[4]);
-              }
-            }
-          }
-#pragma unroll
-          for (int tt = 0; tt < T; ++tt) {
-            acc[tt][0] = fmaf(s_lo, ag[tt][0], acc[tt][0]);
-            acc[tt][1] = fmaf(s_lo, ag[tt][1], acc[tt][1]);
-            acc[tt][2] = fmaf(s_hi, ag[tt][2], acc[tt][2]);
-            acc[tt][3] = fmaf(s_hi, ag[tt][3], acc[tt][3]);
-          }
-        }
+        for (int tt = 0; tt < T; ++tt) xa[tt] += 128;
+        group_mma<T, 1>(acc, st + kBlockBytes, w_off, sc_off, xa, gs_t + (gi + 1) * 8 * T * 4);
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(empty0 + 8 * s);
@@ -235,17 +306,28 @@ __global__ void __launch_bounds__(kThreads, (T <= 2 ? 2 : 1)) gemv_w4_kernel(con
 }
 
 template <int T>
-int launch_t(const GemvParams& p, cudaStream_t stream) {
-  static bool configured[64] = {};
+int launch_t(GemvParams& p, cudaStream_t stream) {
+  // staged rows and chunk length: as much of the split's k range as fits the activation budget
+  int rows = 1;
+  while (rows < p.M) rows *= 2;
+  p.rows = rows;
+  int xcg = (kXBudget / (rows * 2) - 8) / 64;
+  xcg &= ~1;
+  if (xcg > p.gps) xcg = p.gps;
+  if (xcg < 2) xcg = 2;
+  p.xcg = xcg;
+  const int smem = 128 + kRingBytes + 128 + ((xcg * 8 * T * 4 + 127) & ~127) + rows * stride_words(xcg) * 4;
+  static int configured[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
-  if (!configured[dev & 63]) {
-    cudaError_t e = cudaFuncSetAttribute(gemv_w4_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<T>::SMEM);
+  if (configured[dev & 63] < smem) {
+    const int want = 128 + kRingBytes + 128 + 8192 + kXBudget + 4096;
+    cudaError_t e = cudaFuncSetAttribute(gemv_w4_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, want);
     if (e != cudaSuccess) return (int)e;
-    configured[dev & 63] = true;
+    configured[dev & 63] = want;
   }
   dim3 grid((p.N + 127) / 128, p.S);
-  return b2_launch(gemv_w4_kernel<T>, grid, dim3(kThreads), Cfg<T>::SMEM, stream, true, p);
+  return b2_launch(gemv_w4_kernel<T>, grid, dim3(kThreads), smem, stream, true, p);
 }
 
 }  // namespace

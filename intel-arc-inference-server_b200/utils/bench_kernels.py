@@ -42,10 +42,12 @@ def time_ms(fn, iters=20, warmup=3):
     return e0.elapsed_time(e1) / iters
 
 
-def bench_gemv(ms_list=(1, 4, 8, 16, 64)):
+def bench_gemv(ms_list=(1, 4, 8, 16, 64), only=None, iters_mult=4):
     hbm, _, src = peaks()
     shapes = [("qkv", 7168, 5120), ("o", 5120, 5120), ("gate_up", 34816, 5120), ("down", 5120, 17408)]
     for name, n, k in shapes:
+        if only and name != only:
+            continue
         nbytes = (n // 128) * (k // 64) * Q.BLOCK_BYTES
         copies = max(2, int(400e6 // nbytes) + 1)
         ws = [Q.random_w4b(n, k, "cuda", i) for i in range(copies)]
@@ -58,7 +60,7 @@ def bench_gemv(ms_list=(1, 4, 8, 16, 64)):
             def fn():
                 K.gemv_w4(ws[it[0] % copies], x, out, m, n, k, s)
                 it[0] += 1
-            ms = time_ms(fn, iters=4 * copies)
+            ms = time_ms(fn, iters=max(2, iters_mult * copies))
             gbs = nbytes / ms / 1e6
             print(f"gemv_w4 {name:8s} N={n:6d} K={k:6d} M={m:3d} S={s:2d}  {ms * 1e3:8.2f} us  {gbs:8.1f} GB/s  "
                   f"{gbs / hbm:5.2f} of {src} HBM copy bandwidth")
@@ -96,4 +98,7 @@ def bench_gemm():
 
 if __name__ == "__main__":
     what = sys.argv[1] if len(sys.argv) > 1 else "gemv"
-    {"gemv": bench_gemv, "gemm": bench_gemm}[what]()
+    if what == "gemv-one":      # one shape, one M, few launches: the target of an ncu capture
+        bench_gemv((int(sys.argv[3]),), only=sys.argv[2], iters_mult=1)
+    else:
+        {"gemv": bench_gemv, "gemm": bench_gemm}[what]()

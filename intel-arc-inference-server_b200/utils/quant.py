@@ -19,7 +19,9 @@ ordered for a warp-level ``mma.m16n8k16`` A operand: tile ``j`` (16 rows) owns
 steps ``s0 = 2 (c >> 1)``, ``s1 = s0 + 1`` of the group.  Nibble positions
 ``0,4,1,5,2,6,3,7`` hold ``k = 16 s0 + 2t``, ``+1``, ``+8``, ``+9``, then the
 same four for ``s1``; a mask with ``0x000F000F`` after shifts by 0/4/8/12 then
-yields the four bf16x2 operand registers directly.
+yields the four bf16x2 operand registers directly.  The 16 scales of a tile are
+stored as pairs ``(row g, row g + 8)`` so a lane reads its two scales as one
+32-bit word: position ``2 (r % 8) + r / 8`` holds the scale of tile row ``r``.
 """
 from __future__ import annotations
 
@@ -91,6 +93,13 @@ _NIB_STEP = (0, 0, 1, 1, 0, 0, 1, 1)     # which step (s0 / s1) nibble p belongs
 _NIB_KOFF = (0, 8, 0, 8, 1, 9, 1, 9)     # k offset inside the step, plus 2t
 
 
+def _scale_perm(device):
+    """``perm[pos]`` = row (0..127) of the block whose scale is stored at position ``pos``."""
+    pos = torch.arange(BLOCK_N, device=device)
+    j, p_ = pos // 16, pos % 16
+    return j * 16 + (p_ // 2) + 8 * (p_ % 2)
+
+
 def to_w4b(q: torch.Tensor, scales: torch.Tensor) -> torch.Tensor:
     """Repack ``q`` ``[K][N]``, ``scales`` ``[K/64][N]`` into W4B bytes.
 
@@ -122,7 +131,7 @@ def to_w4b(q: torch.Tensor, scales: torch.Tensor) -> torch.Tensor:
     hi = nibs[..., 4] | (nibs[..., 5] << 4) | (nibs[..., 6] << 8) | (nibs[..., 7] << 12)
     wb = torch.stack([lo & 0xFF, lo >> 8, hi & 0xFF, hi >> 8], dim=-1).to(torch.uint8)
     wb = wb.reshape(nb, kg, BLOCK_W_BYTES)
-    sb = scales.reshape(kg, nb, BLOCK_N).permute(1, 0, 2).contiguous().view(torch.uint8)
+    sb = scales.reshape(kg, nb, BLOCK_N).permute(1, 0, 2)[..., _scale_perm(dev)].contiguous().view(torch.uint8)
     sb = sb.reshape(nb, kg, BLOCK_N * 2)
     return torch.cat([wb, sb], dim=-1).contiguous()
 
@@ -148,6 +157,7 @@ def from_w4b(w4b: torch.Tensor, n: int):
     qb[:, :, kk, row] = nibs.reshape(nb, kg, -1).to(torch.uint8)
     q = qb.permute(1, 2, 0, 3).reshape(kg * GROUP, nb * BLOCK_N)[:, :n].contiguous()
     sb = w4b[..., BLOCK_W_BYTES:].contiguous().view(torch.float16).reshape(nb, kg, BLOCK_N)
+    sb = sb[..., torch.argsort(_scale_perm(dev))]
     scales = sb.permute(1, 0, 2).reshape(kg, nb * BLOCK_N)[:, :n].contiguous()
     return q, scales
 
@@ -171,7 +181,7 @@ def random_w4b(n: int, k: int, device, seed: int, std: float = 0.02) -> torch.Te
     if npad != n:
         # padded rows: zero their scales
         sc = out[..., BLOCK_W_BYTES:].view(torch.float16).reshape(nb, kg, BLOCK_N)
-        rows = torch.arange(npad, device=device).reshape(nb, 1, BLOCK_N)
+        rows = (torch.arange(nb, device=device)[:, None] * BLOCK_N + _scale_perm(device)[None, :]).reshape(nb, 1, BLOCK_N)
         sc.masked_fill_(rows >= n, 0.0)
     return out
 
