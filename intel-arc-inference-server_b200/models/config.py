@@ -158,6 +158,11 @@ def tiny_dense() -> ModelConfig:
     return ModelConfig("tiny-dense", 2, 256, 4, 2, 64, 704, 1024)
 
 
+def small_dense() -> ModelConfig:
+    """Small dense model with the production head size (128), for the tensor-core prefill path."""
+    return ModelConfig("small-dense", 2, 512, 8, 2, 128, 1408, 2048)
+
+
 def tiny_moe() -> ModelConfig:
     return ModelConfig("tiny-moe", 2, 256, 4, 2, 64, 0, 1024, n_experts=8, top_k=2,
                        expert_ffn=128, shared_ffn=128, architecture="B200MoeForCausalLM")
@@ -182,7 +187,7 @@ def dflash_drafter(target: ModelConfig) -> ModelConfig:
 
 
 PRESETS = {
-    "tiny-dense": tiny_dense, "tiny-moe": tiny_moe, "dense-27b": dense_27b, "moe-35b-a3b": moe_35b_a3b,
+    "tiny-dense": tiny_dense, "tiny-moe": tiny_moe, "small-dense": small_dense, "dense-27b": dense_27b, "moe-35b-a3b": moe_35b_a3b,
 }
 
 

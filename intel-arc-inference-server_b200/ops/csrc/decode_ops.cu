@@ -132,13 +132,14 @@ struct RopeParams {
   float* k_scale;
   float* v_scale;
   int kv_int8;
+  int req, pos0;  // used when ctrl == nullptr: row m of request `req` sits at position pos0 + m
 };
 
 __global__ void __launch_bounds__(256) rope_append_kernel(const RopeParams p) {
   pdl_wait();
   pdl_launch_dependents();
   const int m = blockIdx.x;
-  const int req = p.ctrl[CTRL_ROW_REQ + m], pos = p.ctrl[CTRL_ROW_POS + m];
+  const int req = p.ctrl ? p.ctrl[CTRL_ROW_REQ + m] : p.req, pos = p.ctrl ? p.ctrl[CTRL_ROW_POS + m] : p.pos0 + m;
   const int D = p.D, Dh = D >> 1;
   const int q_dim = p.n_q * D, kv_dim = p.n_kv * D, ld = q_dim + 2 * kv_dim;
   const float* row = p.qkv + (size_t)m * ld;
@@ -571,11 +572,11 @@ extern "C" int b2_resid_norm(const void* embed, const int* ctrl, const void* res
 extern "C" int b2_rope_append(const float* qkv, long long slice, int S, int M, const int* ctrl, const int* block_table,
                               int max_blocks, const float* cos_t, const float* sin_t, int n_q, int n_kv, int D,
                               void* q_out, void* k_cache, void* v_cache, float* k_scale, float* v_scale, int kv_int8,
-                              void* stream) {
+                              int req, int pos0, void* stream) {
   RopeParams p;
   p.qkv = qkv; p.slice = slice; p.S = S; p.ctrl = ctrl; p.block_table = block_table; p.max_blocks = max_blocks;
   p.cos_t = cos_t; p.sin_t = sin_t; p.n_q = n_q; p.n_kv = n_kv; p.D = D; p.q_out = (__nv_bfloat16*)q_out;
-  p.k_cache = k_cache; p.v_cache = v_cache; p.k_scale = k_scale; p.v_scale = v_scale; p.kv_int8 = kv_int8;
+  p.k_cache = k_cache; p.v_cache = v_cache; p.k_scale = k_scale; p.v_scale = v_scale; p.kv_int8 = kv_int8; p.req = req; p.pos0 = pos0;
   if (D % 64 || D > 256) return -1;
   const int items = (n_q + n_kv) * (D / 2) + n_kv * D / 2;
   int gy = kv_int8 ? max((n_q * D / 2 + 255) / 256, (2 * n_kv + 7) / 8) : (items + 255) / 256;

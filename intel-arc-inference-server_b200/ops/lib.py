@@ -130,10 +130,11 @@ def resid_norm(mode: int, m: int, h: int, w: torch.Tensor, eps: float, resid_out
 
 
 def rope_append(qkv_part, slice_elems, splits, m, ctrl, block_table, max_blocks, cos_t, sin_t, n_q, n_kv, d, q_out,
-                k_cache, v_cache, k_scale=None, v_scale=None, kv_int8=False):
+                k_cache, v_cache, k_scale=None, v_scale=None, kv_int8=False, req=0, pos0=0):
+    """With ``ctrl`` None the ``m`` rows are consecutive positions ``pos0..`` of request ``req`` (prompt chunks)."""
     rc = lib().b2_rope_append(_p(qkv_part), ctypes.c_longlong(slice_elems), splits, m, _p(ctrl), _p(block_table),
                               max_blocks, _p(cos_t), _p(sin_t), n_q, n_kv, d, _p(q_out), _p(k_cache), _p(v_cache),
-                              _p(k_scale), _p(v_scale), int(kv_int8), _stream())
+                              _p(k_scale), _p(v_scale), int(kv_int8), req, pos0, _stream())
     _check(rc, "rope_append")
 
 
@@ -162,3 +163,10 @@ def head_gemv(w, x, out, m, n, k, cand_val=None, cand_idx=None, n_valid=None, ws
 def argmax_finish(cand_val, cand_idx, ncand, m, ctrl, advance: bool):
     rc = lib().b2_argmax_finish(_p(cand_val), _p(cand_idx), ncand, m, _p(ctrl), int(advance), _stream())
     _check(rc, "argmax_finish")
+
+
+def attn_prefill(q, k_cache, v_cache, block_table_row, out, c, pos0, n_q, n_kv, d, num_pages, max_blocks, scale):
+    """Causal flash attention of a prompt chunk (``c`` rows at positions ``pos0..``) over the paged bf16 cache."""
+    rc = lib().b2_attn_prefill(_p(q), _p(k_cache), _p(v_cache), _p(block_table_row), _p(out), c, pos0, n_q, n_kv, d,
+                               num_pages, max_blocks, ctypes.c_float(scale), _stream())
+    _check(rc, "attn_prefill")

@@ -36,7 +36,7 @@ class Row:
 class Engine:
     def __init__(self, weights: ModelWeights, max_seqs: int = 1, max_len: int = 4096, kv_dtype: str = "bf16",
                  max_rows: int = 64, use_graphs: bool = True, int8_head: bool = False, num_pages: Optional[int] = None,
-                 nsplit_attn: int = 32, prefill_backend: str = "rows"):
+                 nsplit_attn: int = 32, prefill_backend: str = "auto"):
         self.cfg = cfg = weights.cfg
         self.device = weights.embed.device
         self.max_seqs, self.max_len, self.max_rows = max_seqs, max_len, max_rows
@@ -143,7 +143,7 @@ class Engine:
     def prefill(self, slot: int, ids: Sequence[int], chunk: Optional[int] = None) -> int:
         """Ingest ``ids`` after the slot's current length; returns the greedy next token."""
         ids = list(ids)
-        if self.prefill_backend != "rows" and len(ids) > self.max_rows:
+        if self._use_tc_prefill(len(ids)):
             from .prefill import PrefillRunner
             if self._prefill is None:
                 self._prefill = PrefillRunner(self)
@@ -156,6 +156,16 @@ class Engine:
             last = c0 + self.max_rows >= len(ids)
             out = self.forward_rows(rows, advance=False, read=last)
         return out[-1]
+
+    def _use_tc_prefill(self, n: int) -> bool:
+        """Prompt chunks longer than the row kernels take go through the tcgen05 path when the shape
+        has one (head size 128, bf16 KV, dense FFN or MoE with a grouped path)."""
+        if self.prefill_backend == "rows" or n <= self.max_rows:
+            return False
+        ok = self.cfg.head_dim == 128 and not self.kv.kv_int8
+        if not ok and self.prefill_backend != "auto":
+            raise ValueError(f"prefill backend {self.prefill_backend!r} needs head_dim 128 and a bf16 KV cache")
+        return ok
 
     def decode_begin(self, slots: Sequence[int], tokens: Sequence[int]):
         """Arm plain decode: one row per slot, starting with ``tokens`` at each slot's current length."""

@@ -1,0 +1,138 @@
+"""Chunked prompt pass on the tensor cores.
+
+The role of the reference's prefill walk (src/runtime/prefill/step.cc:102-319,
+engine_prefill.cc:159-322): the prompt is cut in chunks, each chunk walks the
+layers once with GEMM-shaped kernels, nothing waits on the host inside a chunk.
+Per layer: RMSNorm rows -> qkv GEMM (fp32 out) -> RoPE + paged KV append ->
+causal flash attention over the page pool -> o GEMM with the residual add in its
+epilogue -> RMSNorm -> gate‖up GEMM with SiLU*up in its epilogue -> down GEMM
+with the residual add.  Only the last row of the last chunk goes through the head.
+
+Weight forms for the GEMMs:
+  ``bf16``      W4B is dequantised to a bf16 slab right before each GEMM (two-pass, as the
+                reference's pf_dequant_slab + pf_gemm) -- no second resident copy of the model;
+  ``bf16-resident``  the dequantised matrices stay in HBM (a 27B model is 42 GB of the 180 GB);
+  ``int8``      per-token int8 activations x per-row int8 weights on kind::i8, scales in the epilogue
+                (the reference's ``--prefill-backend l0-int8``, docs/16-int8-prefill.md).
+"""
+from __future__ import annotations
+
+from typing import List, Optional
+
+import torch
+
+from ..models.weights import QLinear
+from ..ops import gemm as G
+from ..ops import lib as K
+
+
+class PrefillRunner:
+    def __init__(self, engine, max_chunk: int = 4096):
+        self.eng = engine
+        self.cfg = cfg = engine.cfg
+        self.dev = engine.device
+        self.max_chunk = max_chunk
+        self.backend = engine.prefill_backend
+        if self.backend in ("auto", "l0"):
+            self.backend = "bf16"
+        if self.backend == "l0-int8":
+            self.backend = "int8"
+        bf, f32 = torch.bfloat16, torch.float32
+        c, h = max_chunk, cfg.hidden
+        self.resid = torch.empty(c, h, dtype=bf, device=self.dev)
+        self.x = torch.empty(c, h, dtype=bf, device=self.dev)
+        self.qkv = torch.empty(c, cfg.qkv_dim, dtype=f32, device=self.dev)
+        self.q = torch.empty(c, cfg.q_dim, dtype=bf, device=self.dev)
+        self.attn = torch.empty(c, cfg.q_dim, dtype=bf, device=self.dev)
+        ffn = cfg.ffn if not cfg.is_moe else max(cfg.expert_ffn, cfg.shared_ffn)
+        self.act = torch.empty(c, max(ffn, 1), dtype=bf, device=self.dev)
+        self.ids_host = torch.empty(max_chunk, dtype=torch.int64).pin_memory()
+        self.ids_dev = torch.empty(max_chunk, dtype=torch.int64, device=self.dev)
+        self._slab: Optional[torch.Tensor] = None
+        if self.backend == "int8":
+            kmax = max(h, cfg.q_dim, ffn)
+            self.a8 = torch.empty(c, kmax, dtype=torch.int8, device=self.dev)
+            self.a_scale = torch.empty(c, dtype=f32, device=self.dev)
+
+    # ------------------------------------------------------------------ weights
+    def _w_bf16(self, ql: QLinear) -> torch.Tensor:
+        if ql._w_bf16 is not None:
+            return ql._w_bf16
+        if self.backend == "bf16-resident":
+            ql._w_bf16 = G.dequant_w4b(ql.w4b, ql.n, ql.k)
+            return ql._w_bf16
+        need = ql.n * ql.k
+        if self._slab is None or self._slab.numel() < need:
+            self._slab = torch.empty(need, dtype=torch.bfloat16, device=self.dev)
+        out = self._slab[:need].view(ql.n, ql.k)
+        return G.dequant_w4b(ql.w4b, ql.n, ql.k, out)
+
+    def _w_i8(self, ql: QLinear):
+        if ql._w_i8 is None:
+            w = G.dequant_w4b(ql.w4b, ql.n, ql.k).float()
+            sc = w.abs().amax(dim=1).clamp_min(1e-12) / 127.0
+            ql._w_i8 = (torch.round(w / sc[:, None]).clamp_(-127, 127).to(torch.int8).contiguous(), sc.contiguous())
+            del w
+        return ql._w_i8
+
+    def linear(self, ql: QLinear, a: torch.Tensor, out: torch.Tensor, epi: int, resid=None):
+        """``out = epilogue(a @ W^T)`` for ``a`` ``[rows][k]`` bf16."""
+        if self.backend == "int8":
+            rows = a.shape[0]
+            a8 = self.a8[:rows, : ql.k] if self.a8.shape[1] == ql.k else self.a8.view(-1)[: rows * ql.k].view(rows, ql.k)
+            G.quant_rows_i8(a, a8, self.a_scale[:rows])
+            w8, ws = self._w_i8(ql)
+            G.gemm_i8(a8, w8, self.a_scale[:rows], ws, out, epi=epi, resid=resid)
+        else:
+            G.gemm_bf16(a, self._w_bf16(ql), out, epi=epi, resid=resid)
+
+    # ------------------------------------------------------------------ one chunk
+    def chunk(self, slot: int, ids: List[int], pos0: int):
+        eng, cfg, m = self.eng, self.cfg, self.eng.model
+        c, h = len(ids), cfg.hidden
+        eng._ensure_pages(slot, pos0 + c)
+        self.ids_host[:c] = torch.as_tensor(ids, dtype=torch.int64)
+        self.ids_dev[:c].copy_(self.ids_host[:c], non_blocking=True)
+        resid, x = self.resid[:c], self.x[:c]
+        torch.index_select(m.w.embed, 0, self.ids_dev[:c], out=resid)
+        bt_row = eng.block_table[slot]
+        for li, lw in enumerate(m.w.layers):
+            kc, vc, ks, vs = eng.kv.layer(li)
+            K.resid_norm(1, c, h, lw.input_norm, cfg.rms_eps, resid, x, resid_in=resid, splits=0)
+            qkv = self.qkv[:c]
+            self.linear(lw.qkv, x, qkv, G.EPI_F32)
+            K.rope_append(qkv, 0, 1, c, None, eng.block_table, eng.max_blocks, m.cos_t, m.sin_t, cfg.n_q_heads,
+                          cfg.n_kv_heads, cfg.head_dim, self.q, kc, vc, ks, vs, eng.kv.kv_int8, req=slot, pos0=pos0)
+            K.attn_prefill(self.q, kc, vc, bt_row, self.attn, c, pos0, cfg.n_q_heads, cfg.n_kv_heads, cfg.head_dim,
+                           eng.kv.num_pages, eng.max_blocks, m.scale)
+            self.linear(lw.o, self.attn[:c], resid, G.EPI_RESID_ADD, resid=resid)
+            K.resid_norm(1, c, h, lw.post_norm, cfg.rms_eps, resid, x, resid_in=resid, splits=0)
+            if lw.gate_up is not None:
+                act = self.act[:c, : cfg.ffn]
+                self.linear(lw.gate_up, x, act, G.EPI_SILU_MUL)
+                self.linear(lw.down, act, resid, G.EPI_RESID_ADD, resid=resid)
+            else:
+                from ..models import moe as _moe
+                _moe.moe_block_prefill(self, lw, c)
+        eng.seq_len[slot] = max(eng.seq_len[slot], pos0 + c)
+        return resid
+
+    def run(self, slot: int, ids: List[int], chunk: Optional[int] = None) -> int:
+        eng, cfg, m = self.eng, self.cfg, self.eng.model
+        chunk = min(chunk or self.max_chunk, self.max_chunk)
+        start = eng.seq_len[slot]
+        resid = None
+        n = len(ids)
+        for c0 in range(0, n, chunk):
+            resid = self.chunk(slot, ids[c0: c0 + chunk], start + c0)
+        last = (n - 1) % chunk
+        b = m.buf
+        b.resid[0].copy_(resid[last])
+        K.resid_norm(1, 1, cfg.hidden, m.w.final_norm, cfg.rms_eps, b.resid, b.x, resid_in=b.resid, splits=0)
+        if m.int8_head:
+            w8, sc = m.w.lm_head_i8
+            K.head_gemv(w8, b.x, b.logits, 1, cfg.vocab, cfg.hidden, b.cand_val, b.cand_idx, wscale=sc)
+        else:
+            K.head_gemv(m.w.lm_head, b.x, b.logits, 1, cfg.vocab, cfg.hidden, b.cand_val, b.cand_idx)
+        K.argmax_finish(b.cand_val, b.cand_idx, b.ncand, 1, eng.ctrl, False)
+        return eng._read_out(1)[0]

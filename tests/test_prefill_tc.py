@@ -1,0 +1,81 @@
+"""Tensor-core prompt pass: flash attention over the page pool and the chunked prefill runner (GPU)."""
+import math
+
+import pytest
+import torch
+
+from b200serve.models.config import small_dense
+from b200serve.models.oracle import OracleModel, OracleKV, argmax_low_tie
+from b200serve.models.weights import random_weights
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("c,pos0,n_q,n_kv", [(128, 0, 2, 1), (300, 0, 8, 2), (200, 150, 4, 4), (77, 1000, 5, 1)])
+def test_attn_prefill_matches_softmax(c, pos0, n_q, n_kv):
+    from b200serve.ops import lib as K
+    torch.manual_seed(c + pos0)
+    d = 128
+    total = pos0 + c
+    max_blocks = (total + 15) // 16 + 3
+    num_pages = max_blocks + 8
+    perm = torch.randperm(num_pages - 1)[:max_blocks] + 1
+    table = perm.to(torch.int32).cuda()
+    kc = torch.zeros(num_pages, n_kv, 16, d, dtype=torch.bfloat16, device="cuda")
+    vc = torch.zeros_like(kc)
+    k = torch.randn(total, n_kv, d).to(torch.bfloat16)
+    v = torch.randn(total, n_kv, d).to(torch.bfloat16)
+    for p in range(total):
+        kc[perm[p // 16], :, p % 16] = k[p].cuda()
+        vc[perm[p // 16], :, p % 16] = v[p].cuda()
+    q = torch.randn(c, n_q, d).to(torch.bfloat16)
+    out = torch.full((c, n_q * d), float("nan"), dtype=torch.bfloat16, device="cuda")
+    K.attn_prefill(q.reshape(c, -1).cuda(), kc, vc, table, out, c, pos0, n_q, n_kv, d, num_pages, max_blocks,
+                   1.0 / math.sqrt(d))
+    torch.cuda.synchronize()
+    K.check_status()
+    g = n_q // n_kv
+    kk, vv = k.float().repeat_interleave(g, 1), v.float().repeat_interleave(g, 1)
+    sc = torch.einsum("rhd,shd->hrs", q.float(), kk) / math.sqrt(d)
+    qpos = pos0 + torch.arange(c)
+    sc = sc.masked_fill((torch.arange(total)[None, :] > qpos[:, None])[None], float("-inf"))
+    ref = torch.einsum("hrs,shd->rhd", torch.softmax(sc, -1), vv).reshape(c, -1)
+    got = out.float().cpu()
+    assert torch.isfinite(got).all()
+    assert (got - ref).abs().max() < 0.02 * ref.abs().max() + 2e-3
+
+
+@pytest.mark.parametrize("backend", ["bf16", "bf16-resident", "int8"])
+def test_prefill_runner_matches_oracle(backend):
+    from b200serve.runtime.engine import Engine
+    from b200serve.ops import lib as K
+    cfg = small_dense()
+    w = random_weights(cfg, seed=3)
+    oracle = OracleModel(w)
+    g = torch.Generator().manual_seed(5)
+    prompt = torch.randint(0, cfg.vocab, (333,), generator=g)
+    wc = random_weights(cfg, device="cuda", seed=3)
+    eng = Engine(wc, max_seqs=2, max_len=1024, prefill_backend=backend, nsplit_attn=4)
+    first = eng.prefill(1, prompt.tolist(), chunk=200)          # two chunks: 200 + 133
+    K.check_status()
+    assert eng._prefill is not None
+    ref_logits = oracle.forward(prompt)[-1]
+    got = eng.logits(1)[0].float().cpu()
+    tol = 0.08 if backend == "int8" else 0.03
+    assert (got - ref_logits).abs().max() < tol * ref_logits.abs().max()
+    want = int(argmax_low_tie(ref_logits[None])[0])
+    if first != want:
+        assert float(ref_logits[want] - ref_logits[first]) < (0.1 if backend == "int8" else 0.03)
+    # decode continues from the prefilled cache; judged against the teacher-forced oracle with the
+    # undetermined-row rule (a near-tie may go either way)
+    eng.decode_begin([1], [first])
+    toks = [first] + [eng.decode_step()[0] for _ in range(6)]
+    K.check_status()
+    kv = OracleKV(cfg)
+    logits = oracle.forward(prompt, kv, 0)[-1]
+    margin = 0.12 if backend == "int8" else 0.04
+    for i, t in enumerate(toks):
+        want = int(argmax_low_tie(logits[None])[0])
+        if t != want:
+            assert float(logits[want] - logits[t]) < margin, (i, t, want)
+        logits = oracle.forward(torch.tensor([t]), kv, len(prompt) + i)[0]
