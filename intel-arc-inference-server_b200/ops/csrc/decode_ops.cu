@@ -650,4 +650,54 @@ extern "C" int b2_argmax_finish(const float* cand_val, const int* cand_idx, int 
                    ctrl, advance);
 }
 
+// ------------------------------------------------------------------ allocation-free decode attention
+// b2_attn_decode_static: the same two kernels as b2_attn_decode, with the split-KV partials kept in a
+// fixed device array that is part of this library's image instead of a buffer the caller allocates.
+// See b200serve_noalloc.h for who needs this and for the limits.
+namespace {
+constexpr int kStaticMaxRows = 4, kStaticMaxHeads = 64, kStaticMaxSplit = 16, kStaticMaxD = 128;
+constexpr size_t kStaticOFloats = (size_t)kStaticMaxRows * kStaticMaxHeads * kStaticMaxSplit * kStaticMaxD;
+constexpr size_t kStaticMlFloats = (size_t)kStaticMaxRows * kStaticMaxHeads * kStaticMaxSplit * 2;
+// 2 MiB + 32 KiB, resident on every GPU that loads the library until the process exits
+static __device__ __align__(256) float g_static_attn_scratch[kStaticOFloats + kStaticMlFloats];
+static float* g_static_attn_ptr[64] = {};  // per device: the array's DEVICE address (the symbol itself is a host-side stand-in)
+}  // namespace
+
+extern "C" int b2_attn_decode_static(const void* q, const void* k_cache, const void* v_cache, const float* k_scale,
+                                     const float* v_scale, const int* block_table, const int* ctrl, void* out, int M,
+                                     int n_q, int n_kv, int D, int nsplit, int max_blocks, float scale, int kv_int8,
+                                     void* stream) {
+  if (M < 1 || M > kStaticMaxRows || n_q < 1 || n_q > kStaticMaxHeads || nsplit < 1 || nsplit > kStaticMaxSplit ||
+      (D != 64 && D != 128) || n_kv < 1 || n_q % n_kv != 0)
+    return -10;  // beyond the fixed scratch: use b2_attn_decode with caller-owned buffers
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= 64) return -11;
+  if (!g_static_attn_ptr[dev]) {
+    // first call on this device: resolve the array's device address (no allocation takes place)
+    void* ptr = nullptr;
+    e = cudaGetSymbolAddress(&ptr, g_static_attn_scratch);
+    if (e != cudaSuccess) return (int)e;
+    g_static_attn_ptr[dev] = static_cast<float*>(ptr);
+  }
+  float* o_part = g_static_attn_ptr[dev];
+  float* ml_part = o_part + kStaticOFloats;
+  // Nothing has to start at zero: every (row, head, split) entry that the merge reads is written by
+  // the split kernel of the same call, empty splits included (they write m = -inf, l = 0).
+  AttnDecParams p;
+  p.q = (const __nv_bfloat16*)q; p.k_cache = k_cache; p.v_cache = v_cache; p.k_scale = k_scale; p.v_scale = v_scale;
+  p.block_table = block_table; p.ctrl = ctrl; p.o_part = o_part; p.ml_part = ml_part;
+  p.n_q = n_q; p.n_kv = n_kv; p.nsplit = nsplit; p.max_blocks = max_blocks;
+  p.scale_log2 = scale * 1.4426950408889634f; p.kv_int8 = kv_int8;
+  dim3 grid(n_kv, nsplit, M);
+  cudaStream_t st = (cudaStream_t)stream;
+  int rc;
+  if (D == 128) rc = attn_decode_dispatch<128>(n_q / n_kv, p, grid, st);
+  else rc = attn_decode_dispatch<64>(n_q / n_kv, p, grid, st);
+  if (rc) return rc;
+  return b2_launch(attn_merge_kernel, dim3(n_q, M), dim3(D), 0, st, true, (const float*)o_part, (const float*)ml_part,
+                   (__nv_bfloat16*)out, n_q, nsplit, D);
+}
+
 B2_DEFINE_STATUS(decode)
