@@ -168,6 +168,12 @@ def tiny_moe() -> ModelConfig:
                        expert_ffn=128, shared_ffn=128, architecture="B200MoeForCausalLM")
 
 
+def small_moe() -> ModelConfig:
+    """Small MoE with the production head size, for the grouped tensor-core path."""
+    return ModelConfig("small-moe", 2, 512, 8, 2, 128, 0, 2048, n_experts=16, top_k=4, expert_ffn=256,
+                       shared_ffn=256, architecture="B200MoeForCausalLM")
+
+
 def dense_27b() -> ModelConfig:
     """27B-shape dense decoder: 64 layers, hidden 5120, 40 q / 8 kv heads of 128, FFN 17408."""
     return ModelConfig("dense-27b", 64, 5120, 40, 8, 128, 17408, 151936)
@@ -187,7 +193,7 @@ def dflash_drafter(target: ModelConfig) -> ModelConfig:
 
 
 PRESETS = {
-    "tiny-dense": tiny_dense, "tiny-moe": tiny_moe, "small-dense": small_dense, "dense-27b": dense_27b, "moe-35b-a3b": moe_35b_a3b,
+    "tiny-dense": tiny_dense, "tiny-moe": tiny_moe, "small-dense": small_dense, "small-moe": small_moe, "dense-27b": dense_27b, "moe-35b-a3b": moe_35b_a3b,
 }
 
 

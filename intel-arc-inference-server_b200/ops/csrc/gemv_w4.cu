@@ -49,6 +49,13 @@ struct GemvParams {
   long long x_slice;  // elements between input slices (x_mode 1)
   int rows;           // staged token rows (M rounded up to 1, 2, 4, 8, 16, 32, 64)
   int xcg;            // groups of x staged at a time
+  int batches;        // grid.z
+  // batched form (MoE decode): blockIdx.z = b selects an expert's weights and that batch's one row
+  const int* expert_ids;     // [batches] or nullptr
+  long long expert_bytes;    // bytes between experts' W4B tensors
+  int x_div;                 // batch b reads activations of batch b / x_div
+  long long x_batch_bytes;   // bytes between activation batches
+  long long out_batch;       // floats between output batches
 };
 
 __host__ __device__ inline int stride_words(int xcg) { return xcg * 32 + 4; }  // +4 words: conflict-free B reads
@@ -163,7 +170,11 @@ __global__ void __launch_bounds__(kThreads, (T <= 2 ? 2 : 1)) gemv_w4_kernel(con
   if (warp == 8) {
     // ---------------- producer: stream this CTA's blocks; weights do not depend on the previous kernel
     if (lane == 0) {
-      const uint8_t* src = p.w + ((size_t)nblk * p.KG + gbeg) * kBlockBytes;
+      // the expert ids come from the routing kernel before this one: in the batched form the producer
+      // has to wait for it too (the dense form streams weights that depend on nothing)
+      if (p.expert_ids) pdl_wait();
+      const uint8_t* wbase = p.expert_ids ? p.w + (size_t)p.expert_ids[blockIdx.z] * p.expert_bytes : p.w;
+      const uint8_t* src = wbase + ((size_t)nblk * p.KG + gbeg) * kBlockBytes;
       bool ok = true;
       int issued = 0;
       for (int i = 0; i < nstage && ok; ++i) {
@@ -190,6 +201,7 @@ __global__ void __launch_bounds__(kThreads, (T <= 2 ? 2 : 1)) gemv_w4_kernel(con
   pdl_wait();  // activations come from the previous kernel
   pdl_launch_dependents();
 
+  const uint8_t* xbase = reinterpret_cast<const uint8_t*>(p.x) + (size_t)(blockIdx.z / p.x_div) * p.x_batch_bytes;
   const int g = lane >> 2, t = lane & 3;
   float acc[T][4];
 #pragma unroll
@@ -221,10 +233,10 @@ __global__ void __launch_bounds__(kThreads, (T <= 2 ? 2 : 1)) gemv_w4_kernel(con
         if (v < total && row < p.M && col < nvec) {
           const int k = k0 + col * 8;
           if (p.x_mode == 0) {
-            val = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p.x) + (size_t)row * p.ldx + k);
+            val = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(xbase) + (size_t)row * p.ldx + k);
           } else {
             // SiLU(gate) * up over summed fp32 slices; gate/up alternate in runs of 16
-            const float* base = reinterpret_cast<const float*>(p.x) + (size_t)row * p.ldx + (k >> 4) * 32 + (k & 15);
+            const float* base = reinterpret_cast<const float*>(xbase) + (size_t)row * p.ldx + (k >> 4) * 32 + (k & 15);
             float gsum[8], usum[8];
 #pragma unroll
             for (int i = 0; i < 8; ++i) gsum[i] = usum[i] = 0.f;
@@ -290,7 +302,7 @@ __global__ void __launch_bounds__(kThreads, (T <= 2 ? 2 : 1)) gemv_w4_kernel(con
 
   // ---- write this split's partial sums
   const int n_lo = nblk * 128 + warp * 16 + g, n_hi = n_lo + 8;
-  float* outp = p.out + (size_t)split * p.M * p.ldo;
+  float* outp = p.out + (size_t)blockIdx.z * p.out_batch + (size_t)split * p.M * p.ldo;
 #pragma unroll
   for (int tt = 0; tt < T; ++tt) {
     const int m0 = tt * 8 + 2 * t, m1 = m0 + 1;
@@ -326,7 +338,7 @@ int launch_t(GemvParams& p, cudaStream_t stream) {
     if (e != cudaSuccess) return (int)e;
     configured[dev & 63] = want;
   }
-  dim3 grid((p.N + 127) / 128, p.S);
+  dim3 grid((p.N + 127) / 128, p.S, p.batches);
   return b2_launch(gemv_w4_kernel<T>, grid, dim3(kThreads), smem, stream, true, p);
 }
 
@@ -355,6 +367,7 @@ extern "C" int b2_gemv_w4(const void* w4b, const void* x, float* out, int M, int
   p.w = reinterpret_cast<const uint8_t*>(w4b);
   p.x = x;
   p.out = out;
+  p.batches = 1; p.expert_ids = nullptr; p.expert_bytes = 0; p.x_div = 1; p.x_batch_bytes = 0; p.out_batch = 0;
   p.M = M; p.N = N; p.KG = K / 64; p.S = S;
   p.gps = (p.KG + S - 1) / S;
   if (p.gps % kG != 0) p.gps += kG - p.gps % kG;   // splits start on a stage boundary
@@ -364,6 +377,25 @@ extern "C" int b2_gemv_w4(const void* w4b, const void* x, float* out, int M, int
   if (M <= 16) return launch_t<2>(p, st);
   if (M <= 32) return launch_t<4>(p, st);
   return launch_t<8>(p, st);
+}
+
+// Batched form for MoE decode: batch b (one row) uses the weights of expert expert_ids[b] out of a stack of
+// equally shaped W4B tensors, reads the activations of batch b / x_div and writes out[b][S][N].
+extern "C" int b2_gemv_w4_experts(const void* w4b_stack, long long expert_bytes, const int* expert_ids, int batches,
+                                  const void* x, int x_div, long long x_batch_bytes, float* out, int N, int K, int S,
+                                  int ldx, int x_mode, int s_in, long long x_slice, void* stream) {
+  if (batches < 1 || batches > 65535 || K % 64 != 0 || S < 1 || x_div < 1) return -1;
+  GemvParams p;
+  p.w = reinterpret_cast<const uint8_t*>(w4b_stack);
+  p.x = x;
+  p.out = out;
+  p.M = 1; p.N = N; p.KG = K / 64; p.S = S;
+  p.gps = (p.KG + S - 1) / S;
+  if (p.gps % kG != 0) p.gps += kG - p.gps % kG;
+  p.ldx = ldx; p.ldo = N; p.x_mode = x_mode; p.s_in = s_in; p.x_slice = x_slice;
+  p.batches = batches; p.expert_ids = expert_ids; p.expert_bytes = expert_bytes; p.x_div = x_div;
+  p.x_batch_bytes = x_batch_bytes; p.out_batch = (long long)S * N;
+  return launch_t<1>(p, reinterpret_cast<cudaStream_t>(stream));
 }
 
 B2_DEFINE_STATUS(gemv)

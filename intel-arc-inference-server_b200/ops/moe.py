@@ -1,0 +1,46 @@
+"""Bindings of the mixture-of-experts kernels (``csrc/moe.cu``) and the batched expert GEMV."""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import lib as K
+
+
+def route(logits: torch.Tensor, ld: int, t: int, e: int, k: int, topk_idx: torch.Tensor, topk_w: torch.Tensor):
+    """softmax over the first ``e`` columns -> top-k (ties to the lower id) -> renormalise."""
+    K._check(K.lib().b2_moe_route(K._p(logits), ld, t, e, k, K._p(topk_idx), K._p(topk_w), K._stream()), "moe_route")
+
+
+def sort(topk_idx, t, k, e, max_blk, counts, rank, expert_base, blk_expert, blk_row0, blk_rows, n_blk, total_rows):
+    """Histogram + ranks, then the padded expert-major plan (block table for the grouped GEMM)."""
+    rc = K.lib().b2_moe_sort(K._p(topk_idx), t, k, e, max_blk, K._p(counts), K._p(rank), K._p(expert_base),
+                             K._p(blk_expert), K._p(blk_row0), K._p(blk_rows), K._p(n_blk), K._p(total_rows),
+                             K._stream())
+    K.launch_count += 1
+    K._check(rc, "moe_sort")
+
+
+def scatter(topk_idx, rank, expert_base, t, k, x, h, row_of, xs):
+    K._check(K.lib().b2_moe_scatter(K._p(topk_idx), K._p(rank), K._p(expert_base), t, k, K._p(x), h, K._p(row_of),
+                                    K._p(xs), K._stream()), "moe_scatter")
+
+
+def combine(y, row_of, topk_w, t, k, h, shared_y, gate_logit, gate_ld, resid, out):
+    K._check(K.lib().b2_moe_combine(K._p(y), K._p(row_of), K._p(topk_w), t, k, h, K._p(shared_y), K._p(gate_logit),
+                                    gate_ld, K._p(resid), K._p(out), K._stream()), "moe_combine")
+
+
+def combine_rows(part, s, m, k, h, topk_w, shared_part, s_sh, gate_logit, gate_ld, out):
+    K._check(K.lib().b2_moe_combine_rows(K._p(part), s, m, k, h, K._p(topk_w), K._p(shared_part), s_sh,
+                                         K._p(gate_logit), gate_ld, K._p(out), K._stream()), "moe_combine_rows")
+
+
+def gemv_experts(w4b_stack, expert_bytes, expert_ids, batches, x, x_div, x_batch_bytes, out, n, k, splits, ldx,
+                 x_mode=0, s_in=1, x_slice=0):
+    """One row per batch against the W4B weights of expert ``expert_ids[b]``; ``out`` is ``[b][splits][n]``."""
+    rc = K.lib().b2_gemv_w4_experts(K._p(w4b_stack), ctypes.c_longlong(expert_bytes), K._p(expert_ids), batches,
+                                    K._p(x), x_div, ctypes.c_longlong(x_batch_bytes), K._p(out), n, k, splits, ldx,
+                                    x_mode, s_in, ctypes.c_longlong(x_slice), K._stream())
+    K._check(rc, "gemv_w4_experts")
