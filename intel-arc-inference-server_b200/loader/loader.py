@@ -1,0 +1,199 @@
+"""Checkpoint loader: HF safetensors (GPTQ / AutoRound W4A16, group 64) -> ``ModelWeights``.
+
+Steps, as in the reference's loader (src/loader/loader.cc:308 load_linear, :460 load_small, :521
+load_mtp, :954 load_impl; docs/13-loader.md): resolve the name view (``model.language_model.``
+prefix stripped, ``model.visual.*`` skipped, ``mtp.*`` optional), check the quantisation config and
+each linear's invariants, fuse (q‖k‖v concatenated, gate‖up interleaved in runs of 16), repack into
+the kernel layout on the target device, convert norms to fp32, and cross-check the bytes a decode
+step reads ("W") against the descriptor's arithmetic.  Tensor parallel: ``tp=(rank, world)`` takes
+the rank's column slice of qkv / gate‖up / lm_head (whole heads, whole interleave runs) and its row
+slice (input channels) of o / down straight from the checkpoint tensors (loader.cc:882-886).
+"""
+from __future__ import annotations
+
+import json
+import os
+import sys
+import time
+from typing import Dict, List, Optional, Tuple
+
+import torch
+
+from ..models.config import ModelConfig
+from ..models.weights import ExpertWeights, LayerWeights, ModelWeights, MtpWeights, QLinear, interleave16
+from ..utils import quant as Q
+from ..utils.safetensors_io import SafetensorsSet
+from .quant_config import QuantConfig, QuantError, assert_quant_invariants
+from .snapshot import resolve_snapshot
+
+
+class NameView:
+    """Checkpoint names as the loader sees them: wrapper prefixes stripped, vision towers skipped."""
+
+    def __init__(self, st: SafetensorsSet, copy: bool = True):
+        self.st = st
+        self.copy = copy   # False when every tensor is moved to a device before the set is dropped
+        self.map: Dict[str, str] = {}
+        for n in st.names():
+            v = n
+            if v.startswith("model.visual.") or v.startswith("visual."):
+                continue
+            if v.startswith("model.language_model."):
+                v = "model." + v[len("model.language_model."):]
+            elif v.startswith("language_model."):
+                v = v[len("language_model."):]
+            self.map[v] = n
+
+    def has(self, name):
+        return name in self.map
+
+    def get(self, name) -> torch.Tensor:
+        if name not in self.map:
+            raise KeyError(f"checkpoint has no tensor {name}")
+        return self.st.get(self.map[name], self.copy)
+
+
+class _LinearSrc:
+    """One quantised (or bf16) linear of the checkpoint: ``q`` uint8 [K][N] + scales, or a dense weight."""
+
+    def __init__(self, view: NameView, prefix: str, qc: QuantConfig):
+        self.prefix = prefix
+        if view.has(prefix + ".qweight"):
+            qw = view.get(prefix + ".qweight")
+            sc = view.get(prefix + ".scales")
+            qz = view.get(prefix + ".qzeros") if view.has(prefix + ".qzeros") else None
+            gi = view.get(prefix + ".g_idx") if view.has(prefix + ".g_idx") else None
+            assert_quant_invariants(prefix, qw, sc, qz, gi, qc.group_size)
+            self.q = Q.unpack_gptq(qw)                      # [K][N]
+            self.scales = sc if qc.group_size == 64 else Q.expand_group128(sc)
+            self.dense = None
+        elif view.has(prefix + ".weight"):
+            self.dense = view.get(prefix + ".weight").float()   # an excluded module: quantise on the host (RTN)
+            self.q, self.scales = Q.quantize_rtn(self.dense)
+        else:
+            raise KeyError(f"checkpoint has neither {prefix}.qweight nor {prefix}.weight")
+
+    @property
+    def n(self):
+        return self.q.shape[1]
+
+    @property
+    def k(self):
+        return self.q.shape[0]
+
+
+def _cols(src: _LinearSrc, lo: int, hi: int):
+    return src.q[:, lo:hi], src.scales[:, lo:hi]
+
+
+def _fuse_cols(parts: List[Tuple[torch.Tensor, torch.Tensor]]):
+    return torch.cat([p[0] for p in parts], dim=1), torch.cat([p[1] for p in parts], dim=1)
+
+
+def _interleave_cols(gate, up):
+    """Column-wise interleave16 of two (q, scales) pairs."""
+    out = []
+    for a, b in zip(gate, up):
+        r, n = a.shape
+        out.append(torch.stack([a.reshape(r, n // 16, 16), b.reshape(r, n // 16, 16)], dim=2).reshape(r, 2 * n))
+    return out[0], out[1]
+
+
+def _ql(q, scales, device) -> QLinear:
+    return QLinear(Q.to_w4b(q.to(device), scales.to(device)), q.shape[1], q.shape[0])
+
+
+def _load_layer(view: NameView, cfg: ModelConfig, prefix: str, qc: QuantConfig, device, tp) -> LayerWeights:
+    rank, world = tp
+    hd = cfg.head_dim
+    q_s = _LinearSrc(view, prefix + ".self_attn.q_proj", qc)
+    k_s = _LinearSrc(view, prefix + ".self_attn.k_proj", qc)
+    v_s = _LinearSrc(view, prefix + ".self_attn.v_proj", qc)
+    o_s = _LinearSrc(view, prefix + ".self_attn.o_proj", qc)
+    if cfg.n_kv_heads % world or cfg.n_q_heads % world:
+        raise ValueError(f"tensor parallel {world} does not divide {cfg.n_q_heads} q / {cfg.n_kv_heads} kv heads")
+    qh, kh = cfg.n_q_heads // world, cfg.n_kv_heads // world
+    qkv = _fuse_cols([_cols(q_s, rank * qh * hd, (rank + 1) * qh * hd), _cols(k_s, rank * kh * hd, (rank + 1) * kh * hd),
+                      _cols(v_s, rank * kh * hd, (rank + 1) * kh * hd)])
+    # row-parallel o: this rank's input channels (its heads' outputs)
+    o_rows = slice(rank * qh * hd, (rank + 1) * qh * hd)
+    o_q, o_sc = o_s.q[o_rows], o_s.scales[o_rows.start // 64: o_rows.stop // 64]
+    lw = LayerWeights(
+        input_norm=view.get(prefix + ".input_layernorm.weight").float().to(device),
+        post_norm=view.get(prefix + ".post_attention_layernorm.weight").float().to(device),
+        qkv=_ql(*qkv, device), o=_ql(o_q, o_sc, device))
+
+    def mlp(p, ffn):
+        g, u, d = (_LinearSrc(view, f"{p}.{n}_proj", qc) for n in ("gate", "up", "down"))
+        if ffn % (16 * world):
+            raise ValueError(f"tensor parallel {world} does not divide FFN {ffn} into runs of 16")
+        lo, hi = rank * ffn // world, (rank + 1) * ffn // world
+        gu = _interleave_cols(_cols(g, lo, hi), _cols(u, lo, hi))
+        if (lo % 64) or (hi % 64):
+            raise ValueError(f"tensor parallel {world}: FFN slice {lo}:{hi} is not a whole number of groups")
+        return _ql(*gu, device), _ql(d.q[lo:hi], d.scales[lo // 64: hi // 64], device)
+
+    if cfg.is_moe:
+        lw.router = view.get(prefix + ".mlp.gate.weight").to(torch.bfloat16).to(device)
+        lw.experts = []
+        for e in range(cfg.n_experts):
+            gu, dn = mlp(f"{prefix}.mlp.experts.{e}", cfg.expert_ffn)
+            lw.experts.append(ExpertWeights(gu, dn))
+        lw.experts_gate_up_w4b = torch.stack([x.gate_up.w4b for x in lw.experts]).contiguous()
+        lw.experts_down_w4b = torch.stack([x.down.w4b for x in lw.experts]).contiguous()
+        if cfg.shared_ffn:
+            gu, dn = mlp(f"{prefix}.mlp.shared_expert", cfg.shared_ffn)
+            lw.shared = ExpertWeights(gu, dn)
+            if view.has(prefix + ".mlp.shared_expert_gate.weight"):
+                lw.shared_gate = view.get(prefix + ".mlp.shared_expert_gate.weight").to(torch.bfloat16).to(device)
+    else:
+        lw.gate_up, lw.down = mlp(prefix + ".mlp", cfg.ffn)
+    return lw
+
+
+def load(snapshot: str, device="cuda", mtp: bool = True, int8_head: bool = False, tp: Tuple[int, int] = (0, 1),
+         report=sys.stderr) -> ModelWeights:
+    t0 = time.time()
+    snap = resolve_snapshot(snapshot)
+    with open(os.path.join(snap, "config.json")) as f:
+        hf = json.load(f)
+    if "text_config" in hf:
+        hf = {**hf["text_config"], "quantization_config": hf.get("quantization_config", hf["text_config"].get("quantization_config"))}
+    cfg = ModelConfig.from_hf_config(hf)
+    qc = QuantConfig.parse(hf)
+    st = SafetensorsSet(snap)
+    view = NameView(st, copy=torch.device(device).type == "cpu")
+    rank, world = tp
+    embed = view.get("model.embed_tokens.weight").to(torch.bfloat16).to(device)
+    head_name = "lm_head.weight" if view.has("lm_head.weight") else "model.embed_tokens.weight"   # tied embeddings
+    head = view.get(head_name).to(torch.bfloat16)
+    if world > 1:   # vocabulary-parallel head
+        per = (cfg.vocab + world - 1) // world
+        head = head[rank * per: min(cfg.vocab, (rank + 1) * per)]
+    head = head.to(device).contiguous()
+    layers = [_load_layer(view, cfg, f"model.layers.{i}", qc, device, tp) for i in range(cfg.n_layers)]
+    w = ModelWeights(cfg, embed, head, view.get("model.norm.weight").float().to(device), layers)
+    if mtp and cfg.mtp_layers and (view.has("mtp.fc.qweight") or view.has("mtp.fc.weight")):
+        fc = _LinearSrc(view, "mtp.fc", qc)
+        w.mtp = MtpWeights(view.get("mtp.pre_fc_norm_embedding.weight").float().to(device),
+                           view.get("mtp.pre_fc_norm_hidden.weight").float().to(device),
+                           _ql(fc.q, fc.scales, device),
+                           [_load_layer(view, cfg, f"mtp.layers.{i}", qc, device, tp)
+                            for i in range(cfg.mtp_layers)],
+                           view.get("mtp.norm.weight").float().to(device))
+    if int8_head:
+        wf = w.lm_head.float()
+        sc = wf.abs().amax(dim=1).clamp_min(1e-8) / 127.0
+        w.lm_head_i8 = (torch.round(wf / sc[:, None]).clamp_(-127, 127).to(torch.int8).contiguous(), sc.contiguous())
+    if report is not None:
+        want = cfg.weight_bytes_per_token(1.0 if int8_head else 2.0) / world
+        got = sum(l.qkv.nbytes + l.o.nbytes + (l.gate_up.nbytes + l.down.nbytes if l.gate_up is not None else 0)
+                  for l in layers) + w.lm_head.numel() * (1 if int8_head else 2)
+        line = (f"load: {cfg.name} {qc.method} g{qc.group_size} from {snap}: {w.nbytes() / 1e9:.3f} GB resident, "
+                f"{time.time() - t0:.1f} s")
+        if not cfg.is_moe:
+            line += f", W = {got / 1e9:.3f} GB / token (descriptor {want / 1e9:.3f})"
+            if abs(got - want) > 0.02 * want:
+                raise QuantError(f"bytes per token {got} differ from the descriptor's {want:.0f} by more than 2 %")
+        report.write(line + "\n")
+    return w

@@ -59,6 +59,7 @@ class Engine:
         self.prefill_backend = prefill_backend
         self._prefill = None
         self.steps_replayed = 0
+        self.last_prefill_row = 0
         self.launches_per_step: Dict[Tuple[int, bool], int] = {}
 
     # ------------------------------------------------------------------ slots and pages
@@ -147,6 +148,7 @@ class Engine:
             from .prefill import PrefillRunner
             if self._prefill is None:
                 self._prefill = PrefillRunner(self)
+            self.last_prefill_row = 0      # row of model.buf.logits that holds the prompt's last position
             return self._prefill.run(slot, ids, chunk)
         start = self.seq_len[slot]
         out = None
@@ -155,6 +157,7 @@ class Engine:
             rows = [Row(slot, start + c0 + i, t) for i, t in enumerate(part)]
             last = c0 + self.max_rows >= len(ids)
             out = self.forward_rows(rows, advance=False, read=last)
+        self.last_prefill_row = len(out) - 1
         return out[-1]
 
     def _use_tc_prefill(self, n: int) -> bool:
