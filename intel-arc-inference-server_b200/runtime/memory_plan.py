@@ -1,0 +1,111 @@
+"""Device-free memory arithmetic: what fits, before anything is allocated.
+
+The role of the reference's planner (src/runtime/memory_plan.h:117-254): from the model
+descriptor and the serving options compute the bytes of weights, KV pool, step scratch and
+prompt-pass scratch; choose ``max_len`` for ``--max-len auto`` as the largest context whose pool
+fits beside the rest with a fixed reserve; refuse at start-up with the numbers when the request
+cannot fit.  One source of sizes for the planner and the allocator keeps the two honest.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+from ..models.config import ModelConfig
+
+RESERVE_BYTES = int(1.5 * 2 ** 30)        # left free for the CUDA context, NCCL, fragmentation
+HBM_BYTES = 183_359 * 2 ** 20             # what nvidia-smi reports for a B200
+
+
+@dataclass
+class MemoryPlan:
+    weights: int
+    kv_pool: int
+    step_scratch: int
+    prefill_scratch: int
+    resident_bf16: int
+    total: int
+    budget: int
+    max_len: int
+    max_seqs: int
+    num_pages: int
+
+    def line(self) -> str:
+        g = 2 ** 30
+        return (f"memory: model {self.weights / g:.2f} GiB, kv {self.kv_pool / g:.2f} GiB ({self.num_pages} pages, "
+                f"{self.max_seqs} x {self.max_len}), decode state {self.step_scratch / g:.2f} GiB, prompt scratch "
+                f"{self.prefill_scratch / g:.2f} GiB, total {self.total / g:.2f} of {self.budget / g:.2f} GiB")
+
+
+def weight_bytes(cfg: ModelConfig, int8_head: bool = False, tp: int = 1, ep: int = 1) -> int:
+    h = cfg.hidden
+    int4 = 0.5 + 2.0 / 64
+    per = (cfg.qkv_dim * h + h * cfg.q_dim) * int4 / tp
+    if cfg.is_moe:
+        per += cfg.n_experts * 3 * cfg.expert_ffn * h * int4 / ep + cfg.n_experts * h * 2
+        per += 3 * cfg.shared_ffn * h * int4 / tp
+    else:
+        per += 3 * cfg.ffn * h * int4 / tp
+    layers = cfg.n_layers + cfg.mtp_layers
+    head = cfg.vocab * h * (1 if int8_head else 2) / tp + (cfg.vocab * h * 2 if int8_head else 0) * 0
+    return int(layers * per + cfg.vocab * h * 2 + head)
+
+
+def kv_bytes_per_page(cfg: ModelConfig, kv_dtype: str, tp: int = 1) -> int:
+    per_tok_head = cfg.head_dim * (1 if kv_dtype == "int8" else 2) + (4 if kv_dtype == "int8" else 0)
+    return (cfg.n_layers + cfg.mtp_layers) * 2 * (cfg.n_kv_heads // tp) * per_tok_head * cfg.page_size
+
+
+def step_scratch_bytes(cfg: ModelConfig, max_rows: int = 64, nsplit: int = 32) -> int:
+    h = cfg.hidden
+    b = max_rows * (2 * h * 2 + 2 * cfg.q_dim * 2 + cfg.vocab * 4)
+    b += max_rows * cfg.n_q_heads * nsplit * (cfg.head_dim + 2) * 4
+    b += 16 * max_rows * (cfg.qkv_dim + 2 * h + 2 * max(cfg.ffn, cfg.expert_ffn * max(cfg.top_k, 1))) * 4
+    return int(b)
+
+
+def prefill_scratch_bytes(cfg: ModelConfig, chunk: int, backend: str) -> int:
+    h = cfg.hidden
+    ffn = cfg.ffn if not cfg.is_moe else max(cfg.expert_ffn, cfg.shared_ffn)
+    b = chunk * (2 * h * 2 + cfg.qkv_dim * 4 + 2 * cfg.q_dim * 2 + ffn * 2)
+    biggest = max(cfg.qkv_dim * h, h * cfg.q_dim, 2 * ffn * h)
+    if backend in ("bf16", "auto"):
+        b += biggest * 2
+        if cfg.is_moe:
+            b += cfg.n_experts * 3 * cfg.expert_ffn * h * 2
+    if cfg.is_moe:
+        rows = (chunk * cfg.top_k // 128 + cfg.n_experts) * 128
+        b += rows * (2 * h + cfg.expert_ffn) * 2
+    return int(b)
+
+
+def plan(cfg: ModelConfig, max_seqs: int, max_len, kv_dtype: str = "bf16", int8_head: bool = False,
+         prefill_backend: str = "auto", prefill_chunk: int = 4096, tp: int = 1, ep: int = 1,
+         budget: int = HBM_BYTES) -> MemoryPlan:
+    """``max_len`` an int or "auto".  Raises ValueError with the numbers when it cannot fit."""
+    w = weight_bytes(cfg, int8_head, tp, ep)
+    resident = 0
+    if prefill_backend == "bf16-resident":
+        resident = (w - 2 * cfg.vocab * cfg.hidden * 2) * 4      # int4 -> bf16 copies of the linears
+    elif prefill_backend in ("int8", "l0-int8"):
+        resident = (w - 2 * cfg.vocab * cfg.hidden * 2) * 2
+    st = step_scratch_bytes(cfg)
+    pf = prefill_scratch_bytes(cfg, prefill_chunk, prefill_backend)
+    page = kv_bytes_per_page(cfg, kv_dtype, tp)
+    fixed = w + resident + st + pf + RESERVE_BYTES
+    if fixed >= budget:
+        raise ValueError(f"{cfg.name}: weights and scratch need {fixed / 2**30:.1f} GiB of {budget / 2**30:.1f} GiB "
+                         "before any KV cache")
+    if max_len == "auto":
+        pages = (budget - fixed) // page
+        max_len = int(min(262144, (pages - 1) // max_seqs * cfg.page_size))
+        if max_len < 2 * cfg.page_size:
+            raise ValueError(f"{cfg.name}: no room for a KV cache of {max_seqs} sequences")
+    max_len = int(max_len)
+    num_pages = max_seqs * ((max_len + cfg.page_size - 1) // cfg.page_size) + 1
+    kv = num_pages * page
+    total = fixed + kv
+    if total > budget:
+        fit = ((budget - fixed) // page - 1) // max_seqs * cfg.page_size
+        raise ValueError(f"{cfg.name}: {max_seqs} x {max_len} positions of {kv_dtype} KV need {kv / 2**30:.1f} GiB; "
+                         f"{(budget - fixed) / 2**30:.1f} GiB are free after the model: at most {fit} positions fit")
+    return MemoryPlan(w, kv, st, pf, resident, total, budget, max_len, max_seqs, num_pages)
