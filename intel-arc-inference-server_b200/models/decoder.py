@@ -50,6 +50,9 @@ class StepBuffers:
         self.cand_val = torch.zeros(max_rows * self.ncand, dtype=f32, device=device)
         self.cand_idx = torch.zeros(max_rows * self.ncand, dtype=torch.int32, device=device)
         self.flag = torch.zeros(4, dtype=torch.int32, device=device)
+        self.tickets = torch.zeros(max_rows * cfg.n_kv_heads, dtype=torch.int32, device=device)
+        self.fold_tickets = torch.zeros((h + 127) // 128, dtype=torch.int32, device=device)
+        self.ssq = torch.zeros(max_rows * ((h + 127) // 128), dtype=f32, device=device)
         self._parts = {}
         self.device = device
 
@@ -100,6 +103,7 @@ class DecoderModel:
             sc = wf.abs().amax(dim=1).clamp_min(1e-8) / 127.0
             weights.lm_head_i8 = (torch.round(wf / sc[:, None]).clamp_(-127, 127).to(torch.int8).contiguous(), sc.contiguous())
         self._splits = {}
+        self.fused = True     # dense layers: residual folds and norms ride inside the GEMVs
 
     # ------------------------------------------------------------------ pieces
     def _gemv(self, name: str, ql: QLinear, x: torch.Tensor, m: int, x_mode=0, s_in=1, x_slice=0):
@@ -118,7 +122,8 @@ class DecoderModel:
         K.rope_append(part, m * cfg.qkv_dim, s, m, ctrl, block_table, max_blocks, self.cos_t, self.sin_t,
                       cfg.n_q_heads, cfg.n_kv_heads, cfg.head_dim, b.q, kc, vc, ks, vs, kv.kv_int8)
         K.attn_decode(b.q, kc, vc, block_table, ctrl, b.o_part, b.ml_part, b.attn_out, m, cfg.n_q_heads,
-                      cfg.n_kv_heads, cfg.head_dim, self.nsplit_attn, max_blocks, self.scale, ks, vs, kv.kv_int8)
+                      cfg.n_kv_heads, cfg.head_dim, self.nsplit_attn, max_blocks, self.scale, ks, vs, kv.kv_int8,
+                      tickets=b.tickets)
         return self._gemv("o", lw.o, b.attn_out, m)
 
     def ffn_block(self, lw: LayerWeights, m: int):
@@ -126,12 +131,53 @@ class DecoderModel:
         gu, s_gu = self._gemv("gate_up", lw.gate_up, b.x, m)
         return self._gemv("down", lw.down, gu, m, x_mode=1, s_in=s_gu, x_slice=m * 2 * cfg.ffn)
 
+    def _gemv_fused(self, name: str, ql: QLinear, x, m: int, norm_w=None, fold: bool = False, x_mode=0, s_in=1,
+                    x_slice=0):
+        key = (ql.n, ql.k)
+        s = self._splits.get(key)
+        if s is None:
+            s = self._splits[key] = K.gemv_splits(ql.n, ql.k)
+        b = self.buf
+        part = b.part(name, s, ql.n)
+        K.gemv_w4_fused(ql.w4b, x, part, m, ql.n, ql.k, s, x_mode=x_mode, s_in=s_in, x_slice=x_slice,
+                        norm_w=norm_w, norm_ssq=b.ssq if norm_w is not None else None, norm_eps=self.cfg.rms_eps,
+                        fold_tickets=b.fold_tickets if fold else None, fold_resid=b.resid if fold else None,
+                        fold_ssq=b.ssq if fold else None)
+        return part, s
+
+    def dense_layer_fused(self, lw: LayerWeights, li: int, m: int, ctrl, block_table, max_blocks, kv: KVCache,
+                          x_ready: bool):
+        """One dense layer in six launches: the residual folds ride in the o / down GEMVs' last CTAs and the
+        two RMSNorms in the qkv / gate‖up GEMVs' activation staging.  ``x_ready``: ``buf.x`` already holds
+        the normalised input (first layer, after the embedding kernel); otherwise ``buf.resid`` and
+        ``buf.ssq`` do."""
+        cfg, b = self.cfg, self.buf
+        if x_ready:
+            part, s = self._gemv("qkv", lw.qkv, b.x, m)
+        else:
+            part, s = self._gemv_fused("qkv", lw.qkv, b.resid, m, norm_w=lw.input_norm, x_mode=2)
+        kc, vc, ks, vs = kv.layer(li)
+        K.rope_append(part, m * cfg.qkv_dim, s, m, ctrl, block_table, max_blocks, self.cos_t, self.sin_t,
+                      cfg.n_q_heads, cfg.n_kv_heads, cfg.head_dim, b.q, kc, vc, ks, vs, kv.kv_int8)
+        K.attn_decode(b.q, kc, vc, block_table, ctrl, b.o_part, b.ml_part, b.attn_out, m, cfg.n_q_heads,
+                      cfg.n_kv_heads, cfg.head_dim, self.nsplit_attn, max_blocks, self.scale, ks, vs, kv.kv_int8,
+                      tickets=b.tickets)
+        self._gemv_fused("o", lw.o, b.attn_out, m, fold=True)
+        gu, s_gu = self._gemv_fused("gate_up", lw.gate_up, b.resid, m, norm_w=lw.post_norm, x_mode=2)
+        self._gemv_fused("down", lw.down, gu, m, fold=True, x_mode=1, s_in=s_gu, x_slice=m * 2 * cfg.ffn)
+
     def layers_walk(self, layers: List[LayerWeights], m: int, ctrl, block_table, max_blocks, kv: KVCache,
                     first_from_embed: bool = True, kv_layer0: int = 0):
         """Runs ``layers``; returns the (partials, splits) of the last residual branch, not yet folded."""
         cfg, b = self.cfg, self.buf
         h = cfg.hidden
         pend = None
+        if self.fused and first_from_embed and all(lw.gate_up is not None for lw in layers) and h % 128 == 0:
+            K.resid_norm(0, m, h, layers[0].input_norm, cfg.rms_eps, b.resid, b.x, embed=self.w.embed, ctrl=ctrl,
+                         vocab=cfg.vocab, flag=b.flag)
+            for i, lw in enumerate(layers):
+                self.dense_layer_fused(lw, kv_layer0 + i, m, ctrl, block_table, max_blocks, kv, x_ready=(i == 0))
+            return None, 0      # the residual stream is already folded
         for i, lw in enumerate(layers):
             if pend is None:
                 if first_from_embed:
@@ -156,8 +202,8 @@ class DecoderModel:
         cfg, b = self.cfg, self.buf
         h = cfg.hidden
         fn = self.w.final_norm if final_norm is None else final_norm
-        K.resid_norm(1, m, h, fn, cfg.rms_eps, b.resid, b.x, resid_in=b.resid, part=pend[0], part_slice=m * h,
-                     splits=pend[1])
+        K.resid_norm(1, m, h, fn, cfg.rms_eps, b.resid, b.x, resid_in=b.resid, part=pend[0],
+                     part_slice=m * h, splits=pend[1])
         if self.int8_head:
             w8, sc = self.w.lm_head_i8
             K.head_gemv(w8, b.x, b.logits, m, cfg.vocab, h, b.cand_val, b.cand_idx, wscale=sc)

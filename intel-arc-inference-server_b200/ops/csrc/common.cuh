@@ -14,6 +14,7 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 namespace b2 {
 
@@ -289,6 +290,7 @@ static inline int b2_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, siz
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = pdl ? 1 : 0;
+  static const bool no_pdl = getenv("B2_NO_PDL") != nullptr;  // measurement switch: plain stream order
+  cfg.numAttrs = (pdl && !no_pdl) ? 1 : 0;
   return (int)cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
 }

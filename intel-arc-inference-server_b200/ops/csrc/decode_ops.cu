@@ -256,12 +256,15 @@ struct AttnDecParams {
   int n_q, n_kv, nsplit, max_blocks;
   float scale_log2;  // softmax scale * log2(e)
   int kv_int8;
+  int* tickets;          // [M][n_kv] zeroed counters: the last split CTA of a (row, KV head) merges in-kernel
+  __nv_bfloat16* out;    // [M][n_q*D], written by the merging CTA when tickets != nullptr
 };
 
 template <int D, int GQA>
 __global__ void __launch_bounds__(256) attn_decode_kernel(const AttnDecParams p) {
   constexpr int DL = D / 32;
-  constexpr int KPI = 4;  // keys per iteration per warp
+  constexpr int KPI = 4;  // keys per iteration per warp (8 row loads per lane in flight; more costs a resident CTA)
+  __shared__ int sm_last;
   __shared__ float sm_o[8][GQA][D];
   __shared__ float sm_ml[8][GQA][2];
   pdl_wait();
@@ -385,6 +388,58 @@ __global__ void __launch_bounds__(256) attn_decode_kernel(const AttnDecParams p)
       p.ml_part[base * 2] = mm;
       p.ml_part[base * 2 + 1] = lt;
     }
+  }
+  if (p.tickets == nullptr) return;
+  // ---- fused merge: the CTA that finishes last for this (row, KV head) folds all splits, in split
+  // order, so the result does not depend on which CTA that is.  The counter returns to zero for
+  // the next launch (graph replays need no host reset).
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int t = atomicAdd(&p.tickets[m * p.n_kv + kh], 1);
+    sm_last = (t == p.nsplit - 1);
+    if (sm_last) p.tickets[m * p.n_kv + kh] = 0;
+  }
+  __syncthreads();
+  if (!sm_last) return;
+  __threadfence();
+  // weights of the splits first (one thread per (head, split)), then every (head, dim) output with its
+  // split loads issued together; the sums run in split order
+  float* cw = &sm_o[0][0][0];  // [GQA][nsplit] reuses the warp-merge buffer (8 * D >= nsplit for nsplit <= 64)
+  for (int i = threadIdx.x; i < GQA * p.nsplit; i += 256) {
+    const int h = i / p.nsplit, sp = i % p.nsplit;
+    const size_t base = ((size_t)m * p.n_q + kh * GQA + h) * p.nsplit;
+    cw[i] = __ldcg(p.ml_part + (base + sp) * 2);
+    sm_o[4][0][i] = __ldcg(p.ml_part + (base + sp) * 2 + 1);
+  }
+  __syncthreads();
+  if (threadIdx.x < GQA) {
+    const int h = threadIdx.x;
+    float mm = -INFINITY;
+    for (int sp = 0; sp < p.nsplit; ++sp) mm = fmaxf(mm, cw[h * p.nsplit + sp]);
+    float lt = 0.f;
+    for (int sp = 0; sp < p.nsplit; ++sp) {
+      const float ms = cw[h * p.nsplit + sp];
+      const float c = (ms == -INFINITY) ? 0.f : exp2f(ms - mm);
+      lt += sm_o[4][0][h * p.nsplit + sp] * c;
+      cw[h * p.nsplit + sp] = c;
+    }
+    const float inv = lt > 0.f ? 1.f / lt : 0.f;
+    for (int sp = 0; sp < p.nsplit; ++sp) cw[h * p.nsplit + sp] *= inv;
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < GQA * D; i += 256) {
+    const int h = i / D, d = i % D;
+    const float* src = p.o_part + (((size_t)m * p.n_q + kh * GQA + h) * p.nsplit) * D + d;
+    float o = 0.f;
+    for (int s0 = 0; s0 < p.nsplit; s0 += 8) {
+      float v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) v[u] = (s0 + u < p.nsplit) ? __ldcg(src + (size_t)(s0 + u) * D) : 0.f;
+#pragma unroll
+      for (int u = 0; u < 8; ++u) o = fmaf(v[u], (s0 + u < p.nsplit) ? cw[h * p.nsplit + s0 + u] : 0.f, o);
+    }
+    p.out[((size_t)m * p.n_q + kh * GQA + h) * D + d] = __float2bfloat16(o);
   }
 }
 
@@ -598,8 +653,9 @@ static int attn_decode_dispatch(int gqa, const AttnDecParams& p, dim3 grid, cuda
 extern "C" int b2_attn_decode(const void* q, const void* k_cache, const void* v_cache, const float* k_scale,
                               const float* v_scale, const int* block_table, const int* ctrl, float* o_part,
                               float* ml_part, void* out, int M, int n_q, int n_kv, int D, int nsplit, int max_blocks,
-                              float scale, int kv_int8, void* stream) {
+                              float scale, int kv_int8, int* tickets, void* stream) {
   AttnDecParams p;
+  p.tickets = tickets; p.out = (__nv_bfloat16*)out;
   p.q = (const __nv_bfloat16*)q; p.k_cache = k_cache; p.v_cache = v_cache; p.k_scale = k_scale; p.v_scale = v_scale;
   p.block_table = block_table; p.ctrl = ctrl; p.o_part = o_part; p.ml_part = ml_part;
   p.n_q = n_q; p.n_kv = n_kv; p.nsplit = nsplit; p.max_blocks = max_blocks;
@@ -610,7 +666,7 @@ extern "C" int b2_attn_decode(const void* q, const void* k_cache, const void* v_
   if (D == 128) rc = attn_decode_dispatch<128>(n_q / n_kv, p, grid, st);
   else if (D == 64) rc = attn_decode_dispatch<64>(n_q / n_kv, p, grid, st);
   else return -2;
-  if (rc) return rc;
+  if (rc || tickets) return rc;
   return b2_launch(attn_merge_kernel, dim3(n_q, M), dim3(D), 0, st, true, (const float*)o_part, (const float*)ml_part,
                    (__nv_bfloat16*)out, n_q, nsplit, D);
 }
@@ -686,6 +742,7 @@ extern "C" int b2_attn_decode_static(const void* q, const void* k_cache, const v
   // Nothing has to start at zero: every (row, head, split) entry that the merge reads is written by
   // the split kernel of the same call, empty splits included (they write m = -inf, l = 0).
   AttnDecParams p;
+  p.tickets = nullptr; p.out = nullptr;
   p.q = (const __nv_bfloat16*)q; p.k_cache = k_cache; p.v_cache = v_cache; p.k_scale = k_scale; p.v_scale = v_scale;
   p.block_table = block_table; p.ctrl = ctrl; p.o_part = o_part; p.ml_part = ml_part;
   p.n_q = n_q; p.n_kv = n_kv; p.nsplit = nsplit; p.max_blocks = max_blocks;

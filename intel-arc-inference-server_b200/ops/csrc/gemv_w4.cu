@@ -56,6 +56,17 @@ struct GemvParams {
   int x_div;                 // batch b reads activations of batch b / x_div
   long long x_batch_bytes;   // bytes between activation batches
   long long out_batch;       // floats between output batches
+  // fused residual fold (producer side): the last split CTA of an n-block adds the slices to the
+  // residual stream, writes it back as bf16 and leaves the block's sum of squares for the next norm
+  int* fold_tickets;                     // [nb] zeroed counters, or nullptr
+  const __nv_bfloat16* fold_resid_in;    // [M][N]
+  __nv_bfloat16* fold_resid_out;         // [M][N] (may alias fold_resid_in)
+  float* fold_ssq;                       // [M][nb]
+  // fused RMSNorm (consumer side, x_mode 2): x = bf16(resid * rsqrt(sum(ssq) / K + eps) * norm_w)
+  const float* norm_w;                   // [K]
+  const float* norm_ssq;                 // [M][norm_nb]
+  int norm_nb;
+  float norm_eps;
 };
 
 __host__ __device__ inline int stride_words(int xcg) { return xcg * 32 + 4; }  // +4 words: conflict-free B reads
@@ -146,7 +157,8 @@ __global__ void __launch_bounds__(kThreads, (T <= 2 ? 2 : 1)) gemv_w4_kernel(con
   const uint32_t smem0 = (smem_u32(smem_raw) + 127u) & ~127u;
   const uint32_t ring = smem0;
   const uint32_t bars = smem0 + kRingBytes;               // 16 mbarriers
-  const uint32_t gs0 = bars + 128;                        // float [xcg][8 T] group sums of x
+  const uint32_t rinv0 = bars + 128;                      // float [64] per-row 1/rms (x_mode 2)
+  const uint32_t gs0 = rinv0 + 256;                       // float [xcg][8 T] group sums of x
   const uint32_t xs0 = gs0 + ((p.xcg * 8 * T * 4 + 127) & ~127);  // bf16 rows, permuted per group
   const uint32_t full0 = bars, empty0 = bars + 8 * kStages;
   const int strideB = stride_words(p.xcg) * 4;
@@ -217,6 +229,14 @@ __global__ void __launch_bounds__(kThreads, (T <= 2 ? 2 : 1)) gemv_w4_kernel(con
   for (int tt = 0; tt < T; ++tt) x_row[tt] = xs0 + min(tt * 8 + g, p.rows - 1) * strideB + t * 32;
   const uint32_t gs_t = gs0 + 2 * t * 4;
 
+  if (p.x_mode == 2) {
+    // 1 / rms of each row from the per-block sums the producing kernel left (summed in block order)
+    if (tid < p.M) {
+      float ss = 0.f;
+      for (int j = 0; j < p.norm_nb; ++j) ss += p.norm_ssq[(size_t)tid * p.norm_nb + j];
+      asm volatile("st.shared.f32 [%0], %1;" ::"r"(rinv0 + tid * 4), "f"(rsqrtf(ss / (float)(p.KG * 64) + p.norm_eps)) : "memory");
+    }
+  }
   const int xvec = p.xcg * 8;  // 16-byte vectors per staged row
   for (int c0 = 0; c0 < ngroups; c0 += p.xcg) {
     const int cg = min(p.xcg, ngroups - c0);  // groups in this chunk
@@ -234,6 +254,15 @@ __global__ void __launch_bounds__(kThreads, (T <= 2 ? 2 : 1)) gemv_w4_kernel(con
           const int k = k0 + col * 8;
           if (p.x_mode == 0) {
             val = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(xbase) + (size_t)row * p.ldx + k);
+          } else if (p.x_mode == 2) {
+            const uint4 rv = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(xbase) + (size_t)row * p.ldx + k);
+            const float4 w0 = *reinterpret_cast<const float4*>(p.norm_w + k), w1 = *reinterpret_cast<const float4*>(p.norm_w + k + 4);
+            float ri;
+            asm volatile("ld.shared.f32 %0, [%1];" : "=f"(ri) : "r"(rinv0 + row * 4));
+            val.x = pack_bf16(bf16_lo(rv.x) * ri * w0.x, bf16_hi(rv.x) * ri * w0.y);
+            val.y = pack_bf16(bf16_lo(rv.y) * ri * w0.z, bf16_hi(rv.y) * ri * w0.w);
+            val.z = pack_bf16(bf16_lo(rv.z) * ri * w1.x, bf16_hi(rv.z) * ri * w1.y);
+            val.w = pack_bf16(bf16_lo(rv.w) * ri * w1.z, bf16_hi(rv.w) * ri * w1.w);
           } else {
             // SiLU(gate) * up over summed fp32 slices; gate/up alternate in runs of 16
             const float* base = reinterpret_cast<const float*>(xbase) + (size_t)row * p.ldx + (k >> 4) * 32 + (k & 15);
@@ -315,6 +344,50 @@ __global__ void __launch_bounds__(kThreads, (T <= 2 ? 2 : 1)) gemv_w4_kernel(con
       if (n_hi < p.N) outp[(size_t)m1 * p.ldo + n_hi] = acc[tt][3];
     }
   }
+  if (p.fold_tickets == nullptr) return;
+  // ---- fused fold: whichever split CTA of this n-block finishes last sums the slices in split order
+  // (so the bits do not depend on which one it is), adds the residual, rounds to bf16 and leaves
+  // the sum of squares of its 128 columns.  The counter returns to zero for the next launch.
+  __threadfence();
+  consumer_sync();
+  if (tid == 0) {
+    const int tk = atomicAdd(&p.fold_tickets[nblk], 1);
+    const int last = tk == p.S - 1;
+    if (last) p.fold_tickets[nblk] = 0;
+    asm volatile("st.shared.u32 [%0], %1;" ::"r"(rinv0 + 252), "r"(last) : "memory");
+  }
+  consumer_sync();
+  uint32_t is_last;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(is_last) : "r"(rinv0 + 252));
+  if (!is_last) return;
+  __threadfence();
+  const int nb_total = (p.N + 127) / 128;
+  // one (row, column) per thread; the slices of an element are loaded together and added in split order
+  const int items = p.M * 128;
+  for (int idx0 = 0; idx0 < items; idx0 += kConsumerThreads) {
+    const int idx = idx0 + tid;
+    const int m = idx >> 7, c = idx & 127, n = nblk * 128 + c;
+    float rf = 0.f;
+    if (idx < items && n < p.N) {
+      float v[16];
+#pragma unroll
+      for (int sp = 0; sp < 16; ++sp) v[sp] = sp < p.S ? __ldcg(p.out + ((size_t)sp * p.M + m) * p.ldo + n) : 0.f;
+      float r = __bfloat162float(p.fold_resid_in[(size_t)m * p.N + n]);
+#pragma unroll
+      for (int sp = 0; sp < 16; ++sp) r += v[sp];
+      const __nv_bfloat16 rb = __float2bfloat16(r);
+      p.fold_resid_out[(size_t)m * p.N + n] = rb;
+      rf = __bfloat162float(rb);
+    }
+    const float ss = warp_sum(rf * rf);  // a warp's 32 columns belong to one row
+    if (lane == 0 && idx < items) asm volatile("st.shared.f32 [%0], %1;" ::"r"(ring + (m * 4 + (c >> 5)) * 4), "f"(ss) : "memory");
+  }
+  consumer_sync();
+  if (tid < p.M) {
+    float4 q4;
+    asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(q4.x), "=f"(q4.y), "=f"(q4.z), "=f"(q4.w) : "r"(ring + tid * 16));
+    p.fold_ssq[(size_t)tid * nb_total + nblk] = ((q4.x + q4.y) + q4.z) + q4.w;
+  }
 }
 
 template <int T>
@@ -328,12 +401,12 @@ int launch_t(GemvParams& p, cudaStream_t stream) {
   if (xcg > p.gps) xcg = p.gps;
   if (xcg < 2) xcg = 2;
   p.xcg = xcg;
-  const int smem = 128 + kRingBytes + 128 + ((xcg * 8 * T * 4 + 127) & ~127) + rows * stride_words(xcg) * 4;
+  const int smem = 128 + kRingBytes + 128 + 256 + ((xcg * 8 * T * 4 + 127) & ~127) + rows * stride_words(xcg) * 4;
   static int configured[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   if (configured[dev & 63] < smem) {
-    const int want = 128 + kRingBytes + 128 + 8192 + kXBudget + 4096;
+    const int want = 128 + kRingBytes + 128 + 256 + 8192 + kXBudget + 4096;
     cudaError_t e = cudaFuncSetAttribute(gemv_w4_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, want);
     if (e != cudaSuccess) return (int)e;
     configured[dev & 63] = want;
@@ -368,10 +441,40 @@ extern "C" int b2_gemv_w4(const void* w4b, const void* x, float* out, int M, int
   p.x = x;
   p.out = out;
   p.batches = 1; p.expert_ids = nullptr; p.expert_bytes = 0; p.x_div = 1; p.x_batch_bytes = 0; p.out_batch = 0;
+  p.fold_tickets = nullptr; p.fold_resid_in = nullptr; p.fold_resid_out = nullptr; p.fold_ssq = nullptr;
+  p.norm_w = nullptr; p.norm_ssq = nullptr; p.norm_nb = 0; p.norm_eps = 0.f;
   p.M = M; p.N = N; p.KG = K / 64; p.S = S;
   p.gps = (p.KG + S - 1) / S;
   if (p.gps % kG != 0) p.gps += kG - p.gps % kG;   // splits start on a stage boundary
   p.ldx = ldx; p.ldo = ldo; p.x_mode = x_mode; p.s_in = s_in; p.x_slice = x_slice;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (M <= 8) return launch_t<1>(p, st);
+  if (M <= 16) return launch_t<2>(p, st);
+  if (M <= 32) return launch_t<4>(p, st);
+  return launch_t<8>(p, st);
+}
+
+// Fused form for the dense decode layers.  x_mode 2 normalises the residual stream while staging it
+// (norm_w, norm_ssq [M][K/128], eps); fold_* make the kernel's last split CTA per n-block add the
+// slices to the residual (N must be the residual width) and leave the per-block sums of squares.
+extern "C" int b2_gemv_w4_fused(const void* w4b, const void* x, float* out, int M, int N, int K, int S, int ldx,
+                                int x_mode, int s_in, long long x_slice, const float* norm_w, const float* norm_ssq,
+                                float norm_eps, int* fold_tickets, const void* fold_resid_in, void* fold_resid_out,
+                                float* fold_ssq, void* stream) {
+  if (M < 1 || M > 64 || K % 64 != 0 || S < 1) return -1;
+  if (x_mode == 2 && (K % 128 != 0 || !norm_w || !norm_ssq)) return -2;
+  GemvParams p;
+  p.w = reinterpret_cast<const uint8_t*>(w4b);
+  p.x = x;
+  p.out = out;
+  p.M = M; p.N = N; p.KG = K / 64; p.S = S;
+  p.gps = (p.KG + S - 1) / S;
+  if (p.gps % kG != 0) p.gps += kG - p.gps % kG;
+  p.ldx = ldx; p.ldo = N; p.x_mode = x_mode; p.s_in = s_in; p.x_slice = x_slice;
+  p.batches = 1; p.expert_ids = nullptr; p.expert_bytes = 0; p.x_div = 1; p.x_batch_bytes = 0; p.out_batch = 0;
+  p.fold_tickets = fold_tickets; p.fold_resid_in = (const __nv_bfloat16*)fold_resid_in;
+  p.fold_resid_out = (__nv_bfloat16*)fold_resid_out; p.fold_ssq = fold_ssq;
+  p.norm_w = norm_w; p.norm_ssq = norm_ssq; p.norm_nb = K / 128; p.norm_eps = norm_eps;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   if (M <= 8) return launch_t<1>(p, st);
   if (M <= 16) return launch_t<2>(p, st);
@@ -395,6 +498,8 @@ extern "C" int b2_gemv_w4_experts(const void* w4b_stack, long long expert_bytes,
   p.ldx = ldx; p.ldo = N; p.x_mode = x_mode; p.s_in = s_in; p.x_slice = x_slice;
   p.batches = batches; p.expert_ids = expert_ids; p.expert_bytes = expert_bytes; p.x_div = x_div;
   p.x_batch_bytes = x_batch_bytes; p.out_batch = (long long)S * N;
+  p.fold_tickets = nullptr; p.fold_resid_in = nullptr; p.fold_resid_out = nullptr; p.fold_ssq = nullptr;
+  p.norm_w = nullptr; p.norm_ssq = nullptr; p.norm_nb = 0; p.norm_eps = 0.f;
   return launch_t<1>(p, reinterpret_cast<cudaStream_t>(stream));
 }
 

@@ -121,6 +121,20 @@ def gemv_w4(w4b: torch.Tensor, x: torch.Tensor, out: torch.Tensor, m: int, n: in
     _check(rc, "gemv_w4")
 
 
+def gemv_w4_fused(w4b, x, out, m, n, k, splits, *, x_mode=0, s_in=1, x_slice=0, ldx=None, norm_w=None, norm_ssq=None,
+                  norm_eps=0.0, fold_tickets=None, fold_resid=None, fold_ssq=None):
+    """The GEMV with its neighbours folded in.  ``x_mode`` 2: ``x`` is the bf16 residual stream and the
+    kernel applies RMSNorm (``norm_w``, per-block sums of squares ``norm_ssq``) while staging it.
+    ``fold_*``: the last split CTA of each 128-column block adds the split-K slices to ``fold_resid``
+    in place and leaves that block's sum of squares in ``fold_ssq`` ``[m][n/128]``."""
+    if ldx is None:
+        ldx = 2 * k if x_mode == 1 else k
+    rc = lib().b2_gemv_w4_fused(_p(w4b), _p(x), _p(out), m, n, k, splits, ldx, x_mode, s_in, ctypes.c_longlong(x_slice),
+                                _p(norm_w), _p(norm_ssq), ctypes.c_float(norm_eps), _p(fold_tickets), _p(fold_resid),
+                                _p(fold_resid), _p(fold_ssq), _stream())
+    _check(rc, "gemv_w4_fused")
+
+
 def resid_norm(mode: int, m: int, h: int, w: torch.Tensor, eps: float, resid_out: torch.Tensor,
                x_out: Optional[torch.Tensor], *, embed=None, ctrl=None, vocab=0, resid_in=None, part=None,
                part_slice=0, splits=0, flag=None):
@@ -139,12 +153,14 @@ def rope_append(qkv_part, slice_elems, splits, m, ctrl, block_table, max_blocks,
 
 
 def attn_decode(q, k_cache, v_cache, block_table, ctrl, o_part, ml_part, out, m, n_q, n_kv, d, nsplit, max_blocks,
-                scale, k_scale=None, v_scale=None, kv_int8=False):
+                scale, k_scale=None, v_scale=None, kv_int8=False, tickets=None):
+    """Split-KV decode attention.  With ``tickets`` (zeroed int32 ``[rows][n_kv]``) the last split CTA of
+    each (row, KV head) merges the splits inside the kernel; without, a second kernel merges."""
     global launch_count
     rc = lib().b2_attn_decode(_p(q), _p(k_cache), _p(v_cache), _p(k_scale), _p(v_scale), _p(block_table), _p(ctrl),
                               _p(o_part), _p(ml_part), _p(out), m, n_q, n_kv, d, nsplit, max_blocks,
-                              ctypes.c_float(scale), int(kv_int8), _stream())
-    launch_count += 1
+                              ctypes.c_float(scale), int(kv_int8), _p(tickets), _stream())
+    launch_count += 0 if tickets is not None else 1
     _check(rc, "attn_decode")
 
 

@@ -220,3 +220,72 @@ def test_head_gemv_and_argmax(int8):
     assert got[0, 17] == got[0, 600]
     assert c[k_.CTRL_CUR_TOKEN: k_.CTRL_CUR_TOKEN + m].tolist() == idx.tolist()
     assert c[k_.CTRL_ROW_POS: k_.CTRL_ROW_POS + m].tolist() == [11 + i for i in range(m)]
+
+
+def test_attn_decode_fused_merge_equals_separate_merge():
+    k_ = K()
+    torch.manual_seed(21)
+    n_q, n_kv, d, ctx, m, nsplit = 40, 8, 128, 1500, 2, 16
+    max_blocks = (ctx + 15) // 16 + 1
+    num_pages = max_blocks + 2
+    table = torch.zeros(1, max_blocks, dtype=torch.int32)
+    table[0, : max_blocks - 1] = torch.randperm(num_pages - 1)[: max_blocks - 1].to(torch.int32) + 1
+    table = table.cuda()
+    kc = (torch.randn(num_pages, n_kv, 16, d, device="cuda") * 0.5).to(torch.bfloat16)
+    vc = (torch.randn(num_pages, n_kv, 16, d, device="cuda") * 0.5).to(torch.bfloat16)
+    q = torch.randn(m, n_q * d, device="cuda").to(torch.bfloat16)
+    ctrl = _ctrl([(0, ctx - m + i, 0) for i in range(m)])
+    o_part = torch.zeros(m * n_q * nsplit * d, device="cuda")
+    ml = torch.zeros(m * n_q * nsplit * 2, device="cuda")
+    ref = torch.zeros(m, n_q * d, dtype=torch.bfloat16, device="cuda")
+    k_.attn_decode(q, kc, vc, table, ctrl, o_part, ml, ref, m, n_q, n_kv, d, nsplit, max_blocks, d ** -0.5)
+    tickets = torch.zeros(m * n_kv, dtype=torch.int32, device="cuda")
+    for _ in range(3):          # the counters return to zero by themselves
+        out = torch.full_like(ref, float("nan"))
+        k_.attn_decode(q, kc, vc, table, ctrl, o_part, ml, out, m, n_q, n_kv, d, nsplit, max_blocks, d ** -0.5,
+                       tickets=tickets)
+        torch.cuda.synchronize()
+        # same sums, different association of the final division: equal to rounding
+        assert (out.float() - ref.float()).abs().max() <= 2e-2 * ref.float().abs().max()
+        assert int(tickets.abs().sum()) == 0
+    k_.check_status()
+
+
+@pytest.mark.parametrize("m", [1, 5, 20])
+def test_gemv_fused_fold_and_norm(m):
+    """o-projection style GEMV that folds into the residual, then a GEMV that normalises while staging."""
+    k_ = K()
+    torch.manual_seed(31 + m)
+    h, kin, n2 = 1024, 512, 768
+    w1 = torch.randn(h, kin) * 0.02
+    q1, s1 = Q.quantize_rtn(w1)
+    w2 = torch.randn(n2, h) * 0.02
+    q2, s2 = Q.quantize_rtn(w2)
+    a = torch.randn(m, kin).to(torch.bfloat16)
+    resid = torch.randn(m, h).to(torch.bfloat16)
+    nw = (1 + 0.1 * torch.randn(h))
+    sp1, sp2 = k_.gemv_splits(h, kin), k_.gemv_splits(n2, h)
+    part1 = torch.zeros(sp1, m, h, device="cuda")
+    tickets = torch.zeros(h // 128, dtype=torch.int32, device="cuda")
+    ssq = torch.zeros(m, h // 128, device="cuda")
+    r_dev = resid.cuda().clone()
+    for rep in range(2):        # tickets reset themselves; the second pass folds again on top
+        k_.gemv_w4_fused(Q.to_w4b(q1, s1).cuda(), a.cuda(), part1, m, h, kin, sp1, fold_tickets=tickets,
+                         fold_resid=r_dev, fold_ssq=ssq)
+    torch.cuda.synchronize()
+    y = a.float() @ Q.dequant(q1, s1).t()
+    r1 = (resid.float() + y).to(torch.bfloat16)
+    r2 = (r1.float() + y).to(torch.bfloat16)
+    assert (r_dev.float().cpu() - r2.float()).abs().max() <= 0.02 * r2.float().abs().max()
+    got_ssq = ssq.sum(1).cpu()
+    assert torch.allclose(got_ssq, r_dev.float().cpu().pow(2).sum(1), rtol=1e-4)
+    assert int(tickets.abs().sum()) == 0
+    part2 = torch.zeros(sp2, m, n2, device="cuda")
+    k_.gemv_w4_fused(Q.to_w4b(q2, s2).cuda(), r_dev, part2, m, n2, h, sp2, x_mode=2, norm_w=nw.cuda(), norm_ssq=ssq,
+                     norm_eps=1e-6)
+    torch.cuda.synchronize()
+    k_.check_status()
+    rf = r_dev.float().cpu()
+    xn = (rf * torch.rsqrt(rf.pow(2).mean(-1, keepdim=True) + 1e-6) * nw).to(torch.bfloat16).float()
+    ref = xn @ Q.dequant(q2, s2).t()
+    assert (part2.sum(0).cpu() - ref).abs().max() <= 5e-3 * ref.abs().max() + 1e-4
