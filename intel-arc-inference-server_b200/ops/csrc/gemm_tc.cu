@@ -279,12 +279,13 @@ __global__ void __launch_bounds__(256) dequant_w4b_kernel(const uint8_t* __restr
     const int row = warp * 16 + g + 8 * (c & 1);
     const float s = (c & 1) ? s_hi : s_lo;
 #pragma unroll
-    for (int e = 0; e < 4; ++e) {  // e: (step h = e >> 1, half = e & 1)
-      const uint32_t x = (wa[c] >> (4 * ((e >> 1) * 2 + (e & 1)))) & 0x000F000Fu;
-      const float f0 = (float)((int)(x & 0xFFFF) - 8) * s, f1 = (float)((int)(x >> 16) - 8) * s;
-      const int step = 2 * (c >> 1) + (e >> 1);
-      const int kpair = (16 * step + 2 * t + 8 * (e & 1)) >> 1;
+    for (int e = 0; e < 2; ++e) {  // e = 0: low nibbles (k = 4t + b of the 32-k step), 1: high nibbles (+ 16)
+      const uint32_t x = (wa[c] >> (4 * e)) & 0x0F0F0F0Fu;
+      const float f0 = (float)((int)(x & 0xFF) - 8) * s, f1 = (float)((int)((x >> 8) & 0xFF) - 8) * s;
+      const float f2 = (float)((int)((x >> 16) & 0xFF) - 8) * s, f3 = (float)((int)(x >> 24) - 8) * s;
+      const int kpair = (32 * (c >> 1) + 16 * e + 4 * t) >> 1;
       tile[row][kpair] = pack_bf16(f0, f1);
+      tile[row][kpair + 1] = pack_bf16(f2, f3);
     }
   }
   __syncthreads();

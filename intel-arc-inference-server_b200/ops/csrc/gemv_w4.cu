@@ -10,16 +10,20 @@
 // 8-stage shared-memory ring guarded by mbarriers; the copies are issued BEFORE
 // griddepcontrol.wait, so under programmatic dependent launch the weights of this
 // linear are already in flight while the previous kernel finishes.  Eight
-// consumer warps each own 16 output rows: they read their 16 bytes per lane,
-// expand nibbles to the exact bf16 integers 128 + q with one shift and one logic
-// op per pair, and feed mma.m16n8k16 with the weights as the 16-row operand and up
-// to 8 tokens as the 8-column operand (tokens beyond 8 reuse the expanded
-// registers, so the weights are read once for any M: weight-stationary).  The
-// zero point is folded in after the MMAs (sum x (q - 8) = sum x (128 + q) - 136
-// sum x, with the per-group sums of x made once while staging the activations)
-// and group scales are applied in fp32 to the per-group partial sums.  The inner
-// loop is bound by the integer pipe, so everything else is kept off it: explicit
-// 32-bit shared-memory addresses, vector loads of the B operand, paired scales.
+// consumer warps each own 16 output rows.  The inner loop of such a kernel is
+// bound by instruction issue (expanding nibbles to a floating-point operand costs
+// more integer instructions than the copy engine leaves time for), so the
+// contraction runs on the integer tensor path instead: the nibbles q = 0..15 are
+// used AS unsigned 8-bit operands (a 32-bit word of eight nibbles becomes two
+// operand registers with three logic instructions), and each token's activations
+// are quantised per 64-k group, while they are staged, to 15-bit integers with one
+// fp32 scale, X = 128 X_hi + X_lo, two signed 8-bit limbs.  mma.m16n8k32.u8.s8 takes
+// the weights as the 16-row operand and up to 8 tokens as the 8-column operand
+// (tokens beyond 8 reuse the weight registers: weight-stationary for any M); four
+// MMAs per group and token tile give exact integer sums, the zero point is folded by
+// starting the low-limb accumulator at -8 sum(X), and the group's weight scale times
+// the token's activation scale is applied in fp32.  The activation grid is 2^-14 of
+// the group's largest value: finer than the bf16 the activations arrive in.
 // Split-K slices are written separately and summed by the consumer kernel in a
 // fixed order: no atomics, bitwise reproducible, and a row's result does not
 // depend on M (the split count is a function of N and K only) -- the
@@ -91,13 +95,24 @@ __device__ __forceinline__ void sts32(uint32_t a, uint32_t v) {
   asm volatile("st.shared.u32 [%0], %1;" ::"r"(a), "r"(v) : "memory");
 }
 
+// One warp-level integer MMA: D (16 x 8, s32) += A (16 x 32, u8, rows) x B (32 x 8, s8, columns).
+__device__ __forceinline__ void mma_u8s8_16832(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                               uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
 // NG quantisation groups (64 k each, consecutive blocks of one ring stage) of one 16-row tile against
-// T token tiles.  The groups are worked on together and each keeps two accumulators (k16 steps 0, 2
-// and 1, 3), so 2 NG independent MMA chains are in flight instead of one chain of four.
+// T token tiles.  A group's activations are 15-bit integers X = 128 X_hi + X_lo with one fp32 scale;
+// the nibbles q (0..15) are the unsigned operand as they are, so a 32-bit word of eight nibbles
+// becomes two operand registers with three integer instructions.  The low-limb accumulator starts
+// at -8 sum(X), which folds the zero point.  2 NG T independent MMA chains are in flight.
 template <int T, int NG>
 __device__ __forceinline__ void group_mma(float (&acc)[T][4], uint32_t blk_addr, uint32_t w_off, uint32_t sc_off,
                                           const uint32_t (&x_addr)[T], uint32_t gs_addr) {
-  constexpr uint32_t kMagic = 0x43004300u, kMask = 0x000F000Fu;
+  constexpr uint32_t kMask = 0x0F0F0F0Fu;
   uint4 wv[NG];
   uint32_t sc2[NG];
 #pragma unroll
@@ -105,48 +120,32 @@ __device__ __forceinline__ void group_mma(float (&acc)[T][4], uint32_t blk_addr,
     wv[q] = lds128(blk_addr + q * kBlockBytes + w_off);
     sc2[q] = lds32(blk_addr + q * kBlockBytes + sc_off);  // scales of rows g and g + 8 (stored as a pair)
   }
-  float ag[NG][2][T][4];
-#pragma unroll
-  for (int q = 0; q < NG; ++q)
-#pragma unroll
-    for (int c = 0; c < 2; ++c)
-#pragma unroll
-      for (int tt = 0; tt < T; ++tt) ag[q][c][tt][0] = ag[q][c][tt][1] = ag[q][c][tt][2] = ag[q][c][tt][3] = 0.f;
-#pragma unroll
-  for (int pr = 0; pr < 2; ++pr) {
-    uint4 xb[NG][T];
-#pragma unroll
-    for (int q = 0; q < NG; ++q)
-#pragma unroll
-      for (int tt = 0; tt < T; ++tt) xb[q][tt] = lds128(x_addr[tt] + q * 128 + pr * 16);
-#pragma unroll
-    for (int h = 0; h < 2; ++h) {
-#pragma unroll
-      for (int q = 0; q < NG; ++q) {
-        const uint32_t w0 = pr ? wv[q].z : wv[q].x, w1 = pr ? wv[q].w : wv[q].y;
-        const uint32_t a0 = ((w0 >> (8 * h)) & kMask) | kMagic;
-        const uint32_t a1 = ((w1 >> (8 * h)) & kMask) | kMagic;
-        const uint32_t a2 = ((w0 >> (8 * h + 4)) & kMask) | kMagic;
-        const uint32_t a3 = ((w1 >> (8 * h + 4)) & kMask) | kMagic;
-#pragma unroll
-        for (int tt = 0; tt < T; ++tt) {
-          const uint32_t b0 = h ? xb[q][tt].z : xb[q][tt].x, b1 = h ? xb[q][tt].w : xb[q][tt].y;
-          mma_bf16_16816(ag[q][h][tt], a0, a1, a2, a3, b0, b1);
-        }
-      }
-    }
-  }
 #pragma unroll
   for (int q = 0; q < NG; ++q) {
+    // words 0, 1: k 0..31 of rows g, g + 8;  words 2, 3: k 32..63.  Low nibbles are k 4t + b, high
+    // nibbles k 16 + 4t + b of the 32-k step: exactly the a0/a1 and a2/a3 registers of the MMA.
+    const uint32_t l0 = wv[q].x & kMask, l1 = wv[q].y & kMask, l2 = wv[q].z & kMask, l3 = wv[q].w & kMask;
+    const uint32_t h0 = (wv[q].x >> 4) & kMask, h1 = (wv[q].y >> 4) & kMask;
+    const uint32_t h2 = (wv[q].z >> 4) & kMask, h3 = (wv[q].w >> 4) & kMask;
     const __half2 sh = *reinterpret_cast<const __half2*>(&sc2[q]);
     const float s_lo = __low2float(sh), s_hi = __high2float(sh);
 #pragma unroll
     for (int tt = 0; tt < T; ++tt) {
-      const float2 sx = lds64f(gs_addr + q * 8 * T * 4 + tt * 32);  // sums of x for tokens 8 tt + 2t, + 1
-      acc[tt][0] = fmaf(s_lo, fmaf(-136.f, sx.x, ag[q][0][tt][0] + ag[q][1][tt][0]), acc[tt][0]);
-      acc[tt][1] = fmaf(s_lo, fmaf(-136.f, sx.y, ag[q][0][tt][1] + ag[q][1][tt][1]), acc[tt][1]);
-      acc[tt][2] = fmaf(s_hi, fmaf(-136.f, sx.x, ag[q][0][tt][2] + ag[q][1][tt][2]), acc[tt][2]);
-      acc[tt][3] = fmaf(s_hi, fmaf(-136.f, sx.y, ag[q][0][tt][3] + ag[q][1][tt][3]), acc[tt][3]);
+      const uint4 xh = lds128(x_addr[tt] + q * 128);       // high limbs: step 0 (b0, b1), step 1 (b0, b1)
+      const uint4 xl = lds128(x_addr[tt] + q * 128 + 16);  // low limbs
+      // (scale, -8 sum X) of tokens 8 tt + 2t and + 1
+      const uint4 gs = lds128(gs_addr + (q * 8 * T + tt * 8) * 8);
+      int ih[4] = {0, 0, 0, 0};
+      int il[4] = {(int)gs.y, (int)gs.w, (int)gs.y, (int)gs.w};
+      mma_u8s8_16832(ih, l0, l1, h0, h1, xh.x, xh.y);
+      mma_u8s8_16832(il, l0, l1, h0, h1, xl.x, xl.y);
+      mma_u8s8_16832(ih, l2, l3, h2, h3, xh.z, xh.w);
+      mma_u8s8_16832(il, l2, l3, h2, h3, xl.z, xl.w);
+      const float sx0 = __uint_as_float(gs.x), sx1 = __uint_as_float(gs.z);
+      acc[tt][0] = fmaf(s_lo * sx0, (float)(ih[0] * 128 + il[0]), acc[tt][0]);
+      acc[tt][1] = fmaf(s_lo * sx1, (float)(ih[1] * 128 + il[1]), acc[tt][1]);
+      acc[tt][2] = fmaf(s_hi * sx0, (float)(ih[2] * 128 + il[2]), acc[tt][2]);
+      acc[tt][3] = fmaf(s_hi * sx1, (float)(ih[3] * 128 + il[3]), acc[tt][3]);
     }
   }
 }
@@ -158,8 +157,8 @@ __global__ void __launch_bounds__(kThreads, (T <= 2 ? 2 : 1)) gemv_w4_kernel(con
   const uint32_t ring = smem0;
   const uint32_t bars = smem0 + kRingBytes;               // 16 mbarriers
   const uint32_t rinv0 = bars + 128;                      // float [64] per-row 1/rms (x_mode 2)
-  const uint32_t gs0 = rinv0 + 256;                       // float [xcg][8 T] group sums of x
-  const uint32_t xs0 = gs0 + ((p.xcg * 8 * T * 4 + 127) & ~127);  // bf16 rows, permuted per group
+  const uint32_t gs0 = rinv0 + 256;                       // {float scale, int -8 sum X} [xcg][8 T]
+  const uint32_t xs0 = gs0 + ((p.xcg * 8 * T * 8 + 127) & ~127);  // int8 limbs of the rows, in operand order
   const uint32_t full0 = bars, empty0 = bars + 8 * kStages;
   const int strideB = stride_words(p.xcg) * 4;
 
@@ -227,7 +226,7 @@ __global__ void __launch_bounds__(kThreads, (T <= 2 ? 2 : 1)) gemv_w4_kernel(con
   uint32_t x_row[T];
 #pragma unroll
   for (int tt = 0; tt < T; ++tt) x_row[tt] = xs0 + min(tt * 8 + g, p.rows - 1) * strideB + t * 32;
-  const uint32_t gs_t = gs0 + 2 * t * 4;
+  const uint32_t gs_t = gs0 + 2 * t * 8;
 
   if (p.x_mode == 2) {
     // 1 / rms of each row from the per-block sums the producing kernel left (summed in block order)
@@ -284,22 +283,51 @@ __global__ void __launch_bounds__(kThreads, (T <= 2 ? 2 : 1)) gemv_w4_kernel(con
             val.w = pack_bf16(silu(gsum[6]) * usum[6], silu(gsum[7]) * usum[7]);
           }
         }
-        // Word (step, half, t) of a group is stored at t * 8 + step * 2 + half, so that lane (g, t) of
-        // the main loop reads its eight B-operand words of the group with two 16-byte loads.
-        float sum = bf16_lo(val.x) + bf16_hi(val.x) + bf16_lo(val.y) + bf16_hi(val.y) + bf16_lo(val.z) +
-                    bf16_hi(val.z) + bf16_lo(val.w) + bf16_hi(val.w);
-        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-        sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-        sum += __shfl_xor_sync(0xffffffffu, sum, 4);
+        // Quantise the group's 64 activations (as rounded to bf16) to 15-bit integers with one scale,
+        // X = rint(x * 16383 / amax) = 128 X_hi + X_lo with X_hi in [-128, 127] and X_lo in [0, 127].
+        // The eight lanes that hold a group share amax and sum(X) by shuffles.
+        float xf[8] = {bf16_lo(val.x), bf16_hi(val.x), bf16_lo(val.y), bf16_hi(val.y),
+                       bf16_lo(val.z), bf16_hi(val.z), bf16_lo(val.w), bf16_hi(val.w)};
+        float amax = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(xf[i]));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
+        const bool live = amax > 0.f && amax < 3.0e38f;
+        const float inv = live ? 16383.f / amax : 0.f;
+        int X[8], sumX = 0;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          X[i] = __float2int_rn(xf[i] * inv);
+          sumX += X[i];
+        }
+        sumX += __shfl_xor_sync(0xffffffffu, sumX, 1);
+        sumX += __shfl_xor_sync(0xffffffffu, sumX, 2);
+        sumX += __shfl_xor_sync(0xffffffffu, sumX, 4);
         if (v < total) {
-          const int step = (col & 7) >> 1, half = col & 1;
-          const uint32_t dst = xs0 + row * strideB + ((col >> 3) * 32 + step * 2 + half) * 4;
-          sts32(dst, val.x);
-          sts32(dst + 32, val.y);
-          sts32(dst + 64, val.z);
-          sts32(dst + 96, val.w);
-          // sum of the group's 64 activations as rounded to bf16: folds the zero point
-          if ((col & 7) == 0) asm volatile("st.shared.f32 [%0], %1;" ::"r"(gs0 + ((col >> 3) * 8 * T + row) * 4), "f"(sum) : "memory");
+          uint32_t hiA = 0, hiB = 0, loA = 0, loB = 0;
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            hiA |= (uint32_t)((X[i] >> 7) & 0xff) << (8 * i);
+            loA |= (uint32_t)(X[i] & 127) << (8 * i);
+            hiB |= (uint32_t)((X[i + 4] >> 7) & 0xff) << (8 * i);
+            loB |= (uint32_t)(X[i + 4] & 127) << (8 * i);
+          }
+          // k = 8 vq .. 8 vq + 7 of the group: 32-k step vq >> 2, operand register (vq & 3) >> 1, lanes
+          // t = 2 (vq & 1) and + 1.  Lane t's words sit at t * 8 + limb * 4 + step * 2 + register, so
+          // the main loop reads a limb's four words with one 16-byte load.
+          const int vq = col & 7;
+          const uint32_t dst = xs0 + row * strideB + ((col >> 3) * 32 + (vq & 1) * 16 + (vq >> 2) * 2 + ((vq & 3) >> 1)) * 4;
+          sts32(dst, hiA);
+          sts32(dst + 16, loA);
+          sts32(dst + 32, hiB);
+          sts32(dst + 48, loB);
+          if (vq == 0) {
+            const uint32_t ga = gs0 + ((col >> 3) * 8 * T + row) * 8;
+            asm volatile("st.shared.v2.u32 [%0], {%1, %2};" ::"r"(ga), "r"(__float_as_uint(live ? amax / 16383.f : 0.f)),
+                         "r"((uint32_t)(-8 * sumX)) : "memory");
+          }
         }
       }
     }
@@ -317,12 +345,12 @@ __global__ void __launch_bounds__(kThreads, (T <= 2 ? 2 : 1)) gemv_w4_kernel(con
       uint32_t xa[T];
 #pragma unroll
       for (int tt = 0; tt < T; ++tt) xa[tt] = x_row[tt] + gi * 128;
-      if (gi + 1 < cg) group_mma<T, (T <= 2 ? 2 : 1)>(acc, st, w_off, sc_off, xa, gs_t + gi * 8 * T * 4);
-      else group_mma<T, 1>(acc, st, w_off, sc_off, xa, gs_t + gi * 8 * T * 4);
+      if (gi + 1 < cg) group_mma<T, (T <= 2 ? 2 : 1)>(acc, st, w_off, sc_off, xa, gs_t + gi * 8 * T * 8);
+      else group_mma<T, 1>(acc, st, w_off, sc_off, xa, gs_t + gi * 8 * T * 8);
       if (T > 2 && gi + 1 < cg) {
 #pragma unroll
         for (int tt = 0; tt < T; ++tt) xa[tt] += 128;
-        group_mma<T, 1>(acc, st + kBlockBytes, w_off, sc_off, xa, gs_t + (gi + 1) * 8 * T * 4);
+        group_mma<T, 1>(acc, st + kBlockBytes, w_off, sc_off, xa, gs_t + (gi + 1) * 8 * T * 8);
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(empty0 + 8 * s);
@@ -398,15 +426,16 @@ int launch_t(GemvParams& p, cudaStream_t stream) {
   p.rows = rows;
   int xcg = (kXBudget / (rows * 2) - 8) / 64;
   xcg &= ~1;
+  if (xcg > 160) xcg = 160;   // keeps two CTAs per SM at one staged row
   if (xcg > p.gps) xcg = p.gps;
   if (xcg < 2) xcg = 2;
   p.xcg = xcg;
-  const int smem = 128 + kRingBytes + 128 + 256 + ((xcg * 8 * T * 4 + 127) & ~127) + rows * stride_words(xcg) * 4;
+  const int smem = 128 + kRingBytes + 128 + 256 + ((xcg * 8 * T * 8 + 127) & ~127) + rows * stride_words(xcg) * 4;
   static int configured[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   if (configured[dev & 63] < smem) {
-    const int want = 128 + kRingBytes + 128 + 256 + 8192 + kXBudget + 4096;
+    const int want = 128 + kRingBytes + 128 + 256 + 16384 + kXBudget + 4096;
     cudaError_t e = cudaFuncSetAttribute(gemv_w4_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, want);
     if (e != cudaSuccess) return (int)e;
     configured[dev & 63] = want;

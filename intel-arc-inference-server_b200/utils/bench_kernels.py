@@ -42,7 +42,7 @@ def time_ms(fn, iters=20, warmup=3):
     return e0.elapsed_time(e1) / iters
 
 
-def bench_gemv(ms_list=(1, 4, 8, 16, 64), only=None, iters_mult=4):
+def bench_gemv(ms_list=(1, 4, 8, 16, 64), only=None, iters_mult=4, graph=False):
     hbm, _, src = peaks()
     shapes = [("qkv", 7168, 5120), ("o", 5120, 5120), ("gate_up", 34816, 5120), ("down", 5120, 17408)]
     for name, n, k in shapes:
@@ -61,6 +61,14 @@ def bench_gemv(ms_list=(1, 4, 8, 16, 64), only=None, iters_mult=4):
                 K.gemv_w4(ws[it[0] % copies], x, out, m, n, k, s)
                 it[0] += 1
             ms = time_ms(fn, iters=max(2, iters_mult * copies))
+            if graph:
+                # the same launches inside a CUDA graph: no host launch cost between kernels
+                n_in = 4 * copies
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g):
+                    for _ in range(n_in):
+                        fn()
+                ms = time_ms(g.replay, iters=5) / n_in
             gbs = nbytes / ms / 1e6
             print(f"gemv_w4 {name:8s} N={n:6d} K={k:6d} M={m:3d} S={s:2d}  {ms * 1e3:8.2f} us  {gbs:8.1f} GB/s  "
                   f"{gbs / hbm:5.2f} of {src} HBM copy bandwidth")
@@ -100,5 +108,7 @@ if __name__ == "__main__":
     what = sys.argv[1] if len(sys.argv) > 1 else "gemv"
     if what == "gemv-one":      # one shape, one M, few launches: the target of an ncu capture
         bench_gemv((int(sys.argv[3]),), only=sys.argv[2], iters_mult=1)
+    elif what == "gemv-graph":  # back-to-back launches inside a CUDA graph
+        bench_gemv((1, 4, 8), graph=True)
     else:
         {"gemv": bench_gemv, "gemm": bench_gemm}[what]()

@@ -13,13 +13,13 @@ blocks of 128 output rows x 64 input channels (one quantisation group).  A
 block is ``4352`` bytes: ``4096`` bytes of nibbles followed by the block's 128
 fp16 scales.  Blocks are stored ``[N/128][K/64]`` so a CTA that owns 128 output
 rows reads one contiguous stream along K.  Inside a block the nibbles are
-ordered for a warp-level ``mma.m16n8k16`` A operand: tile ``j`` (16 rows) owns
-512 bytes, lane ``l`` owns 16 bytes = words ``c = 0..3``; with ``g = l / 4``,
-``t = l % 4`` word ``c`` holds row ``16 j + g + 8 (c & 1)`` and the two k16
-steps ``s0 = 2 (c >> 1)``, ``s1 = s0 + 1`` of the group.  Nibble positions
-``0,4,1,5,2,6,3,7`` hold ``k = 16 s0 + 2t``, ``+1``, ``+8``, ``+9``, then the
-same four for ``s1``; a mask with ``0x000F000F`` after shifts by 0/4/8/12 then
-yields the four bf16x2 operand registers directly.  The 16 scales of a tile are
+ordered for the A operand of the warp-level 8-bit ``mma.m16n8k32``: tile ``j``
+(16 rows) owns 512 bytes, lane ``l`` owns 16 bytes = words ``c = 0..3``; with
+``g = l / 4``, ``t = l % 4`` word ``c`` holds row ``16 j + g + 8 (c & 1)`` and the
+32-k step ``c >> 1`` of the group.  Byte ``b`` of the word holds ``k = 32 (c >> 1) +
+4 t + b`` in its low nibble and ``k + 16`` in its high nibble, so a mask with
+``0x0F0F0F0F`` of the word and of the word shifted by 4 yields the operand
+registers (unsigned bytes 0..15) directly.  The 16 scales of a tile are
 stored as pairs ``(row g, row g + 8)`` so a lane reads its two scales as one
 32-bit word: position ``2 (r % 8) + r / 8`` holds the scale of tile row ``r``.
 """
@@ -87,10 +87,11 @@ def expand_group128(scales: torch.Tensor) -> torch.Tensor:
     return scales.repeat_interleave(2, dim=0)
 
 
-# nibble position p of a W4B word holds this k offset (relative to 16*s0 for the
-# first four, 16*s1 for the last four), given lane%4 = t: see module docstring.
-_NIB_STEP = (0, 0, 1, 1, 0, 0, 1, 1)     # which step (s0 / s1) nibble p belongs to
-_NIB_KOFF = (0, 8, 0, 8, 1, 9, 1, 9)     # k offset inside the step, plus 2t
+# Nibble position p (bits 4p .. 4p+3) of W4B word c of lane (g, t) holds row g + 8 (c & 1) and
+# k = 32 (c >> 1) + 4 t + _NIB_KOFF[p]: the low nibbles of the word's four bytes are k 4t .. 4t+3 of
+# the 32-k step, the high nibbles k 16+4t .. 16+4t+3 -- so ``w & 0x0F0F0F0F`` and
+# ``(w >> 4) & 0x0F0F0F0F`` are the a0/a1 and a2/a3 registers of ``mma.m16n8k32`` (8-bit operands).
+_NIB_KOFF = (0, 16, 1, 17, 2, 18, 3, 19)
 
 
 def _scale_perm(device):
@@ -121,8 +122,7 @@ def to_w4b(q: torch.Tensor, scales: torch.Tensor) -> torch.Tensor:
     p = torch.arange(8, device=dev).view(1, 1, 1, 8)
     g, t = lane // 4, lane % 4
     row = 16 * j + g + 8 * (c & 1) + 0 * p                      # [8,32,4,8]
-    step = 2 * (c >> 1) + torch.tensor(_NIB_STEP, device=dev).view(1, 1, 1, 8)
-    kk = 16 * step + 2 * t + torch.tensor(_NIB_KOFF, device=dev).view(1, 1, 1, 8) + 0 * j
+    kk = 32 * (c >> 1) + 4 * t + torch.tensor(_NIB_KOFF, device=dev).view(1, 1, 1, 8) + 0 * j
     row = row.expand(8, 32, 4, 8).reshape(-1)
     kk = kk.expand(8, 32, 4, 8).reshape(-1)
     qb = q.reshape(kg, GROUP, nb, BLOCK_N).permute(2, 0, 1, 3)   # [nb][kg][64 k][128 n]
@@ -150,8 +150,7 @@ def from_w4b(w4b: torch.Tensor, n: int):
     c = torch.arange(4, device=dev).view(1, 1, 4, 1)
     g, t = lane // 4, lane % 4
     row = (16 * j + g + 8 * (c & 1)).expand(8, 32, 4, 8).reshape(-1)
-    step = 2 * (c >> 1) + torch.tensor(_NIB_STEP, device=dev).view(1, 1, 1, 8)
-    kk = (16 * step + 2 * t + torch.tensor(_NIB_KOFF, device=dev).view(1, 1, 1, 8) + 0 * j)
+    kk = 32 * (c >> 1) + 4 * t + torch.tensor(_NIB_KOFF, device=dev).view(1, 1, 1, 8) + 0 * j
     kk = kk.expand(8, 32, 4, 8).reshape(-1)
     qb = torch.zeros(nb, kg, GROUP, BLOCK_N, dtype=torch.uint8, device=dev)
     qb[:, :, kk, row] = nibs.reshape(nb, kg, -1).to(torch.uint8)

@@ -59,12 +59,11 @@ def test_w4b_nibble_positions_match_mma_fragment():
                 wk = int(bk[j, lane, c]) & 0xFFFFFFFF
                 row = 16 * j + g_ + 8 * (c & 1)
                 assert all(((wr >> (4 * p)) & 15) == row % 16 for p in range(8))
-                for h in range(2):           # step s = 2 (c >> 1) + h
-                    step = 2 * (c >> 1) + h
-                    lo = (wk >> (8 * h)) & 0x000F000F          # a[0]/a[1]: k = 2t, 2t+1
-                    hi = (wk >> (8 * h + 4)) & 0x000F000F      # a[2]/a[3]: k = 2t+8, 2t+9
-                    assert lo & 0xFFFF == (16 * step + 2 * t) % 16 and lo >> 16 == (16 * step + 2 * t + 1) % 16
-                    assert hi & 0xFFFF == (16 * step + 2 * t + 8) % 16 and hi >> 16 == (16 * step + 2 * t + 9) % 16
+                lo = wk & 0x0F0F0F0F              # a0 / a1 of the 32-k step: k = 4t + b
+                hi = (wk >> 4) & 0x0F0F0F0F       # a2 / a3: k = 16 + 4t + b
+                for b in range(4):
+                    assert (lo >> (8 * b)) & 0xFF == (32 * (c >> 1) + 4 * t + b) % 16
+                    assert (hi >> (8 * b)) & 0xFF == (32 * (c >> 1) + 16 + 4 * t + b) % 16
 
 
 def test_random_w4b_statistics():
