@@ -64,6 +64,21 @@ class ModelConfig:
     def is_moe(self) -> bool:
         return self.n_experts > 0
 
+    def tp_shard(self, world: int) -> "ModelConfig":
+        """The shapes one rank of a ``world``-way tensor-parallel group holds: whole attention heads,
+        whole FFN interleave runs; hidden size and vocabulary stay (the lm_head is split by rows outside).
+        The reference's ``tp_card_desc`` does this for its two cards (src/model/model_desc.cc:252-285)."""
+        if world == 1:
+            return self
+        if self.n_q_heads % world or self.n_kv_heads % world:
+            raise ValueError(f"tensor parallel {world} does not divide {self.n_q_heads} q / {self.n_kv_heads} kv heads")
+        if self.ffn % (64 * world) or (self.shared_ffn and self.shared_ffn % (64 * world)):
+            raise ValueError(f"tensor parallel {world} does not divide FFN {self.ffn} into whole groups of 64")
+        import dataclasses
+        return dataclasses.replace(self, name=f"{self.name}/tp{world}", n_q_heads=self.n_q_heads // world,
+                                   n_kv_heads=self.n_kv_heads // world, ffn=self.ffn // world,
+                                   shared_ffn=self.shared_ffn // world)
+
     def linears(self):
         """Fused linear table of one decoder layer (attention + dense FFN part)."""
         h = self.hidden

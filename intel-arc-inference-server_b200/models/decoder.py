@@ -35,9 +35,10 @@ class LinearPlan:
 class StepBuffers:
     """Activations and split-K scratch of one step, sized once for ``max_rows``."""
 
-    def __init__(self, cfg: ModelConfig, max_rows: int, nsplit_attn: int, device):
+    def __init__(self, cfg: ModelConfig, max_rows: int, nsplit_attn: int, device, head_rows: Optional[int] = None):
         bf, f32 = torch.bfloat16, torch.float32
         h = cfg.hidden
+        head_rows = cfg.vocab if head_rows is None else head_rows
         self.max_rows = max_rows
         self.resid = torch.zeros(max_rows, h, dtype=bf, device=device)
         self.x = torch.zeros(max_rows, h, dtype=bf, device=device)
@@ -45,8 +46,8 @@ class StepBuffers:
         self.attn_out = torch.zeros(max_rows, cfg.q_dim, dtype=bf, device=device)
         self.o_part = torch.zeros(max_rows * cfg.n_q_heads * nsplit_attn * cfg.head_dim, dtype=f32, device=device)
         self.ml_part = torch.zeros(max_rows * cfg.n_q_heads * nsplit_attn * 2, dtype=f32, device=device)
-        self.logits = torch.zeros(max_rows, cfg.vocab, dtype=f32, device=device)
-        self.ncand = K.head_ncand(cfg.vocab)
+        self.logits = torch.zeros(max_rows, head_rows, dtype=f32, device=device)
+        self.ncand = K.head_ncand(head_rows)
         self.cand_val = torch.zeros(max_rows * self.ncand, dtype=f32, device=device)
         self.cand_idx = torch.zeros(max_rows * self.ncand, dtype=torch.int32, device=device)
         self.flag = torch.zeros(4, dtype=torch.int32, device=device)
@@ -86,13 +87,28 @@ class KVCache:
 
 class DecoderModel:
     def __init__(self, weights: ModelWeights, max_rows: int = 64, max_pos: int = 8192, nsplit_attn: int = 32,
-                 int8_head: bool = False):
+                 int8_head: bool = False, tp=None, nccl=None):
+        """``tp``: the wires of a tensor-parallel group (``parallel.symm.TpWires``); ``weights`` then hold this
+        rank's shard (``cfg.tp_shard``) and ``lm_head`` this rank's rows of the vocabulary."""
         self.w = weights
         self.cfg = cfg = weights.cfg
         self.device = weights.embed.device
         self.max_rows = max_rows
         self.nsplit_attn = nsplit_attn
-        self.buf = StepBuffers(cfg, max_rows, nsplit_attn, self.device)
+        self.tp = tp if tp is not None and tp.world > 1 else None
+        # ``nccl`` = (rank, world, group): the comparison path -- the same kernels, unfused, with NCCL
+        # all-reduces after the row-parallel linears and an NCCL gather for the arg-max
+        self.nccl = nccl if nccl is not None and nccl[1] > 1 else None
+        if self.nccl is not None:
+            self.vocab_offset_nccl = self.nccl[0] * ((cfg.vocab + self.nccl[1] - 1) // self.nccl[1])
+        self.head_rows = weights.lm_head.shape[0]
+        self.vocab_offset = 0
+        if self.tp is not None:
+            per = (cfg.vocab + tp.world - 1) // tp.world
+            self.vocab_offset = tp.rank * per
+            if max_rows > tp.mcap:
+                raise ValueError(f"max_rows {max_rows} exceeds the wires' row capacity {tp.mcap}")
+        self.buf = StepBuffers(cfg, max_rows, nsplit_attn, self.device, self.head_rows)
         cos, sin = rope_tables(cfg.head_dim, cfg.rope_theta, max_pos)
         self.cos_t, self.sin_t = cos.to(self.device).contiguous(), sin.to(self.device).contiguous()
         self.max_pos = max_pos
@@ -103,7 +119,10 @@ class DecoderModel:
             sc = wf.abs().amax(dim=1).clamp_min(1e-8) / 127.0
             weights.lm_head_i8 = (torch.round(wf / sc[:, None]).clamp_(-127, 127).to(torch.int8).contiguous(), sc.contiguous())
         self._splits = {}
-        self.fused = True     # dense layers: residual folds and norms ride inside the GEMVs
+        self.fused = self.nccl is None     # dense layers: residual folds and norms ride inside the GEMVs
+        if self.nccl is not None:
+            self._red = torch.zeros(max_rows * cfg.hidden, dtype=torch.float32, device=self.device)
+            self._gather = torch.zeros(self.nccl[1], max_rows, 2, dtype=torch.float32, device=self.device)
 
     # ------------------------------------------------------------------ pieces
     def _gemv(self, name: str, ql: QLinear, x: torch.Tensor, m: int, x_mode=0, s_in=1, x_slice=0):
@@ -142,7 +161,8 @@ class DecoderModel:
         K.gemv_w4_fused(ql.w4b, x, part, m, ql.n, ql.k, s, x_mode=x_mode, s_in=s_in, x_slice=x_slice,
                         norm_w=norm_w, norm_ssq=b.ssq if norm_w is not None else None, norm_eps=self.cfg.rms_eps,
                         fold_tickets=b.fold_tickets if fold else None, fold_resid=b.resid if fold else None,
-                        fold_ssq=b.ssq if fold else None)
+                        fold_ssq=b.ssq if fold else None, tp=self.tp.fold if (fold and self.tp is not None) else None,
+                        tp_mcap=self.tp.mcap if self.tp is not None else 0)
         return part, s
 
     def dense_layer_fused(self, lw: LayerWeights, li: int, m: int, ctrl, block_table, max_blocks, kv: KVCache,
@@ -178,6 +198,8 @@ class DecoderModel:
             for i, lw in enumerate(layers):
                 self.dense_layer_fused(lw, kv_layer0 + i, m, ctrl, block_table, max_blocks, kv, x_ready=(i == 0))
             return None, 0      # the residual stream is already folded
+        if self.tp is not None:
+            raise NotImplementedError("tensor parallel decode covers dense models whose hidden size is a multiple of 128")
         for i, lw in enumerate(layers):
             if pend is None:
                 if first_from_embed:
@@ -189,6 +211,7 @@ class DecoderModel:
                 K.resid_norm(1, m, h, lw.input_norm, cfg.rms_eps, b.resid, b.x, resid_in=b.resid, part=pend[0],
                              part_slice=m * h, splits=pend[1])
             po, so = self.attention_block(lw, kv_layer0 + i, m, ctrl, block_table, max_blocks, kv)
+            po, so = self._nccl_reduce(po, so, m)
             K.resid_norm(1, m, h, lw.post_norm, cfg.rms_eps, b.resid, b.x, resid_in=b.resid, part=po,
                          part_slice=m * h, splits=so)
             if lw.gate_up is not None:
@@ -196,7 +219,19 @@ class DecoderModel:
             else:
                 from . import moe as _moe
                 pend = _moe.moe_block_rows(self, lw, m)
+            pend = self._nccl_reduce(pend[0], pend[1], m)
         return pend
+
+    def _nccl_reduce(self, part, splits: int, m: int):
+        """Comparison path: sum the split slices, all-reduce the ranks' partial sums with NCCL."""
+        if self.nccl is None:
+            return part, splits
+        import torch.distributed as dist
+        n = m * self.cfg.hidden
+        red = self._red[:n]
+        torch.sum(part[: splits * n].view(splits, n), dim=0, out=red)
+        dist.all_reduce(red, group=self.nccl[2])
+        return red, 1
 
     def head(self, m: int, pend, ctrl, advance: bool, final_norm: Optional[torch.Tensor] = None):
         cfg, b = self.cfg, self.buf
@@ -204,12 +239,43 @@ class DecoderModel:
         fn = self.w.final_norm if final_norm is None else final_norm
         K.resid_norm(1, m, h, fn, cfg.rms_eps, b.resid, b.x, resid_in=b.resid, part=pend[0],
                      part_slice=m * h, splits=pend[1])
+        nv = self.head_rows
         if self.int8_head:
             w8, sc = self.w.lm_head_i8
-            K.head_gemv(w8, b.x, b.logits, m, cfg.vocab, h, b.cand_val, b.cand_idx, wscale=sc)
+            K.head_gemv(w8, b.x, b.logits, m, nv, h, b.cand_val, b.cand_idx, wscale=sc)
         else:
-            K.head_gemv(self.w.lm_head, b.x, b.logits, m, cfg.vocab, h, b.cand_val, b.cand_idx)
-        K.argmax_finish(b.cand_val, b.cand_idx, b.ncand, m, ctrl, advance)
+            K.head_gemv(self.w.lm_head, b.x, b.logits, m, nv, h, b.cand_val, b.cand_idx)
+        if self.nccl is not None:
+            self._head_nccl(m, ctrl, advance)
+        elif self.tp is not None:   # vocabulary-parallel: exchange (value, id) and merge on the device
+            K.argmax_finish_tp(b.cand_val, b.cand_idx, b.ncand, m, self.vocab_offset, ctrl, advance, self.tp.head,
+                               self.tp.mcap)
+        else:
+            K.argmax_finish(b.cand_val, b.cand_idx, b.ncand, m, ctrl, advance)
+
+    def _head_nccl(self, m: int, ctrl, advance: bool):
+        """Comparison path of the vocabulary-parallel arg-max: local arg-max, NCCL all-gather, torch merge."""
+        import torch.distributed as dist
+        b = self.buf
+        rank, world, group = self.nccl
+        cv = b.cand_val[: m * b.ncand].view(m, b.ncand)
+        ci = b.cand_idx[: m * b.ncand].view(m, b.ncand)
+        best = cv.max(dim=1).values
+        tie = torch.where(cv == best[:, None], ci, torch.full_like(ci, 0x7fffffff)).min(dim=1).values
+        mine = torch.stack([best, (tie + self.vocab_offset_nccl).view(torch.float32)], dim=1).contiguous()
+        dist.all_gather_into_tensor(self._gather_flat(m), mine, group=group)
+        g = self._gather_flat(m).view(world, m, 2)
+        vals, ids = g[:, :, 0], g[:, :, 1].contiguous().view(torch.int32)
+        top = vals.max(dim=0).values
+        tok = torch.where(vals == top[None, :], ids, torch.full_like(ids, 0x7fffffff)).min(dim=0).values
+        ctrl[K.CTRL_OUT_TOKEN: K.CTRL_OUT_TOKEN + m] = tok
+        ctrl[K.CTRL_OUT_VALUE: K.CTRL_OUT_VALUE + m] = top.view(torch.int32)
+        if advance:
+            ctrl[K.CTRL_CUR_TOKEN: K.CTRL_CUR_TOKEN + m] = tok
+            ctrl[K.CTRL_ROW_POS: K.CTRL_ROW_POS + m] += 1
+
+    def _gather_flat(self, m: int):
+        return self._gather.view(-1)[: self.nccl[1] * m * 2]
 
     # ------------------------------------------------------------------ whole step
     def step_rows(self, m: int, ctrl, block_table, max_blocks, kv: KVCache, advance: bool):

@@ -174,19 +174,21 @@ def _rand_layer(cfg: ModelConfig, device, seed: int, exact: bool, std=0.02) -> L
 
 
 def random_weights(cfg: ModelConfig, device="cpu", seed: int = 0, exact: Optional[bool] = None,
-                   std: float = 0.02) -> ModelWeights:
-    """Random-init model. ``exact`` (default: on for < 100M parameters) quantises real fp32 matrices."""
+                   std: float = 0.02, head_rows: Optional[int] = None) -> ModelWeights:
+    """Random-init model. ``exact`` (default: on for < 100M parameters) quantises real fp32 matrices.
+    ``head_rows``: rows of the lm_head this rank holds (vocabulary-parallel head)."""
     if exact is None:
         exact = cfg.param_count() < 100_000_000
     h = cfg.hidden
+    hr = cfg.vocab if head_rows is None else head_rows
     if exact:
         g = torch.Generator(device="cpu")
         g.manual_seed(seed)
         embed = (torch.randn(cfg.vocab, h, generator=g) * std).to(torch.bfloat16).to(device)
-        head = (torch.randn(cfg.vocab, h, generator=g) * std).to(torch.bfloat16).to(device)
+        head = (torch.randn(cfg.vocab, h, generator=g) * std)[:hr].to(torch.bfloat16).to(device).contiguous()
     else:
         embed = torch.empty(cfg.vocab, h, dtype=torch.bfloat16, device=device).normal_(0, std)
-        head = torch.empty(cfg.vocab, h, dtype=torch.bfloat16, device=device).normal_(0, std)
+        head = torch.empty(hr, h, dtype=torch.bfloat16, device=device).normal_(0, std)
     layers = [_rand_layer(cfg, device, seed * 1000 + 1 + i, exact, std) for i in range(cfg.n_layers)]
     mw = ModelWeights(cfg, embed, head, _norm_weight(h, device), layers)
     if cfg.mtp_layers:

@@ -29,6 +29,7 @@
 // depend on M (the split count is a function of N and K only) -- the
 // reference's "property R" (src/kernels/gemm_sm.cl:44-50).
 #include "common.cuh"
+#include "wire.cuh"
 
 using namespace b2;
 
@@ -71,11 +72,26 @@ struct GemvParams {
   const float* norm_ssq;                 // [M][norm_nb]
   int norm_nb;
   float norm_eps;
+  // tensor-parallel fold (row-parallel linear): the n-block's partial sums are pushed into every rank's
+  // landing buffer [2 slots][world][tp_mcap][N], flagged per (slot, source rank, n-block), and the fold
+  // adds the ranks' parts in rank order.  tp.world <= 1: single GPU.
+  Wire tp;
+  int tp_mcap;
 };
 
 __host__ __device__ inline int stride_words(int xcg) { return xcg * 32 + 4; }  // +4 words: conflict-free B reads
 
 __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
+__device__ __forceinline__ int consumers_any(uint32_t scratch, bool pred, int tid) {
+  // OR of `pred` over the 256 consumer threads (named barrier 1); `scratch` is one shared word
+  if (tid == 0) asm volatile("st.shared.u32 [%0], %1;" ::"r"(scratch), "r"(0) : "memory");
+  consumer_sync();
+  if (pred) asm volatile("st.shared.u32 [%0], %1;" ::"r"(scratch), "r"(1) : "memory");
+  consumer_sync();
+  int v;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(scratch));
+  return v;
+}
 __device__ __forceinline__ uint4 lds128(uint32_t a) {
   uint4 v;
   asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
@@ -390,16 +406,63 @@ __global__ void __launch_bounds__(kThreads, (T <= 2 ? 2 : 1)) gemv_w4_kernel(con
   if (!is_last) return;
   __threadfence();
   const int nb_total = (p.N + 127) / 128;
-  // one (row, column) per thread; the slices of an element are loaded together and added in split order
   const int items = p.M * 128;
+  const bool tp = p.tp.world > 1;
+  const float* land_me = nullptr;
+  if (tp) {
+    // ---- all-reduce over NVLink inside the fold.  Step 1: sum the split slices (split order) and store
+    // this rank's part of the n-block into every rank's landing buffer, its own included.
+    if (tid == 0) {
+      const int e = p.tp.epoch[nblk] + 1;   // call number of this n-block: the same on every rank
+      p.tp.epoch[nblk] = e;
+      asm volatile("st.shared.u32 [%0], %1;" ::"r"(rinv0 + 248), "r"(e) : "memory");
+    }
+    consumer_sync();
+    int epoch;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(epoch) : "r"(rinv0 + 248));
+    const int slot = epoch & 1, W = p.tp.world, me = p.tp.rank;
+    const size_t src_stride = (size_t)p.tp_mcap * p.N;
+    for (int idx0 = 0; idx0 < items; idx0 += kConsumerThreads) {
+      const int idx = idx0 + tid;
+      const int m = idx >> 7, c = idx & 127, n = nblk * 128 + c;
+      if (idx < items && n < p.N) {
+        float v[16];
+#pragma unroll
+        for (int sp = 0; sp < 16; ++sp) v[sp] = sp < p.S ? __ldcg(p.out + ((size_t)sp * p.M + m) * p.ldo + n) : 0.f;
+        float part = 0.f;
+#pragma unroll
+        for (int sp = 0; sp < 16; ++sp) part += v[sp];
+        const size_t off = ((size_t)slot * W + me) * src_stride + (size_t)m * p.N + n;
+        for (int r = 0; r < W; ++r) wire_land(p.tp, r)[off] = part;
+      }
+    }
+    __threadfence_system();
+    consumer_sync();
+    // Step 2: flag every peer, then wait (bounded) for every peer's flag in this rank's own memory.
+    bool got = true;
+    if (tid < W && tid != me) {
+      st_release_sys(wire_flags(p.tp, tid) + ((size_t)slot * W + me) * nb_total + nblk, epoch);
+      got = wire_wait(wire_flags(p.tp, me) + ((size_t)slot * W + tid) * nb_total + nblk, epoch, (unsigned)(tid << 16 | nblk));
+    }
+    const int all = consumers_any(rinv0 + 244, !got, tid);
+    if (all) return;  // a peer never arrived: status is set, the residual stream is left as it was
+    land_me = wire_land(p.tp, me) + (size_t)slot * W * src_stride;
+  }
+  // one (row, column) per thread; the parts of an element are loaded together and added in a fixed order
   for (int idx0 = 0; idx0 < items; idx0 += kConsumerThreads) {
     const int idx = idx0 + tid;
     const int m = idx >> 7, c = idx & 127, n = nblk * 128 + c;
     float rf = 0.f;
     if (idx < items && n < p.N) {
       float v[16];
+      if (tp) {
 #pragma unroll
-      for (int sp = 0; sp < 16; ++sp) v[sp] = sp < p.S ? __ldcg(p.out + ((size_t)sp * p.M + m) * p.ldo + n) : 0.f;
+        for (int sp = 0; sp < 16; ++sp)
+          v[sp] = sp < p.tp.world ? ld_sys_f32(land_me + (size_t)sp * p.tp_mcap * p.N + (size_t)m * p.N + n) : 0.f;
+      } else {
+#pragma unroll
+        for (int sp = 0; sp < 16; ++sp) v[sp] = sp < p.S ? __ldcg(p.out + ((size_t)sp * p.M + m) * p.ldo + n) : 0.f;
+      }
       float r = __bfloat162float(p.fold_resid_in[(size_t)m * p.N + n]);
 #pragma unroll
       for (int sp = 0; sp < 16; ++sp) r += v[sp];
@@ -452,7 +515,7 @@ int launch_t(GemvParams& p, cudaStream_t stream) {
 extern "C" int b2_gemv_w4_splits(int N, int K) {
   const int nb = (N + 127) / 128, kg = K / 64;
   int s = 296 / nb;
-  int smax = kg / 8;  // at least 8 groups (512 k) per split
+  int smax = kg / 4;  // at least 4 groups (256 k, two ring stages) per split
   if (smax < 1) smax = 1;
   if (s > smax) s = smax;
   if (s > 16) s = 16;
@@ -472,6 +535,7 @@ extern "C" int b2_gemv_w4(const void* w4b, const void* x, float* out, int M, int
   p.batches = 1; p.expert_ids = nullptr; p.expert_bytes = 0; p.x_div = 1; p.x_batch_bytes = 0; p.out_batch = 0;
   p.fold_tickets = nullptr; p.fold_resid_in = nullptr; p.fold_resid_out = nullptr; p.fold_ssq = nullptr;
   p.norm_w = nullptr; p.norm_ssq = nullptr; p.norm_nb = 0; p.norm_eps = 0.f;
+  p.tp.table = nullptr; p.tp.epoch = nullptr; p.tp.world = 0; p.tp.rank = 0; p.tp_mcap = 0;
   p.M = M; p.N = N; p.KG = K / 64; p.S = S;
   p.gps = (p.KG + S - 1) / S;
   if (p.gps % kG != 0) p.gps += kG - p.gps % kG;   // splits start on a stage boundary
@@ -489,9 +553,13 @@ extern "C" int b2_gemv_w4(const void* w4b, const void* x, float* out, int M, int
 extern "C" int b2_gemv_w4_fused(const void* w4b, const void* x, float* out, int M, int N, int K, int S, int ldx,
                                 int x_mode, int s_in, long long x_slice, const float* norm_w, const float* norm_ssq,
                                 float norm_eps, int* fold_tickets, const void* fold_resid_in, void* fold_resid_out,
-                                float* fold_ssq, void* stream) {
+                                float* fold_ssq, const void* tp_table, int* tp_epoch, int tp_world, int tp_rank,
+                                int tp_mcap, void* stream) {
   if (M < 1 || M > 64 || K % 64 != 0 || S < 1) return -1;
   if (x_mode == 2 && (K % 128 != 0 || !norm_w || !norm_ssq)) return -2;
+  if (tp_world > 1 && (tp_world > kMaxRanks || tp_rank < 0 || tp_rank >= tp_world || !tp_table || !tp_epoch ||
+                       !fold_tickets || M > tp_mcap))
+    return -3;
   GemvParams p;
   p.w = reinterpret_cast<const uint8_t*>(w4b);
   p.x = x;
@@ -504,6 +572,8 @@ extern "C" int b2_gemv_w4_fused(const void* w4b, const void* x, float* out, int 
   p.fold_tickets = fold_tickets; p.fold_resid_in = (const __nv_bfloat16*)fold_resid_in;
   p.fold_resid_out = (__nv_bfloat16*)fold_resid_out; p.fold_ssq = fold_ssq;
   p.norm_w = norm_w; p.norm_ssq = norm_ssq; p.norm_nb = K / 128; p.norm_eps = norm_eps;
+  p.tp.table = (const unsigned long long*)tp_table; p.tp.epoch = tp_epoch; p.tp.world = tp_world; p.tp.rank = tp_rank;
+  p.tp_mcap = tp_mcap;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   if (M <= 8) return launch_t<1>(p, st);
   if (M <= 16) return launch_t<2>(p, st);
@@ -529,6 +599,7 @@ extern "C" int b2_gemv_w4_experts(const void* w4b_stack, long long expert_bytes,
   p.x_batch_bytes = x_batch_bytes; p.out_batch = (long long)S * N;
   p.fold_tickets = nullptr; p.fold_resid_in = nullptr; p.fold_resid_out = nullptr; p.fold_ssq = nullptr;
   p.norm_w = nullptr; p.norm_ssq = nullptr; p.norm_nb = 0; p.norm_eps = 0.f;
+  p.tp.table = nullptr; p.tp.epoch = nullptr; p.tp.world = 0; p.tp.rank = 0; p.tp_mcap = 0;
   return launch_t<1>(p, reinterpret_cast<cudaStream_t>(stream));
 }
 

@@ -122,16 +122,19 @@ def gemv_w4(w4b: torch.Tensor, x: torch.Tensor, out: torch.Tensor, m: int, n: in
 
 
 def gemv_w4_fused(w4b, x, out, m, n, k, splits, *, x_mode=0, s_in=1, x_slice=0, ldx=None, norm_w=None, norm_ssq=None,
-                  norm_eps=0.0, fold_tickets=None, fold_resid=None, fold_ssq=None):
+                  norm_eps=0.0, fold_tickets=None, fold_resid=None, fold_ssq=None, tp=None, tp_mcap=0):
     """The GEMV with its neighbours folded in.  ``x_mode`` 2: ``x`` is the bf16 residual stream and the
     kernel applies RMSNorm (``norm_w``, per-block sums of squares ``norm_ssq``) while staging it.
     ``fold_*``: the last split CTA of each 128-column block adds the split-K slices to ``fold_resid``
-    in place and leaves that block's sum of squares in ``fold_ssq`` ``[m][n/128]``."""
+    in place and leaves that block's sum of squares in ``fold_ssq`` ``[m][n/128]``.  ``tp`` (a wire of
+    ``parallel.symm``) makes the fold all-reduce the ranks' partial sums over NVLink first."""
     if ldx is None:
         ldx = 2 * k if x_mode == 1 else k
+    tpw = tp is not None and tp.world > 1
     rc = lib().b2_gemv_w4_fused(_p(w4b), _p(x), _p(out), m, n, k, splits, ldx, x_mode, s_in, ctypes.c_longlong(x_slice),
                                 _p(norm_w), _p(norm_ssq), ctypes.c_float(norm_eps), _p(fold_tickets), _p(fold_resid),
-                                _p(fold_resid), _p(fold_ssq), _stream())
+                                _p(fold_resid), _p(fold_ssq), _p(tp.table) if tpw else None, _p(tp.epoch) if tpw else None,
+                                tp.world if tpw else 1, tp.rank if tpw else 0, tp_mcap, _stream())
     _check(rc, "gemv_w4_fused")
 
 
@@ -179,6 +182,20 @@ def head_gemv(w, x, out, m, n, k, cand_val=None, cand_idx=None, n_valid=None, ws
 def argmax_finish(cand_val, cand_idx, ncand, m, ctrl, advance: bool):
     rc = lib().b2_argmax_finish(_p(cand_val), _p(cand_idx), ncand, m, _p(ctrl), int(advance), _stream())
     _check(rc, "argmax_finish")
+
+
+def argmax_finish_tp(cand_val, cand_idx, ncand, m, vocab_offset, ctrl, advance: bool, wire, mcap: int):
+    """Vocabulary-parallel arg-max: local reduce, exchange over the wire, merge on the device."""
+    rc = lib().b2_argmax_finish_tp(_p(cand_val), _p(cand_idx), ncand, m, vocab_offset, _p(ctrl), 1 if advance else 0,
+                                   _p(wire.table), _p(wire.epoch), wire.world, wire.rank, mcap, _stream())
+    _check(rc, "argmax_finish_tp")
+
+
+def allreduce_rows(x, out, m, n, wire, mcap: int):
+    """One-shot all-reduce of fp32 ``x[m][n]`` into ``out`` (rank-order fold, same bits on every rank)."""
+    rc = lib().b2_allreduce_rows(_p(x), _p(out), m, n, _p(wire.table), _p(wire.epoch), wire.world, wire.rank, mcap,
+                                 _stream())
+    _check(rc, "allreduce_rows")
 
 
 def attn_prefill(q, k_cache, v_cache, block_table_row, out, c, pos0, n_q, n_kv, d, num_pages, max_blocks, scale):

@@ -1,0 +1,139 @@
+"""Tensor-parallel self-check and timing, run as one process per GPU:
+
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 2 --master-addr 127.0.0.1 \\
+        -m b200serve.parallel.tp_check --model small-dense --check
+    ... -m b200serve.parallel.tp_check --model dense-27b --bench --depth 4096 --steps 32
+
+``--check``: every rank builds the whole (small) model, runs it on its own GPU as the one-GPU
+answer, then the group runs the sharded model in both modes; logits of the prompt's last position
+and a teacher-forced decode must agree with the one-GPU run within rounding, and all ranks must
+hold identical tokens and identical residual bits.  ``--bench``: CUDA-event time of decode steps,
+max over ranks, fused wires against the NCCL comparison path.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import sys
+
+import torch
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--model", default="small-dense")
+    ap.add_argument("--check", action="store_true")
+    ap.add_argument("--bench", action="store_true")
+    ap.add_argument("--depth", type=int, default=1024)
+    ap.add_argument("--steps", type=int, default=32)
+    ap.add_argument("--warmup", type=int, default=4)
+    ap.add_argument("--rows", type=int, default=1)
+    ap.add_argument("--modes", default="fused,nccl")
+    args = ap.parse_args()
+
+    import torch.distributed as dist
+    from ..models.config import preset
+    from ..models.weights import random_weights
+    from ..ops import lib as K
+    from ..runtime.engine import Engine, Row
+    from . import tp as TP
+
+    rank, world, local = TP.init_dist()
+    dev = torch.device("cuda", local)
+    cfg = preset(args.model)
+    ok = True
+    report = {"world": world, "model": cfg.name}
+
+    def maxr(x: float) -> float:
+        t = torch.tensor([x], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t)
+
+    if args.check:
+        full = random_weights(cfg, device=dev, seed=0)
+        g = torch.Generator().manual_seed(5)
+        prompt = torch.randint(0, cfg.vocab, (40,), generator=g).tolist()
+        one = Engine(full, max_seqs=1, max_len=256, use_graphs=False)
+        first = one.prefill(0, prompt)
+        ref_logits = one.model.buf.logits[one.last_prefill_row].clone()
+        ref_toks = [first]
+        for _ in range(12):
+            ref_toks.append(one.forward_rows([Row(0, one.seq_len[0], ref_toks[-1])])[0])
+        shard = TP.shard_weights(full, rank, world, dev)
+        per = (cfg.vocab + world - 1) // world
+        for mode in args.modes.split(","):
+            eng = TP.make_engine(shard, mode=mode, max_seqs=1, max_len=256, use_graphs=(mode == "fused"))
+            t0 = eng.prefill(0, prompt)
+            lg = eng.model.buf.logits[eng.last_prefill_row]
+            want = ref_logits[rank * per: rank * per + lg.numel()]
+            err = float((lg - want).abs().max())
+            scale = float(ref_logits.abs().max())
+            toks = [t0]
+            agree = int(t0 == first)
+            for i in range(12):   # teacher-forced: feed the one-GPU tokens, compare each arg-max
+                t = eng.forward_rows([Row(0, eng.seq_len[0], ref_toks[i])])[0]
+                toks.append(t)
+                agree += int(t == ref_toks[i + 1])
+            tt = torch.tensor(toks, device=dev, dtype=torch.int64)
+            all_t = [torch.empty_like(tt) for _ in range(world)]
+            rs = eng.model.buf.resid[:1].clone().view(torch.int16).to(torch.int64)
+            all_r = [torch.empty_like(rs) for _ in range(world)]
+            if world > 1:
+                dist.all_gather(all_t, tt)
+                dist.all_gather(all_r, rs)
+            else:
+                all_t, all_r = [tt], [rs]
+            same_tok = all(bool((x == all_t[0]).all()) for x in all_t)
+            same_res = all(bool((x == all_r[0]).all()) for x in all_r)
+            K.check_status()
+            good = err < 0.02 * max(scale, 1.0) and agree >= 11 and same_tok and same_res
+            ok = ok and good
+            report[mode] = {"logit_err": err, "logit_scale": scale, "agree": agree, "of": 13,
+                            "ranks_same_tokens": same_tok, "ranks_same_residual": same_res, "ok": good}
+            del eng
+    if args.bench:
+        for mode in args.modes.split(","):
+            if world == 1:
+                w = random_weights(cfg, device=dev, seed=0, exact=False)
+            else:
+                w = TP.random_shard(cfg, rank, world, dev)
+            total = args.depth + 2 * (args.steps + args.warmup) + 64
+            eng = TP.make_engine(w, mode=mode, max_seqs=args.rows, max_len=total,
+                                 nsplit_attn=max(4, min(64, args.depth // 128)))
+            # context at depth: random KV pages instead of a real prompt pass (the timing needs the reads only)
+            for layer in range(cfg.n_layers):
+                kc, vc, _, _ = eng.kv.layer(layer)
+                kc.normal_(0, 0.5)
+                vc.normal_(0, 0.5)
+            for s in range(args.rows):
+                eng._ensure_pages(s, args.depth)
+                eng.seq_len[s] = args.depth
+            eng.decode_begin(list(range(args.rows)), [1 + s for s in range(args.rows)])
+            for _ in range(args.warmup):
+                eng.decode_step(read=False)
+            if world > 1:
+                dist.barrier()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(args.steps):
+                eng.decode_step(read=False)
+            e1.record()
+            torch.cuda.synchronize()
+            ms = maxr(e0.elapsed_time(e1) / args.steps)
+            K.check_status()
+            report[f"bench_{mode}"] = {"ms_per_step": ms, "tokens_per_s": args.rows / (ms / 1e3), "rows": args.rows,
+                                       "depth": args.depth}
+            del eng, w
+            torch.cuda.empty_cache()
+    if rank == 0:
+        print(json.dumps(report))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    return 0 if ok else 1
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -36,15 +36,18 @@ class Row:
 class Engine:
     def __init__(self, weights: ModelWeights, max_seqs: int = 1, max_len: int = 4096, kv_dtype: str = "bf16",
                  max_rows: int = 64, use_graphs: bool = True, int8_head: bool = False, num_pages: Optional[int] = None,
-                 nsplit_attn: int = 32, prefill_backend: str = "auto"):
+                 nsplit_attn: int = 32, prefill_backend: str = "auto", tp=None, nccl=None):
+        """``tp``: wires of a tensor-parallel group; every rank builds the same Engine over its weight shard and
+        is driven with the same calls (same rows, same order) -- the step's kernels do the crossings."""
         self.cfg = cfg = weights.cfg
+        self.tp = tp if tp is not None and tp.world > 1 else None
         self.device = weights.embed.device
         self.max_seqs, self.max_len, self.max_rows = max_seqs, max_len, max_rows
         self.max_blocks = (max_len + PAGE - 1) // PAGE
         if num_pages is None:
             num_pages = max_seqs * self.max_blocks + 1
         self.model = DecoderModel(weights, max_rows=max_rows, max_pos=max_len, nsplit_attn=nsplit_attn,
-                                  int8_head=int8_head)
+                                  int8_head=int8_head, tp=self.tp, nccl=nccl)
         self.kv = KVCache(cfg, cfg.n_layers, num_pages, self.device, kv_dtype)
         self.kv_dtype = kv_dtype
         self.pool = KvPool(num_pages, max_seqs, self.max_blocks)
@@ -163,8 +166,8 @@ class Engine:
     def _use_tc_prefill(self, n: int) -> bool:
         """Prompt chunks longer than the row kernels take go through the tcgen05 path when the shape
         has one (head size 128, bf16 KV, dense FFN or MoE with a grouped path)."""
-        if self.prefill_backend == "rows" or n <= self.max_rows:
-            return False
+        if self.prefill_backend == "rows" or n <= self.max_rows or self.tp is not None or self.model.nccl is not None:
+            return False       # a tensor-parallel engine ingests prompts through its row kernels
         ok = self.cfg.head_dim == 128 and not self.kv.kv_int8
         if not ok and self.prefill_backend != "auto":
             raise ValueError(f"prefill backend {self.prefill_backend!r} needs head_dim 128 and a bf16 KV cache")
