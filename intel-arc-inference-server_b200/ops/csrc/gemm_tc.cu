@@ -19,6 +19,7 @@
 //            overlaps the main loop of tile i + 1), scale / SiLU*up / residual add, global stores
 // Tiles are walked M-fastest so CTAs that run together share one weight tile in L2.
 #include "common.cuh"
+#include "wire.cuh"
 
 #include <map>
 #include <mutex>
@@ -32,7 +33,7 @@ constexpr int BM = 128;
 constexpr int BKB = 128;  // bytes of K per stage row (64 bf16 or 128 int8)
 constexpr int kThreads = 192;
 
-enum Epi : int { EPI_BF16 = 0, EPI_F32 = 1, EPI_SILU_MUL = 2, EPI_RESID_ADD = 3 };
+enum Epi : int { EPI_BF16 = 0, EPI_F32 = 1, EPI_SILU_MUL = 2, EPI_RESID_ADD = 3, EPI_RS_PUSH = 4 };
 
 struct GemmParams {
   int M, N, K;       // K in elements
@@ -48,6 +49,18 @@ struct GemmParams {
   const int* blk_rows;    // [n_blk] valid rows (<= 128)
   const int* n_blk;       // device scalar
   int max_blk;
+  // ---- tensor-parallel forms (see wire.cuh for the protocol)
+  // EPI_RS_PUSH (row-parallel GEMM -> reduce-scatter): the bf16 tile of m-tile mt is stored into the
+  // landing buffer of the rank that owns those rows, [source rank][rows_cap][N], and the owner's counter
+  // [source rank][m-tile of the owner] gets one increment per epilogue warp and n-tile.
+  const unsigned long long* rs_table;  // [2][kMaxRanks]: landing, counters of every rank
+  int rs_rank, rs_world;
+  int rs_tpr;       // m-tiles per owner (rows_cap = 128 rs_tpr)
+  int mt_rot;       // m-tile walk starts here, so ranks do not all push to one owner at a time
+  // all-gather -> GEMM: the producer waits until m-tile mt of A (pushed into this GPU's memory by the
+  // owners of those rows) has ag_expect arrivals
+  const int* ag_cnt;
+  int ag_expect;
 };
 
 template <int BN>
@@ -56,7 +69,8 @@ struct Cfg {
   static constexpr int B_BYTES = BN * BKB;
   static constexpr int STAGE = A_BYTES + B_BYTES;
   static constexpr int STAGES = (BN == 256) ? 4 : 6;
-  static constexpr int SMEM = STAGES * STAGE + 1024 /*align*/ + 256 /*barriers*/;
+  static constexpr int PUSH_STAGE = 4 * 32 * 144;  // per epilogue warp: 32 rows x (128 B + 16 B pad) for coalesced peer stores
+  static constexpr int SMEM = STAGES * STAGE + 1024 /*align*/ + 256 /*barriers*/ + PUSH_STAGE;
   static constexpr int TMEM_COLS = 2 * BN;  // two accumulators
 };
 
@@ -72,6 +86,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   const uint32_t tfull0 = smem_u32(bars + 2 * C::STAGES), tempty0 = smem_u32(bars + 2 * C::STAGES + 2);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * C::STAGES + 4);
   const uint32_t smem_base = smem_u32(smem);
+  const uint32_t push_base = smem_base + C::STAGES * C::STAGE + 256;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const bool grouped = p.blk_expert != nullptr;
@@ -108,11 +123,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       int it = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
-        const int mt = t % tiles_m, nt = t / tiles_m;
+        const int mt = (t % tiles_m + p.mt_rot) % tiles_m, nt = t / tiles_m;
         int row0 = mt * BM, expert = 0;
         if (grouped) {
           row0 = p.blk_row0[mt];
           expert = p.blk_expert[mt];
+        }
+        if (p.ag_cnt) {
+          // rows of this m-tile arrive from their owner rank: bounded wait on the tile's counter in this
+          // GPU's own memory, then order the generic-proxy acquire before the async-proxy (TMA) reads
+          ok = wire_wait(p.ag_cnt + mt, p.ag_expect, (unsigned)(0x20000000u | mt));
+          if (!ok) break;
+          asm volatile("fence.proxy.async;" ::: "memory");
         }
         for (int kb = 0; kb < KB; ++kb, ++it) {
           const int s = it % C::STAGES;
@@ -167,7 +189,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     bool ok = true;
     for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x, ++lt) {
       const int a = lt & 1;
-      const int mt = t % tiles_m, nt = t / tiles_m;
+      const int mt = (t % tiles_m + p.mt_rot) % tiles_m, nt = t / tiles_m;
       int row0 = mt * BM, rows = min(BM, p.M - row0), expert = 0;
       if (grouped) {
         row0 = p.blk_row0[mt];
@@ -190,13 +212,45 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         B2_TMEM_LD_32(taddr, v);
         tmem_ld_wait();
         const int n0 = nt * BN + c * 32;
-        if (row_ok && n0 < p.N) {
+        if (I8) {  // integer accumulators -> scaled floats, once, for every epilogue form
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = __float_as_uint((float)(int)v[j] * asc * bsc[min(n0 + j, p.N - 1)]);
+        }
+        if (p.epi == EPI_RS_PUSH) {
+          // bf16 row piece -> this warp's staging tile; every second chunk the warp copies 32 rows x 128 B
+          // to the owner's landing buffer as whole 128-byte lines (coalesced stores cross NVLink far better
+          // than one row per thread)
+          const uint32_t stg = push_base + (uint32_t)quarter * (32 * 144);
+          const uint32_t mine = stg + lane * 144 + (c & 1) * 64;
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(mine + 16 * j),
+                         "r"(pack_bf16(__uint_as_float(v[8 * j]), __uint_as_float(v[8 * j + 1]))),
+                         "r"(pack_bf16(__uint_as_float(v[8 * j + 2]), __uint_as_float(v[8 * j + 3]))),
+                         "r"(pack_bf16(__uint_as_float(v[8 * j + 4]), __uint_as_float(v[8 * j + 5]))),
+                         "r"(pack_bf16(__uint_as_float(v[8 * j + 6]), __uint_as_float(v[8 * j + 7])))
+                         : "memory");
+          if (c & 1) {
+            __syncwarp();
+            const int owner = mt / p.rs_tpr, mtl = mt - owner * p.rs_tpr;
+            __nv_bfloat16* land = reinterpret_cast<__nv_bfloat16*>(p.rs_table[owner]) +
+                                  ((size_t)p.rs_rank * p.rs_tpr * BM + (size_t)mtl * BM + quarter * 32) * p.N + (n0 - 32);
+            if (n0 - 32 < p.N) {
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                const int rw = i * 4 + (lane >> 3), piece = lane & 7;
+                uint4 q;
+                asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(q.x), "=r"(q.y), "=r"(q.z), "=r"(q.w)
+                             : "r"(stg + rw * 144 + piece * 16));
+                if (quarter * 32 + rw < rows) *reinterpret_cast<uint4*>(land + (size_t)rw * p.N + piece * 8) = q;
+              }
+            }
+            __syncwarp();
+          }
+        } else if (row_ok && n0 < p.N) {
           float f[32];
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            if (I8) f[j] = (float)(int)v[j] * asc * bsc[min(n0 + j, p.N - 1)];
-            else f[j] = __uint_as_float(v[j]);
-          }
+          for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
           if (p.epi == EPI_SILU_MUL) {
             // columns alternate 16 gate, 16 up: 16 outputs per 32 accumulator columns
             __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + (size_t)grow * p.ldc + (n0 >> 1);
@@ -249,6 +303,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(tempty0 + 8 * a);
+      if (p.epi == EPI_RS_PUSH) {
+        // this warp's part of the tile is on its way: make it visible system-wide, then count one arrival
+        // at the owner (4 epilogue warps x tiles_n arrivals complete an m-tile of one source rank)
+        __threadfence_system();
+        __syncwarp();
+        if (lane == 0) {
+          const int owner = mt / p.rs_tpr, mtl = mt - owner * p.rs_tpr;
+          int* cnt = reinterpret_cast<int*>(p.rs_table[kMaxRanks + owner]) + p.rs_rank * p.rs_tpr + mtl;
+          asm volatile("red.release.sys.global.add.s32 [%0], 1;" ::"l"(cnt) : "memory");
+        }
+      }
     }
   }
 
@@ -385,13 +450,20 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, in
 }  // namespace
 
 // C = A * B^T.  a: [M][K], b: [N][K] (or [E][N][K] when blk_* are given), both bf16 (i8 = 0) or int8 (i8 = 1).
-extern "C" int b2_gemm_tc(const void* a, const void* b, void* c, int M, int N, int K, int ldc, int i8, int epi,
-                          const void* resid, const float* a_scale, const float* b_scale, const int* blk_expert,
-                          const int* blk_row0, const int* blk_rows, const int* n_blk, int max_blk, int n_experts,
-                          int bn, void* stream) {
+static int gemm_tc_impl(const void* a, const void* b, void* c, int M, int N, int K, int ldc, int i8, int epi,
+                        const void* resid, const float* a_scale, const float* b_scale, const int* blk_expert,
+                        const int* blk_row0, const int* blk_rows, const int* n_blk, int max_blk, int n_experts,
+                        int bn, const void* rs_table, int rs_rank, int rs_world, int rs_tpr, const int* ag_cnt,
+                        int ag_expect, void* stream) {
   if (K % (i8 ? 128 : 64) != 0 || M < 1 || N % 8 != 0) return -1;
   if (epi == EPI_SILU_MUL && N % 32 != 0) return -2;
+  if (epi == EPI_RS_PUSH && (!rs_table || rs_world < 1 || rs_world > kMaxRanks || rs_rank < 0 || rs_rank >= rs_world ||
+                             rs_tpr < 1 || N % 64 != 0 || blk_expert || (M + BM - 1) / BM > rs_tpr * rs_world))
+    return -3;
   GemmParams p;
+  p.rs_table = (const unsigned long long*)rs_table; p.rs_rank = rs_rank; p.rs_world = rs_world; p.rs_tpr = rs_tpr;
+  p.ag_cnt = ag_cnt; p.ag_expect = ag_expect;
+  p.mt_rot = (epi == EPI_RS_PUSH) ? (rs_rank * rs_tpr) % ((M + BM - 1) / BM) : 0;
   p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.C = c; p.resid = (const __nv_bfloat16*)resid;
   p.a_scale = a_scale; p.b_scale = b_scale; p.epi = epi;
   p.blk_expert = blk_expert; p.blk_row0 = blk_row0; p.blk_rows = blk_rows; p.n_blk = n_blk; p.max_blk = max_blk;
@@ -406,6 +478,26 @@ extern "C" int b2_gemm_tc(const void* a, const void* b, void* c, int M, int N, i
   cudaStream_t st = (cudaStream_t)stream;
   if (bn == 256) return i8 ? launch<256, true>(ma, mb, p, n_tiles, st) : launch<256, false>(ma, mb, p, n_tiles, st);
   return i8 ? launch<128, true>(ma, mb, p, n_tiles, st) : launch<128, false>(ma, mb, p, n_tiles, st);
+}
+
+extern "C" int b2_gemm_tc(const void* a, const void* b, void* c, int M, int N, int K, int ldc, int i8, int epi,
+                          const void* resid, const float* a_scale, const float* b_scale, const int* blk_expert,
+                          const int* blk_row0, const int* blk_rows, const int* n_blk, int max_blk, int n_experts,
+                          int bn, void* stream) {
+  return gemm_tc_impl(a, b, c, M, N, K, ldc, i8, epi, resid, a_scale, b_scale, blk_expert, blk_row0, blk_rows, n_blk,
+                      max_blk, n_experts, bn, nullptr, 0, 1, 1, nullptr, 0, stream);
+}
+
+// Tensor-parallel forms of the same kernel.  epi = 4 (row-parallel GEMM -> reduce-scatter): c is unused, the
+// bf16 tiles go to the row owners' landing buffers of rs_table (rs_tpr m-tiles per owner) and arrivals are
+// counted at the owners.  ag_cnt (all-gather -> GEMM): the rows of a arrive from their owners in this GPU's
+// memory; m-tile i is loaded once ag_cnt[i] has reached ag_expect.
+extern "C" int b2_gemm_tc_tp(const void* a, const void* b, void* c, int M, int N, int K, int ldc, int i8, int epi,
+                             const void* resid, const float* a_scale, const float* b_scale, int bn,
+                             const void* rs_table, int rs_rank, int rs_world, int rs_tpr, const int* ag_cnt,
+                             int ag_expect, void* stream) {
+  return gemm_tc_impl(a, b, c, M, N, K, ldc, i8, epi, resid, a_scale, b_scale, nullptr, nullptr, nullptr, nullptr, 0, 1,
+                      bn, rs_table, rs_rank, rs_world, rs_tpr, ag_cnt, ag_expect, stream);
 }
 
 extern "C" int b2_dequant_w4b(const void* w4b, void* out_bf16, int N, int K, void* stream) {

@@ -8,7 +8,7 @@ import torch
 
 from . import lib as K
 
-EPI_BF16, EPI_F32, EPI_SILU_MUL, EPI_RESID_ADD = 0, 1, 2, 3
+EPI_BF16, EPI_F32, EPI_SILU_MUL, EPI_RESID_ADD, EPI_RS_PUSH = 0, 1, 2, 3, 4
 
 
 def _launch(a, b, c, m, n, k, ldc, i8, epi, resid=None, a_scale=None, b_scale=None, blocks=None, n_experts=0, bn=0):
@@ -36,6 +36,28 @@ def gemm_i8(a8, b8, a_scale, b_scale, c, epi: int = EPI_BF16, resid=None, bn: in
     m, k = a8.shape
     n = b8.shape[0]
     _launch(a8, b8, c, m, n, k, c.stride(0), True, epi, resid=resid, a_scale=a_scale, b_scale=b_scale, bn=bn)
+
+
+def gemm_tp(a, b, c, epi: int, *, rs=None, rs_tpr: int = 1, ag_cnt=None, ag_expect: int = 0, bn: int = 0,
+            a_scale=None, b_scale=None):
+    """The tensor-parallel forms of the GEMM (bf16, or int8 when scales are given).
+
+    ``epi=EPI_RS_PUSH`` with ``rs`` (a wire of ``parallel.symm``): row-parallel GEMM -> reduce-scatter -- the
+    bf16 tiles are stored into the row owners' landing buffers over NVLink and counted there; ``c`` is unused.
+    ``ag_cnt``: all-gather -> GEMM -- ``a`` is this GPU's copy of the gathered activations, whose rows arrive
+    from their owners; m-tile ``i`` is loaded once ``ag_cnt[i] >= ag_expect``.  Returns arrivals per (source,
+    m-tile) that complete a push."""
+    m, k = a.shape
+    n = b.shape[0]
+    if bn == 0:
+        bn = 256 if n % 256 == 0 else 128
+    i8 = a_scale is not None
+    rc = K.lib().b2_gemm_tc_tp(K._p(a), K._p(b), K._p(c), m, n, k, c.stride(0) if c is not None else n, int(i8), epi,
+                               None, K._p(a_scale), K._p(b_scale), bn, K._p(rs.table) if rs is not None else None,
+                               rs.rank if rs is not None else 0, rs.world if rs is not None else 1, rs_tpr,
+                               K._p(ag_cnt), ag_expect, K._stream())
+    K._check(rc, "gemm_tc_tp")
+    return 4 * ((n + bn - 1) // bn)
 
 
 def gemm_grouped_bf16(a, b, c, blocks, epi: int = EPI_BF16, bn: int = 0):

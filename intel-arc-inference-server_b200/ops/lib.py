@@ -198,6 +198,20 @@ def allreduce_rows(x, out, m, n, wire, mcap: int):
     _check(rc, "allreduce_rows")
 
 
+def rs_fold(rs, rs_expect: int, nsrc: int, done, resid, norm_w, eps: float, xw, h: int, tpr: int, c: int):
+    """Owner side of GEMM -> reduce-scatter: wait for the m-tiles' arrivals, fold the partial sums and the
+    residual in rank order, RMSNorm, push the rows into every rank's gathered activations (wire ``xw``)."""
+    rc = lib().b2_rs_fold(_p(rs.land), _p(rs.flags), _p(done), rs_expect, nsrc, _p(resid), _p(norm_w),
+                          ctypes.c_float(eps), _p(xw.table), xw.world, xw.rank, h, tpr, c, _stream())
+    _check(rc, "rs_fold")
+
+
+def wire_wait(cnt: torch.Tensor, expect: int):
+    """Stream-ordered bounded wait until ``cnt[0] >= expect``."""
+    rc = lib().b2_wire_wait(_p(cnt), expect, _stream())
+    _check(rc, "wire_wait")
+
+
 def attn_prefill(q, k_cache, v_cache, block_table_row, out, c, pos0, n_q, n_kv, d, num_pages, max_blocks, scale):
     """Causal flash attention of a prompt chunk (``c`` rows at positions ``pos0..``) over the paged bf16 cache."""
     rc = lib().b2_attn_prefill(_p(q), _p(k_cache), _p(v_cache), _p(block_table_row), _p(out), c, pos0, n_q, n_kv, d,

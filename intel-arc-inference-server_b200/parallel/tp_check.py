@@ -29,6 +29,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=4)
     ap.add_argument("--rows", type=int, default=1)
     ap.add_argument("--modes", default="fused,nccl")
+    ap.add_argument("--prefill", type=int, default=0, help="time prompt passes of this many tokens")
+    ap.add_argument("--prompt", type=int, default=40, help="prompt length of --check (> 64 takes the GEMM path)")
     args = ap.parse_args()
 
     import torch.distributed as dist
@@ -41,6 +43,10 @@ def main():
     rank, world, local = TP.init_dist()
     dev = torch.device("cuda", local)
     cfg = preset(args.model)
+    if args.check and world > 1 and (cfg.n_kv_heads % world or cfg.ffn % (64 * world)):
+        import dataclasses   # widen the small preset so that it divides over this many ranks
+        cfg = dataclasses.replace(cfg, n_kv_heads=max(cfg.n_kv_heads, world), n_q_heads=max(cfg.n_q_heads, 2 * world),
+                                  ffn=192 * world)
     ok = True
     report = {"world": world, "model": cfg.name}
 
@@ -53,8 +59,8 @@ def main():
     if args.check:
         full = random_weights(cfg, device=dev, seed=0)
         g = torch.Generator().manual_seed(5)
-        prompt = torch.randint(0, cfg.vocab, (40,), generator=g).tolist()
-        one = Engine(full, max_seqs=1, max_len=256, use_graphs=False)
+        prompt = torch.randint(0, cfg.vocab, (args.prompt,), generator=g).tolist()
+        one = Engine(full, max_seqs=1, max_len=args.prompt + 216, use_graphs=False)
         first = one.prefill(0, prompt)
         ref_logits = one.model.buf.logits[one.last_prefill_row].clone()
         ref_toks = [first]
@@ -63,7 +69,7 @@ def main():
         shard = TP.shard_weights(full, rank, world, dev)
         per = (cfg.vocab + world - 1) // world
         for mode in args.modes.split(","):
-            eng = TP.make_engine(shard, mode=mode, max_seqs=1, max_len=256, use_graphs=(mode == "fused"))
+            eng = TP.make_engine(shard, mode=mode, max_seqs=1, max_len=args.prompt + 216, use_graphs=(mode == "fused"))
             t0 = eng.prefill(0, prompt)
             lg = eng.model.buf.logits[eng.last_prefill_row]
             want = ref_logits[rank * per: rank * per + lg.numel()]
@@ -125,6 +131,32 @@ def main():
             K.check_status()
             report[f"bench_{mode}"] = {"ms_per_step": ms, "tokens_per_s": args.rows / (ms / 1e3), "rows": args.rows,
                                        "depth": args.depth}
+            del eng, w
+            torch.cuda.empty_cache()
+    if args.prefill:
+        n = args.prefill
+        for mode in args.modes.split(","):
+            w = random_weights(cfg, device=dev, seed=0, exact=False) if world == 1 else TP.random_shard(cfg, rank, world, dev)
+            eng = TP.make_engine(w, mode=mode, max_seqs=1, max_len=n + 64, use_graphs=False, prefill_backend="bf16-resident")
+            g = torch.Generator().manual_seed(1)
+            ids = torch.randint(0, cfg.vocab, (n,), generator=g).tolist()
+            for _ in range(3):
+                eng.reset(0)
+                eng.prefill(0, ids)
+            if world > 1:
+                dist.barrier()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            reps = 4
+            e0.record()
+            for _ in range(reps):
+                eng.reset(0)
+                eng.prefill(0, ids)
+            e1.record()
+            torch.cuda.synchronize()
+            ms = maxr(e0.elapsed_time(e1) / reps)
+            K.check_status()
+            report[f"prefill_{mode}"] = {"ms": ms, "tokens": n, "tokens_per_s": n / (ms / 1e3)}
             del eng, w
             torch.cuda.empty_cache()
     if rank == 0:

@@ -148,9 +148,16 @@ class Engine:
         """Ingest ``ids`` after the slot's current length; returns the greedy next token."""
         ids = list(ids)
         if self._use_tc_prefill(len(ids)):
-            from .prefill import PrefillRunner
             if self._prefill is None:
-                self._prefill = PrefillRunner(self)
+                if self.tp is not None:
+                    from ..parallel.tp_prefill import TpPrefillRunner
+                    self._prefill = TpPrefillRunner(self)
+                elif self.model.nccl is not None:
+                    from ..parallel.tp_prefill import NcclPrefillRunner
+                    self._prefill = NcclPrefillRunner(self, self.model.nccl[2])
+                else:
+                    from .prefill import PrefillRunner
+                    self._prefill = PrefillRunner(self)
             self.last_prefill_row = 0      # row of model.buf.logits that holds the prompt's last position
             return self._prefill.run(slot, ids, chunk)
         start = self.seq_len[slot]
@@ -166,8 +173,8 @@ class Engine:
     def _use_tc_prefill(self, n: int) -> bool:
         """Prompt chunks longer than the row kernels take go through the tcgen05 path when the shape
         has one (head size 128, bf16 KV, dense FFN or MoE with a grouped path)."""
-        if self.prefill_backend == "rows" or n <= self.max_rows or self.tp is not None or self.model.nccl is not None:
-            return False       # a tensor-parallel engine ingests prompts through its row kernels
+        if self.prefill_backend == "rows" or n <= self.max_rows:
+            return False
         ok = self.cfg.head_dim == 128 and not self.kv.kv_int8
         if not ok and self.prefill_backend != "auto":
             raise ValueError(f"prefill backend {self.prefill_backend!r} needs head_dim 128 and a bf16 KV cache")
