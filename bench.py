@@ -140,6 +140,30 @@ def main():
             extra["prefill_int8"] = run_prefill_bench(a2, barrier, model=args.model, backend="int8")
     if args.what in ("all", "moe"):
         extra["moe_prefill"] = run_prefill_bench(args, barrier, model="moe-35b-a3b", backend=args.prefill_backend)
+    if world > 1 and args.what in ("all", "tp"):
+        # the same model as ONE tensor-parallel group over all the GPUs: fused NVLink kernels against the
+        # in-tree NCCL (+ cuBLAS for the prompt pass) comparison, max over ranks
+        from b200serve.models.config import preset
+        from b200serve.parallel import tp as TP
+        cfg = preset(args.model)
+        peaks = {}
+        pk = os.path.join(os.path.dirname(os.path.abspath(__file__)), "MEASURED_PEAKS.json")
+        if os.path.exists(pk):
+            with open(pk) as f:
+                peaks = json.load(f)
+        tpx = {"world": world, "parallelism": f"tp{world}"}
+        for mode in ("fused", "nccl"):
+            tpx[f"decode_{mode}"] = TP.bench_decode(cfg, mode, args.depth, min(args.steps, 32), max(args.warmup, 3))
+            tpx[f"decode8_{mode}"] = TP.bench_decode(cfg, mode, args.depth, min(args.steps, 32), max(args.warmup, 3), rows=8)
+            tpx[f"prefill_{mode}"] = TP.bench_prefill(cfg, mode, args.prefill_len)
+        tpx["fused_ops"] = TP.bench_fused_ops(cfg, args.prefill_len, peaks=peaks)
+        extra["tp"] = tpx
+    if world > 1 and args.what in ("all", "ep"):
+        # the MoE shape with its experts spread over all the GPUs (data-parallel attention): fused dispatch /
+        # return kernels against NCCL all-to-all around the same grouped GEMMs
+        from b200serve.models.config import preset
+        from b200serve.parallel import ep as EP
+        extra["ep"] = {"world": world, **EP.bench_prefill(preset("moe-35b-a3b"), args.prefill_len)}
     clocks = sampler.stop()
     K.check_status()
 
@@ -162,6 +186,8 @@ def main():
     e2e = world * res["tokens_per_step"] / (e2e_ms / 1e3)
     if rank == 0:
         for k, p in extra.items():
+            if "baseline" not in p:
+                continue
             p["tokens_per_s"] = p["tokens"] / (p["ms"] / 1e3)
             p["vs_baseline"] = p["tokens_per_s"] / p["baseline"]
         out = {

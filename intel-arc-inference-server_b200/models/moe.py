@@ -126,6 +126,9 @@ def _expert_bf16(runner, lw: LayerWeights, sc: _PrefillScratch):
 def moe_block_prefill(runner, lw: LayerWeights, c: int):
     """``runner.resid[:c] += MoE(runner.x[:c])`` for a prompt chunk."""
     cfg = runner.cfg
+    ep = getattr(runner, "ep", None)
+    if ep is not None:      # experts spread over the ranks of a group (parallel/ep.py)
+        return ep.block_prefill(runner, lw, c)
     sc = getattr(runner, "_moe_pf", None)
     if sc is None:
         sc = runner._moe_pf = _PrefillScratch(runner)

@@ -1,0 +1,208 @@
+// Expert parallelism: the all-to-all dispatch and the return path of a mixture-of-experts block
+// whose experts are spread over the ranks of a group, written as peer stores over NVLink.
+//
+// The reference has no expert parallelism (its MoE models run every expert on each card:
+// docs/17-running-models.md:455-470); this is the capability an 8-GPU NVSwitch box adds.  The plan
+// follows the reference's one-card sort (src/kernels/prefill/pf_moe_sort_mw.cl): the host never
+// reads a count, the tile table is padded to 128-row blocks and read on the device.
+//
+// Per chunk of T local tokens, on every rank:
+//   1. route + count (moe.cu): counts[E], rank of every (token, slot) inside its expert;
+//   2. ep_counts_push: counts -> every rank's cnt_all[source][E], one flag per (source -> destination);
+//   3. ep_plan: waits (bounded) for all sources' counts; for the rank's OWN experts builds the block
+//      table of the expert-sorted receive buffer (rows of source 0 first, then source 1, ...); for ALL
+//      experts computes where this rank's rows start in the destination's buffer -- every rank runs the
+//      same arithmetic on the same counts, so nothing else has to be exchanged;
+//   4. ep_dispatch: one CTA per (token, slot) stores the token's activation row straight into the
+//      destination's receive buffer, records (source, token slot) beside it and counts one arrival on
+//      the destination's 128-row block; the grouped GEMM there starts a block as soon as its rows are in
+//      (gemm_tc.cu: blk_wait), so the transfer overlaps the expert GEMMs block by block;
+//   5. the down GEMM's epilogue stores each result row into the source rank's return buffer
+//      (gemm_tc.cu: EPI_EP_RETURN); ep_flag_all then tells every source "my rows are back";
+//   6. ep_wait_all on the source, then the weighted sum over a token's slots in slot order (moe.cu:
+//      moe_combine over the return buffer), so the bits do not depend on arrival order.
+#include "wire.cuh"
+
+using namespace b2;
+
+namespace {
+
+struct EpPlanParams {
+  const unsigned long long* cnt_table;  // [2][kMaxRanks]: cnt_all [world][E] ints, flags [world]
+  int epoch;
+  int E, El, world, rank;
+  int max_blk, cap_rows;
+  int* send_base;   // [E] first row of this rank's rows of expert e in the destination's buffer
+  int* blk_expert;  // block table of this rank's receive buffer (local expert ids)
+  int* blk_row0;
+  int* blk_rows;
+  int* n_blk;
+  int* total_rows;
+  int* blk_cnt_next;  // arrival counters of the NEXT call (other parity): zeroed here
+};
+
+__global__ void __launch_bounds__(1024) ep_counts_push_kernel(const int* counts, int E, Wire w, int epoch) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int tid = threadIdx.x;
+  for (int e = tid; e < E; e += blockDim.x) {
+    const int c = counts[e];
+    for (int r = 0; r < w.world; ++r) reinterpret_cast<int*>(w.table[r])[(size_t)w.rank * E + e] = c;
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (tid < w.world) st_release_sys(wire_flags(w, tid) + w.rank, epoch);
+}
+
+__global__ void __launch_bounds__(1024) ep_plan_kernel(const EpPlanParams p) {
+  __shared__ int s_tot[1024];   // rows of expert e over all sources
+  __shared__ int s_pad[1024];   // padded to whole blocks
+  __shared__ int s_bad;
+  pdl_wait();
+  pdl_launch_dependents();
+  const int tid = threadIdx.x;
+  if (tid == 0) s_bad = 0;
+  __syncthreads();
+  const int* cnt_all = reinterpret_cast<const int*>(p.cnt_table[p.rank]);
+  const int* flags = reinterpret_cast<const int*>(p.cnt_table[kMaxRanks + p.rank]);
+  if (tid < p.world && !wire_wait(flags + tid, p.epoch, (unsigned)(0x04000000u | tid))) s_bad = 1;
+  __syncthreads();
+  if (s_bad) {
+    if (tid == 0) {
+      *p.n_blk = 0;
+      *p.total_rows = 0;
+    }
+    return;
+  }
+  int tot = 0, before = 0;
+  if (tid < p.E) {
+    for (int s = 0; s < p.world; ++s) {
+      int c;
+      asm volatile("ld.relaxed.sys.global.s32 %0, [%1];" : "=r"(c) : "l"(cnt_all + (size_t)s * p.E + tid) : "memory");
+      if (s < p.rank) before += c;
+      tot += c;
+    }
+  }
+  s_tot[tid] = tot;
+  s_pad[tid] = (tot + 127) & ~127;
+  __syncthreads();
+  if (tid < p.E) {
+    // first row of expert e in its owner's buffer: padded rows of the owner's experts before it
+    const int owner = tid / p.El;
+    int base = 0;
+    for (int e2 = owner * p.El; e2 < tid; ++e2) base += s_pad[e2];
+    p.send_base[tid] = base + before;
+    if (owner == p.rank) {
+      const int el = tid - owner * p.El;
+      const int b0 = base >> 7, nb = s_pad[tid] >> 7;
+      for (int j = 0; j < nb && b0 + j < p.max_blk; ++j) {
+        p.blk_expert[b0 + j] = el;
+        p.blk_row0[b0 + j] = (b0 + j) * 128;
+        p.blk_rows[b0 + j] = min(128, tot - j * 128);
+      }
+      if (el == p.El - 1) {
+        const int rows = base + s_pad[tid];
+        if (rows > p.cap_rows || (rows >> 7) > p.max_blk) record_error(ERR_BAD_ARG, (unsigned)rows);
+        *p.n_blk = min(rows >> 7, p.max_blk);
+        *p.total_rows = rows;
+      }
+    }
+  }
+  for (int i = tid; i < p.max_blk; i += blockDim.x) p.blk_cnt_next[i] = 0;
+}
+
+struct EpDispatchParams {
+  const int* topk_idx;
+  const int* rank_in_expert;
+  const int* send_base;
+  const __nv_bfloat16* x;   // [T][H]
+  int k, H, El, me, cap_rows, parity, max_blk;
+  const unsigned long long* recv_table;  // [2][kMaxRanks]: receive buffer [cap_rows][H] bf16, block counters [2][max_blk]
+  const unsigned long long* src_table;   // [kMaxRanks]: recv_src [cap_rows] ints
+};
+
+__global__ void __launch_bounds__(256) ep_dispatch_kernel(const EpDispatchParams p) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int i = blockIdx.x;  // token * k + slot
+  const int token = i / p.k;
+  const int e = p.topk_idx[i];
+  const int dest = e / p.El;
+  const int row = p.send_base[e] + p.rank_in_expert[i];
+  if (row >= p.cap_rows) {  // the destination's buffer is full: the token's slot is dropped and reported
+    if (threadIdx.x == 0) record_error(ERR_BAD_ARG, (unsigned)(0x80000000u | row));
+    return;
+  }
+  const uint4* src = reinterpret_cast<const uint4*>(p.x + (size_t)token * p.H);
+  uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.recv_table[dest]) + (size_t)row * p.H);
+  for (int j = threadIdx.x; j < p.H / 8; j += blockDim.x) dst[j] = src[j];
+  if (threadIdx.x == 0) reinterpret_cast<int*>(p.src_table[dest])[row] = (p.me << 24) | i;
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int* cnt = reinterpret_cast<int*>(p.recv_table[kMaxRanks + dest]) + p.parity * p.max_blk + (row >> 7);
+    asm volatile("red.release.sys.global.add.s32 [%0], 1;" ::"l"(cnt) : "memory");
+  }
+}
+
+// flags[me] = epoch on every rank (after everything earlier in the stream, whose peer stores are complete
+// at the kernel boundary)
+__global__ void ep_flag_all_kernel(Wire w, int epoch) {
+  pdl_wait();
+  __threadfence_system();
+  if (threadIdx.x < w.world) st_release_sys(wire_flags(w, threadIdx.x) + w.rank, epoch);
+  pdl_launch_dependents();
+}
+
+__global__ void ep_wait_all_kernel(Wire w, int epoch) {
+  pdl_wait();
+  if (threadIdx.x < w.world) wire_wait(wire_flags(w, w.rank) + threadIdx.x, epoch, (unsigned)(0x02000000u | threadIdx.x));
+  pdl_launch_dependents();
+}
+
+}  // namespace
+
+static Wire make_wire(const void* table, int world, int rank) {
+  Wire w;
+  w.table = (const unsigned long long*)table; w.epoch = nullptr; w.world = world; w.rank = rank;
+  return w;
+}
+
+extern "C" int b2_ep_counts_push(const int* counts, int E, const void* cnt_table, int world, int rank, int epoch,
+                                 void* stream) {
+  if (world < 1 || world > kMaxRanks || E > 1024) return -1;
+  return b2_launch(ep_counts_push_kernel, dim3(1), dim3(1024), 0, (cudaStream_t)stream, true, counts, E,
+                   make_wire(cnt_table, world, rank), epoch);
+}
+
+extern "C" int b2_ep_plan(const void* cnt_table, int epoch, int E, int world, int rank, int max_blk, int cap_rows,
+                          int* send_base, int* blk_expert, int* blk_row0, int* blk_rows, int* n_blk, int* total_rows,
+                          int* blk_cnt_next, void* stream) {
+  if (world < 1 || world > kMaxRanks || E > 1024 || E % world) return -1;
+  EpPlanParams p;
+  p.cnt_table = (const unsigned long long*)cnt_table; p.epoch = epoch; p.E = E; p.El = E / world; p.world = world;
+  p.rank = rank; p.max_blk = max_blk; p.cap_rows = cap_rows; p.send_base = send_base; p.blk_expert = blk_expert;
+  p.blk_row0 = blk_row0; p.blk_rows = blk_rows; p.n_blk = n_blk; p.total_rows = total_rows; p.blk_cnt_next = blk_cnt_next;
+  return b2_launch(ep_plan_kernel, dim3(1), dim3(1024), 0, (cudaStream_t)stream, true, p);
+}
+
+extern "C" int b2_ep_dispatch(const int* topk_idx, const int* rank_in_expert, const int* send_base, const void* x, int T,
+                              int k, int H, int E, int world, int me, int cap_rows, int parity, int max_blk,
+                              const void* recv_table, const void* src_table, void* stream) {
+  if (H % 8 || world < 1 || E % world || T * k >= (1 << 24)) return -1;
+  EpDispatchParams p;
+  p.topk_idx = topk_idx; p.rank_in_expert = rank_in_expert; p.send_base = send_base; p.x = (const __nv_bfloat16*)x;
+  p.k = k; p.H = H; p.El = E / world; p.me = me; p.cap_rows = cap_rows; p.parity = parity; p.max_blk = max_blk;
+  p.recv_table = (const unsigned long long*)recv_table; p.src_table = (const unsigned long long*)src_table;
+  return b2_launch(ep_dispatch_kernel, dim3(T * k), dim3(256), 0, (cudaStream_t)stream, true, p);
+}
+
+extern "C" int b2_ep_flag_all(const void* table, int world, int rank, int epoch, void* stream) {
+  return b2_launch(ep_flag_all_kernel, dim3(1), dim3(32), 0, (cudaStream_t)stream, true, make_wire(table, world, rank), epoch);
+}
+
+extern "C" int b2_ep_wait_all(const void* table, int world, int rank, int epoch, void* stream) {
+  return b2_launch(ep_wait_all_kernel, dim3(1), dim3(32), 0, (cudaStream_t)stream, true, make_wire(table, world, rank), epoch);
+}
+
+B2_DEFINE_STATUS(ep)

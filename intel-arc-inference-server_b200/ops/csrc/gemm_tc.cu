@@ -33,7 +33,7 @@ constexpr int BM = 128;
 constexpr int BKB = 128;  // bytes of K per stage row (64 bf16 or 128 int8)
 constexpr int kThreads = 192;
 
-enum Epi : int { EPI_BF16 = 0, EPI_F32 = 1, EPI_SILU_MUL = 2, EPI_RESID_ADD = 3, EPI_RS_PUSH = 4 };
+enum Epi : int { EPI_BF16 = 0, EPI_F32 = 1, EPI_SILU_MUL = 2, EPI_RESID_ADD = 3, EPI_RS_PUSH = 4, EPI_EP_RETURN = 5 };
 
 struct GemmParams {
   int M, N, K;       // K in elements
@@ -61,6 +61,15 @@ struct GemmParams {
   // owners of those rows) has ag_expect arrivals
   const int* ag_cnt;
   int ag_expect;
+  // ---- expert-parallel forms (grouped mode)
+  // dispatch -> grouped GEMM: block i of the expert-sorted rows is loaded once blk_wait[i] (arrivals counted
+  // by the source ranks' dispatch kernels) has reached the block's row count.
+  const int* blk_wait;
+  // EPI_EP_RETURN (grouped GEMM -> combine): row r of the sorted buffer belongs to slot (row_src[r] & 0xffffff)
+  // of source rank (row_src[r] >> 24); its bf16 result row is stored into that rank's return buffer
+  // ret_table[rank][slot][N] over NVLink, where the source adds its tokens' slots in slot order.
+  const int* row_src;
+  const unsigned long long* ret_table;
 };
 
 template <int BN>
@@ -133,6 +142,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           // rows of this m-tile arrive from their owner rank: bounded wait on the tile's counter in this
           // GPU's own memory, then order the generic-proxy acquire before the async-proxy (TMA) reads
           ok = wire_wait(p.ag_cnt + mt, p.ag_expect, (unsigned)(0x20000000u | mt));
+          if (!ok) break;
+          asm volatile("fence.proxy.async;" ::: "memory");
+        }
+        if (p.blk_wait) {
+          ok = wire_wait(p.blk_wait + mt, p.blk_rows[mt], (unsigned)(0x28000000u | mt));
           if (!ok) break;
           asm volatile("fence.proxy.async;" ::: "memory");
         }
@@ -216,7 +230,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] = __float_as_uint((float)(int)v[j] * asc * bsc[min(n0 + j, p.N - 1)]);
         }
-        if (p.epi == EPI_RS_PUSH) {
+        if (p.epi == EPI_RS_PUSH || p.epi == EPI_EP_RETURN) {
           // bf16 row piece -> this warp's staging tile; every second chunk the warp copies 32 rows x 128 B
           // to the owner's landing buffer as whole 128-byte lines (coalesced stores cross NVLink far better
           // than one row per thread)
@@ -230,7 +244,25 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                          "r"(pack_bf16(__uint_as_float(v[8 * j + 4]), __uint_as_float(v[8 * j + 5]))),
                          "r"(pack_bf16(__uint_as_float(v[8 * j + 6]), __uint_as_float(v[8 * j + 7])))
                          : "memory");
-          if (c & 1) {
+          if ((c & 1) && p.epi == EPI_EP_RETURN) {
+            __syncwarp();
+            if (n0 - 32 < p.N) {
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                const int rw = i * 4 + (lane >> 3), piece = lane & 7;
+                uint4 q;
+                asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(q.x), "=r"(q.y), "=r"(q.z), "=r"(q.w)
+                             : "r"(stg + rw * 144 + piece * 16));
+                if (quarter * 32 + rw < rows) {
+                  const int meta = p.row_src[row0 + quarter * 32 + rw];
+                  __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.ret_table[meta >> 24]) +
+                                       (size_t)(meta & 0xffffff) * p.N + (n0 - 32) + piece * 8;
+                  *reinterpret_cast<uint4*>(dst) = q;
+                }
+              }
+            }
+            __syncwarp();
+          } else if (c & 1) {
             __syncwarp();
             const int owner = mt / p.rs_tpr, mtl = mt - owner * p.rs_tpr;
             __nv_bfloat16* land = reinterpret_cast<__nv_bfloat16*>(p.rs_table[owner]) +
@@ -454,7 +486,7 @@ static int gemm_tc_impl(const void* a, const void* b, void* c, int M, int N, int
                         const void* resid, const float* a_scale, const float* b_scale, const int* blk_expert,
                         const int* blk_row0, const int* blk_rows, const int* n_blk, int max_blk, int n_experts,
                         int bn, const void* rs_table, int rs_rank, int rs_world, int rs_tpr, const int* ag_cnt,
-                        int ag_expect, void* stream) {
+                        int ag_expect, const int* blk_wait, const int* row_src, const void* ret_table, void* stream) {
   if (K % (i8 ? 128 : 64) != 0 || M < 1 || N % 8 != 0) return -1;
   if (epi == EPI_SILU_MUL && N % 32 != 0) return -2;
   if (epi == EPI_RS_PUSH && (!rs_table || rs_world < 1 || rs_world > kMaxRanks || rs_rank < 0 || rs_rank >= rs_world ||
@@ -463,6 +495,8 @@ static int gemm_tc_impl(const void* a, const void* b, void* c, int M, int N, int
   GemmParams p;
   p.rs_table = (const unsigned long long*)rs_table; p.rs_rank = rs_rank; p.rs_world = rs_world; p.rs_tpr = rs_tpr;
   p.ag_cnt = ag_cnt; p.ag_expect = ag_expect;
+  p.blk_wait = blk_wait; p.row_src = row_src; p.ret_table = (const unsigned long long*)ret_table;
+  if (epi == EPI_EP_RETURN && (!row_src || !ret_table || !blk_expert || N % 64 != 0)) return -4;
   p.mt_rot = (epi == EPI_RS_PUSH) ? (rs_rank * rs_tpr) % ((M + BM - 1) / BM) : 0;
   p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.C = c; p.resid = (const __nv_bfloat16*)resid;
   p.a_scale = a_scale; p.b_scale = b_scale; p.epi = epi;
@@ -485,7 +519,7 @@ extern "C" int b2_gemm_tc(const void* a, const void* b, void* c, int M, int N, i
                           const int* blk_row0, const int* blk_rows, const int* n_blk, int max_blk, int n_experts,
                           int bn, void* stream) {
   return gemm_tc_impl(a, b, c, M, N, K, ldc, i8, epi, resid, a_scale, b_scale, blk_expert, blk_row0, blk_rows, n_blk,
-                      max_blk, n_experts, bn, nullptr, 0, 1, 1, nullptr, 0, stream);
+                      max_blk, n_experts, bn, nullptr, 0, 1, 1, nullptr, 0, nullptr, nullptr, nullptr, stream);
 }
 
 // Tensor-parallel forms of the same kernel.  epi = 4 (row-parallel GEMM -> reduce-scatter): c is unused, the
@@ -497,7 +531,18 @@ extern "C" int b2_gemm_tc_tp(const void* a, const void* b, void* c, int M, int N
                              const void* rs_table, int rs_rank, int rs_world, int rs_tpr, const int* ag_cnt,
                              int ag_expect, void* stream) {
   return gemm_tc_impl(a, b, c, M, N, K, ldc, i8, epi, resid, a_scale, b_scale, nullptr, nullptr, nullptr, nullptr, 0, 1,
-                      bn, rs_table, rs_rank, rs_world, rs_tpr, ag_cnt, ag_expect, stream);
+                      bn, rs_table, rs_rank, rs_world, rs_tpr, ag_cnt, ag_expect, nullptr, nullptr, nullptr, stream);
+}
+
+// Expert-parallel forms of the grouped GEMM.  blk_wait: the rows of a block arrive from the source ranks'
+// dispatch kernels; block i is loaded once blk_wait[i] >= blk_rows[i].  epi = 5: every result row is stored
+// into the return buffer of the rank its token came from (row_src, ret_table).
+extern "C" int b2_gemm_tc_ep(const void* a, const void* b, void* c, int M, int N, int K, int ldc, int epi,
+                             const int* blk_expert, const int* blk_row0, const int* blk_rows, const int* n_blk,
+                             int max_blk, int n_experts, int bn, const int* blk_wait, const int* row_src,
+                             const void* ret_table, void* stream) {
+  return gemm_tc_impl(a, b, c, M, N, K, ldc, 0, epi, nullptr, nullptr, nullptr, blk_expert, blk_row0, blk_rows, n_blk,
+                      max_blk, n_experts, bn, nullptr, 0, 1, 1, nullptr, 0, blk_wait, row_src, ret_table, stream);
 }
 
 extern "C" int b2_dequant_w4b(const void* w4b, void* out_bf16, int N, int K, void* stream) {

@@ -212,6 +212,12 @@ extern "C" int b2_moe_sort(const int* topk_idx, int T, int k, int E, int max_blk
   return (int)cudaGetLastError();
 }
 
+// histogram + rank only (the expert-parallel plan needs every rank's counts before it can lay rows out)
+extern "C" int b2_moe_count(const int* topk_idx, int n, int* counts, int* rank, void* stream) {
+  moe_count_kernel<<<(n + 255) / 256, 256, 0, (cudaStream_t)stream>>>(topk_idx, n, counts, rank);
+  return (int)cudaGetLastError();
+}
+
 extern "C" int b2_moe_scatter(const int* topk_idx, const int* rank, const int* expert_base, int T, int k, const void* x,
                               int H, int* row_of, void* xs, void* stream) {
   if (H % 8) return -1;

@@ -8,7 +8,7 @@ import torch
 
 from . import lib as K
 
-EPI_BF16, EPI_F32, EPI_SILU_MUL, EPI_RESID_ADD, EPI_RS_PUSH = 0, 1, 2, 3, 4
+EPI_BF16, EPI_F32, EPI_SILU_MUL, EPI_RESID_ADD, EPI_RS_PUSH, EPI_EP_RETURN = 0, 1, 2, 3, 4, 5
 
 
 def _launch(a, b, c, m, n, k, ldc, i8, epi, resid=None, a_scale=None, b_scale=None, blocks=None, n_experts=0, bn=0):
@@ -65,6 +65,18 @@ def gemm_grouped_bf16(a, b, c, blocks, epi: int = EPI_BF16, bn: int = 0):
     ``(blk_expert, blk_row0, blk_rows, n_blk, max_blk)`` device tables of 128-row blocks."""
     e, n, k = b.shape
     _launch(a, b, c, a.shape[0], n, k, c.stride(0), False, epi, blocks=blocks, n_experts=e, bn=bn)
+
+
+def gemm_grouped_ep(a, b, c, blocks, epi: int, *, blk_wait=None, row_src=None, ret_table=None, bn: int = 0):
+    """Expert-parallel forms of the grouped GEMM.  ``blk_wait``: block ``i`` of ``a`` (rows stored by the source
+    ranks' dispatch kernels) is loaded once ``blk_wait[i] >= blk_rows[i]``.  ``epi=EPI_EP_RETURN``: every result
+    row goes to the return buffer of the rank it came from (``row_src`` per row, ``ret_table`` of buffers)."""
+    e, n, k = b.shape
+    be, br0, brn, nb, max_blk = blocks
+    rc = K.lib().b2_gemm_tc_ep(K._p(a), K._p(b), K._p(c), a.shape[0], n, k, c.stride(0) if c is not None else n, epi,
+                               K._p(be), K._p(br0), K._p(brn), K._p(nb), max_blk, e, bn, K._p(blk_wait), K._p(row_src),
+                               K._p(ret_table), K._stream())
+    K._check(rc, "gemm_tc_ep")
 
 
 def dequant_w4b(w4b: torch.Tensor, n: int, k: int, out: Optional[torch.Tensor] = None) -> torch.Tensor:

@@ -17,7 +17,7 @@ import torch
 from . import build as _build
 
 _lib: Optional[ctypes.CDLL] = None
-_UNITS = ("gemv", "decode", "gemm", "attn", "moe", "comm", "spec")
+_UNITS = ("gemv", "decode", "gemm", "attn", "moe", "comm", "ep", "spec")
 
 # Control block layout (int32 words) -- mirrors decode_ops.cu
 CTRL_N_ROWS = 0

@@ -22,6 +22,11 @@ def sort(topk_idx, t, k, e, max_blk, counts, rank, expert_base, blk_expert, blk_
     K._check(rc, "moe_sort")
 
 
+def count(topk_idx, n, counts, rank):
+    """Per-expert histogram (``counts`` zeroed by the caller) and every entry's rank inside its expert."""
+    K._check(K.lib().b2_moe_count(K._p(topk_idx), n, K._p(counts), K._p(rank), K._stream()), "moe_count")
+
+
 def scatter(topk_idx, rank, expert_base, t, k, x, h, row_of, xs):
     K._check(K.lib().b2_moe_scatter(K._p(topk_idx), K._p(rank), K._p(expert_base), t, k, K._p(x), h, K._p(row_of),
                                     K._p(xs), K._stream()), "moe_scatter")

@@ -1,0 +1,74 @@
+"""Expert-parallel self-check and timing, one process per GPU:
+
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 2 --master-addr 127.0.0.1 \\
+        -m b200serve.parallel.ep_check --model small-moe --check
+    ... -m b200serve.parallel.ep_check --model moe-35b-a3b --prefill 4096
+
+``--check``: every rank holds the whole small model, runs a prompt on one GPU as the answer, then the group
+runs the same prompt with the experts spread over the ranks (fused wires, then the NCCL comparison); logits
+must agree within rounding.  ``--prefill N``: every rank ingests its own N-token prompt (data-parallel
+attention, expert-parallel MoE); tokens/s is the whole group's, time is the max over ranks.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import sys
+
+import torch
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--model", default="small-moe")
+    ap.add_argument("--check", action="store_true")
+    ap.add_argument("--prefill", type=int, default=0)
+    ap.add_argument("--modes", default="fused,nccl")
+    args = ap.parse_args()
+    import torch.distributed as dist
+    from ..models.config import preset
+    from ..models.weights import random_weights
+    from ..ops import lib as K
+    from ..runtime.engine import Engine
+    from ..runtime.prefill import PrefillRunner
+    from . import ep as EP
+    from . import tp as TP
+
+    rank, world, local = TP.init_dist()
+    dev = torch.device("cuda", local)
+    cfg = preset(args.model)
+    report = {"world": world, "model": cfg.name}
+    ok = True
+    if args.check:
+        full = random_weights(cfg, device=dev, seed=4)
+        g = torch.Generator().manual_seed(12)
+        ids = torch.randint(0, cfg.vocab, (300,), generator=g).tolist()
+        one = Engine(full, max_seqs=1, max_len=1024, use_graphs=False)
+        t_ref = PrefillRunner(one, max_chunk=512).run(0, ids)
+        ref = one.model.buf.logits[0].clone()
+        shard = EP.ep_shard_weights(full, rank, world)
+        for mode in args.modes.split(","):
+            eng = Engine(shard, max_seqs=1, max_len=1024, use_graphs=False)
+            runner = PrefillRunner(eng, max_chunk=512)
+            runner.ep = EP.EpMoe(cfg, 512, mode=mode)
+            t = runner.run(0, ids)
+            K.check_status()
+            err = float((eng.model.buf.logits[0] - ref).abs().max())
+            good = err < 0.02 * float(ref.abs().max()) and t == t_ref
+            ok = ok and good
+            report[mode] = {"logit_err": err, "token": t, "want": t_ref, "ok": good}
+            if world > 1:
+                dist.barrier()
+            runner.ep.close()
+    if args.prefill:
+        report.update(EP.bench_prefill(cfg, args.prefill, args.modes.split(",")))
+    if rank == 0:
+        print(json.dumps(report))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    return 0 if ok else 1
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -113,3 +113,157 @@ def make_engine(weights: ModelWeights, mode: str = "fused", group=None, **kw):
     if mode == "nccl":
         return Engine(weights, nccl=(rank, world, group), **kw)
     raise ValueError(f"unknown tensor-parallel mode {mode!r}")
+
+
+# ---------------------------------------------------------------------- timing (CUDA events, max over ranks)
+def _max_over_ranks(x: float, dev) -> float:
+    import torch.distributed as dist
+    t = torch.tensor([x], device=dev, dtype=torch.float64)
+    if dist.is_initialized() and dist.get_world_size() > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t)
+
+
+def _sync_all():
+    import torch.distributed as dist
+    if dist.is_initialized() and dist.get_world_size() > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+
+
+def bench_decode(cfg: ModelConfig, mode: str, depth: int, steps: int, warmup: int, rows: int = 1) -> dict:
+    """Graph-replayed decode steps of ``rows`` requests at context ``depth``; ms per step is the max over ranks."""
+    import torch.distributed as dist
+    from ..ops import lib as K
+    world = dist.get_world_size() if dist.is_initialized() else 1
+    rank = dist.get_rank() if dist.is_initialized() else 0
+    dev = torch.device("cuda", torch.cuda.current_device())
+    w = random_weights(cfg, device=dev, seed=0, exact=False) if world == 1 else random_shard(cfg, rank, world, dev)
+    total = depth + 2 * (steps + warmup) + 64
+    eng = make_engine(w, mode=mode, max_seqs=rows, max_len=total, nsplit_attn=max(4, min(64, depth // 128)))
+    local = eng.cfg
+    for layer in range(local.n_layers):   # context at depth: random KV pages (the timing needs the reads only)
+        kc, vc, _, _ = eng.kv.layer(layer)
+        kc.normal_(0, 0.5)
+        vc.normal_(0, 0.5)
+    for s in range(rows):
+        eng._ensure_pages(s, depth)
+        eng.seq_len[s] = depth
+    eng.decode_begin(list(range(rows)), [1 + s for s in range(rows)])
+    for _ in range(warmup):
+        eng.decode_step(read=False)
+    _sync_all()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        eng.decode_step(read=False)
+    e1.record()
+    _sync_all()
+    ms = _max_over_ranks(e0.elapsed_time(e1) / steps, dev)
+    K.check_status()
+    launches = eng.launches_per_step.get((rows, True), 0)
+    eng.close()
+    del eng, w
+    torch.cuda.empty_cache()
+    return {"ms_per_step": ms, "tokens_per_s": rows / (ms / 1e3), "rows": rows, "depth": depth, "launches_per_step": launches}
+
+
+def bench_prefill(cfg: ModelConfig, mode: str, n: int, reps: int = 4) -> dict:
+    """Whole prompt passes of ``n`` tokens through ``Engine.prefill``; ms is the max over ranks."""
+    import torch.distributed as dist
+    from ..ops import lib as K
+    world = dist.get_world_size() if dist.is_initialized() else 1
+    rank = dist.get_rank() if dist.is_initialized() else 0
+    dev = torch.device("cuda", torch.cuda.current_device())
+    w = random_weights(cfg, device=dev, seed=0, exact=False) if world == 1 else random_shard(cfg, rank, world, dev)
+    eng = make_engine(w, mode=mode, max_seqs=1, max_len=n + 64, use_graphs=False, prefill_backend="bf16-resident")
+    g = torch.Generator().manual_seed(1)
+    ids = torch.randint(0, cfg.vocab, (n,), generator=g).tolist()
+    for _ in range(3):
+        eng.reset(0)
+        eng.prefill(0, ids)
+    _sync_all()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    n0 = K.launch_count
+    e0.record()
+    for _ in range(reps):
+        eng.reset(0)
+        eng.prefill(0, ids)
+    e1.record()
+    _sync_all()
+    ms = _max_over_ranks(e0.elapsed_time(e1) / reps, dev)
+    K.check_status()
+    launches = (K.launch_count - n0) // reps
+    eng.close()
+    del eng, w
+    torch.cuda.empty_cache()
+    return {"ms": ms, "tokens": n, "tokens_per_s": n / (ms / 1e3), "launches": launches}
+
+
+def bench_fused_ops(cfg: ModelConfig, c: int = 4096, reps: int = 20, peaks: Optional[dict] = None) -> dict:
+    """The two fused GEMM+collective kernels alone, at the model's down / gate‖up shapes over a ``c``-row chunk:
+    time (max over ranks) against the slower of the GEMM at the measured cuBLAS peak and the bytes that must
+    cross NVLink at the measured 770 GB/s per direction."""
+    import torch.distributed as dist
+    from ..ops import gemm as G
+    from ..ops import lib as K
+    from .symm import Wire
+    world = dist.get_world_size() if dist.is_initialized() else 1
+    rank = dist.get_rank() if dist.is_initialized() else 0
+    dev = torch.device("cuda", torch.cuda.current_device())
+    peaks = peaks or {}
+    tf = float(peaks.get("bf16_tflops", 1590.0)) * 1e12
+    link = 770e9
+    h, f = cfg.hidden, cfg.ffn // world
+    tiles = (c + 127) // 128
+    tpr = (tiles + world - 1) // world
+    rows_cap = tpr * 128
+    rs = Wire(world * rows_cap * h * 2, world * tpr, 0, None, dev)
+    xw = Wire(world * rows_cap * h * 2, world * tpr, 0, None, dev)
+    x_full = xw.buf.view(torch.bfloat16, 0, world * rows_cap * h).view(world * rows_cap, h)
+    own = torch.zeros(rows_cap, h, dtype=torch.bfloat16, device=dev)
+    done = torch.zeros(tpr, dtype=torch.int32, device=dev)
+    act = torch.randn(c, f, device=dev).to(torch.bfloat16)
+    w_down = (torch.randn(h, f, device=dev) * 0.02).to(torch.bfloat16)
+    w_gu = (torch.randn(2 * f, h, device=dev) * 0.02).to(torch.bfloat16)
+    out_gu = torch.empty(c, f, dtype=torch.bfloat16, device=dev)
+    norm_w = torch.ones(h, device=dev)
+    state = {"ag": 0}
+
+    def rs_step():
+        arr = G.gemm_tp(act, w_down, None, G.EPI_RS_PUSH, rs=rs, rs_tpr=tpr)
+        K.rs_fold(rs, arr, world, done, own, norm_w, 1e-6, xw, h, tpr, c)
+        state["ag"] += 1
+
+    def ag_step():
+        G.gemm_tp(x_full[:c], w_gu, out_gu, G.EPI_SILU_MUL, ag_cnt=xw.flags, ag_expect=128 * state["ag"])
+
+    def timed(fn):
+        for _ in range(3):
+            fn()
+        _sync_all()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        _sync_all()
+        return _max_over_ranks(e0.elapsed_time(e1) / reps, dev)
+
+    def both():
+        rs_step()
+        ag_step()
+
+    t_pair = timed(both)
+    K.check_status()
+    flops_rs = 2.0 * c * h * f
+    flops_ag = 2.0 * c * (2 * f) * h
+    bytes_rs = c * h * 2.0 * (world - 1) / world       # bf16 partial tiles leaving this rank
+    bytes_ag = c * h * 2.0 * (world - 1) / world       # this rank's normalised rows to every peer
+    floor_ms = (max(flops_rs / tf, bytes_rs / link) + max(flops_ag / tf, bytes_ag / link)) * 1e3
+    rs.close()
+    xw.close()
+    return {"chunk_rows": c, "hidden": h, "ffn_local": f, "world": world,
+            "gemm_rs_fold_ag_gemm_ms": t_pair, "roofline_floor_ms": floor_ms, "fraction_of_roofline": floor_ms / t_pair,
+            "roofline": "slower of FLOPs at measured cuBLAS bf16 peak and NVLink bytes at measured 770 GB/s per direction",
+            "peak_tflops_used": tf / 1e12}

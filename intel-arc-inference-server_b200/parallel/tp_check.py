@@ -30,6 +30,7 @@ def main():
     ap.add_argument("--rows", type=int, default=1)
     ap.add_argument("--modes", default="fused,nccl")
     ap.add_argument("--prefill", type=int, default=0, help="time prompt passes of this many tokens")
+    ap.add_argument("--ops", type=int, default=0, help="time the fused GEMM+collective kernels alone on a chunk of this many rows")
     ap.add_argument("--prompt", type=int, default=40, help="prompt length of --check (> 64 takes the GEMM path)")
     args = ap.parse_args()
 
@@ -100,65 +101,18 @@ def main():
             del eng
     if args.bench:
         for mode in args.modes.split(","):
-            if world == 1:
-                w = random_weights(cfg, device=dev, seed=0, exact=False)
-            else:
-                w = TP.random_shard(cfg, rank, world, dev)
-            total = args.depth + 2 * (args.steps + args.warmup) + 64
-            eng = TP.make_engine(w, mode=mode, max_seqs=args.rows, max_len=total,
-                                 nsplit_attn=max(4, min(64, args.depth // 128)))
-            # context at depth: random KV pages instead of a real prompt pass (the timing needs the reads only)
-            for layer in range(cfg.n_layers):
-                kc, vc, _, _ = eng.kv.layer(layer)
-                kc.normal_(0, 0.5)
-                vc.normal_(0, 0.5)
-            for s in range(args.rows):
-                eng._ensure_pages(s, args.depth)
-                eng.seq_len[s] = args.depth
-            eng.decode_begin(list(range(args.rows)), [1 + s for s in range(args.rows)])
-            for _ in range(args.warmup):
-                eng.decode_step(read=False)
-            if world > 1:
-                dist.barrier()
-            torch.cuda.synchronize()
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
-            for _ in range(args.steps):
-                eng.decode_step(read=False)
-            e1.record()
-            torch.cuda.synchronize()
-            ms = maxr(e0.elapsed_time(e1) / args.steps)
-            K.check_status()
-            report[f"bench_{mode}"] = {"ms_per_step": ms, "tokens_per_s": args.rows / (ms / 1e3), "rows": args.rows,
-                                       "depth": args.depth}
-            del eng, w
-            torch.cuda.empty_cache()
+            report[f"bench_{mode}"] = TP.bench_decode(cfg, mode, args.depth, args.steps, args.warmup, args.rows)
     if args.prefill:
-        n = args.prefill
         for mode in args.modes.split(","):
-            w = random_weights(cfg, device=dev, seed=0, exact=False) if world == 1 else TP.random_shard(cfg, rank, world, dev)
-            eng = TP.make_engine(w, mode=mode, max_seqs=1, max_len=n + 64, use_graphs=False, prefill_backend="bf16-resident")
-            g = torch.Generator().manual_seed(1)
-            ids = torch.randint(0, cfg.vocab, (n,), generator=g).tolist()
-            for _ in range(3):
-                eng.reset(0)
-                eng.prefill(0, ids)
-            if world > 1:
-                dist.barrier()
-            torch.cuda.synchronize()
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            reps = 4
-            e0.record()
-            for _ in range(reps):
-                eng.reset(0)
-                eng.prefill(0, ids)
-            e1.record()
-            torch.cuda.synchronize()
-            ms = maxr(e0.elapsed_time(e1) / reps)
-            K.check_status()
-            report[f"prefill_{mode}"] = {"ms": ms, "tokens": n, "tokens_per_s": n / (ms / 1e3)}
-            del eng, w
-            torch.cuda.empty_cache()
+            report[f"prefill_{mode}"] = TP.bench_prefill(cfg, mode, args.prefill)
+    if args.ops:
+        import os
+        peaks = {}
+        path = os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "MEASURED_PEAKS.json")
+        if os.path.exists(path):
+            with open(path) as f:
+                peaks = json.load(f)
+        report["fused_ops"] = TP.bench_fused_ops(cfg, args.ops, peaks=peaks)
     if rank == 0:
         print(json.dumps(report))
     if world > 1:

@@ -65,6 +65,17 @@ class Engine:
         self.last_prefill_row = 0
         self.launches_per_step: Dict[Tuple[int, bool], int] = {}
 
+    def close(self):
+        """Releases the cross-GPU buffers of a tensor-parallel engine (mapped peer memory)."""
+        torch.cuda.synchronize(self.device)
+        self.graphs.clear()
+        if self._prefill is not None and hasattr(self._prefill, "close"):
+            self._prefill.close()
+        self._prefill = None
+        if self.tp is not None:
+            self.tp.close()
+            self.tp = self.model.tp = None
+
     # ------------------------------------------------------------------ slots and pages
     def reset(self, slot: Optional[int] = None):
         slots = range(self.max_seqs) if slot is None else [slot]

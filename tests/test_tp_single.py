@@ -65,3 +65,29 @@ def test_small_allreduce_and_argmax_wire_single_rank():
     want = val.view(2, ncand).argmax(dim=1) + 100
     assert ctrl[K.CTRL_OUT_TOKEN: K.CTRL_OUT_TOKEN + 2].tolist() == want.tolist()
     wires.close()
+
+
+def test_expert_parallel_block_single_rank_matches_plain():
+    """Dispatch -> grouped GEMMs -> return -> weighted sum as a group of one rank, against the one-GPU MoE pass."""
+    from b200serve.ops import lib as K
+    from b200serve.parallel.ep import EpMoe
+    from b200serve.runtime.engine import Engine
+    from b200serve.runtime.prefill import PrefillRunner
+    cfg = preset("small-moe")
+    w = random_weights(cfg, device="cuda", seed=4)
+    eng = Engine(w, max_seqs=1, max_len=1024, use_graphs=False)
+    g = torch.Generator().manual_seed(12)
+    ids = torch.randint(0, cfg.vocab, (300,), generator=g).tolist()
+    plain = PrefillRunner(eng, max_chunk=512)
+    t_ref = plain.run(0, ids)
+    ref_logits = eng.model.buf.logits[0].clone()
+    for mode in ("fused", "nccl"):
+        eng.reset(0)
+        runner = PrefillRunner(eng, max_chunk=512)
+        runner.ep = EpMoe(cfg, 512, mode=mode)
+        t = runner.run(0, ids)
+        K.check_status()
+        err = float((eng.model.buf.logits[0] - ref_logits).abs().max())
+        assert err < 0.02 * float(ref_logits.abs().max()), (mode, err)
+        assert t == t_ref
+        runner.ep.close()
