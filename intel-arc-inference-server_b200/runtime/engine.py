@@ -36,7 +36,8 @@ class Row:
 class Engine:
     def __init__(self, weights: ModelWeights, max_seqs: int = 1, max_len: int = 4096, kv_dtype: str = "bf16",
                  max_rows: int = 64, use_graphs: bool = True, int8_head: bool = False, num_pages: Optional[int] = None,
-                 nsplit_attn: int = 32, prefill_backend: str = "auto", tp=None, nccl=None):
+                 nsplit_attn: int = 32, prefill_backend: str = "auto", tp=None, nccl=None,
+                 extra_kv_layers: int = 0):
         """``tp``: wires of a tensor-parallel group; every rank builds the same Engine over its weight shard and
         is driven with the same calls (same rows, same order) -- the step's kernels do the crossings."""
         self.cfg = cfg = weights.cfg
@@ -48,7 +49,7 @@ class Engine:
             num_pages = max_seqs * self.max_blocks + 1
         self.model = DecoderModel(weights, max_rows=max_rows, max_pos=max_len, nsplit_attn=nsplit_attn,
                                   int8_head=int8_head, tp=self.tp, nccl=nccl)
-        self.kv = KVCache(cfg, cfg.n_layers, num_pages, self.device, kv_dtype)
+        self.kv = KVCache(cfg, cfg.n_layers + extra_kv_layers, num_pages, self.device, kv_dtype)   # + draft-head layers
         self.kv_dtype = kv_dtype
         self.pool = KvPool(num_pages, max_seqs, self.max_blocks)
         self.ctrl = torch.zeros(K.CTRL_WORDS, dtype=torch.int32, device=self.device)
@@ -178,6 +179,9 @@ class Engine:
             rows = [Row(slot, start + c0 + i, t) for i, t in enumerate(part)]
             last = c0 + self.max_rows >= len(ids)
             out = self.forward_rows(rows, advance=False, read=last)
+            hook = getattr(self, "on_chunk_hidden", None)
+            if hook is not None:
+                hook(None, slot, part, start + c0, self.model.buf.resid[: len(part)])
         self.last_prefill_row = len(out) - 1
         return out[-1]
 

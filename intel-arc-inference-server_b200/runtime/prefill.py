@@ -86,6 +86,30 @@ class PrefillRunner:
         else:
             G.gemm_bf16(a, self._w_bf16(ql), out, epi=epi, resid=resid)
 
+    # ------------------------------------------------------------------ one layer over a chunk
+    def layer(self, lw, kv_index: int, slot: int, c: int, pos0: int, resid, x):
+        """``resid[:c]`` through one decoder layer whose KV lives at ``kv_index`` of the cache."""
+        eng, cfg, m = self.eng, self.cfg, self.eng.model
+        h = cfg.hidden
+        bt_row = eng.block_table[slot]
+        kc, vc, ks, vs = eng.kv.layer(kv_index)
+        K.resid_norm(1, c, h, lw.input_norm, cfg.rms_eps, resid, x, resid_in=resid, splits=0)
+        qkv = self.qkv[:c]
+        self.linear(lw.qkv, x, qkv, G.EPI_F32)
+        K.rope_append(qkv, 0, 1, c, None, eng.block_table, eng.max_blocks, m.cos_t, m.sin_t, cfg.n_q_heads,
+                      cfg.n_kv_heads, cfg.head_dim, self.q, kc, vc, ks, vs, eng.kv.kv_int8, req=slot, pos0=pos0)
+        K.attn_prefill(self.q, kc, vc, bt_row, self.attn, c, pos0, cfg.n_q_heads, cfg.n_kv_heads, cfg.head_dim,
+                       eng.kv.num_pages, eng.max_blocks, m.scale)
+        self.linear(lw.o, self.attn[:c], resid, G.EPI_RESID_ADD, resid=resid)
+        K.resid_norm(1, c, h, lw.post_norm, cfg.rms_eps, resid, x, resid_in=resid, splits=0)
+        if lw.gate_up is not None:
+            act = self.act[:c, : cfg.ffn]
+            self.linear(lw.gate_up, x, act, G.EPI_SILU_MUL)
+            self.linear(lw.down, act, resid, G.EPI_RESID_ADD, resid=resid)
+        else:
+            from ..models import moe as _moe
+            _moe.moe_block_prefill(self, lw, c)
+
     # ------------------------------------------------------------------ one chunk
     def chunk(self, slot: int, ids: List[int], pos0: int):
         eng, cfg, m = self.eng, self.cfg, self.eng.model
@@ -97,23 +121,10 @@ class PrefillRunner:
         torch.index_select(m.w.embed, 0, self.ids_dev[:c], out=resid)
         bt_row = eng.block_table[slot]
         for li, lw in enumerate(m.w.layers):
-            kc, vc, ks, vs = eng.kv.layer(li)
-            K.resid_norm(1, c, h, lw.input_norm, cfg.rms_eps, resid, x, resid_in=resid, splits=0)
-            qkv = self.qkv[:c]
-            self.linear(lw.qkv, x, qkv, G.EPI_F32)
-            K.rope_append(qkv, 0, 1, c, None, eng.block_table, eng.max_blocks, m.cos_t, m.sin_t, cfg.n_q_heads,
-                          cfg.n_kv_heads, cfg.head_dim, self.q, kc, vc, ks, vs, eng.kv.kv_int8, req=slot, pos0=pos0)
-            K.attn_prefill(self.q, kc, vc, bt_row, self.attn, c, pos0, cfg.n_q_heads, cfg.n_kv_heads, cfg.head_dim,
-                           eng.kv.num_pages, eng.max_blocks, m.scale)
-            self.linear(lw.o, self.attn[:c], resid, G.EPI_RESID_ADD, resid=resid)
-            K.resid_norm(1, c, h, lw.post_norm, cfg.rms_eps, resid, x, resid_in=resid, splits=0)
-            if lw.gate_up is not None:
-                act = self.act[:c, : cfg.ffn]
-                self.linear(lw.gate_up, x, act, G.EPI_SILU_MUL)
-                self.linear(lw.down, act, resid, G.EPI_RESID_ADD, resid=resid)
-            else:
-                from ..models import moe as _moe
-                _moe.moe_block_prefill(self, lw, c)
+            self.layer(lw, li, slot, c, pos0, resid, x)
+        hook = getattr(eng, "on_chunk_hidden", None)
+        if hook is not None:      # draft heads ingest the prompt from the trunk's hidden states
+            hook(self, slot, ids, pos0, resid)
         eng.seq_len[slot] = max(eng.seq_len[slot], pos0 + c)
         return resid
 

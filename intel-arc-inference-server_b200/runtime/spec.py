@@ -1,0 +1,207 @@
+"""Speculative decoding with a learned draft head: MTP chain or DFlash-style block drafter.
+
+Both heads read the trunk's hidden state: the input of position ``p`` is
+``fc([norm_e(embed(x_p)) ‖ norm_h(h_{p-1})])`` followed by the head's own decoder layers (their KV
+lives in extra layers of the engine's page pool, same block tables), the head's norm and the shared
+lm_head -- the reference's MTP head (src/runtime/capture.cc build_draft / build_verify,
+src/kernels/prefill/pf_mtp_front.cl) and its DFlash drafter (src/kernels/dflash/*.cl).
+
+One iteration (``SpecAdapter.step`` then ``draft``):
+  verify   the pending token and the drafts run as rows of one trunk step (M = k + 1);
+  accept   the server applies the accept rule and truncates the rejected rows;
+  catch-up the head runs the accepted positions with the trunk's TRUE hidden states, which fills
+           its KV and yields the first new draft;
+  draft    MTP: k - 1 more single rows chained on the head's own hidden state;
+           DFlash: the remaining drafts are mask rows of the SAME forward pass (one block).
+Rows the head wrote beyond the accepted length are overwritten by the next catch-up.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from ..models.config import dflash_drafter
+from ..models.weights import MtpWeights, QLinear, _norm_weight, _rand_layer
+from ..ops import gemm as G
+from ..ops import lib as K
+from .engine import Engine, Row
+
+
+def random_drafter(cfg, device, seed: int = 7, layers: int = 2) -> MtpWeights:
+    """Random-init DFlash-shape drafter: ``layers`` W4A16 decoder layers at the trunk's width plus the front."""
+    dcfg = dflash_drafter(cfg)
+    h = cfg.hidden
+    fc = QLinear.random(h, 2 * h, device, seed * 1000 + 777, 0.02)
+    return MtpWeights(_norm_weight(h, device), _norm_weight(h, device), fc,
+                      [_rand_layer(dcfg, device, seed * 1000 + 800 + i, False, 0.02) for i in range(layers)],
+                      _norm_weight(h, device))
+
+
+def _rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
+    xf = x.float()
+    return xf * torch.rsqrt(xf.pow(2).mean(dim=-1, keepdim=True) + eps) * w
+
+
+class DraftHead:
+    def __init__(self, engine: Engine, head: MtpWeights, kind: str = "mtp", kv_layer0: Optional[int] = None,
+                 mask_token: Optional[int] = None):
+        self.eng, self.head, self.kind = engine, head, kind
+        cfg = engine.cfg
+        self.kv0 = cfg.n_layers if kv_layer0 is None else kv_layer0
+        if engine.kv.k.shape[0] < self.kv0 + len(head.layers):
+            raise ValueError("the engine's KV cache has no layers for the draft head (extra_kv_layers)")
+        self.mask_token = cfg.vocab - 1 if mask_token is None else mask_token
+        dev = engine.device
+        self.xcat = torch.zeros(engine.max_rows, 2 * cfg.hidden, dtype=torch.bfloat16, device=dev)
+        self.hid_in = torch.zeros(engine.max_rows, cfg.hidden, dtype=torch.bfloat16, device=dev)
+        self.prev_last: Dict[int, torch.Tensor] = {}    # last hidden of the previous prompt chunk, per slot
+        engine.on_chunk_hidden = self._ingest_chunk
+        self.rows_run = 0
+
+    # ------------------------------------------------------------------ decode-time rows (M <= max_rows)
+    def rows(self, rows: Sequence[Row], hidden: torch.Tensor) -> List[int]:
+        """Runs head rows (token, position) with ``hidden[i]`` = hidden state of the position before row i.
+        Returns each row's arg-max; the head's own hidden states stay in ``engine.model.buf.resid``."""
+        eng, m, head = self.eng, self.eng.model, self.head
+        cfg, b = eng.cfg, m.buf
+        n, h = len(rows), cfg.hidden
+        for r in rows:
+            eng._ensure_pages(r.slot, r.pos + 1)
+        eng._write_rows(rows)
+        K.resid_norm(0, n, h, head.pre_norm_embed, cfg.rms_eps, b.resid, b.x, embed=m.w.embed, ctrl=eng.ctrl,
+                     vocab=cfg.vocab, flag=b.flag)
+        self.xcat[:n, :h] = b.x[:n]
+        self.xcat[:n, h:] = _rmsnorm(hidden[:n], head.pre_norm_hidden, cfg.rms_eps).to(torch.bfloat16)
+        part, s = m._gemv("head_fc", head.fc, self.xcat, n)
+        b.resid[:n] = part[: s * n * h].view(s, n, h).sum(dim=0).to(torch.bfloat16)
+        pend = m.layers_walk(head.layers, n, eng.ctrl, eng.block_table, eng.max_blocks, eng.kv,
+                             first_from_embed=False, kv_layer0=self.kv0)
+        m.head(n, pend, eng.ctrl, False, final_norm=head.norm)
+        self.rows_run += n
+        return eng._read_out(n)
+
+    # ------------------------------------------------------------------ prompt ingestion
+    def _ingest_chunk(self, runner, slot: int, ids: Sequence[int], pos0: int, resid: torch.Tensor):
+        """Fills the head's KV for a prompt chunk: position p takes (h_{p-1}, x_p)."""
+        eng, cfg, head = self.eng, self.eng.cfg, self.head
+        c, h = len(ids), cfg.hidden
+        prev = self.prev_last.get(slot) if pos0 > 0 else None
+        hid = torch.empty(c, h, dtype=torch.bfloat16, device=eng.device)
+        hid[1:] = resid[: c - 1]
+        hid[0] = prev if prev is not None else 0
+        self.prev_last[slot] = resid[c - 1].clone()
+        if runner is None or c <= eng.max_rows:
+            b = eng.model.buf
+            saved = b.logits[:c].clone() if c <= eng.max_rows else None   # the caller may still sample from these rows
+            for c0 in range(0, c, eng.max_rows):
+                part = list(ids[c0: c0 + eng.max_rows])
+                self.rows([Row(slot, pos0 + c0 + i, int(t)) for i, t in enumerate(part)], hid[c0: c0 + len(part)])
+            if saved is not None:
+                b.logits[:c].copy_(saved)
+            return
+        # GEMM path: the runner's buffers are free again (its layers are done); residual rows are overwritten
+        ids_dev = runner.ids_dev[:c]
+        e = _rmsnorm(torch.index_select(eng.model.w.embed, 0, ids_dev), head.pre_norm_embed, cfg.rms_eps)
+        hh = _rmsnorm(hid, head.pre_norm_hidden, cfg.rms_eps)
+        xcat = torch.cat([e, hh], dim=1).to(torch.bfloat16)
+        keep = resid[c - 1].clone()
+        runner.linear(head.fc, xcat, resid, G.EPI_BF16)
+        for i, lw in enumerate(head.layers):
+            runner.layer(lw, self.kv0 + i, slot, c, pos0, resid, runner.x[:c])
+        resid[c - 1].copy_(keep)          # the caller reads the trunk's last row afterwards
+
+    def last_prompt_hidden(self, slot: int) -> torch.Tensor:
+        return self.prev_last[slot]
+
+
+class SpecAdapter:
+    """EngineIface with ``draft``: wraps an ``EngineAdapter`` and a draft head."""
+
+    def __init__(self, inner, spec: str = "mtp", spec_max: int = 3, draft_model=None):
+        self.inner = inner
+        self.e: Engine = inner.e
+        self.spec, self.k_max = spec, spec_max
+        w = self.e.model.w
+        if spec == "mtp":
+            if w.mtp is None:
+                raise ValueError("--spec mtp needs a checkpoint with an MTP head")
+            head, kind = w.mtp, "mtp"
+        else:
+            head = draft_model if isinstance(draft_model, MtpWeights) else random_drafter(self.e.cfg, self.e.device)
+            kind = "dflash"
+        self.head = DraftHead(self.e, head, kind)
+        self.vocab_size, self.max_len, self.max_seqs, self.eos_ids = inner.vocab_size, inner.max_len, inner.max_seqs, inner.eos_ids
+        self.hid: Dict[int, torch.Tensor] = {}     # hidden rows of the slot's last trunk step
+        self.base: Dict[int, int] = {}             # position of its first row
+        self.toks: Dict[int, List[int]] = {}       # its row tokens
+        self.stats = {"drafted": 0, "iterations": 0}
+
+    # ---- pass-through
+    def reset(self, slot):
+        self.inner.reset(slot)
+        self.hid.pop(slot, None)
+
+    def length(self, slot): return self.inner.length(slot)
+    def truncate(self, slot, length): self.inner.truncate(slot, length)
+    def kv_form(self): return self.inner.kv_form()
+    def logits(self, slot, row=0): return self.inner.logits(slot, row)
+
+    def prefill(self, slot, ids):
+        tok = self.inner.prefill(slot, ids)
+        n = self.e.seq_len[slot]
+        self.hid[slot] = self.head.last_prompt_hidden(slot).view(1, -1)
+        self.base[slot] = n - 1
+        self.toks[slot] = [int(ids[-1])]
+        return tok
+
+    def step(self, rows: Dict[int, List[int]]):
+        bases = {slot: self.e.seq_len[slot] for slot in rows}
+        out = self.inner.step(rows)
+        resid = self.e.model.buf.resid
+        for slot, span in self.inner._rows_of.items():
+            self.hid[slot] = resid[span.start: span.stop].clone()
+            self.base[slot] = bases[slot]
+            self.toks[slot] = list(rows[slot])
+        return out
+
+    # ---- drafting
+    def draft(self, slot: int, pending: int, k: int) -> List[int]:
+        """Up to ``k`` draft tokens that follow ``pending`` (the token at position ``length(slot)``)."""
+        if k <= 0 or slot not in self.hid:
+            return []
+        k = min(k, self.k_max, self.e.max_len - self.e.seq_len[slot] - 2)
+        if k <= 0:
+            return []
+        length = self.e.seq_len[slot]
+        base, hid, toks = self.base[slot], self.hid[slot], self.toks[slot]
+        r = length - base                       # trunk rows that were kept: positions base .. length - 1
+        if r < 1 or r > hid.shape[0]:
+            return []
+        # catch-up rows: position base + 1 + j takes the hidden state of position base + j
+        row_toks = [toks[j + 1] for j in range(r - 1)] + [int(pending)]
+        rows = [Row(slot, base + 1 + j, t) for j, t in enumerate(row_toks)]
+        hidden = hid[:r]
+        drafts: List[int] = []
+        saved_len = self.e.seq_len[slot]
+        if self.head.kind == "dflash" and k > 1:
+            extra = min(k - 1, self.e.max_rows - r)
+            rows += [Row(slot, length + 1 + j, self.head.mask_token) for j in range(extra)]
+            hidden = torch.cat([hidden, hid[r - 1: r].expand(extra, -1)], dim=0)
+            out = self.head.rows(rows, hidden)
+            drafts = [int(t) for t in out[r - 1:]]
+        else:
+            out = self.head.rows(rows, hidden)
+            drafts = [int(out[-1])]
+            pos = length + 1
+            while len(drafts) < k:
+                h_own = self.e.model.buf.resid[len(rows) - 1: len(rows)].clone()
+                rows = [Row(slot, pos, drafts[-1])]
+                out = self.head.rows(rows, h_own)
+                drafts.append(int(out[0]))
+                pos += 1
+        self.e.seq_len[slot] = saved_len        # the head's rows are not part of the sequence
+        self.stats["drafted"] += len(drafts)
+        self.stats["iterations"] += 1
+        return drafts

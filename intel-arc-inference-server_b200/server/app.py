@@ -260,7 +260,14 @@ class Server:
                 self.sched.tokens(slot, emitted, False)
 
     def _draft(self, s: Session, k: int) -> List[int]:
-        if self.o.spec != "lookup" or k <= 0:
+        if k <= 0:
+            return []
+        if self.o.spec in ("mtp", "dflash", "dflash-lookup") and hasattr(self.engine, "draft"):
+            room = s.req.max_tokens - len(s.out_ids) - 1     # a learned draft head on the engine side
+            drafts = list(self.engine.draft(s.slot, s.pending, max(0, min(k, room)))) if room > 0 else []
+            if drafts or self.o.spec != "dflash-lookup":
+                return drafts
+        elif self.o.spec != "lookup":
             return []
         if s.lookup is None:
             s.lookup = H.PromptLookup()

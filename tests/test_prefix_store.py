@@ -1,0 +1,122 @@
+"""Prefix store policy on a fake page pool: hits adopt pages, misses compute, spills and restores keep the data."""
+import pytest
+
+from b200serve.runtime.kv_pool import KvPoolPy
+from b200serve.server.prefix import PAGE, PrefixStore
+
+H = pytest.importorskip("b200serve.native.host")
+
+
+class FakeKV:
+    """Pages hold the token ids 'computed' into them, so a restore can be checked position by position."""
+    form = "fake"
+    page_bytes = 64
+
+    def __init__(self, num_pages=64, slots=4):
+        self.pool = KvPoolPy(num_pages, slots, 64)
+        self.data = {}
+        self.num_pages = num_pages
+        self.seq_len = [0] * slots
+
+    def free_pages(self): return self.pool.free_pages()
+    def total_pages(self): return self.num_pages
+    def slot_pages(self, slot): return list(self.pool.table(slot))
+    def pin(self, pages): [self.pool.pin(p) for p in pages]
+    def unpin(self, pages): [self.pool.unpin(p) for p in pages]
+
+    def set_slot(self, slot, pages, length):
+        pages = list(pages)
+        [self.pool.pin(p) for p in pages]
+        self.pool.release(slot)
+        self.pool.adopt(slot, pages)
+        [self.pool.unpin(p) for p in pages]
+        self.seq_len[slot] = length
+
+    def grow(self, slot, n):
+        before = len(self.pool.table(slot))
+        self.pool.ensure(slot, before + n)
+        return list(self.pool.table(slot))[before:]
+
+    def new_host_store(self, n_slots, ppb): return [dict() for _ in range(1)]
+    def to_host(self, store, idx, pages): store[0][idx] = [self.data.get(p) for p in pages]
+    def from_host(self, store, idx, pages):
+        for p, d in zip(pages, store[0][idx]):
+            self.data[p] = d
+
+    # the "engine": computes positions [have, len(ids)) into the slot's pages
+    def prefill(self, slot, ids):
+        have = self.seq_len[slot]
+        self.pool.ensure(slot, (len(ids) + PAGE - 1) // PAGE)
+        t = self.pool.table(slot)
+        for pos in range(have - have % PAGE, len(ids), PAGE):
+            self.data[t[pos // PAGE]] = tuple(ids[pos: pos + PAGE])
+        self.seq_len[slot] = len(ids)
+        return len(ids) - have
+
+    def check(self, slot, ids, upto):
+        t = self.pool.table(slot)
+        for pos in range(0, upto, PAGE):
+            assert self.data[t[pos // PAGE]][: min(PAGE, upto - pos)] == tuple(ids[pos: pos + min(PAGE, upto - pos)])
+
+
+def _store(kv, **kw):
+    return PrefixStore(kv, host_gb=kw.pop("host_gb", 1e-6 * 40), block_tokens=32, **kw)
+
+
+def run(store, kv, slot, ids):
+    cached = store.begin(slot, ids)
+    assert kv.seq_len[slot] == cached
+    kv.check(slot, ids, cached)
+    computed = kv.prefill(slot, ids)
+    store.after_prefill(slot, ids)
+    store.end(slot, ids)
+    return cached, computed
+
+
+def test_cold_then_restore_on_another_slot_shares_pages():
+    kv = FakeKV()
+    st = _store(kv)
+    a = list(range(100, 200))                 # 100 tokens: 3 whole blocks of 32
+    assert run(st, kv, 0, a) == (0, 100)
+    b = a[:70] + [9, 9, 9, 9]                 # shares 70 tokens: 2 whole blocks
+    cached, computed = run(st, kv, 1, b)
+    assert cached == 64 and computed == len(b) - 64
+    assert kv.slot_pages(1)[:4] == kv.slot_pages(0)[:4]          # the same device pages, by reference
+    assert st.stats["hits"] == 1
+
+
+def test_continue_on_the_same_slot_uses_resident_prefix():
+    kv = FakeKV()
+    st = _store(kv)
+    a = list(range(50))
+    run(st, kv, 0, a)
+    assert st.preferred_slot(a + [1, 2, 3]) == 0
+    cached, _ = run(st, kv, 0, a + [1, 2, 3])
+    assert cached == 48                       # whole pages of the 50 resident positions
+    assert st.stats["continued"] == 1
+
+
+def test_split_last_and_full_hit_still_runs_a_row():
+    kv = FakeKV()
+    st = _store(kv)
+    a = list(range(64))
+    run(st, kv, 0, a)
+    cached = st.begin(1, a, True)
+    assert cached <= 63 and cached == 32      # the last position is never served from the cache
+
+
+def test_spill_to_host_and_restore_keeps_data():
+    kv = FakeKV(num_pages=24)
+    st = _store(kv, device_fraction=0.2, host_gb=1e-5)    # device budget: 4 pages = 2 blocks
+    assert st.host_slots >= 4
+    a = list(range(1000, 1128))               # 4 blocks
+    run(st, kv, 0, a)
+    assert st.stats["spilled"] >= 2 and st.device_pages <= st.device_budget
+    st.resident.clear()
+    kv.set_slot(0, [], 0)
+    for p in list(kv.data):                   # wipe what no longer belongs to a pinned page
+        if kv.pool.ref[p] == 0:
+            kv.data[p] = None
+    cached, computed = run(st, kv, 2, a + [5])
+    assert cached == 128 and computed == 1
+    assert st.stats["restored_blocks"] >= 2

@@ -1,0 +1,74 @@
+"""Draft heads on the GPU: the MTP head against the fp32 oracle, and lossless verify-accept loops."""
+import pytest
+import torch
+
+from b200serve.models.config import preset
+from b200serve.models.weights import random_weights
+
+pytestmark = pytest.mark.gpu
+
+
+def _mtp_cfg():
+    import dataclasses
+    return dataclasses.replace(preset("small-dense"), mtp_layers=1, name="small-dense-mtp")
+
+
+def test_mtp_head_rows_match_oracle():
+    from b200serve.models.oracle import OracleKV, OracleModel
+    from b200serve.runtime.engine import Engine
+    from b200serve.runtime.spec import SpecAdapter
+    from b200serve.server.adapter import EngineAdapter
+    cfg = _mtp_cfg()
+    w = random_weights(cfg, device="cuda", seed=2)
+    eng = Engine(w, max_seqs=1, max_len=256, use_graphs=False, extra_kv_layers=1)
+    ad = SpecAdapter(EngineAdapter(eng), "mtp", 3)
+    g = torch.Generator().manual_seed(3)
+    prompt = torch.randint(0, cfg.vocab, (24,), generator=g)
+    first = ad.prefill(0, prompt.tolist())
+    drafts = ad.draft(0, first, 3)
+    assert len(drafts) == 3
+    # oracle: trunk hidden states of the prompt, MTP over the shifted pairs, then the chain
+    wc = random_weights(cfg, device="cpu", seed=2)
+    om = OracleModel(wc)
+    kv = OracleKV(cfg)
+    hidden = om.forward(prompt, kv, 0, return_hidden=True)[1]
+    mkv = OracleKV(cfg)
+    # the head's entry of position p pairs (h_{p-1}, x_p); position 0 pairs a zero state with x_0
+    hid = torch.cat([torch.zeros(1, cfg.hidden), hidden])
+    nxt = torch.cat([prompt, torch.tensor([first])])
+    logits, h = om.mtp_forward(hid, nxt, mkv, 0)
+    want = int(torch.argmax(logits[-1]))
+    top2 = torch.topk(logits[-1], 2).values
+    if float(top2[0] - top2[1]) > 0.05:          # only a clear arg-max is compared
+        assert drafts[0] == want
+
+
+@pytest.mark.parametrize("kind", ["mtp", "dflash"])
+def test_speculative_loop_is_lossless(kind):
+    """Greedy output with drafts + verify + accept equals plain greedy decoding, token for token."""
+    from b200serve.native import host as H
+    from b200serve.runtime.engine import Engine
+    from b200serve.runtime.spec import SpecAdapter
+    from b200serve.server.adapter import EngineAdapter
+    cfg = _mtp_cfg()
+    w = random_weights(cfg, device="cuda", seed=5)
+    g = torch.Generator().manual_seed(9)
+    prompt = torch.randint(0, cfg.vocab, (100,), generator=g).tolist()
+    plain = Engine(w, max_seqs=1, max_len=512, use_graphs=False)
+    want = plain.generate(prompt, 24)
+    eng = Engine(w, max_seqs=1, max_len=512, use_graphs=False, extra_kv_layers=2)
+    ad = SpecAdapter(EngineAdapter(eng), kind, 3)
+    pending = ad.prefill(0, prompt)
+    got = [pending]
+    iters = 0
+    while len(got) < 24:
+        drafts = ad.draft(0, pending, 3)
+        out = ad.step({0: [pending] + drafts})[0]
+        acc, nxt = H.accept_greedy(out, drafts)
+        if acc < len(drafts):
+            ad.truncate(0, ad.length(0) - (len(drafts) - acc))
+        got += drafts[:acc] + [nxt]
+        pending = nxt
+        iters += 1
+    assert got[:24] == want[:24]
+    assert ad.stats["drafted"] >= iters
