@@ -140,7 +140,14 @@ def main():
             extra["prefill_int8"] = run_prefill_bench(a2, barrier, model=args.model, backend="int8")
     if args.what in ("all", "moe"):
         extra["moe_prefill"] = run_prefill_bench(args, barrier, model="moe-35b-a3b", backend=args.prefill_backend)
-    if world > 1 and args.what in ("all", "tp"):
+    def guarded(name, fn):
+        """A failing multi-GPU extra is recorded, never fatal: the headline line is printed regardless."""
+        try:
+            extra[name] = fn()
+        except Exception as e:  # noqa: BLE001
+            extra[name] = {"error": f"{type(e).__name__}: {e}"[:400]}
+
+    def tp_extra():
         # the same model as ONE tensor-parallel group over all the GPUs: fused NVLink kernels against the
         # in-tree NCCL (+ cuBLAS for the prompt pass) comparison, max over ranks
         from b200serve.models.config import preset
@@ -157,15 +164,24 @@ def main():
             tpx[f"decode8_{mode}"] = TP.bench_decode(cfg, mode, args.depth, min(args.steps, 32), max(args.warmup, 3), rows=8)
             tpx[f"prefill_{mode}"] = TP.bench_prefill(cfg, mode, args.prefill_len)
         tpx["fused_ops"] = TP.bench_fused_ops(cfg, args.prefill_len, peaks=peaks)
-        extra["tp"] = tpx
-    if world > 1 and args.what in ("all", "ep"):
+        return tpx
+
+    def ep_extra():
         # the MoE shape with its experts spread over all the GPUs (data-parallel attention): fused dispatch /
         # return kernels against NCCL all-to-all around the same grouped GEMMs
         from b200serve.models.config import preset
         from b200serve.parallel import ep as EP
-        extra["ep"] = {"world": world, **EP.bench_prefill(preset("moe-35b-a3b"), args.prefill_len)}
+        return {"world": world, **EP.bench_prefill(preset("moe-35b-a3b"), args.prefill_len)}
+
+    if world > 1 and args.what in ("all", "tp"):
+        guarded("tp", tp_extra)
+    if world > 1 and args.what in ("all", "ep"):
+        guarded("ep", ep_extra)
     clocks = sampler.stop()
-    K.check_status()
+    try:
+        K.check_status()
+    except Exception as e:  # noqa: BLE001
+        extra["status"] = {"error": str(e)[:400]}
 
     def reduce_max(x: float) -> float:
         if dist is None:

@@ -54,7 +54,7 @@ def random_ep_shard(cfg: ModelConfig, rank: int, world: int, device, seed: int =
     g.manual_seed(seed)            # the router is the same on every rank
     for lw in w.layers:
         if lw.router is not None:
-            lw.router = torch.randn(cfg.n_experts, cfg.hidden, generator=g, device=device).to(torch.bfloat16)
+            lw.router = (torch.randn(cfg.n_experts, cfg.hidden, generator=g, device=device) * cfg.hidden ** -0.5).to(torch.bfloat16)
             if hasattr(lw, "_router_cat"):
                 delattr(lw, "_router_cat")
     w.cfg = cfg
@@ -63,7 +63,7 @@ def random_ep_shard(cfg: ModelConfig, rank: int, world: int, device, seed: int =
 
 class EpMoe:
     def __init__(self, cfg: ModelConfig, max_tokens: int, group=None, device=None, mode: str = "fused",
-                 overflow: float = 2.0):
+                 overflow: Optional[float] = None):
         import torch.distributed as dist
         self.cfg, self.group, self.mode = cfg, group, mode
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
@@ -74,8 +74,11 @@ class EpMoe:
             raise ValueError(f"expert parallel {self.world} does not divide {e} experts")
         self.el = e // self.world
         t = self.t_cap = max_tokens
-        # receive buffer: the expected T k rows (uniform routing) times `overflow`, plus block padding; a
-        # rank that is sent more than this reports it in the status word and drops the excess rows
+        # receive buffer: by default the worst case (every rank sends all its rows here), so routing skew can
+        # never overflow it; `overflow` (a multiple of the uniform-routing T k rows) trades memory for the
+        # risk -- a rank that is sent more than its buffer holds reports it in the status word and drops rows
+        if overflow is None:
+            overflow = float(self.world)
         self.cap_rows = (int(t * k * overflow) + self.el * 128 + 127) // 128 * 128
         self.max_blk = self.cap_rows // 128
         i32, f32, bf = torch.int32, torch.float32, torch.bfloat16
@@ -213,16 +216,19 @@ class EpMoe:
         else:
             rx.copy_(send_x)
             re.copy_(send_e)
+        if n_in == 0:      # nothing was routed to this rank's experts: only the exchange back remains
+            back = rx
         re_local = (re - self.rank * el).contiguous()
         self.counts2.zero_()
-        M.sort(re_local, n_in, 1, el, self.max_blk, self.counts2, self.rank2, self.expert_base, self.blk_expert,
-               self.blk_row0, self.blk_rows, self.n_blk, self.total_rows)
-        M.scatter(re_local, self.rank2, self.expert_base, n_in, 1, rx, h, self.row_of, self.xs)
-        gu, dn = self._expert_bf16(runner, lw)
-        blocks = (self.blk_expert, self.blk_row0, self.blk_rows, self.n_blk, self.max_blk)
-        G.gemm_grouped_bf16(self.xs, gu, self.act, blocks, epi=G.EPI_SILU_MUL)
-        G.gemm_grouped_bf16(self.act, dn, self.y, blocks, epi=G.EPI_BF16)
-        back = self.y[self.row_of[:n_in].long()]
+        if n_in > 0:
+            M.sort(re_local, n_in, 1, el, self.max_blk, self.counts2, self.rank2, self.expert_base, self.blk_expert,
+                   self.blk_row0, self.blk_rows, self.n_blk, self.total_rows)
+            M.scatter(re_local, self.rank2, self.expert_base, n_in, 1, rx, h, self.row_of, self.xs)
+            gu, dn = self._expert_bf16(runner, lw)
+            blocks = (self.blk_expert, self.blk_row0, self.blk_rows, self.n_blk, self.max_blk)
+            G.gemm_grouped_bf16(self.xs, gu, self.act, blocks, epi=G.EPI_SILU_MUL)
+            G.gemm_grouped_bf16(self.act, dn, self.y, blocks, epi=G.EPI_BF16)
+            back = self.y[self.row_of[:n_in].long()]
         ret_sorted = torch.empty(c * k, h, dtype=x.dtype, device=x.device)
         if w > 1:
             dist.all_to_all_single(ret_sorted, back, ins, outs, group=self.group)
