@@ -46,3 +46,66 @@ def find_tokenizer(spec: str):
         return NativeTok(os.path.join(spec, "tokenizer.json"))
     sys.stderr.write("tokenizer: no tokenizer.json beside the model; serving with the byte-level stand-in\n")
     return ByteTok()
+
+
+def build_rank_engine(f, par: str) -> int:
+    """One rank of ``serve --parallel ...`` (started by the torch launcher): builds this rank's engine, then
+    rank 0 serves HTTP through a leader / router and the other ranks follow its commands."""
+    import datetime
+    import signal
+    import torch
+    import torch.distributed as dist
+    from ..parallel import launch as L
+    from ..parallel import tp as TP
+    from ..runtime.engine import Engine
+    from ..server.adapter import EngineAdapter
+    rank, world, local = TP.init_dist()
+    ctl = dist.new_group(backend="gloo", timeout=datetime.timedelta(days=7))     # control plane: host objects only
+    plane = L.ControlPlane(ctl)
+    kind, deg = L.parse_parallel(par)
+    dev = torch.device("cuda", local)
+    max_len = 4096 if f.max_len == "auto" else int(f.max_len)
+    kw = dict(max_seqs=f.max_num_seqs, max_len=max_len, kv_dtype=f.kv_cache, int8_head=f.int8_head)
+    if kind == "replica":
+        engine = Engine(load_model(f.model, dev, f.seed, f.int8_head), **kw)
+    elif kind == "tp":
+        if f.model in PRESETS:
+            w = TP.random_shard(preset(f.model), rank, world, dev, f.seed)
+        else:
+            w = load_model(f.model, dev, f.seed, f.int8_head, tp=(rank, world))
+        engine = TP.make_engine(w, mode="fused", **kw)
+    elif kind == "pp":
+        from ..parallel import pp as PP
+        cfg = preset(f.model) if f.model in PRESETS else None
+        if cfg is None:
+            full = load_model(f.model, dev, f.seed, f.int8_head)
+            a, b = PP.split_layers(full.cfg.n_layers, world)[rank]
+            w = PP.stage_weights(full, a, b)
+        else:
+            a, b = PP.split_layers(cfg.n_layers, world)[rank]
+            w = PP.random_stage(cfg, a, b, dev, f.seed)
+        engine = PP.PipelineEngine(w, rank, world, **kw)
+    else:
+        raise SystemExit("--parallel ep serves through the expert-parallel prompt pass only: use tpN, ppN or replica")
+    adapter = EngineAdapter(engine, eos_ids=(2,))
+    if rank != 0:
+        n = L.serve_replica_worker(adapter, plane) if kind == "replica" else L.follow_lockstep(adapter, plane)
+        sys.stderr.write(f"rank {rank}: {n} commands\n")
+        return 0
+    from ..server.app import Server, ServerOptions
+    from ..server.chat_template import ChatTemplate
+    front = L.ReplicaRouter(adapter, plane) if kind == "replica" else L.LockstepLeader(adapter, plane)
+    tok = find_tokenizer(f.model)
+    template = ChatTemplate.from_snapshot(f.model) if f.model not in PRESETS else ChatTemplate()
+    opts = ServerOptions(model_name=engine.cfg.name, log_requests=f.log_requests, spec="off", spec_max=0,
+                         tool_format=f.tool_format, prefix_split_last=f.prefix_split_last)
+    srv = Server(front, tok, template, opts, host=f.host, port=f.port)
+    sys.stderr.write(f"serving {engine.cfg.name} ({par}, {world} GPUs) on http://{f.host}:{srv.port}/v1\n")
+    signal.signal(signal.SIGINT, lambda *_: setattr(srv, "_stop", True))
+    signal.signal(signal.SIGTERM, lambda *_: setattr(srv, "_stop", True))
+    try:
+        srv.serve_forever()
+    finally:
+        srv.http.stop()
+        front.shutdown()
+    return 0

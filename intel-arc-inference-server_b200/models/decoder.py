@@ -187,11 +187,17 @@ class DecoderModel:
         self._gemv_fused("down", lw.down, gu, m, fold=True, x_mode=1, s_in=s_gu, x_slice=m * 2 * cfg.ffn)
 
     def layers_walk(self, layers: List[LayerWeights], m: int, ctrl, block_table, max_blocks, kv: KVCache,
-                    first_from_embed: bool = True, kv_layer0: int = 0):
-        """Runs ``layers``; returns the (partials, splits) of the last residual branch, not yet folded."""
+                    first_from_embed: bool = True, kv_layer0: int = 0, resid_ready: bool = False):
+        """Runs ``layers``; returns the (partials, splits) of the last residual branch, not yet folded.
+        ``resid_ready``: ``buf.resid`` and ``buf.ssq`` already hold the folded residual rows and their per-block
+        sums of squares (a later pipeline stage that received them from the stage before)."""
         cfg, b = self.cfg, self.buf
         h = cfg.hidden
         pend = None
+        if self.fused and resid_ready and all(lw.gate_up is not None for lw in layers) and h % 128 == 0:
+            for i, lw in enumerate(layers):
+                self.dense_layer_fused(lw, kv_layer0 + i, m, ctrl, block_table, max_blocks, kv, x_ready=False)
+            return None, 0
         if self.fused and first_from_embed and all(lw.gate_up is not None for lw in layers) and h % 128 == 0:
             K.resid_norm(0, m, h, layers[0].input_norm, cfg.rms_eps, b.resid, b.x, embed=self.w.embed, ctrl=ctrl,
                          vocab=cfg.vocab, flag=b.flag)

@@ -31,6 +31,7 @@ def main():
     ap.add_argument("--modes", default="fused,nccl")
     ap.add_argument("--prefill", type=int, default=0, help="time prompt passes of this many tokens")
     ap.add_argument("--ops", type=int, default=0, help="time the fused GEMM+collective kernels alone on a chunk of this many rows")
+    ap.add_argument("--pp", action="store_true", help="pipeline check: the ranks are stages; tokens must equal the one-GPU run")
     ap.add_argument("--prompt", type=int, default=40, help="prompt length of --check (> 64 takes the GEMM path)")
     args = ap.parse_args()
 
@@ -99,6 +100,20 @@ def main():
             report[mode] = {"logit_err": err, "logit_scale": scale, "agree": agree, "of": 13,
                             "ranks_same_tokens": same_tok, "ranks_same_residual": same_res, "ok": good}
             del eng
+    if args.pp:
+        from . import pp as PP
+        full = random_weights(cfg, device=dev, seed=0)
+        g = torch.Generator().manual_seed(5)
+        prompt = torch.randint(0, cfg.vocab, (args.prompt,), generator=g).tolist()
+        one = Engine(full, max_seqs=1, max_len=args.prompt + 64, use_graphs=False, prefill_backend="rows")
+        want = one.generate(prompt, 12)
+        a, b = PP.split_layers(cfg.n_layers, world)[rank]
+        eng = PP.PipelineEngine(PP.stage_weights(full, a, b), rank, world, max_seqs=1, max_len=args.prompt + 64)
+        got = eng.generate(prompt, 12)
+        K.check_status()
+        good = got == want
+        ok = ok and good
+        report["pp"] = {"stages": world, "layers": [a, b], "tokens_equal": good, "sent_bytes": eng.sent_bytes}
     if args.bench:
         for mode in args.modes.split(","):
             report[f"bench_{mode}"] = TP.bench_decode(cfg, mode, args.depth, args.steps, args.warmup, args.rows)
