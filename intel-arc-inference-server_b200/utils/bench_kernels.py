@@ -108,6 +108,20 @@ if __name__ == "__main__":
     what = sys.argv[1] if len(sys.argv) > 1 else "gemv"
     if what == "gemv-one":      # one shape, one M, few launches: the target of an ncu capture
         bench_gemv((int(sys.argv[3]),), only=sys.argv[2], iters_mult=1)
+    elif what == "prefill-one":  # two layers of the 27B shape over a 2048-token prompt: GEMM and attention captures
+        from dataclasses import replace
+        from ..models.config import preset
+        from ..models.weights import random_weights
+        from ..runtime.engine import Engine
+        cfg = replace(preset("dense-27b"), n_layers=2)
+        eng = Engine(random_weights(cfg, device="cuda", seed=0, exact=False), max_seqs=1, max_len=2112, use_graphs=False,
+                     prefill_backend="bf16-resident")
+        ids = torch.randint(0, cfg.vocab, (2048,)).tolist()
+        for _ in range(2):
+            eng.reset(0)
+            eng.prefill(0, ids)
+        torch.cuda.synchronize()
+        K.check_status()
     elif what == "gemv-graph":  # back-to-back launches inside a CUDA graph
         bench_gemv((1, 4, 8), graph=True)
     else:
