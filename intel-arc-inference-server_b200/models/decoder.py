@@ -54,6 +54,9 @@ class StepBuffers:
         self.tickets = torch.zeros(max_rows * cfg.n_kv_heads, dtype=torch.int32, device=device)
         self.fold_tickets = torch.zeros((h + 127) // 128, dtype=torch.int32, device=device)
         self.ssq = torch.zeros(max_rows * ((h + 127) // 128), dtype=f32, device=device)
+        kmax = max(2 * h, cfg.q_dim, cfg.ffn, cfg.expert_ffn, cfg.shared_ffn)
+        self.xq = torch.zeros(max_rows * (kmax // 64) * 128, dtype=torch.uint8, device=device)    # pre-quantised rows
+        self.xq_gs = torch.zeros(max_rows * (kmax // 64) * 2, dtype=torch.int32, device=device)
         self._parts = {}
         self.device = device
 
@@ -119,6 +122,12 @@ class DecoderModel:
             sc = wf.abs().amax(dim=1).clamp_min(1e-8) / 127.0
             weights.lm_head_i8 = (torch.round(wf / sc[:, None]).clamp_(-127, 127).to(torch.int8).contiguous(), sc.contiguous())
         self._splits = {}
+        # from this many rows up the activations are quantised once by their own kernel instead of in every
+        # CTA of the GEMV (whose prologue repeats the rows' work per 128 output columns)
+        self.prequant_rows = 3
+        import os
+        self.attn_rows_min = int(os.environ.get("B2_ATTN_ROWS_MIN", "1"))
+        self.attn_merge_inkernel_rows = int(os.environ.get("B2_ATTN_MERGE_INKERNEL_ROWS", "0"))
         self.fused = self.nccl is None     # dense layers: residual folds and norms ride inside the GEMVs
         if self.nccl is not None:
             self._red = torch.zeros(max_rows * cfg.hidden, dtype=torch.float32, device=self.device)
@@ -131,8 +140,27 @@ class DecoderModel:
         if s is None:
             s = self._splits[key] = K.gemv_splits(ql.n, ql.k)
         part = self.buf.part(name, s, ql.n)
-        K.gemv_w4(ql.w4b, x, part, m, ql.n, ql.k, s, x_mode=x_mode, s_in=s_in, x_slice=x_slice)
+        if m >= self.prequant_rows:
+            b = self.buf
+            K.quant_x(x, m, ql.k, b.xq, b.xq_gs, x_mode=x_mode, s_in=s_in, x_slice=x_slice)
+            K.gemv_w4_fused(ql.w4b, b.xq, part, m, ql.n, ql.k, s, x_mode=3, norm_ssq=b.xq_gs)
+        else:
+            K.gemv_w4(ql.w4b, x, part, m, ql.n, ql.k, s, x_mode=x_mode, s_in=s_in, x_slice=x_slice)
         return part, s
+
+    def _attention(self, m: int, ctrl, block_table, max_blocks, kv: KVCache, kc, vc, ks, vs):
+        """Split-KV attention of the step's rows into ``buf.attn_out``.  bf16 KV with head size 128 goes to the
+        tensor-core kernel that serves a request's consecutive rows together; the rest to the per-row kernel."""
+        cfg, b = self.cfg, self.buf
+        if m >= self.attn_rows_min and cfg.head_dim == 128 and not kv.kv_int8 and self.nsplit_attn <= 64 and cfg.gqa <= 16:
+            inkernel = m <= self.attn_merge_inkernel_rows    # few rows: the last split CTA merges; many: a merge launch
+            K.attn_rows(b.q, kc, vc, block_table, ctrl, b.o_part, b.ml_part, b.attn_out, b.tickets if inkernel else None,
+                        m, cfg.n_q_heads,
+                        cfg.n_kv_heads, cfg.head_dim, self.nsplit_attn, max_blocks, self.scale)
+        else:
+            K.attn_decode(b.q, kc, vc, block_table, ctrl, b.o_part, b.ml_part, b.attn_out, m, cfg.n_q_heads,
+                          cfg.n_kv_heads, cfg.head_dim, self.nsplit_attn, max_blocks, self.scale, ks, vs, kv.kv_int8,
+                          tickets=b.tickets)
 
     def attention_block(self, lw: LayerWeights, li: int, m: int, ctrl, block_table, max_blocks, kv: KVCache):
         cfg, b = self.cfg, self.buf
@@ -140,9 +168,7 @@ class DecoderModel:
         kc, vc, ks, vs = kv.layer(li)
         K.rope_append(part, m * cfg.qkv_dim, s, m, ctrl, block_table, max_blocks, self.cos_t, self.sin_t,
                       cfg.n_q_heads, cfg.n_kv_heads, cfg.head_dim, b.q, kc, vc, ks, vs, kv.kv_int8)
-        K.attn_decode(b.q, kc, vc, block_table, ctrl, b.o_part, b.ml_part, b.attn_out, m, cfg.n_q_heads,
-                      cfg.n_kv_heads, cfg.head_dim, self.nsplit_attn, max_blocks, self.scale, ks, vs, kv.kv_int8,
-                      tickets=b.tickets)
+        self._attention(m, ctrl, block_table, max_blocks, kv, kc, vc, ks, vs)
         return self._gemv("o", lw.o, b.attn_out, m)
 
     def ffn_block(self, lw: LayerWeights, m: int):
@@ -158,8 +184,15 @@ class DecoderModel:
             s = self._splits[key] = K.gemv_splits(ql.n, ql.k)
         b = self.buf
         part = b.part(name, s, ql.n)
+        if m >= self.prequant_rows:
+            K.quant_x(x, m, ql.k, b.xq, b.xq_gs, x_mode=x_mode, s_in=s_in, x_slice=x_slice, norm_w=norm_w,
+                      norm_ssq=b.ssq if norm_w is not None else None, norm_eps=self.cfg.rms_eps)
+            x, x_mode, norm_w, xq_gs = b.xq, 3, None, b.xq_gs
+        else:
+            xq_gs = None
         K.gemv_w4_fused(ql.w4b, x, part, m, ql.n, ql.k, s, x_mode=x_mode, s_in=s_in, x_slice=x_slice,
-                        norm_w=norm_w, norm_ssq=b.ssq if norm_w is not None else None, norm_eps=self.cfg.rms_eps,
+                        norm_w=norm_w, norm_ssq=xq_gs if xq_gs is not None else (b.ssq if norm_w is not None else None),
+                        norm_eps=self.cfg.rms_eps,
                         fold_tickets=b.fold_tickets if fold else None, fold_resid=b.resid if fold else None,
                         fold_ssq=b.ssq if fold else None, tp=self.tp.fold if (fold and self.tp is not None) else None,
                         tp_mcap=self.tp.mcap if self.tp is not None else 0)
@@ -179,9 +212,7 @@ class DecoderModel:
         kc, vc, ks, vs = kv.layer(li)
         K.rope_append(part, m * cfg.qkv_dim, s, m, ctrl, block_table, max_blocks, self.cos_t, self.sin_t,
                       cfg.n_q_heads, cfg.n_kv_heads, cfg.head_dim, b.q, kc, vc, ks, vs, kv.kv_int8)
-        K.attn_decode(b.q, kc, vc, block_table, ctrl, b.o_part, b.ml_part, b.attn_out, m, cfg.n_q_heads,
-                      cfg.n_kv_heads, cfg.head_dim, self.nsplit_attn, max_blocks, self.scale, ks, vs, kv.kv_int8,
-                      tickets=b.tickets)
+        self._attention(m, ctrl, block_table, max_blocks, kv, kc, vc, ks, vs)
         self._gemv_fused("o", lw.o, b.attn_out, m, fold=True)
         gu, s_gu = self._gemv_fused("gate_up", lw.gate_up, b.resid, m, norm_w=lw.post_norm, x_mode=2)
         self._gemv_fused("down", lw.down, gu, m, fold=True, x_mode=1, s_in=s_gu, x_slice=m * 2 * cfg.ffn)

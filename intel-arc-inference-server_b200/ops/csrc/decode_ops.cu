@@ -446,10 +446,36 @@ __global__ void __launch_bounds__(256) attn_decode_kernel(const AttnDecParams p)
 // grid (n_q, M), D threads
 __global__ void attn_merge_kernel(const float* o_part, const float* ml_part, __nv_bfloat16* out, int n_q, int nsplit,
                                   int D) {
+  __shared__ float cw[64];
   pdl_wait();
   pdl_launch_dependents();
   const int h = blockIdx.x, m = blockIdx.y, d = threadIdx.x;
   const size_t base = ((size_t)m * n_q + h) * nsplit;
+  if (nsplit <= 64) {
+    // weights of the splits once per CTA (one lane per split), then every thread's loads are independent
+    if (d < 32) {
+      float m0 = d < nsplit ? ml_part[(base + d) * 2] : -INFINITY, m1 = d + 32 < nsplit ? ml_part[(base + d + 32) * 2] : -INFINITY;
+      const float mm = warp_max(fmaxf(m0, m1));
+      const float c0 = m0 == -INFINITY ? 0.f : exp2f(m0 - mm), c1 = m1 == -INFINITY ? 0.f : exp2f(m1 - mm);
+      float l = (d < nsplit ? ml_part[(base + d) * 2 + 1] * c0 : 0.f) + (d + 32 < nsplit ? ml_part[(base + d + 32) * 2 + 1] * c1 : 0.f);
+      // a fixed-shape tree over the lanes: the same bits on every run
+      l = warp_sum(l);
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+      cw[d] = c0 * inv;
+      cw[d + 32] = c1 * inv;
+    }
+    __syncthreads();
+    float o = 0.f;
+    for (int s0 = 0; s0 < nsplit; s0 += 8) {
+      float v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) v[u] = s0 + u < nsplit ? o_part[(base + s0 + u) * D + d] : 0.f;
+#pragma unroll
+      for (int u = 0; u < 8; ++u) o = fmaf(v[u], s0 + u < nsplit ? cw[s0 + u] : 0.f, o);
+    }
+    out[((size_t)m * n_q + h) * D + d] = __float2bfloat16(o);
+    return;
+  }
   float mm = -INFINITY;
   for (int s = 0; s < nsplit; ++s) mm = fmaxf(mm, ml_part[(base + s) * 2]);
   float lt = 0.f, o = 0.f;
@@ -668,6 +694,13 @@ extern "C" int b2_attn_decode(const void* q, const void* k_cache, const void* v_
   else return -2;
   if (rc || tickets) return rc;
   return b2_launch(attn_merge_kernel, dim3(n_q, M), dim3(D), 0, st, true, (const float*)o_part, (const float*)ml_part,
+                   (__nv_bfloat16*)out, n_q, nsplit, D);
+}
+
+// Merge of split-KV partials as its own launch (one CTA per row and query head).
+extern "C" int b2_attn_merge(const float* o_part, const float* ml_part, void* out, int M, int n_q, int nsplit, int D,
+                             void* stream) {
+  return b2_launch(attn_merge_kernel, dim3(n_q, M), dim3(D), 0, (cudaStream_t)stream, true, o_part, ml_part,
                    (__nv_bfloat16*)out, n_q, nsplit, D);
 }
 

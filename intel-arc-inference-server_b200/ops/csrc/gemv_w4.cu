@@ -72,6 +72,8 @@ struct GemvParams {
   const float* norm_ssq;                 // [M][norm_nb]
   int norm_nb;
   float norm_eps;
+  // x_mode 3: x is the output of quant_x_kernel, [M][KG][128 B] limbs in operand order; xq_gs [M][KG] {scale, -8 sum X}
+  const uint32_t* xq_gs;
   // tensor-parallel fold (row-parallel linear): the n-block's partial sums are pushed into every rank's
   // landing buffer [2 slots][world][tp_mcap][N], flagged per (slot, source rank, n-block), and the fold
   // adds the ranks' parts in rank order.  tp.world <= 1: single GPU.
@@ -165,6 +167,90 @@ __device__ __forceinline__ void group_mma(float (&acc)[T][4], uint32_t blk_addr,
     }
   }
 }
+
+// ---- activation staging, shared by the GEMV's own prologue and the stand-alone quantiser
+// Eight activations (one 16-byte vector of a row, k .. k + 7) as packed bf16, by input mode.
+__device__ __forceinline__ uint4 stage_load(const GemvParams& p, const uint8_t* xbase, int row, int k, float rinv) {
+  uint4 val;
+  if (p.x_mode == 0) {
+    val = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(xbase) + (size_t)row * p.ldx + k);
+  } else if (p.x_mode == 2) {
+    const uint4 rv = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(xbase) + (size_t)row * p.ldx + k);
+    const float4 w0 = *reinterpret_cast<const float4*>(p.norm_w + k), w1 = *reinterpret_cast<const float4*>(p.norm_w + k + 4);
+    val.x = pack_bf16(bf16_lo(rv.x) * rinv * w0.x, bf16_hi(rv.x) * rinv * w0.y);
+    val.y = pack_bf16(bf16_lo(rv.y) * rinv * w0.z, bf16_hi(rv.y) * rinv * w0.w);
+    val.z = pack_bf16(bf16_lo(rv.z) * rinv * w1.x, bf16_hi(rv.z) * rinv * w1.y);
+    val.w = pack_bf16(bf16_lo(rv.w) * rinv * w1.z, bf16_hi(rv.w) * rinv * w1.w);
+  } else {
+    // SiLU(gate) * up over summed fp32 slices; gate/up alternate in runs of 16
+    const float* base = reinterpret_cast<const float*>(xbase) + (size_t)row * p.ldx + (k >> 4) * 32 + (k & 15);
+    float gsum[8], usum[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) gsum[i] = usum[i] = 0.f;
+#pragma unroll 4
+    for (int s = 0; s < p.s_in; ++s) {
+      const float4* gp = reinterpret_cast<const float4*>(base + (size_t)s * p.x_slice);
+      const float4 g0 = gp[0], g1 = gp[1], u0 = gp[4], u1 = gp[5];
+      gsum[0] += g0.x; gsum[1] += g0.y; gsum[2] += g0.z; gsum[3] += g0.w;
+      gsum[4] += g1.x; gsum[5] += g1.y; gsum[6] += g1.z; gsum[7] += g1.w;
+      usum[0] += u0.x; usum[1] += u0.y; usum[2] += u0.z; usum[3] += u0.w;
+      usum[4] += u1.x; usum[5] += u1.y; usum[6] += u1.z; usum[7] += u1.w;
+    }
+    val.x = pack_bf16(silu(gsum[0]) * usum[0], silu(gsum[1]) * usum[1]);
+    val.y = pack_bf16(silu(gsum[2]) * usum[2], silu(gsum[3]) * usum[3]);
+    val.z = pack_bf16(silu(gsum[4]) * usum[4], silu(gsum[5]) * usum[5]);
+    val.w = pack_bf16(silu(gsum[6]) * usum[6], silu(gsum[7]) * usum[7]);
+  }
+  return val;
+}
+
+// Quantises a group's 64 activations (as rounded to bf16) to 15-bit integers with one scale,
+// X = rint(x * 16383 / amax) = 128 X_hi + X_lo with X_hi in [-128, 127] and X_lo in [0, 127].  The eight
+// lanes that hold a group (one 16-byte vector each) share amax and sum(X) by shuffles; every lane of the
+// warp must call this.  w[0..3] = high limbs of k 0..3, low limbs of k 0..3, high of k 4..7, low of k 4..7.
+struct StagedVec {
+  uint32_t w[4];
+  float scale;
+  int m8sum;  // -8 sum(X) of the whole group
+};
+__device__ __forceinline__ StagedVec stage_quant(uint4 val) {
+  float xf[8] = {bf16_lo(val.x), bf16_hi(val.x), bf16_lo(val.y), bf16_hi(val.y),
+                 bf16_lo(val.z), bf16_hi(val.z), bf16_lo(val.w), bf16_hi(val.w)};
+  float amax = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(xf[i]));
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
+  const bool live = amax > 0.f && amax < 3.0e38f;
+  const float inv = live ? 16383.f / amax : 0.f;
+  int X[8], sumX = 0;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    X[i] = __float2int_rn(xf[i] * inv);
+    sumX += X[i];
+  }
+  sumX += __shfl_xor_sync(0xffffffffu, sumX, 1);
+  sumX += __shfl_xor_sync(0xffffffffu, sumX, 2);
+  sumX += __shfl_xor_sync(0xffffffffu, sumX, 4);
+  StagedVec o;
+  o.w[0] = o.w[1] = o.w[2] = o.w[3] = 0;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    o.w[0] |= (uint32_t)((X[i] >> 7) & 0xff) << (8 * i);
+    o.w[1] |= (uint32_t)(X[i] & 127) << (8 * i);
+    o.w[2] |= (uint32_t)((X[i + 4] >> 7) & 0xff) << (8 * i);
+    o.w[3] |= (uint32_t)(X[i + 4] & 127) << (8 * i);
+  }
+  o.scale = live ? amax / 16383.f : 0.f;
+  o.m8sum = -8 * sumX;
+  return o;
+}
+// Word index inside a group's 32 words where vector vq (k = 8 vq .. 8 vq + 7) puts its first word: 32-k step
+// vq >> 2, operand register (vq & 3) >> 1, lanes t = 2 (vq & 1) and + 1.  Lane t's words sit at
+// t * 8 + limb * 4 + step * 2 + register, so the main loop reads a limb's four words with one 16-byte load;
+// the vector's four words go to +0 (high, k 0..3), +4 (low), +8 (high, k 4..7), +12 (low).
+__device__ __forceinline__ int stage_word(int vq) { return (vq & 1) * 16 + (vq >> 2) * 2 + ((vq & 3) >> 1); }
 
 template <int T>
 __global__ void __launch_bounds__(kThreads, (T <= 2 ? 2 : 1)) gemv_w4_kernel(const GemvParams p) {
@@ -261,90 +347,52 @@ __global__ void __launch_bounds__(kThreads, (T <= 2 ? 2 : 1)) gemv_w4_kernel(con
       const int k0 = (gbeg + c0) * 64;
       const int nvec = cg * 8;
       const int total = p.rows * xvec;  // a multiple of 8; lanes of a warp stay together in groups of 8
+      if (p.x_mode == 3) {
+        // the rows were quantised once by quant_x_kernel: plain copies, nothing to compute per CTA
+        const uint8_t* xq = xbase;
+        for (int v0 = 0; v0 < total; v0 += kConsumerThreads) {
+          const int v = v0 + tid;
+          const int row = v / xvec, col = v - row * xvec;
+          if (v < total && col < nvec) {
+            uint4 q = make_uint4(0, 0, 0, 0);
+            if (row < p.M) q = *reinterpret_cast<const uint4*>(xq + ((size_t)row * p.KG + gbeg + c0) * 128 + (size_t)col * 16);
+            asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(xs0 + row * strideB + col * 16), "r"(q.x), "r"(q.y),
+                         "r"(q.z), "r"(q.w) : "memory");
+          }
+        }
+        for (int i0 = 0; i0 < p.rows * cg; i0 += kConsumerThreads) {
+          const int i = i0 + tid;
+          if (i < p.rows * cg) {
+            const int row = i / cg, gq = i - row * cg;
+            uint2 sv = make_uint2(0, 0);
+            if (row < p.M) sv = *reinterpret_cast<const uint2*>(p.xq_gs + ((size_t)row * p.KG + gbeg + c0 + gq) * 2);
+            asm volatile("st.shared.v2.u32 [%0], {%1, %2};" ::"r"(gs0 + (gq * 8 * T + row) * 8), "r"(sv.x), "r"(sv.y) : "memory");
+          }
+        }
+      } else {
       for (int v0 = 0; v0 < total; v0 += kConsumerThreads) {
         const int v = v0 + tid;
         const int row = v / xvec, col = v - row * xvec;
         uint4 val = make_uint4(0, 0, 0, 0);
         if (v < total && row < p.M && col < nvec) {
-          const int k = k0 + col * 8;
-          if (p.x_mode == 0) {
-            val = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(xbase) + (size_t)row * p.ldx + k);
-          } else if (p.x_mode == 2) {
-            const uint4 rv = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(xbase) + (size_t)row * p.ldx + k);
-            const float4 w0 = *reinterpret_cast<const float4*>(p.norm_w + k), w1 = *reinterpret_cast<const float4*>(p.norm_w + k + 4);
-            float ri;
-            asm volatile("ld.shared.f32 %0, [%1];" : "=f"(ri) : "r"(rinv0 + row * 4));
-            val.x = pack_bf16(bf16_lo(rv.x) * ri * w0.x, bf16_hi(rv.x) * ri * w0.y);
-            val.y = pack_bf16(bf16_lo(rv.y) * ri * w0.z, bf16_hi(rv.y) * ri * w0.w);
-            val.z = pack_bf16(bf16_lo(rv.z) * ri * w1.x, bf16_hi(rv.z) * ri * w1.y);
-            val.w = pack_bf16(bf16_lo(rv.w) * ri * w1.z, bf16_hi(rv.w) * ri * w1.w);
-          } else {
-            // SiLU(gate) * up over summed fp32 slices; gate/up alternate in runs of 16
-            const float* base = reinterpret_cast<const float*>(xbase) + (size_t)row * p.ldx + (k >> 4) * 32 + (k & 15);
-            float gsum[8], usum[8];
-#pragma unroll
-            for (int i = 0; i < 8; ++i) gsum[i] = usum[i] = 0.f;
-#pragma unroll 4
-            for (int s = 0; s < p.s_in; ++s) {
-              const float4* gp = reinterpret_cast<const float4*>(base + (size_t)s * p.x_slice);
-              const float4 g0 = gp[0], g1 = gp[1], u0 = gp[4], u1 = gp[5];
-              gsum[0] += g0.x; gsum[1] += g0.y; gsum[2] += g0.z; gsum[3] += g0.w;
-              gsum[4] += g1.x; gsum[5] += g1.y; gsum[6] += g1.z; gsum[7] += g1.w;
-              usum[0] += u0.x; usum[1] += u0.y; usum[2] += u0.z; usum[3] += u0.w;
-              usum[4] += u1.x; usum[5] += u1.y; usum[6] += u1.z; usum[7] += u1.w;
-            }
-            val.x = pack_bf16(silu(gsum[0]) * usum[0], silu(gsum[1]) * usum[1]);
-            val.y = pack_bf16(silu(gsum[2]) * usum[2], silu(gsum[3]) * usum[3]);
-            val.z = pack_bf16(silu(gsum[4]) * usum[4], silu(gsum[5]) * usum[5]);
-            val.w = pack_bf16(silu(gsum[6]) * usum[6], silu(gsum[7]) * usum[7]);
-          }
+          float ri = 1.f;
+          if (p.x_mode == 2) asm volatile("ld.shared.f32 %0, [%1];" : "=f"(ri) : "r"(rinv0 + row * 4));
+          val = stage_load(p, xbase, row, k0 + col * 8, ri);
         }
-        // Quantise the group's 64 activations (as rounded to bf16) to 15-bit integers with one scale,
-        // X = rint(x * 16383 / amax) = 128 X_hi + X_lo with X_hi in [-128, 127] and X_lo in [0, 127].
-        // The eight lanes that hold a group share amax and sum(X) by shuffles.
-        float xf[8] = {bf16_lo(val.x), bf16_hi(val.x), bf16_lo(val.y), bf16_hi(val.y),
-                       bf16_lo(val.z), bf16_hi(val.z), bf16_lo(val.w), bf16_hi(val.w)};
-        float amax = 0.f;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(xf[i]));
-        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
-        const bool live = amax > 0.f && amax < 3.0e38f;
-        const float inv = live ? 16383.f / amax : 0.f;
-        int X[8], sumX = 0;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          X[i] = __float2int_rn(xf[i] * inv);
-          sumX += X[i];
-        }
-        sumX += __shfl_xor_sync(0xffffffffu, sumX, 1);
-        sumX += __shfl_xor_sync(0xffffffffu, sumX, 2);
-        sumX += __shfl_xor_sync(0xffffffffu, sumX, 4);
+        const StagedVec sv = stage_quant(val);
         if (v < total) {
-          uint32_t hiA = 0, hiB = 0, loA = 0, loB = 0;
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            hiA |= (uint32_t)((X[i] >> 7) & 0xff) << (8 * i);
-            loA |= (uint32_t)(X[i] & 127) << (8 * i);
-            hiB |= (uint32_t)((X[i + 4] >> 7) & 0xff) << (8 * i);
-            loB |= (uint32_t)(X[i + 4] & 127) << (8 * i);
-          }
-          // k = 8 vq .. 8 vq + 7 of the group: 32-k step vq >> 2, operand register (vq & 3) >> 1, lanes
-          // t = 2 (vq & 1) and + 1.  Lane t's words sit at t * 8 + limb * 4 + step * 2 + register, so
-          // the main loop reads a limb's four words with one 16-byte load.
           const int vq = col & 7;
-          const uint32_t dst = xs0 + row * strideB + ((col >> 3) * 32 + (vq & 1) * 16 + (vq >> 2) * 2 + ((vq & 3) >> 1)) * 4;
-          sts32(dst, hiA);
-          sts32(dst + 16, loA);
-          sts32(dst + 32, hiB);
-          sts32(dst + 48, loB);
+          const uint32_t dst = xs0 + row * strideB + ((col >> 3) * 32 + stage_word(vq)) * 4;
+          sts32(dst, sv.w[0]);
+          sts32(dst + 16, sv.w[1]);
+          sts32(dst + 32, sv.w[2]);
+          sts32(dst + 48, sv.w[3]);
           if (vq == 0) {
             const uint32_t ga = gs0 + ((col >> 3) * 8 * T + row) * 8;
-            asm volatile("st.shared.v2.u32 [%0], {%1, %2};" ::"r"(ga), "r"(__float_as_uint(live ? amax / 16383.f : 0.f)),
-                         "r"((uint32_t)(-8 * sumX)) : "memory");
+            asm volatile("st.shared.v2.u32 [%0], {%1, %2};" ::"r"(ga), "r"(__float_as_uint(sv.scale)), "r"((uint32_t)sv.m8sum) : "memory");
           }
         }
+      }
       }
     }
     consumer_sync();
@@ -481,6 +529,42 @@ __global__ void __launch_bounds__(kThreads, (T <= 2 ? 2 : 1)) gemv_w4_kernel(con
   }
 }
 
+
+// Stand-alone activation quantiser: what the GEMV's prologue does, once per row instead of once per CTA.
+// Worth its launch from a few rows up, where every CTA of the GEMV would otherwise repeat M rows of work.
+// grid (ceil(KG / 32), M), 256 threads: one 16-byte vector per thread.
+__global__ void __launch_bounds__(256) quant_x_kernel(const GemvParams p, uint8_t* xq, uint32_t* xq_gs) {
+  __shared__ float s_rinv;
+  pdl_wait();
+  pdl_launch_dependents();
+  const int row = blockIdx.y, tid = threadIdx.x;
+  if (p.x_mode == 2) {
+    if (tid < 32) {
+      float ss = 0.f;
+      for (int j = tid; j < p.norm_nb; j += 32) ss += p.norm_ssq[(size_t)row * p.norm_nb + j];
+      ss = warp_sum(ss);
+      if (tid == 0) s_rinv = rsqrtf(ss / (float)(p.KG * 64) + p.norm_eps);
+    }
+    __syncthreads();
+  }
+  const int v = blockIdx.x * 256 + tid;      // vector of the row
+  const int group = v >> 3, vq = v & 7;
+  uint4 val = make_uint4(0, 0, 0, 0);
+  if (group < p.KG) val = stage_load(p, reinterpret_cast<const uint8_t*>(p.x), row, v * 8, p.x_mode == 2 ? s_rinv : 1.f);
+  const StagedVec sv = stage_quant(val);
+  if (group < p.KG) {
+    uint32_t* dst = reinterpret_cast<uint32_t*>(xq + ((size_t)row * p.KG + group) * 128) + stage_word(vq);
+    dst[0] = sv.w[0];
+    dst[4] = sv.w[1];
+    dst[8] = sv.w[2];
+    dst[12] = sv.w[3];
+    if (vq == 0) {
+      xq_gs[((size_t)row * p.KG + group) * 2] = __float_as_uint(sv.scale);
+      xq_gs[((size_t)row * p.KG + group) * 2 + 1] = (uint32_t)sv.m8sum;
+    }
+  }
+}
+
 template <int T>
 int launch_t(GemvParams& p, cudaStream_t stream) {
   // staged rows and chunk length: as much of the split's k range as fits the activation budget
@@ -535,7 +619,7 @@ extern "C" int b2_gemv_w4(const void* w4b, const void* x, float* out, int M, int
   p.batches = 1; p.expert_ids = nullptr; p.expert_bytes = 0; p.x_div = 1; p.x_batch_bytes = 0; p.out_batch = 0;
   p.fold_tickets = nullptr; p.fold_resid_in = nullptr; p.fold_resid_out = nullptr; p.fold_ssq = nullptr;
   p.norm_w = nullptr; p.norm_ssq = nullptr; p.norm_nb = 0; p.norm_eps = 0.f;
-  p.tp.table = nullptr; p.tp.epoch = nullptr; p.tp.world = 0; p.tp.rank = 0; p.tp_mcap = 0;
+  p.tp.table = nullptr; p.tp.epoch = nullptr; p.tp.world = 0; p.tp.rank = 0; p.tp_mcap = 0; p.xq_gs = nullptr;
   p.M = M; p.N = N; p.KG = K / 64; p.S = S;
   p.gps = (p.KG + S - 1) / S;
   if (p.gps % kG != 0) p.gps += kG - p.gps % kG;   // splits start on a stage boundary
@@ -557,6 +641,7 @@ extern "C" int b2_gemv_w4_fused(const void* w4b, const void* x, float* out, int 
                                 int tp_mcap, void* stream) {
   if (M < 1 || M > 64 || K % 64 != 0 || S < 1) return -1;
   if (x_mode == 2 && (K % 128 != 0 || !norm_w || !norm_ssq)) return -2;
+  if (x_mode == 3 && !norm_ssq) return -2;
   if (tp_world > 1 && (tp_world > kMaxRanks || tp_rank < 0 || tp_rank >= tp_world || !tp_table || !tp_epoch ||
                        !fold_tickets || M > tp_mcap))
     return -3;
@@ -574,6 +659,7 @@ extern "C" int b2_gemv_w4_fused(const void* w4b, const void* x, float* out, int 
   p.norm_w = norm_w; p.norm_ssq = norm_ssq; p.norm_nb = K / 128; p.norm_eps = norm_eps;
   p.tp.table = (const unsigned long long*)tp_table; p.tp.epoch = tp_epoch; p.tp.world = tp_world; p.tp.rank = tp_rank;
   p.tp_mcap = tp_mcap;
+  p.xq_gs = reinterpret_cast<const uint32_t*>(norm_ssq);   // x_mode 3: the group scales ride in the norm_ssq slot
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   if (M <= 8) return launch_t<1>(p, st);
   if (M <= 16) return launch_t<2>(p, st);
@@ -599,8 +685,21 @@ extern "C" int b2_gemv_w4_experts(const void* w4b_stack, long long expert_bytes,
   p.x_batch_bytes = x_batch_bytes; p.out_batch = (long long)S * N;
   p.fold_tickets = nullptr; p.fold_resid_in = nullptr; p.fold_resid_out = nullptr; p.fold_ssq = nullptr;
   p.norm_w = nullptr; p.norm_ssq = nullptr; p.norm_nb = 0; p.norm_eps = 0.f;
-  p.tp.table = nullptr; p.tp.epoch = nullptr; p.tp.world = 0; p.tp.rank = 0; p.tp_mcap = 0;
+  p.tp.table = nullptr; p.tp.epoch = nullptr; p.tp.world = 0; p.tp.rank = 0; p.tp_mcap = 0; p.xq_gs = nullptr;
   return launch_t<1>(p, reinterpret_cast<cudaStream_t>(stream));
+}
+
+// Quantise activation rows for x_mode 3.  Input modes as the GEMV's (0 bf16 rows, 1 SiLU*up of fp32 slices,
+// 2 residual rows with RMSNorm); xq is [M][K / 64][128] bytes, xq_gs [M][K / 64][2] words.
+extern "C" int b2_quant_x(const void* x, int M, int K, int ldx, int x_mode, int s_in, long long x_slice,
+                          const float* norm_w, const float* norm_ssq, float norm_eps, void* xq, void* xq_gs, void* stream) {
+  if (M < 1 || K % 64 != 0 || x_mode < 0 || x_mode > 2) return -1;
+  if (x_mode == 2 && (K % 128 != 0 || !norm_w || !norm_ssq)) return -2;
+  GemvParams p = {};
+  p.x = x; p.M = M; p.KG = K / 64; p.ldx = ldx; p.x_mode = x_mode; p.s_in = s_in; p.x_slice = x_slice;
+  p.norm_w = norm_w; p.norm_ssq = norm_ssq; p.norm_nb = K / 128; p.norm_eps = norm_eps;
+  dim3 grid((p.KG * 8 + 255) / 256, M);
+  return b2_launch(quant_x_kernel, grid, dim3(256), 0, (cudaStream_t)stream, true, p, (uint8_t*)xq, (uint32_t*)xq_gs);
 }
 
 B2_DEFINE_STATUS(gemv)

@@ -17,7 +17,7 @@ import torch
 from . import build as _build
 
 _lib: Optional[ctypes.CDLL] = None
-_UNITS = ("gemv", "decode", "gemm", "attn", "moe", "comm", "ep", "spec")
+_UNITS = ("gemv", "decode", "gemm", "attn", "attnrows", "moe", "comm", "ep", "spec")
 
 # Control block layout (int32 words) -- mirrors decode_ops.cu
 CTRL_N_ROWS = 0
@@ -138,6 +138,16 @@ def gemv_w4_fused(w4b, x, out, m, n, k, splits, *, x_mode=0, s_in=1, x_slice=0, 
     _check(rc, "gemv_w4_fused")
 
 
+def quant_x(x, m, k, xq, xq_gs, *, x_mode=0, s_in=1, x_slice=0, ldx=None, norm_w=None, norm_ssq=None, norm_eps=0.0):
+    """Quantises ``m`` activation rows once for ``gemv_w4_fused(..., x_mode=3)``: 15-bit two-limb integers per
+    64-k group in the GEMV's operand order (``xq``) and the groups' {scale, -8 sum} (``xq_gs``)."""
+    if ldx is None:
+        ldx = 2 * k if x_mode == 1 else k
+    rc = lib().b2_quant_x(_p(x), m, k, ldx, x_mode, s_in, ctypes.c_longlong(x_slice), _p(norm_w), _p(norm_ssq),
+                          ctypes.c_float(norm_eps), _p(xq), _p(xq_gs), _stream())
+    _check(rc, "quant_x")
+
+
 def resid_norm(mode: int, m: int, h: int, w: torch.Tensor, eps: float, resid_out: torch.Tensor,
                x_out: Optional[torch.Tensor], *, embed=None, ctrl=None, vocab=0, resid_in=None, part=None,
                part_slice=0, splits=0, flag=None):
@@ -165,6 +175,18 @@ def attn_decode(q, k_cache, v_cache, block_table, ctrl, o_part, ml_part, out, m,
                               ctypes.c_float(scale), int(kv_int8), _p(tickets), _stream())
     launch_count += 0 if tickets is not None else 1
     _check(rc, "attn_decode")
+
+
+def attn_rows(q, k_cache, v_cache, block_table, ctrl, o_part, ml_part, out, tickets, m, n_q, n_kv, d, nsplit,
+              max_blocks, scale):
+    """Decode / verify attention that serves consecutive rows of one request together on the tensor cores
+    (bf16 KV, head size 128); same split-KV partial buffers and in-kernel merge as ``attn_decode``."""
+    rc = lib().b2_attn_rows(_p(q), _p(k_cache), _p(v_cache), _p(block_table), _p(ctrl), _p(o_part), _p(ml_part),
+                            _p(out), _p(tickets), m, n_q, n_kv, d, nsplit, max_blocks, ctypes.c_float(scale), _stream())
+    _check(rc, "attn_rows")
+    if tickets is None:     # many rows: the merge is its own launch, one CTA per row and head
+        rc = lib().b2_attn_merge(_p(o_part), _p(ml_part), _p(out), m, n_q, nsplit, d, _stream())
+        _check(rc, "attn_merge")
 
 
 def head_ncand(n: int) -> int:

@@ -1,0 +1,81 @@
+"""Failure detection without faulting a GPU: the wire's host mirror under injected losses (CPU threads), and a
+device wait that runs out because nothing sets its flag (GPU, bounded, context stays usable)."""
+import numpy as np
+import pytest
+
+from b200serve.parallel.protocol import STALE, TIMEOUT, HostWire, run_ranks
+
+
+def _parts(rank, i):
+    rng = np.random.default_rng(1000 * rank + i)
+    return rng.standard_normal(64).astype(np.float32)
+
+
+def test_host_mirror_all_ranks_hold_identical_bits():
+    w = HostWire(4, 64)
+    out = run_ranks(w, 6, _parts)
+    for i in range(6):
+        want = np.zeros(64, dtype=np.float32)
+        for r in range(4):
+            want = want + _parts(r, i)
+        for r in range(4):
+            assert out[r][i] is not None and np.array_equal(out[r][i], out[0][i])
+            assert np.array_equal(out[r][i], want)
+    assert all(s is None for s in w.status)
+
+
+def test_dropped_flag_times_out_once_and_latches():
+    w = HostWire(2, 64, bound_s=0.1)
+    w.drop_next(writer=1, reader=0)            # rank 0 never sees rank 1's first flag
+    out = run_ranks(w, 3, _parts)
+    assert out[0][0] is None and w.status[0] == (TIMEOUT, 1, 1)
+    assert w.bounds_paid[0] == 1               # later waits do not spin again: one bound per dead peer
+    assert out[1][0] is not None               # the other direction was delivered
+    w.reset(0)
+    assert w.status[0] is None
+
+
+def test_flag_before_data_is_reported_as_stale():
+    w = HostWire(2, 64, bound_s=0.1)
+    w.skip_data(writer=0, reader=1)
+    out = run_ranks(w, 1, _parts)
+    assert out[1][0] is None and w.status[1][0] == STALE
+
+
+def test_rank_that_leaves_between_calls_costs_one_bound():
+    w = HostWire(3, 64, bound_s=0.1)
+    first = run_ranks(w, 1, _parts)
+    assert all(o[0] is not None for o in first)
+    w.kill(2)                                   # leaves between steps, nothing in flight
+    out = run_ranks(w, 2, _parts)
+    assert out[0][0] is None and out[1][0] is None
+    assert w.status[0][0] == TIMEOUT and w.status[0][1] == 2
+    assert w.bounds_paid[0] == 1 and w.bounds_paid[1] == 1
+
+
+@pytest.mark.gpu
+def test_device_wait_runs_out_and_reports_status():
+    """A counter that nothing increments: the kernel gives up after its bound, the status word names the wait,
+    the context stays usable and the status can be cleared."""
+    import time
+    import torch
+    from b200serve.ops import lib as K
+    K.status_clear()
+    cnt = torch.zeros(4, dtype=torch.int32, device="cuda")
+    t0 = time.time()
+    K.wire_wait(cnt, 1)
+    torch.cuda.synchronize()
+    dt = time.time() - t0
+    st = K.status()
+    assert "comm" in st and st["comm"]["code"] == hex(0x501)
+    assert 0.2 < dt < 10.0
+    with pytest.raises(K.KernelError):
+        K.check_status()
+    K.status_clear()
+    assert K.status() == {}
+    x = torch.ones(8, device="cuda")           # the context is still usable
+    assert float(x.sum()) == 8.0
+    cnt.fill_(1)
+    K.wire_wait(cnt, 1)                          # a satisfied wait returns at once
+    torch.cuda.synchronize()
+    assert K.status() == {}

@@ -289,3 +289,69 @@ def test_gemv_fused_fold_and_norm(m):
     xn = (rf * torch.rsqrt(rf.pow(2).mean(-1, keepdim=True) + 1e-6) * nw).to(torch.bfloat16).float()
     ref = xn @ Q.dequant(q2, s2).t()
     assert (part2.sum(0).cpu() - ref).abs().max() <= 5e-3 * ref.abs().max() + 1e-4
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("m", [3, 8, 20])
+def test_prequantised_rows_give_the_same_bits_as_in_kernel_staging(m):
+    """quant_x + x_mode 3 is the GEMV's own prologue run once per row: the partial sums must be bit-identical."""
+    from b200serve.ops import lib as K
+    from b200serve.utils import quant as Q
+    torch.manual_seed(m)
+    n, k = 384, 1024
+    w4b = Q.random_w4b(n, k, "cuda", seed=3)
+    x = (torch.randn(m, k, device="cuda") * 0.7).to(torch.bfloat16)
+    s = K.gemv_splits(n, k)
+    a = torch.zeros(s * m * n, dtype=torch.float32, device="cuda")
+    b = torch.zeros_like(a)
+    K.gemv_w4(w4b, x, a, m, n, k, s)
+    xq = torch.zeros(m * (k // 64) * 128, dtype=torch.uint8, device="cuda")
+    gs = torch.zeros(m * (k // 64) * 2, dtype=torch.int32, device="cuda")
+    K.quant_x(x, m, k, xq, gs)
+    K.gemv_w4_fused(w4b, xq, b, m, n, k, s, x_mode=3, norm_ssq=gs)
+    torch.cuda.synchronize()
+    K.check_status()
+    assert torch.equal(a, b)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("n_q,n_kv,rows,ctx,nsplit", [(40, 8, [(0, 8)], 1500, 16), (16, 4, [(0, 3), (1, 1), (0, 2)], 700, 8),
+                                                       (8, 2, [(0, 1)], 4096, 32), (5, 1, [(1, 8), (0, 5)], 333, 4)])
+def test_attn_rows_matches_per_row_kernel(n_q, n_kv, rows, ctx, nsplit):
+    """The tensor-core multi-row kernel against the per-row kernel (itself checked against fp32): groups of
+    consecutive rows of one request, several requests in one step, ragged contexts, several splits."""
+    k_ = K()
+    torch.manual_seed(ctx)
+    d = 128
+    max_blocks = (ctx + 15) // 16 + 2
+    num_pages = 2 * max_blocks + 2
+    table = torch.zeros(2, max_blocks, dtype=torch.int32)
+    perm = torch.randperm(num_pages - 1) + 1
+    table[0] = perm[:max_blocks].to(torch.int32)
+    table[1] = perm[max_blocks: 2 * max_blocks].to(torch.int32)
+    table = table.cuda()
+    kc = (torch.randn(num_pages, n_kv, 16, d, device="cuda") * 0.5).to(torch.bfloat16)
+    vc = (torch.randn(num_pages, n_kv, 16, d, device="cuda") * 0.5).to(torch.bfloat16)
+    spec = []
+    for req, n in rows:                      # each group's rows sit at consecutive positions ending at ctx - 1
+        base = ctx - n - 7 * req
+        spec += [(req, base + i, 0) for i in range(n)]
+    m = len(spec)
+    q = torch.randn(m, n_q * d, device="cuda").to(torch.bfloat16)
+    ctrl = _ctrl(spec)
+    o_part = torch.zeros(m * n_q * nsplit * d, device="cuda")
+    ml = torch.zeros(m * n_q * nsplit * 2, device="cuda")
+    ref = torch.zeros(m, n_q * d, dtype=torch.bfloat16, device="cuda")
+    k_.attn_decode(q, kc, vc, table, ctrl, o_part, ml, ref, m, n_q, n_kv, d, nsplit, max_blocks, d ** -0.5)
+    tickets = torch.zeros(m * n_kv, dtype=torch.int32, device="cuda")
+    for rep in range(3):
+        out = torch.full_like(ref, float("nan"))
+        o_part.fill_(float("nan"))
+        k_.attn_rows(q, kc, vc, table, ctrl, o_part, ml, out, tickets if rep < 2 else None, m, n_q, n_kv, d, nsplit,
+                     max_blocks, d ** -0.5)
+        torch.cuda.synchronize()
+        k_.check_status()
+        assert not torch.isnan(out.float()).any()
+        err = (out.float() - ref.float()).abs().max()
+        assert err <= 2e-2 * ref.float().abs().max() + 2e-3, float(err)
+        assert int(tickets.abs().sum()) == 0
