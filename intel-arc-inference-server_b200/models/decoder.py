@@ -13,6 +13,8 @@ activation load) = 9; the reference's list has 12 per layer (774 for 64 layers).
 """
 from __future__ import annotations
 
+import os
+
 import math
 from dataclasses import dataclass
 from typing import List, Optional
@@ -125,10 +127,9 @@ class DecoderModel:
         # from this many rows up the activations are quantised once by their own kernel instead of in every
         # CTA of the GEMV (whose prologue repeats the rows' work per 128 output columns)
         self.prequant_rows = 3
-        import os
         self.attn_rows_min = int(os.environ.get("B2_ATTN_ROWS_MIN", "1"))
         self.attn_merge_inkernel_rows = int(os.environ.get("B2_ATTN_MERGE_INKERNEL_ROWS", "0"))
-        self.fused = self.nccl is None     # dense layers: residual folds and norms ride inside the GEMVs
+        self.fused = self.nccl is None and os.environ.get("B2_UNFUSED", "0") != "1"     # dense layers: residual folds and norms ride inside the GEMVs
         if self.nccl is not None:
             self._red = torch.zeros(max_rows * cfg.hidden, dtype=torch.float32, device=self.device)
             self._gather = torch.zeros(self.nccl[1], max_rows, 2, dtype=torch.float32, device=self.device)

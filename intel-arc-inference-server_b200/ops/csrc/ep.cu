@@ -13,7 +13,7 @@
 //      table of the expert-sorted receive buffer (rows of source 0 first, then source 1, ...); for ALL
 //      experts computes where this rank's rows start in the destination's buffer -- every rank runs the
 //      same arithmetic on the same counts, so nothing else has to be exchanged;
-//   4. ep_dispatch: one CTA per (token, slot) stores the token's activation row straight into the
+//   4. ep_dispatch: one warp per (token, slot) stores the token's activation row straight into the
 //      destination's receive buffer, records (source, token slot) beside it and counts one arrival on
 //      the destination's 128-row block; the grouped GEMM there starts a block as soon as its rows are in
 //      (gemm_tc.cu: blk_wait), so the transfer overlaps the expert GEMMs block by block;
@@ -121,26 +121,39 @@ struct EpDispatchParams {
   const unsigned long long* src_table;   // [kMaxRanks]: recv_src [cap_rows] ints
 };
 
-__global__ void __launch_bounds__(256) ep_dispatch_kernel(const EpDispatchParams p) {
+// grid T (one CTA per token), one warp per slot.
+__global__ void __launch_bounds__(1024) ep_dispatch_kernel(const EpDispatchParams p) {
   pdl_wait();
   pdl_launch_dependents();
-  const int i = blockIdx.x;  // token * k + slot
-  const int token = i / p.k;
+  const int token = blockIdx.x, slot = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (slot >= p.k) return;
+  const int i = token * p.k + slot;
   const int e = p.topk_idx[i];
   const int dest = e / p.El;
   const int row = p.send_base[e] + p.rank_in_expert[i];
   if (row >= p.cap_rows) {  // the destination's buffer is full: the token's slot is dropped and reported
-    if (threadIdx.x == 0) record_error(ERR_BAD_ARG, (unsigned)(0x80000000u | row));
+    if (lane == 0) record_error(ERR_BAD_ARG, (unsigned)(0x80000000u | row));
     return;
   }
   const uint4* src = reinterpret_cast<const uint4*>(p.x + (size_t)token * p.H);
   uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.recv_table[dest]) + (size_t)row * p.H);
-  for (int j = threadIdx.x; j < p.H / 8; j += blockDim.x) dst[j] = src[j];
-  if (threadIdx.x == 0) reinterpret_cast<int*>(p.src_table[dest])[row] = (p.me << 24) | i;
-  __threadfence_system();
-  __syncthreads();
-  if (threadIdx.x == 0) {
+  const int nvec = p.H / 8;
+  for (int j0 = 0; j0 < nvec; j0 += 128) {   // four independent 16-byte loads per lane in flight
+    uint4 v[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+      if (j0 + u * 32 + lane < nvec) v[u] = src[j0 + u * 32 + lane];
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+      if (j0 + u * 32 + lane < nvec) dst[j0 + u * 32 + lane] = v[u];
+  }
+  if (lane == 0) reinterpret_cast<int*>(p.src_table[dest])[row] = (p.me << 24) | i;
+  // The warp's stores are ordered before lane 0's release by the warp barrier; the release is at system
+  // scope, so the destination sees the row and its tag before the arrival.
+  __syncwarp();
+  if (lane == 0) {
     int* cnt = reinterpret_cast<int*>(p.recv_table[kMaxRanks + dest]) + p.parity * p.max_blk + (row >> 7);
+    __threadfence_system();
     asm volatile("red.release.sys.global.add.s32 [%0], 1;" ::"l"(cnt) : "memory");
   }
 }
@@ -189,12 +202,12 @@ extern "C" int b2_ep_plan(const void* cnt_table, int epoch, int E, int world, in
 extern "C" int b2_ep_dispatch(const int* topk_idx, const int* rank_in_expert, const int* send_base, const void* x, int T,
                               int k, int H, int E, int world, int me, int cap_rows, int parity, int max_blk,
                               const void* recv_table, const void* src_table, void* stream) {
-  if (H % 8 || world < 1 || E % world || T * k >= (1 << 24)) return -1;
+  if (H % 8 || world < 1 || E % world || T * k >= (1 << 24) || k < 1 || k > 32) return -1;
   EpDispatchParams p;
   p.topk_idx = topk_idx; p.rank_in_expert = rank_in_expert; p.send_base = send_base; p.x = (const __nv_bfloat16*)x;
   p.k = k; p.H = H; p.El = E / world; p.me = me; p.cap_rows = cap_rows; p.parity = parity; p.max_blk = max_blk;
   p.recv_table = (const unsigned long long*)recv_table; p.src_table = (const unsigned long long*)src_table;
-  return b2_launch(ep_dispatch_kernel, dim3(T * k), dim3(256), 0, (cudaStream_t)stream, true, p);
+  return b2_launch(ep_dispatch_kernel, dim3(T), dim3(32 * k), 0, (cudaStream_t)stream, true, p);
 }
 
 extern "C" int b2_ep_flag_all(const void* table, int world, int rank, int epoch, void* stream) {

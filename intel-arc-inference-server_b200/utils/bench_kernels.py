@@ -122,6 +122,34 @@ if __name__ == "__main__":
             eng.prefill(0, ids)
         torch.cuda.synchronize()
         K.check_status()
+    elif what == "fused-one":   # the fused collective kernels as a group of one rank (every "peer" buffer is local)
+        from dataclasses import replace
+        from ..models.config import preset
+        from ..models.weights import random_weights
+        from ..parallel.ep import EpMoe
+        from ..parallel.tp_prefill import TpPrefillRunner
+        from ..runtime.engine import Engine
+        from ..runtime.prefill import PrefillRunner
+        cfg = replace(preset("dense-27b"), n_layers=2)
+        eng = Engine(random_weights(cfg, device="cuda", seed=0, exact=False), max_seqs=1, max_len=2112, use_graphs=False,
+                     prefill_backend="bf16-resident")
+        ids = torch.randint(0, cfg.vocab, (2048,)).tolist()
+        runner = TpPrefillRunner(eng, max_chunk=2048)
+        for _ in range(2):
+            eng.reset(0)
+            runner.run(0, ids)
+        torch.cuda.synchronize()
+        K.check_status()
+        mcfg = replace(preset("moe-35b-a3b"), n_layers=2)
+        meng = Engine(random_weights(mcfg, device="cuda", seed=0, exact=False), max_seqs=1, max_len=2112, use_graphs=False,
+                      prefill_backend="bf16-resident")
+        mrun = PrefillRunner(meng, max_chunk=2048)
+        mrun.ep = EpMoe(mcfg, 2048)
+        for _ in range(2):
+            meng.reset(0)
+            mrun.run(0, ids)
+        torch.cuda.synchronize()
+        K.check_status()
     elif what == "gemv-graph":  # back-to-back launches inside a CUDA graph
         bench_gemv((1, 4, 8), graph=True)
     else:
