@@ -100,3 +100,47 @@ def run_prefill_bench(args, barrier, model: str, backend: str) -> dict:
             "e2e_ms": ms, "h2d": n * 4, "d2h": K.CTRL_WORDS * 4,
             "config": {"model": cfg.name, "global_batch": 1, "seq_len": n, "backend": backend,
                        "parallelism": "replica", "l2": "weights larger than L2"}}
+
+
+def run_spec_bench(args, barrier, iters: int = 12) -> dict:
+    """Draft-and-verify iterations on the 27B shape with FORCED acceptance lengths, so that the step time does
+    not depend on what random-init heads happen to propose: an MTP head (1 layer, draft depth 3) and a
+    DFlash-style block drafter (2 layers, 7 drafts in one block pass), each verified in one trunk step of
+    k + 1 rows.  tokens/s = (accepted + 1) / iteration time (draft + verify, host control included)."""
+    import dataclasses
+    import time
+    from ..runtime.spec import SpecAdapter
+    from ..server.adapter import EngineAdapter
+    cfg = dataclasses.replace(preset(args.model), mtp_layers=1)
+    dev = torch.device("cuda", torch.cuda.current_device())
+    weights = random_weights(cfg, device=dev, seed=0, exact=False)
+    depth = min(args.depth, 4096)
+    out = {}
+    g = torch.Generator().manual_seed(0)
+    ids = torch.randint(0, cfg.vocab - 1, (depth,), generator=g).tolist()
+    for kind, k, accepts in (("mtp", 3, (0, 3)), ("dflash", 7, (0, 3, 7))):
+        eng = Engine(weights, max_seqs=1, max_len=depth + 64 * (iters + 4) + 64, extra_kv_layers=2,
+                     nsplit_attn=max(4, min(64, depth // 128)))
+        ad = SpecAdapter(EngineAdapter(eng), kind, k)
+        pending = ad.prefill(0, ids)
+        for acc in accepts:
+            def iteration(pending):
+                drafts = ad.draft(0, pending, k)
+                res = ad.step({0: [pending] + drafts})[0]
+                keep = min(acc, len(drafts))
+                if keep < len(drafts):
+                    ad.truncate(0, ad.length(0) - (len(drafts) - keep))
+                return res[keep]            # the trunk's token after the last kept row
+            for _ in range(3):
+                pending = iteration(pending)
+            barrier()
+            t0 = time.perf_counter()
+            for _ in range(iters):
+                pending = iteration(pending)
+            torch.cuda.synchronize()
+            dt = (time.perf_counter() - t0) / iters
+            out[f"{kind}_k{k}_accept{acc + 1}"] = {"ms_per_iteration": dt * 1e3, "tokens_per_s": (acc + 1) / dt,
+                                                  "rows_verified": k + 1}
+        del eng, ad
+        torch.cuda.empty_cache()
+    return out
