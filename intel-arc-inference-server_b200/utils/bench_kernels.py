@@ -114,9 +114,10 @@ if __name__ == "__main__":
         from ..models.weights import random_weights
         from ..runtime.engine import Engine
         cfg = replace(preset("dense-27b"), n_layers=2)
-        eng = Engine(random_weights(cfg, device="cuda", seed=0, exact=False), max_seqs=1, max_len=2112, use_graphs=False,
+        ntok = int(sys.argv[2]) if len(sys.argv) > 2 else 2048
+        eng = Engine(random_weights(cfg, device="cuda", seed=0, exact=False), max_seqs=1, max_len=ntok + 64, use_graphs=False,
                      prefill_backend="bf16-resident")
-        ids = torch.randint(0, cfg.vocab, (2048,)).tolist()
+        ids = torch.randint(0, cfg.vocab, (ntok,)).tolist()
         for _ in range(2):
             eng.reset(0)
             eng.prefill(0, ids)
