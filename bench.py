@@ -103,7 +103,7 @@ def main():
     ap.add_argument("--what", default="all", help="decode | prefill | moe | all")
     ap.add_argument("--kv-cache", default="bf16")
     ap.add_argument("--int8-head", action="store_true")
-    ap.add_argument("--prefill-backend", default="bf16")
+    ap.add_argument("--prefill-backend", default="auto")
     ap.add_argument("--parallel", default="replica", help="replica | tp (N > 1)")
     args = ap.parse_args()
     if args.impl == "reference":

@@ -84,6 +84,8 @@ def plan(cfg: ModelConfig, max_seqs: int, max_len, kv_dtype: str = "bf16", int8_
     """``max_len`` an int or "auto".  Raises ValueError with the numbers when it cannot fit."""
     w = weight_bytes(cfg, int8_head, tp, ep)
     resident = 0
+    if prefill_backend == "auto":    # the prompt pass keeps bf16 copies when they take at most 45 % of the memory
+        prefill_backend = "bf16-resident" if 2 * cfg.param_count() / max(tp * ep, 1) <= 0.45 * budget else "bf16"
     if prefill_backend == "bf16-resident":
         resident = (w - 2 * cfg.vocab * cfg.hidden * 2) * 4      # int4 -> bf16 copies of the linears
     elif prefill_backend in ("int8", "l0-int8"):

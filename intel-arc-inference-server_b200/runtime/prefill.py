@@ -33,7 +33,13 @@ class PrefillRunner:
         self.dev = engine.device
         self.max_chunk = max_chunk
         self.backend = engine.prefill_backend
-        if self.backend in ("auto", "l0"):
+        if self.backend == "auto":
+            # keep dequantised bf16 copies of the linears when they take at most 45 % of the GPU's memory (a 27B
+            # model is 54 GB, a 35B-A3B one 70 GB of a B200's 180 GB): the prompt pass then reads them in place
+            # instead of dequantising a slab before every GEMM
+            total = torch.cuda.get_device_properties(self.dev).total_memory if self.dev.type == "cuda" else 0
+            self.backend = "bf16-resident" if 2 * cfg.param_count() <= 0.45 * total else "bf16"
+        if self.backend == "l0":
             self.backend = "bf16"
         if self.backend == "l0-int8":
             self.backend = "int8"

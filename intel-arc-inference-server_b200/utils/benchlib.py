@@ -98,7 +98,8 @@ def run_prefill_bench(args, barrier, model: str, backend: str) -> dict:
     base = 11223.0 if cfg.is_moe else 2800.0
     return {"ms": ms, "tokens": n, "baseline": base, "launches": (K.launch_count - n0),
             "e2e_ms": ms, "h2d": n * 4, "d2h": K.CTRL_WORDS * 4,
-            "config": {"model": cfg.name, "global_batch": 1, "seq_len": n, "backend": backend,
+            "config": {"model": cfg.name, "global_batch": 1, "seq_len": n,
+                       "backend": eng._prefill.backend if eng._prefill is not None else backend,
                        "parallelism": "replica", "l2": "weights larger than L2"}}
 
 
