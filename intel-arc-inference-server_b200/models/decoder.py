@@ -129,6 +129,9 @@ class DecoderModel:
         self.prequant_rows = 3
         self.attn_rows_min = int(os.environ.get("B2_ATTN_ROWS_MIN", "1"))
         self.attn_merge_inkernel_rows = int(os.environ.get("B2_ATTN_MERGE_INKERNEL_ROWS", "0"))
+        # fixed KV split spans make a row's attention bits independent of the rows it is verified with (speculation
+        # then reproduces plain decoding exactly); off, the splits adapt to the context (fastest at any depth)
+        self.attn_fixed_spans = False
         self.fused = self.nccl is None and os.environ.get("B2_UNFUSED", "0") != "1"     # dense layers: residual folds and norms ride inside the GEMVs
         if self.nccl is not None:
             self._red = torch.zeros(max_rows * cfg.hidden, dtype=torch.float32, device=self.device)
@@ -157,7 +160,8 @@ class DecoderModel:
             inkernel = m <= self.attn_merge_inkernel_rows    # few rows: the last split CTA merges; many: a merge launch
             K.attn_rows(b.q, kc, vc, block_table, ctrl, b.o_part, b.ml_part, b.attn_out, b.tickets if inkernel else None,
                         m, cfg.n_q_heads,
-                        cfg.n_kv_heads, cfg.head_dim, self.nsplit_attn, max_blocks, self.scale)
+                        cfg.n_kv_heads, cfg.head_dim, self.nsplit_attn, max_blocks, self.scale,
+                        span_pages=(max_blocks + self.nsplit_attn - 1) // self.nsplit_attn if self.attn_fixed_spans else 0)
         else:
             K.attn_decode(b.q, kc, vc, block_table, ctrl, b.o_part, b.ml_part, b.attn_out, m, cfg.n_q_heads,
                           cfg.n_kv_heads, cfg.head_dim, self.nsplit_attn, max_blocks, self.scale, ks, vs, kv.kv_int8,

@@ -38,6 +38,8 @@ struct AttnRowsParams {
   __nv_bfloat16* out;  // [M][n_q * D]
   int* tickets;        // [M][n_kv]
   int M, n_q, n_kv, gqa, nsplit, max_blocks;
+  int span_pages;  // > 0: every split covers this many pages whatever the context (a row's bits then do not depend
+                   // on which rows share its CTA); 0: the group's context is cut into nsplit equal parts
   float scale_log2;
 };
 
@@ -79,7 +81,7 @@ __global__ void __launch_bounds__(kThreads) attn_rows_kernel(const AttnRowsParam
   int ctx_max = 0;
   for (int r = 0; r < rows; ++r) ctx_max = max(ctx_max, s_pos[z + r] + 1);
   const int total_pages = (ctx_max + 15) >> 4;
-  const int pps = (total_pages + p.nsplit - 1) / p.nsplit;
+  const int pps = p.span_pages > 0 ? p.span_pages : (total_pages + p.nsplit - 1) / p.nsplit;
   const int key0 = split * pps * 16, key1 = min(ctx_max, (split + 1) * pps * 16);
   const int* bt = p.block_table + (size_t)req * p.max_blocks;
 
@@ -285,13 +287,15 @@ __global__ void __launch_bounds__(kThreads) attn_rows_kernel(const AttnRowsParam
 // group merges in the kernel; nullptr: the partials are left for b2_attn_merge.
 extern "C" int b2_attn_rows(const void* q, const void* k_cache, const void* v_cache, const int* block_table,
                             const int* ctrl, float* o_part, float* ml_part, void* out, int* tickets, int M, int n_q,
-                            int n_kv, int D_, int nsplit, int max_blocks, float scale, void* stream) {
+                            int n_kv, int D_, int nsplit, int max_blocks, float scale, int span_pages, void* stream) {
   if (D_ != D || nsplit < 1 || nsplit > 64 || n_q % n_kv != 0 || n_q / n_kv > 16 || M > 64) return -1;
   AttnRowsParams p;
   p.q = (const __nv_bfloat16*)q; p.k_cache = (const __nv_bfloat16*)k_cache; p.v_cache = (const __nv_bfloat16*)v_cache;
   p.block_table = block_table; p.ctrl = ctrl; p.o_part = o_part; p.ml_part = ml_part; p.out = (__nv_bfloat16*)out;
   p.tickets = tickets; p.M = M; p.n_q = n_q; p.n_kv = n_kv; p.gqa = n_q / n_kv; p.nsplit = nsplit; p.max_blocks = max_blocks;
   p.scale_log2 = scale * 1.4426950408889634f;
+  p.span_pages = span_pages;
+  if (span_pages > 0 && (long)span_pages * nsplit < max_blocks) return -2;  // fixed spans must cover the longest sequence
   const int smem = 128 + 2 * KB * ROWB + 64;
   static int configured[64] = {};
   int dev = 0;

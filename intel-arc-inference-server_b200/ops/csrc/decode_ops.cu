@@ -634,6 +634,41 @@ __global__ void __launch_bounds__(256) argmax_finish_kernel(const float* cand_va
   }
 }
 
+// ------------------------------------------------------------------ KV form conversion (int8 cache <-> bf16 scratch)
+// grid (tokens, n_kv), one warp: the row of one (position, KV head), D values.  The int8 cache keeps one fp32
+// scale per row (max |x| / 127), the scheme of rope_append's int8 path (the reference's per-head per-token
+// scale: src/common/kv8.h:1-157).  to_int8 = 1: rows of the bf16 pages (table a) -> int8 pages (table b);
+// 0: the other way.  Positions pos0 .. pos0 + tokens - 1.
+__global__ void __launch_bounds__(32) kv_convert_kernel(__nv_bfloat16* k16, __nv_bfloat16* v16, const int* table16,
+                                                        int8_t* k8, int8_t* v8, float* ks, float* vs, const int* table8,
+                                                        int pos0, int n_kv, int D, int to_int8) {
+  const int pos = pos0 + blockIdx.x, kh = blockIdx.y, lane = threadIdx.x;
+  const size_t r16 = (((size_t)table16[pos >> 4] * n_kv + kh) * 16 + (pos & 15));
+  const size_t r8 = (((size_t)table8[pos >> 4] * n_kv + kh) * 16 + (pos & 15));
+  for (int which = 0; which < 2; ++which) {
+    __nv_bfloat16* p16 = (which ? v16 : k16) + r16 * D;
+    int8_t* p8 = (which ? v8 : k8) + r8 * D;
+    float* sc = (which ? vs : ks) + r8;
+    if (to_int8) {
+      float x[8];
+      float amax = 0.f;
+      const int per = D / 32;
+      for (int u = 0; u < per; ++u) {
+        x[u] = __bfloat162float(p16[lane * per + u]);
+        amax = fmaxf(amax, fabsf(x[u]));
+      }
+      amax = warp_max(amax);
+      const float s = amax > 0.f ? amax / 127.f : 1.f, inv = 1.f / s;
+      for (int u = 0; u < per; ++u) p8[lane * per + u] = (int8_t)__float2int_rn(x[u] * inv);
+      if (lane == 0) *sc = s;
+    } else {
+      const float s = *sc;
+      const int per = D / 32;
+      for (int u = 0; u < per; ++u) p16[lane * per + u] = __float2bfloat16((float)p8[lane * per + u] * s);
+    }
+  }
+}
+
 }  // namespace
 
 // =================================================================== C entry points
@@ -695,6 +730,16 @@ extern "C" int b2_attn_decode(const void* q, const void* k_cache, const void* v_
   if (rc || tickets) return rc;
   return b2_launch(attn_merge_kernel, dim3(n_q, M), dim3(D), 0, st, true, (const float*)o_part, (const float*)ml_part,
                    (__nv_bfloat16*)out, n_q, nsplit, D);
+}
+
+extern "C" int b2_kv_convert(void* k16, void* v16, const int* table16, void* k8, void* v8, float* ks, float* vs,
+                             const int* table8, int pos0, int tokens, int n_kv, int D, int to_int8, void* stream) {
+  if (tokens < 1) return 0;
+  if (D % 32 || D > 256) return -1;
+  kv_convert_kernel<<<dim3(tokens, n_kv), 32, 0, (cudaStream_t)stream>>>((__nv_bfloat16*)k16, (__nv_bfloat16*)v16, table16,
+                                                                        (int8_t*)k8, (int8_t*)v8, ks, vs, table8, pos0, n_kv,
+                                                                        D, to_int8);
+  return (int)cudaGetLastError();
 }
 
 // Merge of split-KV partials as its own launch (one CTA per row and query head).

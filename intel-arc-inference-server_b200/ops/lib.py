@@ -178,15 +178,24 @@ def attn_decode(q, k_cache, v_cache, block_table, ctrl, o_part, ml_part, out, m,
 
 
 def attn_rows(q, k_cache, v_cache, block_table, ctrl, o_part, ml_part, out, tickets, m, n_q, n_kv, d, nsplit,
-              max_blocks, scale):
+              max_blocks, scale, span_pages: int = 0):
     """Decode / verify attention that serves consecutive rows of one request together on the tensor cores
     (bf16 KV, head size 128); same split-KV partial buffers and in-kernel merge as ``attn_decode``."""
     rc = lib().b2_attn_rows(_p(q), _p(k_cache), _p(v_cache), _p(block_table), _p(ctrl), _p(o_part), _p(ml_part),
-                            _p(out), _p(tickets), m, n_q, n_kv, d, nsplit, max_blocks, ctypes.c_float(scale), _stream())
+                            _p(out), _p(tickets), m, n_q, n_kv, d, nsplit, max_blocks, ctypes.c_float(scale), span_pages,
+                            _stream())
     _check(rc, "attn_rows")
     if tickets is None:     # many rows: the merge is its own launch, one CTA per row and head
         rc = lib().b2_attn_merge(_p(o_part), _p(ml_part), _p(out), m, n_q, nsplit, d, _stream())
         _check(rc, "attn_merge")
+
+
+def kv_convert(k16, v16, table16, k8, v8, ks, vs, table8, pos0, tokens, n_kv, d, to_int8: bool):
+    """Rows of positions ``pos0 .. pos0 + tokens`` between bf16 pages (``table16``) and int8 pages + per-row scales
+    (``table8``), one direction per call."""
+    rc = lib().b2_kv_convert(_p(k16), _p(v16), _p(table16), _p(k8), _p(v8), _p(ks), _p(vs), _p(table8), pos0, tokens,
+                             n_kv, d, 1 if to_int8 else 0, _stream())
+    _check(rc, "kv_convert")
 
 
 def head_ncand(n: int) -> int:

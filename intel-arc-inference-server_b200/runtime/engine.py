@@ -190,9 +190,10 @@ class Engine:
         has one (head size 128, bf16 KV, dense FFN or MoE with a grouped path)."""
         if self.prefill_backend == "rows" or n <= self.max_rows:
             return False
-        ok = self.cfg.head_dim == 128 and not self.kv.kv_int8
+        ok = self.cfg.head_dim == 128 and (not self.kv.kv_int8 or (self.tp is None and self.model.nccl is None))
         if not ok and self.prefill_backend != "auto":
-            raise ValueError(f"prefill backend {self.prefill_backend!r} needs head_dim 128 and a bf16 KV cache")
+            raise ValueError(f"prefill backend {self.prefill_backend!r} needs head_dim 128 (and a bf16 KV cache under "
+                             "tensor parallelism)")
         return ok
 
     def decode_begin(self, slots: Sequence[int], tokens: Sequence[int]):

@@ -134,17 +134,87 @@ class PrefillRunner:
         eng.seq_len[slot] = max(eng.seq_len[slot], pos0 + c)
         return resid
 
+    # ------------------------------------------------------------------ int8 KV cache: layer-major pass
+    def _run_int8_kv(self, slot: int, ids: List[int], chunk: int):
+        """Prompt pass into an int8 KV cache.  The attention kernel reads bf16 pages, so the walk is LAYER-major:
+        all chunks go through layer l against a one-layer bf16 scratch (identity page table, positions of the
+        whole sequence), then the layer's new rows are quantised into the int8 cache and the scratch is reused
+        by layer l + 1.  Earlier positions of the sequence (a cached prefix, earlier turns) are dequantised
+        into the scratch first.  Costs one residual row per prompt token (kept across the layer loop) instead
+        of a bf16 cache of all layers."""
+        eng, cfg, m = self.eng, self.cfg, self.eng.model
+        n, start = len(ids), eng.seq_len[slot]
+        total = start + n
+        eng._ensure_pages(slot, total)
+        blocks = (total + 15) // 16
+        sc = getattr(self, "_kv16", None)
+        if sc is None or sc[0].shape[1] < blocks + 1:
+            cap = max(blocks, eng.max_blocks) + 1
+            shape = (1, cap, cfg.n_kv_heads, cfg.page_size, cfg.head_dim)
+            sc = self._kv16 = (torch.zeros(shape, dtype=torch.bfloat16, device=self.dev),
+                               torch.zeros(shape, dtype=torch.bfloat16, device=self.dev),
+                               torch.arange(1, cap + 1, dtype=torch.int32, device=self.dev).clamp_(max=cap - 1).view(1, cap))
+        k16, v16, tab16 = sc
+        if getattr(self, "_resid_all", None) is None or self._resid_all.shape[0] < n:
+            self._resid_all = torch.empty(max(n, self.max_chunk), cfg.hidden, dtype=torch.bfloat16, device=self.dev)
+        resid_all = self._resid_all[:n]
+        ids_dev = torch.as_tensor(ids, dtype=torch.int64).pin_memory().to(self.dev, non_blocking=True)
+        torch.index_select(m.w.embed, 0, ids_dev, out=resid_all)
+        tab8 = eng.block_table[slot]
+        h = cfg.hidden
+        for li, lw in enumerate(m.w.layers):
+            k8, v8, ks, vs = eng.kv.layer(li)
+            if start > 0:
+                K.kv_convert(k16[0], v16[0], tab16[0], k8, v8, ks, vs, tab8, 0, start, cfg.n_kv_heads, cfg.head_dim, False)
+            for c0 in range(0, n, chunk):
+                c = min(chunk, n - c0)
+                resid, x = resid_all[c0: c0 + c], self.x[:c]
+                pos0 = start + c0
+                K.resid_norm(1, c, h, lw.input_norm, cfg.rms_eps, resid, x, resid_in=resid, splits=0)
+                qkv = self.qkv[:c]
+                self.linear(lw.qkv, x, qkv, G.EPI_F32)
+                K.rope_append(qkv, 0, 1, c, None, tab16, tab16.shape[1], m.cos_t, m.sin_t, cfg.n_q_heads, cfg.n_kv_heads,
+                              cfg.head_dim, self.q, k16[0], v16[0], None, None, False, req=0, pos0=pos0)
+                K.attn_prefill(self.q, k16[0], v16[0], tab16[0], self.attn, c, pos0, cfg.n_q_heads, cfg.n_kv_heads,
+                               cfg.head_dim, k16.shape[1], tab16.shape[1], m.scale)
+                self.linear(lw.o, self.attn[:c], resid, G.EPI_RESID_ADD, resid=resid)
+                K.resid_norm(1, c, h, lw.post_norm, cfg.rms_eps, resid, x, resid_in=resid, splits=0)
+                if lw.gate_up is not None:
+                    act = self.act[:c, : cfg.ffn]
+                    self.linear(lw.gate_up, x, act, G.EPI_SILU_MUL)
+                    self.linear(lw.down, act, resid, G.EPI_RESID_ADD, resid=resid)
+                else:
+                    self.resid, keep = resid, self.resid      # the MoE block works on self.resid / self.x
+                    try:
+                        from ..models import moe as _moe
+                        _moe.moe_block_prefill(self, lw, c)
+                    finally:
+                        self.resid = keep
+            K.kv_convert(k16[0], v16[0], tab16[0], k8, v8, ks, vs, tab8, start, n, cfg.n_kv_heads, cfg.head_dim, True)
+        eng.seq_len[slot] = total
+        return resid_all[n - 1: n]
+
     def run(self, slot: int, ids: List[int], chunk: Optional[int] = None) -> int:
         eng, cfg, m = self.eng, self.cfg, self.eng.model
         chunk = min(chunk or self.max_chunk, self.max_chunk)
+        if eng.kv.kv_int8:
+            last_row = self._run_int8_kv(slot, ids, chunk)
+            b = m.buf
+            b.resid[0].copy_(last_row[0])
+            return self._head_of_row0()
         start = eng.seq_len[slot]
         resid = None
         n = len(ids)
         for c0 in range(0, n, chunk):
             resid = self.chunk(slot, ids[c0: c0 + chunk], start + c0)
         last = (n - 1) % chunk
+        m.buf.resid[0].copy_(resid[last])
+        return self._head_of_row0()
+
+    def _head_of_row0(self) -> int:
+        """Final norm, lm_head and arg-max of the residual row in ``buf.resid[0]``."""
+        eng, cfg, m = self.eng, self.cfg, self.eng.model
         b = m.buf
-        b.resid[0].copy_(resid[last])
         K.resid_norm(1, 1, cfg.hidden, m.w.final_norm, cfg.rms_eps, b.resid, b.x, resid_in=b.resid, splits=0)
         if m.int8_head:
             w8, sc = m.w.lm_head_i8

@@ -132,6 +132,8 @@ class SpecAdapter:
             head = draft_model if isinstance(draft_model, MtpWeights) else random_drafter(self.e.cfg, self.e.device)
             kind = "dflash"
         self.head = DraftHead(self.e, head, kind)
+        self.e.model.attn_fixed_spans = True     # verify rows must reproduce single-row decoding bit for bit
+        self.e.graphs.clear()
         self.vocab_size, self.max_len, self.max_seqs, self.eos_ids = inner.vocab_size, inner.max_len, inner.max_seqs, inner.eos_ids
         self.hid: Dict[int, torch.Tensor] = {}     # hidden rows of the slot's last trunk step
         self.base: Dict[int, int] = {}             # position of its first row

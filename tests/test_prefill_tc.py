@@ -79,3 +79,36 @@ def test_prefill_runner_matches_oracle(backend):
         if t != want:
             assert float(logits[want] - logits[t]) < margin, (i, t, want)
         logits = oracle.forward(torch.tensor([t]), kv, len(prompt) + i)[0]
+
+
+@pytest.mark.gpu
+def test_int8_kv_prompt_pass_layer_major_matches_row_kernels():
+    """An int8 KV cache is filled by the layer-major GEMM pass (bf16 scratch per layer, quantised afterwards); the
+    row kernels writing int8 directly are the reference.  A second turn exercises the dequantise-first path."""
+    from b200serve.models.config import preset
+    from b200serve.models.weights import random_weights
+    from b200serve.ops import lib as K
+    from b200serve.runtime.engine import Engine
+    cfg = preset("small-dense")
+    w = random_weights(cfg, device="cuda", seed=6)
+    g = torch.Generator().manual_seed(2)
+    ids = torch.randint(0, cfg.vocab, (300,), generator=g).tolist()
+    more = torch.randint(0, cfg.vocab, (150,), generator=g).tolist()
+    ref = Engine(w, max_seqs=1, max_len=1024, kv_dtype="int8", use_graphs=False, prefill_backend="rows")
+    ref.prefill(0, ids)
+    l_ref1 = ref.model.buf.logits[ref.last_prefill_row].clone()
+    ref.prefill(0, more)
+    l_ref2 = ref.model.buf.logits[ref.last_prefill_row].clone()
+    eng = Engine(w, max_seqs=1, max_len=1024, kv_dtype="int8", use_graphs=False)
+    eng.prefill(0, ids, chunk=128)
+    assert eng._prefill is not None
+    l1 = eng.model.buf.logits[0].clone()
+    eng.prefill(0, more, chunk=128)
+    l2 = eng.model.buf.logits[0].clone()
+    K.check_status()
+    for a, b in ((l1, l_ref1), (l2, l_ref2)):
+        assert float((a - b).abs().max()) < 0.04 * float(b.abs().max())
+    # decode continues on the int8 pages the pass wrote
+    t_ref = ref.forward_rows([__import__("b200serve.runtime.engine", fromlist=["Row"]).Row(0, ref.seq_len[0], 7)])
+    t = eng.forward_rows([__import__("b200serve.runtime.engine", fromlist=["Row"]).Row(0, eng.seq_len[0], 7)])
+    assert float((eng.model.buf.logits[0] - ref.model.buf.logits[0]).abs().max()) < 0.04 * float(l_ref2.abs().max())
