@@ -156,12 +156,13 @@ class DecoderModel:
         """Split-KV attention of the step's rows into ``buf.attn_out``.  bf16 KV with head size 128 goes to the
         tensor-core kernel that serves a request's consecutive rows together; the rest to the per-row kernel."""
         cfg, b = self.cfg, self.buf
-        if m >= self.attn_rows_min and cfg.head_dim == 128 and not kv.kv_int8 and self.nsplit_attn <= 64 and cfg.gqa <= 16:
+        if m >= self.attn_rows_min and cfg.head_dim == 128 and self.nsplit_attn <= 64 and cfg.gqa <= 16:
             inkernel = m <= self.attn_merge_inkernel_rows    # few rows: the last split CTA merges; many: a merge launch
             K.attn_rows(b.q, kc, vc, block_table, ctrl, b.o_part, b.ml_part, b.attn_out, b.tickets if inkernel else None,
                         m, cfg.n_q_heads,
                         cfg.n_kv_heads, cfg.head_dim, self.nsplit_attn, max_blocks, self.scale,
-                        span_pages=(max_blocks + self.nsplit_attn - 1) // self.nsplit_attn if self.attn_fixed_spans else 0)
+                        span_pages=(max_blocks + self.nsplit_attn - 1) // self.nsplit_attn if self.attn_fixed_spans else 0,
+                        k_scale=ks, v_scale=vs, kv_int8=kv.kv_int8)
         else:
             K.attn_decode(b.q, kc, vc, block_table, ctrl, b.o_part, b.ml_part, b.attn_out, m, cfg.n_q_heads,
                           cfg.n_kv_heads, cfg.head_dim, self.nsplit_attn, max_blocks, self.scale, ks, vs, kv.kv_int8,

@@ -12,6 +12,8 @@
 //   * every row masks the keys beyond its own position (causal inside the group);
 //   * split-KV partials and the in-kernel merge by the last CTA ("ticket") have the layout and the fixed
 //     split order of the per-row kernel, so either kernel can serve a row.
+// An int8 cache (one fp32 scale per row) is staged as int8 and expanded to bf16 in shared memory by the thread
+// that owns the key, then takes the same path.
 // The role of the reference's verify attention (src/kernels/attn_verify_dpas.cl) and of its decode
 // attention's GQA packing (src/kernels/attn_v2.cl).
 #include "common.cuh"
@@ -29,8 +31,10 @@ constexpr int kThreads = 128;    // 4 warps = up to 64 query rows
 
 struct AttnRowsParams {
   const __nv_bfloat16* q;  // [M][n_q * D]
-  const __nv_bfloat16* k_cache;
-  const __nv_bfloat16* v_cache;
+  const void* k_cache;     // bf16 or int8 [page][n_kv][16][D]
+  const void* v_cache;
+  const float* k_scale;    // int8 form: [page][n_kv][16]
+  const float* v_scale;
   const int* block_table;
   const int* ctrl;
   float* o_part;   // [M][n_q][nsplit][D]
@@ -52,10 +56,12 @@ __device__ __forceinline__ void ldsm_x4_trans(uint32_t addr, uint32_t& r0, uint3
                : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
 }
 
+template <bool I8>
 __global__ void __launch_bounds__(kThreads) attn_rows_kernel(const AttnRowsParams p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 127u) & ~127u;
   const uint32_t ks = base, vs = base + KB * ROWB, bar = vs + KB * ROWB;
+  const uint32_t k8s = bar + 64, v8s = k8s + KB * D;   // int8 form: staged rows before conversion (128 B each)
   float* scratch = reinterpret_cast<float*>(smem_raw + (base - smem_u32(smem_raw)));  // merge reuses the K / V tiles
   __shared__ int s_last;
   pdl_wait();
@@ -118,14 +124,22 @@ __global__ void __launch_bounds__(kThreads) attn_rows_kernel(const AttnRowsParam
   for (int kb0 = key0; kb0 < key1; kb0 += KB, ++batch) {
     const int nk = min(KB, key1 - kb0);
     __syncthreads();  // the previous batch is consumed
-    if (tid == 0) mbar_expect_tx(bar, (uint32_t)nk * 512u);
+    if (tid == 0) mbar_expect_tx(bar, (uint32_t)nk * (I8 ? 256u : 512u));
     __syncthreads();
+    float ksc = 0.f, vsc = 0.f;
     if (tid < nk) {
       const int key = kb0 + tid;
       const int page = bt[key >> 4], slot = key & 15;
-      const size_t off = (((size_t)page * p.n_kv + kh) * 16 + slot) * D;
-      bulk_g2s(ks + tid * ROWB, p.k_cache + off, 256, bar);
-      bulk_g2s(vs + tid * ROWB, p.v_cache + off, 256, bar);
+      const size_t row = ((size_t)page * p.n_kv + kh) * 16 + slot;
+      if (I8) {
+        bulk_g2s(k8s + tid * D, reinterpret_cast<const int8_t*>(p.k_cache) + row * D, D, bar);
+        bulk_g2s(v8s + tid * D, reinterpret_cast<const int8_t*>(p.v_cache) + row * D, D, bar);
+        ksc = p.k_scale[row];
+        vsc = p.v_scale[row];
+      } else {
+        bulk_g2s(ks + tid * ROWB, reinterpret_cast<const __nv_bfloat16*>(p.k_cache) + row * D, 256, bar);
+        bulk_g2s(vs + tid * ROWB, reinterpret_cast<const __nv_bfloat16*>(p.v_cache) + row * D, 256, bar);
+      }
     } else {
       // rows without a key: V must be finite (its products are multiplied by P = 0)
 #pragma unroll
@@ -133,6 +147,30 @@ __global__ void __launch_bounds__(kThreads) attn_rows_kernel(const AttnRowsParam
         asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};" ::"r"(vs + tid * ROWB + 16 * i), "r"(0) : "memory");
     }
     if (okw) okw = mbar_wait(bar, batch & 1, ERR_ATTN_WAIT);
+    if (I8) {
+      // every thread expands its own key's row: int8 x per-row scale -> bf16 into the operand tiles
+      if (okw && tid < nk) {
+#pragma unroll
+        for (int which = 0; which < 2; ++which) {
+          const uint32_t src = (which ? v8s : k8s) + tid * D, dst = (which ? vs : ks) + tid * ROWB;
+          const float sc = which ? vsc : ksc;
+#pragma unroll
+          for (int i = 0; i < D / 16; ++i) {
+            uint32_t w0, w1, w2, w3;
+            asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(w0), "=r"(w1), "=r"(w2), "=r"(w3) : "r"(src + 16 * i));
+            const uint32_t ww[4] = {w0, w1, w2, w3};
+            uint32_t o[8];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              o[2 * j] = pack_bf16((float)(int8_t)(ww[j] & 0xff) * sc, (float)(int8_t)((ww[j] >> 8) & 0xff) * sc);
+              o[2 * j + 1] = pack_bf16((float)(int8_t)((ww[j] >> 16) & 0xff) * sc, (float)(int8_t)(ww[j] >> 24) * sc);
+            }
+            asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst + 32 * i), "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3]) : "memory");
+            asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst + 32 * i + 16), "r"(o[4]), "r"(o[5]), "r"(o[6]), "r"(o[7]) : "memory");
+          }
+        }
+      }
+    }
     __syncthreads();
     if (!okw || !active) continue;
 
@@ -285,27 +323,33 @@ __global__ void __launch_bounds__(kThreads) attn_rows_kernel(const AttnRowsParam
 // Rows of a request that follow one another in the control block are served together.  bf16 KV, head size 128,
 // nsplit <= 64, GQA <= 16.  tickets [M][n_kv] (zeroed once; the kernel leaves them zero): the last split CTA of a
 // group merges in the kernel; nullptr: the partials are left for b2_attn_merge.
-extern "C" int b2_attn_rows(const void* q, const void* k_cache, const void* v_cache, const int* block_table,
+extern "C" int b2_attn_rows(const void* q, const void* k_cache, const void* v_cache, const float* k_scale,
+                            const float* v_scale, int kv_int8, const int* block_table,
                             const int* ctrl, float* o_part, float* ml_part, void* out, int* tickets, int M, int n_q,
                             int n_kv, int D_, int nsplit, int max_blocks, float scale, int span_pages, void* stream) {
   if (D_ != D || nsplit < 1 || nsplit > 64 || n_q % n_kv != 0 || n_q / n_kv > 16 || M > 64) return -1;
   AttnRowsParams p;
-  p.q = (const __nv_bfloat16*)q; p.k_cache = (const __nv_bfloat16*)k_cache; p.v_cache = (const __nv_bfloat16*)v_cache;
+  p.q = (const __nv_bfloat16*)q; p.k_cache = k_cache; p.v_cache = v_cache; p.k_scale = k_scale; p.v_scale = v_scale;
+  if (kv_int8 && (!k_scale || !v_scale)) return -3;
   p.block_table = block_table; p.ctrl = ctrl; p.o_part = o_part; p.ml_part = ml_part; p.out = (__nv_bfloat16*)out;
   p.tickets = tickets; p.M = M; p.n_q = n_q; p.n_kv = n_kv; p.gqa = n_q / n_kv; p.nsplit = nsplit; p.max_blocks = max_blocks;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.span_pages = span_pages;
   if (span_pages > 0 && (long)span_pages * nsplit < max_blocks) return -2;  // fixed spans must cover the longest sequence
-  const int smem = 128 + 2 * KB * ROWB + 64;
+  const int smem = 128 + 2 * KB * ROWB + 64 + (kv_int8 ? 2 * KB * D : 0);
   static int configured[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   if (!configured[dev & 63]) {
-    cudaError_t e = cudaFuncSetAttribute(attn_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    const int most = 128 + 2 * KB * ROWB + 64 + 2 * KB * D;
+    cudaError_t e = cudaFuncSetAttribute(attn_rows_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, most);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_rows_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, most);
     if (e != cudaSuccess) return (int)e;
     configured[dev & 63] = 1;
   }
-  return b2_launch(attn_rows_kernel, dim3(n_kv, nsplit, M), dim3(kThreads), smem, (cudaStream_t)stream, true, p);
+  if (kv_int8)
+    return b2_launch(attn_rows_kernel<true>, dim3(n_kv, nsplit, M), dim3(kThreads), smem, (cudaStream_t)stream, true, p);
+  return b2_launch(attn_rows_kernel<false>, dim3(n_kv, nsplit, M), dim3(kThreads), smem, (cudaStream_t)stream, true, p);
 }
 
 B2_DEFINE_STATUS(attnrows)

@@ -355,3 +355,34 @@ def test_attn_rows_matches_per_row_kernel(n_q, n_kv, rows, ctx, nsplit):
         err = (out.float() - ref.float()).abs().max()
         assert err <= 2e-2 * ref.float().abs().max() + 2e-3, float(err)
         assert int(tickets.abs().sum()) == 0
+
+
+@pytest.mark.gpu
+def test_attn_rows_int8_kv_matches_per_row_kernel():
+    k_ = K()
+    torch.manual_seed(77)
+    n_q, n_kv, d, ctx, nsplit = 16, 4, 128, 900, 8
+    max_blocks = (ctx + 15) // 16 + 2
+    num_pages = max_blocks + 2
+    table = (torch.randperm(num_pages - 1)[:max_blocks] + 1).to(torch.int32).view(1, -1).cuda()
+    kf = torch.randn(num_pages, n_kv, 16, d, device="cuda") * 0.5
+    vf = torch.randn(num_pages, n_kv, 16, d, device="cuda") * 0.5
+    ks = (kf.abs().amax(dim=-1) / 127).contiguous()
+    vs = (vf.abs().amax(dim=-1) / 127).contiguous()
+    k8 = torch.round(kf / ks[..., None]).clamp(-127, 127).to(torch.int8).contiguous()
+    v8 = torch.round(vf / vs[..., None]).clamp(-127, 127).to(torch.int8).contiguous()
+    spec = [(0, ctx - 5 + i, 0) for i in range(5)]
+    m = len(spec)
+    q = torch.randn(m, n_q * d, device="cuda").to(torch.bfloat16)
+    ctrl = _ctrl(spec)
+    o_part = torch.zeros(m * n_q * nsplit * d, device="cuda")
+    ml = torch.zeros(m * n_q * nsplit * 2, device="cuda")
+    ref = torch.zeros(m, n_q * d, dtype=torch.bfloat16, device="cuda")
+    k_.attn_decode(q, k8, v8, table, ctrl, o_part, ml, ref, m, n_q, n_kv, d, nsplit, max_blocks, d ** -0.5, ks, vs, True)
+    out = torch.full_like(ref, float("nan"))
+    k_.attn_rows(q, k8, v8, table, ctrl, o_part, ml, out, None, m, n_q, n_kv, d, nsplit, max_blocks, d ** -0.5,
+                 k_scale=ks, v_scale=vs, kv_int8=True)
+    torch.cuda.synchronize()
+    k_.check_status()
+    err = (out.float() - ref.float()).abs().max()
+    assert err <= 2e-2 * ref.float().abs().max() + 2e-3, float(err)
