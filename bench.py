@@ -105,6 +105,7 @@ def main():
     ap.add_argument("--int8-head", action="store_true")
     ap.add_argument("--prefill-backend", default="auto")
     ap.add_argument("--parallel", default="replica", help="replica | tp (N > 1)")
+    ap.add_argument("--extras-budget-s", type=float, default=300.0, help="no further extra starts after this many seconds")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
@@ -129,23 +130,51 @@ def main():
 
     sampler = ClockSampler(local)
     sampler.start()
+    t_start = time.time()
     res = {}
     extra = {}
     if args.what in ("all", "decode"):
         res = run_decode_bench(args, barrier)
+    import gc
+    gc.collect()
+    torch.cuda.empty_cache()
     if args.what in ("all", "prefill"):
         extra["prefill"] = run_prefill_bench(args, barrier, model=args.model, backend=args.prefill_backend)
+        gc.collect()
+        torch.cuda.empty_cache()
         if args.what == "all":
             a2 = argparse.Namespace(**vars(args))
             extra["prefill_int8"] = run_prefill_bench(a2, barrier, model=args.model, backend="int8")
+            gc.collect()
+            torch.cuda.empty_cache()
     if args.what in ("all", "moe"):
         extra["moe_prefill"] = run_prefill_bench(args, barrier, model="moe-35b-a3b", backend=args.prefill_backend)
+        gc.collect()
+        torch.cuda.empty_cache()
+    def release():
+        """Engines and their resident weight copies hold reference cycles: collect them before the next section."""
+        import gc
+        gc.collect()
+        torch.cuda.empty_cache()
+
     def guarded(name, fn):
-        """A failing multi-GPU extra is recorded, never fatal: the headline line is printed regardless."""
+        """A failing extra is recorded, never fatal: the headline line is printed regardless.  Extras that
+        would start after the time budget is spent are skipped (the same decision on every rank: the clock
+        reading of rank 0 is shared)."""
+        spent = time.time() - t_start
+        if dist is not None:
+            t = torch.tensor([spent], device="cuda", dtype=torch.float64)
+            dist.broadcast(t, src=0)
+            spent = float(t)
+        if spent > args.extras_budget_s:
+            extra[name] = {"skipped": f"time budget of {args.extras_budget_s:.0f} s for extras was spent"}
+            return
+        release()
         try:
             extra[name] = fn()
         except Exception as e:  # noqa: BLE001
             extra[name] = {"error": f"{type(e).__name__}: {e}"[:400]}
+        release()
 
     def tp_extra():
         # the same model as ONE tensor-parallel group over all the GPUs: fused NVLink kernels against the
