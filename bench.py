@@ -205,6 +205,9 @@ def main():
     if args.what in ("all", "spec"):
         from b200serve.utils.benchlib import run_spec_bench
         guarded("spec_forced_accept", lambda: run_spec_bench(args, barrier))
+    if args.what in ("all", "prefix"):
+        from b200serve.utils.benchlib import run_prefix_bench
+        guarded("prefix_cache", lambda: run_prefix_bench(args, barrier))
     if world > 1 and args.what in ("all", "tp"):
         guarded("tp", tp_extra)
     if world > 1 and args.what in ("all", "ep"):

@@ -145,3 +145,50 @@ def run_spec_bench(args, barrier, iters: int = 12) -> dict:
         del eng, ad
         torch.cuda.empty_cache()
     return out
+
+
+def run_prefix_bench(args, barrier, prefix_tokens: int = 65536, suffix_tokens: int = 512) -> dict:
+    """A request whose first ``prefix_tokens`` positions are already cached: time to the first token cold, with the
+    prefix in the device tier (pages adopted by reference), and with it restored from the pinned host tier."""
+    import time
+    from ..server.prefix import PrefixStore
+    cfg = preset(args.model)
+    dev = torch.device("cuda", torch.cuda.current_device())
+    weights = random_weights(cfg, device=dev, seed=0, exact=False)
+    n = prefix_tokens + suffix_tokens
+    eng = Engine(weights, max_seqs=2, max_len=n + 64, use_graphs=False, prefill_backend=args.prefill_backend)
+    host_gb = eng.kv.k[:, 0].numel() * 2 * 2 * (prefix_tokens // 16) / 2**30 * 1.05
+    store = PrefixStore(eng, host_gb=host_gb, block_tokens=2048, device_fraction=0.6)
+    g = torch.Generator().manual_seed(3)
+    prefix = torch.randint(0, cfg.vocab, (prefix_tokens,), generator=g).tolist()
+    out = {"prefix_tokens": prefix_tokens, "suffix_tokens": suffix_tokens, "block_tokens": 2048}
+
+    def request(slot, seed):
+        gs = torch.Generator().manual_seed(seed)
+        ids = prefix + torch.randint(0, cfg.vocab, (suffix_tokens,), generator=gs).tolist()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        cached = store.begin(slot, ids)
+        eng.prefill(slot, ids[cached:])
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+        store.after_prefill(slot, ids)
+        store.end(slot, ids)
+        return cached, dt * 1e3
+
+    cached, ms = request(0, 10)
+    out["cold"] = {"cached_tokens": cached, "ttft_ms": ms, "tokens_per_s": n / (ms / 1e3)}
+    cached, ms = request(1, 11)           # another slot: the blocks come from the device tier
+    out["device_tier_hit"] = {"cached_tokens": cached, "ttft_ms": ms}
+    # push every block to the host tier, then a third request restores them over PCIe / C2C
+    store.resident.clear()
+    eng.reset(0)
+    eng.reset(1)
+    while store._spill_one():
+        pass
+    cached, ms = request(0, 12)
+    out["host_tier_restore"] = {"cached_tokens": cached, "ttft_ms": ms, "restored_blocks": store.stats["restored_blocks"],
+                                "host_store_gib": host_gb}
+    K.check_status()
+    del eng, store, weights
+    return out
