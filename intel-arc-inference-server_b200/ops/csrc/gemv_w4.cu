@@ -260,9 +260,13 @@ __global__ void __launch_bounds__(kThreads, (T <= 2 ? 2 : 1)) gemv_w4_kernel(con
   const uint32_t bars = smem0 + kRingBytes;               // 16 mbarriers
   const uint32_t rinv0 = bars + 128;                      // float [64] per-row 1/rms (x_mode 2)
   const uint32_t gs0 = rinv0 + 256;                       // {float scale, int -8 sum X} [xcg][8 T]
-  const uint32_t xs0 = gs0 + ((p.xcg * 8 * T * 8 + 127) & ~127);  // int8 limbs of the rows, in operand order
+  const uint32_t xs0 = gs0 + ((p.xcg * 8 * T * 8 + 127) & ~127) * (p.x_mode == 3 ? 2 : 1);  // int8 limbs of the rows, in operand order
   const uint32_t full0 = bars, empty0 = bars + 8 * kStages;
   const int strideB = stride_words(p.xcg) * 4;
+  // x_mode 3: two activation buffers filled by the producer (barriers live in the unused 1/rms slots)
+  const uint32_t xfull0 = rinv0, xempty0 = rinv0 + 16;
+  const uint32_t gsB = (p.xcg * 8 * T * 8 + 127) & ~127;   // bytes of one buffer's group scales
+  const uint32_t xsB = (uint32_t)p.rows * strideB;          // bytes of one buffer's rows
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int nblk = blockIdx.x, split = blockIdx.y;
@@ -275,6 +279,12 @@ __global__ void __launch_bounds__(kThreads, (T <= 2 ? 2 : 1)) gemv_w4_kernel(con
     for (int i = 0; i < kStages; ++i) {
       mbar_init(full0 + 8 * i, 1);
       mbar_init(empty0 + 8 * i, 8);
+    }
+    if (p.x_mode == 3) {
+      for (int i = 0; i < 2; ++i) {
+        mbar_init(xfull0 + 8 * i, 1);
+        mbar_init(xempty0 + 8 * i, 8);
+      }
     }
     mbar_fence_init();
   }
@@ -290,15 +300,52 @@ __global__ void __launch_bounds__(kThreads, (T <= 2 ? 2 : 1)) gemv_w4_kernel(con
       const uint8_t* src = wbase + ((size_t)nblk * p.KG + gbeg) * kBlockBytes;
       bool ok = true;
       int issued = 0;
-      for (int i = 0; i < nstage && ok; ++i) {
+      auto issue_w = [&](int i) {
         const int s = i % kStages;
-        if (i >= kStages) ok = mbar_wait(empty0 + 8 * s, ((i / kStages) - 1) & 1, ERR_GEMV_EMPTY_WAIT);
-        if (!ok) break;
         const int ng = min(kG, ngroups - i * kG);
         const uint32_t bytes = ng * kBlockBytes;
         mbar_expect_tx(full0 + 8 * s, bytes);
         bulk_g2s(ring + s * kStageBytes, src + (size_t)i * kStageBytes, bytes, full0 + 8 * s);
         issued = i + 1;
+      };
+      if (p.x_mode == 3) {
+        // Pre-quantised activations come in by bulk copy too, chunk by chunk into two buffers, so the consumer
+        // warps never stage anything.  The first ring stages go out before griddepcontrol.wait (weights depend
+        // on nothing); the activations are the previous kernel's output.
+        const int first = min(nstage, kStages);
+        for (int i = 0; i < first; ++i) issue_w(i);
+        pdl_wait();
+        const uint8_t* xq = reinterpret_cast<const uint8_t*>(p.x);
+        int next_chunk = 0;
+        for (int i = 0; i < nstage && ok; ++i) {
+          while (ok && next_chunk * p.xcg <= i * kG && next_chunk * p.xcg < ngroups) {   // the chunk this stage reads
+            const int c = next_chunk, b = c & 1;
+            if (c >= 2) ok = mbar_wait(xempty0 + 8 * b, ((c >> 1) - 1) & 1, ERR_GEMV_EMPTY_WAIT);
+            if (!ok) break;
+            const int c0 = c * p.xcg, cg = min(p.xcg, ngroups - c0);
+            const uint32_t gbytes = (uint32_t)cg * 8 * T * 8, rbytes = (uint32_t)cg * 128;
+            mbar_expect_tx(xfull0 + 8 * b, gbytes + rbytes * p.M);
+            bulk_g2s(gs0 + b * gsB, reinterpret_cast<const uint8_t*>(p.xq_gs) + (size_t)(gbeg + c0) * 8 * T * 8, gbytes,
+                     xfull0 + 8 * b);
+            for (int r = 0; r < p.M; ++r)
+              bulk_g2s(xs0 + b * xsB + r * strideB, xq + ((size_t)r * p.KG + gbeg + c0) * 128, rbytes, xfull0 + 8 * b);
+            ++next_chunk;
+          }
+          if (!ok) break;
+          if (i >= kStages) {
+            ok = mbar_wait(empty0 + 8 * (i % kStages), ((i / kStages) - 1) & 1, ERR_GEMV_EMPTY_WAIT);
+            if (!ok) break;
+            issue_w(i);
+          }
+        }
+        if (!ok)   // wait (bounded) for the activation copies that may still be in flight
+          for (int c = max(0, next_chunk - 2); c < next_chunk; ++c) mbar_wait(xfull0 + 8 * (c & 1), (c >> 1) & 1, ERR_GEMV_FULL_WAIT);
+      } else {
+        for (int i = 0; i < nstage && ok; ++i) {
+          if (i >= kStages) ok = mbar_wait(empty0 + 8 * (i % kStages), ((i / kStages) - 1) & 1, ERR_GEMV_EMPTY_WAIT);
+          if (!ok) break;
+          issue_w(i);
+        }
       }
       if (!ok) {
         // drain: wait (bounded) for the copies that were issued and possibly never consumed
@@ -339,37 +386,21 @@ __global__ void __launch_bounds__(kThreads, (T <= 2 ? 2 : 1)) gemv_w4_kernel(con
     }
   }
   const int xvec = p.xcg * 8;  // 16-byte vectors per staged row
-  for (int c0 = 0; c0 < ngroups; c0 += p.xcg) {
+  const bool fed = p.x_mode == 3;   // the producer fills the activation buffers: no staging, no CTA barriers
+  for (int c0 = 0, chunk = 0; c0 < ngroups; c0 += p.xcg, ++chunk) {
     const int cg = min(p.xcg, ngroups - c0);  // groups in this chunk
-    consumer_sync();
+    const int xb = fed ? (chunk & 1) : 0;
+    if (fed) {
+      if (ok) ok = mbar_wait(xfull0 + 8 * xb, (chunk >> 1) & 1, ERR_GEMV_FULL_WAIT);
+    } else {
+      consumer_sync();
+    }
     // ---- stage x[:, k0 : k0 + 64 cg] as bf16, permuted inside each group
-    {
+    if (!fed) {
       const int k0 = (gbeg + c0) * 64;
       const int nvec = cg * 8;
       const int total = p.rows * xvec;  // a multiple of 8; lanes of a warp stay together in groups of 8
-      if (p.x_mode == 3) {
-        // the rows were quantised once by quant_x_kernel: plain copies, nothing to compute per CTA
-        const uint8_t* xq = xbase;
-        for (int v0 = 0; v0 < total; v0 += kConsumerThreads) {
-          const int v = v0 + tid;
-          const int row = v / xvec, col = v - row * xvec;
-          if (v < total && col < nvec) {
-            uint4 q = make_uint4(0, 0, 0, 0);
-            if (row < p.M) q = *reinterpret_cast<const uint4*>(xq + ((size_t)row * p.KG + gbeg + c0) * 128 + (size_t)col * 16);
-            asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(xs0 + row * strideB + col * 16), "r"(q.x), "r"(q.y),
-                         "r"(q.z), "r"(q.w) : "memory");
-          }
-        }
-        for (int i0 = 0; i0 < p.rows * cg; i0 += kConsumerThreads) {
-          const int i = i0 + tid;
-          if (i < p.rows * cg) {
-            const int row = i / cg, gq = i - row * cg;
-            uint2 sv = make_uint2(0, 0);
-            if (row < p.M) sv = *reinterpret_cast<const uint2*>(p.xq_gs + ((size_t)row * p.KG + gbeg + c0 + gq) * 2);
-            asm volatile("st.shared.v2.u32 [%0], {%1, %2};" ::"r"(gs0 + (gq * 8 * T + row) * 8), "r"(sv.x), "r"(sv.y) : "memory");
-          }
-        }
-      } else {
+      {
       for (int v0 = 0; v0 < total; v0 += kConsumerThreads) {
         const int v = v0 + tid;
         const int row = v / xvec, col = v - row * xvec;
@@ -395,7 +426,7 @@ __global__ void __launch_bounds__(kThreads, (T <= 2 ? 2 : 1)) gemv_w4_kernel(con
       }
       }
     }
-    consumer_sync();
+    if (!fed) consumer_sync();
 
     // ---- consume the ring stages that cover this chunk.  After a failed wait the warp skips the rest
     // of its work but still meets the others at the named barrier, so a lost copy costs one bounded
@@ -408,16 +439,21 @@ __global__ void __launch_bounds__(kThreads, (T <= 2 ? 2 : 1)) gemv_w4_kernel(con
       const uint32_t st = ring + s * kStageBytes;
       uint32_t xa[T];
 #pragma unroll
-      for (int tt = 0; tt < T; ++tt) xa[tt] = x_row[tt] + gi * 128;
-      if (gi + 1 < cg) group_mma<T, (T <= 2 ? 2 : 1)>(acc, st, w_off, sc_off, xa, gs_t + gi * 8 * T * 8);
-      else group_mma<T, 1>(acc, st, w_off, sc_off, xa, gs_t + gi * 8 * T * 8);
+      for (int tt = 0; tt < T; ++tt) xa[tt] = x_row[tt] + xb * xsB + gi * 128;
+      const uint32_t gsa = gs_t + xb * gsB;
+      if (gi + 1 < cg) group_mma<T, (T <= 2 ? 2 : 1)>(acc, st, w_off, sc_off, xa, gsa + gi * 8 * T * 8);
+      else group_mma<T, 1>(acc, st, w_off, sc_off, xa, gsa + gi * 8 * T * 8);
       if (T > 2 && gi + 1 < cg) {
 #pragma unroll
         for (int tt = 0; tt < T; ++tt) xa[tt] += 128;
-        group_mma<T, 1>(acc, st + kBlockBytes, w_off, sc_off, xa, gs_t + (gi + 1) * 8 * T * 8);
+        group_mma<T, 1>(acc, st + kBlockBytes, w_off, sc_off, xa, gsa + (gi + 1) * 8 * T * 8);
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(empty0 + 8 * s);
+    }
+    if (fed) {
+      __syncwarp();
+      if (lane == 0) mbar_arrive(xempty0 + 8 * xb);   // this warp is done with the buffer
     }
   }
 
@@ -558,9 +594,9 @@ __global__ void __launch_bounds__(256) quant_x_kernel(const GemvParams p, uint8_
     dst[4] = sv.w[1];
     dst[8] = sv.w[2];
     dst[12] = sv.w[3];
-    if (vq == 0) {
-      xq_gs[((size_t)row * p.KG + group) * 2] = __float_as_uint(sv.scale);
-      xq_gs[((size_t)row * p.KG + group) * 2 + 1] = (uint32_t)sv.m8sum;
+    if (vq == 0) {   // [group][8 T token slots]: a chunk of groups is one contiguous block for the GEMV's bulk copy
+      xq_gs[((size_t)group * p.rows + row) * 2] = __float_as_uint(sv.scale);
+      xq_gs[((size_t)group * p.rows + row) * 2 + 1] = (uint32_t)sv.m8sum;
     }
   }
 }
@@ -574,10 +610,12 @@ int launch_t(GemvParams& p, cudaStream_t stream) {
   int xcg = (kXBudget / (rows * 2) - 8) / 64;
   xcg &= ~1;
   if (xcg > 160) xcg = 160;   // keeps two CTAs per SM at one staged row
+  if (p.x_mode == 3) xcg = (xcg / 2) & ~1;   // two buffers
   if (xcg > p.gps) xcg = p.gps;
   if (xcg < 2) xcg = 2;
   p.xcg = xcg;
-  const int smem = 128 + kRingBytes + 128 + 256 + ((xcg * 8 * T * 8 + 127) & ~127) + rows * stride_words(xcg) * 4;
+  const int nbuf = p.x_mode == 3 ? 2 : 1;
+  const int smem = 128 + kRingBytes + 128 + 256 + nbuf * (((xcg * 8 * T * 8 + 127) & ~127) + rows * stride_words(xcg) * 4);
   static int configured[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -690,7 +728,7 @@ extern "C" int b2_gemv_w4_experts(const void* w4b_stack, long long expert_bytes,
 }
 
 // Quantise activation rows for x_mode 3.  Input modes as the GEMV's (0 bf16 rows, 1 SiLU*up of fp32 slices,
-// 2 residual rows with RMSNorm); xq is [M][K / 64][128] bytes, xq_gs [M][K / 64][2] words.
+// 2 residual rows with RMSNorm); xq is [M][K / 64][128] bytes, xq_gs [K / 64][8, 16, 32 or 64 token slots][2] words.
 extern "C" int b2_quant_x(const void* x, int M, int K, int ldx, int x_mode, int s_in, long long x_slice,
                           const float* norm_w, const float* norm_ssq, float norm_eps, void* xq, void* xq_gs, void* stream) {
   if (M < 1 || K % 64 != 0 || x_mode < 0 || x_mode > 2) return -1;
@@ -698,6 +736,7 @@ extern "C" int b2_quant_x(const void* x, int M, int K, int ldx, int x_mode, int 
   GemvParams p = {};
   p.x = x; p.M = M; p.KG = K / 64; p.ldx = ldx; p.x_mode = x_mode; p.s_in = s_in; p.x_slice = x_slice;
   p.norm_w = norm_w; p.norm_ssq = norm_ssq; p.norm_nb = K / 128; p.norm_eps = norm_eps;
+  p.rows = M <= 8 ? 8 : (M <= 16 ? 16 : (M <= 32 ? 32 : 64));   // token slots per group in xq_gs (8 x the GEMV's tile count)
   dim3 grid((p.KG * 8 + 255) / 256, M);
   return b2_launch(quant_x_kernel, grid, dim3(256), 0, (cudaStream_t)stream, true, p, (uint8_t*)xq, (uint32_t*)xq_gs);
 }
