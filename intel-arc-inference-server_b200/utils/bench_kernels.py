@@ -57,8 +57,17 @@ def bench_gemv(ms_list=(1, 4, 8, 16, 64), only=None, iters_mult=4, graph=False):
             out = torch.zeros(s, m, n, device="cuda")
             it = [0]
 
+            fed = os.environ.get("B2_BENCH_PREQUANT", "0") == "1"   # time the GEMV alone on pre-quantised rows
+            if fed:
+                xq = torch.zeros(m * (k // 64) * 128, dtype=torch.uint8, device="cuda")
+                gs = torch.zeros(64 * (k // 64) * 2, dtype=torch.int32, device="cuda")
+                K.quant_x(x, m, k, xq, gs)
+
             def fn():
-                K.gemv_w4(ws[it[0] % copies], x, out, m, n, k, s)
+                if fed:
+                    K.gemv_w4_fused(ws[it[0] % copies], xq, out, m, n, k, s, x_mode=3, norm_ssq=gs)
+                else:
+                    K.gemv_w4(ws[it[0] % copies], x, out, m, n, k, s)
                 it[0] += 1
             ms = time_ms(fn, iters=max(2, iters_mult * copies))
             if graph:
