@@ -240,10 +240,12 @@ __global__ void __launch_bounds__(1024) rs_fold_kernel(const RsFoldParams p) {
       *reinterpret_cast<uint4*>(xd + (size_t)g * p.H + col) = xo;
     }
   }
-  __threadfence_system();
+  // The CTA barrier orders every thread's stores before the releasing threads' fence; the release is at system
+  // scope, so each destination sees the row before the arrival (one fence per destination, not one per thread).
   __syncthreads();
   if (tid < p.world) {
     int* cnt = reinterpret_cast<int*>(p.x_table[kMaxRanks + tid]) + p.rank * p.tpr + mtl;
+    __threadfence_system();
     asm volatile("red.release.sys.global.add.s32 [%0], 1;" ::"l"(cnt) : "memory");
   }
 }

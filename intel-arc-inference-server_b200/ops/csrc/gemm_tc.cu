@@ -338,11 +338,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       if (p.epi == EPI_RS_PUSH) {
         // this warp's part of the tile is on its way: make it visible system-wide, then count one arrival
         // at the owner (4 epilogue warps x tiles_n arrivals complete an m-tile of one source rank)
-        __threadfence_system();
-        __syncwarp();
+        __syncwarp();   // the warp's stores are ordered before lane 0's fence and release
         if (lane == 0) {
           const int owner = mt / p.rs_tpr, mtl = mt - owner * p.rs_tpr;
           int* cnt = reinterpret_cast<int*>(p.rs_table[kMaxRanks + owner]) + p.rs_rank * p.rs_tpr + mtl;
+          __threadfence_system();
           asm volatile("red.release.sys.global.add.s32 [%0], 1;" ::"l"(cnt) : "memory");
         }
       }
