@@ -134,14 +134,14 @@ __global__ void __launch_bounds__(256) allreduce_rows_kernel(const float* x, flo
 }
 
 // ------------------------------------------------------------------ prefill: reduce-scatter fold + norm + all-gather push
-// The owner side of the row-parallel GEMM -> reduce-scatter, fused with what follows it.  One CTA per row
-// this rank owns (grid = rows_cap = 128 tpr, H / 8 threads).  Row r is token g = rank * rows_cap + r of the
+// The owner side of the row-parallel GEMM -> reduce-scatter, fused with what follows it.  One warp per row
+// this rank owns (eight rows per CTA).  Row r is token g = rank * rows_cap + r of the
 // chunk.  The CTA waits (bounded) until every source rank's counter of the row's m-tile shows the whole tile
 // has landed, adds the bf16 partial sums in rank order to the residual row, writes the residual back,
 // applies RMSNorm with the NEXT layer's weight and pushes the normalised row into every rank's copy of the
 // gathered activations, then counts one arrival for the row's m-tile on every rank: the column-parallel GEMM
 // that follows waits on those counters tile by tile (all-gather -> GEMM).  nsrc = 0: no partial sums (first
-// layer: the residual rows hold the embeddings).
+// layer: the residual rows hold the embeddings).  One warp per row, eight rows per CTA.
 struct RsFoldParams {
   const __nv_bfloat16* land;   // this rank's landing buffer [world][rows_cap][H]
   int* rs_cnt;                 // this rank's counters [world][tpr] (of the slot in use)
@@ -155,98 +155,124 @@ struct RsFoldParams {
   int world, rank, H, tpr, c;
 };
 
-__global__ void __launch_bounds__(1024) rs_fold_kernel(const RsFoldParams p) {
-  __shared__ float red[32];
+constexpr int kFoldRows = 8;   // rows (= warps) per CTA; divides the 128-row m-tile
+
+__global__ void __launch_bounds__(32 * kFoldRows) rs_fold_kernel(const RsFoldParams p) {
   __shared__ int s_bad;
   pdl_wait();
   pdl_launch_dependents();
-  const int r = blockIdx.x, tid = threadIdx.x, nthr = blockDim.x;
-  const int rows_cap = p.tpr * 128, mtl = r >> 7;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int r = blockIdx.x * kFoldRows + warp;      // this warp's row; the CTA's rows share one m-tile
+  const int rows_cap = p.tpr * 128, mtl = (blockIdx.x * kFoldRows) >> 7;
   const int g = p.rank * rows_cap + r;  // token index in the chunk
   const bool exists = g < p.c;
   const int tile_row0 = p.rank * rows_cap + mtl * 128;
+  const int cta_row0 = p.rank * rows_cap + blockIdx.x * kFoldRows;
+  const int cta_rows = max(0, min(kFoldRows, p.c - cta_row0));   // rows of this CTA that exist
   if (tid == 0) s_bad = 0;
   __syncthreads();
-  if (exists && p.nsrc > 0) {
+  if (cta_rows > 0 && p.nsrc > 0) {
     if (tid < p.nsrc && !wire_wait(p.rs_cnt + tid * p.tpr + mtl, p.rs_expect, (unsigned)(0x10000000u | tid << 16 | mtl)))
       s_bad = 1;
     __syncthreads();
     if (s_bad) return;
   }
-  const int col = tid * 8;
-  float f[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-  uint4 xo = make_uint4(0, 0, 0, 0);
-  if (exists && col < p.H) {
-    const uint4 rv = *reinterpret_cast<const uint4*>(p.resid + (size_t)r * p.H + col);
-    const uint32_t rw[4] = {rv.x, rv.y, rv.z, rv.w};
+  const int nvec = p.H / 8;
+  float ss = 0.f;
+  if (exists) {
+    // pass 1: residual + the sources' partial sums in rank order (the same bits whichever rank owns the row),
+    // written back as bf16; the sum of squares of what was stored
+    __nv_bfloat16* rrow = p.resid + (size_t)r * p.H;
+    for (int j0 = lane; j0 < nvec; j0 += 32 * 4) {
+      uint4 rv[4], pv[4];
+      float f[4][8];
 #pragma unroll
-    for (int q = 0; q < 4; ++q) {
-      f[2 * q] = bf16_lo(rw[q]);
-      f[2 * q + 1] = bf16_hi(rw[q]);
-    }
-    for (int src = 0; src < p.nsrc; ++src) {  // rank order: the same bits whichever rank owns the row
-      const uint4 pv = ld_sys_u32x4(p.land + ((size_t)src * rows_cap + r) * p.H + col);
-      const uint32_t pw[4] = {pv.x, pv.y, pv.z, pv.w};
+      for (int u = 0; u < 4; ++u) {
+        const int j = j0 + 32 * u;
+        rv[u] = j < nvec ? *reinterpret_cast<const uint4*>(rrow + 8 * j) : make_uint4(0, 0, 0, 0);
+        const uint32_t rw[4] = {rv[u].x, rv[u].y, rv[u].z, rv[u].w};
 #pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        f[2 * q] += bf16_lo(pw[q]);
-        f[2 * q + 1] += bf16_hi(pw[q]);
+        for (int q = 0; q < 4; ++q) {
+          f[u][2 * q] = bf16_lo(rw[q]);
+          f[u][2 * q + 1] = bf16_hi(rw[q]);
+        }
+      }
+      for (int src = 0; src < p.nsrc; ++src) {
+        const __nv_bfloat16* lrow = p.land + ((size_t)src * rows_cap + r) * p.H;
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {   // four loads in flight per lane
+          const int j = j0 + 32 * u;
+          pv[u] = j < nvec ? ld_sys_u32x4(lrow + 8 * j) : make_uint4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const uint32_t pw[4] = {pv[u].x, pv[u].y, pv[u].z, pv[u].w};
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            f[u][2 * q] += bf16_lo(pw[q]);
+            f[u][2 * q + 1] += bf16_hi(pw[q]);
+          }
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int j = j0 + 32 * u;
+        if (j < nvec) {
+          uint4 ro;
+          ro.x = pack_bf16(f[u][0], f[u][1]); ro.y = pack_bf16(f[u][2], f[u][3]);
+          ro.z = pack_bf16(f[u][4], f[u][5]); ro.w = pack_bf16(f[u][6], f[u][7]);
+          *reinterpret_cast<uint4*>(rrow + 8 * j) = ro;
+          const uint32_t ow[4] = {ro.x, ro.y, ro.z, ro.w};
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {  // the norm sees the residual as stored (bf16)
+            const float a = bf16_lo(ow[q]), b2v = bf16_hi(ow[q]);
+            ss += a * a + b2v * b2v;
+          }
+        }
       }
     }
-    uint4 ro;
-    ro.x = pack_bf16(f[0], f[1]); ro.y = pack_bf16(f[2], f[3]); ro.z = pack_bf16(f[4], f[5]); ro.w = pack_bf16(f[6], f[7]);
-    *reinterpret_cast<uint4*>(p.resid + (size_t)r * p.H + col) = ro;
-    const uint32_t ow[4] = {ro.x, ro.y, ro.z, ro.w};
-#pragma unroll
-    for (int q = 0; q < 4; ++q) {  // the norm sees the residual as stored (bf16)
-      f[2 * q] = bf16_lo(ow[q]);
-      f[2 * q + 1] = bf16_hi(ow[q]);
-    }
   }
-  if (exists && p.nsrc > 0) {
-    // this row has read its partial sums: the tile's last row puts the counters back to zero for the
-    // call after next (the slots alternate; nobody can be two calls ahead)
+  ss = warp_sum(ss);
+  if (cta_rows > 0 && p.nsrc > 0) {
+    // the CTA's rows have read their partial sums: the tile's last CTA puts the counters back to zero for the
+    // next call (nobody can be a whole call ahead: the next push needs every rank's fold of this one)
     __syncthreads();
     if (tid == 0) {
       const int waiting = min(128, p.c - tile_row0);
-      if (atomicAdd(p.done + mtl, 1) == waiting - 1) {
+      if (atomicAdd(p.done + mtl, cta_rows) == waiting - cta_rows) {
         p.done[mtl] = 0;
         for (int src = 0; src < p.nsrc; ++src) p.rs_cnt[src * p.tpr + mtl] = 0;
         __threadfence_system();
       }
     }
   }
-  float ss = 0.f;
-#pragma unroll
-  for (int j = 0; j < 8; ++j) ss += f[j] * f[j];
-  ss = warp_sum(ss);
-  if ((tid & 31) == 0) red[tid >> 5] = ss;
-  __syncthreads();
-  if (tid < 32) {
-    float v = tid < (nthr + 31) / 32 ? red[tid] : 0.f;
-    v = warp_sum(v);
-    if (tid == 0) red[0] = rsqrtf(v / (float)p.H + p.eps);
-  }
-  __syncthreads();
-  const float rinv = red[0];
-  if (exists && col < p.H) {
-    const float4 w0 = *reinterpret_cast<const float4*>(p.norm_w + col), w1 = *reinterpret_cast<const float4*>(p.norm_w + col + 4);
-    xo.x = pack_bf16(f[0] * rinv * w0.x, f[1] * rinv * w0.y);
-    xo.y = pack_bf16(f[2] * rinv * w0.z, f[3] * rinv * w0.w);
-    xo.z = pack_bf16(f[4] * rinv * w1.x, f[5] * rinv * w1.y);
-    xo.w = pack_bf16(f[6] * rinv * w1.z, f[7] * rinv * w1.w);
-    for (int d = 0; d < p.world; ++d) {
-      __nv_bfloat16* xd = reinterpret_cast<__nv_bfloat16*>(p.x_table[d]);
-      *reinterpret_cast<uint4*>(xd + (size_t)g * p.H + col) = xo;
+  if (exists) {
+    // pass 2: RMSNorm of the stored row (this warp wrote it: the reads hit L1 / L2) and the push to every rank
+    const float rinv = rsqrtf(ss / (float)p.H + p.eps);
+    const __nv_bfloat16* rrow = p.resid + (size_t)r * p.H;
+    __syncwarp();
+    for (int j = lane; j < nvec; j += 32) {
+      const uint4 rv = *reinterpret_cast<const uint4*>(rrow + 8 * j);
+      const float4 w0 = *reinterpret_cast<const float4*>(p.norm_w + 8 * j), w1 = *reinterpret_cast<const float4*>(p.norm_w + 8 * j + 4);
+      uint4 xo;
+      xo.x = pack_bf16(bf16_lo(rv.x) * rinv * w0.x, bf16_hi(rv.x) * rinv * w0.y);
+      xo.y = pack_bf16(bf16_lo(rv.y) * rinv * w0.z, bf16_hi(rv.y) * rinv * w0.w);
+      xo.z = pack_bf16(bf16_lo(rv.z) * rinv * w1.x, bf16_hi(rv.z) * rinv * w1.y);
+      xo.w = pack_bf16(bf16_lo(rv.w) * rinv * w1.z, bf16_hi(rv.w) * rinv * w1.w);
+      for (int d = 0; d < p.world; ++d) {
+        __nv_bfloat16* xd = reinterpret_cast<__nv_bfloat16*>(p.x_table[d]);
+        *reinterpret_cast<uint4*>(xd + (size_t)g * p.H + 8 * j) = xo;
+      }
     }
   }
-  // The CTA barrier orders every thread's stores before the releasing threads' fence; the release is at system
-  // scope, so each destination sees the row before the arrival (one fence per destination, not one per thread).
+  // The CTA barrier orders every warp's stores before the releasing threads' fence; the release is at system
+  // scope, so each destination sees the rows before the arrivals.  One arrival per row, added per CTA: rows
+  // that do not exist in this chunk count too, so a tile is always complete at 128.
   __syncthreads();
   if (tid < p.world) {
     int* cnt = reinterpret_cast<int*>(p.x_table[kMaxRanks + tid]) + p.rank * p.tpr + mtl;
     __threadfence_system();
-    asm volatile("red.release.sys.global.add.s32 [%0], 1;" ::"l"(cnt) : "memory");
+    asm volatile("red.release.sys.global.add.s32 [%0], %1;" ::"l"(cnt), "r"(kFoldRows) : "memory");
   }
 }
 
@@ -306,13 +332,12 @@ extern "C" int b2_allreduce_rows(const float* x, float* out, int M, int N, const
 extern "C" int b2_rs_fold(const void* land, int* rs_cnt, int* done, int rs_expect, int nsrc, void* resid,
                           const float* norm_w, float eps, const void* x_table, int world, int rank, int H, int tpr, int c,
                           void* stream) {
-  if (H % 8 || H / 8 > 1024 || world < 1 || world > kMaxRanks || nsrc > world || tpr < 1) return -1;
+  if (H % 8 || world < 1 || world > kMaxRanks || nsrc > world || tpr < 1) return -1;
   RsFoldParams p;
   p.land = (const __nv_bfloat16*)land; p.rs_cnt = rs_cnt; p.done = done; p.rs_expect = rs_expect; p.nsrc = nsrc;
   p.resid = (__nv_bfloat16*)resid; p.norm_w = norm_w; p.eps = eps; p.x_table = (const unsigned long long*)x_table;
   p.world = world; p.rank = rank; p.H = H; p.tpr = tpr; p.c = c;
-  const int threads = ((H / 8 + 31) / 32) * 32;
-  return b2_launch(rs_fold_kernel, dim3(tpr * 128), dim3(threads), 0, (cudaStream_t)stream, true, p);
+  return b2_launch(rs_fold_kernel, dim3(tpr * 128 / kFoldRows), dim3(32 * kFoldRows), 0, (cudaStream_t)stream, true, p);
 }
 
 extern "C" int b2_wire_wait(const int* cnt, int expect, void* stream) {
