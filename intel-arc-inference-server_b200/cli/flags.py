@@ -55,7 +55,7 @@ class ServeFlags:
     max_num_seqs: int = flag(4, "sequence slots (concurrent requests)")
     max_len: str = flag("auto", "context length, or auto for what fits")
     parallel: str = flag("auto", "device placement", ["auto", "1", "tp", "tp2", "tp4", "tp8", "ep", "ep2", "ep4",
-                                                      "ep8", "replica", "pp"])
+                                                      "ep8", "replica", "pp", "pp2", "pp4", "pp8"])
     pipeline_split: str = flag("auto", "first layer of the second pipeline stage, or auto")
     host: str = flag("127.0.0.1", "listen address")
     port: int = flag(8000, "listen port")

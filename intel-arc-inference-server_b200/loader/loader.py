@@ -197,3 +197,34 @@ def load(snapshot: str, device="cuda", mtp: bool = True, int8_head: bool = False
                 raise QuantError(f"bytes per token {got} differ from the descriptor's {want:.0f} by more than 2 %")
         report.write(line + "\n")
     return w
+
+
+def load_drafter(snapshot: str, device="cuda", report=sys.stderr) -> MtpWeights:
+    """A draft head from its own snapshot (``--draft-model``): the front (``fc`` over [norm(embed) ‖ norm(hidden)],
+    the two pre-norms), its decoder layers and its output norm, in the GPTQ layout of the main checkpoint.  Tensor
+    names may carry the prefix ``mtp.`` (a head cut out of a main checkpoint), ``drafter.`` or none.  The
+    reference loads its DFlash drafter the same way (src/loader/loader.cc:521 load_mtp, docs/13-loader.md)."""
+    snap = resolve_snapshot(snapshot)
+    with open(os.path.join(snap, "config.json")) as f:
+        hf = json.load(f)
+    if "text_config" in hf:
+        hf = {**hf["text_config"], "quantization_config": hf.get("quantization_config", hf["text_config"].get("quantization_config"))}
+    cfg = ModelConfig.from_hf_config(hf)
+    qc = QuantConfig.parse(hf)
+    st = SafetensorsSet(snap)
+    view = NameView(st, copy=torch.device(device).type == "cpu")
+    prefix = next((p for p in ("mtp.", "drafter.", "") if view.has(p + "fc.qweight") or view.has(p + "fc.weight")), None)
+    if prefix is None:
+        raise KeyError(f"{snap}: no draft head found (fc.qweight under mtp., drafter. or no prefix)")
+    n_layers = 0
+    while view.has(f"{prefix}layers.{n_layers}.input_layernorm.weight"):
+        n_layers += 1
+    fc = _LinearSrc(view, prefix + "fc", qc)
+    head = MtpWeights(view.get(prefix + "pre_fc_norm_embedding.weight").float().to(device),
+                      view.get(prefix + "pre_fc_norm_hidden.weight").float().to(device),
+                      _ql(fc.q, fc.scales, device),
+                      [_load_layer(view, cfg, f"{prefix}layers.{i}", qc, device, (0, 1)) for i in range(n_layers)],
+                      view.get(prefix + "norm.weight").float().to(device))
+    if report is not None:
+        report.write(f"load: draft head with {n_layers} layer(s) from {snap}\n")
+    return head

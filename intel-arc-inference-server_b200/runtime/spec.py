@@ -129,6 +129,9 @@ class SpecAdapter:
                 raise ValueError("--spec mtp needs a checkpoint with an MTP head")
             head, kind = w.mtp, "mtp"
         else:
+            if isinstance(draft_model, str):      # a drafter snapshot (--draft-model)
+                from ..loader.loader import load_drafter
+                draft_model = load_drafter(draft_model, self.e.device)
             head = draft_model if isinstance(draft_model, MtpWeights) else random_drafter(self.e.cfg, self.e.device)
             kind = "dflash"
         self.head = DraftHead(self.e, head, kind)

@@ -1,0 +1,41 @@
+"""Flag system, parallel-placement parsing and the draft-head loader (CPU)."""
+import dataclasses
+
+import pytest
+import torch
+
+from b200serve.cli import flags as F
+from b200serve.models.config import preset
+from b200serve.models.weights import random_weights
+
+
+def test_serve_flags_parse_and_help():
+    f = F.parse(F.ServeFlags, ["dense-27b", "--spec", "mtp", "--kv-cache", "int8", "--prefill-backend", "int8",
+                               "--parallel", "tp4", "--prefix-split-last", "--max-num-seqs", "8", "--max-len", "auto"],
+                "serve", "x")
+    assert (f.model, f.spec, f.kv_cache, f.prefill_backend, f.parallel) == ("dense-27b", "mtp", "int8", "int8", "tp4")
+    assert f.prefix_split_last is True and f.max_num_seqs == 8 and f.max_len == "auto"
+    help_text = F.build_parser(F.ServeFlags, "serve", "x").format_help()
+    for name in ("--spec", "--draft-model", "--kv-cache", "--prefill-backend", "--parallel", "--prefix-split-last"):
+        assert name in help_text
+    with pytest.raises(SystemExit):
+        F.parse(F.ServeFlags, ["m", "--kv-cache", "fp8"], "serve", "x")
+
+
+def test_decode_flags_defaults():
+    f = F.parse(F.DecodeFlags, ["tiny-dense", "--bench", "--depth", "1024"], "decode", "x")
+    assert f.bench and f.depth == 1024 and f.tg == 128 and not f.profile
+
+
+def test_draft_head_roundtrip_through_a_snapshot(tmp_path):
+    from b200serve.loader.loader import load, load_drafter
+    from b200serve.utils.synth import write_checkpoint
+    cfg = dataclasses.replace(preset("tiny-dense"), mtp_layers=1)
+    w = random_weights(cfg, device="cpu", seed=3)
+    write_checkpoint(w, str(tmp_path))
+    head = load_drafter(str(tmp_path), device="cpu", report=None)
+    full = load(str(tmp_path), device="cpu", report=None)
+    assert len(head.layers) == 1
+    assert torch.equal(head.fc.w4b, full.mtp.fc.w4b)
+    assert torch.equal(head.norm, full.mtp.norm)
+    assert torch.equal(head.layers[0].qkv.w4b, full.mtp.layers[0].qkv.w4b)
