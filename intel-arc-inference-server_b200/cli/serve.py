@@ -52,7 +52,7 @@ def main(argv=None):
     adapter = EngineAdapter(engine, eos_ids=eos or (2,))
     if spec in ("mtp", "dflash", "dflash-lookup"):
         from ..runtime.spec import SpecAdapter
-        adapter = SpecAdapter(adapter, spec, f.spec_max, f.draft_model)
+        adapter = SpecAdapter(adapter, spec, f.spec_max, f.draft_model, f.draft_vocab, f.draft_vocab_ids)
     prefix = None
     if f.prefix_cache_gb != "0":
         from ..server.prefix import PrefixStore

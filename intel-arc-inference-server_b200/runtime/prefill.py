@@ -26,8 +26,44 @@ from ..ops import gemm as G
 from ..ops import lib as K
 
 
+class PhaseProfile:
+    """Per-phase device times of the prompt pass (CUDA events around each phase), switched on with the environment
+    variable ``B200SERVE_PREFILL_PROFILE=1`` and printed per prompt on stderr -- the reference's
+    ``B70_PREFILL_PROFILE`` (src/runtime/prefill/profile.h:20-91).  Events are only recorded, never waited on,
+    until the prompt is done."""
+
+    def __init__(self):
+        self.spans = []      # (phase, start event, end event)
+        self._open = None
+
+    def begin(self, phase: str):
+        ev = torch.cuda.Event(enable_timing=True)
+        ev.record()
+        self._open = (phase, ev)
+
+    def end(self):
+        if self._open is None:
+            return
+        ev = torch.cuda.Event(enable_timing=True)
+        ev.record()
+        self.spans.append((self._open[0], self._open[1], ev))
+        self._open = None
+
+    def report(self, out, tokens: int):
+        torch.cuda.synchronize()
+        tot = {}
+        for name, a, b in self.spans:
+            tot[name] = tot.get(name, 0.0) + a.elapsed_time(b)
+        allms = sum(tot.values()) or 1.0
+        parts = ", ".join(f"{k} {v:.2f} ms ({100 * v / allms:.0f} %)" for k, v in sorted(tot.items(), key=lambda kv: -kv[1]))
+        out.write(f"prefill profile: {tokens} tokens, {allms:.2f} ms in phases: {parts}\n")
+        self.spans = []
+
+
 class PrefillRunner:
     def __init__(self, engine, max_chunk: int = 4096):
+        import os
+        self.profile = PhaseProfile() if os.environ.get("B200SERVE_PREFILL_PROFILE", "0") not in ("", "0") else None
         self.eng = engine
         self.cfg = cfg = engine.cfg
         self.dev = engine.device
@@ -99,22 +135,39 @@ class PrefillRunner:
         h = cfg.hidden
         bt_row = eng.block_table[slot]
         kc, vc, ks, vs = eng.kv.layer(kv_index)
+        pr = self.profile
+
+        def phase(name):
+            if pr is not None:
+                pr.end()
+                pr.begin(name)
+        phase("norm")
         K.resid_norm(1, c, h, lw.input_norm, cfg.rms_eps, resid, x, resid_in=resid, splits=0)
         qkv = self.qkv[:c]
+        phase("qkv")
         self.linear(lw.qkv, x, qkv, G.EPI_F32)
+        phase("rope+append")
         K.rope_append(qkv, 0, 1, c, None, eng.block_table, eng.max_blocks, m.cos_t, m.sin_t, cfg.n_q_heads,
                       cfg.n_kv_heads, cfg.head_dim, self.q, kc, vc, ks, vs, eng.kv.kv_int8, req=slot, pos0=pos0)
+        phase("attention")
         K.attn_prefill(self.q, kc, vc, bt_row, self.attn, c, pos0, cfg.n_q_heads, cfg.n_kv_heads, cfg.head_dim,
                        eng.kv.num_pages, eng.max_blocks, m.scale)
+        phase("o")
         self.linear(lw.o, self.attn[:c], resid, G.EPI_RESID_ADD, resid=resid)
+        phase("norm")
         K.resid_norm(1, c, h, lw.post_norm, cfg.rms_eps, resid, x, resid_in=resid, splits=0)
         if lw.gate_up is not None:
             act = self.act[:c, : cfg.ffn]
+            phase("gate_up")
             self.linear(lw.gate_up, x, act, G.EPI_SILU_MUL)
+            phase("down")
             self.linear(lw.down, act, resid, G.EPI_RESID_ADD, resid=resid)
         else:
             from ..models import moe as _moe
+            phase("moe")
             _moe.moe_block_prefill(self, lw, c)
+        if pr is not None:
+            pr.end()
 
     # ------------------------------------------------------------------ one chunk
     def chunk(self, slot: int, ids: List[int], pos0: int):
@@ -209,7 +262,11 @@ class PrefillRunner:
             resid = self.chunk(slot, ids[c0: c0 + chunk], start + c0)
         last = (n - 1) % chunk
         m.buf.resid[0].copy_(resid[last])
-        return self._head_of_row0()
+        tok = self._head_of_row0()
+        if self.profile is not None:
+            import sys
+            self.profile.report(sys.stderr, n)
+        return tok
 
     def _head_of_row0(self) -> int:
         """Final norm, lm_head and arg-max of the residual row in ``buf.resid[0]``."""

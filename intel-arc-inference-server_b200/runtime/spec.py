@@ -46,8 +46,16 @@ def _rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
 
 class DraftHead:
     def __init__(self, engine: Engine, head: MtpWeights, kind: str = "mtp", kv_layer0: Optional[int] = None,
-                 mask_token: Optional[int] = None):
+                 mask_token: Optional[int] = None, draft_vocab=None):
         self.eng, self.head, self.kind = engine, head, kind
+        self.dv = draft_vocab        # loader.draft_vocab.DraftVocab or None: score a subset of the lm_head
+        if draft_vocab is not None:
+            dev = engine.device
+            nc = K.head_ncand(draft_vocab.size)
+            self.dv_logits = torch.zeros(engine.max_rows, draft_vocab.size, dtype=torch.float32, device=dev)
+            self.dv_cand_val = torch.zeros(engine.max_rows * nc, dtype=torch.float32, device=dev)
+            self.dv_cand_idx = torch.zeros(engine.max_rows * nc, dtype=torch.int32, device=dev)
+            self.dv_ncand = nc
         cfg = engine.cfg
         self.kv0 = cfg.n_layers if kv_layer0 is None else kv_layer0
         if engine.kv.k.shape[0] < self.kv0 + len(head.layers):
@@ -78,9 +86,17 @@ class DraftHead:
         b.resid[:n] = part[: s * n * h].view(s, n, h).sum(dim=0).to(torch.bfloat16)
         pend = m.layers_walk(head.layers, n, eng.ctrl, eng.block_table, eng.max_blocks, eng.kv,
                              first_from_embed=False, kv_layer0=self.kv0)
-        m.head(n, pend, eng.ctrl, False, final_norm=head.norm)
         self.rows_run += n
-        return eng._read_out(n)
+        if self.dv is None:
+            m.head(n, pend, eng.ctrl, False, final_norm=head.norm)
+            return eng._read_out(n)
+        # reduced draft vocabulary: fold + norm as the head does, then only V' rows of the lm_head; the arg-max
+        # is a position in V', mapped back to a token id on the host
+        K.resid_norm(1, n, h, head.norm, cfg.rms_eps, b.resid, b.x, resid_in=b.resid, part=pend[0], part_slice=n * h,
+                     splits=pend[1])
+        K.head_gemv(self.dv.head, b.x, self.dv_logits, n, self.dv.size, h, self.dv_cand_val, self.dv_cand_idx)
+        K.argmax_finish(self.dv_cand_val, self.dv_cand_idx, self.dv_ncand, n, eng.ctrl, False)
+        return [self.dv.to_token(p) for p in eng._read_out(n)]
 
     # ------------------------------------------------------------------ prompt ingestion
     def _ingest_chunk(self, runner, slot: int, ids: Sequence[int], pos0: int, resid: torch.Tensor):
@@ -119,7 +135,8 @@ class DraftHead:
 class SpecAdapter:
     """EngineIface with ``draft``: wraps an ``EngineAdapter`` and a draft head."""
 
-    def __init__(self, inner, spec: str = "mtp", spec_max: int = 3, draft_model=None):
+    def __init__(self, inner, spec: str = "mtp", spec_max: int = 3, draft_model=None, draft_vocab: int = 0,
+                 draft_vocab_ids: Optional[str] = None):
         self.inner = inner
         self.e: Engine = inner.e
         self.spec, self.k_max = spec, spec_max
@@ -134,7 +151,12 @@ class SpecAdapter:
                 draft_model = load_drafter(draft_model, self.e.device)
             head = draft_model if isinstance(draft_model, MtpWeights) else random_drafter(self.e.cfg, self.e.device)
             kind = "dflash"
-        self.head = DraftHead(self.e, head, kind)
+        dv = None
+        if draft_vocab and draft_vocab < self.e.cfg.vocab:
+            from ..loader.draft_vocab import DraftVocab, build_draft_vocab, read_ranked_ids
+            ranked = read_ranked_ids(draft_vocab_ids) if draft_vocab_ids else None
+            dv = DraftVocab(w.lm_head, build_draft_vocab(self.e.cfg.vocab, draft_vocab, inner.eos_ids, ranked))
+        self.head = DraftHead(self.e, head, kind, draft_vocab=dv)
         self.e.model.attn_fixed_spans = True     # verify rows must reproduce single-row decoding bit for bit
         self.e.graphs.clear()
         self.vocab_size, self.max_len, self.max_seqs, self.eos_ids = inner.vocab_size, inner.max_len, inner.max_seqs, inner.eos_ids

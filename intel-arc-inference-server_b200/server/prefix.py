@@ -21,9 +21,20 @@ import numpy as np
 PAGE = 16
 
 
-def parse_gb(text, default_gb: float = 4.0) -> float:
+def auto_host_gb() -> float:
+    """The host store's size when none is given: min(16 GiB, half the RAM, what is available minus 8 GiB), the
+    reference's rule (src/cli/prefix_cache_size.h)."""
+    try:
+        import psutil
+        vm = psutil.virtual_memory()
+        return max(0.0, min(16.0, vm.total / 2**31, vm.available / 2**30 - 8.0))   # 16, not 32: the store is pinned at start
+    except Exception:
+        return 4.0
+
+
+def parse_gb(text, default_gb=None) -> float:
     if text in (None, "", "auto"):
-        return default_gb
+        return auto_host_gb() if default_gb is None else default_gb
     return float(text)
 
 

@@ -39,3 +39,14 @@ def test_draft_head_roundtrip_through_a_snapshot(tmp_path):
     assert torch.equal(head.fc.w4b, full.mtp.fc.w4b)
     assert torch.equal(head.norm, full.mtp.norm)
     assert torch.equal(head.layers[0].qkv.w4b, full.mtp.layers[0].qkv.w4b)
+
+
+def test_draft_vocabulary_rule():
+    from b200serve.loader.draft_vocab import build_draft_vocab
+    ids = build_draft_vocab(1000, 16, forced=[999, 2], ranked=[500, 2, 501, 7])
+    assert len(ids) == 16 and ids == sorted(ids)
+    assert {999, 2, 500, 501, 7} <= set(ids)
+    assert set(ids) - {999, 2, 500, 501, 7} == set(i for i in range(13) if i not in (2, 7))   # lowest ids fill the rest
+    assert build_draft_vocab(100, 0) == list(range(100)) and build_draft_vocab(100, 200) == list(range(100))
+    with pytest.raises(ValueError):
+        build_draft_vocab(100, 2, forced=[1, 2, 3])
