@@ -126,3 +126,28 @@ def run_ranks(wire: HostWire, rounds: int, parts) -> List[List[Optional[np.ndarr
     [t.start() for t in ts]
     [t.join() for t in ts]
     return out
+
+
+def ep_plan_mirror(cnt_all, rank: int, world: int, max_blk: int = 1 << 30):
+    """Host mirror of ``ep_plan_kernel`` (ops/csrc/ep.cu): from every source's per-expert counts
+    (``cnt_all[source][expert]``) the layout one rank derives -- where ITS rows of every expert start in the
+    owner's receive buffer (``send_base``) and, for its own experts, the 128-row block table.  Every rank runs the
+    same arithmetic on the same counts, which is why nothing but the counts is exchanged."""
+    e_total = len(cnt_all[0])
+    el = e_total // world
+    tot = [sum(cnt_all[s][e] for s in range(world)) for e in range(e_total)]
+    pad = [(t + 127) // 128 * 128 for t in tot]
+    send_base, blocks = [0] * e_total, []
+    total_rows = 0
+    for e in range(e_total):
+        owner = e // el
+        base = sum(pad[e2] for e2 in range(owner * el, e))
+        before = sum(cnt_all[s][e] for s in range(rank))
+        send_base[e] = base + before
+        if owner == rank:
+            for j in range(pad[e] // 128):
+                if base // 128 + j < max_blk:
+                    blocks.append((e - owner * el, base + 128 * j, min(128, tot[e] - 128 * j)))
+            if e - owner * el == el - 1:
+                total_rows = base + pad[e]
+    return send_base, blocks, total_rows

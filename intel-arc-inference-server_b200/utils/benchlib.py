@@ -119,10 +119,10 @@ def run_spec_bench(args, barrier, iters: int = 12) -> dict:
     out = {}
     g = torch.Generator().manual_seed(0)
     ids = torch.randint(0, cfg.vocab - 1, (depth,), generator=g).tolist()
-    for kind, k, accepts in (("mtp", 3, (0, 3)), ("dflash", 7, (0, 3, 7))):
+    for kind, k, accepts, dv in (("mtp", 3, (0, 3), 0), ("mtp", 3, (3,), 32768), ("dflash", 7, (0, 3, 7), 0)):
         eng = Engine(weights, max_seqs=1, max_len=depth + 64 * (iters + 4) + 64, extra_kv_layers=2,
                      nsplit_attn=max(4, min(64, depth // 128)))
-        ad = SpecAdapter(EngineAdapter(eng), kind, k)
+        ad = SpecAdapter(EngineAdapter(eng), kind, k, draft_vocab=dv)
         pending = ad.prefill(0, ids)
         for acc in accepts:
             def iteration(pending):
@@ -140,7 +140,7 @@ def run_spec_bench(args, barrier, iters: int = 12) -> dict:
                 pending = iteration(pending)
             torch.cuda.synchronize()
             dt = (time.perf_counter() - t0) / iters
-            out[f"{kind}_k{k}_accept{acc + 1}"] = {"ms_per_iteration": dt * 1e3, "tokens_per_s": (acc + 1) / dt,
+            out[f"{kind}_k{k}{'_dv' + str(dv) if dv else ''}_accept{acc + 1}"] = {"ms_per_iteration": dt * 1e3, "tokens_per_s": (acc + 1) / dt,
                                                   "rows_verified": k + 1}
         del eng, ad
         torch.cuda.empty_cache()

@@ -79,3 +79,35 @@ def test_device_wait_runs_out_and_reports_status():
     K.wire_wait(cnt, 1)                          # a satisfied wait returns at once
     torch.cuda.synchronize()
     assert K.status() == {}
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_expert_parallel_plan_is_consistent_across_ranks(world):
+    """Every rank derives the layout from the same counts: rows of different sources never overlap in a
+    destination's buffer, every expert's rows are contiguous, and the owner's block table covers exactly them."""
+    from b200serve.parallel.protocol import ep_plan_mirror
+    rng = np.random.default_rng(world)
+    e_total, el = 32, 32 // world
+    cnt = rng.integers(0, 300, size=(world, e_total)).tolist()
+    for s in range(world):
+        cnt[s][rng.integers(0, e_total)] = 0          # some experts get nothing from some sources
+    plans = [ep_plan_mirror(cnt, r, world) for r in range(world)]
+    for dest in range(world):
+        _, blocks, total_rows = plans[dest]
+        taken = np.zeros(total_rows, dtype=np.int32)
+        owner_of = np.full(total_rows, -1, dtype=np.int32)
+        for src in range(world):
+            base = plans[src][0]
+            for e in range(dest * el, (dest + 1) * el):
+                lo, n = base[e], cnt[src][e]
+                assert lo + n <= total_rows
+                taken[lo: lo + n] += 1
+                owner_of[lo: lo + n] = e - dest * el
+        assert taken.max() <= 1                        # no two (source, expert) ranges overlap
+        covered = np.zeros(total_rows, dtype=bool)
+        for el_id, row0, rows in blocks:
+            assert row0 % 128 == 0 and 0 < rows <= 128
+            assert (taken[row0: row0 + rows] == 1).all() and (owner_of[row0: row0 + rows] == el_id).all()
+            assert (taken[row0 + rows: row0 + 128] == 0).all()      # padding rows belong to nobody
+            covered[row0: row0 + rows] = True
+        assert (covered == (taken == 1)).all()         # the blocks cover exactly the rows that arrive

@@ -43,8 +43,8 @@ def test_mtp_head_rows_match_oracle():
         assert drafts[0] == want
 
 
-@pytest.mark.parametrize("kind", ["mtp", "dflash"])
-def test_speculative_loop_is_lossless(kind):
+@pytest.mark.parametrize("kind,dv", [("mtp", 0), ("dflash", 0), ("mtp", 512)])
+def test_speculative_loop_is_lossless(kind, dv):
     """Greedy output with drafts + verify + accept equals plain greedy decoding, token for token."""
     from b200serve.native import host as H
     from b200serve.runtime.engine import Engine
@@ -57,7 +57,7 @@ def test_speculative_loop_is_lossless(kind):
     plain = Engine(w, max_seqs=1, max_len=512, use_graphs=False)
     want = plain.generate(prompt, 24)
     eng = Engine(w, max_seqs=1, max_len=512, use_graphs=False, extra_kv_layers=2)
-    ad = SpecAdapter(EngineAdapter(eng), kind, 3)
+    ad = SpecAdapter(EngineAdapter(eng), kind, 3, draft_vocab=dv)      # dv: drafts from a reduced vocabulary
     pending = ad.prefill(0, prompt)
     got = [pending]
     iters = 0
