@@ -207,7 +207,8 @@ def main():
         guarded("spec_forced_accept", lambda: run_spec_bench(args, barrier))
     if args.what in ("all", "prefix"):
         from b200serve.utils.benchlib import run_prefix_bench
-        guarded("prefix_cache", lambda: run_prefix_bench(args, barrier))
+        # every rank pins its own host store: a quarter of the prefix when several ranks share one host
+        guarded("prefix_cache", lambda: run_prefix_bench(args, barrier, 65536 if world == 1 else 16384))
     if world > 1 and args.what in ("all", "tp"):
         guarded("tp", tp_extra)
     if world > 1 and args.what in ("all", "ep"):

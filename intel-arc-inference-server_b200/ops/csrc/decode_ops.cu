@@ -753,12 +753,14 @@ template <typename WT>
 static int head_launch(const HeadParams<WT>& p, cudaStream_t st) {
   const int rows_per_cta = 64;
   dim3 grid((p.N + rows_per_cta - 1) / rows_per_cta);
-  for (int m0 = 0; m0 < p.M; m0 += 4) {
-    const int mt = min(4, p.M - m0);
+  // up to 8 rows per pass over the weights (the rows share every weight vector a lane loads)
+  for (int m0 = 0; m0 < p.M; m0 += 8) {
+    const int mt = min(8, p.M - m0);
     int rc;
     if (mt == 1) rc = b2_launch(head_gemv_kernel<WT, 1>, grid, dim3(256), 0, st, true, p, m0);
     else if (mt == 2) rc = b2_launch(head_gemv_kernel<WT, 2>, grid, dim3(256), 0, st, true, p, m0);
-    else rc = b2_launch(head_gemv_kernel<WT, 4>, grid, dim3(256), 0, st, true, p, m0);
+    else if (mt <= 4) rc = b2_launch(head_gemv_kernel<WT, 4>, grid, dim3(256), 0, st, true, p, m0);
+    else rc = b2_launch(head_gemv_kernel<WT, 8>, grid, dim3(256), 0, st, true, p, m0);
     if (rc) return rc;
   }
   return 0;

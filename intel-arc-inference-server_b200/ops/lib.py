@@ -207,7 +207,7 @@ def head_gemv(w, x, out, m, n, k, cand_val=None, cand_idx=None, n_valid=None, ws
     global launch_count
     rc = lib().b2_head_gemv(_p(w), _p(wscale), int(wscale is not None), _p(x), _p(out), m, n, k, n, _p(cand_val),
                             _p(cand_idx), n if n_valid is None else n_valid, _stream())
-    launch_count += (m + 3) // 4 - 1
+    launch_count += (m + 7) // 8 - 1
     _check(rc, "head_gemv")
 
 
