@@ -109,6 +109,41 @@ class Engine:
             c[K.CTRL_CUR_TOKEN + i] = r.token
         self.ctrl.copy_(c, non_blocking=True)
 
+    # ------------------------------------------------------------------ session snapshots
+    def save_kv(self, slot: int, begin: int, end: int) -> dict:
+        """The KV of positions ``[begin, end)`` of ``slot`` (whole pages: both multiples of 16, or ``end`` the
+        sequence length) as pinned host tensors in page order -- the reference's ``save_kv`` (src/runtime/engine.h:170-209);
+        the layout is ``[layer][page][kv head][16][head dim]`` per tensor and does not depend on the parallel mode."""
+        if begin % PAGE or (end % PAGE and end != self.seq_len[slot]) or not 0 <= begin <= end <= self.seq_len[slot]:
+            raise ValueError("save_kv takes whole pages inside the sequence")
+        pages = list(self.pool.table(slot))[begin // PAGE: (end + PAGE - 1) // PAGE]
+        idx = torch.as_tensor(pages, device=self.device, dtype=torch.int64)
+        tensors = {"k": self.kv.k, "v": self.kv.v}
+        if self.kv.kv_int8:
+            tensors.update({"k_scale": self.kv.k_scale, "v_scale": self.kv.v_scale})
+        out = {"begin": begin, "end": end, "kv_dtype": self.kv_dtype}
+        for name, t in tensors.items():
+            host = torch.empty((t.shape[0], len(pages)) + tuple(t.shape[2:]), dtype=t.dtype).pin_memory()
+            host.copy_(t.index_select(1, idx), non_blocking=True)
+            out[name] = host
+        torch.cuda.current_stream().synchronize()
+        return out
+
+    def load_kv(self, slot: int, blob: dict):
+        """Puts a ``save_kv`` blob back at its positions; the slot must hold exactly ``blob["begin"]`` positions."""
+        begin, end = blob["begin"], blob["end"]
+        if blob["kv_dtype"] != self.kv_dtype or self.seq_len[slot] != begin:
+            raise ValueError("load_kv: the slot must end where the blob begins and use the same KV form")
+        self._ensure_pages(slot, end)
+        pages = list(self.pool.table(slot))[begin // PAGE: (end + PAGE - 1) // PAGE]
+        idx = torch.as_tensor(pages, device=self.device, dtype=torch.int64)
+        tensors = {"k": self.kv.k, "v": self.kv.v}
+        if self.kv.kv_int8:
+            tensors.update({"k_scale": self.kv.k_scale, "v_scale": self.kv.v_scale})
+        for name, t in tensors.items():
+            t.index_copy_(1, idx, blob[name].to(self.device, non_blocking=True))
+        self.seq_len[slot] = end
+
     # ------------------------------------------------------------------ running a step
     def _enqueue(self, m: int, advance: bool):
         self.model.step_rows(m, self.ctrl, self.block_table, self.max_blocks, self.kv, advance)

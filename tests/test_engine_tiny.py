@@ -91,3 +91,27 @@ def test_tiny_dense_logits_close_to_oracle():
     assert (got - ref).abs().max() < 0.03 * ref.abs().max()
     cos = torch.nn.functional.cosine_similarity(got, ref, dim=-1)
     assert cos.min() > 0.999
+
+
+@pytest.mark.gpu
+def test_kv_snapshot_roundtrip_continues_identically():
+    """save_kv / load_kv: a sequence restored into another slot continues with the same tokens."""
+    import torch
+    from b200serve.models.config import preset
+    from b200serve.models.weights import random_weights
+    from b200serve.runtime.engine import Engine, Row
+    cfg = preset("tiny-dense")
+    w = random_weights(cfg, device="cuda", seed=1)
+    eng = Engine(w, max_seqs=2, max_len=256, use_graphs=False)
+    g = torch.Generator().manual_seed(4)
+    ids = torch.randint(0, cfg.vocab, (48,), generator=g).tolist()
+    first = eng.prefill(0, ids)
+    blob = eng.save_kv(0, 0, 48)
+    assert blob["k"].shape[1] == 3 and blob["k"].is_pinned()
+    a = [eng.forward_rows([Row(0, 48, first)])[0]]
+    a.append(eng.forward_rows([Row(0, 49, a[0])])[0])
+    eng.load_kv(1, blob)
+    assert eng.seq_len[1] == 48
+    b = [eng.forward_rows([Row(1, 48, first)])[0]]
+    b.append(eng.forward_rows([Row(1, 49, b[0])])[0])
+    assert a == b
