@@ -42,6 +42,7 @@ struct AttnRowsParams {
   __nv_bfloat16* out;  // [M][n_q * D]
   int* tickets;        // [M][n_kv]
   int M, n_q, n_kv, gqa, nsplit, max_blocks;
+  int nbuf;        // 1: one K / V tile pair; 2: the next batch of keys is fetched while this one is multiplied
   int span_pages;  // > 0: every split covers this many pages whatever the context (a row's bits then do not depend
                    // on which rows share its CTA); 0: the group's context is cut into nsplit equal parts
   float scale_log2;
@@ -60,8 +61,11 @@ template <bool I8>
 __global__ void __launch_bounds__(kThreads) attn_rows_kernel(const AttnRowsParams p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 127u) & ~127u;
-  const uint32_t ks = base, vs = base + KB * ROWB, bar = vs + KB * ROWB;
-  const uint32_t k8s = bar + 64, v8s = k8s + KB * D;   // int8 form: staged rows before conversion (128 B each)
+  // bf16 form: nbuf pairs of operand tiles.  int8 form: one pair of operand tiles, nbuf pairs of staged int8 rows.
+  const int ntile = I8 ? 1 : p.nbuf;
+  const uint32_t ks0 = base, vs0 = base + KB * ROWB, tileB = 2 * KB * ROWB;
+  const uint32_t bar0 = base + ntile * tileB;
+  const uint32_t k8s0 = bar0 + 64, v8s0 = k8s0 + KB * D, stageB = 2 * KB * D;   // int8 rows before expansion (128 B each)
   float* scratch = reinterpret_cast<float*>(smem_raw + (base - smem_u32(smem_raw)));  // merge reuses the K / V tiles
   __shared__ int s_last;
   pdl_wait();
@@ -92,7 +96,8 @@ __global__ void __launch_bounds__(kThreads) attn_rows_kernel(const AttnRowsParam
   const int* bt = p.block_table + (size_t)req * p.max_blocks;
 
   if (tid == 0) {
-    mbar_init(bar, 1);
+    mbar_init(bar0, 1);
+    mbar_init(bar0 + 8, 1);
     mbar_fence_init();
   }
   __syncthreads();
@@ -120,40 +125,61 @@ __global__ void __launch_bounds__(kThreads) attn_rows_kernel(const AttnRowsParam
   float mx[2] = {-INFINITY, -INFINITY}, lsum[2] = {0.f, 0.f};
 
   bool okw = true;
-  int batch = 0;
-  for (int kb0 = key0; kb0 < key1; kb0 += KB, ++batch) {
-    const int nk = min(KB, key1 - kb0);
-    __syncthreads();  // the previous batch is consumed
+  const int nbatch = (max(key1 - key0, 0) + KB - 1) / KB;
+  float ksc[2] = {0.f, 0.f}, vsc[2] = {0.f, 0.f};
+  // One bulk copy per key row into buffer b % nbuf (every thread fetches the row of its own key).
+  auto issue = [&](int b) {
+    const int kb0 = key0 + b * KB, nk = min(KB, key1 - kb0), buf = b % p.nbuf;
+    const uint32_t bar = bar0 + 8 * buf;
     if (tid == 0) mbar_expect_tx(bar, (uint32_t)nk * (I8 ? 256u : 512u));
     __syncthreads();
-    float ksc = 0.f, vsc = 0.f;
+    const uint32_t vt = vs0 + (I8 ? 0 : buf) * tileB;
     if (tid < nk) {
       const int key = kb0 + tid;
       const int page = bt[key >> 4], slot = key & 15;
       const size_t row = ((size_t)page * p.n_kv + kh) * 16 + slot;
       if (I8) {
-        bulk_g2s(k8s + tid * D, reinterpret_cast<const int8_t*>(p.k_cache) + row * D, D, bar);
-        bulk_g2s(v8s + tid * D, reinterpret_cast<const int8_t*>(p.v_cache) + row * D, D, bar);
-        ksc = p.k_scale[row];
-        vsc = p.v_scale[row];
+        bulk_g2s(k8s0 + buf * stageB + tid * D, reinterpret_cast<const int8_t*>(p.k_cache) + row * D, D, bar);
+        bulk_g2s(v8s0 + buf * stageB + tid * D, reinterpret_cast<const int8_t*>(p.v_cache) + row * D, D, bar);
+        ksc[buf] = p.k_scale[row];
+        vsc[buf] = p.v_scale[row];
       } else {
-        bulk_g2s(ks + tid * ROWB, reinterpret_cast<const __nv_bfloat16*>(p.k_cache) + row * D, 256, bar);
-        bulk_g2s(vs + tid * ROWB, reinterpret_cast<const __nv_bfloat16*>(p.v_cache) + row * D, 256, bar);
+        bulk_g2s(ks0 + buf * tileB + tid * ROWB, reinterpret_cast<const __nv_bfloat16*>(p.k_cache) + row * D, 256, bar);
+        bulk_g2s(vt + tid * ROWB, reinterpret_cast<const __nv_bfloat16*>(p.v_cache) + row * D, 256, bar);
       }
-    } else {
+    } else if (!I8) {
       // rows without a key: V must be finite (its products are multiplied by P = 0)
 #pragma unroll
       for (int i = 0; i < 16; ++i)
-        asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};" ::"r"(vs + tid * ROWB + 16 * i), "r"(0) : "memory");
+        asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};" ::"r"(vt + tid * ROWB + 16 * i), "r"(0) : "memory");
     }
-    if (okw) okw = mbar_wait(bar, batch & 1, ERR_ATTN_WAIT);
+  };
+  if (p.nbuf == 2 && nbatch > 0) issue(0);
+  for (int batch = 0; batch < nbatch; ++batch) {
+    const int kb0 = key0 + batch * KB;
+    const int nk = min(KB, key1 - kb0);
+    const int buf = batch % p.nbuf;
+    const uint32_t ks = ks0 + (I8 ? 0 : buf) * tileB, vs = vs0 + (I8 ? 0 : buf) * tileB;
+    const uint32_t k8s = k8s0 + buf * stageB, v8s = v8s0 + buf * stageB, bar = bar0 + 8 * buf;
+    __syncthreads();  // the previous batch is consumed: its buffer may be refilled
+    if (p.nbuf == 2) {
+      if (batch + 1 < nbatch) issue(batch + 1);
+    } else {
+      issue(batch);
+    }
+    if (okw) okw = mbar_wait(bar, (batch / p.nbuf) & 1, ERR_ATTN_WAIT);
     if (I8) {
       // every thread expands its own key's row: int8 x per-row scale -> bf16 into the operand tiles
+      if (tid >= nk) {   // rows without a key: V must be finite (its products are multiplied by P = 0)
+#pragma unroll
+        for (int i = 0; i < 16; ++i)
+          asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};" ::"r"(vs + tid * ROWB + 16 * i), "r"(0) : "memory");
+      }
       if (okw && tid < nk) {
 #pragma unroll
         for (int which = 0; which < 2; ++which) {
           const uint32_t src = (which ? v8s : k8s) + tid * D, dst = (which ? vs : ks) + tid * ROWB;
-          const float sc = which ? vsc : ksc;
+          const float sc = which ? vsc[buf] : ksc[buf];
 #pragma unroll
           for (int i = 0; i < D / 16; ++i) {
             uint32_t w0, w1, w2, w3;
@@ -336,12 +362,16 @@ extern "C" int b2_attn_rows(const void* q, const void* k_cache, const void* v_ca
   p.scale_log2 = scale * 1.4426950408889634f;
   p.span_pages = span_pages;
   if (span_pages > 0 && (long)span_pages * nsplit < max_blocks) return -2;  // fixed spans must cover the longest sequence
-  const int smem = 128 + 2 * KB * ROWB + 64 + (kv_int8 ? 2 * KB * D : 0);
+  // prefetch the next batch when a split holds more than two batches of keys (long contexts); short ones
+  // keep the small footprint that lets two CTAs share an SM
+  const int pages_per_split = span_pages > 0 ? span_pages : (max_blocks + nsplit - 1) / nsplit;
+  p.nbuf = pages_per_split * 16 > 2 * KB ? 2 : 1;
+  const int smem = 128 + (kv_int8 ? 1 : p.nbuf) * 2 * KB * ROWB + 64 + (kv_int8 ? p.nbuf * 2 * KB * D : 0);
   static int configured[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   if (!configured[dev & 63]) {
-    const int most = 128 + 2 * KB * ROWB + 64 + 2 * KB * D;
+    const int most = 128 + 2 * 2 * KB * ROWB + 64 + 2 * 2 * KB * D;
     cudaError_t e = cudaFuncSetAttribute(attn_rows_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, most);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_rows_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, most);
     if (e != cudaSuccess) return (int)e;

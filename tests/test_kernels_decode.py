@@ -316,7 +316,8 @@ def test_prequantised_rows_give_the_same_bits_as_in_kernel_staging(m):
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("n_q,n_kv,rows,ctx,nsplit", [(40, 8, [(0, 8)], 1500, 16), (16, 4, [(0, 3), (1, 1), (0, 2)], 700, 8),
-                                                       (8, 2, [(0, 1)], 4096, 32), (5, 1, [(1, 8), (0, 5)], 333, 4)])
+                                                       (8, 2, [(0, 1)], 4096, 32), (5, 1, [(1, 8), (0, 5)], 333, 4),
+                                                       (8, 2, [(0, 4), (1, 1)], 4000, 4)])   # 8 batches per split: prefetch path
 def test_attn_rows_matches_per_row_kernel(n_q, n_kv, rows, ctx, nsplit):
     """The tensor-core multi-row kernel against the per-row kernel (itself checked against fp32): groups of
     consecutive rows of one request, several requests in one step, ragged contexts, several splits."""
@@ -361,7 +362,7 @@ def test_attn_rows_matches_per_row_kernel(n_q, n_kv, rows, ctx, nsplit):
 def test_attn_rows_int8_kv_matches_per_row_kernel():
     k_ = K()
     torch.manual_seed(77)
-    n_q, n_kv, d, ctx, nsplit = 16, 4, 128, 900, 8
+    n_q, n_kv, d, ctx, nsplit = 16, 4, 128, 900, 2      # 4 batches of keys per split: the prefetch path
     max_blocks = (ctx + 15) // 16 + 2
     num_pages = max_blocks + 2
     table = (torch.randperm(num_pages - 1)[:max_blocks] + 1).to(torch.int32).view(1, -1).cuda()
