@@ -42,8 +42,7 @@ def main(argv=None):
     ids = _ids(f.ids) if f.ids else None
     need = max(depth, len(ids or []), f.prefill_length) + f.tg + f.n + 64
     eng = Engine(w, max_seqs=1, max_len=need, kv_dtype=f.kv_cache, int8_head=f.int8_head,
-                 prefill_backend=f.prefill_backend if f.prefill or f.bench else "rows",
-                 nsplit_attn=max(4, min(64, max(depth, 128) // 128)))
+                 prefill_backend=f.prefill_backend if f.prefill or f.bench else "rows")
     if ids is not None and not (f.bench or f.profile):
         out = eng.generate(ids, f.n)
         K.check_status()

@@ -69,6 +69,15 @@ class StepBuffers:
         return self._parts[key]
 
 
+def attn_splits(n_kv_heads: int, depth: int) -> int:
+    """KV splits of the decode attention for contexts around ``depth``: KV heads x splits CTAs fill the 2 x 148
+    resident slots of the multi-row kernel in one wave, a split keeps at least 64 keys (the merge reads every
+    split), and the partial buffers hold at most 64 splits.  Measured on the 27B shape (8 KV heads), 16 layers:
+    depth 1024 1.41 / 1.43 / 1.45 ms with 16 / 32 / 37 splits, depth 4096 1.50 / 1.49 ms with 32 / 37, depth
+    32768 (8 layers) 1.10 / 1.17 ms with 37 / 64."""
+    return max(4, min(64, 296 // max(1, n_kv_heads), max(depth, 64) // 64))
+
+
 class KVCache:
     """Paged KV: per layer ``[page][kv_head][16][D]`` for K and for V (bf16 or int8 + fp32 scales)."""
 

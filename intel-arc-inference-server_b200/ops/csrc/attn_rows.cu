@@ -4,12 +4,17 @@
 // keys and values; the per-row kernel (decode_ops.cu: attn_decode_kernel) re-reads them for every row and
 // its per-lane loads keep only a few KB in flight.  Here one CTA serves up to 8 rows x GQA query heads
 // of one KV head and one KV split:
-//   * K and V rows of up to 128 keys are fetched with one bulk copy each (cp.async.bulk, 256 B per row, all
-//     in flight at once, one mbarrier) into padded shared-memory rows (272 B: conflict-free ldmatrix);
+//   * K and V of up to 128 keys are fetched page by page with tiled TMA copies (16 keys x 64 dims = 2 KB per
+//     copy, 128-byte swizzle, all of a batch in flight on one mbarrier): one copy instruction per 2 KB keeps the
+//     copy engine fed where one bulk copy per 256-byte row did not (measured: 6 us per 64 KB batch), and the
+//     swizzle gives conflict-free ldmatrix without padded rows;
 //   * S = Q K^T and O += P V run on mma.m16n8k16 (bf16, fp32 accumulate): warp w owns query rows
 //     16 w .. 16 w + 15 (row = token row x GQA + head), K through ldmatrix, V through ldmatrix.trans, P stays
 //     in registers (the accumulator layout of S is the A-operand layout of the next MMA);
 //   * every row masks the keys beyond its own position (causal inside the group);
+//   * a group of at most 16 (32) query rows leaves three (two) of the four warps without rows: those warps
+//     then take a quarter (half) of every batch's keys with their own running maximum and sum, and the
+//     slices are merged in slice order through shared memory before the split's partial is written;
 //   * split-KV partials and the in-kernel merge by the last CTA ("ticket") have the layout and the fixed
 //     split order of the per-row kernel, so either kernel can serve a row.
 // An int8 cache (one fp32 scale per row) is staged as int8 and expanded to bf16 in shared memory by the thread
@@ -18,6 +23,10 @@
 // attention's GQA packing (src/kernels/attn_v2.cl).
 #include "common.cuh"
 
+#include <cstdlib>
+#include <mutex>
+#include <unordered_map>
+
 using namespace b2;
 
 namespace {
@@ -25,14 +34,16 @@ namespace {
 constexpr int CTRL_ROW_REQ = 16, CTRL_ROW_POS = 80;
 constexpr int D = 128;
 constexpr int KB = 128;          // keys per batch
-constexpr int ROWB = 272;        // bytes per staged K / V row (256 + 16 pad)
+constexpr int HALFB = KB * 128;  // one tile half: 128 keys x 64 dims (128-byte rows, TMA 128-byte swizzle)
+constexpr int TILEB = 2 * HALFB; // a K or V tile: dims 0..63, then dims 64..127
 constexpr int kMaxRows = 8;      // token rows per CTA
 constexpr int kThreads = 128;    // 4 warps = up to 64 query rows
+constexpr int kBtSmem = 256;     // page ids of a split kept in shared memory
+constexpr int kPassKeys = 64;    // S of one pass lives in registers: 64 keys = 32 registers
 
 struct AttnRowsParams {
   const __nv_bfloat16* q;  // [M][n_q * D]
-  const void* k_cache;     // bf16 or int8 [page][n_kv][16][D]
-  const void* v_cache;
+  CUtensorMap k_map, v_map;  // the caches [page][n_kv][16][D] as 2-D tensors of rows x D: boxes of 16 rows x 128 bytes
   const float* k_scale;    // int8 form: [page][n_kv][16]
   const float* v_scale;
   const int* block_table;
@@ -43,6 +54,7 @@ struct AttnRowsParams {
   int* tickets;        // [M][n_kv]
   int M, n_q, n_kv, gqa, nsplit, max_blocks;
   int nbuf;        // 1: one K / V tile pair; 2: the next batch of keys is fetched while this one is multiplied
+  int one_slice;   // 1: never cut a batch's keys over idle warps (a row's bits then do not depend on the group's size)
   int span_pages;  // > 0: every split covers this many pages whatever the context (a row's bits then do not depend
                    // on which rows share its CTA); 0: the group's context is cut into nsplit equal parts
   float scale_log2;
@@ -57,43 +69,40 @@ __device__ __forceinline__ void ldsm_x4_trans(uint32_t addr, uint32_t& r0, uint3
                : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
 }
 
-template <bool I8>
-__global__ void __launch_bounds__(kThreads) attn_rows_kernel(const AttnRowsParams p) {
-  extern __shared__ uint8_t smem_raw[];
-  const uint32_t base = (smem_u32(smem_raw) + 127u) & ~127u;
+// byte offset of (key row, dim d) inside a swizzled tile; d a multiple of 8
+__device__ __forceinline__ uint32_t tile_off(int row, int d) {
+  return (uint32_t)((d >> 6) * HALFB + row * 128 + ((((d & 63) >> 3) ^ (row & 7)) << 4));
+}
+
+// NKS: key slices per batch (1, 2 or 4); the four warps are NKS slices x (4 / NKS) groups of 16 query rows.
+template <bool I8, int NKS>
+__device__ __forceinline__ void attn_rows_body(const AttnRowsParams& p, uint8_t* smem_raw, const int* s_pos, int* s_last_p, int* s_bt,
+                                               const int req, const int rows, const int QR, const int ctx_max) {
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;   // the swizzle pattern repeats every 1024 bytes
   // bf16 form: nbuf pairs of operand tiles.  int8 form: one pair of operand tiles, nbuf pairs of staged int8 rows.
   const int ntile = I8 ? 1 : p.nbuf;
-  const uint32_t ks0 = base, vs0 = base + KB * ROWB, tileB = 2 * KB * ROWB;
-  const uint32_t bar0 = base + ntile * tileB;
-  const uint32_t k8s0 = bar0 + 64, v8s0 = k8s0 + KB * D, stageB = 2 * KB * D;   // int8 rows before expansion (128 B each)
-  float* scratch = reinterpret_cast<float*>(smem_raw + (base - smem_u32(smem_raw)));  // merge reuses the K / V tiles
-  __shared__ int s_last;
-  pdl_wait();
-  pdl_launch_dependents();
+  const uint32_t ks0 = base, vs0 = base + TILEB, tileB = 2 * TILEB;
+  const uint32_t k8s0 = base + ntile * tileB, v8s0 = k8s0 + KB * D, stageB = 2 * KB * D;   // int8 rows (128 B each, swizzled)
+  const uint32_t bar0 = k8s0 + (I8 ? p.nbuf * stageB : 0);
+  float* scratch = reinterpret_cast<float*>(smem_raw + (base - smem_u32(smem_raw)));  // merges reuse the K / V tiles
+  int& s_last = *s_last_p;
+  constexpr int NRG = 4 / NKS;    // groups of 16 query rows
+  constexpr int KW = KB / NKS;              // keys per warp and batch
+  constexpr int KS = KW > kPassKeys ? kPassKeys : KW;   // keys per pass over the warp's slice
+  constexpr int NJ = KS / 8;                // n8 tiles of keys per pass
   const int kh = blockIdx.x, split = blockIdx.y, z = blockIdx.z;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
-  // ---- the group: consecutive rows of one request; this CTA is its leader or leaves.  The rows' request
-  // ids and positions are read once, in parallel, into shared memory.
-  __shared__ int s_req[64], s_pos[64];
-  if (tid < 64) {
-    s_req[tid] = tid < p.M ? p.ctrl[CTRL_ROW_REQ + tid] : -1;
-    s_pos[tid] = tid < p.M ? p.ctrl[CTRL_ROW_POS + tid] : 0;
-  }
-  __syncthreads();
-  const int req = s_req[z];
-  int gs = z;
-  while (gs > 0 && s_req[gs - 1] == req) --gs;
-  const int rmax = min(kMaxRows, 64 / p.gqa);
-  if ((z - gs) % rmax != 0) return;
-  int rows = 1;
-  while (rows < rmax && z + rows < p.M && s_req[z + rows] == req) ++rows;
-  const int QR = rows * p.gqa;
-  int ctx_max = 0;
-  for (int r = 0; r < rows; ++r) ctx_max = max(ctx_max, s_pos[z + r] + 1);
+  const int rg = warp % NRG, ksl = warp / NRG;
   const int total_pages = (ctx_max + 15) >> 4;
   const int pps = p.span_pages > 0 ? p.span_pages : (total_pages + p.nsplit - 1) / p.nsplit;
   const int key0 = split * pps * 16, key1 = min(ctx_max, (split + 1) * pps * 16);
-  const int* bt = p.block_table + (size_t)req * p.max_blocks;
+  const int* btg = p.block_table + (size_t)req * p.max_blocks + split * pps;
+  // the split's page ids once, so that a batch's copies do not wait for a table load
+  const int npg = min(pps, max(total_pages - split * pps, 0));
+  const bool bt_smem = npg <= kBtSmem;
+  if (bt_smem)
+    for (int i = tid; i < npg; i += kThreads) s_bt[i] = btg[i];
+  const int* bt = bt_smem ? s_bt : btg;
 
   if (tid == 0) {
     mbar_init(bar0, 1);
@@ -103,12 +112,12 @@ __global__ void __launch_bounds__(kThreads) attn_rows_kernel(const AttnRowsParam
   __syncthreads();
 
   // ---- this warp's 16 query rows: (token row, head) of rows g and g + 8, their contexts, Q fragments
-  const bool active = warp * 16 < QR;
+  const bool active = rg * 16 < QR;
   int ctx[2] = {0, 0};
   uint32_t qa[8][4];
 #pragma unroll
   for (int hf = 0; hf < 2; ++hf) {
-    const int qr = warp * 16 + g + 8 * hf;
+    const int qr = rg * 16 + g + 8 * hf;
     const bool ok = qr < QR;
     const int m = z + (ok ? qr / p.gqa : 0), h = ok ? qr % p.gqa : 0;
     ctx[hf] = ok ? s_pos[m] + 1 : 0;
@@ -127,31 +136,38 @@ __global__ void __launch_bounds__(kThreads) attn_rows_kernel(const AttnRowsParam
   bool okw = true;
   const int nbatch = (max(key1 - key0, 0) + KB - 1) / KB;
   float ksc[2] = {0.f, 0.f}, vsc[2] = {0.f, 0.f};
-  // One bulk copy per key row into buffer b % nbuf (every thread fetches the row of its own key).
+  // The pages of batch b into buffer b % nbuf: lanes of warp 0 issue one tiled copy each (page, K or V, half).
   auto issue = [&](int b) {
     const int kb0 = key0 + b * KB, nk = min(KB, key1 - kb0), buf = b % p.nbuf;
+    const int npages = (nk + 15) >> 4;
     const uint32_t bar = bar0 + 8 * buf;
-    if (tid == 0) mbar_expect_tx(bar, (uint32_t)nk * (I8 ? 256u : 512u));
+    if (tid == 0) mbar_expect_tx(bar, (uint32_t)npages * (I8 ? 4096u : 8192u));
     __syncthreads();
-    const uint32_t vt = vs0 + (I8 ? 0 : buf) * tileB;
-    if (tid < nk) {
-      const int key = kb0 + tid;
-      const int page = bt[key >> 4], slot = key & 15;
-      const size_t row = ((size_t)page * p.n_kv + kh) * 16 + slot;
-      if (I8) {
-        bulk_g2s(k8s0 + buf * stageB + tid * D, reinterpret_cast<const int8_t*>(p.k_cache) + row * D, D, bar);
-        bulk_g2s(v8s0 + buf * stageB + tid * D, reinterpret_cast<const int8_t*>(p.v_cache) + row * D, D, bar);
+    const uint32_t kt = ks0 + (I8 ? 0 : buf) * tileB, vt = vs0 + (I8 ? 0 : buf) * tileB;
+    if (tid < 32) {
+      const int pi = tid >> 2, which = tid & 3;   // which: 0 K low dims, 1 K high dims, 2 V low, 3 V high
+      if (pi < npages && (!I8 || !(which & 1))) {
+        const int page = bt[((kb0 - key0) >> 4) + pi];
+        const int row = (page * p.n_kv + kh) * 16;
+        const CUtensorMap* map = (which & 2) ? &p.v_map : &p.k_map;
+        if (I8)
+          tma_load_2d(((which & 2) ? v8s0 : k8s0) + buf * stageB + pi * 2048, map, 0, row, bar);
+        else
+          tma_load_2d(((which & 2) ? vt : kt) + (which & 1) * HALFB + pi * 2048, map, (which & 1) * 64, row, bar);
+      }
+    }
+    if (I8) {
+      if (tid < nk) {
+        const int key = kb0 + tid;
+        const size_t row = ((size_t)bt[(key - key0) >> 4] * p.n_kv + kh) * 16 + (key & 15);
         ksc[buf] = p.k_scale[row];
         vsc[buf] = p.v_scale[row];
-      } else {
-        bulk_g2s(ks0 + buf * tileB + tid * ROWB, reinterpret_cast<const __nv_bfloat16*>(p.k_cache) + row * D, 256, bar);
-        bulk_g2s(vt + tid * ROWB, reinterpret_cast<const __nv_bfloat16*>(p.v_cache) + row * D, 256, bar);
       }
-    } else if (!I8) {
-      // rows without a key: V must be finite (its products are multiplied by P = 0)
+    } else if (tid >= npages * 16) {
+      // rows of pages that are not fetched: V must be finite (its products are multiplied by P = 0)
 #pragma unroll
       for (int i = 0; i < 16; ++i)
-        asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};" ::"r"(vt + tid * ROWB + 16 * i), "r"(0) : "memory");
+        asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};" ::"r"(vt + (i >> 3) * HALFB + tid * 128 + 16 * (i & 7)), "r"(0) : "memory");
     }
   };
   if (p.nbuf == 2 && nbatch > 0) issue(0);
@@ -173,17 +189,17 @@ __global__ void __launch_bounds__(kThreads) attn_rows_kernel(const AttnRowsParam
       if (tid >= nk) {   // rows without a key: V must be finite (its products are multiplied by P = 0)
 #pragma unroll
         for (int i = 0; i < 16; ++i)
-          asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};" ::"r"(vs + tid * ROWB + 16 * i), "r"(0) : "memory");
+          asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};" ::"r"(vs + (i >> 3) * HALFB + tid * 128 + 16 * (i & 7)), "r"(0) : "memory");
       }
       if (okw && tid < nk) {
 #pragma unroll
         for (int which = 0; which < 2; ++which) {
-          const uint32_t src = (which ? v8s : k8s) + tid * D, dst = (which ? vs : ks) + tid * ROWB;
+          const uint32_t src = (which ? v8s : k8s) + tid * D, dst = which ? vs : ks;
           const float sc = which ? vsc[buf] : ksc[buf];
 #pragma unroll
           for (int i = 0; i < D / 16; ++i) {
             uint32_t w0, w1, w2, w3;
-            asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(w0), "=r"(w1), "=r"(w2), "=r"(w3) : "r"(src + 16 * i));
+            asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(w0), "=r"(w1), "=r"(w2), "=r"(w3) : "r"(src + ((i ^ (tid & 7)) << 4)));
             const uint32_t ww[4] = {w0, w1, w2, w3};
             uint32_t o[8];
 #pragma unroll
@@ -191,25 +207,29 @@ __global__ void __launch_bounds__(kThreads) attn_rows_kernel(const AttnRowsParam
               o[2 * j] = pack_bf16((float)(int8_t)(ww[j] & 0xff) * sc, (float)(int8_t)((ww[j] >> 8) & 0xff) * sc);
               o[2 * j + 1] = pack_bf16((float)(int8_t)((ww[j] >> 16) & 0xff) * sc, (float)(int8_t)(ww[j] >> 24) * sc);
             }
-            asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst + 32 * i), "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3]) : "memory");
-            asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst + 32 * i + 16), "r"(o[4]), "r"(o[5]), "r"(o[6]), "r"(o[7]) : "memory");
+            asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst + tile_off(tid, 16 * i)), "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3]) : "memory");
+            asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst + tile_off(tid, 16 * i + 8)), "r"(o[4]), "r"(o[5]), "r"(o[6]), "r"(o[7]) : "memory");
           }
         }
       }
     }
     __syncthreads();
     if (!okw || !active) continue;
+#pragma unroll 1
+    for (int sub = 0; sub < KW / KS; ++sub) {
+    const int kofs = ksl * KW + sub * KS;   // this warp's slice of the batch, this pass
+    if (kofs >= nk) break;
 
-    // ---- S = Q K^T for 128 keys: 16 n8 tiles x 8 k16 steps
-    float s[16][4];
+    // ---- S = Q K^T for this pass's keys: NJ n8 tiles x 8 k16 steps
+    float s[NJ][4];
 #pragma unroll
-    for (int j = 0; j < 16; ++j) {
+    for (int j = 0; j < NJ; ++j) {
       s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
 #pragma unroll
       for (int kk = 0; kk < 8; kk += 2) {
         uint32_t b0, b1, b2, b3;
         // matrices: (keys 8j.., d 16kk..), (d 16kk + 8..), (d 16(kk+1)..), (d 16(kk+1) + 8..)
-        ldsm_x4(ks + (8 * j + (lane & 7)) * ROWB + (16 * kk + 8 * (lane >> 3)) * 2, b0, b1, b2, b3);
+        ldsm_x4(ks + tile_off(kofs + 8 * j + (lane & 7), 16 * kk + 8 * (lane >> 3)), b0, b1, b2, b3);
         mma_bf16_16816(s[j], qa[kk][0], qa[kk][1], qa[kk][2], qa[kk][3], b0, b1);
         mma_bf16_16816(s[j], qa[kk + 1][0], qa[kk + 1][1], qa[kk + 1][2], qa[kk + 1][3], b2, b3);
       }
@@ -217,10 +237,10 @@ __global__ void __launch_bounds__(kThreads) attn_rows_kernel(const AttnRowsParam
     // ---- scale, causal mask per row, online softmax (rows g and g + 8 of the tile)
     float mnew[2] = {mx[0], mx[1]};
 #pragma unroll
-    for (int j = 0; j < 16; ++j)
+    for (int j = 0; j < NJ; ++j)
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
-        const int key = kb0 + 8 * j + 2 * t + (e & 1);
+        const int key = kb0 + kofs + 8 * j + 2 * t + (e & 1);
         const int hf = e >> 1;
         const float v = key < ctx[hf] && key < key1 ? s[j][e] * p.scale_log2 : -INFINITY;
         s[j][e] = v;
@@ -243,7 +263,7 @@ __global__ void __launch_bounds__(kThreads) attn_rows_kernel(const AttnRowsParam
       o[j][0] *= corr[0]; o[j][1] *= corr[0]; o[j][2] *= corr[1]; o[j][3] *= corr[1];
     }
 #pragma unroll
-    for (int j = 0; j < 16; ++j)
+    for (int j = 0; j < NJ; ++j)
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const int hf = e >> 1;
@@ -251,9 +271,9 @@ __global__ void __launch_bounds__(kThreads) attn_rows_kernel(const AttnRowsParam
         s[j][e] = pe;
         lsum[hf] += pe;
       }
-    // ---- O += P V: 8 k16 steps over the keys, 16 n8 tiles over d
+    // ---- O += P V: NJ / 2 k16 steps over this warp's keys, 16 n8 tiles over d
 #pragma unroll
-    for (int kk = 0; kk < 8; ++kk) {
+    for (int kk = 0; kk < NJ / 2; ++kk) {
       const uint32_t pa0 = pack_bf16(s[2 * kk][0], s[2 * kk][1]), pa1 = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
       const uint32_t pa2 = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]), pa3 = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
 #pragma unroll
@@ -261,11 +281,12 @@ __global__ void __launch_bounds__(kThreads) attn_rows_kernel(const AttnRowsParam
         uint32_t b0, b1, b2, b3;
         // matrices: (keys 16kk.., d 8jd..), (keys 16kk + 8.., d 8jd..), (keys 16kk.., d 8(jd+1)..), (keys + 8, d 8(jd+1)..)
         const int mi = lane >> 3;
-        ldsm_x4_trans(vs + (16 * kk + 8 * (mi & 1) + (lane & 7)) * ROWB + (8 * (jd + (mi >> 1))) * 2, b0, b1, b2, b3);
+        ldsm_x4_trans(vs + tile_off(kofs + 16 * kk + 8 * (mi & 1) + (lane & 7), 8 * (jd + (mi >> 1))), b0, b1, b2, b3);
         mma_bf16_16816(o[jd], pa0, pa1, pa2, pa3, b0, b1);
         mma_bf16_16816(o[jd + 1], pa0, pa1, pa2, pa3, b2, b3);
       }
     }
+    }  // pass
   }
 
   // ---- this split's partials: unnormalised O against the running maximum, (max, sum)
@@ -274,10 +295,53 @@ __global__ void __launch_bounds__(kThreads) attn_rows_kernel(const AttnRowsParam
     lsum[hf] += __shfl_xor_sync(0xffffffffu, lsum[hf], 1);
     lsum[hf] += __shfl_xor_sync(0xffffffffu, lsum[hf], 2);
   }
-  if (active) {
+  if (NKS > 1) {
+    // ---- the slices of a query row meet in shared memory (slice order), then one partial per row is written
+    constexpr int SROW = D + 4;   // O, maximum, sum, pad
+    __syncthreads();              // every warp is done with the K / V tiles
+    if (active) {
+#pragma unroll
+      for (int hf = 0; hf < 2; ++hf) {
+        float* dst = scratch + (size_t)(ksl * (NRG * 16) + rg * 16 + g + 8 * hf) * SROW;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) *reinterpret_cast<float2*>(dst + 8 * j + 2 * t) = make_float2(o[j][2 * hf], o[j][2 * hf + 1]);
+        if (t == 0) {
+          dst[D] = mx[hf];
+          dst[D + 1] = lsum[hf];
+        }
+      }
+    }
+    __syncthreads();
+    for (int i = tid; i < QR * (D / 4); i += kThreads) {
+      const int qr = i / (D / 4), d4 = (i % (D / 4)) * 4;
+      const float* src = scratch + (size_t)qr * SROW;
+      float mm = -INFINITY;
+#pragma unroll
+      for (int sl = 0; sl < NKS; ++sl) mm = fmaxf(mm, src[(size_t)sl * (NRG * 16) * SROW + D]);
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      float lt = 0.f;
+#pragma unroll
+      for (int sl = 0; sl < NKS; ++sl) {
+        const float* ss = src + (size_t)sl * (NRG * 16) * SROW;
+        const float ms = ss[D];
+        const float c = ms == -INFINITY ? 0.f : exp2f(ms - mm);
+        const float4 v = *reinterpret_cast<const float4*>(ss + d4);
+        lt = fmaf(ss[D + 1], c, lt);
+        acc.x = fmaf(v.x, c, acc.x); acc.y = fmaf(v.y, c, acc.y);
+        acc.z = fmaf(v.z, c, acc.z); acc.w = fmaf(v.w, c, acc.w);
+      }
+      const int m = z + qr / p.gqa, h = qr % p.gqa;
+      const size_t pb = ((size_t)m * p.n_q + kh * p.gqa + h) * p.nsplit + split;
+      *reinterpret_cast<float4*>(p.o_part + pb * D + d4) = acc;
+      if (d4 == 0) {
+        p.ml_part[pb * 2] = mm;
+        p.ml_part[pb * 2 + 1] = lt;
+      }
+    }
+  } else if (active) {
 #pragma unroll
     for (int hf = 0; hf < 2; ++hf) {
-      const int qr = warp * 16 + g + 8 * hf;
+      const int qr = rg * 16 + g + 8 * hf;
       if (qr < QR) {
         const int m = z + qr / p.gqa, h = qr % p.gqa;
         const size_t pb = ((size_t)m * p.n_q + kh * p.gqa + h) * p.nsplit + split;
@@ -344,6 +408,95 @@ __global__ void __launch_bounds__(kThreads) attn_rows_kernel(const AttnRowsParam
   }
 }
 
+template <bool I8>
+__global__ void __launch_bounds__(kThreads, 2) attn_rows_kernel(const __grid_constant__ AttnRowsParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ int s_last;
+  const int z = blockIdx.z, tid = threadIdx.x;
+  if (tid == 0) {   // the descriptors are launch parameters: their fetch overlaps the wait for the previous kernel
+    prefetch_tmap(&p.k_map);
+    prefetch_tmap(&p.v_map);
+  }
+  pdl_wait();
+  pdl_launch_dependents();
+  // ---- the group: consecutive rows of one request; this CTA is its leader or leaves.  The rows' request
+  // ids and positions are read once, in parallel, into shared memory.
+  __shared__ int s_req[64], s_pos[64], s_bt[kBtSmem];
+  if (tid < 64) {
+    s_req[tid] = tid < p.M ? p.ctrl[CTRL_ROW_REQ + tid] : -1;
+    s_pos[tid] = tid < p.M ? p.ctrl[CTRL_ROW_POS + tid] : 0;
+  }
+  __syncthreads();
+  const int req = s_req[z];
+  int gs = z;
+  while (gs > 0 && s_req[gs - 1] == req) --gs;
+  const int rmax = min(kMaxRows, 64 / p.gqa);
+  if ((z - gs) % rmax != 0) return;
+  int rows = 1;
+  while (rows < rmax && z + rows < p.M && s_req[z + rows] == req) ++rows;
+  const int QR = rows * p.gqa;
+  int ctx_max = 0;
+  for (int r = 0; r < rows; ++r) ctx_max = max(ctx_max, s_pos[z + r] + 1);
+  if (QR <= 16 && !p.one_slice)
+    attn_rows_body<I8, 4>(p, smem_raw, s_pos, &s_last, s_bt, req, rows, QR, ctx_max);
+  else if (QR <= 32 && !p.one_slice)
+    attn_rows_body<I8, 2>(p, smem_raw, s_pos, &s_last, s_bt, req, rows, QR, ctx_max);
+  else
+    attn_rows_body<I8, 1>(p, smem_raw, s_pos, &s_last, s_bt, req, rows, QR, ctx_max);
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return fn;
+}
+
+// A cache [rows][128 elements] as a 2-D tensor with boxes of 16 rows x 128 bytes (64 bf16 or 128 int8), 128-byte
+// swizzle.  The maps of a KV pool never change, so they are kept per (pointer, rows, form).
+struct MapKey {
+  const void* ptr; uint64_t rows; int i8;
+  bool operator==(const MapKey& o) const { return ptr == o.ptr && rows == o.rows && i8 == o.i8; }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& k) const { return std::hash<const void*>()(k.ptr) ^ (size_t)(k.rows * 0x9E3779B97F4A7C15ull) ^ (size_t)k.i8; }
+};
+int cache_map(CUtensorMap* out, const void* ptr, uint64_t rows, int i8) {
+  static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> maps;
+  static std::mutex mu;
+  std::lock_guard<std::mutex> lock(mu);
+  const MapKey key{ptr, rows, i8};
+  auto it = maps.find(key);
+  if (it != maps.end()) {
+    *out = it->second;
+    return 0;
+  }
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return -100;
+  const cuuint64_t esz = i8 ? 1 : 2;
+  cuuint64_t dims[2] = {(cuuint64_t)D, rows};
+  cuuint64_t strides[1] = {(cuuint64_t)D * esz};
+  cuuint32_t box[2] = {(cuuint32_t)(128 / esz), 16};
+  cuuint32_t estr[2] = {1, 1};
+  CUtensorMap m;
+  CUresult r = fn(&m, i8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr),
+                  dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return -101;
+  if (maps.size() > 8192) maps.clear();
+  maps.emplace(key, m);
+  *out = m;
+  return 0;
+}
+
 }  // namespace
 
 // Rows of a request that follow one another in the control block are served together.  bf16 KV, head size 128,
@@ -352,26 +505,36 @@ __global__ void __launch_bounds__(kThreads) attn_rows_kernel(const AttnRowsParam
 extern "C" int b2_attn_rows(const void* q, const void* k_cache, const void* v_cache, const float* k_scale,
                             const float* v_scale, int kv_int8, const int* block_table,
                             const int* ctrl, float* o_part, float* ml_part, void* out, int* tickets, int M, int n_q,
-                            int n_kv, int D_, int nsplit, int max_blocks, float scale, int span_pages, void* stream) {
-  if (D_ != D || nsplit < 1 || nsplit > 64 || n_q % n_kv != 0 || n_q / n_kv > 16 || M > 64) return -1;
+                            int n_kv, int D_, int nsplit, int max_blocks, float scale, int span_pages, int num_pages,
+                            void* stream) {
+  if (D_ != D || nsplit < 1 || nsplit > 64 || n_q % n_kv != 0 || n_q / n_kv > 16 || M > 64 || num_pages < 1) return -1;
+  if (((uintptr_t)k_cache | (uintptr_t)v_cache) & 15) return -4;
   AttnRowsParams p;
-  p.q = (const __nv_bfloat16*)q; p.k_cache = k_cache; p.v_cache = v_cache; p.k_scale = k_scale; p.v_scale = v_scale;
+  p.q = (const __nv_bfloat16*)q; p.k_scale = k_scale; p.v_scale = v_scale;
+  const uint64_t cache_rows = (uint64_t)num_pages * n_kv * 16;
+  int mrc = cache_map(&p.k_map, k_cache, cache_rows, kv_int8 ? 1 : 0);
+  if (mrc == 0) mrc = cache_map(&p.v_map, v_cache, cache_rows, kv_int8 ? 1 : 0);
+  if (mrc) return mrc;
   if (kv_int8 && (!k_scale || !v_scale)) return -3;
   p.block_table = block_table; p.ctrl = ctrl; p.o_part = o_part; p.ml_part = ml_part; p.out = (__nv_bfloat16*)out;
   p.tickets = tickets; p.M = M; p.n_q = n_q; p.n_kv = n_kv; p.gqa = n_q / n_kv; p.nsplit = nsplit; p.max_blocks = max_blocks;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.span_pages = span_pages;
+  p.one_slice = span_pages > 0 ? 1 : 0;   // fixed spans promise bits that do not depend on the group
   if (span_pages > 0 && (long)span_pages * nsplit < max_blocks) return -2;  // fixed spans must cover the longest sequence
-  // prefetch the next batch when a split holds more than two batches of keys (long contexts); short ones
-  // keep the small footprint that lets two CTAs share an SM
+  // Two CTAs per SM, each with one batch in flight, hide the copies as well as one CTA that prefetches (measured
+  // at depth 32768: 1.10 against 1.12 ms for 8 layers); the second tile pair pays only when the grid leaves SMs
+  // with a single CTA and a split holds several batches.  B2_ATTN_NBUF=1|2 overrides.
   const int pages_per_split = span_pages > 0 ? span_pages : (max_blocks + nsplit - 1) / nsplit;
-  p.nbuf = pages_per_split * 16 > 2 * KB ? 2 : 1;
-  const int smem = 128 + (kv_int8 ? 1 : p.nbuf) * 2 * KB * ROWB + 64 + (kv_int8 ? p.nbuf * 2 * KB * D : 0);
+  p.nbuf = (pages_per_split * 16 > 2 * KB && n_kv * nsplit * M <= 148) ? 2 : 1;
+  static const int nbuf_env = [] { const char* e = getenv("B2_ATTN_NBUF"); return e ? atoi(e) : 0; }();
+  if (nbuf_env == 1 || nbuf_env == 2) p.nbuf = nbuf_env;
+  const int smem = 1024 + (kv_int8 ? 1 : p.nbuf) * 2 * TILEB + 64 + (kv_int8 ? p.nbuf * 2 * KB * D : 0);
   static int configured[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   if (!configured[dev & 63]) {
-    const int most = 128 + 2 * 2 * KB * ROWB + 64 + 2 * 2 * KB * D;
+    const int most = 1024 + 2 * 2 * TILEB + 64;
     cudaError_t e = cudaFuncSetAttribute(attn_rows_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, most);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_rows_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, most);
     if (e != cudaSuccess) return (int)e;

@@ -464,14 +464,19 @@ __global__ void attn_merge_kernel(const float* o_part, const float* ml_part, __n
       cw[d] = c0 * inv;
       cw[d + 32] = c1 * inv;
     }
+    // the first 32 splits' values are requested before the weights are known: one round trip for both
+    float v0[32];
+#pragma unroll
+    for (int u = 0; u < 32; ++u) v0[u] = u < nsplit ? o_part[(base + u) * D + d] : 0.f;
     __syncthreads();
     float o = 0.f;
-    for (int s0 = 0; s0 < nsplit; s0 += 8) {
-      float v[8];
 #pragma unroll
-      for (int u = 0; u < 8; ++u) v[u] = s0 + u < nsplit ? o_part[(base + s0 + u) * D + d] : 0.f;
+    for (int u = 0; u < 32; ++u) o = fmaf(v0[u], u < nsplit ? cw[u] : 0.f, o);
+    if (nsplit > 32) {
 #pragma unroll
-      for (int u = 0; u < 8; ++u) o = fmaf(v[u], s0 + u < nsplit ? cw[s0 + u] : 0.f, o);
+      for (int u = 0; u < 32; ++u) v0[u] = 32 + u < nsplit ? o_part[(base + 32 + u) * D + d] : 0.f;
+#pragma unroll
+      for (int u = 0; u < 32; ++u) o = fmaf(v0[u], 32 + u < nsplit ? cw[32 + u] : 0.f, o);
     }
     out[((size_t)m * n_q + h) * D + d] = __float2bfloat16(o);
     return;

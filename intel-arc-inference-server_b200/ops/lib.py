@@ -184,7 +184,7 @@ def attn_rows(q, k_cache, v_cache, block_table, ctrl, o_part, ml_part, out, tick
     rc = lib().b2_attn_rows(_p(q), _p(k_cache), _p(v_cache), _p(k_scale), _p(v_scale), 1 if kv_int8 else 0,
                             _p(block_table), _p(ctrl), _p(o_part), _p(ml_part),
                             _p(out), _p(tickets), m, n_q, n_kv, d, nsplit, max_blocks, ctypes.c_float(scale), span_pages,
-                            _stream())
+                            k_cache.numel() // (n_kv * 16 * d), _stream())
     _check(rc, "attn_rows")
     if tickets is None:     # many rows: the merge is its own launch, one CTA per row and head
         rc = lib().b2_attn_merge(_p(o_part), _p(ml_part), _p(out), m, n_q, nsplit, d, _stream())

@@ -140,7 +140,7 @@ def bench_decode(cfg: ModelConfig, mode: str, depth: int, steps: int, warmup: in
     dev = torch.device("cuda", torch.cuda.current_device())
     w = random_weights(cfg, device=dev, seed=0, exact=False) if world == 1 else random_shard(cfg, rank, world, dev)
     total = depth + 2 * (steps + warmup) + 64
-    eng = make_engine(w, mode=mode, max_seqs=rows, max_len=total, nsplit_attn=max(4, min(64, depth // 128)))
+    eng = make_engine(w, mode=mode, max_seqs=rows, max_len=total)
     local = eng.cfg
     for layer in range(local.n_layers):   # context at depth: random KV pages (the timing needs the reads only)
         kc, vc, _, _ = eng.kv.layer(layer)

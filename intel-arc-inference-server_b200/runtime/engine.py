@@ -18,7 +18,7 @@ import numpy as np
 import torch
 
 from ..models.config import ModelConfig
-from ..models.decoder import DecoderModel, KVCache
+from ..models.decoder import DecoderModel, KVCache, attn_splits
 from ..models.weights import ModelWeights
 from ..ops import lib as K
 from .kv_pool import KvPool
@@ -36,7 +36,7 @@ class Row:
 class Engine:
     def __init__(self, weights: ModelWeights, max_seqs: int = 1, max_len: int = 4096, kv_dtype: str = "bf16",
                  max_rows: int = 64, use_graphs: bool = True, int8_head: bool = False, num_pages: Optional[int] = None,
-                 nsplit_attn: int = 32, prefill_backend: str = "auto", tp=None, nccl=None,
+                 nsplit_attn: int = 0, prefill_backend: str = "auto", tp=None, nccl=None,
                  extra_kv_layers: int = 0):
         """``tp``: wires of a tensor-parallel group; every rank builds the same Engine over its weight shard and
         is driven with the same calls (same rows, same order) -- the step's kernels do the crossings."""
@@ -47,6 +47,8 @@ class Engine:
         self.max_blocks = (max_len + PAGE - 1) // PAGE
         if num_pages is None:
             num_pages = max_seqs * self.max_blocks + 1
+        if not nsplit_attn:     # sized for contexts near the longest one the engine holds
+            nsplit_attn = attn_splits(cfg.n_kv_heads, max_len)
         self.model = DecoderModel(weights, max_rows=max_rows, max_pos=max_len, nsplit_attn=nsplit_attn,
                                   int8_head=int8_head, tp=self.tp, nccl=nccl)
         self.kv = KVCache(cfg, cfg.n_layers + extra_kv_layers, num_pages, self.device, kv_dtype)   # + draft-head layers

@@ -24,8 +24,7 @@ def run_decode_bench(args, barrier) -> dict:
     weights = random_weights(cfg, device=dev, seed=0, exact=False)
     total = args.depth + 2 * (args.steps + args.warmup) + 64
     eng = Engine(weights, max_seqs=1, max_len=total, kv_dtype=args.kv_cache, int8_head=args.int8_head,
-                 prefill_backend=args.prefill_backend,
-                 nsplit_attn=max(4, min(64, args.depth // 128)))
+                 prefill_backend=args.prefill_backend)
     g = torch.Generator().manual_seed(0)
     ids = torch.randint(0, cfg.vocab, (args.depth,), generator=g).tolist()
     first = eng.prefill(0, ids)
@@ -120,8 +119,7 @@ def run_spec_bench(args, barrier, iters: int = 12) -> dict:
     g = torch.Generator().manual_seed(0)
     ids = torch.randint(0, cfg.vocab - 1, (depth,), generator=g).tolist()
     for kind, k, accepts, dv in (("mtp", 3, (0, 3), 0), ("mtp", 3, (3,), 32768), ("dflash", 7, (0, 3, 7), 0)):
-        eng = Engine(weights, max_seqs=1, max_len=depth + 64 * (iters + 4) + 64, extra_kv_layers=2,
-                     nsplit_attn=max(4, min(64, depth // 128)))
+        eng = Engine(weights, max_seqs=1, max_len=depth + 64 * (iters + 4) + 64, extra_kv_layers=2)
         ad = SpecAdapter(EngineAdapter(eng), kind, k, draft_vocab=dv)
         pending = ad.prefill(0, ids)
         for acc in accepts:

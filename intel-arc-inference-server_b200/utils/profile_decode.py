@@ -23,7 +23,7 @@ def main():
     ap.add_argument("--rows", type=int, default=1)
     ap.add_argument("--kv-cache", default="bf16")
     ap.add_argument("--graphs", action="store_true")
-    ap.add_argument("--nsplit", type=int, default=0, help="KV splits of the decode attention (0: depth / 128, 4..64)")
+    ap.add_argument("--nsplit", type=int, default=0, help="KV splits of the decode attention (0: chosen from the KV heads and the depth)")
     ap.add_argument("--time", action="store_true", help="print CUDA-event ms per step")
     args = ap.parse_args()
     from ..models.config import preset
@@ -33,7 +33,7 @@ def main():
     cfg = replace(preset(args.model), n_layers=args.layers)
     w = random_weights(cfg, device="cuda", seed=0, exact=False)
     eng = Engine(w, max_seqs=1, max_len=args.depth + 256, kv_dtype=args.kv_cache, use_graphs=args.graphs,
-                 nsplit_attn=args.nsplit or max(4, min(64, args.depth // 128)))
+                 nsplit_attn=args.nsplit)
     if args.kv_cache == "bf16":
         eng.kv.k.normal_(0, 0.5); eng.kv.v.normal_(0, 0.5)
     eng._ensure_pages(0, args.depth)
