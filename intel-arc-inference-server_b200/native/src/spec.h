@@ -80,7 +80,9 @@ inline void apply_repetition_penalty(float* logits, uint32_t vocab_used, const s
   }
 }
 
-inline double uniform01(std::mt19937_64& rng) { return std::generate_canonical<double, 53>(rng); }
+// 53 random bits as a double in [0, 1): spelled out so that the device sampler (ops/csrc/sampler.cu) draws the
+// same number from the same seed whatever the standard library does in generate_canonical.
+inline double uniform01(std::mt19937_64& rng) { return (double)(rng() >> 11) * (1.0 / 9007199254740992.0); }
 
 inline uint32_t draw(const FilteredProbs& f, std::mt19937_64& rng) {
   const double u = uniform01(rng) * f.mass;

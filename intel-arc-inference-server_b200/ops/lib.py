@@ -17,7 +17,7 @@ import torch
 from . import build as _build
 
 _lib: Optional[ctypes.CDLL] = None
-_UNITS = ("gemv", "decode", "gemm", "attn", "attnrows", "moe", "comm", "ep", "spec")
+_UNITS = ("gemv", "decode", "gemm", "attn", "attnrows", "moe", "comm", "ep", "spec", "sampler")
 
 # Control block layout (int32 words) -- mirrors decode_ops.cu
 CTRL_N_ROWS = 0
@@ -189,6 +189,17 @@ def attn_rows(q, k_cache, v_cache, block_table, ctrl, o_part, ml_part, out, tick
     if tickets is None:     # many rows: the merge is its own launch, one CTA per row and head
         rc = lib().b2_attn_merge(_p(o_part), _p(ml_part), _p(out), m, n_q, nsplit, d, _stream())
         _check(rc, "attn_merge")
+
+
+def sample_rows(logits, m, n_valid, temperature, top_k, top_p, seed, token, status, penalty=None, hist=None,
+                hist_len=None, kept=None):
+    """One token per row of ``logits`` [m][ld] by the host sampler's rule (temperature, top-k, top-p, optional
+    repetition penalty over ``hist`` [m][cap] ids, ``seed`` uint64 per row as int64 storage).  ``status[i] = 1``
+    marks a row that must be sampled on the host (filtered set wider than 1024 candidates)."""
+    rc = lib().b2_sample_rows(_p(logits), m, logits.stride(0) if logits.dim() == 2 else logits.numel() // m, n_valid,
+                              _p(temperature), _p(top_k), _p(top_p), _p(seed), _p(penalty), _p(hist), _p(hist_len),
+                              hist.shape[1] if hist is not None else 0, _p(token), _p(status), _p(kept), _stream())
+    _check(rc, "sample_rows")
 
 
 def kv_convert(k16, v16, table16, k8, v8, ks, vs, table8, pos0, tokens, n_kv, d, to_int8: bool):

@@ -175,6 +175,10 @@ class SpecAdapter:
     def kv_form(self): return self.inner.kv_form()
     def logits(self, slot, row=0): return self.inner.logits(slot, row)
 
+    def sample(self, *args, **kw):
+        fn = getattr(self.inner, "sample", None)
+        return fn(*args, **kw) if fn is not None else None
+
     def prefill(self, slot, ids):
         tok = self.inner.prefill(slot, ids)
         n = self.e.seq_len[slot]

@@ -201,18 +201,28 @@ class Server:
             if self.prefix:
                 self.prefix.after_prefill(s.slot, s.prompt_ids)
             if not s.req.greedy:
-                tok = self._sample(s, self.engine.logits(s.slot, 0))
+                tok = self._sample(s)
             s.t_first = time.time()
             self._emit_token(s, tok)       # the first token goes out before the first decode step
 
-    def _sample(self, s: Session, logits: np.ndarray) -> int:
+    def _sample(self, s: Session, logits=None, row: int = 0) -> int:
+        """The request's next token from its logits row: on the device when the engine has a sampler (only the
+        token comes back), else -- or when the kernel leaves the row to the host -- over the logits read back."""
         r = s.req
+        seed = (s.rng_seed * 1000003 + len(s.out_ids)) & 0xFFFFFFFFFFFFFFFF
+        dev = getattr(self.engine, "sample", None) if logits is None else None
+        if dev is not None:
+            tok = dev(s.slot, row, 0.0 if r.greedy else r.temperature, r.top_k, r.top_p, seed, r.repetition_penalty,
+                      s.prompt_ids + s.out_ids if r.repetition_penalty != 1.0 else ())
+            if tok is not None:
+                return int(tok)
+        if logits is None:
+            logits = self.engine.logits(s.slot, row)
         lg = np.array(logits, dtype=np.float32, copy=True)
         if r.repetition_penalty != 1.0:
             H.apply_repetition_penalty(lg, self.engine.vocab_size, s.prompt_ids + s.out_ids, r.repetition_penalty)
         if r.greedy:
             return int(H.argmax_low_tie(lg, self.engine.vocab_size))
-        seed = (s.rng_seed * 1000003 + len(s.out_ids)) & 0xFFFFFFFFFFFFFFFF
         return int(H.sample(lg, self.engine.vocab_size, r.temperature, r.top_k, r.top_p, seed))
 
     def _decode(self, a):
@@ -244,7 +254,7 @@ class Server:
                 acc, nxt = H.accept_point_mass(p_rows, drafts, self.engine.vocab_size, s.req.temperature,
                                                s.req.top_k, s.req.top_p, seed)
             else:
-                acc, nxt = 0, (self._sample(s, self.engine.logits(slot, 0)) if host_rule else out[0])
+                acc, nxt = 0, (self._sample(s) if host_rule else out[0])
             if acc < len(drafts):       # rejected rows leave the cache
                 self.engine.truncate(slot, self.engine.length(slot) - (len(drafts) - acc))
             emitted = 0
