@@ -43,6 +43,11 @@ class ModelConfig:
     mtp_layers: int = 0
     architecture: str = "B200DenseForCausalLM"
     page_size: int = 16
+    # sliding-window attention: a row attends to its last ``sliding_window`` positions (0: the whole context);
+    # with ``full_attn_every`` = n > 0 every n-th layer (li % n == n - 1) keeps full attention, as in the
+    # reference's windowed families (src/kernels/kolibri/kol_attn.cl: sliding ring 4096 / full layers)
+    sliding_window: int = 0
+    full_attn_every: int = 0
 
     @property
     def q_dim(self) -> int:
@@ -63,6 +68,14 @@ class ModelConfig:
     @property
     def is_moe(self) -> bool:
         return self.n_experts > 0
+
+    def window_of(self, li: int) -> int:
+        """Attention window of layer ``li`` in positions (0: full attention)."""
+        if self.sliding_window <= 0:
+            return 0
+        if self.full_attn_every > 0 and li % self.full_attn_every == self.full_attn_every - 1:
+            return 0
+        return self.sliding_window
 
     def tp_shard(self, world: int) -> "ModelConfig":
         """The shapes one rank of a ``world``-way tensor-parallel group holds: whole attention heads,
@@ -141,6 +154,8 @@ class ModelConfig:
             "moe_intermediate_size": self.expert_ffn,
             "shared_expert_intermediate_size": self.shared_ffn,
             "mtp_num_hidden_layers": self.mtp_layers,
+            "sliding_window": self.sliding_window or None,
+            "full_attention_interval": self.full_attn_every,
             "torch_dtype": "bfloat16",
             "quantization_config": {
                 "bits": 4, "group_size": self.group_size, "sym": True, "desc_act": False,
@@ -164,6 +179,7 @@ class ModelConfig:
             expert_ffn=d.get("moe_intermediate_size", 0) or 0,
             shared_ffn=d.get("shared_expert_intermediate_size", 0) or 0,
             mtp_layers=d.get("mtp_num_hidden_layers", 0) or 0,
+            sliding_window=d.get("sliding_window", 0) or 0, full_attn_every=d.get("full_attention_interval", 0) or 0,
             architecture=(d.get("architectures") or ["B200DenseForCausalLM"])[0],
         )
 
@@ -176,6 +192,11 @@ def tiny_dense() -> ModelConfig:
 def small_dense() -> ModelConfig:
     """Small dense model with the production head size (128), for the tensor-core prefill path."""
     return ModelConfig("small-dense", 2, 512, 8, 2, 128, 1408, 2048)
+
+
+def small_windowed() -> ModelConfig:
+    """Four layers of the small dense shape; layers 0 and 2 attend to the last 48 positions, 1 and 3 to all."""
+    return ModelConfig("small-windowed", 4, 512, 8, 2, 128, 1408, 2048, sliding_window=48, full_attn_every=2)
 
 
 def tiny_moe() -> ModelConfig:
@@ -208,7 +229,7 @@ def dflash_drafter(target: ModelConfig) -> ModelConfig:
 
 
 PRESETS = {
-    "tiny-dense": tiny_dense, "tiny-moe": tiny_moe, "small-dense": small_dense, "small-moe": small_moe, "dense-27b": dense_27b, "moe-35b-a3b": moe_35b_a3b,
+    "tiny-dense": tiny_dense, "tiny-moe": tiny_moe, "small-dense": small_dense, "small-windowed": small_windowed, "small-moe": small_moe, "dense-27b": dense_27b, "moe-35b-a3b": moe_35b_a3b,
 }
 
 

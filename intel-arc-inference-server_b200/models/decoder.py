@@ -161,7 +161,7 @@ class DecoderModel:
             K.gemv_w4(ql.w4b, x, part, m, ql.n, ql.k, s, x_mode=x_mode, s_in=s_in, x_slice=x_slice)
         return part, s
 
-    def _attention(self, m: int, ctrl, block_table, max_blocks, kv: KVCache, kc, vc, ks, vs):
+    def _attention(self, m: int, ctrl, block_table, max_blocks, kv: KVCache, kc, vc, ks, vs, window: int = 0):
         """Split-KV attention of the step's rows into ``buf.attn_out``.  bf16 KV with head size 128 goes to the
         tensor-core kernel that serves a request's consecutive rows together; the rest to the per-row kernel."""
         cfg, b = self.cfg, self.buf
@@ -171,11 +171,16 @@ class DecoderModel:
                         m, cfg.n_q_heads,
                         cfg.n_kv_heads, cfg.head_dim, self.nsplit_attn, max_blocks, self.scale,
                         span_pages=(max_blocks + self.nsplit_attn - 1) // self.nsplit_attn if self.attn_fixed_spans else 0,
-                        k_scale=ks, v_scale=vs, kv_int8=kv.kv_int8)
+                        k_scale=ks, v_scale=vs, kv_int8=kv.kv_int8, window=window)
         else:
+            if window > 0:
+                raise NotImplementedError("sliding-window layers need the multi-row attention kernel (head size 128)")
             K.attn_decode(b.q, kc, vc, block_table, ctrl, b.o_part, b.ml_part, b.attn_out, m, cfg.n_q_heads,
                           cfg.n_kv_heads, cfg.head_dim, self.nsplit_attn, max_blocks, self.scale, ks, vs, kv.kv_int8,
                           tickets=b.tickets)
+
+    def _window(self, li: int) -> int:
+        return self.cfg.window_of(li) if li < self.cfg.n_layers else 0   # draft-head layers: the whole context
 
     def attention_block(self, lw: LayerWeights, li: int, m: int, ctrl, block_table, max_blocks, kv: KVCache):
         cfg, b = self.cfg, self.buf
@@ -183,7 +188,7 @@ class DecoderModel:
         kc, vc, ks, vs = kv.layer(li)
         K.rope_append(part, m * cfg.qkv_dim, s, m, ctrl, block_table, max_blocks, self.cos_t, self.sin_t,
                       cfg.n_q_heads, cfg.n_kv_heads, cfg.head_dim, b.q, kc, vc, ks, vs, kv.kv_int8)
-        self._attention(m, ctrl, block_table, max_blocks, kv, kc, vc, ks, vs)
+        self._attention(m, ctrl, block_table, max_blocks, kv, kc, vc, ks, vs, self._window(li))
         return self._gemv("o", lw.o, b.attn_out, m)
 
     def ffn_block(self, lw: LayerWeights, m: int):
@@ -227,7 +232,7 @@ class DecoderModel:
         kc, vc, ks, vs = kv.layer(li)
         K.rope_append(part, m * cfg.qkv_dim, s, m, ctrl, block_table, max_blocks, self.cos_t, self.sin_t,
                       cfg.n_q_heads, cfg.n_kv_heads, cfg.head_dim, b.q, kc, vc, ks, vs, kv.kv_int8)
-        self._attention(m, ctrl, block_table, max_blocks, kv, kc, vc, ks, vs)
+        self._attention(m, ctrl, block_table, max_blocks, kv, kc, vc, ks, vs, self._window(li))
         self._gemv_fused("o", lw.o, b.attn_out, m, fold=True)
         gu, s_gu = self._gemv_fused("gate_up", lw.gate_up, b.resid, m, norm_w=lw.post_norm, x_mode=2)
         self._gemv_fused("down", lw.down, gu, m, fold=True, x_mode=1, s_in=s_gu, x_slice=m * 2 * cfg.ffn)

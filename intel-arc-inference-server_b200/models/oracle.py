@@ -111,6 +111,9 @@ class OracleModel:
         scores = torch.einsum("thd,shd->hts", q, kk) / math.sqrt(c.head_dim)
         key_pos = torch.arange(s_len)
         mask = key_pos[None, :] > pos[:, None]
+        win = c.window_of(li) if li < c.n_layers else 0      # draft-head layers attend to the whole context
+        if win > 0:
+            mask = mask | (key_pos[None, :] <= pos[:, None] - win)
         scores = scores.masked_fill(mask[None], float("-inf"))
         p = F.softmax(scores, dim=-1)
         o = torch.einsum("hts,shd->thd", p, vv).reshape(t, c.q_dim)

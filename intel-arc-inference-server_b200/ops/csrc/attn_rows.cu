@@ -54,6 +54,7 @@ struct AttnRowsParams {
   int* tickets;        // [M][n_kv]
   int M, n_q, n_kv, gqa, nsplit, max_blocks;
   int nbuf;        // 1: one K / V tile pair; 2: the next batch of keys is fetched while this one is multiplied
+  int window;      // > 0: a row attends to its last `window` positions only (sliding-window layers)
   int one_slice;   // 1: never cut a batch's keys over idle warps (a row's bits then do not depend on the group's size)
   int span_pages;  // > 0: every split covers this many pages whatever the context (a row's bits then do not depend
                    // on which rows share its CTA); 0: the group's context is cut into nsplit equal parts
@@ -94,11 +95,21 @@ __device__ __forceinline__ void attn_rows_body(const AttnRowsParams& p, uint8_t*
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
   const int rg = warp % NRG, ksl = warp / NRG;
   const int total_pages = (ctx_max + 15) >> 4;
-  const int pps = p.span_pages > 0 ? p.span_pages : (total_pages + p.nsplit - 1) / p.nsplit;
-  const int key0 = split * pps * 16, key1 = min(ctx_max, (split + 1) * pps * 16);
-  const int* btg = p.block_table + (size_t)req * p.max_blocks + split * pps;
+  // sliding window: pages before the first row's window are never read
+  const int page0 = p.window > 0 ? max(0, s_pos[z] + 1 - p.window) >> 4 : 0;
+  int pps, key0, key1;
+  if (p.span_pages > 0) {   // fixed spans of absolute pages, cut at the window
+    pps = p.span_pages;
+    key0 = max(split * pps, page0) * 16;
+    key1 = min(ctx_max, (split + 1) * pps * 16);
+  } else {                  // the pages from the window's first one on, in nsplit equal parts
+    pps = (total_pages - page0 + p.nsplit - 1) / p.nsplit;
+    key0 = (page0 + split * pps) * 16;
+    key1 = min(ctx_max, key0 + pps * 16);
+  }
+  const int* btg = p.block_table + (size_t)req * p.max_blocks + (key0 >> 4);
   // the split's page ids once, so that a batch's copies do not wait for a table load
-  const int npg = min(pps, max(total_pages - split * pps, 0));
+  const int npg = max(key1 - key0 + 15, 0) >> 4;
   const bool bt_smem = npg <= kBtSmem;
   if (bt_smem)
     for (int i = tid; i < npg; i += kThreads) s_bt[i] = btg[i];
@@ -113,7 +124,7 @@ __device__ __forceinline__ void attn_rows_body(const AttnRowsParams& p, uint8_t*
 
   // ---- this warp's 16 query rows: (token row, head) of rows g and g + 8, their contexts, Q fragments
   const bool active = rg * 16 < QR;
-  int ctx[2] = {0, 0};
+  int ctx[2] = {0, 0}, wlo[2] = {0, 0};   // a row's keys: wlo <= key < ctx
   uint32_t qa[8][4];
 #pragma unroll
   for (int hf = 0; hf < 2; ++hf) {
@@ -121,6 +132,7 @@ __device__ __forceinline__ void attn_rows_body(const AttnRowsParams& p, uint8_t*
     const bool ok = qr < QR;
     const int m = z + (ok ? qr / p.gqa : 0), h = ok ? qr % p.gqa : 0;
     ctx[hf] = ok ? s_pos[m] + 1 : 0;
+    wlo[hf] = p.window > 0 ? ctx[hf] - p.window : 0;
     const __nv_bfloat16* qp = p.q + (size_t)m * p.n_q * D + (size_t)(kh * p.gqa + h) * D;
 #pragma unroll
     for (int kk = 0; kk < 8; ++kk) {
@@ -242,7 +254,7 @@ __device__ __forceinline__ void attn_rows_body(const AttnRowsParams& p, uint8_t*
       for (int e = 0; e < 4; ++e) {
         const int key = kb0 + kofs + 8 * j + 2 * t + (e & 1);
         const int hf = e >> 1;
-        const float v = key < ctx[hf] && key < key1 ? s[j][e] * p.scale_log2 : -INFINITY;
+        const float v = key < ctx[hf] && key < key1 && key >= wlo[hf] ? s[j][e] * p.scale_log2 : -INFINITY;
         s[j][e] = v;
         mnew[hf] = fmaxf(mnew[hf], v);
       }
@@ -506,7 +518,7 @@ extern "C" int b2_attn_rows(const void* q, const void* k_cache, const void* v_ca
                             const float* v_scale, int kv_int8, const int* block_table,
                             const int* ctrl, float* o_part, float* ml_part, void* out, int* tickets, int M, int n_q,
                             int n_kv, int D_, int nsplit, int max_blocks, float scale, int span_pages, int num_pages,
-                            void* stream) {
+                            int window, void* stream) {
   if (D_ != D || nsplit < 1 || nsplit > 64 || n_q % n_kv != 0 || n_q / n_kv > 16 || M > 64 || num_pages < 1) return -1;
   if (((uintptr_t)k_cache | (uintptr_t)v_cache) & 15) return -4;
   AttnRowsParams p;
@@ -520,6 +532,7 @@ extern "C" int b2_attn_rows(const void* q, const void* k_cache, const void* v_ca
   p.tickets = tickets; p.M = M; p.n_q = n_q; p.n_kv = n_kv; p.gqa = n_q / n_kv; p.nsplit = nsplit; p.max_blocks = max_blocks;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.span_pages = span_pages;
+  p.window = window > 0 ? window : 0;
   p.one_slice = span_pages > 0 ? 1 : 0;   // fixed spans promise bits that do not depend on the group
   if (span_pages > 0 && (long)span_pages * nsplit < max_blocks) return -2;  // fixed spans must cover the longest sequence
   // Two CTAs per SM, each with one batch in flight, hide the copies as well as one CTA that prefetches (measured

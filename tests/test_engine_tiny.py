@@ -35,9 +35,9 @@ def _to_cuda(w):
     return mv(w)
 
 
-def _check_generate(use_graphs, kv_dtype, margin_tol):
+def _check_generate(use_graphs, kv_dtype, margin_tol, cfg=None):
     from b200serve.runtime.engine import Engine, Row
-    cfg = tiny_dense()
+    cfg = cfg or tiny_dense()
     w = random_weights(cfg, seed=0)
     oracle = OracleModel(w)
     g = torch.Generator().manual_seed(0)
@@ -60,6 +60,14 @@ def _check_generate(use_graphs, kv_dtype, margin_tol):
         logits = oracle.forward(torch.tensor([t]), kv, 128 + i)[0]
     assert undetermined <= 3
     return eng, oracle, prompt, toks
+
+
+def test_sliding_window_model_matches_oracle():
+    """Layers 0 and 2 attend to the last 48 positions, 1 and 3 to everything; the 128-token prompt goes through
+    the row kernels (the tcgen05 prompt attention has no window)."""
+    from b200serve.models.config import preset
+    _check_generate(True, "bf16", 0.03, cfg=preset("small-windowed"))
+    _check_generate(False, "int8", 0.08, cfg=preset("small-windowed"))
 
 
 def test_tiny_dense_greedy_matches_oracle_eager():

@@ -359,6 +359,47 @@ def test_attn_rows_matches_per_row_kernel(n_q, n_kv, rows, ctx, nsplit):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("window,fixed", [(40, False), (300, False), (300, True), (5000, False)])
+def test_attn_rows_sliding_window_matches_fp32(window, fixed):
+    """Sliding-window layers: every row attends to its last ``window`` positions; pages before the first row's
+    window are not read.  Compared with an fp32 softmax over the gathered pages."""
+    k_ = K()
+    torch.manual_seed(window)
+    n_q, n_kv, d, ctx, nsplit = 8, 2, 128, 1100, 6
+    max_blocks = (ctx + 15) // 16 + 2
+    num_pages = 2 * max_blocks + 2
+    table = torch.zeros(2, max_blocks, dtype=torch.int32)
+    perm = torch.randperm(num_pages - 1) + 1
+    table[0] = perm[:max_blocks].to(torch.int32)
+    table[1] = perm[max_blocks: 2 * max_blocks].to(torch.int32)
+    kc = (torch.randn(num_pages, n_kv, 16, d) * 0.5).to(torch.bfloat16)
+    vc = (torch.randn(num_pages, n_kv, 16, d) * 0.5).to(torch.bfloat16)
+    spec = [(0, ctx - 5 + i, 0) for i in range(5)] + [(1, 17, 0)] + [(1, 600 + i, 0) for i in range(3)]
+    m = len(spec)
+    q = torch.randn(m, n_q * d).to(torch.bfloat16)
+    ref = torch.zeros(m, n_q, d)
+    for i, (req, pos, _) in enumerate(spec):
+        lo = max(0, pos + 1 - window)
+        keys = torch.arange(lo, pos + 1)
+        pg, sl = table[req][keys // 16].long(), keys % 16
+        for h in range(n_q):
+            kk, vv = kc[pg, h // (n_q // n_kv), sl].float(), vc[pg, h // (n_q // n_kv), sl].float()
+            p = torch.softmax(kk @ q[i, h * d:(h + 1) * d].float() * d ** -0.5, dim=0)
+            ref[i, h] = p @ vv
+    ctrl = _ctrl(spec)
+    o_part = torch.full((m * n_q * nsplit * d,), float("nan"), device="cuda")
+    ml = torch.zeros(m * n_q * nsplit * 2, device="cuda")
+    out = torch.full((m, n_q * d), float("nan"), dtype=torch.bfloat16, device="cuda")
+    k_.attn_rows(q.cuda(), kc.cuda(), vc.cuda(), table.cuda(), ctrl, o_part, ml, out, None, m, n_q, n_kv, d, nsplit,
+                 max_blocks, d ** -0.5, span_pages=(max_blocks + nsplit - 1) // nsplit if fixed else 0, window=window)
+    torch.cuda.synchronize()
+    k_.check_status()
+    err = (out.float().cpu().view(m, n_q, d) - ref).abs().max()
+    assert not torch.isnan(out.float()).any()
+    assert err <= 2e-2 * ref.abs().max() + 2e-3, float(err)
+
+
+@pytest.mark.gpu
 def test_attn_rows_int8_kv_matches_per_row_kernel():
     k_ = K()
     torch.manual_seed(77)

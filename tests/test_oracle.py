@@ -56,3 +56,25 @@ def test_dense_incremental_equals_full():
 
 def test_moe_incremental_equals_full():
     _consistency(tiny_moe())
+
+
+def test_sliding_window_layers_and_config_round_trip():
+    import dataclasses
+    from b200serve.models.config import ModelConfig
+    cfg = dataclasses.replace(tiny_dense(), n_layers=4, sliding_window=8, full_attn_every=2)
+    assert [cfg.window_of(i) for i in range(4)] == [8, 0, 8, 0]
+    assert dataclasses.replace(cfg, full_attn_every=0).window_of(1) == 8
+    back = ModelConfig.from_hf_config(cfg.to_hf_config())
+    assert back.sliding_window == 8 and back.full_attn_every == 2
+    assert ModelConfig.from_hf_config(tiny_dense().to_hf_config()).sliding_window == 0
+    _consistency(cfg)       # incremental and chunked passes see the same windows as one pass
+    # the window changes the result once the context is longer than it, and not before
+    w = random_weights(cfg)
+    full = dataclasses.replace(cfg, sliding_window=0)
+    w_full = dataclasses.replace(w, cfg=full) if dataclasses.is_dataclass(w) else None
+    if w_full is not None:
+        g = torch.Generator().manual_seed(1)
+        ids = torch.randint(0, cfg.vocab, (20,), generator=g)
+        a, b = OracleModel(w).forward(ids), OracleModel(w_full).forward(ids)
+        assert (a[:8] - b[:8]).abs().max() < 1e-5
+        assert (a[12:] - b[12:]).abs().max() > 1e-4
