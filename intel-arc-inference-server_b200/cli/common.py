@@ -28,6 +28,15 @@ def hardware_gate(min_devices: int = 1, out=sys.stderr):
             for j in range(min_devices):
                 if i != j and not torch.cuda.can_device_access_peer(i, j):
                     raise SystemExit(f"GPU {i} cannot access GPU {j} peer to peer")
+    try:    # memory, BAR1 and NVLink report (read-only NVML queries); a warning, never a refusal
+        from ..utils import vram
+        gpus = vram.probe(indices=list(range(min_devices)))
+        for line in vram.describe(gpus):
+            out.write(line + "\n")
+        for problem in vram.check_placement(gpus, need_nvlink=min_devices > 1):
+            out.write(f"warning: {problem}: the fused collective kernels will run over PCIe\n")
+    except Exception as e:  # noqa: BLE001   (no NVML in the container)
+        out.write(f"memory: NVML probe unavailable ({type(e).__name__})\n")
 
 
 def load_model(spec: str, device, seed: int = 0, int8_head: bool = False, tp=(0, 1)):

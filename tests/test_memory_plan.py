@@ -32,3 +32,49 @@ def test_tp_and_moe_shrink_per_gpu_bytes():
     with pytest.raises(ValueError):
         plan(moe, 16, 131072 + 64)      # the same in bf16 does not fit one GPU
     assert plan(tiny_dense(), 2, 512).num_pages == 2 * 32 + 1
+
+
+def test_vram_probe_with_fake_nvml():
+    """The memory / BAR1 / NVLink probe over a fake NVML: two NVLink-connected GPUs and one behind PCIe."""
+    from types import SimpleNamespace as NS
+    from b200serve.utils import vram
+
+    class FakeNvml:
+        NVML_P2P_CAPS_INDEX_NVLINK = 2
+        NVML_P2P_STATUS_OK = 0
+        calls = []
+
+        def nvmlDeviceGetCount(self): return 3
+        def nvmlDeviceGetHandleByIndex(self, i): return i
+        def nvmlDeviceGetName(self, h): return b"NVIDIA B200"
+        def nvmlDeviceGetMemoryInfo(self, h): return NS(total=180 << 30, free=(170 - 60 * h) << 30, used=0)
+
+        def nvmlDeviceGetBAR1MemoryInfo(self, h):
+            if h == 2:
+                raise RuntimeError("not supported")
+            return NS(bar1Total=(256 << 30) if h == 0 else (64 << 30), bar1Free=1 << 30)
+
+        def nvmlDeviceGetNvLinkState(self, h, link):
+            if link >= 18:
+                raise RuntimeError("invalid link")
+            return 1 if h < 2 else 0
+
+        def nvmlDeviceGetP2PStatus(self, a, b, idx):
+            assert idx == self.NVML_P2P_CAPS_INDEX_NVLINK
+            return 0 if (a < 2 and b < 2) else 5
+
+        def __getattr__(self, name):        # anything that would change a setting is a test failure
+            raise AssertionError(f"unexpected NVML call {name}")
+
+    g = vram.probe(FakeNvml())
+    assert [x.index for x in g] == [0, 1, 2]
+    assert g[0].bar1_covers_memory and not g[1].bar1_covers_memory and g[2].bar1_total == 0
+    assert g[0].nvlinks_up == 18 and g[2].nvlinks_up == 0
+    assert g[0].peers_nvlink == {1: True, 2: False}
+    lines = vram.describe(g)
+    assert "NVLink peers [1]" in lines[0] and "NOT over NVLink [2]" in lines[0] and "covers the memory" in lines[0]
+    assert vram.check_placement(g[:2], need_bytes=100 << 30, need_nvlink=False) == []
+    two = vram.probe(FakeNvml(), indices=[0, 1])
+    assert vram.check_placement(two, need_nvlink=True) == []
+    bad = vram.check_placement(g, need_bytes=100 << 30, need_nvlink=True)
+    assert any("GPU 2" in b and "GiB free" in b for b in bad) and any("not connected by NVLink" in b for b in bad)
