@@ -39,6 +39,7 @@ struct AttnPfParams {
   int C;        // rows in the chunk
   int pos0;     // absolute position of row 0
   int max_blocks;  // entries in block_table
+  int window;      // > 0: a row attends to its last `window` positions only; key tiles before the CTA's first window are skipped
   float scale_log2;
   __nv_bfloat16* out;  // [C][n_q * D]
 };
@@ -72,7 +73,8 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   const int head = blockIdx.y, kh = head / (p.n_q / p.n_kv);
   const int row0 = qt * BQ;
   const int last_pos = p.pos0 + min(row0 + BQ, p.C) - 1;
-  const int n_tiles = last_pos / BK + 1;
+  const int t0 = p.window > 0 ? max(0, p.pos0 + row0 - p.window + 1) / BK : 0;   // first key tile any row of the CTA needs
+  const int n_tiles = last_pos / BK + 1 - t0;
 
   if (threadIdx.x == 0) {
     mbar_init(b_qfull, 1);
@@ -121,7 +123,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         int rowc[n_pages];
 #pragma unroll
         for (int pg = 0; pg < n_pages; ++pg) {
-          const int page = (i * 8 + pg < p.max_blocks) ? __ldg(p.block_table + i * 8 + pg) : 0;
+          const int page = ((t0 + i) * 8 + pg < p.max_blocks) ? __ldg(p.block_table + (t0 + i) * 8 + pg) : 0;
           rowc[pg] = (page * p.n_kv + kh) * 16;
         }
         if (i >= 2) ok = mbar_wait(b_kempty + 8 * s, ((i >> 1) - 1) & 1, ERR_ATTN_WAIT);
@@ -205,6 +207,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     const int half = (warp - 2) >> 2;     // which 64 of the row's 128 columns: the threads of a pair share a row
     const int r = quarter * 32 + lane;
     const int qpos = p.pos0 + row0 + r;
+    const int qlo = p.window > 0 ? qpos - p.window + 1 : 0;   // the row's keys: qlo <= key <= qpos
     const bool row_ok = row0 + r < p.C;
     const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
     const uint32_t xch = bars + 256;      // float [2][128]: the halves exchange their row maxima / sums here
@@ -217,8 +220,9 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       const int sb = i & 1;
       if (ok) ok = mbar_wait(b_sfull + 8 * sb, (i >> 1) & 1, ERR_ATTN_WAIT);
       tc_fence_after();
-      const int key0 = i * BK;
-      const bool diag = key0 + BK - 1 > p.pos0 + row0;  // only tiles that reach past the CTA's first row need the mask
+      const int key0 = (t0 + i) * BK;
+      // only tiles that reach past the CTA's first row, or below the window of its last row, need the mask
+      const bool diag = key0 + BK - 1 > p.pos0 + row0 || (p.window > 0 && key0 < p.pos0 + row0 + BQ - p.window);
       // pass 1: the maximum of this thread's 64 columns (raw scores: the scale is positive)
       float tmax = -INFINITY;
       if (ok) {
@@ -229,7 +233,10 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
           tmem_ld_wait();
           if (diag) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) tmax = fmaxf(tmax, (key0 + c * 32 + j <= qpos) ? __uint_as_float(v[j]) : -INFINITY);
+            for (int j = 0; j < 32; ++j) {
+              const int kj = key0 + c * 32 + j;
+              tmax = fmaxf(tmax, (kj <= qpos && kj >= qlo) ? __uint_as_float(v[j]) : -INFINITY);
+            }
           } else {
 #pragma unroll
             for (int j = 0; j < 32; ++j) tmax = fmaxf(tmax, __uint_as_float(v[j]));
@@ -285,8 +292,8 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e1) : "f"(fmaf(__uint_as_float(v[2 * j + 1]), p.scale_log2, nmref)));
             if (diag) {
               const int k0 = key0 + c * 32 + 2 * j;
-              e0 = (k0 <= qpos) ? e0 : 0.f;
-              e1 = (k0 + 1 <= qpos) ? e1 : 0.f;
+              e0 = (k0 <= qpos && k0 >= qlo) ? e0 : 0.f;
+              e1 = (k0 + 1 <= qpos && k0 + 1 >= qlo) ? e1 : 0.f;
             }
             lsum += e0 + e1;
             pk[j] = pack_bf16(e0, e1);
@@ -381,7 +388,7 @@ int make_map_bf16(CUtensorMap* map, const void* ptr, uint64_t rows, uint64_t col
 // already be in the cache.
 extern "C" int b2_attn_prefill(const void* q, const void* k_cache, const void* v_cache, const int* block_table,
                                void* out, int C, int pos0, int n_q, int n_kv, int head_dim, int num_pages,
-                               int max_blocks, float scale, void* stream) {
+                               int max_blocks, float scale, int window, void* stream) {
   if (head_dim != D || n_q % n_kv != 0 || C < 1) return -1;
   CUtensorMap mq, mk, mv;
   int rc = make_map_bf16(&mq, q, (uint64_t)C, (uint64_t)n_q * D, BQ);
@@ -401,6 +408,7 @@ extern "C" int b2_attn_prefill(const void* q, const void* k_cache, const void* v
   AttnPfParams p;
   p.block_table = block_table; p.n_q = n_q; p.n_kv = n_kv; p.C = C; p.pos0 = pos0; p.max_blocks = max_blocks;
   p.scale_log2 = scale * 1.4426950408889634f; p.out = (__nv_bfloat16*)out;
+  p.window = window > 0 ? window : 0;
   dim3 grid((C + BQ - 1) / BQ, n_q);
   attn_prefill_kernel<<<grid, kThreads, SMEM, (cudaStream_t)stream>>>(mq, mk, mv, p);
   return (int)cudaGetLastError();

@@ -256,8 +256,10 @@ def wire_wait(cnt: torch.Tensor, expect: int):
     _check(rc, "wire_wait")
 
 
-def attn_prefill(q, k_cache, v_cache, block_table_row, out, c, pos0, n_q, n_kv, d, num_pages, max_blocks, scale):
-    """Causal flash attention of a prompt chunk (``c`` rows at positions ``pos0..``) over the paged bf16 cache."""
+def attn_prefill(q, k_cache, v_cache, block_table_row, out, c, pos0, n_q, n_kv, d, num_pages, max_blocks, scale,
+                 window: int = 0):
+    """Causal flash attention of a prompt chunk (``c`` rows at positions ``pos0..``) over the paged bf16 cache;
+    ``window`` > 0: every row attends to its last ``window`` positions only."""
     rc = lib().b2_attn_prefill(_p(q), _p(k_cache), _p(v_cache), _p(block_table_row), _p(out), c, pos0, n_q, n_kv, d,
-                               num_pages, max_blocks, ctypes.c_float(scale), _stream())
+                               num_pages, max_blocks, ctypes.c_float(scale), window, _stream())
     _check(rc, "attn_prefill")

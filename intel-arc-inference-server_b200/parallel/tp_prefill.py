@@ -77,7 +77,7 @@ class TpPrefillRunner(PrefillRunner):
             K.rope_append(qkv, 0, 1, c, None, eng.block_table, eng.max_blocks, m.cos_t, m.sin_t, cfg.n_q_heads,
                           cfg.n_kv_heads, cfg.head_dim, self.q, kc, vc, ks, vs, eng.kv.kv_int8, req=slot, pos0=pos0)
             K.attn_prefill(self.q, kc, vc, bt_row, self.attn, c, pos0, cfg.n_q_heads, cfg.n_kv_heads, cfg.head_dim,
-                           eng.kv.num_pages, eng.max_blocks, m.scale)
+                           eng.kv.num_pages, eng.max_blocks, m.scale, window=m._window(li))
             arr = G.gemm_tp(self.attn[:c], self._w_bf16(lw.o), None, G.EPI_RS_PUSH, rs=self.rs, rs_tpr=self.tpr)
             self._fold(w, arr, lw.post_norm, c)
             act = self.act[:c, : cfg.ffn]
@@ -149,7 +149,7 @@ class NcclPrefillRunner(PrefillRunner):
             K.rope_append(qkv, 0, 1, c, None, eng.block_table, eng.max_blocks, m.cos_t, m.sin_t, cfg.n_q_heads,
                           cfg.n_kv_heads, cfg.head_dim, self.q, kc, vc, ks, vs, eng.kv.kv_int8, req=slot, pos0=pos0)
             K.attn_prefill(self.q, kc, vc, bt_row, self.attn, c, pos0, cfg.n_q_heads, cfg.n_kv_heads, cfg.head_dim,
-                           eng.kv.num_pages, eng.max_blocks, m.scale)
+                           eng.kv.num_pages, eng.max_blocks, m.scale, window=m._window(li))
             part = self.part[:c]
             torch.matmul(self.attn[:c], self._w_bf16(lw.o).t(), out=part)
             if self.world > 1:

@@ -227,8 +227,6 @@ class Engine:
         has one (head size 128, bf16 KV, dense FFN or MoE with a grouped path)."""
         if self.prefill_backend == "rows" or n <= self.max_rows:
             return False
-        if self.cfg.sliding_window > 0:      # the tcgen05 prompt attention has no window mask: windowed models
-            return False                     # ingest prompts through the row kernels
         ok = self.cfg.head_dim == 128 and (not self.kv.kv_int8 or (self.tp is None and self.model.nccl is None))
         if not ok and self.prefill_backend != "auto":
             raise ValueError(f"prefill backend {self.prefill_backend!r} needs head_dim 128 (and a bf16 KV cache under "

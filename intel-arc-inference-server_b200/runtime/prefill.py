@@ -151,7 +151,7 @@ class PrefillRunner:
                       cfg.n_kv_heads, cfg.head_dim, self.q, kc, vc, ks, vs, eng.kv.kv_int8, req=slot, pos0=pos0)
         phase("attention")
         K.attn_prefill(self.q, kc, vc, bt_row, self.attn, c, pos0, cfg.n_q_heads, cfg.n_kv_heads, cfg.head_dim,
-                       eng.kv.num_pages, eng.max_blocks, m.scale)
+                       eng.kv.num_pages, eng.max_blocks, m.scale, window=m._window(kv_index))
         phase("o")
         self.linear(lw.o, self.attn[:c], resid, G.EPI_RESID_ADD, resid=resid)
         phase("norm")
@@ -229,7 +229,7 @@ class PrefillRunner:
                 K.rope_append(qkv, 0, 1, c, None, tab16, tab16.shape[1], m.cos_t, m.sin_t, cfg.n_q_heads, cfg.n_kv_heads,
                               cfg.head_dim, self.q, k16[0], v16[0], None, None, False, req=0, pos0=pos0)
                 K.attn_prefill(self.q, k16[0], v16[0], tab16[0], self.attn, c, pos0, cfg.n_q_heads, cfg.n_kv_heads,
-                               cfg.head_dim, k16.shape[1], tab16.shape[1], m.scale)
+                               cfg.head_dim, k16.shape[1], tab16.shape[1], m.scale, window=m._window(li))
                 self.linear(lw.o, self.attn[:c], resid, G.EPI_RESID_ADD, resid=resid)
                 K.resid_norm(1, c, h, lw.post_norm, cfg.rms_eps, resid, x, resid_in=resid, splits=0)
                 if lw.gate_up is not None:

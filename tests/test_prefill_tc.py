@@ -11,8 +11,10 @@ from b200serve.models.weights import random_weights
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("c,pos0,n_q,n_kv", [(128, 0, 2, 1), (300, 0, 8, 2), (200, 150, 4, 4), (77, 1000, 5, 1)])
-def test_attn_prefill_matches_softmax(c, pos0, n_q, n_kv):
+@pytest.mark.parametrize("c,pos0,n_q,n_kv,window", [(128, 0, 2, 1, 0), (300, 0, 8, 2, 0), (200, 150, 4, 4, 0),
+                                                    (77, 1000, 5, 1, 0), (300, 0, 4, 2, 100), (260, 700, 4, 1, 40),
+                                                    (200, 150, 2, 2, 300), (128, 512, 2, 1, 128)])
+def test_attn_prefill_matches_softmax(c, pos0, n_q, n_kv, window):
     from b200serve.ops import lib as K
     torch.manual_seed(c + pos0)
     d = 128
@@ -31,25 +33,31 @@ def test_attn_prefill_matches_softmax(c, pos0, n_q, n_kv):
     q = torch.randn(c, n_q, d).to(torch.bfloat16)
     out = torch.full((c, n_q * d), float("nan"), dtype=torch.bfloat16, device="cuda")
     K.attn_prefill(q.reshape(c, -1).cuda(), kc, vc, table, out, c, pos0, n_q, n_kv, d, num_pages, max_blocks,
-                   1.0 / math.sqrt(d))
+                   1.0 / math.sqrt(d), window=window)
     torch.cuda.synchronize()
     K.check_status()
     g = n_q // n_kv
     kk, vv = k.float().repeat_interleave(g, 1), v.float().repeat_interleave(g, 1)
     sc = torch.einsum("rhd,shd->hrs", q.float(), kk) / math.sqrt(d)
     qpos = pos0 + torch.arange(c)
-    sc = sc.masked_fill((torch.arange(total)[None, :] > qpos[:, None])[None], float("-inf"))
+    masked = torch.arange(total)[None, :] > qpos[:, None]
+    if window > 0:      # sliding window: keys at or before qpos - window are skipped tile-wise or masked
+        masked = masked | (torch.arange(total)[None, :] <= qpos[:, None] - window)
+    sc = sc.masked_fill(masked[None], float("-inf"))
     ref = torch.einsum("hrs,shd->rhd", torch.softmax(sc, -1), vv).reshape(c, -1)
     got = out.float().cpu()
     assert torch.isfinite(got).all()
     assert (got - ref).abs().max() < 0.02 * ref.abs().max() + 2e-3
 
 
-@pytest.mark.parametrize("backend", ["bf16", "bf16-resident", "int8"])
+@pytest.mark.parametrize("backend", ["bf16", "bf16-resident", "int8", "bf16-windowed"])
 def test_prefill_runner_matches_oracle(backend):
     from b200serve.runtime.engine import Engine
     from b200serve.ops import lib as K
     cfg = small_dense()
+    if backend == "bf16-windowed":      # layers 0 and 2 attend to the last 48 positions
+        from b200serve.models.config import preset
+        cfg, backend = preset("small-windowed"), "bf16"
     w = random_weights(cfg, seed=3)
     oracle = OracleModel(w)
     g = torch.Generator().manual_seed(5)
