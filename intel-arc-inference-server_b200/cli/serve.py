@@ -49,12 +49,18 @@ def main(argv=None):
     if hasattr(tok, "token_to_id"):
         eos = [i for i in (tok.token_to_id("<|im_end|>"), tok.token_to_id("<|endoftext|>")) if i is not None and i >= 0]
     spec = f.spec if f.spec != "auto" else ("mtp" if weights.mtp is not None else "off")
+    hybrid = cfg.n_gdn_layers > 0
+    if hybrid and (spec != "off" or f.prefix_cache_gb != "0"):
+        # rejected draft rows and reused prefixes both rewind a sequence; a recurrent state cannot be rewound
+        sys.stderr.write("serve: gated delta-net layers keep a recurrent state per slot: speculative decoding and the "
+                         "prefix cache are switched off for this model\n")
+        spec = "off"
     adapter = EngineAdapter(engine, eos_ids=eos or (2,))
     if spec in ("mtp", "dflash", "dflash-lookup"):
         from ..runtime.spec import SpecAdapter
         adapter = SpecAdapter(adapter, spec, f.spec_max, f.draft_model, f.draft_vocab, f.draft_vocab_ids)
     prefix = None
-    if f.prefix_cache_gb != "0":
+    if f.prefix_cache_gb != "0" and not hybrid:
         from ..server.prefix import PrefixStore
         prefix = PrefixStore(engine, f.prefix_cache_gb)
     opts = ServerOptions(model_name=cfg.name, log_requests=f.log_requests, spec=spec, spec_max=f.spec_max,

@@ -106,6 +106,8 @@ def _ql(q, scales, device) -> QLinear:
 def _load_layer(view: NameView, cfg: ModelConfig, prefix: str, qc: QuantConfig, device, tp) -> LayerWeights:
     rank, world = tp
     hd = cfg.head_dim
+    if view.has(prefix + ".linear_attn.A_log"):
+        return _load_gdn_layer(view, cfg, prefix, qc, device, tp)
     q_s = _LinearSrc(view, prefix + ".self_attn.q_proj", qc)
     k_s = _LinearSrc(view, prefix + ".self_attn.k_proj", qc)
     v_s = _LinearSrc(view, prefix + ".self_attn.v_proj", qc)
@@ -122,6 +124,36 @@ def _load_layer(view: NameView, cfg: ModelConfig, prefix: str, qc: QuantConfig, 
         input_norm=view.get(prefix + ".input_layernorm.weight").float().to(device),
         post_norm=view.get(prefix + ".post_attention_layernorm.weight").float().to(device),
         qkv=_ql(*qkv, device), o=_ql(o_q, o_sc, device))
+    _load_ffn(lw, view, cfg, prefix, qc, device, tp)
+    return lw
+
+
+def _load_gdn_layer(view: NameView, cfg: ModelConfig, prefix: str, qc: QuantConfig, device, tp) -> LayerWeights:
+    """A gated delta-net layer: ``linear_attn.in_proj_qkvz`` (columns [ q | k | v | z ], heads in order) and
+    ``linear_attn.in_proj_ba`` ([ b | a ]) are fused into one projection; ``conv1d.weight`` is [channels][1][4]."""
+    from ..models.weights import GdnWeights
+    if tp[1] != 1:
+        raise ValueError("gated delta-net layers are not sliced for tensor parallelism")
+    p = prefix + ".linear_attn"
+    qkvz, ba = _LinearSrc(view, p + ".in_proj_qkvz", qc), _LinearSrc(view, p + ".in_proj_ba", qc)
+    if qkvz.n != 2 * cfg.gdn_key_dim + 2 * cfg.gdn_value_dim or ba.n != 2 * cfg.gdn_v_heads:
+        raise ValueError(f"{p}: projection widths {qkvz.n} / {ba.n} do not match the configured heads")
+    out = _LinearSrc(view, p + ".out_proj", qc)
+    conv = view.get(p + ".conv1d.weight").float().reshape(cfg.gdn_conv_channels, 4)
+    lw = LayerWeights(
+        input_norm=view.get(prefix + ".input_layernorm.weight").float().to(device),
+        post_norm=view.get(prefix + ".post_attention_layernorm.weight").float().to(device), qkv=None, o=None)
+    lw.gdn = GdnWeights(
+        in_proj=_ql(*_fuse_cols([_cols(qkvz, 0, qkvz.n), _cols(ba, 0, ba.n)]), device),
+        conv_w=conv.contiguous().to(device), a_log=view.get(p + ".A_log").float().to(device),
+        dt_bias=view.get(p + ".dt_bias").float().to(device), norm_w=view.get(p + ".norm.weight").float().to(device),
+        out_proj=_ql(out.q, out.scales, device))
+    _load_ffn(lw, view, cfg, prefix, qc, device, tp)
+    return lw
+
+
+def _load_ffn(lw: LayerWeights, view: NameView, cfg: ModelConfig, prefix: str, qc: QuantConfig, device, tp):
+    rank, world = tp
 
     def mlp(p, ffn):
         g, u, d = (_LinearSrc(view, f"{p}.{n}_proj", qc) for n in ("gate", "up", "down"))
@@ -148,7 +180,6 @@ def _load_layer(view: NameView, cfg: ModelConfig, prefix: str, qc: QuantConfig, 
                 lw.shared_gate = view.get(prefix + ".mlp.shared_expert_gate.weight").to(torch.bfloat16).to(device)
     else:
         lw.gate_up, lw.down = mlp(prefix + ".mlp", cfg.ffn)
-    return lw
 
 
 def load(snapshot: str, device="cuda", mtp: bool = True, int8_head: bool = False, tp: Tuple[int, int] = (0, 1),

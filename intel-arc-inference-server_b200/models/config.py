@@ -48,6 +48,13 @@ class ModelConfig:
     # reference's windowed families (src/kernels/kolibri/kol_attn.cl: sliding ring 4096 / full layers)
     sliding_window: int = 0
     full_attn_every: int = 0
+    # hybrid family: gated delta-net (linear attention) layers with n_k key heads and n_v value heads of 128;
+    # with ``gdn_v_heads`` > 0 every layer is a GDN layer except each ``full_attn_every``-th one, which keeps
+    # softmax attention (the reference's hybrid checkpoints: src/kernels/gdn_step.cl, three GDN layers per
+    # attention layer)
+    gdn_k_heads: int = 0
+    gdn_v_heads: int = 0
+    gdn_head_dim: int = 128
 
     @property
     def q_dim(self) -> int:
@@ -69,9 +76,39 @@ class ModelConfig:
     def is_moe(self) -> bool:
         return self.n_experts > 0
 
+    def is_gdn_layer(self, li: int) -> bool:
+        if self.gdn_v_heads <= 0 or li >= self.n_layers:
+            return False
+        return not (self.full_attn_every > 0 and li % self.full_attn_every == self.full_attn_every - 1)
+
+    def gdn_index(self, li: int) -> int:
+        """Index of GDN layer ``li`` among the GDN layers (its slice of the recurrent-state buffers)."""
+        return sum(1 for i in range(li) if self.is_gdn_layer(i))
+
+    @property
+    def n_gdn_layers(self) -> int:
+        return sum(1 for i in range(self.n_layers) if self.is_gdn_layer(i))
+
+    @property
+    def gdn_key_dim(self) -> int:
+        return self.gdn_k_heads * self.gdn_head_dim
+
+    @property
+    def gdn_value_dim(self) -> int:
+        return self.gdn_v_heads * self.gdn_head_dim
+
+    @property
+    def gdn_conv_channels(self) -> int:
+        return 2 * self.gdn_key_dim + self.gdn_value_dim
+
+    @property
+    def gdn_proj_dim(self) -> int:
+        """Columns of the fused input projection [ q | k | v | z | b | a ]."""
+        return 2 * self.gdn_key_dim + 2 * self.gdn_value_dim + 2 * self.gdn_v_heads
+
     def window_of(self, li: int) -> int:
         """Attention window of layer ``li`` in positions (0: full attention)."""
-        if self.sliding_window <= 0:
+        if self.sliding_window <= 0 or self.gdn_v_heads > 0:
             return 0
         if self.full_attn_every > 0 and li % self.full_attn_every == self.full_attn_every - 1:
             return 0
@@ -156,6 +193,9 @@ class ModelConfig:
             "mtp_num_hidden_layers": self.mtp_layers,
             "sliding_window": self.sliding_window or None,
             "full_attention_interval": self.full_attn_every,
+            "linear_num_key_heads": self.gdn_k_heads,
+            "linear_num_value_heads": self.gdn_v_heads,
+            "linear_key_head_dim": self.gdn_head_dim,
             "torch_dtype": "bfloat16",
             "quantization_config": {
                 "bits": 4, "group_size": self.group_size, "sym": True, "desc_act": False,
@@ -180,6 +220,8 @@ class ModelConfig:
             shared_ffn=d.get("shared_expert_intermediate_size", 0) or 0,
             mtp_layers=d.get("mtp_num_hidden_layers", 0) or 0,
             sliding_window=d.get("sliding_window", 0) or 0, full_attn_every=d.get("full_attention_interval", 0) or 0,
+            gdn_k_heads=d.get("linear_num_key_heads", 0) or 0, gdn_v_heads=d.get("linear_num_value_heads", 0) or 0,
+            gdn_head_dim=d.get("linear_key_head_dim", 128) or 128,
             architecture=(d.get("architectures") or ["B200DenseForCausalLM"])[0],
         )
 
@@ -197,6 +239,13 @@ def small_dense() -> ModelConfig:
 def small_windowed() -> ModelConfig:
     """Four layers of the small dense shape; layers 0 and 2 attend to the last 48 positions, 1 and 3 to all."""
     return ModelConfig("small-windowed", 4, 512, 8, 2, 128, 1408, 2048, sliding_window=48, full_attn_every=2)
+
+
+def small_hybrid() -> ModelConfig:
+    """Four layers of the small dense shape: layers 0 and 2 are gated delta-net layers (2 key / 4 value heads of
+    128), layers 1 and 3 softmax attention."""
+    return ModelConfig("small-hybrid", 4, 512, 8, 2, 128, 1408, 2048, full_attn_every=2, gdn_k_heads=2, gdn_v_heads=4,
+                       architecture="B200HybridForCausalLM")
 
 
 def tiny_moe() -> ModelConfig:
@@ -229,7 +278,7 @@ def dflash_drafter(target: ModelConfig) -> ModelConfig:
 
 
 PRESETS = {
-    "tiny-dense": tiny_dense, "tiny-moe": tiny_moe, "small-dense": small_dense, "small-windowed": small_windowed, "small-moe": small_moe, "dense-27b": dense_27b, "moe-35b-a3b": moe_35b_a3b,
+    "tiny-dense": tiny_dense, "tiny-moe": tiny_moe, "small-dense": small_dense, "small-windowed": small_windowed, "small-hybrid": small_hybrid, "small-moe": small_moe, "dense-27b": dense_27b, "moe-35b-a3b": moe_35b_a3b,
 }
 
 

@@ -56,7 +56,10 @@ class StepBuffers:
         self.tickets = torch.zeros(max_rows * cfg.n_kv_heads, dtype=torch.int32, device=device)
         self.fold_tickets = torch.zeros((h + 127) // 128, dtype=torch.int32, device=device)
         self.ssq = torch.zeros(max_rows * ((h + 127) // 128), dtype=f32, device=device)
-        kmax = max(2 * h, cfg.q_dim, cfg.ffn, cfg.expert_ffn, cfg.shared_ffn)
+        kmax = max(2 * h, cfg.q_dim, cfg.ffn, cfg.expert_ffn, cfg.shared_ffn, cfg.gdn_value_dim)
+        if cfg.n_gdn_layers:
+            self.gdn_act = torch.zeros(max_rows, cfg.gdn_proj_dim, dtype=f32, device=device)
+            self.gdn_out = torch.zeros(max_rows, cfg.gdn_value_dim, dtype=bf, device=device)
         self.xq = torch.zeros(max_rows * (kmax // 64) * 128, dtype=torch.uint8, device=device)    # pre-quantised rows
         self.xq_gs = torch.zeros(max_rows * (kmax // 64) * 2, dtype=torch.int32, device=device)
         self._parts = {}
@@ -81,7 +84,7 @@ def attn_splits(n_kv_heads: int, depth: int) -> int:
 class KVCache:
     """Paged KV: per layer ``[page][kv_head][16][D]`` for K and for V (bf16 or int8 + fp32 scales)."""
 
-    def __init__(self, cfg: ModelConfig, n_layers: int, num_pages: int, device, kv_dtype: str = "bf16"):
+    def __init__(self, cfg: ModelConfig, n_layers: int, num_pages: int, device, kv_dtype: str = "bf16", n_slots: int = 1):
         self.kv_int8 = kv_dtype == "int8"
         dt = torch.int8 if self.kv_int8 else torch.bfloat16
         self.num_pages = num_pages
@@ -92,6 +95,18 @@ class KVCache:
             self.v_scale = torch.zeros_like(self.k_scale)
         else:
             self.k_scale = self.v_scale = None
+        # gated delta-net layers keep, per slot, the last three convolution inputs and one fp32 state per value head
+        self.gdn_conv = self.gdn_state = None
+        if cfg.n_gdn_layers:
+            g = cfg.n_gdn_layers
+            self.gdn_conv = torch.zeros(g, n_slots, cfg.gdn_conv_channels, 3, dtype=torch.float32, device=device)
+            self.gdn_state = torch.zeros(g, n_slots, cfg.gdn_v_heads, cfg.gdn_head_dim, cfg.gdn_head_dim,
+                                         dtype=torch.float32, device=device)
+
+    def reset_slot(self, slot: int):
+        if self.gdn_conv is not None:
+            self.gdn_conv[:, slot].zero_()
+            self.gdn_state[:, slot].zero_()
 
     def layer(self, li: int):
         ks = self.k_scale[li] if self.kv_int8 else None
@@ -179,6 +194,18 @@ class DecoderModel:
                           cfg.n_kv_heads, cfg.head_dim, self.nsplit_attn, max_blocks, self.scale, ks, vs, kv.kv_int8,
                           tickets=b.tickets)
 
+    def gdn_block(self, lw: LayerWeights, li: int, m: int, ctrl, kv: KVCache):
+        """A gated delta-net layer's mixer for the step's rows: projection GEMV, convolution + SiLU, the recurrent
+        step per value head, output projection (partials, like the attention block's)."""
+        cfg, b, g = self.cfg, self.buf, lw.gdn
+        gi = cfg.gdn_index(li)
+        part, s = self._gemv("gdn_in", g.in_proj, b.x, m)
+        n = cfg.gdn_proj_dim
+        K.gdn_conv(part, s, m, n, cfg.gdn_conv_channels, ctrl, g.conv_w, kv.gdn_conv[gi], b.gdn_act)
+        K.gdn_step(b.gdn_act, m, n, cfg.gdn_k_heads, cfg.gdn_v_heads, cfg.gdn_head_dim, ctrl, g.a_log, g.dt_bias,
+                   g.norm_w, cfg.rms_eps, kv.gdn_state[gi], b.gdn_out)
+        return self._gemv("gdn_out", g.out_proj, b.gdn_out, m)
+
     def _window(self, li: int) -> int:
         return self.cfg.window_of(li) if li < self.cfg.n_layers else 0   # draft-head layers: the whole context
 
@@ -245,11 +272,11 @@ class DecoderModel:
         cfg, b = self.cfg, self.buf
         h = cfg.hidden
         pend = None
-        if self.fused and resid_ready and all(lw.gate_up is not None for lw in layers) and h % 128 == 0:
+        if self.fused and resid_ready and all(lw.gate_up is not None and lw.gdn is None for lw in layers) and h % 128 == 0:
             for i, lw in enumerate(layers):
                 self.dense_layer_fused(lw, kv_layer0 + i, m, ctrl, block_table, max_blocks, kv, x_ready=False)
             return None, 0
-        if self.fused and first_from_embed and all(lw.gate_up is not None for lw in layers) and h % 128 == 0:
+        if self.fused and first_from_embed and all(lw.gate_up is not None and lw.gdn is None for lw in layers) and h % 128 == 0:
             K.resid_norm(0, m, h, layers[0].input_norm, cfg.rms_eps, b.resid, b.x, embed=self.w.embed, ctrl=ctrl,
                          vocab=cfg.vocab, flag=b.flag)
             for i, lw in enumerate(layers):
@@ -267,7 +294,10 @@ class DecoderModel:
             else:
                 K.resid_norm(1, m, h, lw.input_norm, cfg.rms_eps, b.resid, b.x, resid_in=b.resid, part=pend[0],
                              part_slice=m * h, splits=pend[1])
-            po, so = self.attention_block(lw, kv_layer0 + i, m, ctrl, block_table, max_blocks, kv)
+            if lw.gdn is not None:
+                po, so = self.gdn_block(lw, kv_layer0 + i, m, ctrl, kv)
+            else:
+                po, so = self.attention_block(lw, kv_layer0 + i, m, ctrl, block_table, max_blocks, kv)
             po, so = self._nccl_reduce(po, so, m)
             K.resid_norm(1, m, h, lw.post_norm, cfg.rms_eps, b.resid, b.x, resid_in=b.resid, part=po,
                          part_slice=m * h, splits=so)

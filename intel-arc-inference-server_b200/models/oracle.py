@@ -67,9 +67,13 @@ class OracleKV:
         n = cfg.n_layers if n_layers is None else n_layers
         self.k: List[Optional[torch.Tensor]] = [None] * n
         self.v: List[Optional[torch.Tensor]] = [None] * n
+        self.gdn = {}      # layer -> (conv inputs [channels][3], state [n_v][dk][dv]) of gated delta-net layers
 
     def length(self) -> int:
-        return 0 if self.k[0] is None else self.k[0].shape[0]
+        for k in self.k:
+            if k is not None:
+                return k.shape[0]
+        return 0
 
     def truncate(self, n: int):
         for i in range(len(self.k)):
@@ -137,9 +141,40 @@ class OracleModel:
             out += gate * self.swiglu(lw.shared.gate_up, lw.shared.down, x)
         return out
 
+    def gdn(self, lw: LayerWeights, x: torch.Tensor, kv: OracleKV, li: int) -> torch.Tensor:
+        """Gated delta-net layer, token by token (the recurrence the device kernel runs: ops/csrc/gdn.cu)."""
+        c, g = self.cfg, lw.gdn
+        dh, nk, nv = c.gdn_head_dim, c.gdn_k_heads, c.gdn_v_heads
+        kd, vd, cc = c.gdn_key_dim, c.gdn_value_dim, c.gdn_conv_channels
+        proj = self.linear(g.in_proj, x)
+        conv_w, a_log, dt_bias, norm_w = (t.float().cpu() for t in (g.conv_w, g.a_log, g.dt_bias, g.norm_w))
+        conv, S = kv.gdn.get(li, (torch.zeros(cc, 3), torch.zeros(nv, dh, dh)))
+        outs = []
+        for t in range(x.shape[0]):
+            hist = torch.cat([conv, proj[t, :cc, None]], dim=1)
+            y = F.silu((hist * conv_w).sum(dim=1))
+            conv = hist[:, 1:]
+            q, k, v = y[:kd].view(nk, dh), y[kd: 2 * kd].view(nk, dh), y[2 * kd:].view(nv, dh)
+            z = proj[t, cc: cc + vd].view(nv, dh)
+            b, a = proj[t, cc + vd: cc + vd + nv], proj[t, cc + vd + nv:]
+            q = q * torch.rsqrt((q * q).sum(-1, keepdim=True) + 1e-6) * dh ** -0.5
+            k = k * torch.rsqrt((k * k).sum(-1, keepdim=True) + 1e-6)
+            q, k = q.repeat_interleave(nv // nk, dim=0), k.repeat_interleave(nv // nk, dim=0)
+            beta = torch.sigmoid(b)
+            decay = torch.exp(-torch.exp(a_log) * F.softplus(a + dt_bias))
+            S = S * decay[:, None, None]
+            delta = (v - torch.einsum("hij,hi->hj", S, k)) * beta[:, None]
+            S = S + torch.einsum("hi,hj->hij", k, delta)
+            o = torch.einsum("hij,hi->hj", S, q)
+            o = o * torch.rsqrt((o * o).mean(-1, keepdim=True) + c.rms_eps) * norm_w * F.silu(z)
+            outs.append(o.reshape(vd))
+        kv.gdn[li] = (conv, S)
+        return self.linear(g.out_proj, torch.stack(outs))
+
     def layer(self, lw: LayerWeights, h: torch.Tensor, pos: torch.Tensor, kv: OracleKV, li: int):
         c = self.cfg
-        h = h + self.attention(lw, rmsnorm(h, lw.input_norm, c.rms_eps), pos, kv, li)
+        xin = rmsnorm(h, lw.input_norm, c.rms_eps)
+        h = h + (self.gdn(lw, xin, kv, li) if lw.gdn is not None else self.attention(lw, xin, pos, kv, li))
         x = rmsnorm(h, lw.post_norm, c.rms_eps)
         if lw.experts is not None:
             h = h + self.moe(lw, x)

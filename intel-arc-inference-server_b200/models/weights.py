@@ -73,11 +73,23 @@ class ExpertWeights:
 
 
 @dataclass
+class GdnWeights:
+    """A gated delta-net layer: fused input projection [ q | k | v | z | b | a ], depthwise 4-tap convolution over
+    q, k, v, per-head decay parameters, the gated output norm and the output projection."""
+    in_proj: QLinear               # [gdn_proj_dim][hidden]
+    conv_w: torch.Tensor           # fp32 [conv_channels][4]; tap 3 multiplies the newest input
+    a_log: torch.Tensor            # fp32 [n_v]
+    dt_bias: torch.Tensor          # fp32 [n_v]
+    norm_w: torch.Tensor           # fp32 [head_dim]
+    out_proj: QLinear              # [hidden][value_dim]
+
+
+@dataclass
 class LayerWeights:
     input_norm: torch.Tensor       # fp32 [hidden]
     post_norm: torch.Tensor        # fp32 [hidden]
-    qkv: QLinear
-    o: QLinear
+    qkv: Optional[QLinear]         # None on gated delta-net layers
+    o: Optional[QLinear]
     gate_up: Optional[QLinear] = None
     down: Optional[QLinear] = None
     router: Optional[torch.Tensor] = None          # bf16 [n_experts][hidden]
@@ -87,6 +99,7 @@ class LayerWeights:
     # experts stacked for the grouped kernels: uint8 [E][nb][kg][4352]
     experts_gate_up_w4b: Optional[torch.Tensor] = None
     experts_down_w4b: Optional[torch.Tensor] = None
+    gdn: Optional[GdnWeights] = None               # set instead of qkv / o on gated delta-net layers
 
 
 @dataclass
@@ -115,6 +128,8 @@ class ModelWeights:
             for ql in (lw.qkv, lw.o, lw.gate_up, lw.down):
                 if ql is not None:
                     tot += ql.nbytes
+            if lw.gdn is not None:
+                tot += lw.gdn.in_proj.nbytes + lw.gdn.out_proj.nbytes
             if lw.experts_gate_up_w4b is not None:
                 tot += lw.experts_gate_up_w4b.numel() + lw.experts_down_w4b.numel()
             if lw.shared is not None:
@@ -126,7 +141,7 @@ def _norm_weight(h, device, gen=None):
     return torch.ones(h, dtype=torch.float32, device=device)
 
 
-def _rand_layer(cfg: ModelConfig, device, seed: int, exact: bool, std=0.02) -> LayerWeights:
+def _rand_layer(cfg: ModelConfig, device, seed: int, exact: bool, std=0.02, gdn: bool = False) -> LayerWeights:
     h = cfg.hidden
     g = torch.Generator(device="cpu")
     g.manual_seed(seed)
@@ -143,9 +158,20 @@ def _rand_layer(cfg: ModelConfig, device, seed: int, exact: bool, std=0.02) -> L
             return QLinear.from_f32(interleave16(gate, up), device)
         return QLinear.random(2 * i, k, device, seed * 131 + sub, std)
 
-    lw = LayerWeights(
-        input_norm=_norm_weight(h, device), post_norm=_norm_weight(h, device),
-        qkv=lin(cfg.qkv_dim, h, 1), o=lin(h, cfg.q_dim, 2))
+    if gdn:
+        nv = cfg.gdn_v_heads
+        lw = LayerWeights(input_norm=_norm_weight(h, device), post_norm=_norm_weight(h, device), qkv=None, o=None)
+        lw.gdn = GdnWeights(
+            in_proj=lin(cfg.gdn_proj_dim, h, 1),
+            conv_w=(torch.randn(cfg.gdn_conv_channels, 4, generator=g) * 0.5).to(device),
+            a_log=torch.log(torch.rand(nv, generator=g) * 4.0 + 0.5).to(device),
+            dt_bias=(torch.randn(nv, generator=g) * 0.5).to(device),
+            norm_w=(1.0 + 0.1 * torch.randn(cfg.gdn_head_dim, generator=g)).to(device),
+            out_proj=lin(h, cfg.gdn_value_dim, 2))
+    else:
+        lw = LayerWeights(
+            input_norm=_norm_weight(h, device), post_norm=_norm_weight(h, device),
+            qkv=lin(cfg.qkv_dim, h, 1), o=lin(h, cfg.q_dim, 2))
     if exact:
         # non-trivial norm weights so the norm kernels are actually exercised
         lw.input_norm = (1.0 + 0.1 * torch.randn(h, generator=g)).to(device)
@@ -189,7 +215,7 @@ def random_weights(cfg: ModelConfig, device="cpu", seed: int = 0, exact: Optiona
     else:
         embed = torch.empty(cfg.vocab, h, dtype=torch.bfloat16, device=device).normal_(0, std)
         head = torch.empty(hr, h, dtype=torch.bfloat16, device=device).normal_(0, std)
-    layers = [_rand_layer(cfg, device, seed * 1000 + 1 + i, exact, std) for i in range(cfg.n_layers)]
+    layers = [_rand_layer(cfg, device, seed * 1000 + 1 + i, exact, std, gdn=cfg.is_gdn_layer(i)) for i in range(cfg.n_layers)]
     mw = ModelWeights(cfg, embed, head, _norm_weight(h, device), layers)
     if cfg.mtp_layers:
         dense_cfg = cfg

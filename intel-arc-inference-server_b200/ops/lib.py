@@ -17,7 +17,7 @@ import torch
 from . import build as _build
 
 _lib: Optional[ctypes.CDLL] = None
-_UNITS = ("gemv", "decode", "gemm", "attn", "attnrows", "moe", "comm", "ep", "spec", "sampler")
+_UNITS = ("gemv", "decode", "gemm", "attn", "attnrows", "moe", "comm", "ep", "spec", "sampler", "gdn")
 
 # Control block layout (int32 words) -- mirrors decode_ops.cu
 CTRL_N_ROWS = 0
@@ -190,6 +190,20 @@ def attn_rows(q, k_cache, v_cache, block_table, ctrl, o_part, ml_part, out, tick
     if tickets is None:     # many rows: the merge is its own launch, one CTA per row and head
         rc = lib().b2_attn_merge(_p(o_part), _p(ml_part), _p(out), m, n_q, nsplit, d, _stream())
         _check(rc, "attn_merge")
+
+
+def gdn_conv(part, splits, m, n, conv_ch, ctrl, conv_w, conv_state, act):
+    """Folds the split-K partials of a gated delta-net layer's input projection into ``act`` [m][n]; the first
+    ``conv_ch`` columns pass through the slot's 4-tap causal convolution (state [slots][conv_ch][3]) and SiLU."""
+    _check(lib().b2_gdn_conv(_p(part), splits, m, n, conv_ch, _p(ctrl), _p(conv_w), _p(conv_state), _p(act), _stream()),
+           "gdn_conv")
+
+
+def gdn_step(act, m, n, n_k, n_v, head_dim, ctrl, a_log, dt_bias, norm_w, eps, state, out):
+    """One recurrent step per row and value head over ``state`` [slots][n_v][128][128]; ``out`` [m][n_v * 128] bf16
+    is the gated, normalised read-out."""
+    _check(lib().b2_gdn_step(_p(act), m, n, n_k, n_v, head_dim, _p(ctrl), _p(a_log), _p(dt_bias), _p(norm_w),
+                             ctypes.c_float(eps), _p(state), _p(out), _stream()), "gdn_step")
 
 
 def sample_rows(logits, m, n_valid, temperature, top_k, top_p, seed, token, status, penalty=None, hist=None,

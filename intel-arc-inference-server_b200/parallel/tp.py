@@ -61,6 +61,8 @@ def _cat_cols(parts, device) -> QLinear:
 
 
 def shard_layer(lw: LayerWeights, cfg: ModelConfig, rank: int, world: int, device) -> LayerWeights:
+    if lw.gdn is not None:
+        raise NotImplementedError("gated delta-net layers are not sliced for tensor parallelism")
     hd = cfg.head_dim
     qh, kh = cfg.n_q_heads // world, cfg.n_kv_heads // world
     q0, k0, v0 = 0, cfg.q_dim, cfg.q_dim + cfg.kv_dim

@@ -51,7 +51,8 @@ class Engine:
             nsplit_attn = attn_splits(cfg.n_kv_heads, max_len)
         self.model = DecoderModel(weights, max_rows=max_rows, max_pos=max_len, nsplit_attn=nsplit_attn,
                                   int8_head=int8_head, tp=self.tp, nccl=nccl)
-        self.kv = KVCache(cfg, cfg.n_layers + extra_kv_layers, num_pages, self.device, kv_dtype)   # + draft-head layers
+        self.kv = KVCache(cfg, cfg.n_layers + extra_kv_layers, num_pages, self.device, kv_dtype,   # + draft-head layers
+                          n_slots=max_seqs)
         self.kv_dtype = kv_dtype
         self.pool = KvPool(num_pages, max_seqs, self.max_blocks)
         self.ctrl = torch.zeros(K.CTRL_WORDS, dtype=torch.int32, device=self.device)
@@ -85,10 +86,14 @@ class Engine:
         for s in slots:
             self.pool.release(s)
             self.seq_len[s] = 0
+            self.kv.reset_slot(s)       # recurrent state of gated delta-net layers
 
     def truncate(self, slot: int, length: int):
         """Drop everything after ``length`` positions (rejected draft rows)."""
         assert length <= self.seq_len[slot]
+        if length < self.seq_len[slot] and self.cfg.n_gdn_layers:
+            raise NotImplementedError("a gated delta-net layer's recurrent state cannot be rewound: speculative rows and "
+                                      "prefix reuse are not available for the hybrid family")
         self.seq_len[slot] = length
         self.pool.truncate(slot, (length + PAGE - 1) // PAGE)
 
@@ -160,11 +165,16 @@ class Engine:
             # warm-up outside capture (sets function attributes, allocates split-K scratch), then
             # restore the control block the warm-up advanced
             saved = self.ctrl.clone()
+            # KV appends repeat harmlessly; a gated delta-net layer's recurrent update does not: its state is put back
+            saved_gdn = None if self.kv.gdn_state is None else (self.kv.gdn_conv.clone(), self.kv.gdn_state.clone())
             n0 = K.launch_count
             self._enqueue(m, advance)
             self.launches_per_step[key] = K.launch_count - n0
             torch.cuda.current_stream().synchronize()
             self.ctrl.copy_(saved)
+            if saved_gdn is not None:
+                self.kv.gdn_conv.copy_(saved_gdn[0])
+                self.kv.gdn_state.copy_(saved_gdn[1])
             g = torch.cuda.CUDAGraph()
             with torch.cuda.graph(g):
                 self._enqueue(m, advance)
@@ -225,8 +235,8 @@ class Engine:
     def _use_tc_prefill(self, n: int) -> bool:
         """Prompt chunks longer than the row kernels take go through the tcgen05 path when the shape
         has one (head size 128, bf16 KV, dense FFN or MoE with a grouped path)."""
-        if self.prefill_backend == "rows" or n <= self.max_rows:
-            return False
+        if self.prefill_backend == "rows" or n <= self.max_rows or self.cfg.n_gdn_layers:
+            return False        # (hybrid models ingest prompts through the row kernels: no chunked GDN prompt pass)
         ok = self.cfg.head_dim == 128 and (not self.kv.kv_int8 or (self.tp is None and self.model.nccl is None))
         if not ok and self.prefill_backend != "auto":
             raise ValueError(f"prefill backend {self.prefill_backend!r} needs head_dim 128 (and a bf16 KV cache under "

@@ -42,12 +42,22 @@ def _split_gate_up(ql: QLinear):
 def _emit_layer(out, cfg: ModelConfig, prefix: str, lw: LayerWeights, g_idx: bool):
     out[prefix + ".input_layernorm.weight"] = lw.input_norm.cpu().to(torch.bfloat16)
     out[prefix + ".post_attention_layernorm.weight"] = lw.post_norm.cpu().to(torch.bfloat16)
-    q, s = Q.from_w4b(lw.qkv.w4b.cpu(), lw.qkv.n)
-    a, b = cfg.q_dim, cfg.q_dim + cfg.kv_dim
-    _emit_linear(out, prefix + ".self_attn.q_proj", q[:, :a], s[:, :a], g_idx)
-    _emit_linear(out, prefix + ".self_attn.k_proj", q[:, a:b], s[:, a:b], g_idx)
-    _emit_linear(out, prefix + ".self_attn.v_proj", q[:, b:], s[:, b:], g_idx)
-    _emit_linear(out, prefix + ".self_attn.o_proj", *Q.from_w4b(lw.o.w4b.cpu(), lw.o.n), g_idx)
+    if lw.gdn is not None:
+        g, p = lw.gdn, prefix + ".linear_attn"
+        q, s = Q.from_w4b(g.in_proj.w4b.cpu(), g.in_proj.n)
+        a = g.in_proj.n - 2 * cfg.gdn_v_heads
+        _emit_linear(out, p + ".in_proj_qkvz", q[:, :a], s[:, :a], g_idx)
+        _emit_linear(out, p + ".in_proj_ba", q[:, a:], s[:, a:], g_idx)
+        _emit_linear(out, p + ".out_proj", *Q.from_w4b(g.out_proj.w4b.cpu(), g.out_proj.n), g_idx)
+        out[p + ".conv1d.weight"] = g.conv_w.cpu().reshape(-1, 1, 4).contiguous()
+        out[p + ".A_log"], out[p + ".dt_bias"], out[p + ".norm.weight"] = g.a_log.cpu(), g.dt_bias.cpu(), g.norm_w.cpu()
+    else:
+        q, s = Q.from_w4b(lw.qkv.w4b.cpu(), lw.qkv.n)
+        a, b = cfg.q_dim, cfg.q_dim + cfg.kv_dim
+        _emit_linear(out, prefix + ".self_attn.q_proj", q[:, :a], s[:, :a], g_idx)
+        _emit_linear(out, prefix + ".self_attn.k_proj", q[:, a:b], s[:, a:b], g_idx)
+        _emit_linear(out, prefix + ".self_attn.v_proj", q[:, b:], s[:, b:], g_idx)
+        _emit_linear(out, prefix + ".self_attn.o_proj", *Q.from_w4b(lw.o.w4b.cpu(), lw.o.n), g_idx)
 
     def mlp(p, gate_up: QLinear, down: QLinear):
         (gq, gs), (uq, us) = _split_gate_up(gate_up)

@@ -70,6 +70,18 @@ def test_sliding_window_model_matches_oracle():
     _check_generate(False, "int8", 0.08, cfg=preset("small-windowed"))
 
 
+def test_hybrid_gdn_model_matches_oracle():
+    """Layers 0 and 2 are gated delta-net layers (recurrent state per slot), 1 and 3 softmax attention; the prompt
+    goes through the row kernels in chunks of 64 rows, each chunk continuing the state of the one before."""
+    from b200serve.models.config import preset
+    eng, oracle, prompt, toks = _check_generate(True, "bf16", 0.05, cfg=preset("small-hybrid"))
+    # a second request in another slot starts from a zero state, and slot reuse resets it
+    again = eng.generate(prompt.tolist(), 8, slot=1)
+    assert again == toks[:8]
+    with pytest.raises(NotImplementedError):
+        eng.truncate(1, eng.seq_len[1] - 1)
+
+
 def test_tiny_dense_greedy_matches_oracle_eager():
     _check_generate(False, "bf16", 0.02)
 

@@ -428,3 +428,57 @@ def test_attn_rows_int8_kv_matches_per_row_kernel():
     k_.check_status()
     err = (out.float() - ref.float()).abs().max()
     assert err <= 2e-2 * ref.float().abs().max() + 2e-3, float(err)
+
+
+@pytest.mark.gpu
+def test_gdn_conv_and_step_match_fp32():
+    """Gated delta-net kernels against the same recurrence in fp32 torch: several rows of two slots in one step
+    (rows of a slot see each other's state), split-K partials folded by the convolution kernel."""
+    import torch.nn.functional as F
+    k_ = K()
+    torch.manual_seed(11)
+    n_k, n_v, dh, splits, slots = 2, 4, 128, 3, 3
+    kd, vd = n_k * dh, n_v * dh
+    cc, n = 2 * kd + vd, 2 * kd + 2 * vd + 2 * n_v
+    spec = [(2, 5, 0), (2, 6, 0), (0, 9, 0), (2, 7, 0), (0, 10, 0)]
+    m = len(spec)
+    part = torch.randn(splits, m, n) * 0.7
+    conv_w = torch.randn(cc, 4) * 0.5
+    conv_state = torch.randn(slots, cc, 3)
+    state = torch.randn(slots, n_v, dh, dh) * 0.1
+    a_log, dt_bias, norm_w = torch.log(torch.rand(n_v) * 4 + 0.5), torch.randn(n_v) * 0.5, 1 + 0.1 * torch.randn(dh)
+    eps = 1e-6
+    # reference
+    proj = part.sum(0)
+    conv_r, st_r = conv_state.clone(), state.clone()
+    ref = torch.zeros(m, vd)
+    for i, (slot, _, _) in enumerate(spec):
+        hist = torch.cat([conv_r[slot], proj[i, :cc, None]], dim=1)
+        y = F.silu((hist * conv_w).sum(1))
+        conv_r[slot] = hist[:, 1:]
+        q, k, v = y[:kd].view(n_k, dh), y[kd:2 * kd].view(n_k, dh), y[2 * kd:].view(n_v, dh)
+        z = proj[i, cc:cc + vd].view(n_v, dh)
+        b, a = proj[i, cc + vd:cc + vd + n_v], proj[i, cc + vd + n_v:]
+        q = q * torch.rsqrt((q * q).sum(-1, keepdim=True) + 1e-6) * dh ** -0.5
+        k = k * torch.rsqrt((k * k).sum(-1, keepdim=True) + 1e-6)
+        q, k = q.repeat_interleave(n_v // n_k, 0), k.repeat_interleave(n_v // n_k, 0)
+        S = st_r[slot] * torch.exp(-torch.exp(a_log) * F.softplus(a + dt_bias))[:, None, None]
+        delta = (v - torch.einsum("hij,hi->hj", S, k)) * torch.sigmoid(b)[:, None]
+        S = S + torch.einsum("hi,hj->hij", k, delta)
+        st_r[slot] = S
+        o = torch.einsum("hij,hi->hj", S, q)
+        ref[i] = (o * torch.rsqrt((o * o).mean(-1, keepdim=True) + eps) * norm_w * F.silu(z)).reshape(vd)
+    # device
+    ctrl = _ctrl(spec)
+    d = lambda t: t.cuda().contiguous()
+    act = torch.zeros(m, n, device="cuda")
+    conv_d, st_d = d(conv_state), d(state)
+    out = torch.zeros(m, vd, dtype=torch.bfloat16, device="cuda")
+    k_.gdn_conv(d(part), splits, m, n, cc, ctrl, d(conv_w), conv_d, act)
+    k_.gdn_step(act, m, n, n_k, n_v, dh, ctrl, d(a_log), d(dt_bias), d(norm_w), eps, st_d, out)
+    torch.cuda.synchronize()
+    k_.check_status()
+    assert (conv_d.cpu() - conv_r).abs().max() < 1e-5
+    assert (st_d.cpu() - st_r).abs().max() < 2e-3 * st_r.abs().max()
+    assert (st_d.cpu()[1] - state[1]).abs().max() == 0          # a slot without rows keeps its state
+    assert (out.float().cpu() - ref).abs().max() < 0.02 * ref.abs().max() + 1e-3

@@ -143,3 +143,24 @@ def test_snapshot_resolution(tmp_path, monkeypatch):
     assert resolve_snapshot(str(tmp_path)) == str(tmp_path)
     with pytest.raises(FileNotFoundError):
         resolve_snapshot("org/missing")
+
+
+def test_hybrid_checkpoint_round_trip(tmp_path):
+    """Gated delta-net layers (linear_attn.*) beside attention layers: write, load, same logits."""
+    from b200serve.models.config import preset
+    cfg = preset("small-hybrid")
+    w = _bf16_norms(random_weights(cfg, seed=7))
+    snap = write_checkpoint(w, str(tmp_path / "snap"))
+    got = load(snap, device="cpu", report=None)
+    assert got.cfg == replace(cfg, name=got.cfg.name)
+    assert [lw.gdn is not None for lw in got.layers] == [True, False, True, False]
+    for a, b in zip(got.layers, w.layers):
+        if b.gdn is None:
+            assert torch.equal(a.qkv.w4b, b.qkv.w4b)
+            continue
+        assert a.qkv is None and a.o is None
+        assert torch.equal(a.gdn.in_proj.w4b, b.gdn.in_proj.w4b) and torch.equal(a.gdn.out_proj.w4b, b.gdn.out_proj.w4b)
+        for f in ("conv_w", "a_log", "dt_bias", "norm_w"):
+            assert torch.equal(getattr(a.gdn, f), getattr(b.gdn, f)), f
+    ids = torch.arange(12) % cfg.vocab
+    assert torch.equal(OracleModel(got).forward(ids), OracleModel(w).forward(ids))

@@ -78,3 +78,15 @@ def test_sliding_window_layers_and_config_round_trip():
         a, b = OracleModel(w).forward(ids), OracleModel(w_full).forward(ids)
         assert (a[:8] - b[:8]).abs().max() < 1e-5
         assert (a[12:] - b[12:]).abs().max() > 1e-4
+
+
+def test_hybrid_gdn_incremental_equals_full():
+    """Gated delta-net layers: token-by-token and chunked passes carry the recurrent state and the convolution
+    window, so they equal one pass over the whole sequence."""
+    from b200serve.models.config import ModelConfig, preset
+    cfg = preset("small-hybrid")
+    assert [cfg.is_gdn_layer(i) for i in range(4)] == [True, False, True, False]
+    assert cfg.n_gdn_layers == 2 and cfg.gdn_index(2) == 1 and cfg.gdn_proj_dim == 2 * 256 + 2 * 512 + 8
+    back = ModelConfig.from_hf_config(cfg.to_hf_config())
+    assert (back.gdn_k_heads, back.gdn_v_heads, back.full_attn_every) == (2, 4, 2)
+    _consistency(cfg)
