@@ -50,11 +50,11 @@ def main(argv=None):
         eos = [i for i in (tok.token_to_id("<|im_end|>"), tok.token_to_id("<|endoftext|>")) if i is not None and i >= 0]
     spec = f.spec if f.spec != "auto" else ("mtp" if weights.mtp is not None else "off")
     hybrid = cfg.n_gdn_layers > 0
-    if hybrid and (spec != "off" or f.prefix_cache_gb != "0"):
-        # rejected draft rows and reused prefixes both rewind a sequence; a recurrent state cannot be rewound
-        sys.stderr.write("serve: gated delta-net layers keep a recurrent state per slot: speculative decoding and the "
-                         "prefix cache are switched off for this model\n")
-        spec = "off"
+    if hybrid and f.prefix_cache_gb != "0":
+        # a reused prefix needs the recurrent state at its end, which is not stored (rejected draft rows are
+        # handled: the engine keeps the state from before the last multi-row step and replays the kept rows)
+        sys.stderr.write("serve: gated delta-net layers keep a recurrent state per slot: the prefix cache is switched "
+                         "off for this model\n")
     adapter = EngineAdapter(engine, eos_ids=eos or (2,))
     if spec in ("mtp", "dflash", "dflash-lookup"):
         from ..runtime.spec import SpecAdapter

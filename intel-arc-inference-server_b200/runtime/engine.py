@@ -61,6 +61,7 @@ class Engine:
         self.block_table = torch.zeros(max_seqs, self.max_blocks, dtype=torch.int32, device=self.device)
         self.block_table_host = torch.zeros(max_seqs, self.max_blocks, dtype=torch.int32).pin_memory()
         self.seq_len = [0] * max_seqs
+        self._gdn_snap = None       # (rows, {slot: state before them}) of the last multi-row step of a hybrid model
         self.use_graphs = use_graphs
         self.graphs: Dict[Tuple[int, bool], torch.cuda.CUDAGraph] = {}
         self.prefill_backend = prefill_backend
@@ -91,11 +92,28 @@ class Engine:
     def truncate(self, slot: int, length: int):
         """Drop everything after ``length`` positions (rejected draft rows)."""
         assert length <= self.seq_len[slot]
+        replay = None
         if length < self.seq_len[slot] and self.cfg.n_gdn_layers:
-            raise NotImplementedError("a gated delta-net layer's recurrent state cannot be rewound: speculative rows and "
-                                      "prefix reuse are not available for the hybrid family")
-        self.seq_len[slot] = length
+            # A recurrent state cannot be rewound.  The last multi-row step left a copy of the slot's state from
+            # before its rows (the reference snapshots its GDN state the same way around verify rows): put it
+            # back and run the rows that stay once more.
+            snap = self._gdn_snap
+            rows = [] if snap is None else [r for r in snap[0] if r.slot == slot]
+            if not rows or slot not in snap[1] or length < rows[0].pos or self.seq_len[slot] != rows[-1].pos + 1:
+                raise NotImplementedError("a gated delta-net layer's recurrent state can only be rewound to a position "
+                                          "inside the last multi-row step (prefix reuse is not available for the "
+                                          "hybrid family)")
+            conv, state = snap[1][slot]
+            self.kv.gdn_conv[:, slot].copy_(conv)
+            self.kv.gdn_state[:, slot].copy_(state)
+            replay = [r for r in rows if r.pos < length]
+            self.seq_len[slot] = rows[0].pos
+            self._gdn_snap = None
+        self.seq_len[slot] = min(self.seq_len[slot], length)
         self.pool.truncate(slot, (length + PAGE - 1) // PAGE)
+        if replay:
+            self.forward_rows(replay, advance=False, read=False)
+            self._gdn_snap = None       # one rewind per step
 
     def _ensure_pages(self, slot: int, upto_len: int):
         if upto_len > self.max_len:
@@ -193,6 +211,11 @@ class Engine:
         """Run arbitrary rows (verify, batched decode, chunked ingest). KV of each row is appended."""
         for r in rows:
             self._ensure_pages(r.slot, r.pos + 1)
+        self._gdn_snap = None
+        if self.kv.gdn_state is not None and len(rows) > 1:
+            slots = sorted({r.slot for r in rows})
+            self._gdn_snap = (list(rows), {s: (self.kv.gdn_conv[:, s].clone(), self.kv.gdn_state[:, s].clone())
+                                           for s in slots})
         self._write_rows(rows)
         self._run(len(rows), advance)
         for r in rows:

@@ -43,14 +43,20 @@ def test_mtp_head_rows_match_oracle():
         assert drafts[0] == want
 
 
-@pytest.mark.parametrize("kind,dv", [("mtp", 0), ("dflash", 0), ("mtp", 512)])
+@pytest.mark.parametrize("kind,dv", [("mtp", 0), ("dflash", 0), ("mtp", 512), ("mtp-hybrid", 0)])
 def test_speculative_loop_is_lossless(kind, dv):
-    """Greedy output with drafts + verify + accept equals plain greedy decoding, token for token."""
+    """Greedy output with drafts + verify + accept equals plain greedy decoding, token for token.  The hybrid
+    variant has gated delta-net layers: rejected rows rewind the recurrent state through the engine's copy from
+    before the verify step and a replay of the kept rows."""
     from b200serve.native import host as H
     from b200serve.runtime.engine import Engine
     from b200serve.runtime.spec import SpecAdapter
     from b200serve.server.adapter import EngineAdapter
     cfg = _mtp_cfg()
+    if kind == "mtp-hybrid":
+        import dataclasses
+        from b200serve.models.config import preset
+        cfg, kind = dataclasses.replace(preset("small-hybrid"), mtp_layers=1), "mtp"
     w = random_weights(cfg, device="cuda", seed=5)
     g = torch.Generator().manual_seed(9)
     prompt = torch.randint(0, cfg.vocab, (100,), generator=g).tolist()
