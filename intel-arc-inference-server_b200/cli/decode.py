@@ -40,7 +40,7 @@ def main(argv=None):
     cfg = w.cfg
     depth = f.depth if (f.bench or f.profile) else 0
     ids = _ids(f.ids) if f.ids else None
-    need = max(depth, len(ids or []), f.prefill_length) + f.tg + f.n + 64
+    need = max(depth, len(ids or []), f.prefill_length) + (f.tg + 4) * max(1, f.repeats if cfg.n_gdn_layers else 1) + f.n + 64
     eng = Engine(w, max_seqs=1, max_len=need, kv_dtype=f.kv_cache, int8_head=f.int8_head,
                  prefill_backend=f.prefill_backend if f.prefill or f.bench else "rows")
     if ids is not None and not (f.bench or f.profile):
@@ -56,7 +56,8 @@ def main(argv=None):
     hbm, _, src = peaks()
     rows = []
     for _ in range(f.repeats):
-        eng.truncate(0, len(prompt))
+        if not cfg.n_gdn_layers:    # (a recurrent state is not rewound: a hybrid model's repeats continue the sequence)
+            eng.truncate(0, len(prompt))
         eng.decode_begin([0], [first])
         for _ in range(4):
             eng.decode_step(read=False)

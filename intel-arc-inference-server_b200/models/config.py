@@ -143,16 +143,26 @@ class ModelConfig:
             ]
         return out
 
+    def _mixer_params(self) -> float:
+        """Mean weights per layer of the token mixer (attention projections, or a gated delta-net layer's)."""
+        h = self.hidden
+        attn = self.qkv_dim * h + h * self.q_dim
+        g = self.n_gdn_layers
+        if not g:
+            return attn
+        gdn = self.gdn_proj_dim * h + h * self.gdn_value_dim
+        return (g * gdn + (self.n_layers - g) * attn) / self.n_layers
+
     def param_count(self) -> int:
         h = self.hidden
-        per = self.qkv_dim * h + h * self.q_dim
+        per = self._mixer_params()
         if self.is_moe:
             per += self.n_experts * 3 * self.expert_ffn * h + self.n_experts * h
             if self.shared_ffn:
                 per += 3 * self.shared_ffn * h + h
         else:
             per += 3 * self.ffn * h
-        return self.n_layers * per + 2 * self.vocab * h
+        return int(self.n_layers * per + 2 * self.vocab * h)
 
     def weight_bytes_per_token(self, lm_head_bytes_per_weight: float = 2.0) -> float:
         """Bytes of weights one decode step must read ("W" in the reference's
@@ -160,7 +170,7 @@ class ModelConfig:
         for every linear that is touched, plus the head."""
         h = self.hidden
         int4 = 0.5 + 2.0 / self.group_size
-        per = (self.qkv_dim * h + h * self.q_dim) * int4
+        per = self._mixer_params() * int4
         if self.is_moe:
             per += self.top_k * 3 * self.expert_ffn * h * int4 + self.n_experts * h * 2
             if self.shared_ffn:
@@ -171,7 +181,7 @@ class ModelConfig:
 
     def kv_bytes_per_token(self, kv_dtype: str = "bf16") -> int:
         per_head = self.head_dim * (2 if kv_dtype == "bf16" else 1) + (4 if kv_dtype == "int8" else 0)
-        return self.n_layers * 2 * self.n_kv_heads * per_head
+        return (self.n_layers - self.n_gdn_layers) * 2 * self.n_kv_heads * per_head
 
     def to_hf_config(self) -> dict:
         d = {
@@ -264,6 +274,13 @@ def dense_27b() -> ModelConfig:
     return ModelConfig("dense-27b", 64, 5120, 40, 8, 128, 17408, 151936)
 
 
+def hybrid_27b() -> ModelConfig:
+    """27B-shape hybrid decoder: the dense 27B shape with three gated delta-net layers (16 key / 48 value heads of
+    128) before every softmax-attention layer."""
+    return ModelConfig("hybrid-27b", 64, 5120, 40, 8, 128, 17408, 151936, full_attn_every=4, gdn_k_heads=16,
+                       gdn_v_heads=48, architecture="B200HybridForCausalLM")
+
+
 def moe_35b_a3b() -> ModelConfig:
     """35B-A3B-shape MoE: 40 layers, hidden 2048, 16 q / 4 kv heads, 256 experts top-8 + shared."""
     return ModelConfig("moe-35b-a3b", 40, 2048, 16, 4, 128, 0, 151936, n_experts=256, top_k=8,
@@ -278,7 +295,7 @@ def dflash_drafter(target: ModelConfig) -> ModelConfig:
 
 
 PRESETS = {
-    "tiny-dense": tiny_dense, "tiny-moe": tiny_moe, "small-dense": small_dense, "small-windowed": small_windowed, "small-hybrid": small_hybrid, "small-moe": small_moe, "dense-27b": dense_27b, "moe-35b-a3b": moe_35b_a3b,
+    "tiny-dense": tiny_dense, "tiny-moe": tiny_moe, "small-dense": small_dense, "small-windowed": small_windowed, "small-hybrid": small_hybrid, "small-moe": small_moe, "dense-27b": dense_27b, "hybrid-27b": hybrid_27b, "moe-35b-a3b": moe_35b_a3b,
 }
 
 

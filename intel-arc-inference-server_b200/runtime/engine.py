@@ -61,7 +61,7 @@ class Engine:
         self.block_table = torch.zeros(max_seqs, self.max_blocks, dtype=torch.int32, device=self.device)
         self.block_table_host = torch.zeros(max_seqs, self.max_blocks, dtype=torch.int32).pin_memory()
         self.seq_len = [0] * max_seqs
-        self._gdn_snap = None       # (rows, {slot: state before them}) of the last multi-row step of a hybrid model
+        self._gdn_snap = None       # (rows, {slot: state before them}) of the last forward_rows step of a hybrid model
         self.use_graphs = use_graphs
         self.graphs: Dict[Tuple[int, bool], torch.cuda.CUDAGraph] = {}
         self.prefill_backend = prefill_backend
@@ -212,7 +212,7 @@ class Engine:
         for r in rows:
             self._ensure_pages(r.slot, r.pos + 1)
         self._gdn_snap = None
-        if self.kv.gdn_state is not None and len(rows) > 1:
+        if self.kv.gdn_state is not None:
             slots = sorted({r.slot for r in rows})
             self._gdn_snap = (list(rows), {s: (self.kv.gdn_conv[:, s].clone(), self.kv.gdn_state[:, s].clone())
                                            for s in slots})
