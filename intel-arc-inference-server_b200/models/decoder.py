@@ -61,7 +61,7 @@ class StepBuffers:
             self.gdn_act = torch.zeros(max_rows, cfg.gdn_proj_dim, dtype=f32, device=device)
             self.gdn_out = torch.zeros(max_rows, cfg.gdn_value_dim, dtype=bf, device=device)
         self.xq = torch.zeros(max_rows * (kmax // 64) * 128, dtype=torch.uint8, device=device)    # pre-quantised rows
-        self.xq_gs = torch.zeros(max_rows * (kmax // 64) * 2, dtype=torch.int32, device=device)
+        self.xq_gs = torch.zeros(K.quant_slots(max_rows) * (kmax // 64) * 2, dtype=torch.int32, device=device)   # {scale, -8 sum} per group and token slot
         self._parts = {}
         self.device = device
 

@@ -138,11 +138,19 @@ def gemv_w4_fused(w4b, x, out, m, n, k, splits, *, x_mode=0, s_in=1, x_slice=0, 
     _check(rc, "gemv_w4_fused")
 
 
+def quant_slots(m: int) -> int:
+    """Token slots per 64-k group in ``xq_gs`` for ``m`` rows: 8 per row tile of the GEMV (8, 16, 32 or 64)."""
+    return 8 if m <= 8 else (16 if m <= 16 else (32 if m <= 32 else 64))
+
+
 def quant_x(x, m, k, xq, xq_gs, *, x_mode=0, s_in=1, x_slice=0, ldx=None, norm_w=None, norm_ssq=None, norm_eps=0.0):
     """Quantises ``m`` activation rows once for ``gemv_w4_fused(..., x_mode=3)``: 15-bit two-limb integers per
     64-k group in the GEMV's operand order (``xq``) and the groups' {scale, -8 sum} (``xq_gs``)."""
     if ldx is None:
         ldx = 2 * k if x_mode == 1 else k
+    if m > 64 or xq.numel() * xq.element_size() < m * (k // 64) * 128 \
+            or xq_gs.numel() * xq_gs.element_size() < quant_slots(m) * (k // 64) * 8:
+        raise ValueError(f"quant_x: buffers too small for {m} rows of {k} (xq_gs holds {quant_slots(m)} token slots per group)")
     rc = lib().b2_quant_x(_p(x), m, k, ldx, x_mode, s_in, ctypes.c_longlong(x_slice), _p(norm_w), _p(norm_ssq),
                           ctypes.c_float(norm_eps), _p(xq), _p(xq_gs), _stream())
     _check(rc, "quant_x")
@@ -192,18 +200,27 @@ def attn_rows(q, k_cache, v_cache, block_table, ctrl, o_part, ml_part, out, tick
         _check(rc, "attn_merge")
 
 
-def gdn_conv(part, splits, m, n, conv_ch, ctrl, conv_w, conv_state, act):
+def gdn_conv(part, splits, m, n, conv_ch, ctrl, conv_w, conv_state, act, slot: int = -1):
     """Folds the split-K partials of a gated delta-net layer's input projection into ``act`` [m][n]; the first
-    ``conv_ch`` columns pass through the slot's 4-tap causal convolution (state [slots][conv_ch][3]) and SiLU."""
-    _check(lib().b2_gdn_conv(_p(part), splits, m, n, conv_ch, _p(ctrl), _p(conv_w), _p(conv_state), _p(act), _stream()),
-           "gdn_conv")
+    ``conv_ch`` columns pass through the slot's 4-tap causal convolution (state [slots][conv_ch][3]) and SiLU.
+    ``ctrl`` maps rows to slots (decode / verify rows); ``ctrl=None`` with ``slot``: a prompt chunk of one slot."""
+    _check(lib().b2_gdn_conv(_p(part), splits, m, n, conv_ch, _p(ctrl), slot, _p(conv_w), _p(conv_state), _p(act),
+                             _stream()), "gdn_conv")
 
 
-def gdn_step(act, m, n, n_k, n_v, head_dim, ctrl, a_log, dt_bias, norm_w, eps, state, out):
+def gdn_step(act, m, n, n_k, n_v, head_dim, ctrl, a_log, dt_bias, norm_w, eps, state, out, slot: int = -1):
     """One recurrent step per row and value head over ``state`` [slots][n_v][128][128]; ``out`` [m][n_v * 128] bf16
     is the gated, normalised read-out."""
-    _check(lib().b2_gdn_step(_p(act), m, n, n_k, n_v, head_dim, _p(ctrl), _p(a_log), _p(dt_bias), _p(norm_w),
+    _check(lib().b2_gdn_step(_p(act), m, n, n_k, n_v, head_dim, _p(ctrl), slot, _p(a_log), _p(dt_bias), _p(norm_w),
                              ctypes.c_float(eps), _p(state), _p(out), _stream()), "gdn_step")
+
+
+def gdn_chunk(act, m, n, n_k, n_v, head_dim, slot, a_log, dt_bias, norm_w, eps, state, out):
+    """A prompt chunk of ``m`` rows of ``slot`` through a gated delta-net layer's recurrence (after ``gdn_conv``):
+    normalisation and gates in parallel over the rows, one sequential scan per value head, gated norm in parallel.
+    ``act`` is overwritten with intermediate values."""
+    _check(lib().b2_gdn_chunk(_p(act), m, n, n_k, n_v, head_dim, slot, _p(a_log), _p(dt_bias), _p(norm_w),
+                              ctypes.c_float(eps), _p(state), _p(out), _stream()), "gdn_chunk")
 
 
 def sample_rows(logits, m, n_valid, temperature, top_k, top_p, seed, token, status, penalty=None, hist=None,

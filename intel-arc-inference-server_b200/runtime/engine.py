@@ -258,8 +258,10 @@ class Engine:
     def _use_tc_prefill(self, n: int) -> bool:
         """Prompt chunks longer than the row kernels take go through the tcgen05 path when the shape
         has one (head size 128, bf16 KV, dense FFN or MoE with a grouped path)."""
-        if self.prefill_backend == "rows" or n <= self.max_rows or self.cfg.n_gdn_layers:
-            return False        # (hybrid models ingest prompts through the row kernels: no chunked GDN prompt pass)
+        if self.prefill_backend == "rows" or n <= self.max_rows:
+            return False
+        if self.cfg.n_gdn_layers and (self.kv.kv_int8 or self.tp is not None or self.model.nccl is not None):
+            return False        # hybrid models: the layer-major int8-KV pass and the parallel runners know no GDN layers
         ok = self.cfg.head_dim == 128 and (not self.kv.kv_int8 or (self.tp is None and self.model.nccl is None))
         if not ok and self.prefill_backend != "auto":
             raise ValueError(f"prefill backend {self.prefill_backend!r} needs head_dim 128 (and a bf16 KV cache under "

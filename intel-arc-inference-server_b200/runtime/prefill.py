@@ -88,6 +88,10 @@ class PrefillRunner:
         self.attn = torch.empty(c, cfg.q_dim, dtype=bf, device=self.dev)
         ffn = cfg.ffn if not cfg.is_moe else max(cfg.expert_ffn, cfg.shared_ffn)
         self.act = torch.empty(c, max(ffn, 1), dtype=bf, device=self.dev)
+        if cfg.n_gdn_layers:     # gated delta-net layers: projection, convolved activations, read-out
+            self.gdn_proj = torch.empty(c, cfg.gdn_proj_dim, dtype=f32, device=self.dev)
+            self.gdn_act = torch.empty(c, cfg.gdn_proj_dim, dtype=f32, device=self.dev)
+            self.gdn_out = torch.empty(c, cfg.gdn_value_dim, dtype=bf, device=self.dev)
         self.ids_host = torch.empty(max_chunk, dtype=torch.int64).pin_memory()
         self.ids_dev = torch.empty(max_chunk, dtype=torch.int64, device=self.dev)
         self._slab: Optional[torch.Tensor] = None
@@ -143,17 +147,31 @@ class PrefillRunner:
                 pr.begin(name)
         phase("norm")
         K.resid_norm(1, c, h, lw.input_norm, cfg.rms_eps, resid, x, resid_in=resid, splits=0)
-        qkv = self.qkv[:c]
-        phase("qkv")
-        self.linear(lw.qkv, x, qkv, G.EPI_F32)
-        phase("rope+append")
-        K.rope_append(qkv, 0, 1, c, None, eng.block_table, eng.max_blocks, m.cos_t, m.sin_t, cfg.n_q_heads,
-                      cfg.n_kv_heads, cfg.head_dim, self.q, kc, vc, ks, vs, eng.kv.kv_int8, req=slot, pos0=pos0)
-        phase("attention")
-        K.attn_prefill(self.q, kc, vc, bt_row, self.attn, c, pos0, cfg.n_q_heads, cfg.n_kv_heads, cfg.head_dim,
-                       eng.kv.num_pages, eng.max_blocks, m.scale, window=m._window(kv_index))
-        phase("o")
-        self.linear(lw.o, self.attn[:c], resid, G.EPI_RESID_ADD, resid=resid)
+        if lw.gdn is not None:
+            # gated delta-net layer: the projections run as GEMMs over the chunk; the recurrence walks the chunk's
+            # rows in order inside one CTA per value head (a sequential scan, not the chunked WY form)
+            g, gi, n = lw.gdn, cfg.gdn_index(kv_index), cfg.gdn_proj_dim
+            phase("gdn_in")
+            self.linear(g.in_proj, x, self.gdn_proj[:c], G.EPI_F32)
+            phase("gdn_scan")
+            K.gdn_conv(self.gdn_proj, 1, c, n, cfg.gdn_conv_channels, None, g.conv_w, eng.kv.gdn_conv[gi],
+                       self.gdn_act, slot=slot)
+            K.gdn_chunk(self.gdn_act, c, n, cfg.gdn_k_heads, cfg.gdn_v_heads, cfg.gdn_head_dim, slot, g.a_log,
+                        g.dt_bias, g.norm_w, cfg.rms_eps, eng.kv.gdn_state[gi], self.gdn_out)
+            phase("gdn_out")
+            self.linear(g.out_proj, self.gdn_out[:c], resid, G.EPI_RESID_ADD, resid=resid)
+        else:
+            qkv = self.qkv[:c]
+            phase("qkv")
+            self.linear(lw.qkv, x, qkv, G.EPI_F32)
+            phase("rope+append")
+            K.rope_append(qkv, 0, 1, c, None, eng.block_table, eng.max_blocks, m.cos_t, m.sin_t, cfg.n_q_heads,
+                          cfg.n_kv_heads, cfg.head_dim, self.q, kc, vc, ks, vs, eng.kv.kv_int8, req=slot, pos0=pos0)
+            phase("attention")
+            K.attn_prefill(self.q, kc, vc, bt_row, self.attn, c, pos0, cfg.n_q_heads, cfg.n_kv_heads, cfg.head_dim,
+                           eng.kv.num_pages, eng.max_blocks, m.scale, window=m._window(kv_index))
+            phase("o")
+            self.linear(lw.o, self.attn[:c], resid, G.EPI_RESID_ADD, resid=resid)
         phase("norm")
         K.resid_norm(1, c, h, lw.post_norm, cfg.rms_eps, resid, x, resid_in=resid, splits=0)
         if lw.gate_up is not None:
@@ -174,6 +192,7 @@ class PrefillRunner:
         eng, cfg, m = self.eng, self.cfg, self.eng.model
         c, h = len(ids), cfg.hidden
         eng._ensure_pages(slot, pos0 + c)
+        eng._gdn_snap = None      # (a hybrid model's recurrent state moves on: nothing to rewind to)
         self.ids_host[:c] = torch.as_tensor(ids, dtype=torch.int64)
         self.ids_dev[:c].copy_(self.ids_host[:c], non_blocking=True)
         resid, x = self.resid[:c], self.x[:c]

@@ -306,7 +306,7 @@ def test_prequantised_rows_give_the_same_bits_as_in_kernel_staging(m):
     b = torch.zeros_like(a)
     K.gemv_w4(w4b, x, a, m, n, k, s)
     xq = torch.zeros(m * (k // 64) * 128, dtype=torch.uint8, device="cuda")
-    gs = torch.zeros(m * (k // 64) * 2, dtype=torch.int32, device="cuda")
+    gs = torch.zeros(K.quant_slots(m) * (k // 64) * 2, dtype=torch.int32, device="cuda")   # 8 token slots per row tile
     K.quant_x(x, m, k, xq, gs)
     K.gemv_w4_fused(w4b, xq, b, m, n, k, s, x_mode=3, norm_ssq=gs)
     torch.cuda.synchronize()
@@ -482,3 +482,18 @@ def test_gdn_conv_and_step_match_fp32():
     assert (st_d.cpu() - st_r).abs().max() < 2e-3 * st_r.abs().max()
     assert (st_d.cpu()[1] - state[1]).abs().max() == 0          # a slot without rows keeps its state
     assert (out.float().cpu() - ref).abs().max() < 0.02 * ref.abs().max() + 1e-3
+    # the prompt-chunk form (normalisation and gates in parallel over the rows, one scan, gated norm in parallel):
+    # the same rows as ONE slot's chunk give what the step kernel gives for them
+    ctrl1 = _ctrl([(1, i, 0) for i in range(m)])
+    conv_a, conv_b, st_a, st_b = d(conv_state), d(conv_state), d(state), d(state)
+    act_a, act_b = torch.zeros(m, n, device="cuda"), torch.zeros(m, n, device="cuda")
+    out_a, out_b = torch.zeros_like(out), torch.zeros_like(out)
+    k_.gdn_conv(d(part), splits, m, n, cc, ctrl1, d(conv_w), conv_a, act_a)
+    k_.gdn_step(act_a, m, n, n_k, n_v, dh, ctrl1, d(a_log), d(dt_bias), d(norm_w), eps, st_a, out_a)
+    k_.gdn_conv(d(part), splits, m, n, cc, None, d(conv_w), conv_b, act_b, slot=1)
+    k_.gdn_chunk(act_b, m, n, n_k, n_v, dh, 1, d(a_log), d(dt_bias), d(norm_w), eps, st_b, out_b)
+    torch.cuda.synchronize()
+    k_.check_status()
+    assert torch.equal(conv_a, conv_b)
+    assert (st_a - st_b).abs().max() < 1e-4 * st_a.abs().max()
+    assert (out_a.float() - out_b.float()).abs().max() < 0.01 * out_a.float().abs().max() + 1e-3

@@ -50,7 +50,7 @@ def test_attn_prefill_matches_softmax(c, pos0, n_q, n_kv, window):
     assert (got - ref).abs().max() < 0.02 * ref.abs().max() + 2e-3
 
 
-@pytest.mark.parametrize("backend", ["bf16", "bf16-resident", "int8", "bf16-windowed"])
+@pytest.mark.parametrize("backend", ["bf16", "bf16-resident", "int8", "bf16-windowed", "bf16-hybrid", "int8-hybrid"])
 def test_prefill_runner_matches_oracle(backend):
     from b200serve.runtime.engine import Engine
     from b200serve.ops import lib as K
@@ -58,6 +58,9 @@ def test_prefill_runner_matches_oracle(backend):
     if backend == "bf16-windowed":      # layers 0 and 2 attend to the last 48 positions
         from b200serve.models.config import preset
         cfg, backend = preset("small-windowed"), "bf16"
+    if backend.endswith("-hybrid"):     # layers 0 and 2 are gated delta-net layers: GEMM projections + sequential scan
+        from b200serve.models.config import preset
+        cfg, backend = preset("small-hybrid"), backend.split("-")[0]
     w = random_weights(cfg, seed=3)
     oracle = OracleModel(w)
     g = torch.Generator().manual_seed(5)
