@@ -100,7 +100,7 @@ def main():
     ap.add_argument("--model", default="dense-27b")
     ap.add_argument("--depth", type=int, default=4096, help="context length the decode steps run at")
     ap.add_argument("--prefill-len", type=int, default=4096)
-    ap.add_argument("--what", default="all", help="decode | prefill | moe | all")
+    ap.add_argument("--what", default="all", help="decode | prefill | moe | spec | prefix | hybrid | tp | ep | all")
     ap.add_argument("--kv-cache", default="bf16")
     ap.add_argument("--int8-head", action="store_true")
     ap.add_argument("--prefill-backend", default="auto")
@@ -209,6 +209,9 @@ def main():
         from b200serve.utils.benchlib import run_prefix_bench
         # every rank pins its own host store: a quarter of the prefix when several ranks share one host
         guarded("prefix_cache", lambda: run_prefix_bench(args, barrier, 65536 if world == 1 else 16384))
+    if world == 1 and args.what in ("all", "hybrid"):
+        from b200serve.utils.benchlib import run_hybrid_bench
+        guarded("hybrid", lambda: run_hybrid_bench(args, barrier))
     if world > 1 and args.what in ("all", "tp"):
         guarded("tp", tp_extra)
     if world > 1 and args.what in ("all", "ep"):

@@ -190,3 +190,43 @@ def run_prefix_bench(args, barrier, prefix_tokens: int = 65536, suffix_tokens: i
     K.check_status()
     del eng, store, weights
     return out
+
+
+def run_hybrid_bench(args, barrier) -> dict:
+    """The 27B shape with gated delta-net layers (three before every attention layer): prompt pass (GEMM
+    projections + sequential scan) and decode of one request, device-timed like the headline numbers."""
+    cfg = preset("hybrid-27b")
+    dev = torch.device("cuda", torch.cuda.current_device())
+    weights = random_weights(cfg, device=dev, seed=0, exact=False)
+    n, steps = args.prefill_len, max(8, min(args.steps, 64))
+    eng = Engine(weights, max_seqs=1, max_len=n + 2 * steps + 64, prefill_backend=args.prefill_backend)
+    g = torch.Generator().manual_seed(2)
+    ids = torch.randint(0, cfg.vocab, (n,), generator=g).tolist()
+    for _ in range(2):
+        eng.reset(0)
+        first = eng.prefill(0, ids)
+    barrier()
+    e0, e1 = _events()
+    e0.record()
+    eng.reset(0)
+    first = eng.prefill(0, ids)
+    e1.record()
+    barrier()
+    pf_ms = e0.elapsed_time(e1)
+    eng.decode_begin([0], [first])
+    for _ in range(max(3, args.warmup)):
+        eng.decode_step(read=False)
+    barrier()
+    e0, e1 = _events()
+    e0.record()
+    for _ in range(steps):
+        eng.decode_step(read=False)
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1) / steps
+    nbytes = cfg.weight_bytes_per_token(2.0) + cfg.kv_bytes_per_token("bf16") * n
+    return {"model": cfg.name, "layers": f"{cfg.n_gdn_layers} gated delta-net + {cfg.n_layers - cfg.n_gdn_layers} attention",
+            "decode": {"ms_per_step": ms, "tokens_per_s": 1e3 / ms, "depth": n, "steps": steps,
+                       "achieved_GBps": nbytes / (ms / 1e3) / 1e9},
+            "prefill": {"ms": pf_ms, "tokens": n, "tokens_per_s": n / pf_ms * 1e3,
+                        "backend": eng._prefill.backend if eng._prefill is not None else "rows"}}
