@@ -62,6 +62,11 @@ class HostWire:
         self.calls[rank] += 1
         n = self.calls[rank]
         slot = n & 1
+        if self.status[rank] is not None:
+            # Failure latch: a rank whose wait ran out takes no further part until it is reset.  Without it the
+            # rank's next push would reuse the slot of the epoch its peer may still be waiting for, and the peer
+            # would report that late flag as stale data instead of its own time-out.
+            return None
         for reader in range(self.world):
             key = (rank, reader)
             with self._lock:

@@ -141,12 +141,20 @@ class Engine:
         the layout is ``[layer][page][kv head][16][head dim]`` per tensor and does not depend on the parallel mode."""
         if begin % PAGE or (end % PAGE and end != self.seq_len[slot]) or not 0 <= begin <= end <= self.seq_len[slot]:
             raise ValueError("save_kv takes whole pages inside the sequence")
+        if self.kv.gdn_state is not None and end != self.seq_len[slot]:
+            raise ValueError("save_kv: a hybrid model's snapshot ends at the sequence end (the recurrent state of its "
+                             "gated delta-net layers is the one after the last position)")
         pages = list(self.pool.table(slot))[begin // PAGE: (end + PAGE - 1) // PAGE]
         idx = torch.as_tensor(pages, device=self.device, dtype=torch.int64)
         tensors = {"k": self.kv.k, "v": self.kv.v}
         if self.kv.kv_int8:
             tensors.update({"k_scale": self.kv.k_scale, "v_scale": self.kv.v_scale})
         out = {"begin": begin, "end": end, "kv_dtype": self.kv_dtype}
+        if self.kv.gdn_state is not None:      # the recurrent state and the convolution window after position end - 1
+            for name, t in (("gdn_conv", self.kv.gdn_conv), ("gdn_state", self.kv.gdn_state)):
+                host = torch.empty((t.shape[0],) + tuple(t.shape[2:]), dtype=t.dtype).pin_memory()
+                host.copy_(t[:, slot], non_blocking=True)
+                out[name] = host
         for name, t in tensors.items():
             host = torch.empty((t.shape[0], len(pages)) + tuple(t.shape[2:]), dtype=t.dtype).pin_memory()
             host.copy_(t.index_select(1, idx), non_blocking=True)
@@ -167,6 +175,12 @@ class Engine:
             tensors.update({"k_scale": self.kv.k_scale, "v_scale": self.kv.v_scale})
         for name, t in tensors.items():
             t.index_copy_(1, idx, blob[name].to(self.device, non_blocking=True))
+        if self.kv.gdn_state is not None:
+            if "gdn_state" not in blob:
+                raise ValueError("load_kv: the blob holds no recurrent state for this hybrid model")
+            self.kv.gdn_conv[:, slot].copy_(blob["gdn_conv"].to(self.device, non_blocking=True))
+            self.kv.gdn_state[:, slot].copy_(blob["gdn_state"].to(self.device, non_blocking=True))
+            self._gdn_snap = None
         self.seq_len[slot] = end
 
     # ------------------------------------------------------------------ running a step

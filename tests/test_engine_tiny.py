@@ -80,6 +80,19 @@ def test_hybrid_gdn_model_matches_oracle():
     assert again == toks[:8]
     with pytest.raises(NotImplementedError):
         eng.truncate(1, eng.seq_len[1] - 1)
+    # a session snapshot carries the recurrent state: saved after the prompt, put into the other slot, the
+    # continuation is the same
+    eng.reset(1)
+    first = eng.prefill(1, prompt.tolist())
+    blob = eng.save_kv(1, 0, eng.seq_len[1])
+    assert "gdn_state" in blob
+    with pytest.raises(ValueError):
+        eng.save_kv(1, 0, 64)
+    eng.reset(0)
+    eng.load_kv(0, blob)
+    eng.decode_begin([0], [first])
+    cont = [first] + [eng.decode_step()[0] for _ in range(7)]
+    assert cont == toks[:8]
 
 
 def test_tiny_dense_greedy_matches_oracle_eager():

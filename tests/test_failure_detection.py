@@ -25,7 +25,7 @@ def test_host_mirror_all_ranks_hold_identical_bits():
 
 
 def test_dropped_flag_times_out_once_and_latches():
-    w = HostWire(2, 64, bound_s=0.1)
+    w = HostWire(2, 64, bound_s=0.2)
     w.drop_next(writer=1, reader=0)            # rank 0 never sees rank 1's first flag
     out = run_ranks(w, 3, _parts)
     assert out[0][0] is None and w.status[0] == (TIMEOUT, 1, 1)
@@ -36,14 +36,14 @@ def test_dropped_flag_times_out_once_and_latches():
 
 
 def test_flag_before_data_is_reported_as_stale():
-    w = HostWire(2, 64, bound_s=0.1)
+    w = HostWire(2, 64, bound_s=0.2)
     w.skip_data(writer=0, reader=1)
     out = run_ranks(w, 1, _parts)
     assert out[1][0] is None and w.status[1][0] == STALE
 
 
 def test_rank_that_leaves_between_calls_costs_one_bound():
-    w = HostWire(3, 64, bound_s=0.1)
+    w = HostWire(3, 64, bound_s=0.2)
     first = run_ranks(w, 1, _parts)
     assert all(o[0] is not None for o in first)
     w.kill(2)                                   # leaves between steps, nothing in flight
