@@ -39,7 +39,7 @@ class MemoryPlan:
 def weight_bytes(cfg: ModelConfig, int8_head: bool = False, tp: int = 1, ep: int = 1) -> int:
     h = cfg.hidden
     int4 = 0.5 + 2.0 / 64
-    per = (cfg.qkv_dim * h + h * cfg.q_dim) * int4 / tp
+    per = cfg._mixer_params() * int4 / tp      # attention projections, or a gated delta-net layer's (mean over layers)
     if cfg.is_moe:
         per += cfg.n_experts * 3 * cfg.expert_ffn * h * int4 / ep + cfg.n_experts * h * 2
         per += 3 * cfg.shared_ffn * h * int4 / tp
@@ -52,7 +52,16 @@ def weight_bytes(cfg: ModelConfig, int8_head: bool = False, tp: int = 1, ep: int
 
 def kv_bytes_per_page(cfg: ModelConfig, kv_dtype: str, tp: int = 1) -> int:
     per_tok_head = cfg.head_dim * (1 if kv_dtype == "int8" else 2) + (4 if kv_dtype == "int8" else 0)
-    return (cfg.n_layers + cfg.mtp_layers) * 2 * (cfg.n_kv_heads // tp) * per_tok_head * cfg.page_size
+    return (cfg.n_layers - cfg.n_gdn_layers + cfg.mtp_layers) * 2 * (cfg.n_kv_heads // tp) * per_tok_head * cfg.page_size
+
+
+def gdn_state_bytes_per_slot(cfg: ModelConfig) -> int:
+    """Recurrent state (fp32, one head_dim x head_dim matrix per value head) and convolution window of the gated
+    delta-net layers of one sequence slot; twice, for the copy that rewinds rejected rows."""
+    if not cfg.n_gdn_layers:
+        return 0
+    per = cfg.gdn_v_heads * cfg.gdn_head_dim * cfg.gdn_head_dim * 4 + cfg.gdn_conv_channels * 3 * 4
+    return 2 * cfg.n_gdn_layers * per
 
 
 def step_scratch_bytes(cfg: ModelConfig, max_rows: int = 64, nsplit: int = 32) -> int:
@@ -93,7 +102,7 @@ def plan(cfg: ModelConfig, max_seqs: int, max_len, kv_dtype: str = "bf16", int8_
     st = step_scratch_bytes(cfg)
     pf = prefill_scratch_bytes(cfg, prefill_chunk, prefill_backend)
     page = kv_bytes_per_page(cfg, kv_dtype, tp)
-    fixed = w + resident + st + pf + RESERVE_BYTES
+    fixed = w + resident + st + pf + RESERVE_BYTES + max_seqs * gdn_state_bytes_per_slot(cfg)
     if fixed >= budget:
         raise ValueError(f"{cfg.name}: weights and scratch need {fixed / 2**30:.1f} GiB of {budget / 2**30:.1f} GiB "
                          "before any KV cache")

@@ -78,3 +78,17 @@ def test_vram_probe_with_fake_nvml():
     assert vram.check_placement(two, need_nvlink=True) == []
     bad = vram.check_placement(g, need_bytes=100 << 30, need_nvlink=True)
     assert any("GPU 2" in b and "GiB free" in b for b in bad) and any("not connected by NVLink" in b for b in bad)
+
+
+def test_plan_counts_the_recurrent_state_of_hybrid_models():
+    from b200serve.models.config import preset
+    from b200serve.runtime import memory_plan as MP
+    dense, hyb = preset("dense-27b"), preset("hybrid-27b")
+    per_slot = MP.gdn_state_bytes_per_slot(hyb)
+    assert MP.gdn_state_bytes_per_slot(dense) == 0
+    assert per_slot == 2 * 48 * (48 * 128 * 128 * 4 + (2 * 16 * 128 + 48 * 128) * 3 * 4)
+    # only the 16 attention layers hold KV pages
+    assert MP.kv_bytes_per_page(hyb, "bf16") * 4 == MP.kv_bytes_per_page(dense, "bf16")
+    a, b = MP.plan(hyb, 1, 4096), MP.plan(hyb, 8, 4096)
+    assert b.total - a.total >= 7 * per_slot
+    assert MP.weight_bytes(hyb) > MP.weight_bytes(dense)
