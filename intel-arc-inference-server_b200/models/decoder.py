@@ -88,10 +88,17 @@ class KVCache:
         self.kv_int8 = kv_dtype == "int8"
         dt = torch.int8 if self.kv_int8 else torch.bfloat16
         self.num_pages = num_pages
-        self.k = torch.zeros(n_layers, num_pages, cfg.n_kv_heads, cfg.page_size, cfg.head_dim, dtype=dt, device=device)
+        self.n_layers = n_layers                # layers addressed by ``layer`` (trunk + draft-head layers)
+        # gated delta-net layers hold no KV: only the others get a plane of the cache
+        self._plane = {}
+        for li in range(n_layers):
+            if not cfg.is_gdn_layer(li):
+                self._plane[li] = len(self._plane)
+        planes = max(1, len(self._plane))
+        self.k = torch.zeros(planes, num_pages, cfg.n_kv_heads, cfg.page_size, cfg.head_dim, dtype=dt, device=device)
         self.v = torch.zeros_like(self.k)
         if self.kv_int8:
-            self.k_scale = torch.zeros(n_layers, num_pages, cfg.n_kv_heads, cfg.page_size, dtype=torch.float32, device=device)
+            self.k_scale = torch.zeros(planes, num_pages, cfg.n_kv_heads, cfg.page_size, dtype=torch.float32, device=device)
             self.v_scale = torch.zeros_like(self.k_scale)
         else:
             self.k_scale = self.v_scale = None
@@ -109,9 +116,10 @@ class KVCache:
             self.gdn_state[:, slot].zero_()
 
     def layer(self, li: int):
-        ks = self.k_scale[li] if self.kv_int8 else None
-        vs = self.v_scale[li] if self.kv_int8 else None
-        return self.k[li], self.v[li], ks, vs
+        j = self._plane[li]
+        ks = self.k_scale[j] if self.kv_int8 else None
+        vs = self.v_scale[j] if self.kv_int8 else None
+        return self.k[j], self.v[j], ks, vs
 
 
 class DecoderModel:

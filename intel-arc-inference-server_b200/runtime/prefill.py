@@ -138,7 +138,6 @@ class PrefillRunner:
         eng, cfg, m = self.eng, self.cfg, self.eng.model
         h = cfg.hidden
         bt_row = eng.block_table[slot]
-        kc, vc, ks, vs = eng.kv.layer(kv_index)
         pr = self.profile
 
         def phase(name):
@@ -161,6 +160,7 @@ class PrefillRunner:
             phase("gdn_out")
             self.linear(g.out_proj, self.gdn_out[:c], resid, G.EPI_RESID_ADD, resid=resid)
         else:
+            kc, vc, ks, vs = eng.kv.layer(kv_index)
             qkv = self.qkv[:c]
             phase("qkv")
             self.linear(lw.qkv, x, qkv, G.EPI_F32)

@@ -58,7 +58,7 @@ class DraftHead:
             self.dv_ncand = nc
         cfg = engine.cfg
         self.kv0 = cfg.n_layers if kv_layer0 is None else kv_layer0
-        if engine.kv.k.shape[0] < self.kv0 + len(head.layers):
+        if engine.kv.n_layers < self.kv0 + len(head.layers):
             raise ValueError("the engine's KV cache has no layers for the draft head (extra_kv_layers)")
         self.mask_token = cfg.vocab - 1 if mask_token is None else mask_token
         dev = engine.device
