@@ -185,7 +185,7 @@ class DecoderModel:
         return part, s
 
     def _attention(self, m: int, ctrl, block_table, max_blocks, kv: KVCache, kc, vc, ks, vs, window: int = 0):
-        """Split-KV attention of the step's rows into ``buf.attn_out``.  bf16 KV with head size 128 goes to the
+        """Split-KV attention of the step's rows into ``buf.attn_out``.  Head size 128 (bf16 or int8 KV) goes to the
         tensor-core kernel that serves a request's consecutive rows together; the rest to the per-row kernel."""
         cfg, b = self.cfg, self.buf
         if m >= self.attn_rows_min and cfg.head_dim == 128 and self.nsplit_attn <= 64 and cfg.gqa <= 16:

@@ -511,7 +511,7 @@ int cache_map(CUtensorMap* out, const void* ptr, uint64_t rows, int i8) {
 
 }  // namespace
 
-// Rows of a request that follow one another in the control block are served together.  bf16 KV, head size 128,
+// Rows of a request that follow one another in the control block are served together.  bf16 or int8 KV, head size 128,
 // nsplit <= 64, GQA <= 16.  tickets [M][n_kv] (zeroed once; the kernel leaves them zero): the last split CTA of a
 // group merges in the kernel; nullptr: the partials are left for b2_attn_merge.
 extern "C" int b2_attn_rows(const void* q, const void* k_cache, const void* v_cache, const float* k_scale,

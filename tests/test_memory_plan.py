@@ -92,3 +92,14 @@ def test_plan_counts_the_recurrent_state_of_hybrid_models():
     a, b = MP.plan(hyb, 1, 4096), MP.plan(hyb, 8, 4096)
     assert b.total - a.total >= 7 * per_slot
     assert MP.weight_bytes(hyb) > MP.weight_bytes(dense)
+
+
+def test_attention_split_rule_and_quantiser_slots():
+    from b200serve.models.decoder import attn_splits
+    from b200serve.ops.lib import quant_slots
+    assert attn_splits(8, 4096) == 37            # 8 KV heads x 37 splits = one wave of 2 x 148 CTAs
+    assert attn_splits(8, 1024) == 16            # never fewer than 64 keys per split
+    assert attn_splits(8, 100) == 4
+    assert attn_splits(1, 32768) == 64           # the partial buffers hold at most 64 splits
+    assert attn_splits(4, 262144) == 64
+    assert [quant_slots(m) for m in (1, 8, 9, 16, 17, 33, 64)] == [8, 8, 16, 16, 32, 64, 64]
