@@ -39,6 +39,48 @@ def hardware_gate(min_devices: int = 1, out=sys.stderr):
         out.write(f"memory: NVML probe unavailable ({type(e).__name__})\n")
 
 
+def peek_config(spec: str):
+    """The model's shape without loading a weight: a preset, or ``config.json`` of the snapshot."""
+    if spec in PRESETS:
+        return preset(spec)
+    import json
+    from ..loader.snapshot import resolve_snapshot
+    from ..models.config import ModelConfig
+    with open(os.path.join(resolve_snapshot(spec), "config.json")) as f:
+        hf = json.load(f)
+    if "text_config" in hf:
+        hf = hf["text_config"]
+    return ModelConfig.from_hf_config(hf)
+
+
+def parallel_auto(cfg, n_gpus: int, mem_bytes: int, max_seqs: int = 1, kv_dtype: str = "bf16", int8_head: bool = False,
+                  min_len: int = 8192) -> str:
+    """What ``--parallel auto`` means: one GPU when the model and ``min_len`` positions per sequence fit on it (a
+    copy per GPU is opt-in: ``replica``); else the fewest GPUs that hold it -- tensor parallel 2 / 4 / 8 for dense
+    models, expert parallel for mixture-of-experts models whose experts are what does not fit.  The reference
+    chooses between one card, ``tp`` and ``pp`` the same way, from its planner's numbers
+    (src/cli/b70_serve.cc:1310-1324, cli::parallel_auto)."""
+    from ..runtime.memory_plan import plan
+
+    def fits(tp=1, ep=1):
+        try:
+            plan(cfg, max_seqs, min_len, kv_dtype, int8_head, "bf16", tp=tp, ep=ep, budget=mem_bytes)
+            return True
+        except ValueError:
+            return False
+    if fits():
+        return "1"
+    for n in (2, 4, 8):
+        if n > n_gpus:
+            break
+        heads_ok = cfg.n_kv_heads % n == 0 and cfg.n_q_heads % n == 0 and not cfg.n_gdn_layers
+        if cfg.is_moe and cfg.n_experts % n == 0 and fits(ep=n):
+            return f"ep{n}"
+        if not cfg.is_moe and heads_ok and fits(tp=n):
+            return f"tp{n}"
+    raise SystemExit(f"{cfg.name} does not fit on {n_gpus} GPU(s) of {mem_bytes / 2**30:.0f} GiB in any placement")
+
+
 def load_model(spec: str, device, seed: int = 0, int8_head: bool = False, tp=(0, 1)):
     """A preset name gives random-init weights in that shape; anything else is a snapshot."""
     if spec in PRESETS:

@@ -29,6 +29,13 @@ def main(argv=None):
     from . import common
 
     par = f.parallel
+    if par == "auto" and not torch.cuda.is_available():
+        par = "1"           # the hardware gate below says what is missing
+    if par == "auto":
+        par = common.parallel_auto(common.peek_config(f.model), torch.cuda.device_count() if torch.cuda.is_available() else 0,
+                                   torch.cuda.get_device_properties(0).total_memory if torch.cuda.is_available() else 0,
+                                   f.max_num_seqs, f.kv_cache, f.int8_head)
+        sys.stderr.write(f"placement: --parallel auto -> {par}\n")
     world = int(par[2:]) if par[:2] in ("tp", "ep") and par[2:].isdigit() else (2 if par in ("tp", "ep", "pp") else 1)
     common.hardware_gate(world if par != "replica" else 1)
     if world > 1 or par == "replica":

@@ -50,3 +50,31 @@ def test_draft_vocabulary_rule():
     assert build_draft_vocab(100, 0) == list(range(100)) and build_draft_vocab(100, 200) == list(range(100))
     with pytest.raises(ValueError):
         build_draft_vocab(100, 2, forced=[1, 2, 3])
+
+
+def test_parallel_auto_picks_the_fewest_gpus_that_hold_the_model(tmp_path):
+    import dataclasses
+    from b200serve.cli import common
+    from b200serve.models.config import preset
+    from b200serve.models.weights import random_weights
+    from b200serve.utils.synth import write_checkpoint
+    gib = 1 << 30
+    dense, moe = preset("dense-27b"), preset("moe-35b-a3b")
+    assert common.parallel_auto(dense, 8, 180 * gib) == "1"
+    assert common.parallel_auto(moe, 8, 180 * gib) == "1"
+    # a 24 GiB card does not hold the 27B shape (12.8 GB of weights + head + scratch): two of them do
+    assert common.parallel_auto(dense, 8, 16 * gib) == "tp2"
+    big = dataclasses.replace(dense, n_layers=1280, name="dense-540b")       # 256 GB of W4 weights
+    assert common.parallel_auto(big, 8, 180 * gib) == "tp2"
+    assert common.parallel_auto(big, 8, 60 * gib) == "tp8"
+    big_moe = dataclasses.replace(moe, n_layers=400, name="moe-350b")
+    assert common.parallel_auto(big_moe, 8, 80 * gib) == "ep4"
+    assert common.parallel_auto(big_moe, 8, 180 * gib) == "1"
+    with pytest.raises(SystemExit):
+        common.parallel_auto(big, 1, 16 * gib)
+    # the shape comes from config.json without loading a weight
+    cfg = preset("tiny-dense")
+    snap = write_checkpoint(random_weights(cfg, seed=1), str(tmp_path / "snap"))
+    got = common.peek_config(snap)
+    assert (got.n_layers, got.hidden, got.vocab) == (cfg.n_layers, cfg.hidden, cfg.vocab)
+    assert common.peek_config("small-hybrid").n_gdn_layers == 2
