@@ -170,6 +170,17 @@ class Server:
                 s.finished = True
                 s.finish_reason = "cancelled"
         for a in self.sched.tick():
+            try:
+                self._act(a)
+            except Exception as e:  # noqa: BLE001   (whatever a request trips over fails that request, not the server)
+                slots = [a["slot"]] if "slot" in a else list(a.get("slots", ()))
+                for slot in slots:
+                    s = self.by_slot.get(slot)
+                    if s is not None and not s.finished:
+                        self._fail(s, e)
+
+    def _act(self, a):
+        if True:
             kind = a["kind"]
             if kind == "release":
                 s = self.by_slot.pop(a["slot"], None)

@@ -110,13 +110,15 @@ class TokIface:
 
 
 class ByteTok(TokIface):
-    """Mock tokenizer: one id per UTF-8 byte (+3), ids 0..2 are specials (pad, bos, eos)."""
+    """Mock tokenizer: one id per UTF-8 byte (+3), ids 0..2 are specials (pad, bos, eos).  A model whose
+    vocabulary is larger than 259 (every preset with random weights) emits ids that are no byte: they fold onto
+    the byte range (``(id - 3) % 256``) so that serving a preset streams something instead of failing."""
 
     def encode(self, text):
         return [b + 3 for b in text.encode("utf-8")]
 
     def decode(self, ids):
-        return bytes(i - 3 for i in ids if i >= 3).decode("utf-8", "replace")
+        return bytes((i - 3) % 256 for i in ids if i >= 3).decode("utf-8", "replace")
 
     def streamer(self):
         tok = self
@@ -128,7 +130,7 @@ class ByteTok(TokIface):
             def push(self, i):
                 if i < 3:
                     return b""
-                self.buf += bytes([i - 3])
+                self.buf += bytes([(i - 3) % 256])
                 # hold an unfinished UTF-8 character
                 for back in range(1, min(4, len(self.buf)) + 1):
                     c = self.buf[-back]

@@ -174,3 +174,37 @@ def test_failing_slot_fails_only_its_request(server):
     assert codes == [200, 500] or codes == [500, 500]      # a shared step fails the rows that were in it
     eng.fail_slots.clear()
     assert post(srv.port, "/v1/completions", {"prompt": "again", "max_tokens": 5})[0] == 200
+
+
+def test_ids_beyond_the_byte_range_and_a_failing_streamer_do_not_stop_the_server(server):
+    """A preset with random weights emits ids the byte-level stand-in has no byte for: they fold onto the byte range.
+    Whatever else fails while a token is emitted fails that request only."""
+    assert ByteTok().decode([3 + 65, 3 + 256 + 66, 1500]) == "AB" + bytes([(1500 - 3) % 256]).decode("utf-8", "replace")
+    pid = enc("wide")
+    eng = MockEngine(vocab_size=2048, max_len=2048, max_seqs=2, script={pid: [700, 3 + 72, 3 + 256 + 105, 2]})
+    srv = Server(eng, TOK, ChatTemplate(), ServerOptions()).start()
+    request_stop = srv.stop
+    try:
+        _wide_ids_and_broken_streamer(srv)
+    finally:
+        request_stop()
+
+
+def _wide_ids_and_broken_streamer(srv):
+    st, body = post(srv.port, "/v1/completions", {"prompt": "wide", "max_tokens": 8})
+    assert st == 200 and body["usage"]["completion_tokens"] == 3 and "Hi" in body["choices"][0]["text"]
+
+    class Boom:
+        def push(self, i):
+            raise RuntimeError("streamer broke")
+
+        def finish(self):
+            return b""
+    real = TOK.streamer
+    TOK.streamer = lambda: Boom()
+    try:
+        st, _ = post(srv.port, "/v1/completions", {"prompt": "wide", "max_tokens": 8})
+        assert st == 500
+    finally:
+        TOK.streamer = real
+    assert post(srv.port, "/v1/completions", {"prompt": "wide", "max_tokens": 8})[0] == 200
