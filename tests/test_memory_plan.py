@@ -103,3 +103,20 @@ def test_attention_split_rule_and_quantiser_slots():
     assert attn_splits(1, 32768) == 64           # the partial buffers hold at most 64 splits
     assert attn_splits(4, 262144) == 64
     assert [quant_slots(m) for m in (1, 8, 9, 16, 17, 33, 64)] == [8, 8, 16, 16, 32, 64, 64]
+
+
+def test_quant_x_refuses_buffers_that_are_too_small():
+    """The binding checks the sizes before the kernel runs: 3 rows still need 8 token slots per 64-k group."""
+    import pytest
+    import torch
+    from b200serve.ops import lib as K
+    m, k = 3, 1024
+    x = torch.zeros(m, k, dtype=torch.bfloat16)
+    xq = torch.zeros(m * (k // 64) * 128, dtype=torch.uint8)
+    with pytest.raises(ValueError):
+        K.quant_x(x, m, k, xq, torch.zeros(m * (k // 64) * 2, dtype=torch.int32))
+    with pytest.raises(ValueError):
+        K.quant_x(x, m, k, xq[:-1], torch.zeros(8 * (k // 64) * 2, dtype=torch.int32))
+    with pytest.raises(ValueError):
+        K.quant_x(torch.zeros(65, k, dtype=torch.bfloat16), 65, k, torch.zeros(65 * (k // 64) * 128, dtype=torch.uint8),
+                  torch.zeros(64 * (k // 64) * 2, dtype=torch.int32))
