@@ -1,4 +1,5 @@
-"""EngineIface over the single-GPU engine: host-driven rows, logits read-back for host sampling.
+"""EngineIface over the single-GPU engine: host-driven rows, sampling on the device (``sample``) with the logits
+read-back for the host sampler as the fallback.
 
 The role of the reference's ``EngineAdapter`` / ``SlotsEngine`` (src/cli/serve_adapters.h:153-470,
 src/cli/slots_engine.h:1-60): a lone greedy row replays the captured decode graph; several rows
