@@ -12,6 +12,7 @@
 #include "safetensors.h"
 #include "scheduler.h"
 #include "spec.h"
+#include "draft_policy.h"
 #include "tokenizer.h"
 #include "toolcall.h"
 
@@ -191,53 +192,49 @@ PYBIND11_MODULE(b200host, m) {
     return py::make_tuple(r.accepted, r.next_token);
   });
 
-  py::class_<MtpCost>(m, "MtpCost")
+  py::class_<StepCosts>(m, "StepCosts")
       .def(py::init<>())
-      .def_readwrite("verify", &MtpCost::verify)
-      .def_readwrite("draft", &MtpCost::draft)
-      .def("max_k", &MtpCost::max_k)
-      .def("cost", &MtpCost::cost)
-      .def("with_free_drafts", &MtpCost::with_free_drafts);
-  py::class_<AdaptiveKOptions>(m, "AdaptiveKOptions")
+      .def(py::init<std::vector<double>, std::vector<double>>(), py::arg("verify_rows"), py::arg("draft_depth"))
+      .def_readwrite("verify_rows", &StepCosts::verify_rows)
+      .def_readwrite("draft_depth", &StepCosts::draft_depth)
+      .def("deepest", &StepCosts::deepest)
+      .def("iteration", &StepCosts::iteration)
+      .def("free_drafts", &StepCosts::free_drafts);
+  py::class_<DraftLengthOptions>(m, "DraftLengthOptions")
       .def(py::init<>())
-      .def_readwrite("max_k", &AdaptiveKOptions::max_k)
-      .def_readwrite("prior", &AdaptiveKOptions::prior)
-      .def_readwrite("prior_weight", &AdaptiveKOptions::prior_weight)
-      .def_readwrite("decay", &AdaptiveKOptions::decay)
-      .def_readwrite("warmup", &AdaptiveKOptions::warmup)
-      .def_readwrite("hysteresis", &AdaptiveKOptions::hysteresis)
-      .def_readwrite("probe_every", &AdaptiveKOptions::probe_every)
-      .def_readwrite("probe_max", &AdaptiveKOptions::probe_max)
-      .def_readwrite("cost", &AdaptiveKOptions::cost);
-  py::class_<AdaptiveK>(m, "AdaptiveK")
-      .def(py::init<const AdaptiveKOptions&>(), py::arg("options") = AdaptiveKOptions())
-      .def("next", &AdaptiveK::next)
-      .def("observe", &AdaptiveK::observe)
-      .def("alpha", &AdaptiveK::alpha)
-      .def("current", &AdaptiveK::current)
-      .def("max_k", &AdaptiveK::max_k)
-      .def("best", &AdaptiveK::best)
-      .def("rate", &AdaptiveK::rate)
-      .def_static("expected_ids", &AdaptiveK::expected_ids);
-  py::class_<DraftCalib>(m, "DraftCalib")
-      .def(py::init<>())
-      .def_static("bin", &DraftCalib::bin)
-      .def("rate", &DraftCalib::rate)
-      .def("observe", &DraftCalib::observe);
-  py::class_<StepKOptions>(m, "StepKOptions")
-      .def(py::init<>())
-      .def_readwrite("max_k", &StepKOptions::max_k)
-      .def_readwrite("prior", &StepKOptions::prior)
-      .def_readwrite("probe_every", &StepKOptions::probe_every)
-      .def_readwrite("cost", &StepKOptions::cost);
-  py::class_<StepK>(m, "StepK")
-      .def(py::init<const StepKOptions&, DraftCalib&>(), py::keep_alive<1, 3>())
-      .def("begin", &StepK::begin)
-      .def("choose", &StepK::choose)
-      .def("observe", &StepK::observe)
-      .def("verified", &StepK::verified)
-      .def("max_k", &StepK::max_k)
-      .def("position_rate", &StepK::position_rate);
+      .def_readwrite("deepest", &DraftLengthOptions::deepest)
+      .def_readwrite("prior_accept", &DraftLengthOptions::prior_accept)
+      .def_readwrite("prior_trials", &DraftLengthOptions::prior_trials)
+      .def_readwrite("forget", &DraftLengthOptions::forget)
+      .def_readwrite("settle", &DraftLengthOptions::settle)
+      .def_readwrite("switch_margin", &DraftLengthOptions::switch_margin)
+      .def_readwrite("probe_wait", &DraftLengthOptions::probe_wait)
+      .def_readwrite("probe_wait_max", &DraftLengthOptions::probe_wait_max)
+      .def_readwrite("costs", &DraftLengthOptions::costs);
+  py::class_<DraftLengthPolicy>(m, "DraftLengthPolicy")
+      .def(py::init<const DraftLengthOptions&>(), py::arg("options") = DraftLengthOptions())
+      .def("next", &DraftLengthPolicy::next)
+      .def("observe", &DraftLengthPolicy::observe)
+      .def("current", &DraftLengthPolicy::current)
+      .def("deepest", &DraftLengthPolicy::deepest)
+      .def("acceptance", &DraftLengthPolicy::acceptance)
+      .def("expected_tokens", &DraftLengthPolicy::expected_tokens)
+      .def("tokens_per_cost", &DraftLengthPolicy::tokens_per_cost)
+      .def("best_depth", &DraftLengthPolicy::best_depth);
+  py::class_<ConfidenceModel>(m, "ConfidenceModel")
+      .def(py::init<double>(), py::arg("learning_rate") = 0.05)
+      .def("accept_prob", &ConfidenceModel::accept_prob)
+      .def("learn", &ConfidenceModel::learn)
+      .def("bias", &ConfidenceModel::bias)
+      .def("slope", &ConfidenceModel::slope);
+  py::class_<ConfidenceStop>(m, "ConfidenceStop")
+      .def(py::init<const StepCosts&, uint32_t, ConfidenceModel&>(), py::keep_alive<1, 4>())
+      .def("begin", &ConfidenceStop::begin)
+      .def("after_draft", &ConfidenceStop::after_draft)
+      .def("observe", &ConfidenceStop::observe)
+      .def("verified", &ConfidenceStop::verified)
+      .def("deepest", &ConfidenceStop::deepest)
+      .def("typical", &ConfidenceStop::typical);
 
   // ------------------------------------------------------------ prefix cache
   py::class_<PrefixCache>(m, "PrefixCache")

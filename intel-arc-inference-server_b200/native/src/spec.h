@@ -203,202 +203,4 @@ inline AcceptResult accept_sparse(const float* p_rows, const SparseQ* q, const u
   return {k, draw(filter_probs(p_rows + k * row_stride, vocab_used, s), rng)};
 }
 
-// ------------------------------------------------------------------ cost table and K policies
-// Step costs in units of one plain decode step: verify[m-1] for M = m rows, draft[k-1] for k drafts.
-struct MtpCost {
-  std::vector<double> verify{1.00, 1.04, 1.09, 1.13};
-  std::vector<double> draft{0.19, 0.37, 0.55};
-  uint32_t max_k() const { return (uint32_t)std::min(verify.size() - 1, draft.size()); }
-  double cost(uint32_t k) const { return k == 0 ? 1.0 : verify.at(k) + draft.at(k - 1); }
-  MtpCost with_free_drafts() const {
-    MtpCost c = *this;
-    c.draft.assign(c.verify.size() - 1, 0.0);
-    return c;
-  }
-};
-
-struct AdaptiveKOptions {
-  uint32_t max_k = 3;
-  double prior = 0.8, prior_weight = 4, decay = 0.9;
-  uint32_t warmup = 2;
-  double hysteresis = 0.03;
-  uint32_t probe_every = 4, probe_max = 32;
-  MtpCost cost;
-};
-
-class AdaptiveK {
- public:
-  explicit AdaptiveK(const AdaptiveKOptions& o = {})
-      : o_(o), max_k_(std::min(o.max_k, o.cost.max_k())), s_(o.prior * o.prior_weight), t_(o.prior_weight),
-        cur_(max_k_), probe_gap_(o.probe_every) {}
-
-  static double expected_ids(double a, uint32_t k) {
-    if (a >= 1.0) return k + 1.0;
-    return (1.0 - std::pow(a, double(k + 1))) / (1.0 - a);
-  }
-  double rate(double a, uint32_t k) const { return expected_ids(a, k) / o_.cost.cost(k); }
-  uint32_t best(double a) const {
-    uint32_t b = 0;
-    for (uint32_t k = 1; k <= max_k_; ++k)
-      if (rate(a, k) > rate(a, b)) b = k;
-    return b;
-  }
-  double alpha() const { return s_ / t_; }
-  uint32_t current() const { return cur_; }
-  uint32_t max_k() const { return max_k_; }
-
-  uint32_t next() {
-    if (iters_ < o_.warmup) return max_k_;
-    if (cur_ == 0 && plain_run_ >= probe_gap_) return 1;  // a probe
-    return cur_;
-  }
-  void observe(uint32_t k, uint32_t accepted) {
-    ++iters_;
-    if (k > 0) {
-      // drafts tried: the accepted ones plus the first rejected one
-      const double tried = std::min(k, accepted + 1);
-      s_ = s_ * o_.decay + accepted;
-      t_ = t_ * o_.decay + tried;
-    }
-    if (iters_ < o_.warmup) return;
-    const bool was_probe = cur_ == 0 && k > 0;
-    const uint32_t b = best(alpha());
-    if (b != cur_ && rate(alpha(), b) > rate(alpha(), cur_) * (1.0 + o_.hysteresis)) cur_ = b;
-    if (cur_ == 0) {
-      if (k == 0) ++plain_run_;
-      else {
-        plain_run_ = 0;
-        if (was_probe) probe_gap_ = std::min(probe_gap_ * 2, o_.probe_max);
-      }
-    } else {
-      plain_run_ = 0;
-      probe_gap_ = o_.probe_every;
-    }
-  }
-
- private:
-  AdaptiveKOptions o_;
-  uint32_t max_k_;
-  double s_, t_;
-  uint32_t iters_ = 0, cur_, plain_run_ = 0, probe_gap_;
-};
-
-// Calibration of the draft head's stated probability: accepted / tested per (position, bin).
-class DraftCalib {
- public:
-  static constexpr uint32_t kPositions = 3, kBins = 9;
-  static constexpr double kDecay = 0.98, kPriorN = 10;
-  static uint32_t bin(float p) {
-    if (!(p > 0)) return 0;
-    const int b = int(p * kBins);
-    return (uint32_t)std::min<int>(std::max(b, 0), kBins - 1);
-  }
-  double rate(uint32_t i, float p) const {
-    i = std::min(i, kPositions - 1);
-    const uint32_t b = bin(p);
-    return (ok_[i][b] + kPriorN * p) / (n_[i][b] + kPriorN);
-  }
-  void observe(uint32_t i, float p, bool accepted) {
-    i = std::min(i, kPositions - 1);
-    const uint32_t b = bin(p);
-    ok_[i][b] = ok_[i][b] * kDecay + (accepted ? 1.0 : 0.0);
-    n_[i][b] = n_[i][b] * kDecay + 1.0;
-  }
-
- private:
-  std::array<std::array<double, kBins>, kPositions> ok_{}, n_{};
-};
-
-struct StepKOptions {
-  uint32_t max_k = 3;
-  double prior = 0.8, prior_weight = 4, decay = 0.9;
-  uint32_t probe_every = 4;
-  MtpCost cost;
-};
-
-// Per-step draft count: after each draft, verify the best K so far or draft another.
-class StepK {
- public:
-  StepK(const StepKOptions& o, DraftCalib& calib)
-      : o_(o), calib_(calib), max_k_(std::min({o.max_k, o.cost.max_k(), DraftCalib::kPositions})) {
-    for (uint32_t i = 0; i < DraftCalib::kPositions; ++i) {
-      s_[i] = o.prior * o.prior_weight;
-      t_[i] = o.prior_weight;
-    }
-  }
-  uint32_t max_k() const { return max_k_; }
-  uint32_t verified() const { return verified_; }
-  double position_rate(uint32_t i) const { return s_[i] / t_[i]; }
-
-  // E(K)/cost for known q[0..j) and, past them, the last known q (or the request's rates)
-  double best(const double* q, uint32_t j, uint32_t lo, uint32_t hi, uint32_t drafted, uint32_t* k_out) const {
-    double best_rate = -1;
-    uint32_t bk = lo;
-    for (uint32_t k = lo; k <= hi; ++k) {
-      double e = 1.0, prod = 1.0;
-      for (uint32_t i = 0; i < k; ++i) {
-        const double qi = i < j ? q[i] : (j > 0 ? q[j - 1] : position_rate(i));
-        prod *= qi;
-        e += prod;
-      }
-      const uint32_t d = std::max(drafted, k);
-      const double c = (k == 0 && d == 0) ? 1.0 : o_.cost.verify.at(k) + (d > 0 ? o_.cost.draft.at(d - 1) : 0.0);
-      const double r = e / c;
-      if (r > best_rate) {
-        best_rate = r;
-        bk = k;
-      }
-    }
-    if (k_out) *k_out = bk;
-    return best_rate;
-  }
-  uint32_t begin() {
-    drafted_ = 0;
-    verified_ = 0;
-    answered_ = false;
-    uint32_t k;
-    best(nullptr, 0, 0, max_k_, 0, &k);
-    if (k == 0 && plain_run_ >= o_.probe_every) k = 1;
-    cap_ = k == 0 ? 0 : max_k_;
-    if (k == 0) answered_ = true;
-    return cap_;
-  }
-  // after draft j (1-based) with the head's probability p: < 0 = draft another, else verify that many
-  int choose(uint32_t j, float p) {
-    drafted_ = j;
-    p_[j - 1] = p;
-    q_[j - 1] = calib_.rate(j - 1, p);
-    uint32_t k_now, k_more;
-    const double r_now = best(q_.data(), j, 0, j, j, &k_now);
-    if (j < cap_) {
-      const double r_more = best(q_.data(), j, j + 1, cap_, j, &k_more);
-      if (r_more > r_now) return -1;
-    }
-    verified_ = k_now;
-    answered_ = true;
-    return (int)k_now;
-  }
-  void observe(uint32_t accepted) {
-    if (!answered_) verified_ = drafted_;
-    for (uint32_t i = 0; i < verified_; ++i) {
-      const bool ok = i < accepted;
-      calib_.observe(i, p_[i], ok);
-      s_[i] = s_[i] * o_.decay + (ok ? 1.0 : 0.0);
-      t_[i] = t_[i] * o_.decay + 1.0;
-      if (!ok) break;  // positions past the first rejection were not tested
-    }
-    plain_run_ = drafted_ == 0 ? plain_run_ + 1 : 0;
-  }
-
- private:
-  StepKOptions o_;
-  DraftCalib& calib_;
-  uint32_t max_k_;
-  std::array<double, DraftCalib::kPositions> s_{}, t_{};
-  std::array<float, DraftCalib::kPositions> p_{};
-  std::array<double, DraftCalib::kPositions> q_{};
-  uint32_t cap_ = 0, drafted_ = 0, verified_ = 0, plain_run_ = 0;
-  bool answered_ = false;
-};
-
 }  // namespace b2host

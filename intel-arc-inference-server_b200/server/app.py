@@ -40,6 +40,8 @@ class ServerOptions:
     spec: str = "off"                 # off | lookup | mtp | dflash (drafting is done by the engine adapter)
     spec_max: int = 3
     prefix_split_last: bool = False
+    spec_adaptive: bool = True        # per-request draft length from the acceptance seen so far (native DraftLengthPolicy)
+    spec_costs: Optional[tuple] = None   # (verify_rows, draft_depth) in plain steps, measured at start-up; None: B200 defaults
 
 
 @dataclass
@@ -67,6 +69,9 @@ class Session:
     t0: float = 0.0
     t_first: float = 0.0
     lookup: object = None
+    klen: object = None                # DraftLengthPolicy of this request
+    copy: object = None                # LookupPolicy (spec = dflash-lookup): copy steps inside a block drafter
+    copy_step: bool = False            # the drafts of the step in flight came from the copy proposer
 
 
 class Server:
@@ -242,7 +247,7 @@ class Server:
             s = self.by_slot.get(slot)
             if s is None or s.finished or s.pending is None:
                 continue
-            drafts = self._draft(s, n - 1) if n > 1 else []
+            drafts = self._draft(s, self._draft_budget(s, n - 1)) if n > 1 else []
             rows[slot] = [s.pending] + drafts
         if not rows:
             return
@@ -266,6 +271,7 @@ class Server:
                                                s.req.top_k, s.req.top_p, seed)
             else:
                 acc, nxt = 0, (self._sample(s) if host_rule else out[0])
+            self._observe_drafts(s, len(drafts), acc)
             if acc < len(drafts):       # rejected rows leave the cache
                 self.engine.truncate(slot, self.engine.length(slot) - (len(drafts) - acc))
             emitted = 0
@@ -280,21 +286,63 @@ class Server:
             if not s.finished:
                 self.sched.tokens(slot, emitted, False)
 
-    def _draft(self, s: Session, k: int) -> List[int]:
-        if k <= 0:
-            return []
-        if self.o.spec in ("mtp", "dflash", "dflash-lookup") and hasattr(self.engine, "draft"):
-            room = s.req.max_tokens - len(s.out_ids) - 1     # a learned draft head on the engine side
-            drafts = list(self.engine.draft(s.slot, s.pending, max(0, min(k, room)))) if room > 0 else []
-            if drafts or self.o.spec != "dflash-lookup":
-                return drafts
-        elif self.o.spec != "lookup":
-            return []
+    def _step_costs(self):
+        if self.o.spec_costs is not None:
+            return H.StepCosts(list(self.o.spec_costs[0]), list(self.o.spec_costs[1]))
+        return H.StepCosts()
+
+    def _draft_budget(self, s: Session, k: int) -> int:
+        """Drafts this step may spend: the scheduler's row budget, cut by the request's draft-length policy (which
+        pauses speculation while drafts keep being rejected and probes now and then)."""
+        if k <= 0 or not self.o.spec_adaptive or self.o.spec == "off":
+            return k
+        if s.klen is None:
+            o = H.DraftLengthOptions()
+            o.deepest = min(self.o.spec_max, k) if self.o.spec_max > 0 else k
+            costs = self._step_costs()
+            # copied drafts cost nothing to make; a block drafter makes all its drafts in one pass
+            o.costs = costs.free_drafts() if self.o.spec == "lookup" else costs
+            s.klen = H.DraftLengthPolicy(o)
+        return min(k, s.klen.next()) if self.o.spec != "dflash-lookup" else k
+
+    def _observe_drafts(self, s: Session, proposed: int, accepted: int):
+        if s.copy_step:
+            s.copy.observe(proposed, accepted)
+            s.copy_step = False
+        elif s.klen is not None:
+            s.klen.observe(proposed, accepted)
+
+    def _lookup(self, s: Session):
         if s.lookup is None:
             s.lookup = H.PromptLookup()
             s.lookup.extend(s.prompt_ids + s.out_ids)
+        return s.lookup
+
+    def _draft(self, s: Session, k: int) -> List[int]:
+        if k <= 0:
+            return []
         room = s.req.max_tokens - len(s.out_ids) - 1
-        return list(s.lookup.propose(max(0, min(k, room)), 2)) if room > 0 else []
+        if room <= 0:
+            return []
+        if self.o.spec == "dflash-lookup":
+            # the copy proposer takes the step while the context repeats an earlier stretch (enter at 8 matching
+            # tokens, stay down to 3) and widens its verify as whole copies are accepted; else the block drafter drafts
+            if s.copy is None:
+                s.copy = H.LookupPolicy()
+            lk = self._lookup(s)
+            width = s.copy.decide(lk.match(2)[1]) if lk.size() >= 2 else 0
+            if width > 0:
+                # a lone request may use the step's whole row budget for a wide copy; with company it keeps its share
+                cap = self.o.row_budget - 1 if len(self.by_slot) == 1 else k
+                drafts = list(lk.propose(min(width - 1, cap, room), 3))
+                if drafts:
+                    s.copy_step = True
+                    return drafts
+        if self.o.spec in ("mtp", "dflash", "dflash-lookup") and hasattr(self.engine, "draft"):
+            return list(self.engine.draft(s.slot, s.pending, min(k, room)))     # a learned draft head on the engine side
+        if self.o.spec not in ("lookup", "dflash-lookup"):
+            return []
+        return list(self._lookup(s).propose(min(k, room), 2))
 
     # ------------------------------------------------------------------ output
     def _emit_token(self, s: Session, tok: int):

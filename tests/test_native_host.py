@@ -199,37 +199,66 @@ def test_accept_sparse_is_lossless():
 
 
 # ----------------------------------------------------------------------------- K policies
-def test_adaptive_k_follows_acceptance():
-    k = H.AdaptiveK()
-    assert k.next() == 3                                   # warm-up at the deepest K
+def test_draft_length_policy_follows_acceptance():
+    k = H.DraftLengthPolicy()
+    assert k.next() == 3                                   # settles at the deepest depth first
     for _ in range(30):
         kk = k.next()
         k.observe(kk, kk)                                  # everything accepted
-    assert k.current() == 3 and k.alpha() > 0.9
+    assert k.current() == 3 and k.acceptance(0) > 0.9 and k.acceptance(2) > 0.9
+    assert k.expected_tokens(3) > 3.5
     for _ in range(60):
         kk = k.next()
         k.observe(kk, 0)                                   # nothing accepted
-    assert k.current() == 0
+    assert k.current() == 0 and k.acceptance(0) < 0.1
     probes = 0
-    for _ in range(40):
+    for _ in range(60):
         kk = k.next()
         probes += kk > 0
         k.observe(kk, 0)
-    assert 1 <= probes <= 8                                # K = 0 probes now and then, with a growing gap
-    assert abs(H.AdaptiveK.expected_ids(0.5, 2) - 1.75) < 1e-12
+    assert 1 <= probes <= 8                                # at depth 0 a probe now and then, the gap growing
+    for _ in range(200):                                   # the text becomes predictable again: probes bring depth back
+        kk = k.next()
+        k.observe(kk, kk)
+    assert k.current() == 3
 
 
-def test_step_k_stops_on_unsure_draft():
-    calib = H.DraftCalib()
-    o = H.StepKOptions()
-    s = H.StepK(o, calib)
+def test_draft_length_policy_is_per_position():
+    # a head whose first draft is reliable and whose later drafts are not: depth 1 pays, depth 3 does not
+    k = H.DraftLengthPolicy()
+    for _ in range(80):
+        kk = k.next()
+        k.observe(kk, min(kk, 1))
+    assert k.acceptance(0) > 0.9 and k.acceptance(1) < 0.3
+    assert k.current() == 1 and k.best_depth() == 1
+
+
+def test_step_costs_table():
+    c = H.StepCosts([1.0, 1.1, 1.2, 1.3], [0.2, 0.4, 0.6])
+    assert c.deepest() == 3 and abs(c.iteration(2) - 1.6) < 1e-12 and c.iteration(0) == 1.0
+    f = c.free_drafts()
+    assert abs(f.iteration(3) - 1.3) < 1e-12
+
+
+def test_confidence_stop_drops_unsure_draft():
+    model = H.ConfidenceModel()
+    s = H.ConfidenceStop(H.StepCosts(), 3, model)
     assert s.begin() == 3
-    assert s.choose(1, 0.99) == -1                          # confident: draft another
-    r = s.choose(2, 0.02)                                   # unsure: verify only the first
+    assert s.after_draft(1, 0.99) == -1                     # confident: draft another
+    r = s.after_draft(2, 0.02)                              # unsure: verify only the first
     assert r == 1
     s.observe(1)
     assert s.verified() == 1
-    assert H.DraftCalib.bin(0.0) == 0 and H.DraftCalib.bin(1.0) == 8
+
+
+def test_confidence_model_learns_overconfidence():
+    model = H.ConfidenceModel()
+    assert abs(model.accept_prob(1, 0.9) - 0.9) < 1e-9      # starts by believing the head
+    rnd = random.Random(3)
+    for _ in range(3000):                                   # position 1 says 0.9 but is right half of the time
+        model.learn(1, 0.9, rnd.random() < 0.5)
+    assert 0.35 < model.accept_prob(1, 0.9) < 0.65         # near one half, up to the noise of single-sample steps
+    assert abs(model.accept_prob(0, 0.9) - 0.9) < 1e-9      # other positions are untouched
 
 
 # ----------------------------------------------------------------------------- prefix cache
