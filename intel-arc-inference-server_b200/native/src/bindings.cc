@@ -148,19 +148,29 @@ PYBIND11_MODULE(b200host, m) {
       .def("observe", &LookupPolicy::observe);
 
   // ------------------------------------------------------------ sampling / acceptance
-  m.def("filter_probs", [](FArr logits, uint32_t vocab_used, float temperature, uint32_t top_k, float top_p) {
+  // the samplers read `vocab_used` floats from the row: a shorter row (a vocabulary shard, say) is refused
+  auto need_row = [](size_t have, uint32_t vocab_used) {
+    if (have < vocab_used) throw std::invalid_argument("logits row is shorter than the vocabulary in use");
+  };
+  m.def("filter_probs", [need_row](FArr logits, uint32_t vocab_used, float temperature, uint32_t top_k, float top_p) {
+    need_row((size_t)logits.size(), vocab_used);
     auto f = filter_probs(logits.data(), vocab_used, make_sampling(temperature, top_k, top_p));
     return py::make_tuple(f.ids, f.probs, f.mass);
   });
-  m.def("apply_repetition_penalty", [](py::array_t<float, py::array::c_style> logits, uint32_t vocab_used,
+  m.def("apply_repetition_penalty", [need_row](py::array_t<float, py::array::c_style> logits, uint32_t vocab_used,
                                         const std::vector<uint32_t>& ids, float penalty) {
+    need_row((size_t)logits.size(), vocab_used);
     apply_repetition_penalty(logits.mutable_data(), vocab_used, ids, penalty);
   });
-  m.def("sample", [](FArr logits, uint32_t vocab_used, float temperature, uint32_t top_k, float top_p, uint64_t seed) {
+  m.def("sample", [need_row](FArr logits, uint32_t vocab_used, float temperature, uint32_t top_k, float top_p, uint64_t seed) {
+    need_row((size_t)logits.size(), vocab_used);
     std::mt19937_64 rng(seed);
     return draw(filter_probs(logits.data(), vocab_used, make_sampling(temperature, top_k, top_p)), rng);
   });
-  m.def("argmax_low_tie", [](FArr logits, uint32_t n) { return argmax_low_tie(logits.data(), n); });
+  m.def("argmax_low_tie", [need_row](FArr logits, uint32_t n) {
+    need_row((size_t)logits.size(), n);
+    return argmax_low_tie(logits.data(), n);
+  });
   m.def("accept_greedy", [](const std::vector<uint32_t>& verify_argmax, const std::vector<uint32_t>& drafts) {
     if (verify_argmax.size() < drafts.size() + 1) throw std::invalid_argument("need k + 1 verify rows");
     auto r = accept_greedy(verify_argmax.data(), drafts.data(), (uint32_t)drafts.size());

@@ -79,8 +79,22 @@ class LockstepLeader(EngineIface):
     def prefill(self, slot, ids): return self._all("prefill", slot, list(ids))
     def step(self, rows): return self._all("step", {int(k): list(v) for k, v in rows.items()})
     def length(self, slot): return self.e.length(slot)
-    def logits(self, slot, row=0): return self.e.logits(slot, row)
     def kv_form(self): return self.e.kv_form()
+
+    def logits(self, slot, row=0):
+        """The row's logits over the WHOLE vocabulary.  Under tensor parallelism every rank holds a slice of the
+        vocabulary, under pipeline parallelism only the last stage holds the row: every rank reports its part
+        (first id, values) over the control plane and the leader puts the row together, so the host sampler never
+        sees a shard (the reference gathers both halves of a sampled row on the host: src/runtime/tp_engine.h:240-243)."""
+        if not hasattr(self.e, "logits_shard"):
+            return self.e.logits(slot, row)
+        self.plane.broadcast(("logits_shard", (slot, row)))
+        parts = [self.e.logits_shard(slot, row)] + [self.plane.recv(r) for r in range(1, self.plane.world)]
+        full = np.full(self.vocab_size, -np.inf, dtype=np.float32)
+        for off, vals in parts:
+            vals = np.asarray(vals, dtype=np.float32)
+            full[off: off + len(vals)] = vals[: max(0, self.vocab_size - off)]
+        return full
 
     def shutdown(self):
         self.plane.broadcast((SHUTDOWN, ()))
@@ -93,7 +107,9 @@ def follow_lockstep(engine: EngineIface, plane: ControlPlane) -> int:
         msg = plane.next_broadcast()
         if msg[0] == SHUTDOWN:
             return n
-        _apply(engine, msg)
+        res = _apply(engine, msg)
+        if msg[0] == "logits_shard":     # the one call whose result the leader needs from every rank
+            plane.send(0, res)
         n += 1
 
 

@@ -163,7 +163,7 @@ def bench_decode(cfg: ModelConfig, mode: str, depth: int, steps: int, warmup: in
     _sync_all()
     ms = _max_over_ranks(e0.elapsed_time(e1) / steps, dev)
     K.check_status()
-    launches = eng.launches_per_step.get((rows, True), 0)
+    launches = eng.launches(rows, True)
     eng.close()
     del eng, w
     torch.cuda.empty_cache()

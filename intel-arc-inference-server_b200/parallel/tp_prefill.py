@@ -60,8 +60,9 @@ class TpPrefillRunner(PrefillRunner):
         eng, cfg, m = self.eng, self.cfg, self.eng.model
         c, h, w = len(ids), cfg.hidden, self.world
         eng._ensure_pages(slot, pos0 + c)
-        self.ids_host[:c] = torch.as_tensor(ids, dtype=torch.int64)
-        self.ids_dev[:c].copy_(self.ids_host[:c], non_blocking=True)
+        ids_host = self.ids_stage.begin()
+        ids_host[:c] = torch.as_tensor(ids, dtype=torch.int64)
+        self.ids_stage.push(self.ids_dev[:c], ids_host[:c])
         lo = self.rank * self.rows_cap
         hi = min(c, lo + self.rows_cap)
         if hi > lo:
@@ -135,8 +136,9 @@ class NcclPrefillRunner(PrefillRunner):
         eng, cfg, m = self.eng, self.cfg, self.eng.model
         c, h = len(ids), cfg.hidden
         eng._ensure_pages(slot, pos0 + c)
-        self.ids_host[:c] = torch.as_tensor(ids, dtype=torch.int64)
-        self.ids_dev[:c].copy_(self.ids_host[:c], non_blocking=True)
+        ids_host = self.ids_stage.begin()
+        ids_host[:c] = torch.as_tensor(ids, dtype=torch.int64)
+        self.ids_stage.push(self.ids_dev[:c], ids_host[:c])
         resid, x = self.resid[:c], self.x[:c]
         torch.index_select(m.w.embed, 0, self.ids_dev[:c], out=resid)
         bt_row = eng.block_table[slot]

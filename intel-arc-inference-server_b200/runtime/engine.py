@@ -21,6 +21,7 @@ from ..models.config import ModelConfig
 from ..models.decoder import DecoderModel, KVCache, attn_splits
 from ..models.weights import ModelWeights
 from ..ops import lib as K
+from ..utils.staging import Staged
 from .kv_pool import KvPool
 
 PAGE = 16
@@ -56,19 +57,21 @@ class Engine:
         self.kv_dtype = kv_dtype
         self.pool = KvPool(num_pages, max_seqs, self.max_blocks)
         self.ctrl = torch.zeros(K.CTRL_WORDS, dtype=torch.int32, device=self.device)
-        self.ctrl_host = torch.zeros(K.CTRL_WORDS, dtype=torch.int32).pin_memory()
+        # pinned staging rings: a queued non-blocking copy may run long after the host moved on (see utils/staging.py)
+        self.ctrl_stage = Staged((K.CTRL_WORDS,), torch.int32)
+        self.table_stage = Staged((self.max_blocks,), torch.int32, depth=4)
         self.out_host = torch.zeros(K.CTRL_WORDS, dtype=torch.int32).pin_memory()
         self.block_table = torch.zeros(max_seqs, self.max_blocks, dtype=torch.int32, device=self.device)
-        self.block_table_host = torch.zeros(max_seqs, self.max_blocks, dtype=torch.int32).pin_memory()
         self.seq_len = [0] * max_seqs
         self._gdn_snap = None       # (rows, {slot: state before them}) of the last forward_rows step of a hybrid model
         self.use_graphs = use_graphs
-        self.graphs: Dict[Tuple[int, bool], torch.cuda.CUDAGraph] = {}
+        self.graphs: Dict[Tuple[int, bool, bool], torch.cuda.CUDAGraph] = {}
+        self._one_request = False   # the rows last written are consecutive positions of one request
         self.prefill_backend = prefill_backend
         self._prefill = None
         self.steps_replayed = 0
         self.last_prefill_row = 0
-        self.launches_per_step: Dict[Tuple[int, bool], int] = {}
+        self.launches_per_step: Dict[Tuple[int, bool, bool], int] = {}
 
     def close(self):
         """Releases the cross-GPU buffers of a tensor-parallel engine (mapped peer memory)."""
@@ -121,18 +124,20 @@ class Engine:
         changed = self.pool.ensure(slot, (upto_len + PAGE - 1) // PAGE)
         if changed:
             row = self.pool.table(slot)
-            self.block_table_host[slot, : len(row)] = torch.from_numpy(np.asarray(row, dtype=np.int32))
-            self.block_table[slot].copy_(self.block_table_host[slot], non_blocking=True)
+            host = self.table_stage.begin()
+            host[: len(row)] = torch.from_numpy(np.asarray(row, dtype=np.int32))
+            self.table_stage.push(self.block_table[slot, : len(row)], host[: len(row)])
 
     def _write_rows(self, rows: Sequence[Row]):
         m = len(rows)
-        c = self.ctrl_host
+        c = self.ctrl_stage.begin()
         c[K.CTRL_N_ROWS] = m
         for i, r in enumerate(rows):
             c[K.CTRL_ROW_REQ + i] = r.slot
             c[K.CTRL_ROW_POS + i] = r.pos
             c[K.CTRL_CUR_TOKEN + i] = r.token
-        self.ctrl.copy_(c, non_blocking=True)
+        self._one_request = all(r.slot == rows[0].slot and r.pos == rows[0].pos + i for i, r in enumerate(rows))
+        self.ctrl_stage.push(self.ctrl)
 
     # ------------------------------------------------------------------ session snapshots
     def save_kv(self, slot: int, begin: int, end: int) -> dict:
@@ -185,13 +190,14 @@ class Engine:
 
     # ------------------------------------------------------------------ running a step
     def _enqueue(self, m: int, advance: bool):
-        self.model.step_rows(m, self.ctrl, self.block_table, self.max_blocks, self.kv, advance)
+        self.model.step_rows(m, self.ctrl, self.block_table, self.max_blocks, self.kv, advance,
+                             one_request=self._one_request)
 
     def _run(self, m: int, advance: bool):
         if not self.use_graphs:
             self._enqueue(m, advance)
             return
-        key = (m, advance)
+        key = (m, advance, self._one_request)
         g = self.graphs.get(key)
         if g is None:
             # warm-up outside capture (sets function attributes, allocates split-K scratch), then
@@ -214,6 +220,10 @@ class Engine:
             self.graphs[key] = g
         g.replay()
         self.steps_replayed += 1
+
+    def launches(self, m: int, advance: bool = True) -> int:
+        """Kernel launches of one captured step of ``m`` rows (0 before the first such step)."""
+        return max((v for (mm, adv, _), v in self.launches_per_step.items() if mm == m and adv == advance), default=0)
 
     def _read_out(self, m: int) -> List[int]:
         self.out_host.copy_(self.ctrl, non_blocking=True)

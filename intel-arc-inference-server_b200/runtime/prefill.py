@@ -21,6 +21,8 @@ from typing import List, Optional
 
 import torch
 
+from ..utils.staging import Staged
+
 from ..models.weights import QLinear
 from ..ops import gemm as G
 from ..ops import lib as K
@@ -92,7 +94,7 @@ class PrefillRunner:
             self.gdn_proj = torch.empty(c, cfg.gdn_proj_dim, dtype=f32, device=self.dev)
             self.gdn_act = torch.empty(c, cfg.gdn_proj_dim, dtype=f32, device=self.dev)
             self.gdn_out = torch.empty(c, cfg.gdn_value_dim, dtype=bf, device=self.dev)
-        self.ids_host = torch.empty(max_chunk, dtype=torch.int64).pin_memory()
+        self.ids_stage = Staged((max_chunk,), torch.int64)   # ring of pinned buffers: the host runs a chunk ahead of the copies
         self.ids_dev = torch.empty(max_chunk, dtype=torch.int64, device=self.dev)
         self._slab: Optional[torch.Tensor] = None
         if self.backend == "int8":
@@ -193,8 +195,9 @@ class PrefillRunner:
         c, h = len(ids), cfg.hidden
         eng._ensure_pages(slot, pos0 + c)
         eng._gdn_snap = None      # (a hybrid model's recurrent state moves on: nothing to rewind to)
-        self.ids_host[:c] = torch.as_tensor(ids, dtype=torch.int64)
-        self.ids_dev[:c].copy_(self.ids_host[:c], non_blocking=True)
+        ids_host = self.ids_stage.begin()
+        ids_host[:c] = torch.as_tensor(ids, dtype=torch.int64)
+        self.ids_stage.push(self.ids_dev[:c], ids_host[:c])
         resid, x = self.resid[:c], self.x[:c]
         torch.index_select(m.w.embed, 0, self.ids_dev[:c], out=resid)
         bt_row = eng.block_table[slot]

@@ -64,6 +64,17 @@ class EngineAdapter(EngineIface):
             self._logits_host = self.e.logits(n).float().cpu().numpy()
         return self._logits_host[self._rows_of[slot][row]]
 
+    def logits_shard(self, slot, row=0):
+        """(first vocabulary id, fp32 values) of the part of the row's logits that this rank holds: the whole row
+        on one GPU, this rank's slice of the vocabulary under tensor parallelism, nothing on a pipeline stage that
+        does not run the head."""
+        m = self.e.model
+        if not getattr(self.e, "last", True):      # a pipeline stage before the last one: the head did not run here
+            return 0, np.zeros(0, dtype=np.float32)
+        off = m.vocab_offset if self.e.tp is not None else (getattr(m, "vocab_offset_nccl", 0) if m.nccl is not None else 0)
+        part = np.asarray(self.logits(slot, row))
+        return int(off), part[: max(0, min(len(part), self.vocab_size - off))]
+
     # ------------------------------------------------------------------ sampling on the device
     _SAMP_HEAD = 8      # parameter words before the history ids
 

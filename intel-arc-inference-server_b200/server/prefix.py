@@ -90,8 +90,11 @@ class EngineKV:
     def _sync_table(self, slot: int):
         e, torch = self.e, self.torch
         row = list(e.pool.table(slot))
-        e.block_table_host[slot, : len(row)] = torch.from_numpy(np.asarray(row, dtype=np.int32)) if row else 0
-        e.block_table[slot].copy_(e.block_table_host[slot], non_blocking=True)
+        if not row:
+            return
+        host = e.table_stage.begin()
+        host[: len(row)] = torch.from_numpy(np.asarray(row, dtype=np.int32))
+        e.table_stage.push(e.block_table[slot, : len(row)], host[: len(row)])
 
     def new_host_store(self, n_slots: int, pages_per_block: int):
         torch = self.torch

@@ -35,6 +35,37 @@ def _lockstep(rank, world, port, q):
         q.put(("follower", n, eng.length(0), list(eng.seqs[0])))
 
 
+def _sharded(rank, world, port, q):
+    """A tensor-parallel mock: every rank holds its slice of the vocabulary, as the GPU engines do."""
+    sys.path.insert(0, ROOT)
+    import numpy as np
+    from b200serve.parallel import launch as L
+    from b200serve.server.iface import MockEngine
+    _init(rank, world, port)
+    plane = L.ControlPlane()
+
+    class Sharded(MockEngine):
+        def logits_shard(self, slot, row=0):
+            full = np.asarray(MockEngine.logits(self, slot, row), dtype=np.float32)
+            per = (self.vocab_size + world - 1) // world
+            return rank * per, full[rank * per: (rank + 1) * per]
+
+        def logits(self, slot, row=0):           # what a shard-holding engine returns by itself: its slice only
+            return self.logits_shard(slot, row)[1]
+
+    eng = Sharded(vocab_size=259, max_seqs=2)
+    if rank == 0:
+        lead = L.LockstepLeader(eng, plane)
+        first = lead.prefill(0, [5, 6, 7])
+        row = lead.logits(0, 0)
+        want = np.asarray(MockEngine.logits(eng, 0, 0), dtype=np.float32)
+        lead.shutdown()
+        q.put(("leader", len(row), bool(np.array_equal(row, want)), int(row.argmax()), first))
+    else:
+        n = L.follow_lockstep(eng, plane)
+        q.put(("follower", n))
+
+
 def _replica(rank, world, port, q):
     sys.path.insert(0, ROOT)
     from b200serve.parallel import launch as L
@@ -75,6 +106,24 @@ def test_lockstep_followers_execute_every_leader_call():
     _, n, flen, fseq = res["follower"]
     assert n == 3 and flen == length == 3          # prefill, step, truncate reached the follower
     assert fseq == [5, 6, 7]
+
+
+def test_lockstep_leader_assembles_full_vocabulary_row_from_shards():
+    # a sampled request under tensor parallelism must see vocab_size logits, not rank 0's slice
+    res = _spawn(_sharded, port=29703)
+    _, n, equal, top, first = res["leader"]
+    assert n == 259 and equal and top == first
+    assert res["follower"][1] == 2                  # prefill and the shard request reached the follower
+
+
+def test_native_samplers_refuse_a_short_row():
+    import numpy as np
+    from b200serve.native import host as H
+    row = np.zeros(100, dtype=np.float32)
+    for call in (lambda: H.sample(row, 259, 1.0, 0, 1.0, 1), lambda: H.argmax_low_tie(row, 259),
+                 lambda: H.apply_repetition_penalty(row, 259, [1, 2], 1.1)):
+        with pytest.raises(ValueError):
+            call()
 
 
 def test_replica_router_routes_slots_to_ranks():
