@@ -82,7 +82,8 @@ class PrefixCache {
   Plan plan(int root, const std::vector<uint32_t>& prompt, const std::vector<uint32_t>& resident, bool split_last) {
     Plan pl;
     const int n = (int)prompt.size();
-    const int limit = split_last ? n - 1 : n - 1;  // logits of the last prompt token are always needed
+    // the last prompt token is always run (its logits are needed); split_last keeps one more position out
+    const int limit = split_last ? n - 2 : n - 1;
     int common = 0;
     while (common < (int)resident.size() && common < limit && resident[common] == prompt[common]) ++common;
     pl.path = match(root, prompt, std::max(0, limit));

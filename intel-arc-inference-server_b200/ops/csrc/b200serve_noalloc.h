@@ -17,10 +17,11 @@
  * Limits (the fixed array is 2 MiB + 32 KiB and stays resident on every GPU that loads the
  * library, until the process exits):
  *     M (rows)        1 .. 4
- *     n_q (heads)     1 .. 64, a multiple of n_kv
+ *     n_q (heads)     1 .. 64, a multiple of n_kv with n_q / n_kv one of 1, 2, 4, 5, 8
  *     nsplit          1 .. 16
  *     D (head size)   64 or 128
- * A call beyond them returns -10 and launches nothing; use b2_attn_decode with your own buffers.
+ * A call beyond them (or on a device whose index is 64 or more) returns -10 and launches nothing; use
+ * b2_attn_decode with your own buffers.
  *
  * Set-up.  The first call on each device resolves the array's device address (with that device
  * current); it launches nothing extra and allocates nothing, but it is a runtime query, so make

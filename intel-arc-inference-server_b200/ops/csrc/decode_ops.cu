@@ -811,10 +811,14 @@ extern "C" int b2_attn_decode_static(const void* q, const void* k_cache, const v
   if (M < 1 || M > kStaticMaxRows || n_q < 1 || n_q > kStaticMaxHeads || nsplit < 1 || nsplit > kStaticMaxSplit ||
       (D != 64 && D != 128) || n_kv < 1 || n_q % n_kv != 0)
     return -10;  // beyond the fixed scratch: use b2_attn_decode with caller-owned buffers
+  {
+    const int gqa = n_q / n_kv;   // the head groupings the kernel is built for
+    if (gqa != 1 && gqa != 2 && gqa != 4 && gqa != 5 && gqa != 8) return -10;
+  }
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return (int)e;
-  if (dev < 0 || dev >= 64) return -11;
+  if (dev < 0 || dev >= 64) return -10;   // the per-device address table holds 64 devices
   if (!g_static_attn_ptr[dev]) {
     // first call on this device: resolve the array's device address (no allocation takes place)
     void* ptr = nullptr;

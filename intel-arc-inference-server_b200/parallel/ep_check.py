@@ -18,6 +18,42 @@ import sys
 import torch
 
 
+def self_check(cfg, modes=("fused", "nccl"), n_tokens: int = 300) -> dict:
+    """The model with its experts spread over the ranks against the same model on one GPU: every rank holds the whole
+    (small) model, runs a prompt alone as the answer, then the group runs the same prompt in each mode; logits must
+    agree within rounding and the next token must be the same.  Returns ``{mode: {..., "ok": bool}}``."""
+    import torch.distributed as dist
+    from ..models.weights import random_weights
+    from ..ops import lib as K
+    from ..runtime.engine import Engine
+    from ..runtime.prefill import PrefillRunner
+    from . import ep as EP
+    world = dist.get_world_size() if dist.is_initialized() else 1
+    rank = dist.get_rank() if dist.is_initialized() else 0
+    dev = torch.device("cuda", torch.cuda.current_device())
+    report = {}
+    full = random_weights(cfg, device=dev, seed=4)
+    g = torch.Generator().manual_seed(12)
+    ids = torch.randint(0, cfg.vocab, (n_tokens,), generator=g).tolist()
+    one = Engine(full, max_seqs=1, max_len=1024, use_graphs=False)
+    t_ref = PrefillRunner(one, max_chunk=512).run(0, ids)
+    ref = one.model.buf.logits[0].clone()
+    shard = EP.ep_shard_weights(full, rank, world)
+    for mode in modes:
+        eng = Engine(shard, max_seqs=1, max_len=1024, use_graphs=False)
+        runner = PrefillRunner(eng, max_chunk=512)
+        runner.ep = EP.EpMoe(cfg, 512, mode=mode)
+        t = runner.run(0, ids)
+        K.check_status()
+        err = float((eng.model.buf.logits[0] - ref).abs().max())
+        good = err < 0.02 * float(ref.abs().max()) and t == t_ref
+        report[mode] = {"logit_err": err, "logit_scale": float(ref.abs().max()), "token": t, "want": t_ref, "ok": good}
+        if world > 1:
+            dist.barrier()
+        runner.ep.close()
+    return report
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--model", default="small-moe")
@@ -40,26 +76,9 @@ def main():
     report = {"world": world, "model": cfg.name}
     ok = True
     if args.check:
-        full = random_weights(cfg, device=dev, seed=4)
-        g = torch.Generator().manual_seed(12)
-        ids = torch.randint(0, cfg.vocab, (300,), generator=g).tolist()
-        one = Engine(full, max_seqs=1, max_len=1024, use_graphs=False)
-        t_ref = PrefillRunner(one, max_chunk=512).run(0, ids)
-        ref = one.model.buf.logits[0].clone()
-        shard = EP.ep_shard_weights(full, rank, world)
-        for mode in args.modes.split(","):
-            eng = Engine(shard, max_seqs=1, max_len=1024, use_graphs=False)
-            runner = PrefillRunner(eng, max_chunk=512)
-            runner.ep = EP.EpMoe(cfg, 512, mode=mode)
-            t = runner.run(0, ids)
-            K.check_status()
-            err = float((eng.model.buf.logits[0] - ref).abs().max())
-            good = err < 0.02 * float(ref.abs().max()) and t == t_ref
-            ok = ok and good
-            report[mode] = {"logit_err": err, "token": t, "want": t_ref, "ok": good}
-            if world > 1:
-                dist.barrier()
-            runner.ep.close()
+        chk = self_check(cfg, args.modes.split(","))
+        ok = ok and all(v["ok"] for v in chk.values())
+        report.update(chk)
     if args.prefill:
         report.update(EP.bench_prefill(cfg, args.prefill, args.modes.split(",")))
     if rank == 0:

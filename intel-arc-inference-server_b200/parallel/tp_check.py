@@ -19,6 +19,73 @@ import sys
 import torch
 
 
+def widen_for(cfg, world: int):
+    """A small preset widened (heads, FFN) so that it divides over ``world`` ranks."""
+    if world > 1 and (cfg.n_kv_heads % world or cfg.ffn % (64 * world)):
+        import dataclasses
+        cfg = dataclasses.replace(cfg, n_kv_heads=max(cfg.n_kv_heads, world), n_q_heads=max(cfg.n_q_heads, 2 * world),
+                                  ffn=192 * world)
+    return cfg
+
+
+def self_check(cfg, modes=("fused", "nccl"), prompt_len: int = 40) -> dict:
+    """The sharded model against the same model on one GPU (every rank computes the one-GPU answer itself): logits of
+    the prompt's last position, 12 teacher-forced decode steps, and bit-equal tokens and residual rows on all ranks.
+    Returns ``{mode: {...,"ok": bool}}``; call it on every rank of an initialised process group."""
+    import torch.distributed as dist
+    from ..models.weights import random_weights
+    from ..ops import lib as K
+    from ..runtime.engine import Engine, Row
+    from . import tp as TP
+    world = dist.get_world_size() if dist.is_initialized() else 1
+    rank = dist.get_rank() if dist.is_initialized() else 0
+    dev = torch.device("cuda", torch.cuda.current_device())
+    report = {}
+    full = random_weights(cfg, device=dev, seed=0)
+    g = torch.Generator().manual_seed(5)
+    prompt = torch.randint(0, cfg.vocab, (prompt_len,), generator=g).tolist()
+    one = Engine(full, max_seqs=1, max_len=prompt_len + 216, use_graphs=False)
+    first = one.prefill(0, prompt)
+    ref_logits = one.model.buf.logits[one.last_prefill_row].clone()
+    ref_toks = [first]
+    for _ in range(12):
+        ref_toks.append(one.forward_rows([Row(0, one.seq_len[0], ref_toks[-1])])[0])
+    shard = TP.shard_weights(full, rank, world, dev)
+    per = (cfg.vocab + world - 1) // world
+    for mode in modes:
+        eng = TP.make_engine(shard, mode=mode, max_seqs=1, max_len=prompt_len + 216, use_graphs=(mode == "fused"))
+        t0 = eng.prefill(0, prompt)
+        lg = eng.model.buf.logits[eng.last_prefill_row]
+        want = ref_logits[rank * per: rank * per + lg.numel()]
+        err = float((lg - want).abs().max())
+        scale = float(ref_logits.abs().max())
+        toks = [t0]
+        agree = int(t0 == first)
+        for i in range(12):   # teacher-forced: feed the one-GPU tokens, compare each arg-max
+            t = eng.forward_rows([Row(0, eng.seq_len[0], ref_toks[i])])[0]
+            toks.append(t)
+            agree += int(t == ref_toks[i + 1])
+        tt = torch.tensor(toks, device=dev, dtype=torch.int64)
+        all_t = [torch.empty_like(tt) for _ in range(world)]
+        rs = eng.model.buf.resid[:1].clone().view(torch.int16).to(torch.int64)
+        all_r = [torch.empty_like(rs) for _ in range(world)]
+        if world > 1:
+            dist.all_gather(all_t, tt)
+            dist.all_gather(all_r, rs)
+        else:
+            all_t, all_r = [tt], [rs]
+        same_tok = all(bool((x == all_t[0]).all()) for x in all_t)
+        same_res = all(bool((x == all_r[0]).all()) for x in all_r)
+        K.check_status()
+        good = err < 0.02 * max(scale, 1.0) and agree >= 11 and same_tok and same_res
+        report[mode] = {"logit_err": err, "logit_scale": scale, "agree": agree, "of": 13,
+                        "ranks_same_tokens": same_tok, "ranks_same_residual": same_res, "ok": good}
+        if hasattr(eng, "close"):
+            eng.close()
+        del eng
+    return report
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--model", default="small-dense")
@@ -45,10 +112,8 @@ def main():
     rank, world, local = TP.init_dist()
     dev = torch.device("cuda", local)
     cfg = preset(args.model)
-    if args.check and world > 1 and (cfg.n_kv_heads % world or cfg.ffn % (64 * world)):
-        import dataclasses   # widen the small preset so that it divides over this many ranks
-        cfg = dataclasses.replace(cfg, n_kv_heads=max(cfg.n_kv_heads, world), n_q_heads=max(cfg.n_q_heads, 2 * world),
-                                  ffn=192 * world)
+    if args.check:
+        cfg = widen_for(cfg, world)   # so that the small preset divides over this many ranks
     ok = True
     report = {"world": world, "model": cfg.name}
 
@@ -59,47 +124,9 @@ def main():
         return float(t)
 
     if args.check:
-        full = random_weights(cfg, device=dev, seed=0)
-        g = torch.Generator().manual_seed(5)
-        prompt = torch.randint(0, cfg.vocab, (args.prompt,), generator=g).tolist()
-        one = Engine(full, max_seqs=1, max_len=args.prompt + 216, use_graphs=False)
-        first = one.prefill(0, prompt)
-        ref_logits = one.model.buf.logits[one.last_prefill_row].clone()
-        ref_toks = [first]
-        for _ in range(12):
-            ref_toks.append(one.forward_rows([Row(0, one.seq_len[0], ref_toks[-1])])[0])
-        shard = TP.shard_weights(full, rank, world, dev)
-        per = (cfg.vocab + world - 1) // world
-        for mode in args.modes.split(","):
-            eng = TP.make_engine(shard, mode=mode, max_seqs=1, max_len=args.prompt + 216, use_graphs=(mode == "fused"))
-            t0 = eng.prefill(0, prompt)
-            lg = eng.model.buf.logits[eng.last_prefill_row]
-            want = ref_logits[rank * per: rank * per + lg.numel()]
-            err = float((lg - want).abs().max())
-            scale = float(ref_logits.abs().max())
-            toks = [t0]
-            agree = int(t0 == first)
-            for i in range(12):   # teacher-forced: feed the one-GPU tokens, compare each arg-max
-                t = eng.forward_rows([Row(0, eng.seq_len[0], ref_toks[i])])[0]
-                toks.append(t)
-                agree += int(t == ref_toks[i + 1])
-            tt = torch.tensor(toks, device=dev, dtype=torch.int64)
-            all_t = [torch.empty_like(tt) for _ in range(world)]
-            rs = eng.model.buf.resid[:1].clone().view(torch.int16).to(torch.int64)
-            all_r = [torch.empty_like(rs) for _ in range(world)]
-            if world > 1:
-                dist.all_gather(all_t, tt)
-                dist.all_gather(all_r, rs)
-            else:
-                all_t, all_r = [tt], [rs]
-            same_tok = all(bool((x == all_t[0]).all()) for x in all_t)
-            same_res = all(bool((x == all_r[0]).all()) for x in all_r)
-            K.check_status()
-            good = err < 0.02 * max(scale, 1.0) and agree >= 11 and same_tok and same_res
-            ok = ok and good
-            report[mode] = {"logit_err": err, "logit_scale": scale, "agree": agree, "of": 13,
-                            "ranks_same_tokens": same_tok, "ranks_same_residual": same_res, "ok": good}
-            del eng
+        chk = self_check(cfg, args.modes.split(","), args.prompt)
+        ok = ok and all(v["ok"] for v in chk.values())
+        report.update(chk)
     if args.pp:
         from . import pp as PP
         full = random_weights(cfg, device=dev, seed=0)

@@ -59,6 +59,10 @@ class EngineKV:
     def slot_pages(self, slot: int) -> List[int]:
         return list(self.e.pool.table(slot))
 
+    def slot_length(self, slot: int) -> int:
+        """Positions of the slot whose KV has been written."""
+        return int(self.e.seq_len[slot])
+
     def pin(self, pages: Sequence[int]):
         for p in pages:
             self.e.pool.pin(p)
@@ -203,17 +207,24 @@ class PrefixStore:
         return 0
 
     # ------------------------------------------------------------------ after the prompt pass / at the end
+    def _held(self, slot: int, ids: Sequence[int]) -> List[int]:
+        """The ids whose KV the slot really holds: a token that was emitted but never fed (the last one of a request
+        that ended by length or by a stop string), or the rest of a prompt whose pass was cancelled, has no KV."""
+        n = self.kv.slot_length(slot)
+        return [int(t) for t in ids[: max(0, n)]]
+
     def after_prefill(self, slot: int, prompt: Sequence[int]):
-        self._insert_blocks(slot, [int(t) for t in prompt])
+        self._insert_blocks(slot, self._held(slot, prompt))
 
     def end(self, slot: int, ids: Sequence[int]):
-        ids = [int(t) for t in ids]
+        ids = self._held(slot, ids)
         self._insert_blocks(slot, ids)
         self.resident[slot] = ids
 
     def _insert_blocks(self, slot: int, ids: List[int]):
         pages = self.kv.slot_pages(slot)
-        n_blocks = min(len(ids) // self.block, len(pages) // self.ppb)
+        # whole blocks of WRITTEN positions only: a block whose last position has no KV yet is not shared
+        n_blocks = min(len(ids) // self.block, len(pages) // self.ppb, max(0, self.kv.slot_length(slot)) // self.block)
         parent = self.root
         for b in range(n_blocks):
             blk_ids = ids[b * self.block: (b + 1) * self.block]

@@ -21,6 +21,7 @@ class FakeKV:
     def free_pages(self): return self.pool.free_pages()
     def total_pages(self): return self.num_pages
     def slot_pages(self, slot): return list(self.pool.table(slot))
+    def slot_length(self, slot): return self.seq_len[slot]
     def pin(self, pages): [self.pool.pin(p) for p in pages]
     def unpin(self, pages): [self.pool.unpin(p) for p in pages]
 
@@ -120,3 +121,55 @@ def test_spill_to_host_and_restore_keeps_data():
     cached, computed = run(st, kv, 2, a + [5])
     assert cached == 128 and computed == 1
     assert st.stats["restored_blocks"] >= 2
+
+
+def _boundary_store(block=32):
+    kv = FakeKV()
+    return kv, PrefixStore(kv, host_gb=0, block_tokens=block, device_fraction=0.9)
+
+
+@pytest.mark.parametrize("n_prompt,n_out", [(60, 4), (28, 4), (16, 16), (30, 3)])
+def test_end_records_only_positions_whose_kv_was_written(n_prompt, n_out):
+    # a request that ends by length: its last emitted token was never fed, so the slot holds P + n - 1 positions.
+    # Total lengths on a page boundary (16), on a block boundary (32, 64) and in between.
+    kv, st = _boundary_store()
+    prompt = list(range(100, 100 + n_prompt))
+    out = list(range(500, 500 + n_out))
+    st.begin(0, prompt)
+    kv.prefill(0, prompt)
+    st.after_prefill(0, prompt)
+    kv.prefill(0, prompt + out[:-1])                       # decode steps feed every token but the last one
+    st.end(0, prompt + out)
+    held = n_prompt + n_out - 1
+    assert len(st.resident[0]) == held
+    nxt = prompt + out + [7, 8, 9]
+    got = st.begin(0, nxt)
+    assert got <= held and got % PAGE == 0
+    kv.check(0, nxt, got)
+    # blocks in the index cover written positions only
+    assert st.stats["inserted"] == held // 32
+
+
+def test_cancel_in_the_middle_of_the_prompt_pass_keeps_the_written_part_only():
+    kv, st = _boundary_store()
+    prompt = list(range(200, 300))
+    st.begin(1, prompt)
+    kv.prefill(1, prompt[:40])                              # the pass was cancelled after 40 positions
+    st.end(1, prompt)
+    assert len(st.resident[1]) == 40
+    got = st.begin(1, prompt)
+    assert got <= 40 and got % PAGE == 0
+    kv.check(1, prompt, got)
+
+
+def test_split_last_keeps_one_more_position_out():
+    ix = H.PrefixCache(16)
+    root = ix.root("bf16")
+    ids = list(range(33))
+    ix.insert(root, ids[0:16], [1])
+    node = ix.match(root, ids, 32)[0]
+    ix.insert(node, ids[16:32], [2])
+    # 33-token prompt: positions 0..31 may come from the cache, the last token is run
+    assert ix.plan(root, ids, [], False)["matched_tokens"] == 32
+    # split_last: the match must end before position n - 2 as well, so the second block no longer fits
+    assert ix.plan(root, ids, [], True)["matched_tokens"] == 16
