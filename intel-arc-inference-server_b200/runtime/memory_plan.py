@@ -13,7 +13,18 @@ from dataclasses import dataclass
 from ..models.config import ModelConfig
 
 RESERVE_BYTES = int(1.5 * 2 ** 30)        # left free for the CUDA context, NCCL, fragmentation
-HBM_BYTES = 183_359 * 2 ** 20             # what nvidia-smi reports for a B200
+HBM_BYTES = 183_359 * 2 ** 20             # what nvidia-smi reports for a B200 (used when no device can be asked)
+
+
+def device_budget() -> int:
+    """Total memory of the current CUDA device as the driver reports it; the B200 figure on a machine without one."""
+    try:
+        import torch
+        if torch.cuda.is_available():
+            return int(torch.cuda.get_device_properties(torch.cuda.current_device()).total_memory)
+    except Exception:  # noqa: BLE001
+        pass
+    return HBM_BYTES
 
 
 @dataclass
@@ -69,6 +80,10 @@ def step_scratch_bytes(cfg: ModelConfig, max_rows: int = 64, nsplit: int = 32) -
     b = max_rows * (2 * h * 2 + 2 * cfg.q_dim * 2 + cfg.vocab * 4)
     b += max_rows * cfg.n_q_heads * nsplit * (cfg.head_dim + 2) * 4
     b += 16 * max_rows * (cfg.qkv_dim + 2 * h + 2 * max(cfg.ffn, cfg.expert_ffn * max(cfg.top_k, 1))) * 4
+    kmax = max(2 * h, cfg.q_dim, cfg.ffn, cfg.expert_ffn, cfg.shared_ffn, cfg.gdn_value_dim)
+    b += max_rows * (kmax // 64) * (128 + 8) + (1 << 16)      # quantised rows + group scales, small control words
+    if cfg.n_gdn_layers:
+        b += max_rows * (cfg.gdn_proj_dim * 4 + cfg.gdn_value_dim * 2)
     return int(b)
 
 
@@ -89,8 +104,10 @@ def prefill_scratch_bytes(cfg: ModelConfig, chunk: int, backend: str) -> int:
 
 def plan(cfg: ModelConfig, max_seqs: int, max_len, kv_dtype: str = "bf16", int8_head: bool = False,
          prefill_backend: str = "auto", prefill_chunk: int = 4096, tp: int = 1, ep: int = 1,
-         budget: int = HBM_BYTES) -> MemoryPlan:
-    """``max_len`` an int or "auto".  Raises ValueError with the numbers when it cannot fit."""
+         budget: int = 0) -> MemoryPlan:
+    """``max_len`` an int or "auto"; ``budget`` 0: what the current device reports.  Raises ValueError with the
+    numbers when it cannot fit."""
+    budget = budget or device_budget()
     w = weight_bytes(cfg, int8_head, tp, ep)
     resident = 0
     if prefill_backend == "auto":    # the prompt pass keeps bf16 copies when they take at most 45 % of the memory

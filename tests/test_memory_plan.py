@@ -120,3 +120,25 @@ def test_quant_x_refuses_buffers_that_are_too_small():
     with pytest.raises(ValueError):
         K.quant_x(torch.zeros(65, k, dtype=torch.bfloat16), 65, k, torch.zeros(65 * (k // 64) * 128, dtype=torch.uint8),
                   torch.zeros(64 * (k // 64) * 2, dtype=torch.int32))
+
+
+@pytest.mark.parametrize("name", ["tiny-dense", "small-dense", "small-moe", "small-hybrid", "dense-27b"])
+def test_every_step_buffer_is_known_to_the_planner(name):
+    """The allocator and the planner agree: every tensor of StepBuffers / KVCache has a registry entry, and each
+    group holds no more than the planner budgets (the reference enforces this at compile time)."""
+    import torch
+    from b200serve.models.config import preset
+    from b200serve.models.decoder import KVCache, StepBuffers, attn_splits
+    from b200serve.ops import lib as K
+    from b200serve.runtime import buffer_registry as R
+    cfg = preset(name)
+    rows = 8 if name == "dense-27b" else 64
+    buf = StepBuffers(cfg, rows, attn_splits(cfg.n_kv_heads, 4096), "cpu")
+    for lin in cfg.linears():                   # the split-K partial sums a step allocates on first use
+        buf.part(lin.name, K.gemv_splits(lin.n, lin.k), lin.n)
+    kv = KVCache(cfg, cfg.n_layers, 9, "cpu", "bf16", n_slots=2)
+    groups = R.audit(buf, kv, cfg, "bf16", max_seqs=2)
+    assert groups["step"] > 0 and groups["kv"] > 0
+    buf.surprise = torch.zeros(4)               # a buffer nobody told the planner about
+    with pytest.raises(AssertionError, match="surprise"):
+        R.audit(buf, kv, cfg, "bf16", max_seqs=2)
