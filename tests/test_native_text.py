@@ -63,6 +63,53 @@ def test_tokenizer_random_strings(trained):
         assert mine.encode(s) == ref.encode(s, add_special_tokens=False).ids, repr(s)
 
 
+# the reference checkout, when there is one beside this repository (or where REFERENCE_DIR points)
+REF_TOK_DIR = os.path.join(os.environ.get("REFERENCE_DIR") or os.path.join(
+    os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "reference"), "tests")
+
+
+def test_tokenizer_parity_over_the_reference_corpus(tmp_path):
+    """Every line of the reference's tokenizer parity corpus (10,240 cases: prose, code, numbers, scripts, whitespace
+    runs) through both libraries, with a vocabulary trained on part of that corpus and the pre-tokeniser pattern
+    read from the reference's own tokenizer file.  (The reference's expected ids belong to a full vocabulary that is
+    not on this machine, so the library it wraps is the judge.)"""
+    import json
+    corpus = os.path.join(REF_TOK_DIR, "tokenizer", "corpus.txt")
+    tokjson = os.path.join(REF_TOK_DIR, "model", "qwen4exp-q38tok", "tokenizer.json")
+    if not (os.path.exists(corpus) and os.path.exists(tokjson)):
+        pytest.skip("the reference's tokenizer corpus is not on this machine")
+    pytest.importorskip("tokenizers")
+    from tokenizers import Regex, Tokenizer, decoders, models, pre_tokenizers, trainers
+    with open(tokjson) as f:
+        pat = json.load(f)["pre_tokenizer"]["pretokenizers"][0]["pattern"]["Regex"]
+    with open(corpus, encoding="utf-8") as f:
+        lines = f.read().split("\n")
+    tok = Tokenizer(models.BPE())
+    tok.pre_tokenizer = pre_tokenizers.Sequence([
+        pre_tokenizers.Split(Regex(pat), behavior="isolated"),
+        pre_tokenizers.ByteLevel(add_prefix_space=False, use_regex=False)])
+    tok.decoder = decoders.ByteLevel()
+    trainer = trainers.BpeTrainer(vocab_size=4000, special_tokens=["<|endoftext|>", "<|im_start|>", "<|im_end|>"],
+                                  initial_alphabet=pre_tokenizers.ByteLevel.alphabet())
+    tok.train_from_iterator(lines[::3], trainer)
+    path = str(tmp_path / "tokenizer.json")
+    tok.save(path)
+    mine = H.Tokenizer.from_file(path)
+    bad = []
+    for i, s in enumerate(lines):
+        want = tok.encode(s, add_special_tokens=False).ids
+        got = mine.encode(s)
+        if got != want:
+            bad.append((i, s[:80]))
+            if len(bad) > 5:
+                break
+    assert not bad, bad
+    # the whole file as one text too: line ends meet the whitespace rules of the pattern
+    blob = "\n".join(lines[:2000])
+    assert mine.encode(blob) == tok.encode(blob, add_special_tokens=False).ids
+    assert mine.decode(mine.encode(blob)).decode("utf-8") == blob
+
+
 def test_special_tokens_and_streamer(trained):
     _, mine, _ = trained
     ids = mine.encode("<|im_start|>héllo 😀<|im_end|>")
