@@ -64,7 +64,7 @@ class ServeFlags:
     prefix_split_last: bool = flag(False, "keep the prompt's last position out of the cached prefix")
     kv_cache: str = flag("bf16", "KV cache element type", ["bf16", "int8"])
     prefill_backend: str = flag("auto", "prompt-pass GEMM path",
-                                ["auto", "bf16", "bf16-resident", "int8", "l0", "l0-int8", "rows"])
+                                ["auto", "w4", "bf16", "bf16-resident", "int8", "l0", "l0-int8", "rows"])
     int8_head: bool = flag(False, "quantise lm_head to int8 with per-row scales")
     draft_vocab: int = flag(0, "reduced draft vocabulary size (0: full)")
     draft_vocab_ids: Optional[str] = flag(None, "file with the ranked ids of the draft vocabulary")
@@ -88,6 +88,6 @@ class DecodeFlags:
     steps: int = flag(8, "--profile: steps averaged")
     repeats: int = flag(3, "--profile / --bench: repetitions, the median is reported")
     kv_cache: str = flag("bf16", "KV cache element type", ["bf16", "int8"])
-    prefill_backend: str = flag("auto", "prompt-pass GEMM path", ["auto", "bf16", "bf16-resident", "int8", "rows"])
+    prefill_backend: str = flag("auto", "prompt-pass GEMM path", ["auto", "w4", "bf16", "bf16-resident", "int8", "rows"])
     int8_head: bool = flag(False, "int8 lm_head")
     seed: int = flag(0, "seed of random-init weights (preset models)")

@@ -142,10 +142,14 @@ def moe_block_prefill(runner, lw: LayerWeights, c: int):
     M.sort(sc.topk_idx, c, k, e, sc.max_blk, sc.counts, sc.rank, sc.expert_base, sc.blk_expert, sc.blk_row0,
            sc.blk_rows, sc.n_blk, sc.total_rows)
     M.scatter(sc.topk_idx, sc.rank, sc.expert_base, c, k, x, h, sc.row_of, sc.xs)
-    gu, dn = _expert_bf16(runner, lw, sc)
     blocks = (sc.blk_expert, sc.blk_row0, sc.blk_rows, sc.n_blk, sc.max_blk)
-    G.gemm_grouped_bf16(sc.xs, gu, sc.act, blocks, epi=G.EPI_SILU_MUL)
-    G.gemm_grouped_bf16(sc.act, dn, sc.y, blocks, epi=G.EPI_BF16)
+    if runner.backend == "w4":      # grouped GEMMs over the experts' int4 blocks (a quarter of the bf16 bytes from HBM)
+        G.gemm_w4(sc.xs, lw.experts_gate_up_w4b, 2 * i, h, sc.act, epi=G.EPI_SILU_MUL, blocks=blocks, n_experts=e)
+        G.gemm_w4(sc.act, lw.experts_down_w4b, h, i, sc.y, epi=G.EPI_BF16, blocks=blocks, n_experts=e)
+    else:
+        gu, dn = _expert_bf16(runner, lw, sc)
+        G.gemm_grouped_bf16(sc.xs, gu, sc.act, blocks, epi=G.EPI_SILU_MUL)
+        G.gemm_grouped_bf16(sc.act, dn, sc.y, blocks, epi=G.EPI_BF16)
     shared_y, gate = None, None
     if lw.shared is not None:
         act = runner.act[:c, : cfg.shared_ffn]

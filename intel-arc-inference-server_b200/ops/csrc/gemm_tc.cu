@@ -18,6 +18,14 @@
 //   warps 2-5 epilogue: tcgen05.ld of the accumulator (two TMEM buffers, so the epilogue of tile i
 //            overlaps the main loop of tile i + 1), scale / SiLU*up / residual add, global stores
 // Tiles are walked M-fastest so CTAs that run together share one weight tile in L2.
+//
+// W4 form (template parameter W4): B is never materialised in global memory.  The producer fetches the W4B blocks of
+// a stage (4352 bytes per 128 rows x 64 k: nibbles + fp16 group scales) with bulk copies; eight more warps expand them
+// to bf16 -- bf16_rne((q - 8) * scale), the same rounding as the dequantising pass -- straight into the stage's
+// B tile in the 128-byte-swizzled K-major layout the MMA descriptors expect, fence the generic stores against the
+// async proxy and complete the stage's barrier.  The weights cross HBM as int4 (a quarter of the bf16 bytes) and
+// no bf16 copy of the model is resident.  The role of the reference's direct-int4 GEMMs
+// (src/kernels/prefill/pf_gemm_q4.cl, src/kernels/prefill/pf_moe_q4gemm.cl:1-40).
 #include "common.cuh"
 #include "wire.cuh"
 
@@ -70,32 +78,43 @@ struct GemmParams {
   // ret_table[rank][slot][N] over NVLink, where the source adds its tokens' slots in slot order.
   const int* row_src;
   const unsigned long long* ret_table;
+  // ---- W4 form: B as W4B blocks [expert][ceil(N / 128)][K / 64][4352 bytes]
+  const uint8_t* w4;
+  long long w4_expert_bytes;
 };
 
-template <int BN>
+constexpr int kW4Block = 4352;     // one W4B block: 128 rows x 64 k of nibbles (4096 B) + 128 fp16 scales
+constexpr int kDequantWarps = 8;   // W4 form: warps that expand the blocks into the B tile
+
+template <int BN, bool W4 = false>
 struct Cfg {
   static constexpr int A_BYTES = BM * BKB;
   static constexpr int B_BYTES = BN * BKB;
   static constexpr int STAGE = A_BYTES + B_BYTES;
-  static constexpr int STAGES = (BN == 256) ? 4 : 6;
+  static constexpr int RAW = W4 ? (BN / 128) * kW4Block : 0;   // the stage's W4B blocks, kept apart so that tiles stay 1024-aligned
+  static constexpr int STAGES = W4 ? ((BN == 256) ? 3 : 5) : ((BN == 256) ? 4 : 6);
   static constexpr int PUSH_STAGE = 4 * 32 * 144;  // per epilogue warp: 32 rows x (128 B + 16 B pad) for coalesced peer stores
-  static constexpr int SMEM = STAGES * STAGE + 1024 /*align*/ + 256 /*barriers*/ + PUSH_STAGE;
+  static constexpr int BARS = 384;
+  static constexpr int SMEM = STAGES * STAGE + 1024 /*align*/ + BARS + PUSH_STAGE + STAGES * RAW;
   static constexpr int TMEM_COLS = 2 * BN;  // two accumulators
+  static constexpr int THREADS = kThreads + (W4 ? kDequantWarps * 32 : 0);
 };
 
-template <int BN, bool I8>
-__global__ void __launch_bounds__(kThreads, 1)
+template <int BN, bool I8, bool W4 = false>
+__global__ void __launch_bounds__(Cfg<BN, W4>::THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                const GemmParams p) {
-  using C = Cfg<BN>;
+  using C = Cfg<BN, W4>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::STAGES * C::STAGE);
   const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + C::STAGES);
   const uint32_t tfull0 = smem_u32(bars + 2 * C::STAGES), tempty0 = smem_u32(bars + 2 * C::STAGES + 2);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * C::STAGES + 4);
+  const uint32_t rawfull0 = smem_u32(bars + 2 * C::STAGES + 6);   // W4 form: a stage's W4B blocks have landed
   const uint32_t smem_base = smem_u32(smem);
-  const uint32_t push_base = smem_base + C::STAGES * C::STAGE + 256;
+  const uint32_t push_base = smem_base + C::STAGES * C::STAGE + C::BARS;
+  const uint32_t raw_base = push_base + C::PUSH_STAGE;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const bool grouped = p.blk_expert != nullptr;
@@ -106,8 +125,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < C::STAGES; ++i) {
-      mbar_init(full0 + 8 * i, 1);
+      mbar_init(full0 + 8 * i, W4 ? 1 + kDequantWarps : 1);   // W4: the A tile's copy and every expanding warp
       mbar_init(empty0 + 8 * i, 1);
+      if (W4) mbar_init(rawfull0 + 8 * i, 1);
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(tfull0 + 8 * i, 1);
@@ -155,16 +175,30 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           if (it >= C::STAGES) ok = mbar_wait(empty0 + 8 * s, ((it / C::STAGES) - 1) & 1, ERR_GEMM_EMPTY_WAIT);
           if (!ok) break;
           const uint32_t sa = smem_base + s * C::STAGE, sb = sa + C::A_BYTES;
-          mbar_expect_tx(full0 + 8 * s, C::STAGE);
           const int kx = kb * (I8 ? BKB : BKB / 2);
-          tma_load_2d(sa, &map_a, kx, row0, full0 + 8 * s);
-          if (grouped) tma_load_3d(sb, &map_b, kx, nt * BN, expert, full0 + 8 * s);
-          else tma_load_2d(sb, &map_b, kx, nt * BN, full0 + 8 * s);
+          if (W4) {
+            // A by TMA; B as the W4B blocks of this 64-k group (one block per 128 rows), expanded by the other warps
+            mbar_expect_tx(full0 + 8 * s, C::A_BYTES);
+            tma_load_2d(sa, &map_a, kx, row0, full0 + 8 * s);
+            const int nb_total = (p.N + 127) / 128, nb0 = nt * (BN / 128);
+            const int nblk = min(BN / 128, nb_total - nb0);
+            const uint8_t* wsrc = p.w4 + (size_t)expert * p.w4_expert_bytes + ((size_t)nb0 * KB + kb) * kW4Block;
+            mbar_expect_tx(rawfull0 + 8 * s, (uint32_t)nblk * kW4Block);
+            for (int b = 0; b < nblk; ++b)
+              bulk_g2s(raw_base + s * C::RAW + b * kW4Block, wsrc + (size_t)b * KB * kW4Block, kW4Block, rawfull0 + 8 * s);
+          } else {
+            mbar_expect_tx(full0 + 8 * s, C::STAGE);
+            tma_load_2d(sa, &map_a, kx, row0, full0 + 8 * s);
+            if (grouped) tma_load_3d(sb, &map_b, kx, nt * BN, expert, full0 + 8 * s);
+            else tma_load_2d(sb, &map_b, kx, nt * BN, full0 + 8 * s);
+          }
         }
       }
       if (!ok) {  // drain what was issued and may never be consumed
-        for (int i = max(0, it - C::STAGES); i < it; ++i)
-          mbar_wait(full0 + 8 * (i % C::STAGES), (i / C::STAGES) & 1, ERR_GEMM_FULL_WAIT);
+        for (int i = max(0, it - C::STAGES); i < it; ++i) {
+          if (W4) mbar_wait(rawfull0 + 8 * (i % C::STAGES), (i / C::STAGES) & 1, ERR_GEMM_FULL_WAIT);
+          else mbar_wait(full0 + 8 * (i % C::STAGES), (i / C::STAGES) & 1, ERR_GEMM_FULL_WAIT);
+        }
       }
     }
   } else if (warp == 1) {
@@ -194,6 +228,59 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           tc_commit(empty0 + 8 * s);  // stage is free once these MMAs have read it
         }
         if (ok) tc_commit(tfull0 + 8 * a);
+      }
+    }
+  } else if (W4 && warp >= 6) {
+    // ------------------------------------------------------------ W4 expansion (warps 6..13)
+    // One 16-byte vector of a W4B block holds rows g and g + 8 of a 16-row tile, 64 k: low nibbles are k 4t..4t+3 of a
+    // 32-k step, high nibbles k + 16 (the operand order of the decode GEMV).  Each vector becomes sixteen 8-byte
+    // pieces of the B tile: row r at r * 128 bytes, 16-byte chunk (k / 8) XOR (r mod 8) -- the 128-byte swizzle.
+    const int dt = threadIdx.x - 6 * 32;   // 0 .. 255
+    int it = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
+      const int nt = t / tiles_m;
+      const int nb_total = (p.N + 127) / 128, nb0 = nt * (BN / 128);
+      const int nblk = min(BN / 128, nb_total - nb0);
+      for (int kb = 0; kb < KB; ++kb, ++it) {
+        const int s = it % C::STAGES;
+        if (ok) ok = __all_sync(0xffffffffu, mbar_wait(rawfull0 + 8 * s, (it / C::STAGES) & 1, ERR_GEMM_FULL_WAIT));
+        if (!ok) break;
+        const uint32_t sb = smem_base + s * C::STAGE + C::A_BYTES, raw = raw_base + s * C::RAW;
+        for (int u = dt; u < nblk * 256; u += kDequantWarps * 32) {
+          const int b = u >> 8, v = u & 255, j = v >> 5, l = v & 31, g = l >> 2, tq = l & 3;
+          uint4 wv;
+          asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(wv.x), "=r"(wv.y), "=r"(wv.z), "=r"(wv.w)
+                       : "r"(raw + b * kW4Block + v * 16));
+          uint32_t sc2;
+          asm volatile("ld.shared.u32 %0, [%1];" : "=r"(sc2) : "r"(raw + b * kW4Block + 4096 + (j * 16 + 2 * g) * 2));
+          const __half2 sh = *reinterpret_cast<const __half2*>(&sc2);
+          const float s_lo = __low2float(sh), s_hi = __high2float(sh);
+          const uint32_t wa[4] = {wv.x, wv.y, wv.z, wv.w};
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            const int row = b * 128 + j * 16 + g + 8 * (c & 1);
+            const float sc = (c & 1) ? s_hi : s_lo;
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+              const uint32_t x = (wa[c] >> (4 * e)) & 0x0F0F0F0Fu;
+              // bytes -> floats through the 2^23 trick: 0x4B0000qq is 8388608 + q, so (q - 8) * s = f * s - 8388616 * s
+              const float f0 = __uint_as_float(__byte_perm(x, 0x4B000000u, 0x7440));
+              const float f1 = __uint_as_float(__byte_perm(x, 0x4B000000u, 0x7441));
+              const float f2 = __uint_as_float(__byte_perm(x, 0x4B000000u, 0x7442));
+              const float f3 = __uint_as_float(__byte_perm(x, 0x4B000000u, 0x7443));
+              const float off = -8388616.f;
+              const uint32_t p01 = pack_bf16((f0 + off) * sc, (f1 + off) * sc);
+              const uint32_t p23 = pack_bf16((f2 + off) * sc, (f3 + off) * sc);
+              const int k0 = 32 * (c >> 1) + 16 * e + 4 * tq;
+              const uint32_t dst = sb + row * 128 + ((((uint32_t)k0 >> 3) ^ ((uint32_t)row & 7u)) << 4) + (k0 & 7) * 2;
+              asm volatile("st.shared.v2.u32 [%0], {%1, %2};" ::"r"(dst), "r"(p01), "r"(p23) : "memory");
+            }
+          }
+        }
+        fence_proxy_async_smem();   // the MMA reads the tile through the async proxy
+        __syncwarp();
+        if (lane == 0) mbar_arrive(full0 + 8 * s);
       }
     }
   } else {
@@ -479,7 +566,48 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, in
   return (int)cudaGetLastError();
 }
 
+template <int BN>
+int launch_w4(const CUtensorMap& ma, const GemmParams& p, int n_tiles_max, cudaStream_t st) {
+  static bool configured[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (!configured[dev & 63]) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         Cfg<BN, true>::SMEM);
+    if (e != cudaSuccess) return (int)e;
+    configured[dev & 63] = true;
+  }
+  const int grid = min(n_tiles_max, sm_count());
+  gemm_tc_kernel<BN, false, true><<<grid, Cfg<BN, true>::THREADS, Cfg<BN, true>::SMEM, st>>>(ma, ma, p);
+  return (int)cudaGetLastError();
+}
+
 }  // namespace
+
+// C = A * W^T with W read as int4: a [M][K] bf16, w4b the W4B blocks [E][ceil(N / 128)][K / 64][4352] (E = 1 unless the
+// blk_* tables of the grouped form are given).  Epilogues 0..3 as b2_gemm_tc.
+extern "C" int b2_gemm_w4(const void* a, const void* w4b, void* c, int M, int N, int K, int ldc, int epi, const void* resid,
+                          const int* blk_expert, const int* blk_row0, const int* blk_rows, const int* n_blk, int max_blk,
+                          int n_experts, int bn, void* stream) {
+  if (K % 64 != 0 || M < 1 || N % 8 != 0 || epi < EPI_BF16 || epi > EPI_RESID_ADD) return -1;
+  if (epi == EPI_SILU_MUL && N % 32 != 0) return -2;
+  if (((uintptr_t)w4b) & 15) return -3;
+  GemmParams p = {};
+  p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.C = c; p.resid = (const __nv_bfloat16*)resid; p.epi = epi;
+  p.blk_expert = blk_expert; p.blk_row0 = blk_row0; p.blk_rows = blk_rows; p.n_blk = n_blk; p.max_blk = max_blk;
+  p.rs_world = 1; p.rs_tpr = 1;
+  p.w4 = (const uint8_t*)w4b;
+  p.w4_expert_bytes = (long long)((N + 127) / 128) * (K / 64) * kW4Block;
+  if (bn != 128 && bn != 256) bn = (N >= 256 && (N % 256 == 0 || N > 2048)) ? 256 : 128;
+  CUtensorMap ma;
+  int rc = make_map(&ma, a, false, (uint64_t)M, (uint64_t)K, 1, BM);
+  if (rc) return rc;
+  const int tiles_m = blk_expert ? max_blk : (M + BM - 1) / BM;
+  const int n_tiles = tiles_m * ((N + bn - 1) / bn);
+  (void)n_experts;
+  cudaStream_t st = (cudaStream_t)stream;
+  return bn == 256 ? launch_w4<256>(ma, p, n_tiles, st) : launch_w4<128>(ma, p, n_tiles, st);
+}
 
 // C = A * B^T.  a: [M][K], b: [N][K] (or [E][N][K] when blk_* are given), both bf16 (i8 = 0) or int8 (i8 = 1).
 static int gemm_tc_impl(const void* a, const void* b, void* c, int M, int N, int K, int ldc, int i8, int epi,

@@ -38,6 +38,21 @@ def gemm_i8(a8, b8, a_scale, b_scale, c, epi: int = EPI_BF16, resid=None, bn: in
     _launch(a8, b8, c, m, n, k, c.stride(0), True, epi, resid=resid, a_scale=a_scale, b_scale=b_scale, bn=bn)
 
 
+def gemm_w4(a: torch.Tensor, w4b: torch.Tensor, n: int, k: int, c: torch.Tensor, epi: int = EPI_BF16,
+            resid: Optional[torch.Tensor] = None, blocks=None, n_experts: int = 1, bn: int = 0):
+    """``c = epilogue(a @ W.T)`` with ``W`` read as int4: ``w4b`` holds the W4B blocks of an ``[n][k]`` weight (or of
+    ``n_experts`` stacked ones with ``blocks`` = the grouped form's tables).  The blocks are expanded to bf16 inside
+    the kernel's shared-memory tiles (``bf16_rne((q - 8) * scale)``, the bits ``dequant_w4b`` produces); no bf16
+    copy of the weight exists in global memory."""
+    be = br0 = brn = nb = None
+    max_blk = 0
+    if blocks is not None:
+        be, br0, brn, nb, max_blk = blocks
+    rc = K.lib().b2_gemm_w4(K._p(a), K._p(w4b), K._p(c), a.shape[0], n, k, c.stride(0), epi, K._p(resid), K._p(be),
+                            K._p(br0), K._p(brn), K._p(nb), max_blk, n_experts, bn, K._stream())
+    K._check(rc, "gemm_w4")
+
+
 def gemm_tp(a, b, c, epi: int, *, rs=None, rs_tpr: int = 1, ag_cnt=None, ag_expect: int = 0, bn: int = 0,
             a_scale=None, b_scale=None):
     """The tensor-parallel forms of the GEMM (bf16, or int8 when scales are given).

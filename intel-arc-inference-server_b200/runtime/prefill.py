@@ -77,6 +77,8 @@ class PrefillRunner:
             # instead of dequantising a slab before every GEMM
             total = torch.cuda.get_device_properties(self.dev).total_memory if self.dev.type == "cuda" else 0
             self.backend = "bf16-resident" if 2 * cfg.param_count() <= 0.45 * total else "bf16"
+        if self.backend in ("int4", "w4a16"):
+            self.backend = "w4"
         if self.backend == "l0":
             self.backend = "bf16"
         if self.backend == "l0-int8":
@@ -131,6 +133,8 @@ class PrefillRunner:
             G.quant_rows_i8(a, a8, self.a_scale[:rows])
             w8, ws = self._w_i8(ql)
             G.gemm_i8(a8, w8, self.a_scale[:rows], ws, out, epi=epi, resid=resid)
+        elif self.backend == "w4":      # the GEMM reads the int4 blocks itself: nothing but the W4B weights is resident
+            G.gemm_w4(a, ql.w4b, ql.n, ql.k, out, epi=epi, resid=resid)
         else:
             G.gemm_bf16(a, self._w_bf16(ql), out, epi=epi, resid=resid)
 

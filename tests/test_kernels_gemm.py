@@ -122,3 +122,76 @@ def test_gemm_grouped():
         assert (c[r0:r0 + rn].float() - ref).abs().max() <= 1e-2 * ref.abs().max()
     # rows beyond a block's valid count are not written
     assert (c[130:256] == 0).all()
+
+
+def _rowwise_close(got, ref, cos_min=0.9995, tile=32, tile_tol=0.03):
+    """Per-row cosine and per-32-column-piece error against the piece's own scale: a wrong piece of small values does
+    not hide behind the tensor's largest element."""
+    cos = torch.nn.functional.cosine_similarity(got.float(), ref.float(), dim=1)
+    assert float(cos.min()) > cos_min, float(cos.min())
+    m, n = ref.shape
+    n32 = n // tile * tile
+    g = got.float()[:, :n32].reshape(m, n32 // tile, tile)
+    r = ref.float()[:, :n32].reshape(m, n32 // tile, tile)
+    scale = r.abs().amax(dim=2).clamp_min(float(ref.abs().mean()))
+    assert float(((g - r).abs().amax(dim=2) / scale).max()) < tile_tol
+
+
+@pytest.mark.parametrize("m,n,k,bn", [(128, 256, 64, 256), (128, 128, 128, 128), (300, 512, 256, 256),
+                                      (200, 384, 192, 128), (4096, 1024, 512, 0), (77, 264, 128, 0),
+                                      (1000, 5120, 1024, 0), (512, 1408, 512, 256)])
+def test_gemm_w4_reads_int4_and_matches_the_dequantised_gemm(m, n, k, bn):
+    """The GEMM that expands W4B blocks in shared memory against (a) the bf16 GEMM over the dequantised weight:
+    the same bits, both accumulate the same bf16 operands in the same order; (b) fp32 matmul, per row and per piece."""
+    g = G()
+    torch.manual_seed(m + n + k)
+    w4b = Q.random_w4b(n, k, "cuda", seed=n + k)
+    a = torch.randn(m, k, device="cuda").to(torch.bfloat16)
+    wb = g.dequant_w4b(w4b, n, k)
+    c = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device="cuda")
+    g.gemm_w4(a, w4b, n, k, c, bn=bn)
+    c2 = torch.empty_like(c)
+    g.gemm_bf16(a, wb, c2, bn=bn)
+    torch.cuda.synchronize()
+    K().check_status()
+    assert torch.isfinite(c.float()).all()
+    assert torch.equal(c, c2)
+    _rowwise_close(c, a.float() @ wb.float().t())
+
+
+def test_gemm_w4_epilogues_and_grouped_form():
+    g = G()
+    torch.manual_seed(9)
+    m, n, k = 300, 512, 256
+    w4b = Q.random_w4b(n, k, "cuda", seed=1)
+    wb = g.dequant_w4b(w4b, n, k)
+    a = torch.randn(m, k, device="cuda").to(torch.bfloat16)
+    ref = a.float() @ wb.float().t()
+    cs = torch.zeros(m, n // 2, dtype=torch.bfloat16, device="cuda")
+    g.gemm_w4(a, w4b, n, k, cs, epi=g.EPI_SILU_MUL)
+    v = ref.reshape(m, n // 32, 2, 16)
+    _rowwise_close(cs, (torch.nn.functional.silu(v[:, :, 0]) * v[:, :, 1]).reshape(m, n // 2), tile=16, tile_tol=0.05)
+    r = torch.randn(m, n, device="cuda").to(torch.bfloat16)
+    want = r.float() + ref
+    g.gemm_w4(a, w4b, n, k, r, epi=g.EPI_RESID_ADD, resid=r)
+    _rowwise_close(r, want)
+    # grouped: three experts, blocks of uneven row counts, one launch
+    e = 3
+    ws = torch.stack([Q.random_w4b(n, k, "cuda", seed=10 + i) for i in range(e)])
+    rows = [130, 0, 77]
+    blk_e, blk_r0, blk_n, row = [], [], [], 0
+    for ei, cnt in enumerate(rows):
+        for b0 in range(0, cnt, 128):
+            blk_e.append(ei); blk_r0.append(row + b0); blk_n.append(min(128, cnt - b0))
+        row += (cnt + 127) // 128 * 128
+    i32 = dict(dtype=torch.int32, device="cuda")
+    blocks = (torch.tensor(blk_e, **i32), torch.tensor(blk_r0, **i32), torch.tensor(blk_n, **i32),
+              torch.tensor([len(blk_e)], **i32), len(blk_e) + 2)
+    xs = torch.randn(row, k, device="cuda").to(torch.bfloat16)
+    y = torch.zeros(row, n, dtype=torch.bfloat16, device="cuda")
+    g.gemm_w4(xs, ws, n, k, y, blocks=blocks, n_experts=e)
+    torch.cuda.synchronize()
+    K().check_status()
+    for ei, r0, cnt in zip(blk_e, blk_r0, blk_n):
+        wref = g.dequant_w4b(ws[ei], n, k).float()
+        _rowwise_close(y[r0: r0 + cnt], xs[r0: r0 + cnt].float() @ wref.t())
