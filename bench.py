@@ -3,9 +3,10 @@
 
     python bench.py --gpus N --steps K --warmup W
 
-One JSON line on rank 0.  ``value`` is decode tokens/s of the whole job (replica
-mode for N > 1: every GPU serves its own request, so the scaling is weak);
-``extra`` carries the prefill numbers.  Weights are random-init in the named
+One JSON line on rank 0.  N = 1: ``value`` is decode tokens/s of one request on the 27B shape.  N > 1: ``value`` is
+the decode tokens/s of ONE model sharded over the N GPUs (tensor parallel, fused NVLink kernels, 8 concurrent
+requests): strong scaling, total work fixed as N grows.  Replica mode (a full copy per GPU) and the NCCL + cuBLAS
+comparison are lines of ``extra``, next to the prompt-pass numbers.  Weights are random-init in the named
 shapes and token ids are synthetic (no network for checkpoints or datasets).
 Timing: CUDA events on the launching stream after W warm-up steps, bracketed by
 a barrier and a device synchronize, max over ranks.  A decode step streams the
@@ -106,6 +107,8 @@ def main():
     ap.add_argument("--prefill-backend", default="auto")
     ap.add_argument("--parallel", default="replica", help="replica | tp (N > 1)")
     ap.add_argument("--extras-budget-s", type=float, default=300.0, help="no further extra starts after this many seconds")
+    ap.add_argument("--windows", type=int, default=5, help="timed windows of --steps steps; the median window is reported")
+    ap.add_argument("--tp-rows", type=int, default=8, help="concurrent requests of the multi-GPU decode headline")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
@@ -116,9 +119,13 @@ def main():
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
     dist = None
+    ctl = None
     if world > 1:
+        import datetime
         import torch.distributed as dist
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        # a short collective timeout: a rank that left a section early must end the job, not hang the GPUs
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local), timeout=datetime.timedelta(minutes=4))
+        ctl = dist.new_group(backend="gloo", timeout=datetime.timedelta(minutes=4))   # host-side agreement between sections
 
     from b200serve.utils.benchlib import run_decode_bench, run_prefill_bench
     from b200serve.ops import lib as K
@@ -133,74 +140,135 @@ def main():
     t_start = time.time()
     res = {}
     extra = {}
-    if args.what in ("all", "decode"):
-        res = run_decode_bench(args, barrier)
-    import gc
-    gc.collect()
-    torch.cuda.empty_cache()
-    if args.what in ("all", "prefill"):
-        extra["prefill"] = run_prefill_bench(args, barrier, model=args.model, backend=args.prefill_backend)
-        gc.collect()
-        torch.cuda.empty_cache()
-        if args.what == "all":
-            a2 = argparse.Namespace(**vars(args))
-            extra["prefill_int8"] = run_prefill_bench(a2, barrier, model=args.model, backend="int8")
-            gc.collect()
-            torch.cuda.empty_cache()
-    if args.what in ("all", "moe"):
-        extra["moe_prefill"] = run_prefill_bench(args, barrier, model="moe-35b-a3b", backend=args.prefill_backend)
-        gc.collect()
-        torch.cuda.empty_cache()
+    state = {"multi_failed": False}
+
     def release():
         """Engines and their resident weight copies hold reference cycles: collect them before the next section."""
         import gc
         gc.collect()
         torch.cuda.empty_cache()
 
-    def guarded(name, fn):
-        """A failing extra is recorded, never fatal: the headline line is printed regardless.  Extras that
-        would start after the time budget is spent are skipped (the same decision on every rank: the clock
-        reading of rank 0 is shared)."""
+    def agree_failed(failed: bool) -> bool:
+        """True on every rank if the section failed on any rank (host-side all-reduce, never queued behind GPU work)."""
+        if ctl is None:
+            return failed
+        t = torch.tensor([1 if failed else 0], dtype=torch.int32)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX, group=ctl)
+        return bool(int(t))
+
+    def guarded(name, fn, multi_rank: bool = False):
+        """A failing extra is recorded, never fatal: the headline line is printed regardless.  Extras that would start
+        after the time budget is spent are skipped (the same decision on every rank: rank 0's clock is shared).
+        After a section whose ranks talk to each other (``multi_rank``) the ranks agree on the outcome: if one of
+        them raised, all record it and no further multi-rank section starts -- the ranks would meet in different
+        collectives otherwise."""
         spent = time.time() - t_start
-        if dist is not None:
-            t = torch.tensor([spent], device="cuda", dtype=torch.float64)
-            dist.broadcast(t, src=0)
+        if ctl is not None:
+            t = torch.tensor([spent], dtype=torch.float64)
+            dist.broadcast(t, src=0, group=ctl)
             spent = float(t)
         if spent > args.extras_budget_s:
             extra[name] = {"skipped": f"time budget of {args.extras_budget_s:.0f} s for extras was spent"}
-            return
+            return None
+        if multi_rank and state["multi_failed"]:
+            extra[name] = {"skipped": "an earlier multi-rank section failed on some rank"}
+            return None
         release()
+        out, err = None, None
         try:
-            extra[name] = fn()
+            out = fn()
         except Exception as e:  # noqa: BLE001
-            extra[name] = {"error": f"{type(e).__name__}: {e}"[:400]}
+            err = f"{type(e).__name__}: {e}"[:400]
+        if multi_rank and agree_failed(err is not None):
+            state["multi_failed"] = True
+            err = err or "another rank raised in this section"
+        extra[name] = {"error": err} if err is not None else out
+        release()
+        return None if err is not None else out
+
+    one_gpu_sections = world == 1 or args.what in ("decode", "prefill", "moe")
+    if args.what in ("all", "decode") and one_gpu_sections:
+        res = run_decode_bench(args, barrier)
+        release()
+    if args.what in ("all", "prefill") and one_gpu_sections:
+        extra["prefill"] = run_prefill_bench(args, barrier, model=args.model, backend=args.prefill_backend)
+        release()
+        if args.what == "all":
+            extra["prefill_int8"] = run_prefill_bench(args, barrier, model=args.model, backend="int8")
+            release()
+    if world == 1 and args.what in ("all", "prefill32k"):
+        # the long prompt of the 27B configuration (32,768 tokens), both prompt-pass forms
+        for name, backend in (("prefill_32k", args.prefill_backend), ("prefill_32k_int8", "int8")):
+            guarded(name, lambda b=backend: run_prefill_bench(args, barrier, model=args.model, backend=b, n=32768, warm=1, reps=2))
+    if args.what in ("all", "moe") and one_gpu_sections:
+        extra["moe_prefill"] = run_prefill_bench(args, barrier, model="moe-35b-a3b", backend=args.prefill_backend)
         release()
 
-    def tp_extra():
-        # the same model as ONE tensor-parallel group over all the GPUs: fused NVLink kernels against the
-        # in-tree NCCL (+ cuBLAS for the prompt pass) comparison, max over ranks
-        from b200serve.models.config import preset
-        from b200serve.parallel import tp as TP
-        cfg = preset(args.model)
-        peaks = {}
+    def load_peaks():
         pk = os.path.join(os.path.dirname(os.path.abspath(__file__)), "MEASURED_PEAKS.json")
         if os.path.exists(pk):
             with open(pk) as f:
-                peaks = json.load(f)
+                return json.load(f)
+        return {}
+
+    def tp_headline():
+        # ONE model over all the GPUs (tensor parallel, fused NVLink kernels), 8 concurrent requests: the whole job's
+        # decode tokens/s, device-timed and end to end (host rows in, tokens out every step)
+        from b200serve.models.config import preset
+        from b200serve.parallel import tp as TP
+        return TP.bench_decode(preset(args.model), "fused", args.depth, args.steps, max(args.warmup, 3), rows=args.tp_rows,
+                               windows=args.windows, e2e=True, kv_dtype=args.kv_cache)
+
+    def tp_extra():
+        # the same group against the in-tree NCCL (+ cuBLAS for the prompt pass) build, the one-request step, the
+        # prompt pass, the fused GEMM pair against its roofline, and a small sharded model against one GPU
+        from b200serve.models.config import preset
+        from b200serve.parallel import tp as TP
+        from b200serve.parallel import tp_check as TPC
+        cfg = preset(args.model)
+        steps, warm = min(args.steps, 32), max(args.warmup, 3)
         tpx = {"world": world, "parallelism": f"tp{world}"}
+        tpx["self_check_small_dense"] = TPC.self_check(TPC.widen_for(preset("small-dense"), world), ("fused", "nccl"), 200)
+        tpx["decode8_nccl"] = TP.bench_decode(cfg, "nccl", args.depth, steps, warm, rows=args.tp_rows, kv_dtype=args.kv_cache)
         for mode in ("fused", "nccl"):
-            tpx[f"decode_{mode}"] = TP.bench_decode(cfg, mode, args.depth, min(args.steps, 32), max(args.warmup, 3))
-            tpx[f"decode8_{mode}"] = TP.bench_decode(cfg, mode, args.depth, min(args.steps, 32), max(args.warmup, 3), rows=8)
+            tpx[f"decode_{mode}"] = TP.bench_decode(cfg, mode, args.depth, steps, warm)
             tpx[f"prefill_{mode}"] = TP.bench_prefill(cfg, mode, args.prefill_len)
-        tpx["fused_ops"] = TP.bench_fused_ops(cfg, args.prefill_len, peaks=peaks)
+        tpx["fused_ops"] = TP.bench_fused_ops(cfg, args.prefill_len, peaks=load_peaks())
         return tpx
+
+    def replica_extra():
+        # a full copy of the model per GPU, one request each (no collective involved): total tokens/s = N x one GPU
+        r = run_decode_bench(args, barrier)
+        t = torch.tensor([r["ms_per_step"]], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_max = float(t)
+        return {"parallelism": f"replica x{world}", "ms_per_step_max_over_ranks": ms_max,
+                "tokens_per_s_total": world * 1e3 / ms_max, "per_gpu_vs_baseline": (1e3 / ms_max) / BASELINE_DECODE_TPS,
+                "config": r["config"]}
 
     def ep_extra():
         # the MoE shape with its experts spread over all the GPUs (data-parallel attention): fused dispatch /
-        # return kernels against NCCL all-to-all around the same grouped GEMMs
+        # return kernels against NCCL all-to-all around the same grouped GEMMs; a small model against one GPU first
         from b200serve.models.config import preset
         from b200serve.parallel import ep as EP
-        return {"world": world, **EP.bench_prefill(preset("moe-35b-a3b"), args.prefill_len)}
+        from b200serve.parallel import ep_check as EPC
+        out = {"world": world, "self_check_small_moe": EPC.self_check(preset("small-moe"))}
+        out.update(EP.bench_prefill(preset("moe-35b-a3b"), args.prefill_len))
+        return out
+
+    if world > 1 and args.what in ("all", "tp", "decode"):
+        hd = guarded("tp_decode_headline", tp_headline, multi_rank=True)
+        if hd is not None:
+            res = {"metric": "decode_tokens_per_s", "baseline": 342.0,      # 8 requests, MTP, replica on 2 cards (README.md:6,51)
+                   "ms_per_step": hd["ms_per_step"], "job_tokens_per_step": hd["rows"],
+                   "e2e_ms_per_step": hd["e2e_ms_per_step"], "h2d": hd["h2d_bytes_per_step"], "d2h": hd["d2h_bytes_per_step"],
+                   "launches": hd["launches_per_step"] * args.steps, "scaling": "strong",
+                   "config": {"model": args.model, "global_batch": hd["rows"], "seq_len": args.depth,
+                              "parallelism": f"tp{world}", "kv_cache": args.kv_cache, "lm_head": "bf16, vocabulary-parallel",
+                              "weights": "W4A16 int4 g64, random init, sharded by heads / FFN columns",
+                              "collectives": "fused NVLink kernels (peer stores + flags inside the GEMV / arg-max); no NCCL on the step",
+                              "l2": "inputs larger than L2 (12.7 GB of weights per step over the group)",
+                              "windows_ms_per_step": hd["windows_ms_per_step"]}}
 
     # The one-GPU features (speculation, prefix cache, hybrid model) are measured in one-GPU runs; a multi-GPU run
     # repeats them only when asked by name, so that its time goes to the scaling numbers and the fused collectives.
@@ -215,9 +283,11 @@ def main():
         from b200serve.utils.benchlib import run_hybrid_bench
         guarded("hybrid", lambda: run_hybrid_bench(args, barrier))
     if world > 1 and args.what in ("all", "tp"):
-        guarded("tp", tp_extra)
+        guarded("tp", tp_extra, multi_rank=True)
     if world > 1 and args.what in ("all", "ep"):
-        guarded("ep", ep_extra)
+        guarded("ep", ep_extra, multi_rank=True)
+    if world > 1 and args.what in ("all", "replica"):
+        guarded("replica", replica_extra, multi_rank=True)
     clocks = sampler.stop()
     try:
         K.check_status()
@@ -243,8 +313,10 @@ def main():
                    "launches": 0, "metric": "extras_only", "baseline": None, "config": {"what": args.what}}
     ms = reduce_max(res["ms_per_step"])
     e2e_ms = reduce_max(res["e2e_ms_per_step"])
-    value = world * res["tokens_per_step"] / (ms / 1e3) if ms else None
-    e2e = world * res["tokens_per_step"] / (e2e_ms / 1e3) if e2e_ms else None
+    # tokens of the WHOLE job per step: a sharded model emits its rows once; independent copies emit one row set each
+    job_tokens = res["job_tokens_per_step"] if "job_tokens_per_step" in res else world * res["tokens_per_step"]
+    value = job_tokens / (ms / 1e3) if ms else None
+    e2e = job_tokens / (e2e_ms / 1e3) if e2e_ms else None
     if rank == 0:
         for k, p in extra.items():
             if "baseline" not in p:
@@ -254,9 +326,16 @@ def main():
         out = {
             "metric": res.get("metric", "decode_tokens_per_s"),
             "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+            "ms_per_step": ms, "higher_is_better": True, "scaling": res.get("scaling", "weak"),
             "vs_baseline": value / res["baseline"] if (value and res["baseline"]) else None,
-            "dtype": "bf16 activations, int4 g64 weights (W4A16), fp32 accumulate", "data": "synthetic",
+            "vs_baseline_per_gpu": value / world / res["baseline"] if (value and res["baseline"]) else None,
+            "dtype": "bf16",
+            "dtype_detail": "W4A16: int4 g64 weights with fp16 group scales; bf16 activations, residual stream and KV; inside "
+                            "the decode GEMV each 64-k group of a row's activations is re-quantised to 15-bit integers "
+                            "(two int8 limbs, one fp32 scale) so the contraction runs as exact integer tensor-core sums; "
+                            "fp32 accumulation across groups, bf16 lm_head",
+            "data": "synthetic",
+            "timing": f"median of {args.windows} windows of {args.steps} steps, each bracketed by barrier + synchronize, CUDA events, max over ranks",
             "config": res["config"],
             "clocks": clocks,
             "e2e": {"value": e2e, "unit": "tokens/s", "h2d_bytes_per_step": res["h2d"],

@@ -165,6 +165,12 @@ class DecoderModel:
         # then reproduces plain decoding exactly); off, the splits adapt to the context (fastest at any depth)
         self.attn_fixed_spans = False
         self.fused = self.nccl is None and os.environ.get("B2_UNFUSED", "0") != "1"     # dense layers: residual folds and norms ride inside the GEMVs
+        # whole-step kernel (one launch for embedding + all dense layers of a one-request step of up to 8 rows)
+        self.use_mega = os.environ.get("B2_NO_MEGA", "0") != "1"
+        self.mega_cooperative = os.environ.get("B2_MEGA_COOP", "1") != "0"
+        self._mega_bufs = {}
+        self._mega_tables = {}
+        self._mega_shared = None
         if self.nccl is not None:
             self._red = torch.zeros(max_rows * cfg.hidden, dtype=torch.float32, device=self.device)
             self._gather = torch.zeros(self.nccl[1], max_rows, 2, dtype=torch.float32, device=self.device)
@@ -272,8 +278,75 @@ class DecoderModel:
         gu, s_gu = self._gemv_fused("gate_up", lw.gate_up, b.resid, m, norm_w=lw.post_norm, x_mode=2)
         self._gemv_fused("down", lw.down, gu, m, fold=True, x_mode=1, s_in=s_gu, x_slice=m * 2 * cfg.ffn)
 
+    # ------------------------------------------------------------------ whole-step kernel
+    def mega_plan(self, layers: List[LayerWeights], m: int, kv: KVCache):
+        """The schedule of the whole-step kernel for ``m`` rows, or None when this step is outside what it covers:
+        dense SwiGLU layers with full softmax attention, head size 128, bf16 KV, one GPU, at most 8 rows."""
+        cfg = self.cfg
+        if not (self.use_mega and self.fused and self.tp is None and self.nccl is None and m <= 8):
+            return None
+        if kv.kv_int8 or cfg.head_dim != 128 or cfg.hidden % 128 or cfg.ffn % 128 or cfg.ffn <= 0:
+            return None
+        if any(lw.gate_up is None or lw.gdn is not None or lw.qkv is None for lw in layers):
+            return None
+        if any(lw.qkv.n != cfg.qkv_dim or lw.gate_up.n != 2 * cfg.ffn for lw in layers):
+            return None
+        if cfg.sliding_window > 0:
+            return None
+        key = (m, cfg.hidden, cfg.n_q_heads, cfg.n_kv_heads, cfg.ffn)
+        if key not in self._mega_bufs:
+            n_cta = K.decode_mega_sms()
+            plan = K.decode_mega_plan(n_cta, m, cfg.hidden, cfg.n_q_heads, cfg.n_kv_heads, cfg.ffn)
+            if plan is not None:
+                plan["n_cta"] = n_cta
+                dev, u8, i32, f32 = self.device, torch.uint8, torch.int32, torch.float32
+                ks = (cfg.hidden // 64, cfg.q_dim // 64, cfg.ffn // 64)     # groups of the three quantised-row buffers
+                plan["xq"] = [torch.zeros(g * plan["rows"] * 144, dtype=u8, device=dev) for g in ks]
+                plan["gs"] = [torch.zeros(g * 8 * 2, dtype=i32, device=dev) for g in ks]
+                plan["part"] = torch.zeros(plan["part_floats"], dtype=f32, device=dev)
+                plan["o_part"] = torch.zeros(m * cfg.n_q_heads * plan["nsplit"] * 128, dtype=f32, device=dev)
+                plan["ml_part"] = torch.zeros(m * cfg.n_q_heads * plan["nsplit"] * 2, dtype=f32, device=dev)
+                if self._mega_shared is None:
+                    self._mega_shared = {"tickets": torch.zeros(max(plan["max_nb"], 8), dtype=i32, device=dev),
+                                         "attn_tickets": torch.zeros(max(cfg.n_kv_heads, 8), dtype=i32, device=dev),
+                                         "bar": torch.zeros(4, dtype=i32, device=dev)}
+            self._mega_bufs[key] = plan
+        return self._mega_bufs[key]
+
+    def mega_reset(self):
+        """Zeroes the kernel's ticket and barrier words (after a bounded wait ran out in the middle of a step)."""
+        if self._mega_shared is not None:
+            for t in self._mega_shared.values():
+                t.zero_()
+
+    def _mega_table(self, layers: List[LayerWeights], kv: KVCache, kv_layer0: int) -> torch.Tensor:
+        key = (tuple(id(lw) for lw in layers), id(kv), kv_layer0)
+        t = self._mega_tables.get(key)
+        if t is None:
+            rows = []
+            for i, lw in enumerate(layers):
+                rows.append([lw.qkv.w4b.data_ptr(), lw.o.w4b.data_ptr(), lw.gate_up.w4b.data_ptr(), lw.down.w4b.data_ptr(),
+                             lw.input_norm.data_ptr(), lw.post_norm.data_ptr(), kv._plane[kv_layer0 + i], 0])
+            t = torch.tensor(rows, dtype=torch.int64).to(self.device)
+            self._mega_tables[key] = t
+        return t
+
+    def mega_layers(self, layers: List[LayerWeights], m: int, ctrl, block_table, max_blocks, kv: KVCache, plan,
+                    kv_layer0: int = 0, n_phases: int = 0):
+        """Embedding + ``layers`` for the step's rows in one launch; leaves the folded residual stream in
+        ``buf.resid`` and its per-block sums of squares in ``buf.ssq``."""
+        cfg, b, sh = self.cfg, self.buf, self._mega_shared
+        span = (max_blocks + plan["nsplit"] - 1) // plan["nsplit"] if self.attn_fixed_spans else 0
+        K.decode_mega(self._mega_table(layers, kv, kv_layer0), len(layers), m, cfg.hidden, cfg.n_q_heads, cfg.n_kv_heads,
+                      cfg.ffn, ctrl, block_table, max_blocks, kv.num_pages, kv.k.shape[0], self.w.embed, cfg.vocab, b.flag,
+                      self.cos_t, self.sin_t, kv.k, kv.v, b.resid, b.ssq, plan["xq"], plan["gs"], plan["part"],
+                      sh["tickets"], b.q, plan["o_part"], plan["ml_part"], sh["attn_tickets"], sh["bar"], cfg.rms_eps,
+                      self.scale, span, plan["n_cta"], n_phases=n_phases, cooperative=self.mega_cooperative,
+                      dbg=getattr(self, "mega_dbg", None))
+
     def layers_walk(self, layers: List[LayerWeights], m: int, ctrl, block_table, max_blocks, kv: KVCache,
-                    first_from_embed: bool = True, kv_layer0: int = 0, resid_ready: bool = False):
+                    first_from_embed: bool = True, kv_layer0: int = 0, resid_ready: bool = False,
+                    one_request: bool = False):
         """Runs ``layers``; returns the (partials, splits) of the last residual branch, not yet folded.
         ``resid_ready``: ``buf.resid`` and ``buf.ssq`` already hold the folded residual rows and their per-block
         sums of squares (a later pipeline stage that received them from the stage before)."""
@@ -284,6 +357,12 @@ class DecoderModel:
             for i, lw in enumerate(layers):
                 self.dense_layer_fused(lw, kv_layer0 + i, m, ctrl, block_table, max_blocks, kv, x_ready=False)
             return None, 0
+        if one_request and first_from_embed:
+            # rows of ONE request at consecutive positions: the whole walk is one persistent kernel
+            plan = self.mega_plan(layers, m, kv)
+            if plan is not None:
+                self.mega_layers(layers, m, ctrl, block_table, max_blocks, kv, plan, kv_layer0)
+                return None, 0
         if self.fused and first_from_embed and all(lw.gate_up is not None and lw.gdn is None for lw in layers) and h % 128 == 0:
             K.resid_norm(0, m, h, layers[0].input_norm, cfg.rms_eps, b.resid, b.x, embed=self.w.embed, ctrl=ctrl,
                          vocab=cfg.vocab, flag=b.flag)
@@ -373,9 +452,10 @@ class DecoderModel:
         return self._gather.view(-1)[: self.nccl[1] * m * 2]
 
     # ------------------------------------------------------------------ whole step
-    def step_rows(self, m: int, ctrl, block_table, max_blocks, kv: KVCache, advance: bool):
+    def step_rows(self, m: int, ctrl, block_table, max_blocks, kv: KVCache, advance: bool, one_request: bool = False):
         """One forward pass for the ``m`` rows described by ``ctrl``; the arg-max of each row lands in
-        ``ctrl[out_token]``; with ``advance`` the rows' tokens and positions move on for the next replay."""
+        ``ctrl[out_token]``; with ``advance`` the rows' tokens and positions move on for the next replay.
+        ``one_request``: the rows are consecutive positions of one request (plain decode, verify rows)."""
         assert 1 <= m <= self.max_rows
-        pend = self.layers_walk(self.w.layers, m, ctrl, block_table, max_blocks, kv)
+        pend = self.layers_walk(self.w.layers, m, ctrl, block_table, max_blocks, kv, one_request=one_request)
         self.head(m, pend, ctrl, advance)

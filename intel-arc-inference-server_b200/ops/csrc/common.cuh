@@ -22,6 +22,9 @@ namespace b2 {
 // One word set per translation unit (no relocatable device code is needed); each
 // .cu file exports its own reader with B2_DEFINE_STATUS and the Python side reads them all.
 static __device__ unsigned int g_status[4] = {0, 0, 0, 0};
+// Optional word in pinned host memory: the first error code also lands there, so the serving loop can look for a
+// failure after every step by reading host memory instead of copying every unit's status words from the device.
+static __device__ unsigned int* g_host_flag = nullptr;
 
 enum : unsigned int {
   ERR_NONE = 0,
@@ -38,7 +41,14 @@ enum : unsigned int {
 };
 
 __device__ __forceinline__ void record_error(unsigned int code, unsigned int detail) {
-  if (atomicCAS(&g_status[0], 0u, code) == 0u) g_status[1] = detail;
+  if (atomicCAS(&g_status[0], 0u, code) == 0u) {
+    g_status[1] = detail;
+    unsigned int* hf = g_host_flag;
+    if (hf != nullptr) {
+      *reinterpret_cast<volatile unsigned int*>(hf) = code;
+      __threadfence_system();
+    }
+  }
   atomicAdd(&g_status[2], 1u);
 }
 
@@ -276,6 +286,9 @@ __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint3
   extern "C" int b2_status_clear_##unit() {                                                 \
     unsigned int z[4] = {0, 0, 0, 0};                                                       \
     return (int)cudaMemcpyToSymbol(b2::g_status, z, sizeof(z));                             \
+  }                                                                                         \
+  extern "C" int b2_status_hostflag_##unit(void* pinned_word) {                             \
+    return (int)cudaMemcpyToSymbol(b2::g_host_flag, &pinned_word, sizeof(pinned_word));     \
   }
 
 template <typename... KArgs, typename... Args>

@@ -111,6 +111,67 @@ __global__ void __launch_bounds__(1024) resid_norm_kernel(const ResidNormParams 
   }
 }
 
+// ------------------------------------------------------------------ draft-head front
+// One CTA per row: xcat[m] = [ RMSNorm(embed[cur_token[m]]) * w_e  |  RMSNorm(hidden[m]) * w_h ]  (bf16, 2 H wide),
+// the input of a draft head's fc projection (the reference's pf_mtp_front: src/kernels/prefill/pf_mtp_front.cl).
+// The token comes from the control block, so a captured draft step chains on the token the step before it left there.
+__global__ void __launch_bounds__(1024) draft_front_kernel(const __nv_bfloat16* embed, const int* ctrl, int vocab,
+                                                           const __nv_bfloat16* hidden, long long hidden_ld,
+                                                           const float* w_e, const float* w_h, float eps, int H,
+                                                           __nv_bfloat16* xcat, int* flag) {
+  extern __shared__ float vals[];   // [2][H]
+  __shared__ float red[2][32];
+  pdl_wait();
+  pdl_launch_dependents();
+  const int m = blockIdx.x, tid = threadIdx.x, nthr = blockDim.x, H8 = H >> 3;
+  int tok = ctrl[CTRL_CUR_TOKEN + m];
+  if (tok < 0 || tok >= vocab) {
+    if (tid == 0 && flag) atomicExch(flag, 0xDEAD0001);
+    tok = 0;
+  }
+  const uint4* src[2] = {reinterpret_cast<const uint4*>(embed + (size_t)tok * H),
+                         reinterpret_cast<const uint4*>(hidden + (size_t)m * hidden_ld)};
+  float ss[2] = {0.f, 0.f};
+  for (int i = tid; i < H8; i += nthr)
+#pragma unroll
+    for (int which = 0; which < 2; ++which) {
+      const uint4 rv = src[which][i];
+      const uint32_t rw[4] = {rv.x, rv.y, rv.z, rv.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float f0 = bf16_lo(rw[j]), f1 = bf16_hi(rw[j]);
+        vals[which * H + 8 * i + 2 * j] = f0;
+        vals[which * H + 8 * i + 2 * j + 1] = f1;
+        ss[which] += f0 * f0 + f1 * f1;
+      }
+    }
+#pragma unroll
+  for (int which = 0; which < 2; ++which) {
+    ss[which] = warp_sum(ss[which]);
+    if ((tid & 31) == 0) red[which][tid >> 5] = ss[which];
+  }
+  __syncthreads();
+  float rinv[2];
+#pragma unroll
+  for (int which = 0; which < 2; ++which) {
+    float tot = 0.f;
+    for (int i = 0; i < (nthr >> 5); ++i) tot += red[which][i];
+    rinv[which] = rsqrtf(tot / (float)H + eps);
+  }
+  for (int i = tid; i < H8; i += nthr)
+#pragma unroll
+    for (int which = 0; which < 2; ++which) {
+      const float* w = (which ? w_h : w_e) + 8 * i;
+      const float* vv = vals + which * H + 8 * i;
+      uint4 o;
+      o.x = pack_bf16(vv[0] * rinv[which] * w[0], vv[1] * rinv[which] * w[1]);
+      o.y = pack_bf16(vv[2] * rinv[which] * w[2], vv[3] * rinv[which] * w[3]);
+      o.z = pack_bf16(vv[4] * rinv[which] * w[4], vv[5] * rinv[which] * w[5]);
+      o.w = pack_bf16(vv[6] * rinv[which] * w[6], vv[7] * rinv[which] * w[7]);
+      reinterpret_cast<uint4*>(xcat + (size_t)m * 2 * H + (size_t)which * H)[i] = o;
+    }
+}
+
 // ------------------------------------------------------------------ rope_append
 // One CTA per row.  Folds the qkv split-K slices, applies rotate-half RoPE to q and k,
 // writes q (bf16 [M][q_dim]) and appends k, v to the paged cache at the row's position.
@@ -688,6 +749,17 @@ extern "C" int b2_resid_norm(const void* embed, const int* ctrl, const void* res
   int threads = ((H / 8 + 31) / 32) * 32;
   if (threads > 1024) threads = 1024;
   return b2_launch(resid_norm_kernel, dim3(M), dim3(threads), (size_t)H * 4, (cudaStream_t)stream, true, p);
+}
+
+extern "C" int b2_draft_front(const void* embed, const int* ctrl, int vocab, const void* hidden, long long hidden_ld,
+                              const float* w_e, const float* w_h, float eps, int M, int H, void* xcat, int* flag,
+                              void* stream) {
+  if (H % 8 || hidden_ld % 8) return -1;
+  int threads = ((H / 8 + 31) / 32) * 32;
+  if (threads > 1024) threads = 1024;
+  return b2_launch(draft_front_kernel, dim3(M), dim3(threads), (size_t)H * 8, (cudaStream_t)stream, true,
+                   (const __nv_bfloat16*)embed, ctrl, vocab, (const __nv_bfloat16*)hidden, hidden_ld, w_e, w_h, eps, H,
+                   (__nv_bfloat16*)xcat, flag);
 }
 
 extern "C" int b2_rope_append(const float* qkv, long long slice, int S, int M, const int* ctrl, const int* block_table,

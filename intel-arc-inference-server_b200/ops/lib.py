@@ -17,7 +17,7 @@ import torch
 from . import build as _build
 
 _lib: Optional[ctypes.CDLL] = None
-_UNITS = ("gemv", "decode", "gemm", "attn", "attnrows", "moe", "comm", "ep", "spec", "sampler", "gdn")
+_UNITS = ("gemv", "decode", "gemm", "attn", "attnrows", "moe", "comm", "ep", "spec", "sampler", "gdn", "mega")
 
 # Control block layout (int32 words) -- mirrors decode_ops.cu
 CTRL_N_ROWS = 0
@@ -93,6 +93,35 @@ def status_clear():
         fn = getattr(L, f"b2_status_clear_{u}", None)
         if fn is not None:
             fn()
+    for t in _fail_words.values():
+        t.zero_()
+
+
+_fail_words: dict = {}      # device index -> pinned host word the kernels' first error code is also written to
+
+
+def arm_failure_word() -> torch.Tensor:
+    """Gives every kernel unit of the current device a word in pinned host memory for its first bounded-wait
+    failure, so that ``failed_fast()`` after a step costs a host read, not a copy per unit.  Idempotent."""
+    dev = torch.cuda.current_device()
+    if dev not in _fail_words:
+        word = torch.zeros(1, dtype=torch.int32).pin_memory()
+        L = lib()
+        for u in _UNITS:
+            fn = getattr(L, f"b2_status_hostflag_{u}", None)
+            if fn is not None:
+                rc = fn(ctypes.c_void_p(word.data_ptr()))
+                if rc != 0:
+                    raise KernelError(f"cannot arm the failure word ({u}): cuda error {rc}")
+        _fail_words[dev] = word
+    return _fail_words[dev]
+
+
+def failed_fast() -> bool:
+    """True when some kernel of the current device has recorded a failure since the last ``status_clear()``
+    (meaningful after a synchronize; needs ``arm_failure_word()`` once per device)."""
+    w = _fail_words.get(torch.cuda.current_device()) if torch.cuda.is_available() else None
+    return w is not None and int(w[0]) != 0
 
 
 def check_status():
@@ -156,12 +185,58 @@ def quant_x(x, m, k, xq, xq_gs, *, x_mode=0, s_in=1, x_slice=0, ldx=None, norm_w
     _check(rc, "quant_x")
 
 
+def decode_mega_sms() -> int:
+    """CTAs of the whole-step decode kernel: one per SM of the current device."""
+    n = lib().b2_decode_mega_sms()
+    if n <= 0:
+        raise KernelError("decode_mega: cannot read the SM count of the current device")
+    return n
+
+
+def decode_mega_plan(n_cta: int, m: int, h: int, n_q: int, n_kv: int, ffn: int) -> Optional[dict]:
+    """Schedule constants of the whole-step decode kernel for ``m`` rows of this shape (pure host arithmetic; also
+    checks that the CTAs' runs cover every ring stage of every linear exactly once).  None: the kernel does not
+    cover the shape."""
+    out = (ctypes.c_int * 5)()
+    pf = ctypes.c_longlong(0)
+    rc = lib().b2_decode_mega_plan(n_cta, m, h, n_q, n_kv, ffn, out, ctypes.byref(pf))
+    if rc in (-1, -2, -3):
+        return None
+    if rc != 0:
+        raise KernelError(f"decode_mega_plan: schedule self-check failed with code {rc}")
+    return {"rows": out[0], "nsplit": out[1], "max_nb": out[2], "stages": out[3], "smem": out[4], "part_floats": pf.value}
+
+
+def decode_mega(layers_table, n_layers, m, h, n_q, n_kv, ffn, ctrl, block_table, max_blocks, num_pages, planes, embed,
+                vocab, flag, cos_t, sin_t, k_cache, v_cache, resid, ssq, xq, gs, part, tickets, q, o_part, ml_part,
+                attn_tickets, bar, eps, scale, span_pages, n_cta, n_phases: int = 0, cooperative: bool = True, dbg=None):
+    """Embedding + ``n_layers`` dense layers of one decode / verify step (``m`` <= 8 consecutive rows of one request)
+    in one launch.  ``xq`` / ``gs``: three quantised-row buffers and their group scales (hidden-wide, o-proj input,
+    down-proj input); ``bar``: three zeroed uint32 words.  ``n_phases`` > 0 stops after that many phases (1 embed +
+    5 per layer: qkv, attention, o, gate||up, down) -- a debugging cut."""
+    rc = lib().b2_decode_mega(_p(layers_table), n_layers, m, h, n_q, n_kv, ffn, _p(ctrl), _p(block_table), max_blocks,
+                              num_pages, planes, _p(embed), vocab, _p(flag), _p(cos_t), _p(sin_t), _p(k_cache), _p(v_cache),
+                              _p(resid), _p(ssq), _p(xq[0]), _p(xq[1]), _p(xq[2]), _p(gs[0]), _p(gs[1]), _p(gs[2]),
+                              _p(part), _p(tickets), _p(q), _p(o_part), _p(ml_part), _p(attn_tickets), _p(bar),
+                              ctypes.c_float(eps), ctypes.c_float(scale), span_pages, n_phases, n_cta,
+                              1 if cooperative else 0, _p(dbg), _stream())
+    _check(rc, "decode_mega")
+
+
 def resid_norm(mode: int, m: int, h: int, w: torch.Tensor, eps: float, resid_out: torch.Tensor,
                x_out: Optional[torch.Tensor], *, embed=None, ctrl=None, vocab=0, resid_in=None, part=None,
                part_slice=0, splits=0, flag=None):
     rc = lib().b2_resid_norm(_p(embed), _p(ctrl), _p(resid_in), _p(part), ctypes.c_longlong(part_slice), splits, m, h,
                              mode, vocab, _p(w), ctypes.c_float(eps), _p(resid_out), _p(x_out), _p(flag), _stream())
     _check(rc, "resid_norm")
+
+
+def draft_front(embed, ctrl, vocab, hidden, w_e, w_h, eps, m, h, xcat, flag=None):
+    """Input of a draft head's fc projection for ``m`` rows: ``xcat[i] = [norm(embed[cur_token[i]]) | norm(hidden[i])]``
+    (bf16 ``[m][2h]``); the tokens are read from the control block."""
+    rc = lib().b2_draft_front(_p(embed), _p(ctrl), vocab, _p(hidden), ctypes.c_longlong(hidden.stride(0)), _p(w_e),
+                              _p(w_h), ctypes.c_float(eps), m, h, _p(xcat), _p(flag), _stream())
+    _check(rc, "draft_front")
 
 
 def rope_append(qkv_part, slice_elems, splits, m, ctrl, block_table, max_blocks, cos_t, sin_t, n_q, n_kv, d, q_out,

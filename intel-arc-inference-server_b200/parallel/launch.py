@@ -79,6 +79,10 @@ class LockstepLeader(EngineIface):
     def prefill(self, slot, ids): return self._all("prefill", slot, list(ids))
     def step(self, rows): return self._all("step", {int(k): list(v) for k, v in rows.items()})
     def length(self, slot): return self.e.length(slot)
+
+    def reset_failure(self):
+        if hasattr(self.e, "reset_failure"):
+            self._all("reset_failure")
     def kv_form(self): return self.e.kv_form()
 
     def logits(self, slot, row=0):
@@ -107,9 +111,13 @@ def follow_lockstep(engine: EngineIface, plane: ControlPlane) -> int:
         msg = plane.next_broadcast()
         if msg[0] == SHUTDOWN:
             return n
-        res = _apply(engine, msg)
+        try:
+            res = _apply(engine, msg)
+        except Exception as e:  # noqa: BLE001   a failed step latches this rank's engine; the leader's own copy of
+            res = e             # the step fails too (the ranks meet inside it) and sends reset_failure next
+            sys.stderr.write(f"[rank {plane.rank}] {msg[0]} failed: {e}\n")
         if msg[0] == "logits_shard":     # the one call whose result the leader needs from every rank
-            plane.send(0, res)
+            plane.send(0, res if not isinstance(res, Exception) else (0, np.zeros(0, dtype=np.float32)))
         n += 1
 
 

@@ -118,6 +118,12 @@ class TpWires:
         nblk = (hidden + 1023) // 1024
         self.sum = Wire(2 * w * mcap * hidden * 4, 2 * w * mcap * nblk, mcap * nblk, group, device)
 
+    def reset(self):
+        """Flags and call counters back to zero (after a failure; every rank must do it before the next step)."""
+        for x in (self.fold, self.head, self.sum):
+            x.flags.zero_()
+            x.epoch.zero_()
+
     def close(self):
         for x in (self.fold, self.head, self.sum):
             x.close()

@@ -133,41 +133,73 @@ def _sync_all():
     torch.cuda.synchronize()
 
 
-def bench_decode(cfg: ModelConfig, mode: str, depth: int, steps: int, warmup: int, rows: int = 1) -> dict:
-    """Graph-replayed decode steps of ``rows`` requests at context ``depth``; ms per step is the max over ranks."""
+def bench_decode(cfg: ModelConfig, mode: str, depth: int, steps: int, warmup: int, rows: int = 1, windows: int = 1,
+                 e2e: bool = False, kv_dtype: str = "bf16") -> dict:
+    """Graph-replayed decode steps of ``rows`` requests at context ``depth``; ms per step is the max over ranks of
+    the median of ``windows`` timed windows of ``steps`` steps.  ``e2e``: also time steps driven from the host through
+    ``Engine.forward_rows`` -- every step copies the rows' control words from pinned host memory and reads the
+    tokens back."""
     import torch.distributed as dist
     from ..ops import lib as K
+    from ..runtime.engine import Row
     world = dist.get_world_size() if dist.is_initialized() else 1
     rank = dist.get_rank() if dist.is_initialized() else 0
     dev = torch.device("cuda", torch.cuda.current_device())
     w = random_weights(cfg, device=dev, seed=0, exact=False) if world == 1 else random_shard(cfg, rank, world, dev)
-    total = depth + 2 * (steps + warmup) + 64
-    eng = make_engine(w, mode=mode, max_seqs=rows, max_len=total)
+    total = depth + (windows + (3 if e2e else 0) + 2) * (steps + warmup) + 64
+    eng = make_engine(w, mode=mode, max_seqs=rows, max_len=total, kv_dtype=kv_dtype)
     local = eng.cfg
     for layer in range(local.n_layers):   # context at depth: random KV pages (the timing needs the reads only)
-        kc, vc, _, _ = eng.kv.layer(layer)
-        kc.normal_(0, 0.5)
-        vc.normal_(0, 0.5)
+        kc, vc, ks, vs = eng.kv.layer(layer)
+        if eng.kv.kv_int8:
+            kc.copy_(torch.randint(-127, 128, kc.shape, device=dev, dtype=torch.int8))
+            vc.copy_(torch.randint(-127, 128, vc.shape, device=dev, dtype=torch.int8))
+            ks.fill_(0.5 / 127)
+            vs.fill_(0.5 / 127)
+        else:
+            kc.normal_(0, 0.5)
+            vc.normal_(0, 0.5)
     for s in range(rows):
         eng._ensure_pages(s, depth)
         eng.seq_len[s] = depth
     eng.decode_begin(list(range(rows)), [1 + s for s in range(rows)])
     for _ in range(warmup):
         eng.decode_step(read=False)
-    _sync_all()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(steps):
-        eng.decode_step(read=False)
-    e1.record()
-    _sync_all()
-    ms = _max_over_ranks(e0.elapsed_time(e1) / steps, dev)
+    win = []
+    for _ in range(max(1, windows)):
+        _sync_all()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            eng.decode_step(read=False)
+        e1.record()
+        _sync_all()
+        win.append(e0.elapsed_time(e1) / steps)
+    ms = _max_over_ranks(sorted(win)[len(win) // 2], dev)
+    out = {"ms_per_step": ms, "tokens_per_s": rows / (ms / 1e3), "rows": rows, "depth": depth,
+           "launches_per_step": eng.launches(rows, True), "kv_cache": kv_dtype, "windows_ms_per_step": [round(x, 4) for x in win]}
+    if e2e:
+        toks = eng._read_out(rows)
+        for _ in range(warmup):
+            toks = eng.forward_rows([Row(s, eng.seq_len[s], toks[s]) for s in range(rows)], advance=False, read=True)
+        win = []
+        for _ in range(min(3, max(1, windows))):
+            _sync_all()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(steps):
+                toks = eng.forward_rows([Row(s, eng.seq_len[s], toks[s]) for s in range(rows)], advance=False, read=True)
+            e1.record()
+            _sync_all()
+            win.append(e0.elapsed_time(e1) / steps)
+        out["e2e_ms_per_step"] = _max_over_ranks(sorted(win)[len(win) // 2], dev)
+        out["h2d_bytes_per_step"] = K.CTRL_WORDS * 4
+        out["d2h_bytes_per_step"] = K.CTRL_WORDS * 4
     K.check_status()
-    launches = eng.launches(rows, True)
     eng.close()
     del eng, w
     torch.cuda.empty_cache()
-    return {"ms_per_step": ms, "tokens_per_s": rows / (ms / 1e3), "rows": rows, "depth": depth, "launches_per_step": launches}
+    return out
 
 
 def bench_prefill(cfg: ModelConfig, mode: str, n: int, reps: int = 4) -> dict:

@@ -71,6 +71,14 @@ class Engine:
         self._prefill = None
         self.steps_replayed = 0
         self.last_prefill_row = 0
+        # failure latch (the reference's TpEngine keeps `broken_` until reset(): src/runtime/tp_engine.cc:203-256,418-424)
+        self.broken: Optional[str] = None
+        if self.device.type == "cuda":
+            K.arm_failure_word()
+        import os
+        if os.environ.get("B200SERVE_AUDIT", "0") == "1":     # every buffer has a planner entry (see buffer_registry.py)
+            from .buffer_registry import audit
+            audit(self.model.buf, self.kv, cfg, kv_dtype, max_seqs)
         self.launches_per_step: Dict[Tuple[int, bool, bool], int] = {}
 
     def close(self):
@@ -225,14 +233,43 @@ class Engine:
         """Kernel launches of one captured step of ``m`` rows (0 before the first such step)."""
         return max((v for (mm, adv, _), v in self.launches_per_step.items() if mm == m and adv == advance), default=0)
 
+    # ------------------------------------------------------------------ failure latch
+    def require_ok(self):
+        if self.broken is not None:
+            raise K.KernelError(f"engine is latched after a failed step ({self.broken}); call reset_failure()")
+
+    def check_failed(self, what: str = "step"):
+        """After a synchronize: if any kernel's bounded wait ran out during the work just finished, latch the engine and
+        raise an error that names the unit, the code and where it gave up (rank, tile).  The step's outputs are garbage."""
+        if not K.failed_fast():
+            return
+        st = K.status()
+        rank = self.tp.rank if self.tp is not None else (self.model.nccl[0] if self.model.nccl is not None else 0)
+        self.broken = f"{what} on rank {rank}: " + ", ".join(
+            f"{u}: code {v['code']} detail {v['detail']:#x} ({v['count']} waits)" for u, v in st.items())
+        raise K.KernelError(f"device kernels gave up on a bounded wait during {self.broken}")
+
+    def reset_failure(self):
+        """Clears the status words, the whole-step kernel's barrier words and the wires' flags and call counters, and
+        releases the latch.  Under tensor parallelism every rank must call it before the next step."""
+        torch.cuda.synchronize(self.device)
+        K.status_clear()
+        self.model.mega_reset()
+        if self.tp is not None:
+            self.tp.reset()
+        torch.cuda.synchronize(self.device)
+        self.broken = None
+
     def _read_out(self, m: int) -> List[int]:
         self.out_host.copy_(self.ctrl, non_blocking=True)
         torch.cuda.current_stream().synchronize()
+        self.check_failed()
         return self.out_host[K.CTRL_OUT_TOKEN: K.CTRL_OUT_TOKEN + m].tolist()
 
     # ------------------------------------------------------------------ public API
     def forward_rows(self, rows: Sequence[Row], advance: bool = False, read: bool = True):
         """Run arbitrary rows (verify, batched decode, chunked ingest). KV of each row is appended."""
+        self.require_ok()
         for r in rows:
             self._ensure_pages(r.slot, r.pos + 1)
         self._gdn_snap = None
@@ -252,6 +289,7 @@ class Engine:
 
     def prefill(self, slot: int, ids: Sequence[int], chunk: Optional[int] = None) -> int:
         """Ingest ``ids`` after the slot's current length; returns the greedy next token."""
+        self.require_ok()
         ids = list(ids)
         if self._use_tc_prefill(len(ids)):
             if self._prefill is None:
@@ -265,7 +303,9 @@ class Engine:
                     from .prefill import PrefillRunner
                     self._prefill = PrefillRunner(self)
             self.last_prefill_row = 0      # row of model.buf.logits that holds the prompt's last position
-            return self._prefill.run(slot, ids, chunk)
+            tok = self._prefill.run(slot, ids, chunk)
+            self.check_failed("prompt pass")
+            return tok
         start = self.seq_len[slot]
         out = None
         for c0 in range(0, len(ids), self.max_rows):
@@ -300,6 +340,7 @@ class Engine:
 
     def decode_step(self, read: bool = True):
         """One replay of the armed decode rows; the device advances tokens and positions itself."""
+        self.require_ok()
         slots = self._decode_slots
         for s in slots:
             self._ensure_pages(s, self.seq_len[s] + 1)

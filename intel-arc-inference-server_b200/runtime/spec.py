@@ -64,39 +64,98 @@ class DraftHead:
         dev = engine.device
         self.xcat = torch.zeros(engine.max_rows, 2 * cfg.hidden, dtype=torch.bfloat16, device=dev)
         self.hid_in = torch.zeros(engine.max_rows, cfg.hidden, dtype=torch.bfloat16, device=dev)
+        self.zero_rows = torch.zeros(engine.max_rows, cfg.hidden, dtype=torch.bfloat16, device=dev)
+        self.draft_list = torch.zeros(64, dtype=torch.int32, device=dev)     # arg-maxes of chained rows, in order
+        self.draft_n = torch.zeros(1, dtype=torch.int64, device=dev)
+        self.graphs = {}
         self.prev_last: Dict[int, torch.Tensor] = {}    # last hidden of the previous prompt chunk, per slot
         engine.on_chunk_hidden = self._ingest_chunk
         self.rows_run = 0
 
     # ------------------------------------------------------------------ decode-time rows (M <= max_rows)
-    def rows(self, rows: Sequence[Row], hidden: torch.Tensor) -> List[int]:
-        """Runs head rows (token, position) with ``hidden[i]`` = hidden state of the position before row i.
-        Returns each row's arg-max; the head's own hidden states stay in ``engine.model.buf.resid``."""
+    def _enqueue(self, n: int, chain: bool):
+        """The head's forward pass for ``n`` rows as device work only (no host read, so it can be captured): tokens
+        and positions come from the control block, hidden inputs from ``hid_in``.  ``chain``: leave the control block
+        and ``hid_in`` ready for ONE more row that follows the last one -- its token is this pass's arg-max, its
+        hidden input this pass's own hidden state -- and append the arg-max to the device-side draft list."""
         eng, m, head = self.eng, self.eng.model, self.head
         cfg, b = eng.cfg, m.buf
-        n, h = len(rows), cfg.hidden
-        for r in rows:
-            eng._ensure_pages(r.slot, r.pos + 1)
-        eng._write_rows(rows)
-        K.resid_norm(0, n, h, head.pre_norm_embed, cfg.rms_eps, b.resid, b.x, embed=m.w.embed, ctrl=eng.ctrl,
-                     vocab=cfg.vocab, flag=b.flag)
-        self.xcat[:n, :h] = b.x[:n]
-        self.xcat[:n, h:] = _rmsnorm(hidden[:n], head.pre_norm_hidden, cfg.rms_eps).to(torch.bfloat16)
+        h = cfg.hidden
+        K.draft_front(m.w.embed, eng.ctrl, cfg.vocab, self.hid_in, head.pre_norm_embed, head.pre_norm_hidden,
+                      cfg.rms_eps, n, h, self.xcat, b.flag)
         part, s = m._gemv("head_fc", head.fc, self.xcat, n)
-        b.resid[:n] = part[: s * n * h].view(s, n, h).sum(dim=0).to(torch.bfloat16)
+        # residual stream of the head = the fc output (the split-K slices folded onto zero rows)
+        K.resid_norm(1, n, h, head.norm, cfg.rms_eps, b.resid, None, resid_in=self.zero_rows, part=part,
+                     part_slice=n * h, splits=s)
         pend = m.layers_walk(head.layers, n, eng.ctrl, eng.block_table, eng.max_blocks, eng.kv,
                              first_from_embed=False, kv_layer0=self.kv0)
-        self.rows_run += n
         if self.dv is None:
             m.head(n, pend, eng.ctrl, False, final_norm=head.norm)
+        else:
+            # reduced draft vocabulary: fold + norm as the head does, then only V' rows of the lm_head; the arg-max
+            # is a position in V', mapped to a token id through the id table (on the device)
+            K.resid_norm(1, n, h, head.norm, cfg.rms_eps, b.resid, b.x, resid_in=b.resid, part=pend[0],
+                         part_slice=n * h, splits=pend[1])
+            K.head_gemv(self.dv.head, b.x, self.dv_logits, n, self.dv.size, h, self.dv_cand_val, self.dv_cand_idx)
+            K.argmax_finish(self.dv_cand_val, self.dv_cand_idx, self.dv_ncand, n, eng.ctrl, False)
+            out = eng.ctrl[K.CTRL_OUT_TOKEN: K.CTRL_OUT_TOKEN + n]
+            out.copy_(torch.index_select(self.dv.ids32, 0, out.to(torch.int64)))
+        if chain:
+            c = eng.ctrl
+            last = n - 1
+            c[K.CTRL_CUR_TOKEN: K.CTRL_CUR_TOKEN + 1] = c[K.CTRL_OUT_TOKEN + last: K.CTRL_OUT_TOKEN + last + 1]
+            c[K.CTRL_ROW_POS: K.CTRL_ROW_POS + 1] = c[K.CTRL_ROW_POS + last: K.CTRL_ROW_POS + last + 1] + 1
+            c[K.CTRL_ROW_REQ: K.CTRL_ROW_REQ + 1] = c[K.CTRL_ROW_REQ + last: K.CTRL_ROW_REQ + last + 1]
+            self.hid_in[0:1].copy_(b.resid[last: last + 1])
+            self.draft_list.index_copy_(0, self.draft_n, c[K.CTRL_OUT_TOKEN + last: K.CTRL_OUT_TOKEN + last + 1])
+            self.draft_n += 1
+
+    def _run(self, n: int, chain: bool):
+        """Replays (capturing it first) the head's pass for ``n`` rows; eager when the engine runs without graphs."""
+        eng = self.eng
+        if not eng.use_graphs:
+            return self._enqueue(n, chain)
+        key = (n, chain)
+        g = self.graphs.get(key)
+        if g is None:
+            saved = (eng.ctrl.clone(), self.hid_in.clone(), self.draft_n.clone(), self.draft_list.clone())
+            self._enqueue(n, chain)          # warm-up outside capture: function attributes, scratch allocation
+            torch.cuda.current_stream().synchronize()
+            for dst, src in zip((eng.ctrl, self.hid_in, self.draft_n, self.draft_list), saved):
+                dst.copy_(src)
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                self._enqueue(n, chain)
+            for dst, src in zip((eng.ctrl, self.hid_in, self.draft_n, self.draft_list), saved):
+                dst.copy_(src)               # KV rows written by the warm-up and the capture are rewritten by the replay
+            self.graphs[key] = g
+        g.replay()
+
+    def rows(self, rows: Sequence[Row], hidden: torch.Tensor, chain: int = -1) -> List[int]:
+        """Runs head rows (token, position) with ``hidden[i]`` = hidden state of the position before row i; the head's
+        own hidden states stay in ``engine.model.buf.resid``.  ``chain`` < 0: returns each row's arg-max.  ``chain``
+        >= 0: the last row's arg-max is the first draft and ``chain`` more single rows follow ON THE DEVICE, each taking
+        the arg-max and the hidden state of the row before it (the MTP chain); returns the ``chain + 1`` drafts.
+        Either way the host reads the device once."""
+        eng = self.eng
+        n = len(rows)
+        upto = max(r.pos for r in rows) + 1 + max(chain, 0)
+        for r in rows:
+            eng._ensure_pages(r.slot, min(upto, eng.max_len))
+        eng._write_rows(rows)
+        self.hid_in[:n].copy_(hidden[:n])
+        if chain < 0:
+            self._run(n, False)
+            self.rows_run += n
             return eng._read_out(n)
-        # reduced draft vocabulary: fold + norm as the head does, then only V' rows of the lm_head; the arg-max
-        # is a position in V', mapped back to a token id on the host
-        K.resid_norm(1, n, h, head.norm, cfg.rms_eps, b.resid, b.x, resid_in=b.resid, part=pend[0], part_slice=n * h,
-                     splits=pend[1])
-        K.head_gemv(self.dv.head, b.x, self.dv_logits, n, self.dv.size, h, self.dv_cand_val, self.dv_cand_idx)
-        K.argmax_finish(self.dv_cand_val, self.dv_cand_idx, self.dv_ncand, n, eng.ctrl, False)
-        return [self.dv.to_token(p) for p in eng._read_out(n)]
+        self.draft_n.zero_()
+        self._run(n, True)
+        for _ in range(chain):
+            self._run(1, True)
+        self.rows_run += n + chain
+        drafts = self.draft_list[: chain + 1].tolist()      # the one read: it also orders the host after the passes
+        eng.check_failed("draft")
+        return [int(t) for t in drafts]
 
     # ------------------------------------------------------------------ prompt ingestion
     def _ingest_chunk(self, runner, slot: int, ids: Sequence[int], pos0: int, resid: torch.Tensor):
@@ -223,15 +282,8 @@ class SpecAdapter:
             out = self.head.rows(rows, hidden)
             drafts = [int(t) for t in out[r - 1:]]
         else:
-            out = self.head.rows(rows, hidden)
-            drafts = [int(out[-1])]
-            pos = length + 1
-            while len(drafts) < k:
-                h_own = self.e.model.buf.resid[len(rows) - 1: len(rows)].clone()
-                rows = [Row(slot, pos, drafts[-1])]
-                out = self.head.rows(rows, h_own)
-                drafts.append(int(out[0]))
-                pos += 1
+            # MTP: the catch-up rows, then k - 1 rows chained on the device (token and hidden state of the row before)
+            drafts = self.head.rows(rows, hidden, chain=k - 1)
         self.e.seq_len[slot] = saved_len        # the head's rows are not part of the sequence
         self.stats["drafted"] += len(drafts)
         self.stats["iterations"] += 1

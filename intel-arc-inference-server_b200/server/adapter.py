@@ -40,6 +40,10 @@ class EngineAdapter(EngineIface):
     def kv_form(self):
         return self.e.kv_dtype
 
+    def reset_failure(self):
+        """After a step failed on a bounded wait: clear the device status and release the engine's latch."""
+        self.e.reset_failure()
+
     def prefill(self, slot, ids):
         tok = self.e.prefill(slot, list(ids))
         r = self.e.last_prefill_row

@@ -211,7 +211,8 @@ class Server:
         try:
             tok = self.engine.prefill(s.slot, s.prompt_ids[a["begin"]: a["end"]])
         except Exception as e:  # noqa: BLE001
-            return self._fail(s, e)
+            self._fail(s, e)
+            return self._recover_engine()
         self.sched.prefill_done(s.slot, a["end"])
         if a["last"]:
             if self.prefix:
@@ -256,6 +257,7 @@ class Server:
         except Exception as e:  # noqa: BLE001   (a failing step fails its rows, not the server)
             for slot in rows:
                 self._fail(self.by_slot[slot], e)
+            self._recover_engine()
             return
         for slot, toks in rows.items():
             s = self.by_slot[slot]
@@ -317,6 +319,16 @@ class Server:
             s.lookup = H.PromptLookup()
             s.lookup.extend(s.prompt_ids + s.out_ids)
         return s.lookup
+
+    def _recover_engine(self):
+        """A step that gave up on a bounded wait latches the engine (its rows were failed above); clearing the latch
+        lets the other requests and later ones run."""
+        fn = getattr(self.engine, "reset_failure", None)
+        if fn is not None:
+            try:
+                fn()
+            except Exception as e:  # noqa: BLE001
+                sys.stderr.write(f"engine recovery failed: {e}\n")
 
     def _draft(self, s: Session, k: int) -> List[int]:
         if k <= 0:

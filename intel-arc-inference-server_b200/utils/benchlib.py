@@ -22,41 +22,48 @@ def run_decode_bench(args, barrier) -> dict:
     cfg = preset(args.model)
     dev = torch.device("cuda", torch.cuda.current_device())
     weights = random_weights(cfg, device=dev, seed=0, exact=False)
-    total = args.depth + 2 * (args.steps + args.warmup) + 64
+    total = args.depth + (max(1, getattr(args, "windows", 5)) + 4) * (args.steps + args.warmup) + 64
     eng = Engine(weights, max_seqs=1, max_len=total, kv_dtype=args.kv_cache, int8_head=args.int8_head,
                  prefill_backend=args.prefill_backend)
     g = torch.Generator().manual_seed(0)
     ids = torch.randint(0, cfg.vocab, (args.depth,), generator=g).tolist()
     first = eng.prefill(0, ids)
-    # ---- device-timed: graph replays, tokens and positions advance on the device
+    # ---- device-timed: graph replays, tokens and positions advance on the device.  ``windows`` timed regions of
+    # ``steps`` steps each; the reported time per step is the median window (one hiccup cannot move it)
+    windows = max(1, getattr(args, "windows", 5))
     eng.decode_begin([0], [first])
     for _ in range(args.warmup):
         eng.decode_step(read=False)
-    barrier()
-    e0, e1 = _events()
-    n0 = K.launch_count
-    e0.record()
-    for _ in range(args.steps):
-        eng.decode_step(read=False)
-    e1.record()
-    barrier()
-    ms = e0.elapsed_time(e1) / args.steps
-    launches = eng.launches_per_step.get((1, True), 0) * args.steps
+    win_ms = []
+    for _ in range(windows):
+        barrier()
+        e0, e1 = _events()
+        e0.record()
+        for _ in range(args.steps):
+            eng.decode_step(read=False)
+        e1.record()
+        barrier()
+        win_ms.append(e0.elapsed_time(e1) / args.steps)
+    ms = sorted(win_ms)[len(win_ms) // 2]
+    launches = eng.launches(1, True) * args.steps
     # ---- end to end: every step the host sends the row (pinned H2D) and reads the token back (D2H)
     tok = eng._read_out(1)[0]
     pos = eng.seq_len[0]
     for _ in range(args.warmup):
         tok = eng.forward_rows([Row(0, pos, tok)], advance=False, read=True)[0]
         pos += 1
-    barrier()
-    e0, e1 = _events()
-    e0.record()
-    for _ in range(args.steps):
-        tok = eng.forward_rows([Row(0, pos, tok)], advance=False, read=True)[0]
-        pos += 1
-    e1.record()
-    barrier()
-    e2e_ms = e0.elapsed_time(e1) / args.steps
+    e2e_win = []
+    for _ in range(min(3, windows)):
+        barrier()
+        e0, e1 = _events()
+        e0.record()
+        for _ in range(args.steps):
+            tok = eng.forward_rows([Row(0, pos, tok)], advance=False, read=True)[0]
+            pos += 1
+        e1.record()
+        barrier()
+        e2e_win.append(e0.elapsed_time(e1) / args.steps)
+    e2e_ms = sorted(e2e_win)[len(e2e_win) // 2]
     w_bytes = cfg.weight_bytes_per_token(1.0 if args.int8_head else 2.0)
     kv_bytes = cfg.kv_bytes_per_token(args.kv_cache) * args.depth
     return {
@@ -66,22 +73,23 @@ def run_decode_bench(args, barrier) -> dict:
         "config": {"model": cfg.name, "global_batch": 1, "seq_len": args.depth, "parallelism": "replica",
                    "kv_cache": args.kv_cache, "lm_head": "int8" if args.int8_head else "bf16",
                    "weights": "W4A16 int4 g64, random init", "l2": "inputs larger than L2 (12.7 GB of weights per step)",
-                   "bytes_per_step": w_bytes + kv_bytes,
+                   "bytes_per_step": w_bytes + kv_bytes, "windows_ms_per_step": [round(x, 4) for x in win_ms],
+                   "launches_per_step": eng.launches(1, True),
                    "achieved_GBps": (w_bytes + kv_bytes) / (ms / 1e3) / 1e9},
     }
 
 
-def run_prefill_bench(args, barrier, model: str, backend: str) -> dict:
+def run_prefill_bench(args, barrier, model: str, backend: str, n: int = 0, warm: int = 3, reps: int = 0) -> dict:
     cfg = preset(model)
     dev = torch.device("cuda", torch.cuda.current_device())
     weights = random_weights(cfg, device=dev, seed=0, exact=False)
-    n = args.prefill_len
+    n = n or args.prefill_len
     eng = Engine(weights, max_seqs=1, max_len=n + 64, kv_dtype="bf16", prefill_backend=backend, use_graphs=False)
     g = torch.Generator().manual_seed(1)
     ids_t = torch.randint(0, cfg.vocab, (n,), generator=g, dtype=torch.int32).pin_memory()
     ids = ids_t.tolist()
-    reps = max(3, min(args.steps, 8))
-    for _ in range(3):
+    reps = reps or max(3, min(args.steps, 8))
+    for _ in range(warm):
         eng.reset(0)
         eng.prefill(0, ids)
     barrier()

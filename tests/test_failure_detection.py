@@ -111,3 +111,36 @@ def test_expert_parallel_plan_is_consistent_across_ranks(world):
             assert (taken[row0 + rows: row0 + 128] == 0).all()      # padding rows belong to nobody
             covered[row0: row0 + rows] = True
         assert (covered == (taken == 1)).all()         # the blocks cover exactly the rows that arrive
+
+
+@pytest.mark.gpu
+def test_engine_latches_on_a_wait_that_ran_out_and_recovers_bitwise():
+    """The serving path reads the failure word after every step: a bounded wait that ran out while a step was in
+    flight (here: a stream-ordered wait on a counter nothing increments) raises an error that names the unit and the
+    code, the engine refuses further steps until reset_failure(), and after it the same step gives the same bits."""
+    import torch
+    from b200serve.models.config import small_dense
+    from b200serve.models.weights import random_weights
+    from b200serve.ops import lib as K
+    from b200serve.runtime.engine import Engine, Row
+    K.status_clear()
+    cfg = small_dense()
+    eng = Engine(random_weights(cfg, device="cuda", seed=0), max_seqs=1, max_len=256, use_graphs=False)
+    g = torch.Generator().manual_seed(0)
+    prompt = torch.randint(0, cfg.vocab, (40,), generator=g).tolist()
+    first = eng.prefill(0, prompt)
+    want = eng.forward_rows([Row(0, 40, first)])
+    want_logits = eng.logits(1).clone()
+    eng.truncate(0, 40)
+    cnt = torch.zeros(4, dtype=torch.int32, device="cuda")
+    K.wire_wait(cnt, 1)                       # gives up after its bound and records 0x501 in the comm unit
+    with pytest.raises(K.KernelError, match="comm: code 0x501"):
+        eng.forward_rows([Row(0, 40, first)])
+    assert eng.broken is not None
+    with pytest.raises(K.KernelError, match="latched"):
+        eng.forward_rows([Row(0, 40, first)])
+    eng.reset_failure()
+    assert eng.broken is None and K.status() == {}
+    eng.truncate(0, 40)
+    got = eng.forward_rows([Row(0, 40, first)])
+    assert got == want and torch.equal(eng.logits(1), want_logits)

@@ -208,3 +208,32 @@ def _wide_ids_and_broken_streamer(srv):
     finally:
         TOK.streamer = real
     assert post(srv.port, "/v1/completions", {"prompt": "wide", "max_tokens": 8})[0] == 200
+
+
+def test_failed_step_fails_its_request_and_the_engine_latch_is_cleared(server):
+    """An engine whose step gives up once (a bounded wait that ran out) stays latched until reset_failure(): the
+    request in flight gets an error, the server clears the latch, and the next request is served."""
+    srv, eng = server()
+    state = {"latched": False, "resets": 0, "fail_next": True}
+    real_step = eng.step
+
+    def step(rows):
+        if state["latched"]:
+            raise RuntimeError("engine is latched after a failed step")
+        if state["fail_next"]:
+            state["fail_next"] = False
+            state["latched"] = True
+            raise RuntimeError("device kernels gave up on a bounded wait during step on rank 0: comm: code 0x501")
+        return real_step(rows)
+
+    def reset_failure():
+        state["latched"] = False
+        state["resets"] += 1
+
+    eng.step = step
+    eng.reset_failure = reset_failure
+    st, body = post(srv.port, "/v1/completions", {"prompt": "abc", "max_tokens": 4})
+    assert st == 500 and body["error"]["type"] == "server_error"
+    assert state["resets"] == 1 and not state["latched"]
+    st, body = post(srv.port, "/v1/completions", {"prompt": "abc", "max_tokens": 4})
+    assert st == 200 and body["usage"]["completion_tokens"] == 4
