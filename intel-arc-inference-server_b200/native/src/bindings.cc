@@ -360,6 +360,8 @@ PYBIND11_MODULE(b200host, m) {
            })
       .def("waiting", &HttpServer::waiting)
       .def("cancelled", &HttpServer::cancelled)
+      .def("close", &HttpServer::close)
+      .def("active", &HttpServer::active)
       .def("respond", &HttpServer::respond, py::call_guard<py::gil_scoped_release>())
       .def("begin_stream", &HttpServer::begin_stream, py::call_guard<py::gil_scoped_release>())
       .def("send_event", &HttpServer::send_event, py::call_guard<py::gil_scoped_release>())

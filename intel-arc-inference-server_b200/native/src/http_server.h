@@ -13,6 +13,7 @@
 #include <netinet/tcp.h>
 #include <poll.h>
 #include <sys/socket.h>
+#include <sys/time.h>
 #include <unistd.h>
 
 #include <atomic>
@@ -83,6 +84,7 @@ class HttpServer {
     queue_.pop_front();
     return r;
   }
+  int active() const { return active_.load(); }   // connection threads alive
   int waiting() {
     std::lock_guard<std::mutex> g(mu_);
     return (int)queue_.size();
@@ -102,6 +104,9 @@ class HttpServer {
     finish(id);
     return ok;
   }
+  // Drops a request that will get no answer (its client went away before a slot was granted): the connection
+  // thread stops watching the socket and closes it.
+  void close(uint64_t id) { finish(id); }
   bool begin_stream(uint64_t id) {
     auto c = conn(id);
     if (!c) return false;
@@ -189,6 +194,10 @@ class HttpServer {
       }
       int one = 1;
       setsockopt(cfd, IPPROTO_TCP, TCP_NODELAY, &one, sizeof one);
+      // a client that stops reading must not hold the serving thread: a send that cannot make progress for this
+      // long fails, and write_all marks the connection gone (its request is then cancelled like a hang-up)
+      timeval snd{kSendTimeoutSec, 0};
+      setsockopt(cfd, SOL_SOCKET, SO_SNDTIMEO, &snd, sizeof snd);
       ++active_;
       std::thread([this, cfd] {
         serve(cfd);
@@ -301,6 +310,7 @@ class HttpServer {
     ::close(cfd);
   }
 
+  static constexpr int kSendTimeoutSec = 5;
   int fd_ = -1, port_ = 0, max_waiting_;
   std::atomic<bool> stopping_{false};
   std::thread acceptor_;

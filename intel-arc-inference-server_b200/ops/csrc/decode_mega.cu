@@ -9,27 +9,32 @@
 //     down; for every linear this CTA's contiguous run of ring stages ("stream-K": the linear's stages, two
 //     4352-byte W4B blocks each, are dealt to the CTAs in equal contiguous runs, so every SM streams the same
 //     number of bytes whatever N and K are) -- and issues one bulk copy per stage as soon as a ring slot is free.
-//     Weights depend on nothing, so the producer runs ahead through phase boundaries: while the CTAs meet at a
-//     grid barrier, or run the attention phase, the ring (about 145 KB per SM) keeps filling from HBM.
-//   * the activations of a stage (the two 64-k groups of every row, already quantised to the two-limb 15-bit form
-//     of gemv_w4.cu by whoever produced them) ride in the same ring slot on a second mbarrier; the producer issues
-//     that copy once the grid barrier before the phase has been passed.  The consumer warps never wait on
-//     anything but their stage's two mbarriers.
+//     Weights depend on nothing, so it never looks at the grid barrier: while the CTAs meet there, or run the
+//     attention phase, the ring (about 145 KB per SM) keeps filling from HBM.
+//   * warp 17 is the activation producer.  The activations of a stage (the two 64-k groups of every row, already
+//     quantised to the two-limb 15-bit form of gemv_w4.cu by whoever produced them) ride in the same ring slot on
+//     a second mbarrier; this warp issues the copy once the grid barrier before the phase has been passed, so it
+//     is the only party that polls the barrier during the linears.
 //   * 16 consumer warps in two groups of 8 take alternate stages (warp w of a group owns rows 16w..16w+15 of the
-//     128-row block, mma.m16n8k32.u8.s8 on raw nibbles exactly as gemv_w4.cu).  At the end of an n-block's run the
-//     partial sums go to a slot of that n-block; the last CTA to finish an n-block ("ticket") sums the slots in
-//     slot order and does the linear's epilogue:
+//     128-row block, mma.m16n8k32.u8.s8 on raw nibbles exactly as gemv_w4.cu).  They wait on nothing but their
+//     stage's two mbarriers.  At the end of an n-block's run the accumulators go to a shared-memory hand-off buffer
+//     and the warps carry on with the next stage at once.
+//   * warp 18 is the epilogue warp.  It takes each hand-off, adds the two groups' sums, stores them in a slot of
+//     that n-block and takes a ticket; the last CTA to finish an n-block sums the slots in slot order and does the
+//     linear's epilogue:
 //        qkv      RoPE, q -> bf16 rows, k / v -> the paged cache at the rows' positions
 //        o, down  residual add -> bf16 stream, per-block sums of squares, next RMSNorm weight, quantised rows
 //        gate||up SiLU(gate) * up -> quantised rows for down
+//     and after the CTA's last run of a phase it makes the CTA's arrival at the grid barrier.  The fences, the
+//     ticket's round trip and the fold (microseconds of latency in all) are off the consumers' path this way.
 //     RMSNorm's 1/rms is a per-row scalar, so it is applied to the partial sums of the NEXT linear when they
 //     are written, not to its input.
 //   * attention is its own phase: CTA (KV head, KV split) serves all rows x GQA heads on mma.m16n8k16 over
 //     pages fetched with tiled TMA copies (128-byte swizzle, two 64-key buffers), the last CTA of a KV head
 //     merges the splits in split order and quantises the o-proj input.
 //
-// Phases are separated by a grid barrier (one arrival per CTA on a monotonic counter; only the producer lane and,
-// for the attention phase, one consumer thread poll it).  Every wait is bounded; a wait that runs out sets the
+// Phases are separated by a grid barrier (one arrival per CTA on a monotonic counter; only the activation producer
+// and, for the attention phase, one consumer thread poll it).  Every wait is bounded; a wait that runs out sets the
 // status word and a CTA-wide flag that makes all later waits fail at once, the CTA still walks to its exit.
 // All sums run in a fixed order (stage order inside a run, slot order across runs, split order in attention):
 // bitwise reproducible, and a row's bits do not depend on M.
@@ -44,9 +49,12 @@ namespace {
 
 constexpr int CTRL_ROW_REQ = 16, CTRL_ROW_POS = 80, CTRL_CUR_TOKEN = 144;
 constexpr int kBlockBytes = 4352;
-constexpr int kWStage = 2 * kBlockBytes;   // weights of one ring stage: two quantisation groups of a 128-row block
+constexpr int kSB = 4;                     // 64-k groups (W4B blocks) of one 128-row block per ring stage; an n-block's last stage may hold 2
+constexpr int kWStage = kSB * kBlockBytes;  // weight bytes of a full stage
 constexpr int kXRow = 144;                 // one (group, row) of activation limbs: 128 bytes + 16 (conflict-free reads)
-constexpr int kConsWarps = 16, kCons = kConsWarps * 32, kThreads = kCons + 32;
+constexpr int kConsWarps = 16, kCons = kConsWarps * 32;
+constexpr int kGroups = 4, kGroupWarps = kConsWarps / kGroups;   // consumer groups take stages round-robin
+constexpr int kThreads = kCons + 96;   // + weight producer, activation producer, epilogue warp
 constexpr int kMaxNS = 18;
 constexpr int kMaxRows = 8;
 constexpr int D = 128;
@@ -72,6 +80,7 @@ struct MegaParams {
   int n_layers, M, rows, nCTA, NS;
   int H, n_q, n_kv, gqa, nbH;
   int nb[4], SG[4], T[4], maxseg[4];     // per linear: n-blocks, stages per n-block, stages, most runs per n-block
+  int KG[4];                             // per linear: 64-k groups per row (K / 64)
   const int* ctrl;
   const int* block_table;
   int max_blocks, num_pages;
@@ -97,11 +106,16 @@ struct MegaParams {
   float eps, scale_log2;
   int nsplit, span_pages;
   int n_phases;               // phases to run (1 + 5 * n_layers for a whole step; fewer: a debugging cut)
-  unsigned long long* dbg;    // optional [nCTA][2][32] timestamps: arrival per phase, first activation copy per phase
+  int variant;                // measurement switches (environment B2_MEGA_VARIANT; results are wrong with any bit set):
+                              // 1 consumers skip the maths, 2 no weight copies, 4 no activation copies, 8 no attention work,
+  unsigned long long* dbg;    // optional [nCTA][8][32] timestamps per phase: arrival, barrier seen by the activation producer,
+                              // consumers done with their last stage, consumers holding their first stage; the epilogue
+                              // warp's last run end: handed over, sums stored, ticket known, folded
 };
 
 struct Smem {   // byte addresses in the shared window
   uint32_t ring, fullW, fullX, empty, kvbar, misc, attn;
+  uint32_t out, outfull, outempty;   // run-end hand-off: [2 buffers][2 groups][M][128] floats and their barriers
   int stageB;
 };
 
@@ -125,6 +139,25 @@ __device__ __forceinline__ uint32_t lds32v(uint32_t a) {
 __device__ __forceinline__ void sts32(uint32_t a, uint32_t v) {
   asm volatile("st.shared.u32 [%0], %1;" ::"r"(a), "r"(v) : "memory");
 }
+__device__ __forceinline__ unsigned ld_acquire_gpu(const unsigned* p) {
+  unsigned v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
+// Ticket / arrival in one operation: the release covers the warp's earlier stores (ordered before it by the warp
+// barrier in front), the acquire the loads that follow.
+__device__ __forceinline__ int atom_add_acq_rel(int* p, int v) {
+  int old;
+  asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], %2;" : "=r"(old) : "l"(p), "r"(v) : "memory");
+  return old;
+}
+__device__ __forceinline__ void red_add_release(unsigned* p, unsigned v) {
+  asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+// Wait on an mbarrier, bounded.  After any wait of this CTA has run out (or the CTA has learnt that the launch is
+// being abandoned) every wait fails: at once if it has not begun, else at its next look at the flag.
 __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
@@ -136,20 +169,42 @@ __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-__device__ __forceinline__ unsigned ld_acquire_gpu(const unsigned* p) {
-  unsigned v;
-  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-__device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
-
-// Wait on an mbarrier; after any wait of this CTA has run out, every later one fails at once.
-__device__ __forceinline__ bool mwait(uint32_t bar, uint32_t parity, uint32_t failed_addr, unsigned code) {
+#ifdef B2_MEGA_PROF
+#define MISS_ARG , long long* miss = nullptr
+#define MISS_COUNT if (miss) ++*miss;
+#else
+#define MISS_ARG
+#define MISS_COUNT
+#endif
+__device__ __forceinline__ bool mwait(uint32_t bar, uint32_t parity, uint32_t failed_addr, unsigned code MISS_ARG) {
+  if (mbar_test(bar, parity)) return true;   // in the steady state the phase is complete already
+  MISS_COUNT
   if (mbar_try(bar, parity)) return true;
-  if (lds32v(failed_addr)) return false;
-  if (mbar_wait(bar, parity, code)) return true;
-  sts32(failed_addr, 1u);
-  return false;
+  const long long t0 = clock64();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 32; ++i)
+      if (mbar_try(bar, parity)) return true;
+    if (lds32v(failed_addr)) return false;
+    if (clock64() - t0 > kWaitCycles) {
+      record_error(code, (blockIdx.x << 8) | (threadIdx.x >> 5));
+      sts32(failed_addr, 1u);
+      return false;
+    }
+  }
+}
+
+// A whole warp waits: one lane polls (every lane's poll of one mbarrier is a shared-memory operation of its own, and
+// they are served one after the other: 32 of them cost some 400 cycles even on a completed phase), the shuffle
+// hands the result to the others and orders their reads after the lane's acquire.
+__device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, uint32_t failed_addr, unsigned code, int lane MISS_ARG) {
+  int r = 1;
+#ifdef B2_MEGA_PROF
+  if (lane == 0) r = mwait(bar, parity, failed_addr, code, miss) ? 1 : 0;
+#else
+  if (lane == 0) r = mwait(bar, parity, failed_addr, code) ? 1 : 0;
+#endif
+  return __shfl_sync(0xffffffffu, r, 0) != 0;
 }
 
 __device__ __forceinline__ void mma_u8s8_16832(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
@@ -173,7 +228,10 @@ __device__ __forceinline__ uint32_t tile_off(int row, int d) {
 }
 
 // The CTA that owns stage s of a linear with T stages dealt to n CTAs in runs [T c / n, T (c + 1) / n).
-__host__ __device__ inline int stage_owner(int s, int n, int T) { return (int)((((long long)s + 1) * n - 1) / T); }
+// (32-bit arithmetic: the plan refuses shapes with T * n >= 2^31; a 64-bit division is a long subroutine on the GPU)
+__host__ __device__ inline int stage_owner(int s, int n, int T) { return (int)((((unsigned)s + 1u) * (unsigned)n - 1u) / (unsigned)T); }
+// First stage of CTA c's run: T c / n.
+__host__ __device__ inline int run_begin(int T, int c, int n) { return (int)((unsigned)T * (unsigned)c / (unsigned)n); }
 
 // ------------------------------------------------------------------ activation quantiser (the form of gemv_w4.cu)
 // X = rint(x * 16383 / amax) = 128 X_hi + X_lo per 64-k group; eight lanes (one 8-vector each) hold a group and share
@@ -252,7 +310,7 @@ __device__ __forceinline__ void grid_arrive(const MegaParams& p, int tid, int ph
   cons_sync();
   if (tid == 0) {
     __threadfence();
-    if (p.dbg && phase >= 0 && phase < 32) p.dbg[((size_t)blockIdx.x * 2 + 0) * 32 + phase] = globaltimer_ns();
+    if (p.dbg && phase >= 0 && phase < 32) p.dbg[((size_t)blockIdx.x * 8 + 0) * 32 + phase] = globaltimer_ns();
     atomicAdd(p.bar, 1u);
   }
 }
@@ -285,138 +343,221 @@ __device__ __forceinline__ bool grid_wait(const MegaParams& p, const Smem& sm, i
   return ok;
 }
 
-// ------------------------------------------------------------------ the weight / activation producer (one thread)
+// ------------------------------------------------------------------ optional cycle accounting (compile with -DB2_MEGA_PROF)
+// One thread per role adds up the cycles between marks; at its exit it stores the sums behind the phase timestamps
+// of `dbg`: [nCTA][4 roles][8] after the first nCTA * 64 words.
+#ifdef B2_MEGA_PROF
+struct Prof {
+  long long t, v[8];
+  __device__ __forceinline__ void start() {
+    t = clock64();
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = 0;
+  }
+  __device__ __forceinline__ void mark(int k) {
+    const long long now = clock64();
+    v[k] += now - t;
+    t = now;
+  }
+  __device__ __forceinline__ void dump(const MegaParams& p, int role) {
+    if (!p.dbg) return;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) p.dbg[(size_t)p.nCTA * 256 + ((size_t)blockIdx.x * 4 + role) * 8 + i] = (unsigned long long)v[i];
+  }
+};
+// stage trace of CTA 0 (SM cycle counter): [5][1024] words after the cycle sums
+#define TRACE(row, G) if (p.dbg && blockIdx.x == 0 && (G) < 1024) p.dbg[(size_t)p.nCTA * 288 + (row) * 1024 + (G)] = (unsigned long long)clock64();
+#define PROF_DECL Prof prof; prof.start();
+#define PROF_MARK(k) prof.mark(k);
+#define PROF_DUMP(role) prof.dump(p, role);
+#else
+#define TRACE(row, G)
+#define PROF_DECL
+#define PROF_MARK(k)
+#define PROF_DUMP(role)
+#endif
+
+// ------------------------------------------------------------------ the schedule every role of a CTA walks
 struct Cursor {
   int gphase;        // global phase of the linear the cursor is in
   int kind, layer;
   int s, s1;         // next stage, end of this CTA's run
+  int ks;            // the stage's position inside its n-block (k groups kSB * ks ...)
+  bool fresh;        // the cursor has just entered a linear
 };
 __device__ __forceinline__ bool cursor_load(const MegaParams& p, Cursor& c) {
   // positions the cursor on the first stage of this CTA's run of (layer, kind); false when past the last phase
   for (;;) {
     if (c.layer >= p.n_layers) return false;
-    c.gphase = 1 + 5 * c.layer + (c.kind == 0 ? 0 : c.kind + 1);   // qkv, (attention), o, gate||up, down
+    c.gphase = 1 + 5 * c.layer + (c.kind == 0 ? 0 : c.kind + 1);
     if (c.gphase >= p.n_phases) return false;
     const int T = p.T[c.kind];
-    c.s = (int)((long long)T * blockIdx.x / p.nCTA);
-    c.s1 = (int)((long long)T * (blockIdx.x + 1) / p.nCTA);
+    c.s = run_begin(T, blockIdx.x, p.nCTA);
+    c.s1 = run_begin(T, blockIdx.x + 1, p.nCTA);
+    c.ks = c.s % p.SG[c.kind];
+    c.fresh = true;
     if (c.s < c.s1) return true;
     if (++c.kind == 4) { c.kind = 0; ++c.layer; }
   }
 }
 __device__ __forceinline__ bool cursor_next(const MegaParams& p, Cursor& c) {
+  c.fresh = false;
+  if (++c.ks == p.SG[c.kind]) c.ks = 0;
   if (++c.s < c.s1) return true;
   if (++c.kind == 4) { c.kind = 0; ++c.layer; }
   return cursor_load(p, c);
 }
 
-// Sixteen bytes global -> shared through L2 only (no L1 allocation), asynchronously.  The activation buffers are
-// rewritten by other SMs between two reads of the same addresses inside one launch (xq_h is read for qkv and again
-// for gate||up); copies that may be served from an SM-local cache returned the earlier contents for some lines, so
-// the activations take this path and only the weights (constant during the launch) take bulk copies.
-__device__ __forceinline__ void cp_async_cg16(uint32_t dst, const void* src) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
-}
-// The mbarrier gets one arrival from this thread once all its earlier cp.async copies have landed.
-__device__ __forceinline__ void cp_async_arrive(uint32_t bar) {
-  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
+// One thread polls the arrival counter until `need` arrivals are in (phases 0 .. need / nCTA - 1 complete).
+// Returns the counter, or 0xffffffff when the launch is being abandoned or the bound ran out.
+__device__ __forceinline__ unsigned poll_arrivals(const MegaParams& p, const Smem& sm, unsigned need, unsigned code, int phase) {
+  unsigned v = ld_acquire_gpu(p.bar);
+  if (v >= need) return v;
+  const long long t0 = clock64();
+  int spins = 0;
+  for (;;) {
+    v = ld_acquire_gpu(p.bar);
+    if (v >= need) return v;
+    if (++spins > 16) {
+      __nanosleep(64);
+      if ((spins & 15) == 0) {
+        const bool stale = clock64() - t0 > 3000000000ll;
+        if (stale || lds32v(sm.misc) != 0u || ld_acquire_gpu(p.bar + 1) != 0u) {
+          if (stale && ld_acquire_gpu(p.bar + 1) == 0u) record_error(code, (unsigned)phase << 16 | blockIdx.x);
+          atomicExch(p.bar + 1, 1u);
+          sts32(sm.misc, 1u);
+          return 0xffffffffu;
+        }
+      }
+    }
+  }
 }
 
-// The producer WARP: every lane walks the same schedule (uniform control flow); lane 0 issues the weight copies and
-// polls, all lanes share the activation copies of a stage.
-__device__ void producer(const MegaParams& p, const Smem& sm, const int lane) {
-  Cursor cw{0, 0, 0, 0, 0}, cx{0, 0, 0, 0, 0};
-  bool more_w = cursor_load(p, cw), more_x = cursor_load(p, cx);
-  int Gw = 0, Gx = 0;
-  unsigned seen = 0;
-  const int xchunks = (2 * p.rows * kXRow) / 16, gchunks = 128 / 16;
-  long long t_idle = 0;
-  bool idle = false, ok = true;
-  while (more_x) {
-    bool did = false;
-    if (more_w) {
-      const int slot = Gw % p.NS;
-      const int use = Gw / p.NS;
-      int free_slot = 1;
-      if (use > 0) {
-        if (lane == 0) free_slot = mbar_test(sm.empty + 8 * slot, (uint32_t)((use - 1) & 1)) ? 1 : 0;
-        free_slot = __shfl_sync(0xffffffffu, free_slot, 0);
-      }
-      if (free_slot) {
-        if (lane == 0) {
-          const uint8_t* src = p.layers[cw.layer].w[cw.kind] + (size_t)cw.s * kWStage;
-          mbar_expect_tx(sm.fullW + 8 * slot, kWStage);
-          bulk_g2s(sm.ring + slot * sm.stageB, src, kWStage, sm.fullW + 8 * slot);
-        }
-        ++Gw;
-        more_w = cursor_next(p, cw);
-        did = true;
-      }
-    }
-    if (Gx < Gw) {
-      const unsigned need = (unsigned)cx.gphase * (unsigned)p.nCTA;   // the phase before this linear's is complete
-      if (seen < need) {
-        unsigned v = 0;
-        if (lane == 0) v = ld_acquire_gpu(p.bar);
-        seen = __shfl_sync(0xffffffffu, v, 0);
-        if (seen >= need) __threadfence();   // every lane's copies below come after the other CTAs' stores
-      }
-      if (seen >= need) {
-        const int slot = Gx % p.NS;
-        const int which = cx.kind == 1 ? 1 : (cx.kind == 3 ? 2 : 0);
-        const int kg0 = 2 * (cx.s % p.SG[cx.kind]);
-        const uint32_t dst = sm.ring + slot * sm.stageB + kWStage;
-        const uint8_t* xsrc = p.xq[which] + (size_t)kg0 * p.rows * kXRow;
-        const uint8_t* gsrc = reinterpret_cast<const uint8_t*>(p.gs[which]) + (size_t)kg0 * 64;
-        if (p.dbg && lane == 0 && cx.gphase < 32 && p.dbg[((size_t)blockIdx.x * 2 + 1) * 32 + cx.gphase] == 0ull)
-          p.dbg[((size_t)blockIdx.x * 2 + 1) * 32 + cx.gphase] = globaltimer_ns();
-        for (int i = lane; i < xchunks; i += 32) cp_async_cg16(dst + 16 * i, xsrc + 16 * i);
-        if (lane < gchunks) cp_async_cg16(dst + 16 * xchunks + 16 * lane, gsrc + 16 * lane);
-        cp_async_arrive(sm.fullX + 8 * slot);   // 32 arrivals complete the stage's activation barrier
-        ++Gx;
-        more_x = cursor_next(p, cx);
-        did = true;
-      }
-    }
-    if (did) {
-      idle = false;
-      continue;
-    }
-    int stop = 0;
-    if (lane == 0) {
-      if (!idle) {
-        idle = true;
-        t_idle = clock64();
-      } else if (clock64() - t_idle > 3000000000ll || lds32v(sm.misc) != 0u || ld_acquire_gpu(p.bar + 1) != 0u) {
-        if (ld_acquire_gpu(p.bar + 1) == 0u && lds32v(sm.misc) == 0u) record_error(ERR_MEGA_PRODUCER, (unsigned)cx.gphase << 16 | blockIdx.x);
-        atomicExch(p.bar + 1, 1u);
-        sts32(sm.misc, 1u);
-        stop = 1;
-      }
-    }
-    if (__shfl_sync(0xffffffffu, stop, 0)) {
+// ------------------------------------------------------------------ the weight producer (one thread)
+// Walks the schedule and refills every ring slot the consumers give back.  Weights depend on nothing, so this
+// thread never looks at the grid barrier: the stream runs on through phase changes and through attention.
+__device__ void w_producer(const MegaParams& p, const Smem& sm) {
+  Cursor c{0, 0, 0, 0, 0, 0, true};
+  bool more = cursor_load(p, c);
+  int slot = 0, issued = 0;
+  unsigned use = 0;
+  bool ok = true;
+  const uint8_t* wptr = nullptr;   // a CTA's run of a linear is one contiguous byte range of its W4B tensor
+  int KG = 0;
+  PROF_DECL
+  while (more) {
+#ifdef B2_MEGA_PROF
+    ++prof.v[6];
+    if (use > 0 && !mwait(sm.empty + 8 * slot, (use - 1) & 1u, sm.misc, ERR_MEGA_RING, &prof.v[7])) {
+#else
+    if (use > 0 && !mwait(sm.empty + 8 * slot, (use - 1) & 1u, sm.misc, ERR_MEGA_RING)) {
+#endif
       ok = false;
       break;
     }
-    __nanosleep(20);
+    if (c.fresh) {
+      KG = p.KG[c.kind];
+      const int j = c.s / p.SG[c.kind];
+      wptr = p.layers[c.layer].w[c.kind] + ((size_t)j * KG + (size_t)c.ks * kSB) * kBlockBytes;
+    }
+    const uint32_t wbytes = (uint32_t)min(kSB, KG - c.ks * kSB) * kBlockBytes;
+    if (p.variant & 2) {
+      mbar_arrive(sm.fullW + 8 * slot);
+    } else {
+      mbar_expect_tx(sm.fullW + 8 * slot, wbytes);
+      bulk_g2s(sm.ring + slot * sm.stageB, wptr, wbytes, sm.fullW + 8 * slot);
+    }
+    wptr += wbytes;
+    ++issued;
+    if (++slot == p.NS) { slot = 0; ++use; }
+    more = cursor_next(p, c);
   }
+  PROF_DUMP(0)
   if (!ok) {
     // drain: the copies that were issued must have landed before the CTA gives its shared memory back
-    asm volatile("cp.async.wait_all;" ::: "memory");
-    if (lane == 0)
-      for (int G = (Gw > p.NS ? Gw - p.NS : 0); G < Gw; ++G) mbar_wait(sm.fullW + 8 * (G % p.NS), (uint32_t)((G / p.NS) & 1), ERR_MEGA_RING);
+    atomicExch(p.bar + 1, 1u);
+    for (int G = (issued > p.NS ? issued - p.NS : 0); G < issued; ++G)
+      mbar_wait(sm.fullW + 8 * (G % p.NS), (uint32_t)((G / p.NS) & 1), ERR_MEGA_RING);
+  }
+}
+
+// ------------------------------------------------------------------ the activation producer (one thread)
+// The two 64-k groups of a stage for every row (contiguous in the quantised buffer) and their {scale, -8 sum} words:
+// two bulk copies into the stage's slot behind the weights, on the slot's second mbarrier.  A linear's rows exist
+// once the phase before it is complete, so this thread is the one that meets the grid barrier; the consumers only
+// ever wait on their stage's two mbarriers.  The rows were written with ordinary stores by other CTAs: their
+// writers fence towards the async proxy before they arrive at the barrier, and so does this thread after it.
+__device__ void x_producer(const MegaParams& p, const Smem& sm) {
+  Cursor c{0, 0, 0, 0, 0, 0, true};
+  bool more = cursor_load(p, c);
+  int slot = 0, issued = 0;
+  unsigned use = 0, seen = 0;
+  bool ok = true;
+  const uint32_t xgroup = (uint32_t)p.rows * kXRow;   // bytes of one 64-k group of every row
+  int KG = 0;
+  const uint8_t* xbase = nullptr;
+  const uint8_t* gbase = nullptr;
+  PROF_DECL
+  while (more) {
+#ifdef B2_MEGA_PROF
+    ++prof.v[6];
+    if (use > 0 && !mwait(sm.empty + 8 * slot, (use - 1) & 1u, sm.misc, ERR_MEGA_RING, &prof.v[7])) {
+#else
+    if (use > 0 && !mwait(sm.empty + 8 * slot, (use - 1) & 1u, sm.misc, ERR_MEGA_RING)) {
+#endif
+      ok = false;
+      break;
+    }
+    const unsigned need = (unsigned)c.gphase * (unsigned)p.nCTA;   // the phase before this linear's is complete
+    if (seen < need) {
+      const unsigned v = poll_arrivals(p, sm, need, ERR_MEGA_PRODUCER, c.gphase);
+      if (v == 0xffffffffu) {
+        ok = false;
+        break;
+      }
+      seen = v;
+      __threadfence();
+      fence_proxy_async_all();   // the copies below (async proxy) come after the other CTAs' stores
+      if (p.dbg && c.gphase < 32) p.dbg[((size_t)blockIdx.x * 8 + 1) * 32 + c.gphase] = globaltimer_ns();
+    }
+    if (c.fresh) {
+      const int which = c.kind == 1 ? 1 : (c.kind == 3 ? 2 : 0);
+      xbase = p.xq[which];
+      gbase = reinterpret_cast<const uint8_t*>(p.gs[which]);
+      KG = p.KG[c.kind];
+    }
+    const uint32_t dst = sm.ring + slot * sm.stageB + kWStage;
+    if (p.variant & 4) {
+      mbar_arrive(sm.fullX + 8 * slot);
+    } else {
+      // the stage's k groups walk round and round the row: kSB * ks .. (an n-block's last stage may be short)
+      const uint32_t ng = (uint32_t)min(kSB, KG - c.ks * kSB);
+      mbar_expect_tx(sm.fullX + 8 * slot, ng * (xgroup + 64u));
+      bulk_g2s(dst, xbase + (size_t)(c.ks * kSB) * xgroup, ng * xgroup, sm.fullX + 8 * slot);
+      bulk_g2s(dst + kSB * xgroup, gbase + (size_t)(c.ks * kSB) * 64, ng * 64u, sm.fullX + 8 * slot);
+    }
+    ++issued;
+    if (++slot == p.NS) { slot = 0; ++use; }
+    more = cursor_next(p, c);
+  }
+  PROF_DUMP(1)
+  if (!ok) {
+    sts32(sm.misc, 1u);
+    atomicExch(p.bar + 1, 1u);
+    for (int G = (issued > p.NS ? issued - p.NS : 0); G < issued; ++G)
+      mbar_wait(sm.fullX + 8 * (G % p.NS), (uint32_t)((G / p.NS) & 1), ERR_MEGA_RING);
   }
 }
 
 // ------------------------------------------------------------------ linear epilogues, run by the CTA that finishes an n-block last
 // KIND 0 qkv: RoPE; q rows as bf16, k / v rows into the cache.  Items (row m, 8-vector v of the head's 128 dims).
-__device__ void fold_qkv(const MegaParams& p, const MegaLayer& L, int j, int nslots, int tid) {
+__device__ void fold_qkv(const MegaParams& p, const MegaLayer& L, int j, int nslots, int tid, int nthreads) {
   const int warp = tid >> 5, lane = tid & 31;
   const int items = p.M * 16;
   const int pos0 = p.ctrl[CTRL_ROW_POS], req = p.ctrl[CTRL_ROW_REQ];
   const size_t slot_stride = (size_t)p.M * 128;
   const float* pbase = p.part + (size_t)j * 2 * p.maxseg[0] * slot_stride;   // qkv: half 0
-  for (int it0 = warp * 32; it0 < items; it0 += kCons) {
+  for (int it0 = warp * 32; it0 < items; it0 += nthreads) {
     const int it = it0 + lane;
     const bool act = it < items;
     const int m = act ? it >> 4 : 0, v = it & 15;
@@ -456,12 +597,12 @@ __device__ void fold_qkv(const MegaParams& p, const MegaLayer& L, int j, int nsl
 
 // KIND 1 / 3 (and the embedding, nslots = 0 with `src` the rows' embedding vectors): residual add, bf16 stream,
 // the block's sums of squares, next norm weight and quantised rows for the next hidden-wide linear.
-__device__ void fold_resid(const MegaParams& p, int kind, const float* norm_next, int j, int nslots, int tid, bool embed) {
+__device__ void fold_resid(const MegaParams& p, int kind, const float* norm_next, int j, int nslots, int tid, int nthreads, bool embed) {
   const int warp = tid >> 5, lane = tid & 31;
   const int items = p.M * 16;
   const size_t slot_stride = (size_t)p.M * 128;
   const float* pbase = embed ? nullptr : p.part + (kind & 1) * p.part_half + (size_t)j * 2 * p.maxseg[kind] * slot_stride;
-  for (int it0 = warp * 32; it0 < items; it0 += kCons) {
+  for (int it0 = warp * 32; it0 < items; it0 += nthreads) {
     const int it = it0 + lane;
     const bool act = it < items;
     const int m = act ? it >> 4 : 0, v = it & 15;
@@ -514,12 +655,12 @@ __device__ void fold_resid(const MegaParams& p, int kind, const float* norm_next
 }
 
 // KIND 2 gate||up (interleave16: runs of 16 gate, 16 up): SiLU(gate) * up -> one quantised group of down's input.
-__device__ void fold_act(const MegaParams& p, int j, int nslots, int tid) {
+__device__ void fold_act(const MegaParams& p, int j, int nslots, int tid, int nthreads) {
   const int warp = tid >> 5, lane = tid & 31;
   const int items = p.M * 8;
   const size_t slot_stride = (size_t)p.M * 128;
   const float* pbase = p.part + (size_t)j * 2 * p.maxseg[2] * slot_stride;   // gate||up: half 0
-  for (int it0 = warp * 32; it0 < items; it0 += kCons) {
+  for (int it0 = warp * 32; it0 < items; it0 += nthreads) {
     const int it = it0 + lane;
     const bool act = it < items;
     const int m = act ? it >> 3 : 0, a = it & 7;
@@ -542,173 +683,343 @@ __device__ void fold_act(const MegaParams& p, int j, int nslots, int tid) {
 
 // ------------------------------------------------------------------ one linear: this CTA's run of stages
 struct Lane {
-  int tid, warp, lane, w8, gidx, g, t;
+  int tid, warp, lane, wq, gidx, g, t;
 };
+// What a consumer thread carries from phase to phase: stages and run ends of this CTA so far (every role counts
+// them the same way), and the ring position of its group's next stage (the groups take alternate stages).
+struct ConsState {
+  int G, R, slot;
+  uint32_t par;
+#ifdef B2_MEGA_PROF
+  Prof prof;
+#endif
+};
+#ifdef B2_MEGA_PROF
+#define CPROF(k) cs.prof.mark(k);
+#else
+#define CPROF(k)
+#endif
 
-__device__ __forceinline__ void compute_rinv(const MegaParams& p, const Lane& ln, float& r0, float& r1) {
-  for (int m = 0; m < p.M; ++m) {
-    float s = 0.f;
-    for (int jj = ln.lane; jj < p.nbH; jj += 32) s += __ldcg(p.ssq + (size_t)m * p.nbH + jj);
-    s = warp_sum(s);
-    const float r = rsqrtf(s / (float)p.H + p.eps);
-    if (m == 2 * ln.t) r0 = r;
-    if (m == 2 * ln.t + 1) r1 = r;
+__device__ __forceinline__ void sts_f32(uint32_t a, float v) { asm volatile("st.shared.f32 [%0], %1;" ::"r"(a), "f"(v) : "memory"); }
+__device__ __forceinline__ float4 lds_f4(uint32_t a) {
+  float4 v;
+  asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(a));
+  return v;
+}
+
+// Which runs meet in n-block j of a linear, and which of them is CTA c's (whose last stage there is s_last).  With
+// at least one stage per CTA the runs belong to consecutive CTAs; a linear with fewer stages than CTAs gives
+// single-stage runs to scattered CTAs, one per stage.
+__device__ __forceinline__ void run_slots(const MegaParams& p, int kind, int c, int j, int s_last, int& nseg, int& seg) {
+  const int T = p.T[kind], SG = p.SG[kind];
+  if (T >= p.nCTA) {
+    const int c_first = stage_owner(j * SG, p.nCTA, T), c_last = stage_owner((j + 1) * SG - 1, p.nCTA, T);
+    nseg = c_last - c_first + 1;
+    seg = c - c_first;
+  } else {
+    nseg = SG;
+    seg = s_last - j * SG;
   }
 }
 
+// The consumer side: wait for a stage's two mbarriers, multiply, give the slot back.  At the end of a run inside an
+// n-block the accumulators go to a shared-memory hand-off buffer and the warps carry on with the next stage at
+// once: global stores, fences, tickets and folds are the epilogue warp's business.
 template <int KIND>
-__device__ void gemv_phase(const MegaParams& p, const Smem& sm, int layer, int gphase, int& G, bool& ok, const Lane& ln) {
+__device__ void gemv_phase(const MegaParams& p, const Smem& sm, ConsState& cs, bool& ok, const Lane& ln, int layer_dbg) {
   const int T = p.T[KIND], SG = p.SG[KIND];
   const int c = blockIdx.x;
-  const int s0 = (int)((long long)T * c / p.nCTA), s1 = (int)((long long)T * (c + 1) / p.nCTA);
-  const MegaLayer& L = p.layers[layer];
-  if (s0 == s1) {   // no stage of this linear: the arrival still has to come after the phase before
-    if (!grid_wait(p, sm, gphase, ln.tid)) ok = false;   // every consumer thread takes part, failed or not
-    grid_arrive(p, ln.tid, gphase);
-    return;
-  }
-  constexpr bool kNorm = KIND == 0 || KIND == 2;   // the input is RMS-normalised: 1/rms multiplies the partial sums
-  float r0 = 1.f, r1 = 1.f;
-  bool have_r = false;
-  float acc[4] = {0.f, 0.f, 0.f, 0.f};
-  const uint32_t w_off = ln.w8 * 512 + ln.lane * 16;
-  const uint32_t sc_off = 4096 + (ln.w8 * 16 + 2 * ln.g) * 2;
+  const int s0 = run_begin(T, c, p.nCTA), s1 = run_begin(T, c + 1, p.nCTA);
+  if (s0 == s1) return;
+  // A warp of a group owns rows 32 wq .. 32 wq + 31 of the 128-row block as two 16-row tiles: two independent chains
+  // of integer MMAs per 64-k group, and the activation fragments are read once for both.
+  float acc[2][4];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) acc[h][0] = acc[h][1] = acc[h][2] = acc[h][3] = 0.f;
+  const uint32_t w_off = ln.wq * 1024 + ln.lane * 16;
+  const uint32_t sc_off = 4096 + (ln.wq * 32 + 2 * ln.g) * 2;
   const uint32_t x_off = kWStage + min(ln.g, p.rows - 1) * kXRow + ln.t * 32;
-  const uint32_t gs_off = kWStage + 2 * p.rows * kXRow + 2 * ln.t * 8;
+  const uint32_t gs_off = kWStage + kSB * p.rows * kXRow + 2 * ln.t * 8;
+  const int KG = p.KG[KIND];
+  int ks = s0 % SG;   // the stage's position inside its n-block
+  const uint32_t out_g = sm.out + ln.gidx * p.M * 512;
   constexpr uint32_t kMask = 0x0F0F0F0Fu;
+  int jend = (s0 / SG + 1) * SG;   // first stage of the next n-block
+  const int gphase_dbg = 1 + 5 * layer_dbg + (KIND == 0 ? 0 : KIND + 1);
+  bool first_dbg = p.dbg != nullptr && ln.tid == 0 && gphase_dbg < 32;
   for (int s = s0; s < s1; ++s) {
-    const int Gs = G + (s - s0);
-    if ((Gs & 1) == ln.gidx) {
-      const int slot = Gs % p.NS;
-      const uint32_t par = (uint32_t)((Gs / p.NS) & 1);
-      // the votes keep `ok` the same in every lane: the code below shuffles with the full mask
-      if (ok) ok = __all_sync(0xffffffffu, mwait(sm.fullW + 8 * slot, par, sm.misc, ERR_MEGA_RING));
-      if (ok) ok = __all_sync(0xffffffffu, mwait(sm.fullX + 8 * slot, par, sm.misc, ERR_MEGA_RING));
-      if (ok) {
-        if (kNorm && !have_r) {
-          compute_rinv(p, ln, r0, r1);
-          have_r = true;
-        }
+    if (((cs.G + s - s0) & (kGroups - 1)) == ln.gidx) {
+      const int slot = cs.slot;
+      const uint32_t par = cs.par;
+      // the shuffle inside keeps `ok` the same in every lane: the code below runs warp-wide
+#ifdef B2_MEGA_PROF
+      ++cs.prof.v[6];
+      if (ok) ok = warp_wait(sm.fullW + 8 * slot, par, sm.misc, ERR_MEGA_RING, ln.lane, &cs.prof.v[0]);
+      if (ok) ok = warp_wait(sm.fullX + 8 * slot, par, sm.misc, ERR_MEGA_RING, ln.lane, &cs.prof.v[1]);
+#else
+      if (ok) ok = warp_wait(sm.fullW + 8 * slot, par, sm.misc, ERR_MEGA_RING, ln.lane);
+      if (ok) ok = warp_wait(sm.fullX + 8 * slot, par, sm.misc, ERR_MEGA_RING, ln.lane);
+#endif
+      if (first_dbg) {
+        first_dbg = false;
+        p.dbg[((size_t)blockIdx.x * 8 + 3) * 32 + gphase_dbg] = globaltimer_ns();
+      }
+      if (ok && !(p.variant & 1)) {
         const uint32_t st = sm.ring + slot * sm.stageB;
-        uint4 wv[2];
-        uint32_t sc2[2];
-#pragma unroll
-        for (int q = 0; q < 2; ++q) {
-          wv[q] = lds128(st + q * kBlockBytes + w_off);
-          sc2[q] = lds32(st + q * kBlockBytes + sc_off);
-        }
-#pragma unroll
-        for (int q = 0; q < 2; ++q) {
-          const uint32_t l0 = wv[q].x & kMask, l1 = wv[q].y & kMask, l2 = wv[q].z & kMask, l3 = wv[q].w & kMask;
-          const uint32_t h0 = (wv[q].x >> 4) & kMask, h1 = (wv[q].y >> 4) & kMask;
-          const uint32_t h2 = (wv[q].z >> 4) & kMask, h3 = (wv[q].w >> 4) & kMask;
-          const __half2 sh = *reinterpret_cast<const __half2*>(&sc2[q]);
-          const float s_lo = __low2float(sh), s_hi = __high2float(sh);
+        const int ng = min(kSB, KG - ks * kSB);
+#pragma unroll 2
+        for (int q = 0; q < ng; ++q) {
           const uint4 xh = lds128(st + x_off + q * p.rows * kXRow);
           const uint4 xl = lds128(st + x_off + q * p.rows * kXRow + 16);
           const uint4 gsv = lds128(st + gs_off + q * 64);
-          int ih[4] = {0, 0, 0, 0};
-          int il[4] = {(int)gsv.y, (int)gsv.w, (int)gsv.y, (int)gsv.w};
-          mma_u8s8_16832(ih, l0, l1, h0, h1, xh.x, xh.y);
-          mma_u8s8_16832(il, l0, l1, h0, h1, xl.x, xl.y);
-          mma_u8s8_16832(ih, l2, l3, h2, h3, xh.z, xh.w);
-          mma_u8s8_16832(il, l2, l3, h2, h3, xl.z, xl.w);
           const float sx0 = __uint_as_float(gsv.x), sx1 = __uint_as_float(gsv.z);
-          acc[0] = fmaf(s_lo * sx0, (float)(ih[0] * 128 + il[0]), acc[0]);
-          acc[1] = fmaf(s_lo * sx1, (float)(ih[1] * 128 + il[1]), acc[1]);
-          acc[2] = fmaf(s_hi * sx0, (float)(ih[2] * 128 + il[2]), acc[2]);
-          acc[3] = fmaf(s_hi * sx1, (float)(ih[3] * 128 + il[3]), acc[3]);
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            const uint4 wv = lds128(st + q * kBlockBytes + w_off + h * 512);
+            const uint32_t sc2 = lds32(st + q * kBlockBytes + sc_off + h * 32);
+            const uint32_t l0 = wv.x & kMask, l1 = wv.y & kMask, l2 = wv.z & kMask, l3 = wv.w & kMask;
+            const uint32_t h0 = (wv.x >> 4) & kMask, h1 = (wv.y >> 4) & kMask;
+            const uint32_t h2 = (wv.z >> 4) & kMask, h3 = (wv.w >> 4) & kMask;
+            const __half2 sh = *reinterpret_cast<const __half2*>(&sc2);
+            const float s_lo = __low2float(sh), s_hi = __high2float(sh);
+            int ih[4] = {0, 0, 0, 0};
+            int il[4] = {(int)gsv.y, (int)gsv.w, (int)gsv.y, (int)gsv.w};
+            mma_u8s8_16832(ih, l0, l1, h0, h1, xh.x, xh.y);
+            mma_u8s8_16832(il, l0, l1, h0, h1, xl.x, xl.y);
+            mma_u8s8_16832(ih, l2, l3, h2, h3, xh.z, xh.w);
+            mma_u8s8_16832(il, l2, l3, h2, h3, xl.z, xl.w);
+            acc[h][0] = fmaf(s_lo * sx0, (float)(ih[0] * 128 + il[0]), acc[h][0]);
+            acc[h][1] = fmaf(s_lo * sx1, (float)(ih[1] * 128 + il[1]), acc[h][1]);
+            acc[h][2] = fmaf(s_hi * sx0, (float)(ih[2] * 128 + il[2]), acc[h][2]);
+            acc[h][3] = fmaf(s_hi * sx1, (float)(ih[3] * 128 + il[3]), acc[h][3]);
+          }
         }
+      }
+      if (ok) {
         __syncwarp();
         if (ln.lane == 0) mbar_arrive(sm.empty + 8 * slot);
       }
-    }
-    const int j = s / SG;
-    if (s + 1 < s1 && (s + 1) / SG == j) continue;
-    // ---- end of this CTA's run inside n-block j: leave the partial sums, take a ticket
-    // runs that meet in n-block j: with at least one stage per CTA they belong to consecutive CTAs; a linear with
-    // fewer stages than CTAs gives single-stage runs to scattered CTAs, one per stage
-    int nseg, seg;
-    if (T >= p.nCTA) {
-      const int c_first = stage_owner(j * SG, p.nCTA, T), c_last = stage_owner((j + 1) * SG - 1, p.nCTA, T);
-      nseg = c_last - c_first + 1;
-      seg = c - c_first;
-    } else {
-      nseg = SG;
-      seg = s - j * SG;
-    }
-    {
-      // The warp group without a stage in this run gets here at once, before the barrier in front of this phase:
-      // its (zero) partial must not land where the folds of the phase before may still be reading, hence the halves.
-      float* dst = p.part + (KIND & 1) * p.part_half + ((size_t)j * 2 * p.maxseg[KIND] + (size_t)seg * 2 + ln.gidx) * p.M * 128;
-      const int n_lo = ln.w8 * 16 + ln.g, m0 = 2 * ln.t, m1 = m0 + 1;
-      if (m0 < p.M) {
-        dst[m0 * 128 + n_lo] = acc[0] * r0;
-        dst[m0 * 128 + n_lo + 8] = acc[2] * r0;
-      }
-      if (m1 < p.M) {
-        dst[m1 * 128 + n_lo] = acc[1] * r1;
-        dst[m1 * 128 + n_lo + 8] = acc[3] * r1;
-      }
-      acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
-    }
-    __threadfence();
-    cons_sync();
-    if (ln.tid == 0) {
-      const int tk = atomicAdd(&p.tickets[j], 1);
-      const int last = tk == nseg - 1;
-      if (last) p.tickets[j] = 0;
-      sts32(sm.misc + 8, (uint32_t)last);
-    }
-    cons_sync();
-    const bool last = __all_sync(0xffffffffu, lds32v(sm.misc + 8) != 0u && lds32v(sm.misc) == 0u);
-    if (last) {
-      __threadfence();
-      if (KIND == 0) fold_qkv(p, L, j, 2 * nseg, ln.tid);
-      else if (KIND == 2) fold_act(p, j, 2 * nseg, ln.tid);
-      else {
-        const float* nn = KIND == 1 ? L.post_norm : (layer + 1 < p.n_layers ? p.layers[layer + 1].input_norm : nullptr);
-        fold_resid(p, KIND, nn, j, 2 * nseg, ln.tid, false);
+      cs.slot += kGroups;
+      if (cs.slot >= p.NS) {
+        cs.slot -= p.NS;
+        cs.par ^= 1u;
       }
     }
-    cons_sync();   // the ticket word is rewritten at the next run end
+    if (++ks == SG) ks = 0;
+    if (s + 1 < s1 && s + 1 < jend) continue;
+    // ---- end of this CTA's run inside an n-block: hand the sums (zeros from a group without a stage) over
+    jend += SG;
+    const int buf = cs.R & 1;
+    if (ok && cs.R >= 2) ok = warp_wait(sm.outempty + 8 * buf, (uint32_t)(((cs.R >> 1) - 1) & 1), sm.misc, ERR_MEGA_RING, ln.lane);
+    if (ok) {
+      const uint32_t o = out_g + buf * (kGroups * p.M * 512);
+      const int m0 = 2 * ln.t, m1 = m0 + 1;
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int n_lo = ln.wq * 32 + h * 16 + ln.g;
+        if (m0 < p.M) {
+          sts_f32(o + (m0 * 128 + n_lo) * 4, acc[h][0]);
+          sts_f32(o + (m0 * 128 + n_lo + 8) * 4, acc[h][2]);
+        }
+        if (m1 < p.M) {
+          sts_f32(o + (m1 * 128 + n_lo) * 4, acc[h][1]);
+          sts_f32(o + (m1 * 128 + n_lo + 8) * 4, acc[h][3]);
+        }
+      }
+      __syncwarp();
+      if (ln.lane == 0) mbar_arrive(sm.outfull + 8 * buf);
+    }
+#pragma unroll
+    for (int h = 0; h < 2; ++h) acc[h][0] = acc[h][1] = acc[h][2] = acc[h][3] = 0.f;
+    ++cs.R;
   }
-  G += s1 - s0;
-  grid_arrive(p, ln.tid, gphase);
+  cs.G += s1 - s0;
+  if (p.dbg != nullptr && ln.tid == 256 && gphase_dbg < 32) p.dbg[((size_t)blockIdx.x * 8 + 2) * 32 + gphase_dbg] = globaltimer_ns();
+}
+
+// ------------------------------------------------------------------ the epilogue warp
+// Takes every run end of this CTA from the hand-off buffer: adds the two groups' sums (times 1/rms of the row where
+// the linear's input is RMS-normalised), stores them in the n-block's slot, takes a ticket; as the last of an
+// n-block's runs it sums the slots in slot order and applies the linear's epilogue.  After the CTA's last run of a
+// phase it makes the CTA's arrival at the grid barrier.  None of this holds the consumer warps up.
+__device__ void epilogue(const MegaParams& p, const Smem& sm, const int lane) {
+  const int c = blockIdx.x;
+  int R = 0;
+  bool ok = true;
+  PROF_DECL
+  for (int layer = 0; layer < p.n_layers && ok; ++layer) {
+    const MegaLayer& L = p.layers[layer];
+#pragma unroll 1
+    for (int kind = 0; kind < 4 && ok; ++kind) {
+      const int gphase = 1 + 5 * layer + (kind == 0 ? 0 : kind + 1);
+      if (gphase >= p.n_phases) {
+        if (lane == 0) { PROF_DUMP(3) }
+        return;
+      }
+      const int T = p.T[kind], SG = p.SG[kind];
+      const int s0 = run_begin(T, c, p.nCTA), s1 = run_begin(T, c + 1, p.nCTA);
+      if (s0 == s1) {
+        // no stage of this linear here: the arrival still has to come after the phase before
+        unsigned v = 0;
+        if (lane == 0) v = poll_arrivals(p, sm, (unsigned)gphase * (unsigned)p.nCTA, ERR_MEGA_GRID, gphase);
+        if (__shfl_sync(0xffffffffu, v, 0) == 0xffffffffu) ok = false;
+      } else {
+        const bool normed = kind == 0 || kind == 2;   // the input is RMS-normalised: 1/rms multiplies the sums
+        float rinv[kMaxRows];
+#pragma unroll
+        for (int m = 0; m < kMaxRows; ++m) rinv[m] = 1.f;
+        if (normed) {
+          // 1 / rms of the rows: their sums of squares are final once the phase before is complete.  This warp
+          // has nothing else to do until the consumers hand their first run over, so it meets the barrier itself.
+          unsigned v = 0;
+          if (lane == 0) v = poll_arrivals(p, sm, (unsigned)gphase * (unsigned)p.nCTA, ERR_MEGA_GRID, gphase);
+          if (__shfl_sync(0xffffffffu, v, 0) == 0xffffffffu) {
+            ok = false;
+            break;
+          }
+#pragma unroll
+          for (int m = 0; m < kMaxRows; ++m) {
+            if (m < p.M) {
+              float s = 0.f;
+              for (int jj = lane; jj < p.nbH; jj += 32) s += __ldcg(p.ssq + (size_t)m * p.nbH + jj);
+              s = warp_sum(s);
+              rinv[m] = rsqrtf(s / (float)p.H + p.eps);
+            }
+          }
+        }
+        for (int j = s0 / SG; j <= (s1 - 1) / SG && ok && !(p.variant & 64); ++j) {
+          const int buf = R & 1;
+          ok = warp_wait(sm.outfull + 8 * buf, (uint32_t)((R >> 1) & 1), sm.misc, ERR_MEGA_RING, lane);
+          if (!ok) break;
+          const bool stamp = p.dbg != nullptr && lane == 0 && gphase < 32 && j == (s1 - 1) / SG;
+          if (stamp) p.dbg[((size_t)blockIdx.x * 8 + 4) * 32 + gphase] = globaltimer_ns();
+          int nseg, seg;
+          run_slots(p, kind, c, j, min(s1, (j + 1) * SG) - 1, nseg, seg);
+          float* dst = p.part + (kind & 1) * p.part_half + ((size_t)j * 2 * p.maxseg[kind] + (size_t)seg) * p.M * 128;
+          const uint32_t o = sm.out + buf * (kGroups * p.M * 512);
+#pragma unroll
+          for (int m = 0; m < kMaxRows; ++m) {
+            if (m < p.M) {
+              float4 a = lds_f4(o + (m * 128 + 4 * lane) * 4);
+#pragma unroll
+              for (int gq = 1; gq < kGroups; ++gq) {   // group order: the order the stages were dealt in
+                const float4 b = lds_f4(o + gq * p.M * 512 + (m * 128 + 4 * lane) * 4);
+                a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
+              }
+              const float r = rinv[m];
+              *reinterpret_cast<float4*>(dst + m * 128 + 4 * lane) = make_float4(a.x * r, a.y * r, a.z * r, a.w * r);
+            }
+          }
+          __syncwarp();
+          if (lane == 0) mbar_arrive(sm.outempty + 8 * buf);
+          if (stamp) p.dbg[((size_t)blockIdx.x * 8 + 5) * 32 + gphase] = globaltimer_ns();
+          int last = 1;
+          if (nseg > 1) {
+            __syncwarp();
+            if (lane == 0) {
+              const int tk = atom_add_acq_rel(&p.tickets[j], 1);
+              last = tk == nseg - 1;
+              if (last) p.tickets[j] = 0;   // next used after a grid barrier
+            }
+            last = __shfl_sync(0xffffffffu, last, 0);
+            __syncwarp();   // the other lanes' loads of the slots come after lane 0's acquire
+          } else {
+            __threadfence_block();   // the whole n-block is this CTA's: the fold below reads this warp's own stores
+            __syncwarp();
+          }
+          if (stamp) p.dbg[((size_t)blockIdx.x * 8 + 6) * 32 + gphase] = globaltimer_ns();
+          if (last) {
+            if (kind == 0) fold_qkv(p, L, j, nseg, lane, 32);
+            else if (kind == 2) fold_act(p, j, nseg, lane, 32);
+            else {
+              const float* nn = kind == 1 ? L.post_norm : (layer + 1 < p.n_layers ? p.layers[layer + 1].input_norm : nullptr);
+              fold_resid(p, kind, nn, j, nseg, lane, 32, false);
+            }
+          }
+          if (stamp) p.dbg[((size_t)blockIdx.x * 8 + 7) * 32 + gphase] = globaltimer_ns() | (last ? 1ull : 0ull);
+          ++R;
+        }
+      }
+      if (!ok) break;
+      // ---- this CTA's arrival for the phase
+      fence_proxy_async_all();   // the phase's generic-proxy stores are read by TMA / bulk copies of other CTAs next
+      __syncwarp();
+      if (lane == 0) {
+        if (p.dbg && gphase < 32) p.dbg[((size_t)blockIdx.x * 8 + 0) * 32 + gphase] = globaltimer_ns();
+        red_add_release(p.bar, 1u);
+      }
+    }
+  }
+  if (lane == 0) { PROF_DUMP(3) }
+  if (!ok && lane == 0) {
+    sts32(sm.misc, 1u);
+    atomicExch(p.bar + 1, 1u);
+  }
 }
 
 // ------------------------------------------------------------------ attention phase
 __device__ void attn_phase(const MegaParams& p, const Smem& sm, int layer, int gphase, unsigned& use0, unsigned& use1, bool& ok,
-                           const Lane& ln) {
+                           const Lane& ln, ConsState& cs) {
+  // What does not depend on this step's rows comes before the barrier: the split's key range and pages, and its
+  // first two batches when they hold only keys of earlier steps (their K / V rows are not written in this launch).
+  const int c = blockIdx.x, tid = ln.tid, warp = ln.warp, lane = ln.lane, g = ln.g, t = ln.t;
+  const bool mine = c < p.n_kv * p.nsplit && !(p.variant & 8);
+  const MegaLayer& L = p.layers[layer];
+  const int kh = c / p.nsplit, split = c % p.nsplit;
+  const int pos0 = p.ctrl[CTRL_ROW_POS], req = p.ctrl[CTRL_ROW_REQ];
+  const int ctx_max = pos0 + p.M;
+  const int total_pages = (ctx_max + 15) >> 4;
+  int key0, key1;
+  if (p.span_pages > 0) {
+    key0 = split * p.span_pages * 16;
+    key1 = min(ctx_max, (split + 1) * p.span_pages * 16);
+  } else {
+    const int pps = (total_pages + p.nsplit - 1) / p.nsplit;
+    key0 = split * pps * 16;
+    key1 = min(ctx_max, key0 + pps * 16);
+  }
+  const int nkeys = mine ? max(key1 - key0, 0) : 0;
+  const int nbatch = (nkeys + KB - 1) / KB;
+  const int* bt = p.block_table + (size_t)req * p.max_blocks + (key0 >> 4);
+  const long long row_plane = L.kv_plane * (long long)p.num_pages;
+  const uint32_t tiles = sm.attn;
+  // batch b into buffer b & 1: warp 0 issues one tiled copy per (page, K | V, low | high dims)
+  auto issue = [&](int b) {
+    const int kb0 = key0 + b * KB, nk = min(KB, key1 - kb0), buf = b & 1;
+    const int npages = (nk + 15) >> 4;
+    const uint32_t bar = sm.kvbar + 8 * buf, base = tiles + buf * KVBUF;
+    if (warp == 0) {
+      if (lane == 0) mbar_expect_tx(bar, (uint32_t)npages * 8192u);
+      __syncwarp();
+      if (lane < 16) {
+        const int pi = lane >> 2, which = lane & 3;
+        if (pi < npages) {
+          const int page = bt[((kb0 - key0) >> 4) + pi];
+          const int row = (int)(((row_plane + page) * p.n_kv + kh) * 16);
+          tma_load_2d(base + (which & 2 ? TILEB : 0) + (which & 1) * HALFB + pi * 2048, (which & 2) ? &p.v_map : &p.k_map,
+                      (which & 1) * 64, row, bar);
+        }
+      }
+    }
+    if (tid < KB && tid >= npages * 16) {   // rows of pages that are not fetched: V must be finite (P = 0 there)
+#pragma unroll
+      for (int i = 0; i < 16; ++i)
+        asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};" ::"r"(base + TILEB + (i >> 3) * HALFB + tid * 128 + 16 * (i & 7)), "r"(0) : "memory");
+    }
+  };
+  int issued = 0;
+  while (ok && issued < 2 && issued < nbatch && key0 + (issued + 1) * KB <= pos0) issue(issued++);
   if (!grid_wait(p, sm, gphase, ln.tid)) ok = false;
   const bool run = lds32v(sm.misc + 4) != 0u;   // the wait's result: the same in every consumer thread
   fence_proxy_async_all();                       // the new K / V rows were stored by other CTAs; TMA reads them next
-  const int c = blockIdx.x, tid = ln.tid, warp = ln.warp, lane = ln.lane, g = ln.g, t = ln.t;
-  if (c < p.n_kv * p.nsplit && run) {
-    const MegaLayer& L = p.layers[layer];
-    const int kh = c / p.nsplit, split = c % p.nsplit;
-    const int pos0 = p.ctrl[CTRL_ROW_POS], req = p.ctrl[CTRL_ROW_REQ];
-    const int ctx_max = pos0 + p.M;
-    const int total_pages = (ctx_max + 15) >> 4;
-    int key0, key1;
-    if (p.span_pages > 0) {
-      key0 = split * p.span_pages * 16;
-      key1 = min(ctx_max, (split + 1) * p.span_pages * 16);
-    } else {
-      const int pps = (total_pages + p.nsplit - 1) / p.nsplit;
-      key0 = split * pps * 16;
-      key1 = min(ctx_max, key0 + pps * 16);
-    }
-    const int nkeys = max(key1 - key0, 0);
-    const int nbatch = (nkeys + KB - 1) / KB;
-    const int* bt = p.block_table + (size_t)req * p.max_blocks + (key0 >> 4);
-    const long long row_plane = L.kv_plane * (long long)p.num_pages;
+  if (!run && tid == 0)                          // abandoned: the copies in flight still have to land before the CTA exits
+    for (int b = 0; b < issued; ++b) mbar_wait(sm.kvbar + 8 * (b & 1), ((b ? use1 : use0)) & 1u, ERR_MEGA_KV);
+  if (mine && run) {
     const int QR = p.M * p.gqa;
     // 16 warps = 4 groups of 16 query rows x 4 quarters of the head's 128 dims: every warp scores all keys of a batch
     // for its rows (the four quarter warps repeat that small product) and owns 32 dims of O, so no slices meet later
     const int rg = warp & 3, dq = warp >> 2;
     const bool active = rg * 16 < QR;
-    const uint32_t tiles = sm.attn;
 
     int ctx[2] = {0, 0};
     uint32_t qa[8][4];
@@ -730,36 +1041,12 @@ __device__ void attn_phase(const MegaParams& p, const Smem& sm, int layer, int g
     for (int jd = 0; jd < 4; ++jd) o[jd][0] = o[jd][1] = o[jd][2] = o[jd][3] = 0.f;
     float mx[2] = {-INFINITY, -INFINITY}, lsum[2] = {0.f, 0.f};
 
-    // batch b into buffer b & 1: warp 0 issues one tiled copy per (page, K | V, low | high dims)
-    auto issue = [&](int b) {
-      const int kb0 = key0 + b * KB, nk = min(KB, key1 - kb0), buf = b & 1;
-      const int npages = (nk + 15) >> 4;
-      const uint32_t bar = sm.kvbar + 8 * buf, base = tiles + buf * KVBUF;
-      if (warp == 0) {
-        if (lane == 0) mbar_expect_tx(bar, (uint32_t)npages * 8192u);
-        __syncwarp();
-        if (lane < 16) {
-          const int pi = lane >> 2, which = lane & 3;
-          if (pi < npages) {
-            const int page = bt[((kb0 - key0) >> 4) + pi];
-            const int row = (int)(((row_plane + page) * p.n_kv + kh) * 16);
-            tma_load_2d(base + (which & 2 ? TILEB : 0) + (which & 1) * HALFB + pi * 2048, (which & 2) ? &p.v_map : &p.k_map,
-                        (which & 1) * 64, row, bar);
-          }
-        }
-      }
-      if (tid < KB && tid >= npages * 16) {   // rows of pages that are not fetched: V must be finite (P = 0 there)
-#pragma unroll
-        for (int i = 0; i < 16; ++i)
-          asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};" ::"r"(base + TILEB + (i >> 3) * HALFB + tid * 128 + 16 * (i & 7)), "r"(0) : "memory");
-      }
-    };
-    if (nbatch > 0) issue(0);
+    if (issued == 0 && nbatch > 0) issue(issued++);
     for (int b = 0; b < nbatch; ++b) {
       const int buf = b & 1;
       cons_sync();   // batch b - 1 is consumed: its buffer may be refilled
-      if (b + 1 < nbatch) issue(b + 1);
-      if (ok) ok = __all_sync(0xffffffffu, mwait(sm.kvbar + 8 * buf, ((buf ? use1 : use0) + (unsigned)(b >> 1)) & 1u, sm.misc, ERR_MEGA_KV));
+      if (b + 1 < nbatch && issued < b + 2) issue(issued++);
+      if (ok) ok = warp_wait(sm.kvbar + 8 * buf, ((buf ? use1 : use0) + (unsigned)(b >> 1)) & 1u, sm.misc, ERR_MEGA_KV, lane);
       const int kb0 = key0 + b * KB, nk = min(KB, key1 - kb0);
       if (!ok || !active) continue;
       const uint32_t ks = tiles + buf * KVBUF, vs = ks + TILEB;
@@ -866,55 +1153,68 @@ __device__ void attn_phase(const MegaParams& p, const Smem& sm, int layer, int g
     const bool last = lds32v(sm.misc + 8) != 0u;
     if (last) {
       __threadfence();
-      const uint32_t cw = tiles, mlb = tiles + (uint32_t)(QR * p.nsplit) * 4;   // [QR][nsplit] weights; staged (m, l)
-      for (int i = tid; i < QR * p.nsplit; i += kCons) {
-        const int qr = i / p.nsplit, sp = i % p.nsplit;
-        const int m = qr / p.gqa, h = qr % p.gqa;
-        const size_t pb = ((size_t)m * p.n_q + kh * p.gqa + h) * p.nsplit + sp;
-        sts32(mlb + (uint32_t)i * 8, __float_as_uint(__ldcg(p.ml_part + pb * 2)));
-        sts32(mlb + (uint32_t)i * 8 + 4, __float_as_uint(__ldcg(p.ml_part + pb * 2 + 1)));
-      }
-      cons_sync();
-      if (tid < QR) {
-        float mm = -INFINITY;
-        for (int sp = 0; sp < p.nsplit; ++sp) mm = fmaxf(mm, __uint_as_float(lds32(mlb + (uint32_t)(tid * p.nsplit + sp) * 8)));
-        float lt = 0.f;
-        for (int sp = 0; sp < p.nsplit; ++sp) {
-          const float ms = __uint_as_float(lds32(mlb + (uint32_t)(tid * p.nsplit + sp) * 8));
-          const float cc = ms == -INFINITY ? 0.f : exp2f(ms - mm);
-          lt = fmaf(__uint_as_float(lds32(mlb + (uint32_t)(tid * p.nsplit + sp) * 8 + 4)), cc, lt);
-          sts32(cw + (uint32_t)(tid * p.nsplit + sp) * 4, __float_as_uint(cc));
-        }
-        const float inv = lt > 0.f ? 1.f / lt : 0.f;
-        for (int sp = 0; sp < p.nsplit; ++sp) {
-          const uint32_t a = cw + (uint32_t)(tid * p.nsplit + sp) * 4;
-          sts32(a, __float_as_uint(__uint_as_float(lds32(a)) * inv));
-        }
-      }
-      cons_sync();
+      // Eight lanes per (row, 8-vector): lane `sub` folds splits sub, sub + 8, ... in that order with a running
+      // maximum (every load independent of the others: one trip to L2), then the eight meet in a fixed butterfly.
+      const int sub = lane & 7, iw = lane >> 3;
       const int items = QR * 16;
+      for (int it0 = warp * 4; it0 < items; it0 += kConsWarps * 4) {
+        const int it = it0 + iw;
+        const bool act = it < items;
+        const int qr = act ? it >> 4 : 0, v = it & 15;
+        const int m = qr / p.gqa, h = qr % p.gqa;
+        const size_t pb = ((size_t)m * p.n_q + kh * p.gqa + h) * p.nsplit;
+        float mm = -INFINITY, lt = 0.f, y[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) y[i] = 0.f;
+        if (act) {
+#pragma unroll 4
+          for (int sp = sub; sp < p.nsplit; sp += 8) {
+            const float2 ml = __ldcg(reinterpret_cast<const float2*>(p.ml_part + (pb + sp) * 2));
+            const float4 a = __ldcg(reinterpret_cast<const float4*>(p.o_part + (pb + sp) * D + 8 * v));
+            const float4 bq = __ldcg(reinterpret_cast<const float4*>(p.o_part + (pb + sp) * D + 8 * v + 4));
+            const float mnew = fmaxf(mm, ml.x);
+            const float c0 = mm == -INFINITY ? 0.f : exp2f(mm - mnew);
+            const float c1 = ml.x == -INFINITY ? 0.f : exp2f(ml.x - mnew);
+            lt = lt * c0 + ml.y * c1;
+            y[0] = y[0] * c0 + a.x * c1; y[1] = y[1] * c0 + a.y * c1; y[2] = y[2] * c0 + a.z * c1; y[3] = y[3] * c0 + a.w * c1;
+            y[4] = y[4] * c0 + bq.x * c1; y[5] = y[5] * c0 + bq.y * c1; y[6] = y[6] * c0 + bq.z * c1; y[7] = y[7] * c0 + bq.w * c1;
+            mm = mnew;
+          }
+        }
+        float mall = mm;
+        mall = fmaxf(mall, __shfl_xor_sync(0xffffffffu, mall, 1));
+        mall = fmaxf(mall, __shfl_xor_sync(0xffffffffu, mall, 2));
+        mall = fmaxf(mall, __shfl_xor_sync(0xffffffffu, mall, 4));
+        const float cc = mm == -INFINITY ? 0.f : exp2f(mm - mall);
+        lt *= cc;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) y[i] *= cc;
+#pragma unroll
+        for (int d = 1; d < 8; d <<= 1) {
+          lt += __shfl_xor_sync(0xffffffffu, lt, d);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) y[i] += __shfl_xor_sync(0xffffffffu, y[i], d);
+        }
+        if (act && sub == 0) {
+          const float inv = lt > 0.f ? 1.f / lt : 0.f;
+          const uint32_t dst = tiles + (uint32_t)(qr * 128 + 8 * v) * 4;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) sts_f32(dst + 4 * i, y[i] * inv);
+        }
+      }
+      cons_sync();
       for (int it0 = warp * 32; it0 < items; it0 += kCons) {
         const int it = it0 + lane;
         const bool act = it < items;
         const int qr = act ? it >> 4 : 0, v = it & 15;
         const int m = qr / p.gqa, h = qr % p.gqa;
-        const float* src = p.o_part + (((size_t)m * p.n_q + kh * p.gqa + h) * p.nsplit) * D + 8 * v;
         float y[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) y[i] = 0.f;
-        if (act) {
-#pragma unroll 4
-          for (int sp = 0; sp < p.nsplit; ++sp) {
-            const float cc = __uint_as_float(lds32(cw + (uint32_t)(qr * p.nsplit + sp) * 4));
-            const float4 a = __ldcg(reinterpret_cast<const float4*>(src + (size_t)sp * D));
-            const float4 bq = __ldcg(reinterpret_cast<const float4*>(src + (size_t)sp * D + 4));
-            y[0] = fmaf(a.x, cc, y[0]); y[1] = fmaf(a.y, cc, y[1]); y[2] = fmaf(a.z, cc, y[2]); y[3] = fmaf(a.w, cc, y[3]);
-            y[4] = fmaf(bq.x, cc, y[4]); y[5] = fmaf(bq.y, cc, y[5]); y[6] = fmaf(bq.z, cc, y[6]); y[7] = fmaf(bq.w, cc, y[7]);
-          }
-        }
+        const float4 a = lds_f4(tiles + (uint32_t)(qr * 128 + 8 * v) * 4);
+        const float4 bq = lds_f4(tiles + (uint32_t)(qr * 128 + 8 * v) * 4 + 16);
+        y[0] = a.x; y[1] = a.y; y[2] = a.z; y[3] = a.w; y[4] = bq.x; y[5] = bq.y; y[6] = bq.z; y[7] = bq.w;
 #pragma unroll
         for (int i = 0; i < 8; i += 2) {   // the attention output is a bf16 tensor, as in the launch-per-kernel form
-          const uint32_t pk = pack_bf16(y[i], y[i + 1]);
+          const uint32_t pk = act ? pack_bf16(y[i], y[i + 1]) : 0u;
           y[i] = bf16_lo(pk);
           y[i + 1] = bf16_hi(pk);
         }
@@ -927,29 +1227,49 @@ __device__ void attn_phase(const MegaParams& p, const Smem& sm, int layer, int g
   grid_arrive(p, ln.tid, gphase);
 }
 
+// The consumers and the epilogue warp of every CTA sign out; the last one puts the barrier words back for the next
+// launch (by then no CTA polls them: the activation producers are done before their consumers are).
+__device__ __forceinline__ void leave(const MegaParams& p) {
+  __threadfence();
+  const unsigned n = atomicAdd(p.bar + 2, 1u);
+  if (n == 2u * (unsigned)p.nCTA - 1u) {
+    p.bar[0] = 0u;
+    p.bar[1] = 0u;
+    p.bar[2] = 0u;
+    __threadfence();
+  }
+}
+
 // ------------------------------------------------------------------ the kernel
 __global__ void __launch_bounds__(kThreads, 1) decode_mega_kernel(const __grid_constant__ MegaParams p) {
   extern __shared__ uint8_t smem_raw[];
   Smem sm;
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   sm.attn = base;                       // 1024-aligned: the swizzle pattern repeats every 1024 bytes
-  sm.stageB = kWStage + 2 * p.rows * kXRow + 128;
+  sm.stageB = kWStage + kSB * p.rows * kXRow + kSB * 64;
   sm.fullW = base + kAttnBytes;
   sm.fullX = sm.fullW + 8 * kMaxNS;
   sm.empty = sm.fullX + 8 * kMaxNS;
   sm.kvbar = sm.empty + 8 * kMaxNS;
-  sm.misc = sm.kvbar + 16;              // [0] failed, [4] grid-wait result, [8] ticket result
-  sm.ring = (sm.misc + 16 + 127u) & ~127u;
+  sm.outfull = sm.kvbar + 16;
+  sm.outempty = sm.outfull + 16;
+  sm.misc = sm.outempty + 16;           // [0] failed, [4] grid-wait result, [8] ticket result
+  sm.out = (sm.misc + 16 + 15u) & ~15u;
+  sm.ring = (sm.out + 2u * kGroups * (uint32_t)p.M * 512u + 127u) & ~127u;
 
   const int tid = threadIdx.x;
   if (tid == 0) {
     for (int i = 0; i < p.NS; ++i) {
       mbar_init(sm.fullW + 8 * i, 1);
-      mbar_init(sm.fullX + 8 * i, 32);   // one arrival per producer lane, after its share of the copies
-      mbar_init(sm.empty + 8 * i, 8);
+      mbar_init(sm.fullX + 8 * i, 1);
+      mbar_init(sm.empty + 8 * i, kGroupWarps);
     }
     mbar_init(sm.kvbar, 1);
     mbar_init(sm.kvbar + 8, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(sm.outfull + 8 * i, kConsWarps);   // one arrival per consumer warp
+      mbar_init(sm.outempty + 8 * i, 1);
+    }
     sts32(sm.misc, 0u);
     sts32(sm.misc + 4, 0u);
     sts32(sm.misc + 8, 0u);
@@ -960,46 +1280,51 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mega_kernel(const __grid_c
   __syncthreads();
 
   if (tid >= kCons) {
-    producer(p, sm, tid - kCons);
+    const int role = (tid - kCons) >> 5, lane = tid & 31;
+    if (role == 0) {
+      if (lane == 0) w_producer(p, sm);
+    } else if (role == 1) {
+      if (lane == 0) x_producer(p, sm);
+    } else {
+      epilogue(p, sm, lane);
+      if (lane == 0) leave(p);
+    }
     return;
   }
   Lane ln;
-  ln.tid = tid; ln.warp = tid >> 5; ln.lane = tid & 31; ln.w8 = ln.warp & 7; ln.gidx = ln.warp >> 3;
+  ln.tid = tid; ln.warp = tid >> 5; ln.lane = tid & 31; ln.wq = ln.warp & (kGroupWarps - 1); ln.gidx = ln.warp / kGroupWarps;
   ln.g = ln.lane >> 2; ln.t = ln.lane & 3;
   bool ok = true;
-  int G = 0;
+  ConsState cs;
+  cs.G = 0; cs.R = 0; cs.slot = ln.gidx; cs.par = 0u;
+#ifdef B2_MEGA_PROF
+  cs.prof.start();
+#endif
   unsigned use0 = 0u, use1 = 0u;
 
   // ---- phase 0: embedding rows -> residual stream, sums of squares, quantised rows for layer 0's qkv
   if (p.n_phases > 0) {
-    if ((int)blockIdx.x < p.nbH) fold_resid(p, 1, p.layers[0].input_norm, blockIdx.x, 0, tid, true);
+    if ((int)blockIdx.x < p.nbH) fold_resid(p, 1, p.layers[0].input_norm, blockIdx.x, 0, tid, kCons, true);
     grid_arrive(p, tid, 0);
   }
   for (int layer = 0; layer < p.n_layers; ++layer) {
     const int g0 = 1 + 5 * layer;
     if (g0 >= p.n_phases) break;
-    gemv_phase<0>(p, sm, layer, g0, G, ok, ln);
+    gemv_phase<0>(p, sm, cs, ok, ln, layer);
     if (g0 + 1 >= p.n_phases) break;
-    attn_phase(p, sm, layer, g0 + 1, use0, use1, ok, ln);
+    attn_phase(p, sm, layer, g0 + 1, use0, use1, ok, ln, cs);
     if (g0 + 2 >= p.n_phases) break;
-    gemv_phase<1>(p, sm, layer, g0 + 2, G, ok, ln);
+    gemv_phase<1>(p, sm, cs, ok, ln, layer);
     if (g0 + 3 >= p.n_phases) break;
-    gemv_phase<2>(p, sm, layer, g0 + 3, G, ok, ln);
+    gemv_phase<2>(p, sm, cs, ok, ln, layer);
     if (g0 + 4 >= p.n_phases) break;
-    gemv_phase<3>(p, sm, layer, g0 + 4, G, ok, ln);
+    gemv_phase<3>(p, sm, cs, ok, ln, layer);
   }
-  // ---- the last CTA out puts the barrier words back for the next launch
+#ifdef B2_MEGA_PROF
+  if (tid == 0) cs.prof.dump(p, 2);
+#endif
   cons_sync();
-  if (tid == 0) {
-    __threadfence();
-    const unsigned n = atomicAdd(p.bar + 2, 1u);
-    if (n == (unsigned)p.nCTA - 1u) {
-      p.bar[0] = 0u;
-      p.bar[1] = 0u;
-      p.bar[2] = 0u;
-      __threadfence();
-    }
-  }
+  if (tid == 0) leave(p);
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -1030,7 +1355,7 @@ int kv_map(CUtensorMap* out, const void* ptr, uint64_t rows) {
 }
 
 struct Plan {
-  int nb[4], SG[4], T[4], maxseg[4];
+  int nb[4], SG[4], T[4], maxseg[4], KG[4];
   int rows, NS, nsplit, smem;
   long long part_floats;
   int max_nb;
@@ -1046,8 +1371,10 @@ int make_plan(Plan& pl, int nCTA, int M, int H, int n_q, int n_kv, int ffn) {
   pl.max_nb = 0;
   for (int k = 0; k < 4; ++k) {
     pl.nb[k] = N[k] / 128;
-    pl.SG[k] = Kd[k] / 128;
+    pl.KG[k] = Kd[k] / 64;
+    pl.SG[k] = (pl.KG[k] + kSB - 1) / kSB;
     pl.T[k] = pl.nb[k] * pl.SG[k];
+    if ((long long)(pl.T[k] + 1) * (nCTA + 1) >= (1ll << 31)) return -2;
     int mx = 0;
     for (int j = 0; j < pl.nb[k]; ++j) {
       const int a = stage_owner(j * pl.SG[k], nCTA, pl.T[k]), b = stage_owner((j + 1) * pl.SG[k] - 1, nCTA, pl.T[k]);
@@ -1062,11 +1389,11 @@ int make_plan(Plan& pl, int nCTA, int M, int H, int n_q, int n_kv, int ffn) {
   int rows = 1;
   while (rows < M) rows *= 2;
   pl.rows = rows;
-  const int stageB = kWStage + 2 * rows * kXRow + 128;
-  const int fixed = 1024 + kAttnBytes + 8 * kMaxNS * 3 + 16 + 16 + 128;
+  const int stageB = kWStage + kSB * rows * kXRow + kSB * 64;
+  const int fixed = 1024 + kAttnBytes + 8 * kMaxNS * 3 + 16 + 32 + 16 + 16 + 2 * kGroups * M * 512 + 128;
   int ns = (232448 - fixed) / stageB;
   if (ns > kMaxNS) ns = kMaxNS;
-  if (ns < 4) return -3;
+  if (ns < kGroups + 1) return -3;   // every consumer group can hold a stage while one more is in flight
   pl.NS = ns;
   pl.smem = fixed + ns * stageB;
   int nsplit = nCTA / n_kv;
@@ -1087,7 +1414,7 @@ extern "C" int b2_decode_mega_plan(int nCTA, int M, int H, int n_q, int n_kv, in
   for (int k = 0; k < 4; ++k) {
     int prev_end = 0;
     for (int c = 0; c < nCTA; ++c) {
-      const int s0 = (int)((long long)pl.T[k] * c / nCTA), s1 = (int)((long long)pl.T[k] * (c + 1) / nCTA);
+      const int s0 = run_begin(pl.T[k], c, nCTA), s1 = run_begin(pl.T[k], c + 1, nCTA);
       if (s0 != prev_end) return -20;
       for (int s = s0; s < s1; ++s)
         if (stage_owner(s, nCTA, pl.T[k]) != c) return -21;
@@ -1127,7 +1454,7 @@ extern "C" int b2_decode_mega(const void* layers_dev, int n_layers, int M, int H
   p.layers = reinterpret_cast<const MegaLayer*>(layers_dev);
   p.n_layers = n_layers; p.M = M; p.rows = pl.rows; p.nCTA = nCTA; p.NS = pl.NS;
   p.H = H; p.n_q = n_q; p.n_kv = n_kv; p.gqa = n_q / n_kv; p.nbH = H / 128;
-  for (int k = 0; k < 4; ++k) { p.nb[k] = pl.nb[k]; p.SG[k] = pl.SG[k]; p.T[k] = pl.T[k]; p.maxseg[k] = pl.maxseg[k]; }
+  for (int k = 0; k < 4; ++k) { p.nb[k] = pl.nb[k]; p.SG[k] = pl.SG[k]; p.T[k] = pl.T[k]; p.maxseg[k] = pl.maxseg[k]; p.KG[k] = pl.KG[k]; }
   p.ctrl = ctrl; p.block_table = block_table; p.max_blocks = max_blocks; p.num_pages = num_pages;
   p.embed = (const __nv_bfloat16*)embed; p.vocab = vocab; p.flag = flag; p.cos_t = cos_t; p.sin_t = sin_t;
   p.k_cache = (__nv_bfloat16*)k_cache; p.v_cache = (__nv_bfloat16*)v_cache;
@@ -1137,6 +1464,7 @@ extern "C" int b2_decode_mega(const void* layers_dev, int n_layers, int M, int H
   p.part = part; p.part_half = pl.part_floats; p.tickets = tickets; p.q = (__nv_bfloat16*)q; p.o_part = o_part; p.ml_part = ml_part;
   p.attn_tickets = attn_tickets; p.bar = bar; p.eps = eps; p.scale_log2 = scale * 1.4426950408889634f;
   p.nsplit = pl.nsplit; p.span_pages = span_pages; p.dbg = dbg;
+  { const char* v = getenv("B2_MEGA_VARIANT"); p.variant = v ? atoi(v) : 0; }
   const int all = 1 + 5 * n_layers;
   p.n_phases = (n_phases <= 0 || n_phases > all) ? all : n_phases;
   if (span_pages > 0 && (long long)span_pages * pl.nsplit < max_blocks) return -6;

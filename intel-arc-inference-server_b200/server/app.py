@@ -174,6 +174,9 @@ class Server:
                 self.sched.cancel(s.http_id)
                 s.finished = True
                 s.finish_reason = "cancelled"
+                if s.slot < 0:      # still waiting for a slot: no release action will come for it
+                    self.http.close(s.http_id)
+                    self.sessions.pop(s.http_id, None)
         for a in self.sched.tick():
             try:
                 self._act(a)

@@ -237,3 +237,36 @@ def test_failed_step_fails_its_request_and_the_engine_latch_is_cleared(server):
     assert state["resets"] == 1 and not state["latched"]
     st, body = post(srv.port, "/v1/completions", {"prompt": "abc", "max_tokens": 4})
     assert st == 200 and body["usage"]["completion_tokens"] == 4
+
+
+def test_client_that_leaves_while_queued_is_cleaned_up(server):
+    """A request that waits for a slot and whose client hangs up gets no release action: the tick itself must
+    drop its session and let the connection thread close the socket."""
+    import socket
+    import time
+    msgs = [{"role": "user", "content": "long"}]
+    pid = prompt_ids(msgs, enable_thinking=False)
+    srv, eng = server({pid: list(enc("x" * 400))}, max_seqs=1, step_delay=0.01)
+    body = json.dumps({"messages": msgs, "max_tokens": 300, "stream": True,
+                       "chat_template_kwargs": {"enable_thinking": False}}).encode()
+    head = (f"POST /v1/chat/completions HTTP/1.1\r\nHost: x\r\nContent-Type: application/json\r\n"
+            f"Content-Length: {len(body)}\r\n\r\n").encode()
+    busy = socket.create_connection(("127.0.0.1", srv.port))
+    busy.sendall(head + body)
+    assert busy.recv(64).startswith(b"HTTP/1.1 200")          # the only slot is taken and streaming
+    queued = socket.create_connection(("127.0.0.1", srv.port))
+    queued.sendall(head + body)
+    deadline = time.time() + 3
+    while time.time() < deadline and len(srv.sessions) < 2:
+        time.sleep(0.01)
+    assert len(srv.sessions) == 2
+    queued.close()                                             # leaves before a slot was granted
+    deadline = time.time() + 3
+    while time.time() < deadline and len(srv.sessions) > 1:
+        time.sleep(0.02)
+    assert len(srv.sessions) == 1
+    busy.close()
+    deadline = time.time() + 3
+    while time.time() < deadline and (srv.sessions or srv.http.active() > 0):
+        time.sleep(0.02)
+    assert not srv.sessions and srv.http.active() == 0
