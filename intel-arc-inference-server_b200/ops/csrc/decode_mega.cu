@@ -305,13 +305,11 @@ __device__ __forceinline__ void sum_slots8(const float* base, int nslots, size_t
 // phase g only after it has seen phase g - 1 complete (its stages' activations, or an explicit wait), which is what
 // makes the plain counter a barrier.
 __device__ __forceinline__ void grid_arrive(const MegaParams& p, int tid, int phase = -1) {
-  __threadfence();
   fence_proxy_async_all();   // this phase's generic-proxy stores are read by TMA / bulk copies of other CTAs next
   cons_sync();
   if (tid == 0) {
-    __threadfence();
     if (p.dbg && phase >= 0 && phase < 32) p.dbg[((size_t)blockIdx.x * 8 + 0) * 32 + phase] = globaltimer_ns();
-    atomicAdd(p.bar, 1u);
+    red_add_release(p.bar, 1u);   // releases the consumers' stores of the phase (ordered before it by the barrier)
   }
 }
 // Consumer-side wait until `phases` phases are complete (tid 0 polls, bounded).
@@ -365,13 +363,10 @@ struct Prof {
     for (int i = 0; i < 8; ++i) p.dbg[(size_t)p.nCTA * 256 + ((size_t)blockIdx.x * 4 + role) * 8 + i] = (unsigned long long)v[i];
   }
 };
-// stage trace of CTA 0 (SM cycle counter): [5][1024] words after the cycle sums
-#define TRACE(row, G) if (p.dbg && blockIdx.x == 0 && (G) < 1024) p.dbg[(size_t)p.nCTA * 288 + (row) * 1024 + (G)] = (unsigned long long)clock64();
 #define PROF_DECL Prof prof; prof.start();
 #define PROF_MARK(k) prof.mark(k);
 #define PROF_DUMP(role) prof.dump(p, role);
 #else
-#define TRACE(row, G)
 #define PROF_DECL
 #define PROF_MARK(k)
 #define PROF_DUMP(role)
@@ -410,7 +405,8 @@ __device__ __forceinline__ bool cursor_next(const MegaParams& p, Cursor& c) {
 
 // One thread polls the arrival counter until `need` arrivals are in (phases 0 .. need / nCTA - 1 complete).
 // Returns the counter, or 0xffffffff when the launch is being abandoned or the bound ran out.
-__device__ __forceinline__ unsigned poll_arrivals(const MegaParams& p, const Smem& sm, unsigned need, unsigned code, int phase) {
+__device__ __forceinline__ unsigned poll_arrivals(const MegaParams& p, const Smem& sm, unsigned need, unsigned code, int phase,
+                                                  unsigned nap = 64) {
   unsigned v = ld_acquire_gpu(p.bar);
   if (v >= need) return v;
   const long long t0 = clock64();
@@ -419,7 +415,7 @@ __device__ __forceinline__ unsigned poll_arrivals(const MegaParams& p, const Sme
     v = ld_acquire_gpu(p.bar);
     if (v >= need) return v;
     if (++spins > 16) {
-      __nanosleep(64);
+      __nanosleep(nap);
       if ((spins & 15) == 0) {
         const bool stale = clock64() - t0 > 3000000000ll;
         if (stale || lds32v(sm.misc) != 0u || ld_acquire_gpu(p.bar + 1) != 0u) {
@@ -872,7 +868,7 @@ __device__ void epilogue(const MegaParams& p, const Smem& sm, const int lane) {
           // 1 / rms of the rows: their sums of squares are final once the phase before is complete.  This warp
           // has nothing else to do until the consumers hand their first run over, so it meets the barrier itself.
           unsigned v = 0;
-          if (lane == 0) v = poll_arrivals(p, sm, (unsigned)gphase * (unsigned)p.nCTA, ERR_MEGA_GRID, gphase);
+          if (lane == 0) v = poll_arrivals(p, sm, (unsigned)gphase * (unsigned)p.nCTA, ERR_MEGA_GRID, gphase, 400);   // in no hurry
           if (__shfl_sync(0xffffffffu, v, 0) == 0xffffffffu) {
             ok = false;
             break;
@@ -1007,33 +1003,53 @@ __device__ void attn_phase(const MegaParams& p, const Smem& sm, int layer, int g
         asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};" ::"r"(base + TILEB + (i >> 3) * HALFB + tid * 128 + 16 * (i & 7)), "r"(0) : "memory");
     }
   };
+  const bool stamp = p.dbg != nullptr && tid == 0 && gphase < 32;
+  unsigned long long* stamps = p.dbg + ((size_t)blockIdx.x * 8) * 32 + gphase;   // rows 1..6 of this phase
+  if (stamp) stamps[1 * 32] = globaltimer_ns();
   int issued = 0;
   while (ok && issued < 2 && issued < nbatch && key0 + (issued + 1) * KB <= pos0) issue(issued++);
   if (!grid_wait(p, sm, gphase, ln.tid)) ok = false;
+  if (stamp) stamps[2 * 32] = globaltimer_ns();
   const bool run = lds32v(sm.misc + 4) != 0u;   // the wait's result: the same in every consumer thread
   fence_proxy_async_all();                       // the new K / V rows were stored by other CTAs; TMA reads them next
   if (!run && tid == 0)                          // abandoned: the copies in flight still have to land before the CTA exits
     for (int b = 0; b < issued; ++b) mbar_wait(sm.kvbar + 8 * (b & 1), ((b ? use1 : use0)) & 1u, ERR_MEGA_KV);
   if (mine && run) {
     const int QR = p.M * p.gqa;
-    // 16 warps = 4 groups of 16 query rows x 4 quarters of the head's 128 dims: every warp scores all keys of a batch
-    // for its rows (the four quarter warps repeat that small product) and owns 32 dims of O, so no slices meet later
-    const int rg = warp & 3, dq = warp >> 2;
-    const bool active = rg * 16 < QR;
+    // 16 warps = (row groups x key slices) x 4 quarters of the head's 128 dims.  rgN groups of 16 query rows; with
+    // fewer than four of them the 64 keys of a batch are cut into kqN slices, one per warp, and the slices meet in
+    // shared memory after the last batch (slice order).  Every warp scores its keys for its rows (the four quarter
+    // warps repeat that small product) and owns 32 dims of O.
+    const int rgN = (QR + 15) >> 4;
+    const int kqN = rgN == 1 ? 4 : (rgN == 2 ? 2 : 1);
+    const int w4 = warp & 3, dq = warp >> 2;
+    const int rg = rgN == 1 ? 0 : (rgN == 2 ? (w4 & 1) : w4);
+    const int kq = rgN == 1 ? w4 : (rgN == 2 ? (w4 >> 1) : 0);
+    const bool active = rg < rgN;
+    const int kslice = KB / kqN;
 
+    // The head group's query rows, once per CTA: 16-byte loads into the (idle) hand-off buffer, rows 272 bytes apart
+    // (conflict-free fragment reads), then every warp takes its A fragments from there.
+    constexpr uint32_t kQRow = 272;
+    if (tid < QR * 16) {
+      const int qr = tid >> 4, c16 = tid & 15;
+      const int m = qr / p.gqa, h = qr % p.gqa;
+      const uint4 v = __ldcg(reinterpret_cast<const uint4*>(p.q + (size_t)m * p.n_q * D + (size_t)(kh * p.gqa + h) * D + 8 * c16));
+      asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(sm.out + qr * kQRow + c16 * 16), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+    }
+    cons_sync();
     int ctx[2] = {0, 0};
     uint32_t qa[8][4];
 #pragma unroll
     for (int hf = 0; hf < 2; ++hf) {
       const int qr = rg * 16 + g + 8 * hf;
-      const bool okr = qr < QR;
-      const int m = okr ? qr / p.gqa : 0, h = okr ? qr % p.gqa : 0;
-      ctx[hf] = okr ? pos0 + m + 1 : 0;
-      const __nv_bfloat16* qp = p.q + (size_t)m * p.n_q * D + (size_t)(kh * p.gqa + h) * D;
+      const bool okr = active && qr < QR;
+      ctx[hf] = okr ? pos0 + qr / p.gqa + 1 : 0;
+      const uint32_t qs = sm.out + (okr ? qr : 0) * kQRow + 4 * t;
 #pragma unroll
       for (int kk = 0; kk < 8; ++kk) {
-        qa[kk][hf] = okr ? __ldcg(reinterpret_cast<const unsigned int*>(qp + 16 * kk + 2 * t)) : 0u;
-        qa[kk][2 + hf] = okr ? __ldcg(reinterpret_cast<const unsigned int*>(qp + 16 * kk + 8 + 2 * t)) : 0u;
+        qa[kk][hf] = okr ? lds32(qs + 32 * kk) : 0u;
+        qa[kk][2 + hf] = okr ? lds32(qs + 32 * kk + 16) : 0u;
       }
     }
     float o[4][4];
@@ -1047,14 +1063,16 @@ __device__ void attn_phase(const MegaParams& p, const Smem& sm, int layer, int g
       cons_sync();   // batch b - 1 is consumed: its buffer may be refilled
       if (b + 1 < nbatch && issued < b + 2) issue(issued++);
       if (ok) ok = warp_wait(sm.kvbar + 8 * buf, ((buf ? use1 : use0) + (unsigned)(b >> 1)) & 1u, sm.misc, ERR_MEGA_KV, lane);
+      if (stamp && b == 0) stamps[3 * 32] = globaltimer_ns();
       const int kb0 = key0 + b * KB, nk = min(KB, key1 - kb0);
       if (!ok || !active) continue;
       const uint32_t ks = tiles + buf * KVBUF, vs = ks + TILEB;
+      const int kend = min(nk, (kq + 1) * kslice);
 #pragma unroll 1
-      for (int kofs = 0; kofs < nk; kofs += 32) {
-        float s[4][4];
+      for (int kofs = kq * kslice; kofs < kend; kofs += 16) {
+        float s[2][4];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
+        for (int j = 0; j < 2; ++j) {
           s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
 #pragma unroll
           for (int kk = 0; kk < 8; kk += 2) {
@@ -1066,7 +1084,7 @@ __device__ void attn_phase(const MegaParams& p, const Smem& sm, int layer, int g
         }
         float mnew[2] = {mx[0], mx[1]};
 #pragma unroll
-        for (int j = 0; j < 4; ++j)
+        for (int j = 0; j < 2; ++j)
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
             const int key = kb0 + kofs + 8 * j + 2 * t + (e & 1);
@@ -1092,7 +1110,7 @@ __device__ void attn_phase(const MegaParams& p, const Smem& sm, int layer, int g
           o[jd][0] *= corr[0]; o[jd][1] *= corr[0]; o[jd][2] *= corr[1]; o[jd][3] *= corr[1];
         }
 #pragma unroll
-        for (int j = 0; j < 4; ++j)
+        for (int j = 0; j < 2; ++j)
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
             const int hf = e >> 1;
@@ -1100,21 +1118,19 @@ __device__ void attn_phase(const MegaParams& p, const Smem& sm, int layer, int g
             s[j][e] = pe;
             lsum[hf] += pe;
           }
+        const uint32_t pa0 = pack_bf16(s[0][0], s[0][1]), pa1 = pack_bf16(s[0][2], s[0][3]);
+        const uint32_t pa2 = pack_bf16(s[1][0], s[1][1]), pa3 = pack_bf16(s[1][2], s[1][3]);
 #pragma unroll
-        for (int kk = 0; kk < 2; ++kk) {
-          const uint32_t pa0 = pack_bf16(s[2 * kk][0], s[2 * kk][1]), pa1 = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
-          const uint32_t pa2 = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]), pa3 = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
-#pragma unroll
-          for (int jd = 0; jd < 4; jd += 2) {
-            uint32_t b0, b1, b2, b3;
-            const int mi = lane >> 3;
-            ldsm_x4_trans(vs + tile_off(kofs + 16 * kk + 8 * (mi & 1) + (lane & 7), 32 * dq + 8 * (jd + (mi >> 1))), b0, b1, b2, b3);
-            mma_bf16_16816(o[jd], pa0, pa1, pa2, pa3, b0, b1);
-            mma_bf16_16816(o[jd + 1], pa0, pa1, pa2, pa3, b2, b3);
-          }
+        for (int jd = 0; jd < 4; jd += 2) {
+          uint32_t b0, b1, b2, b3;
+          const int mi = lane >> 3;
+          ldsm_x4_trans(vs + tile_off(kofs + 8 * (mi & 1) + (lane & 7), 32 * dq + 8 * (jd + (mi >> 1))), b0, b1, b2, b3);
+          mma_bf16_16816(o[jd], pa0, pa1, pa2, pa3, b0, b1);
+          mma_bf16_16816(o[jd + 1], pa0, pa1, pa2, pa3, b2, b3);
         }
       }
     }
+    if (stamp) stamps[4 * 32] = globaltimer_ns();
     use0 += (unsigned)((nbatch + 1) >> 1);   // batch b used buffer b & 1: the barriers' phase parities follow these counts
     use1 += (unsigned)(nbatch >> 1);
 #pragma unroll
@@ -1122,8 +1138,60 @@ __device__ void attn_phase(const MegaParams& p, const Smem& sm, int layer, int g
       lsum[hf] += __shfl_xor_sync(0xffffffffu, lsum[hf], 1);
       lsum[hf] += __shfl_xor_sync(0xffffffffu, lsum[hf], 2);
     }
+    if (kqN > 1) {
+      // ---- the key slices of a row group meet: [slice][row][128] sums and [slice][row] (max, sum), slice order
+      const int R16 = rgN * 16;
+      const uint32_t oS = tiles, mlS = tiles + (uint32_t)(kqN * R16) * 512u;
+      cons_sync();   // every warp is done with the K / V tiles
+      if (active) {
+#pragma unroll
+        for (int hf = 0; hf < 2; ++hf) {
+          const int r = rg * 16 + g + 8 * hf;
+          const uint32_t ob = oS + (uint32_t)((kq * R16 + r) * 128 + 32 * dq + 2 * t) * 4;
+#pragma unroll
+          for (int jd = 0; jd < 4; ++jd) {
+            sts_f32(ob + 32 * jd, o[jd][2 * hf]);
+            sts_f32(ob + 32 * jd + 4, o[jd][2 * hf + 1]);
+          }
+          if (t == 0 && dq == 0) {
+            sts_f32(mlS + (uint32_t)(kq * R16 + r) * 8, mx[hf]);
+            sts_f32(mlS + (uint32_t)(kq * R16 + r) * 8 + 4, lsum[hf]);
+          }
+        }
+      }
+      cons_sync();
+      if (active && kq == 0) {
+#pragma unroll
+        for (int hf = 0; hf < 2; ++hf) {
+          const int r = rg * 16 + g + 8 * hf;
+          float mm = -INFINITY;
+          for (int k2 = 0; k2 < kqN; ++k2) mm = fmaxf(mm, __uint_as_float(lds32(mlS + (uint32_t)(k2 * R16 + r) * 8)));
+          float lt = 0.f, acc2[4][2];
+#pragma unroll
+          for (int jd = 0; jd < 4; ++jd) acc2[jd][0] = acc2[jd][1] = 0.f;
+          for (int k2 = 0; k2 < kqN; ++k2) {
+            const float mk = __uint_as_float(lds32(mlS + (uint32_t)(k2 * R16 + r) * 8));
+            const float wk = mk == -INFINITY ? 0.f : exp2f(mk - mm);
+            lt = fmaf(__uint_as_float(lds32(mlS + (uint32_t)(k2 * R16 + r) * 8 + 4)), wk, lt);
+            const uint32_t ob = oS + (uint32_t)((k2 * R16 + r) * 128 + 32 * dq + 2 * t) * 4;
+#pragma unroll
+            for (int jd = 0; jd < 4; ++jd) {
+              acc2[jd][0] = fmaf(__uint_as_float(lds32(ob + 32 * jd)), wk, acc2[jd][0]);
+              acc2[jd][1] = fmaf(__uint_as_float(lds32(ob + 32 * jd + 4)), wk, acc2[jd][1]);
+            }
+          }
+          mx[hf] = mm;
+          lsum[hf] = lt;
+#pragma unroll
+          for (int jd = 0; jd < 4; ++jd) {
+            o[jd][2 * hf] = acc2[jd][0];
+            o[jd][2 * hf + 1] = acc2[jd][1];
+          }
+        }
+      }
+    }
     // ---- this split's partials: unnormalised O against the running maximum, (max, sum)
-    if (active) {
+    if (active && kq == 0) {
 #pragma unroll
       for (int hf = 0; hf < 2; ++hf) {
         const int qr = rg * 16 + g + 8 * hf;
@@ -1141,23 +1209,22 @@ __device__ void attn_phase(const MegaParams& p, const Smem& sm, int layer, int g
       }
     }
     // ---- the last split CTA of this KV head merges all splits in split order and quantises the o-proj input
-    __threadfence();
     cons_sync();
     if (tid == 0) {
-      const int tk = atomicAdd(&p.attn_tickets[kh], 1);
+      const int tk = atom_add_acq_rel(&p.attn_tickets[kh], 1);   // releases the CTA's stores (ordered by the barrier)
       const int last = tk == p.nsplit - 1;
       if (last) p.attn_tickets[kh] = 0;
       sts32(sm.misc + 8, (uint32_t)last);
     }
     cons_sync();
     const bool last = lds32v(sm.misc + 8) != 0u;
+    if (stamp) stamps[5 * 32] = globaltimer_ns();
     if (last) {
-      __threadfence();
-      // Eight lanes per (row, 8-vector): lane `sub` folds splits sub, sub + 8, ... in that order with a running
-      // maximum (every load independent of the others: one trip to L2), then the eight meet in a fixed butterfly.
-      const int sub = lane & 7, iw = lane >> 3;
+      // Four lanes per (row, 8-vector): lane `sub` folds splits sub, sub + 4, ... in that order with a running
+      // maximum (every load independent of the others: one trip to L2), then the four meet in a fixed butterfly.
+      const int sub = lane & 3, iw = lane >> 2;
       const int items = QR * 16;
-      for (int it0 = warp * 4; it0 < items; it0 += kConsWarps * 4) {
+      for (int it0 = warp * 8; it0 < items; it0 += kConsWarps * 8) {
         const int it = it0 + iw;
         const bool act = it < items;
         const int qr = act ? it >> 4 : 0, v = it & 15;
@@ -1167,8 +1234,8 @@ __device__ void attn_phase(const MegaParams& p, const Smem& sm, int layer, int g
 #pragma unroll
         for (int i = 0; i < 8; ++i) y[i] = 0.f;
         if (act) {
-#pragma unroll 4
-          for (int sp = sub; sp < p.nsplit; sp += 8) {
+#pragma unroll 5
+          for (int sp = sub; sp < p.nsplit; sp += 4) {
             const float2 ml = __ldcg(reinterpret_cast<const float2*>(p.ml_part + (pb + sp) * 2));
             const float4 a = __ldcg(reinterpret_cast<const float4*>(p.o_part + (pb + sp) * D + 8 * v));
             const float4 bq = __ldcg(reinterpret_cast<const float4*>(p.o_part + (pb + sp) * D + 8 * v + 4));
@@ -1184,13 +1251,12 @@ __device__ void attn_phase(const MegaParams& p, const Smem& sm, int layer, int g
         float mall = mm;
         mall = fmaxf(mall, __shfl_xor_sync(0xffffffffu, mall, 1));
         mall = fmaxf(mall, __shfl_xor_sync(0xffffffffu, mall, 2));
-        mall = fmaxf(mall, __shfl_xor_sync(0xffffffffu, mall, 4));
         const float cc = mm == -INFINITY ? 0.f : exp2f(mm - mall);
         lt *= cc;
 #pragma unroll
         for (int i = 0; i < 8; ++i) y[i] *= cc;
 #pragma unroll
-        for (int d = 1; d < 8; d <<= 1) {
+        for (int d = 1; d < 4; d <<= 1) {
           lt += __shfl_xor_sync(0xffffffffu, lt, d);
 #pragma unroll
           for (int i = 0; i < 8; ++i) y[i] += __shfl_xor_sync(0xffffffffu, y[i], d);
@@ -1223,6 +1289,7 @@ __device__ void attn_phase(const MegaParams& p, const Smem& sm, int layer, int g
       }
     }
     cons_sync();
+    if (stamp) stamps[6 * 32] = globaltimer_ns() | (last ? 1ull : 0ull);
   }
   grid_arrive(p, ln.tid, gphase);
 }

@@ -37,6 +37,7 @@ def _setup(m_rows, prompt_len=200, graphs=False):
     prompt = torch.randint(0, cfg.vocab, (prompt_len,), generator=g)
     mega = Engine(wc, max_seqs=1, max_len=1024, use_graphs=graphs)
     plain = Engine(wc, max_seqs=1, max_len=1024, use_graphs=graphs)
+    mega.model.use_mega = True       # off by default
     plain.model.use_mega = False
     return cfg, w, wc, prompt, mega, plain, g
 
