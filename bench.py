@@ -101,12 +101,12 @@ def main():
     ap.add_argument("--model", default="dense-27b")
     ap.add_argument("--depth", type=int, default=4096, help="context length the decode steps run at")
     ap.add_argument("--prefill-len", type=int, default=4096)
-    ap.add_argument("--what", default="all", help="decode | prefill | moe | spec | prefix | hybrid | tp | ep | all")
+    ap.add_argument("--what", default="all", help="decode | prefill | prefill32k | moe | w4 | spec | spec65k | batch32k | prefix | hybrid | tp | ep | replica | all")
     ap.add_argument("--kv-cache", default="bf16")
     ap.add_argument("--int8-head", action="store_true")
     ap.add_argument("--prefill-backend", default="auto")
     ap.add_argument("--parallel", default="replica", help="replica | tp (N > 1)")
-    ap.add_argument("--extras-budget-s", type=float, default=300.0, help="no further extra starts after this many seconds")
+    ap.add_argument("--extras-budget-s", type=float, default=420.0, help="no further extra starts after this many seconds")
     ap.add_argument("--windows", type=int, default=5, help="timed windows of --steps steps; the median window is reported")
     ap.add_argument("--tp-rows", type=int, default=8, help="concurrent requests of the multi-GPU decode headline")
     args = ap.parse_args()
@@ -203,6 +203,12 @@ def main():
     if args.what in ("all", "moe") and one_gpu_sections:
         extra["moe_prefill"] = run_prefill_bench(args, barrier, model="moe-35b-a3b", backend=args.prefill_backend)
         release()
+    if world == 1 and args.what in ("all", "prefill", "moe", "w4"):
+        # the prompt pass that keeps ONLY the int4 weights resident: the GEMM expands W4B blocks inside its shared-memory tiles
+        if args.what != "moe":
+            guarded("prefill_w4", lambda: run_prefill_bench(args, barrier, model=args.model, backend="w4"))
+        if args.what != "prefill":
+            guarded("moe_prefill_w4", lambda: run_prefill_bench(args, barrier, model="moe-35b-a3b", backend="w4"))
 
     def load_peaks():
         pk = os.path.join(os.path.dirname(os.path.abspath(__file__)), "MEASURED_PEAKS.json")
@@ -254,6 +260,9 @@ def main():
         from b200serve.parallel import ep_check as EPC
         out = {"world": world, "self_check_small_moe": EPC.self_check(preset("small-moe"))}
         out.update(EP.bench_prefill(preset("moe-35b-a3b"), args.prefill_len))
+        for total in (16384, 131072):     # the MoE configuration's prompt sizes, as totals over the group
+            r = EP.bench_prefill(preset("moe-35b-a3b"), total // world, modes=("fused",), reps=2)
+            out[f"prefill_fused_total_{total}"] = r["prefill_fused"]
         return out
 
     if world > 1 and args.what in ("all", "tp", "decode"):
@@ -275,6 +284,14 @@ def main():
     if args.what == "spec" or (args.what == "all" and world == 1):
         from b200serve.utils.benchlib import run_spec_bench
         guarded("spec_forced_accept", lambda: run_spec_bench(args, barrier))
+    if args.what == "spec65k" or (args.what == "all" and world == 1):
+        from b200serve.utils.benchlib import run_spec_bench
+        # the same loop behind a 65,536-token context (its prompt pass runs first, draft heads included)
+        guarded("spec_after_65536", lambda: run_spec_bench(args, barrier, iters=8, depth=65536,
+                                                           cases=(("mtp", 3, (3,), 0), ("dflash", 7, (7,), 0))))
+    if args.what == "batch32k" or (args.what == "all" and world == 1):
+        from b200serve.utils.benchlib import run_batch_after_long_prompt
+        guarded("decode_8req_after_32k_int8kv", lambda: run_batch_after_long_prompt(args, barrier))
     if args.what == "prefix" or (args.what == "all" and world == 1):
         from b200serve.utils.benchlib import run_prefix_bench
         # every rank pins its own host store: a quarter of the prefix when several ranks share one host

@@ -110,7 +110,7 @@ def run_prefill_bench(args, barrier, model: str, backend: str, n: int = 0, warm:
                        "parallelism": "replica", "l2": "weights larger than L2"}}
 
 
-def run_spec_bench(args, barrier, iters: int = 12) -> dict:
+def run_spec_bench(args, barrier, iters: int = 12, depth: int = 0, cases=None) -> dict:
     """Draft-and-verify iterations on the 27B shape with FORCED acceptance lengths, so that the step time does
     not depend on what random-init heads happen to propose: an MTP head (1 layer, draft depth 3) and a
     DFlash-style block drafter (2 layers, 7 drafts in one block pass), each verified in one trunk step of
@@ -122,11 +122,11 @@ def run_spec_bench(args, barrier, iters: int = 12) -> dict:
     cfg = dataclasses.replace(preset(args.model), mtp_layers=1)
     dev = torch.device("cuda", torch.cuda.current_device())
     weights = random_weights(cfg, device=dev, seed=0, exact=False)
-    depth = min(args.depth, 4096)
-    out = {}
+    depth = depth or min(args.depth, 4096)     # a real prompt pass of this many tokens comes first (draft heads included)
+    out = {"depth": depth}
     g = torch.Generator().manual_seed(0)
     ids = torch.randint(0, cfg.vocab - 1, (depth,), generator=g).tolist()
-    for kind, k, accepts, dv in (("mtp", 3, (0, 3), 0), ("mtp", 3, (3,), 32768), ("dflash", 7, (0, 3, 7), 0)):
+    for kind, k, accepts, dv in (cases or (("mtp", 3, (0, 3), 0), ("mtp", 3, (3,), 32768), ("dflash", 7, (0, 3, 7), 0))):
         eng = Engine(weights, max_seqs=1, max_len=depth + 64 * (iters + 4) + 64, extra_kv_layers=2)
         ad = SpecAdapter(EngineAdapter(eng), kind, k, draft_vocab=dv)
         pending = ad.prefill(0, ids)
@@ -238,3 +238,40 @@ def run_hybrid_bench(args, barrier) -> dict:
                        "achieved_GBps": nbytes / (ms / 1e3) / 1e9},
             "prefill": {"ms": pf_ms, "tokens": n, "tokens_per_s": n / pf_ms * 1e3,
                         "backend": eng._prefill.backend if eng._prefill is not None else "rows"}}
+
+
+def run_batch_after_long_prompt(args, barrier, requests: int = 8, prompt: int = 32768, new_tokens: int = 256,
+                                kv_dtype: str = "int8") -> dict:
+    """The 8-request serving case of the 27B configuration on ONE GPU: every request ingests a ``prompt``-token
+    context (int8 KV cache), then all of them decode ``new_tokens`` tokens together, one step of ``requests`` rows per
+    token.  Prompt tokens/s over all requests and decode tokens/s of the batch (CUDA events around each part)."""
+    cfg = preset(args.model)
+    dev = torch.device("cuda", torch.cuda.current_device())
+    weights = random_weights(cfg, device=dev, seed=0, exact=False)
+    eng = Engine(weights, max_seqs=requests, max_len=prompt + new_tokens + 64, kv_dtype=kv_dtype,
+                 prefill_backend="int8" if kv_dtype == "int8" else args.prefill_backend)
+    g = torch.Generator().manual_seed(5)
+    prompts = [torch.randint(0, cfg.vocab, (prompt,), generator=g).tolist() for _ in range(requests)]
+    e = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+    barrier()
+    e[0].record()
+    toks = [eng.prefill(slot, prompts[slot]) for slot in range(requests)]
+    e[1].record()
+    from ..runtime.engine import Row
+    for _ in range(3):      # capture the 8-row step before the timed part
+        rows = [Row(slot, eng.seq_len[slot], toks[slot]) for slot in range(requests)]
+        toks = eng.forward_rows(rows)
+    torch.cuda.synchronize()
+    e[2].record()
+    for _ in range(new_tokens - 3):
+        rows = [Row(slot, eng.seq_len[slot], toks[slot]) for slot in range(requests)]
+        toks = eng.forward_rows(rows)
+    e[3].record()
+    torch.cuda.synchronize()
+    K.check_status()
+    pms, dms = e[0].elapsed_time(e[1]), e[2].elapsed_time(e[3])
+    steps = new_tokens - 3
+    return {"requests": requests, "prompt_tokens_each": prompt, "new_tokens_each": new_tokens, "kv_cache": kv_dtype,
+            "prompt_ms": pms, "prompt_tokens_per_s": requests * prompt / (pms / 1e3),
+            "decode_ms_per_step": dms / steps, "decode_tokens_per_s_total": requests * steps / (dms / 1e3),
+            "note": "every step's rows go host -> device and its tokens device -> host (the engine's public call)"}
