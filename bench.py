@@ -260,6 +260,9 @@ def main():
         from b200serve.parallel import ep_check as EPC
         out = {"world": world, "self_check_small_moe": EPC.self_check(preset("small-moe"))}
         out.update(EP.bench_prefill(preset("moe-35b-a3b"), args.prefill_len))
+        # batched decode with the experts spread over the ranks: 16 requests over the group (the MoE configuration's batch)
+        out["decode_batch16"] = EP.bench_decode_rows(preset("moe-35b-a3b"), max(16 // world, 1), args.depth,
+                                                     min(args.steps, 32), max(args.warmup, 3))
         for total in (16384, 131072):     # the MoE configuration's prompt sizes, as totals over the group
             r = EP.bench_prefill(preset("moe-35b-a3b"), total // world, modes=("fused",), reps=2)
             out[f"prefill_fused_total_{total}"] = r["prefill_fused"]

@@ -170,6 +170,7 @@ class DecoderModel:
         # step against 5.1 ms for the launch-per-linear walk, whose several CTAs per SM hide the latency of the
         # fold / barrier chain between two linears better than one resident CTA per SM does
         self.use_mega = os.environ.get("B2_MEGA", "0") == "1"
+        self.ep = None      # parallel.ep.EpMoe with the row form enabled: MoE layers of a decode step go through it
         self.mega_cooperative = os.environ.get("B2_MEGA_COOP", "1") != "0"
         self._mega_bufs = {}
         self._mega_tables = {}
@@ -356,6 +357,7 @@ class DecoderModel:
         cfg, b = self.cfg, self.buf
         h = cfg.hidden
         pend = None
+        embedded = False
         if self.fused and resid_ready and all(lw.gate_up is not None and lw.gdn is None for lw in layers) and h % 128 == 0:
             for i, lw in enumerate(layers):
                 self.dense_layer_fused(lw, kv_layer0 + i, m, ctrl, block_table, max_blocks, kv, x_ready=False)
@@ -376,7 +378,8 @@ class DecoderModel:
             raise NotImplementedError("tensor parallel decode covers dense models whose hidden size is a multiple of 128")
         for i, lw in enumerate(layers):
             if pend is None:
-                if first_from_embed:
+                if first_from_embed and not embedded:
+                    embedded = True
                     K.resid_norm(0, m, h, lw.input_norm, cfg.rms_eps, b.resid, b.x, embed=self.w.embed, ctrl=ctrl,
                                  vocab=cfg.vocab, flag=b.flag)
                 else:   # resid already holds the layer input
@@ -393,11 +396,16 @@ class DecoderModel:
                          part_slice=m * h, splits=so)
             if lw.gate_up is not None:
                 pend = self.ffn_block(lw, m)
+            elif self.ep is not None:
+                # experts spread over the ranks: the block adds its result to the residual rows itself
+                self.ep.block_rows(lw, m, b.x, b.resid)
+                pend = None
+                continue
             else:
                 from . import moe as _moe
                 pend = _moe.moe_block_rows(self, lw, m)
             pend = self._nccl_reduce(pend[0], pend[1], m)
-        return pend
+        return pend if pend is not None else (None, 0)
 
     def _nccl_reduce(self, part, splits: int, m: int):
         """Comparison path: sum the split slices, all-reduce the ranks' partial sums with NCCL."""

@@ -173,6 +173,107 @@ __global__ void ep_wait_all_kernel(Wire w, int epoch) {
   pdl_launch_dependents();
 }
 
+// ---------------------------------------------------------------- decode rows on the experts' owner
+// A decode step sends a handful of rows per expert, so the owner runs the batched W4 GEMV (one row against one
+// expert's int4 weights, gemv_w4.cu) instead of a grouped GEMM over 128-row blocks.  The receive buffer is expert-
+// sorted with every expert padded to whole blocks; ep_rows_gather waits (bounded) for each block's rows, packs
+// them into consecutive batches and notes every batch's expert and (source rank, slot).  Batches past the last row
+// get expert -1, which the GEMV skips.  ep_rows_return sums a batch's split-K slices in slice order and stores the
+// bf16 row into the source rank's return buffer, where the usual slot-order combine finds it.
+struct EpRowsParams {
+  const int* blk_expert;
+  const int* blk_row0;
+  const int* blk_rows;
+  const int* n_blk;
+  const int* blk_cnt;          // arrival counters of this call's parity
+  const __nv_bfloat16* recv_x; // [cap_rows][H]
+  const int* recv_src;         // [cap_rows]
+  int H, cap_pairs;
+  __nv_bfloat16* cx;           // [cap_pairs][H]
+  int* cexp;                   // [cap_pairs]
+  int* csrc;                   // [cap_pairs]
+  int* n_valid;
+};
+
+// grid max_blk (>= 1), 256 threads
+__global__ void __launch_bounds__(256) ep_rows_gather_kernel(const EpRowsParams p) {
+  __shared__ int s_before, s_total, s_ok;
+  pdl_wait();
+  pdl_launch_dependents();
+  const int b = blockIdx.x, tid = threadIdx.x;
+  const int nb = *p.n_blk;
+  if (tid == 0) {
+    int before = 0, total = 0;
+    for (int j = 0; j < nb; ++j) {
+      const int r = p.blk_rows[j];
+      if (j < b) before += r;
+      total += r;
+    }
+    s_before = before;
+    s_total = total;
+    s_ok = 1;
+  }
+  __syncthreads();
+  if (b == 0) {
+    for (int c = s_total + tid; c < p.cap_pairs; c += 256) p.cexp[c] = -1;
+    if (tid == 0) {
+      if (s_total > p.cap_pairs) record_error(ERR_BAD_ARG, (unsigned)s_total);
+      *p.n_valid = min(s_total, p.cap_pairs);
+    }
+  }
+  if (b >= nb) return;
+  const int rows = p.blk_rows[b], row0 = p.blk_row0[b], before = s_before;
+  if (rows <= 0) return;
+  if (tid == 0 && !wire_wait(p.blk_cnt + b, rows, (unsigned)(0x05000000u | b))) s_ok = 0;
+  __syncthreads();
+  const int nvec = p.H / 8;
+  for (int r = 0; r < rows; ++r) {
+    const int c = before + r;
+    if (c >= p.cap_pairs) break;
+    if (!s_ok) {   // the rows never came: the batch is skipped, its source slot keeps what it held (reported)
+      if (tid == 0) p.cexp[c] = -1;
+      continue;
+    }
+    const uint8_t* src = reinterpret_cast<const uint8_t*>(p.recv_x + (size_t)(row0 + r) * p.H);
+    uint4* dst = reinterpret_cast<uint4*>(p.cx + (size_t)c * p.H);
+    for (int v = tid; v < nvec; v += 256) dst[v] = ld_sys_u32x4(src + 16 * (size_t)v);
+    if (tid == 0) {
+      p.cexp[c] = p.blk_expert[b];
+      p.csrc[c] = ld_acquire_sys(p.recv_src + row0 + r);
+    }
+  }
+}
+
+struct EpRowsReturnParams {
+  const float* part;   // [cap_pairs][S][H]
+  const int* cexp;
+  const int* csrc;
+  int S, H;
+  const unsigned long long* ret_table;   // [kMaxRanks]: return buffers [slots][H] bf16
+};
+
+// grid cap_pairs, 256 threads
+__global__ void __launch_bounds__(256) ep_rows_return_kernel(const EpRowsReturnParams p) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int c = blockIdx.x, tid = threadIdx.x;
+  if (p.cexp[c] < 0) return;
+  const int src = p.csrc[c];
+  __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.ret_table[src >> 24]) + (size_t)(src & 0xffffff) * p.H;
+  const float* base = p.part + (size_t)c * p.S * p.H;
+  for (int v = tid; v < p.H / 8; v += 256) {
+    float a[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int s = 0; s < p.S; ++s) {
+      const float4 x = *reinterpret_cast<const float4*>(base + (size_t)s * p.H + 8 * v);
+      const float4 y = *reinterpret_cast<const float4*>(base + (size_t)s * p.H + 8 * v + 4);
+      a[0] += x.x; a[1] += x.y; a[2] += x.z; a[3] += x.w; a[4] += y.x; a[5] += y.y; a[6] += y.z; a[7] += y.w;
+    }
+    uint4 o;
+    o.x = pack_bf16(a[0], a[1]); o.y = pack_bf16(a[2], a[3]); o.z = pack_bf16(a[4], a[5]); o.w = pack_bf16(a[6], a[7]);
+    *reinterpret_cast<uint4*>(dst + 8 * v) = o;
+  }
+}
+
 }  // namespace
 
 static Wire make_wire(const void* table, int world, int rank) {
@@ -216,6 +317,25 @@ extern "C" int b2_ep_flag_all(const void* table, int world, int rank, int epoch,
 
 extern "C" int b2_ep_wait_all(const void* table, int world, int rank, int epoch, void* stream) {
   return b2_launch(ep_wait_all_kernel, dim3(1), dim3(32), 0, (cudaStream_t)stream, true, make_wire(table, world, rank), epoch);
+}
+
+extern "C" int b2_ep_rows_gather(const int* blk_expert, const int* blk_row0, const int* blk_rows, const int* n_blk, int max_blk,
+                                 const int* blk_cnt, const void* recv_x, const int* recv_src, int H, int cap_pairs, void* cx,
+                                 int* cexp, int* csrc, int* n_valid, void* stream) {
+  if (H % 8 || max_blk < 1 || cap_pairs < 1) return -1;
+  EpRowsParams p;
+  p.blk_expert = blk_expert; p.blk_row0 = blk_row0; p.blk_rows = blk_rows; p.n_blk = n_blk; p.blk_cnt = blk_cnt;
+  p.recv_x = (const __nv_bfloat16*)recv_x; p.recv_src = recv_src; p.H = H; p.cap_pairs = cap_pairs;
+  p.cx = (__nv_bfloat16*)cx; p.cexp = cexp; p.csrc = csrc; p.n_valid = n_valid;
+  return b2_launch(ep_rows_gather_kernel, dim3(max_blk), dim3(256), 0, (cudaStream_t)stream, true, p);
+}
+
+extern "C" int b2_ep_rows_return(const float* part, const int* cexp, const int* csrc, int cap_pairs, int S, int H,
+                                 const void* ret_table, void* stream) {
+  if (H % 8 || S < 1 || cap_pairs < 1) return -1;
+  EpRowsReturnParams p;
+  p.part = part; p.cexp = cexp; p.csrc = csrc; p.S = S; p.H = H; p.ret_table = (const unsigned long long*)ret_table;
+  return b2_launch(ep_rows_return_kernel, dim3(cap_pairs), dim3(256), 0, (cudaStream_t)stream, true, p);
 }
 
 B2_DEFINE_STATUS(ep)

@@ -57,6 +57,7 @@ struct GemvParams {
   int batches;        // grid.z
   // batched form (MoE decode): blockIdx.z = b selects an expert's weights and that batch's one row
   const int* expert_ids;     // [batches] or nullptr
+  int skip_negative;         // batched form: a batch whose expert id is negative does nothing (its CTAs leave at once)
   long long expert_bytes;    // bytes between experts' W4B tensors
   int x_div;                 // batch b reads activations of batch b / x_div
   long long x_batch_bytes;   // bytes between activation batches
@@ -270,6 +271,10 @@ __global__ void __launch_bounds__(kThreads, (T <= 2 ? 2 : 1)) gemv_w4_kernel(con
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int nblk = blockIdx.x, split = blockIdx.y;
+  if (p.skip_negative) {   // the ids are the previous kernel's output
+    pdl_wait();
+    if (p.expert_ids[blockIdx.z] < 0) return;
+  }
   const int gbeg = split * p.gps;
   const int gend = min(p.KG, gbeg + p.gps);
   const int ngroups = max(0, gend - gbeg);
@@ -654,7 +659,7 @@ extern "C" int b2_gemv_w4(const void* w4b, const void* x, float* out, int M, int
   p.w = reinterpret_cast<const uint8_t*>(w4b);
   p.x = x;
   p.out = out;
-  p.batches = 1; p.expert_ids = nullptr; p.expert_bytes = 0; p.x_div = 1; p.x_batch_bytes = 0; p.out_batch = 0;
+  p.batches = 1; p.expert_ids = nullptr; p.skip_negative = 0; p.expert_bytes = 0; p.x_div = 1; p.x_batch_bytes = 0; p.out_batch = 0;
   p.fold_tickets = nullptr; p.fold_resid_in = nullptr; p.fold_resid_out = nullptr; p.fold_ssq = nullptr;
   p.norm_w = nullptr; p.norm_ssq = nullptr; p.norm_nb = 0; p.norm_eps = 0.f;
   p.tp.table = nullptr; p.tp.epoch = nullptr; p.tp.world = 0; p.tp.rank = 0; p.tp_mcap = 0; p.xq_gs = nullptr;
@@ -691,7 +696,7 @@ extern "C" int b2_gemv_w4_fused(const void* w4b, const void* x, float* out, int 
   p.gps = (p.KG + S - 1) / S;
   if (p.gps % kG != 0) p.gps += kG - p.gps % kG;
   p.ldx = ldx; p.ldo = N; p.x_mode = x_mode; p.s_in = s_in; p.x_slice = x_slice;
-  p.batches = 1; p.expert_ids = nullptr; p.expert_bytes = 0; p.x_div = 1; p.x_batch_bytes = 0; p.out_batch = 0;
+  p.batches = 1; p.expert_ids = nullptr; p.skip_negative = 0; p.expert_bytes = 0; p.x_div = 1; p.x_batch_bytes = 0; p.out_batch = 0;
   p.fold_tickets = fold_tickets; p.fold_resid_in = (const __nv_bfloat16*)fold_resid_in;
   p.fold_resid_out = (__nv_bfloat16*)fold_resid_out; p.fold_ssq = fold_ssq;
   p.norm_w = norm_w; p.norm_ssq = norm_ssq; p.norm_nb = K / 128; p.norm_eps = norm_eps;
@@ -707,9 +712,9 @@ extern "C" int b2_gemv_w4_fused(const void* w4b, const void* x, float* out, int 
 
 // Batched form for MoE decode: batch b (one row) uses the weights of expert expert_ids[b] out of a stack of
 // equally shaped W4B tensors, reads the activations of batch b / x_div and writes out[b][S][N].
-extern "C" int b2_gemv_w4_experts(const void* w4b_stack, long long expert_bytes, const int* expert_ids, int batches,
-                                  const void* x, int x_div, long long x_batch_bytes, float* out, int N, int K, int S,
-                                  int ldx, int x_mode, int s_in, long long x_slice, void* stream) {
+static int gemv_w4_experts_impl(const void* w4b_stack, long long expert_bytes, const int* expert_ids, int batches,
+                                const void* x, int x_div, long long x_batch_bytes, float* out, int N, int K, int S,
+                                int ldx, int x_mode, int s_in, long long x_slice, int skip_negative, void* stream) {
   if (batches < 1 || batches > 65535 || K % 64 != 0 || S < 1 || x_div < 1) return -1;
   GemvParams p;
   p.w = reinterpret_cast<const uint8_t*>(w4b_stack);
@@ -719,12 +724,26 @@ extern "C" int b2_gemv_w4_experts(const void* w4b_stack, long long expert_bytes,
   p.gps = (p.KG + S - 1) / S;
   if (p.gps % kG != 0) p.gps += kG - p.gps % kG;
   p.ldx = ldx; p.ldo = N; p.x_mode = x_mode; p.s_in = s_in; p.x_slice = x_slice;
-  p.batches = batches; p.expert_ids = expert_ids; p.expert_bytes = expert_bytes; p.x_div = x_div;
+  p.batches = batches; p.expert_ids = expert_ids; p.expert_bytes = expert_bytes; p.x_div = x_div; p.skip_negative = skip_negative;
   p.x_batch_bytes = x_batch_bytes; p.out_batch = (long long)S * N;
   p.fold_tickets = nullptr; p.fold_resid_in = nullptr; p.fold_resid_out = nullptr; p.fold_ssq = nullptr;
   p.norm_w = nullptr; p.norm_ssq = nullptr; p.norm_nb = 0; p.norm_eps = 0.f;
   p.tp.table = nullptr; p.tp.epoch = nullptr; p.tp.world = 0; p.tp.rank = 0; p.tp_mcap = 0; p.xq_gs = nullptr;
   return launch_t<1>(p, reinterpret_cast<cudaStream_t>(stream));
+}
+
+extern "C" int b2_gemv_w4_experts(const void* w4b_stack, long long expert_bytes, const int* expert_ids, int batches,
+                                  const void* x, int x_div, long long x_batch_bytes, float* out, int N, int K, int S,
+                                  int ldx, int x_mode, int s_in, long long x_slice, void* stream) {
+  return gemv_w4_experts_impl(w4b_stack, expert_bytes, expert_ids, batches, x, x_div, x_batch_bytes, out, N, K, S, ldx, x_mode,
+                              s_in, x_slice, 0, stream);
+}
+// The same with batches whose expert id is negative skipped (an owner's receive buffer is sized for the worst case).
+extern "C" int b2_gemv_w4_experts_sparse(const void* w4b_stack, long long expert_bytes, const int* expert_ids, int batches,
+                                         const void* x, int x_div, long long x_batch_bytes, float* out, int N, int K, int S,
+                                         int ldx, int x_mode, int s_in, long long x_slice, void* stream) {
+  return gemv_w4_experts_impl(w4b_stack, expert_bytes, expert_ids, batches, x, x_div, x_batch_bytes, out, N, K, S, ldx, x_mode,
+                              s_in, x_slice, 1, stream);
 }
 
 // Quantise activation rows for x_mode 3.  Input modes as the GEMV's (0 bf16 rows, 1 SiLU*up of fp32 slices,

@@ -43,9 +43,11 @@ def combine_rows(part, s, m, k, h, topk_w, shared_part, s_sh, gate_logit, gate_l
 
 
 def gemv_experts(w4b_stack, expert_bytes, expert_ids, batches, x, x_div, x_batch_bytes, out, n, k, splits, ldx,
-                 x_mode=0, s_in=1, x_slice=0):
-    """One row per batch against the W4B weights of expert ``expert_ids[b]``; ``out`` is ``[b][splits][n]``."""
-    rc = K.lib().b2_gemv_w4_experts(K._p(w4b_stack), ctypes.c_longlong(expert_bytes), K._p(expert_ids), batches,
+                 x_mode=0, s_in=1, x_slice=0, sparse=False):
+    """One row per batch against the W4B weights of expert ``expert_ids[b]``; ``out`` is ``[b][splits][n]``.
+    ``sparse``: batches whose id is negative are skipped (their output rows are left as they are)."""
+    fn = K.lib().b2_gemv_w4_experts_sparse if sparse else K.lib().b2_gemv_w4_experts
+    rc = fn(K._p(w4b_stack), ctypes.c_longlong(expert_bytes), K._p(expert_ids), batches,
                                     K._p(x), x_div, ctypes.c_longlong(x_batch_bytes), K._p(out), n, k, splits, ldx,
                                     x_mode, s_in, ctypes.c_longlong(x_slice), K._stream())
     K._check(rc, "gemv_w4_experts")

@@ -121,6 +121,84 @@ class EpMoe:
             self.expert_base = torch.zeros(self.el, dtype=i32, device=dev)
             self.row_of = torch.empty(self.cap_rows, dtype=i32, device=dev)
 
+    # ------------------------------------------------------------------ decode rows
+    def enable_rows(self, max_rows: int):
+        """Buffers of the decode / verify form (at most ``max_rows`` rows per rank and step): on the experts' owner
+        the received rows go through the batched W4 GEMV, one (row, expert) pair per batch, reading int4 weights."""
+        cfg, dev = self.cfg, self.dev
+        k, h, i = cfg.top_k, cfg.hidden, cfg.expert_ffn
+        if max_rows > self.t_cap:
+            raise ValueError("more decode rows than the exchange buffers were sized for")
+        self.rows_cap = max_rows
+        self.cap_pairs = max_rows * k * self.world            # every pair of every rank could land here
+        if self.cap_pairs > 65535:
+            raise ValueError("too many (row, expert) pairs for one batched GEMV launch")
+        i32, f32, bf = torch.int32, torch.float32, torch.bfloat16
+        self.cx = torch.zeros(self.cap_pairs, h, dtype=bf, device=dev)
+        self.cexp = torch.full((self.cap_pairs,), -1, dtype=i32, device=dev)
+        self.csrc = torch.zeros(self.cap_pairs, dtype=i32, device=dev)
+        self.n_valid = torch.zeros(1, dtype=i32, device=dev)
+        self.s_gu, self.s_dn = K.gemv_splits(2 * i, h), K.gemv_splits(h, i)
+        self.part_gu = torch.zeros(self.cap_pairs * self.s_gu * 2 * i, dtype=f32, device=dev)
+        self.part_dn = torch.zeros(self.cap_pairs * self.s_dn * h, dtype=f32, device=dev)
+        self.rows_act = torch.empty(max_rows, max(cfg.shared_ffn, 8), dtype=bf, device=dev) if cfg.shared_ffn else None
+
+    def block_rows(self, lw, c: int, x, resid):
+        """``resid[:c] += MoE(x[:c])`` for the ``c`` rows of a decode / verify step (``c`` may differ between ranks,
+        every rank calls this once per MoE layer).  Fused mode only: route -> counts exchange -> plan -> dispatch as in the
+        prompt form; the owner gathers the rows that arrived, runs gate‖up and down as batched int4 GEMVs, and stores
+        each result row into its source's return buffer; the source sums a row's slots in slot order."""
+        if self.mode != "fused":
+            raise NotImplementedError("decode rows under expert parallelism use the fused wire")
+        cfg = self.cfg
+        e, k, h, i = cfg.n_experts, cfg.top_k, cfg.hidden, cfg.expert_ffn
+        x, resid = x[:c], resid[:c]
+        logits = self.logits[:c]
+        rc = router_cat(lw, cfg)
+        if c > 0:
+            K.head_gemv(rc, x, logits, c, rc.shape[0], h)
+            M.route(logits, self.ld, c, e, k, self.topk_idx, self.topk_w)
+        self.epoch += 1
+        ep, par = self.epoch, self.epoch & 1
+        self.counts.zero_()
+        if c > 0:
+            M.count(self.topk_idx, c * k, self.counts, self.rank_in)
+        L = K.lib()
+        K._check(L.b2_ep_counts_push(K._p(self.counts), e, K._p(self.cntw.table), self.world, self.rank, ep, K._stream()),
+                 "ep_counts_push")
+        blk_cnt = self.recvw.flags
+        K._check(L.b2_ep_plan(K._p(self.cntw.table), ep, e, self.world, self.rank, self.max_blk, self.cap_rows,
+                              K._p(self.send_base), K._p(self.blk_expert), K._p(self.blk_row0), K._p(self.blk_rows),
+                              K._p(self.n_blk), K._p(self.total_rows), K._p(blk_cnt[(par ^ 1) * self.max_blk:]),
+                              K._stream()), "ep_plan")
+        if c > 0:
+            K._check(L.b2_ep_dispatch(K._p(self.topk_idx), K._p(self.rank_in), K._p(self.send_base), K._p(x), c, k, h, e,
+                                      self.world, self.rank, self.cap_rows, par, self.max_blk, K._p(self.recvw.table),
+                                      K._p(self.src_table), K._stream()), "ep_dispatch")
+        K._check(L.b2_ep_rows_gather(K._p(self.blk_expert), K._p(self.blk_row0), K._p(self.blk_rows), K._p(self.n_blk),
+                                     self.max_blk, K._p(blk_cnt[par * self.max_blk:]), K._p(self.recv_x), K._p(self.recv_src),
+                                     h, self.cap_pairs, K._p(self.cx), K._p(self.cexp), K._p(self.csrc), K._p(self.n_valid),
+                                     K._stream()), "ep_rows_gather")
+        gu_bytes = lw.experts_gate_up_w4b[0].numel()
+        dn_bytes = lw.experts_down_w4b[0].numel()
+        M.gemv_experts(lw.experts_gate_up_w4b, gu_bytes, self.cexp, self.cap_pairs, self.cx, 1, h * 2, self.part_gu, 2 * i, h,
+                       self.s_gu, h, sparse=True)
+        M.gemv_experts(lw.experts_down_w4b, dn_bytes, self.cexp, self.cap_pairs, self.part_gu, 1, self.s_gu * 2 * i * 4,
+                       self.part_dn, h, i, self.s_dn, 2 * i, x_mode=1, s_in=self.s_gu, x_slice=2 * i, sparse=True)
+        K._check(L.b2_ep_rows_return(K._p(self.part_dn), K._p(self.cexp), K._p(self.csrc), self.cap_pairs, self.s_dn, h,
+                                     K._p(self.retw.table), K._stream()), "ep_rows_return")
+        K._check(L.b2_ep_flag_all(K._p(self.retw.table), self.world, self.rank, ep, K._stream()), "ep_flag_all")
+        shared_y, gate = None, None
+        if lw.shared is not None and c > 0:
+            act = self.rows_act[:c, : cfg.shared_ffn]
+            G.gemm_w4(x, lw.shared.gate_up.w4b, lw.shared.gate_up.n, lw.shared.gate_up.k, act, epi=G.EPI_SILU_MUL)
+            shared_y = self.shared_y[:c]
+            G.gemm_w4(act, lw.shared.down.w4b, lw.shared.down.n, lw.shared.down.k, shared_y, epi=G.EPI_BF16)
+            gate = logits[:, e:]
+        ep_wait_all(self.retw, self.epoch)
+        if c > 0:
+            M.combine(self.ret, self.ident, self.topk_w, c, k, h, shared_y, gate, self.ld, resid, resid)
+
     # ------------------------------------------------------------------ expert weights (bf16 forms)
     def _expert_bf16(self, runner, lw):
         cfg = self.cfg
@@ -286,4 +364,55 @@ def bench_prefill(cfg: ModelConfig, n: int, modes=("fused", "nccl"), reps: int =
         runner.ep.close()
         del eng, runner
         torch.cuda.empty_cache()
+    return out
+
+
+def attach_rows(engine, max_rows: int) -> "EpMoe":
+    """Makes ``engine`` (which holds only this rank's experts) run the MoE layers of its decode / verify steps through
+    the expert-parallel row form.  Such an engine steps eagerly: the exchange's call numbers are launch arguments."""
+    if engine.use_graphs:
+        raise ValueError("an expert-parallel decode engine runs without CUDA graphs (use_graphs=False)")
+    ep = EpMoe(engine.cfg, max(max_rows, 8), mode="fused")
+    ep.enable_rows(max_rows)
+    engine.model.ep = ep
+    return ep
+
+
+def bench_decode_rows(cfg: ModelConfig, rows_per_rank: int, depth: int, steps: int = 32, warmup: int = 4) -> dict:
+    """Batched decode with the experts spread over the ranks: every rank serves ``rows_per_rank`` requests of its own
+    at context ``depth`` (data-parallel attention); one step emits ``world * rows_per_rank`` tokens.  CUDA events,
+    max over ranks."""
+    import torch.distributed as dist
+    from ..runtime.engine import Engine, Row
+    from .tp import _max_over_ranks, _sync_all
+    world = dist.get_world_size() if dist.is_initialized() else 1
+    rank = dist.get_rank() if dist.is_initialized() else 0
+    dev = torch.device("cuda", torch.cuda.current_device())
+    w = random_ep_shard(cfg, rank, world, dev)
+    eng = Engine(w, max_seqs=rows_per_rank, max_len=depth + steps + warmup + 64, use_graphs=False)
+    ep = attach_rows(eng, rows_per_rank)
+    eng.kv.k.normal_(0, 0.5)
+    eng.kv.v.normal_(0, 0.5)
+    for slot in range(rows_per_rank):
+        eng._ensure_pages(slot, depth)
+        eng.seq_len[slot] = depth
+    toks = [17 + slot for slot in range(rows_per_rank)]
+
+    def step(toks):
+        return eng.forward_rows([Row(slot, eng.seq_len[slot], toks[slot]) for slot in range(rows_per_rank)])
+    for _ in range(warmup):
+        toks = step(toks)
+    _sync_all()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        toks = step(toks)
+    e1.record()
+    _sync_all()
+    ms = _max_over_ranks(e0.elapsed_time(e1) / steps, dev)
+    K.check_status()
+    out = {"ms_per_step": ms, "rows_total": world * rows_per_rank, "tokens_per_s": world * rows_per_rank / (ms / 1e3),
+           "depth": depth, "parallelism": f"dp{world} attention + ep{world} experts",
+           "note": "eager steps (no CUDA graph), each with its host round trip"}
+    ep.close()
     return out

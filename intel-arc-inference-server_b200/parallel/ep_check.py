@@ -51,7 +51,47 @@ def self_check(cfg, modes=("fused", "nccl"), n_tokens: int = 300) -> dict:
         if world > 1:
             dist.barrier()
         runner.ep.close()
+    if "fused" in modes:
+        report["decode_rows_fused"] = check_rows(cfg, full, shard, ids[:64])
     return report
+
+
+def check_rows(cfg, full, shard, ids, steps: int = 6) -> dict:
+    """Decode steps with the experts spread over the ranks against the same model on one GPU.  Every rank runs its OWN
+    request (the prompt rotated by its rank), so the ranks send each other different rows; each compares its tokens and
+    last logits with a one-GPU engine run of the same request."""
+    import torch.distributed as dist
+    from ..ops import lib as K
+    from ..runtime.engine import Engine
+    from . import ep as EP
+    world = dist.get_world_size() if dist.is_initialized() else 1
+    rank = dist.get_rank() if dist.is_initialized() else 0
+    mine = ids[rank:] + ids[:rank]
+    # both engines ingest the prompt through row steps (up to max_rows positions per step), so the sharded one's
+    # prompt goes through the row form of the exchange too
+    from ..runtime.engine import Row
+    one = Engine(full, max_seqs=1, max_len=256, use_graphs=False, prefill_backend="rows")
+    eng = Engine(shard, max_seqs=1, max_len=256, use_graphs=False, prefill_backend="rows")
+    ep = EP.attach_rows(eng, eng.max_rows)
+    tok, mine_tok = one.prefill(0, mine), eng.prefill(0, mine)
+    want, got = [tok], [mine_tok]
+    scale = float(one.model.buf.logits[0].abs().max())
+    err = float((eng.model.buf.logits[eng.last_prefill_row] - one.model.buf.logits[one.last_prefill_row]).abs().max())
+    for _ in range(steps - 1):      # teacher-forced with the one-GPU tokens: every step's logits are comparable
+        r = one.forward_rows([Row(0, one.seq_len[0], tok)])[0]
+        g = eng.forward_rows([Row(0, eng.seq_len[0], tok)])[0]
+        err = max(err, float((eng.model.buf.logits[0] - one.model.buf.logits[0]).abs().max()))
+        want.append(r)
+        got.append(g)
+        tok = r
+    K.check_status()
+    agree = sum(int(a == b) for a, b in zip(got, want))
+    good = err < 0.02 * scale and agree >= steps - 1       # the return rows are bf16: a near-tie may flip
+    t = torch.tensor([1 if good else 0], device="cuda")
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MIN)
+    ep.close()
+    return {"tokens": got, "want": want, "agree": agree, "of": steps, "logit_err": err, "logit_scale": scale, "ok": bool(int(t))}
 
 
 def main():

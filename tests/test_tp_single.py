@@ -91,3 +91,33 @@ def test_expert_parallel_block_single_rank_matches_plain():
         assert err < 0.02 * float(ref_logits.abs().max()), (mode, err)
         assert t == t_ref
         runner.ep.close()
+
+
+def test_expert_parallel_decode_rows_single_rank_match_plain():
+    """Decode / verify rows through the exchange's row form (dispatch -> gather on the owner -> batched int4 GEMVs ->
+    return -> slot-order sum) as a group of one rank, against the plain MoE row path of the same engine weights."""
+    from b200serve.ops import lib as K
+    from b200serve.parallel.ep import attach_rows
+    from b200serve.runtime.engine import Engine
+    cfg = preset("small-moe")
+    w = random_weights(cfg, device="cuda", seed=4)
+    g = torch.Generator().manual_seed(12)
+    ids = torch.randint(0, cfg.vocab, (70,), generator=g).tolist()
+    from b200serve.runtime.engine import Row
+    plain = Engine(w, max_seqs=1, max_len=256, use_graphs=False, prefill_backend="rows")
+    eng = Engine(w, max_seqs=1, max_len=256, use_graphs=False, prefill_backend="rows")
+    ep = attach_rows(eng, eng.max_rows)      # the prompt goes through row steps of up to max_rows positions as well
+    tok, tok2 = plain.prefill(0, ids), eng.prefill(0, ids)
+    scale = float(plain.model.buf.logits[plain.last_prefill_row].abs().max())
+    err = float((eng.model.buf.logits[eng.last_prefill_row] - plain.model.buf.logits[plain.last_prefill_row]).abs().max())
+    agree = int(tok == tok2)
+    for _ in range(7):     # teacher-forced: each step's logits are comparable
+        r = plain.forward_rows([Row(0, plain.seq_len[0], tok)])[0]
+        g2 = eng.forward_rows([Row(0, eng.seq_len[0], tok)])[0]
+        err = max(err, float((eng.model.buf.logits[0] - plain.model.buf.logits[0]).abs().max()))
+        agree += int(r == g2)
+        tok = r
+    K.check_status()
+    assert err < 0.02 * scale, err        # the returned rows are bf16 where the plain path folds fp32 slices
+    assert agree >= 7, agree
+    ep.close()
