@@ -101,7 +101,7 @@ def main():
     ap.add_argument("--model", default="dense-27b")
     ap.add_argument("--depth", type=int, default=4096, help="context length the decode steps run at")
     ap.add_argument("--prefill-len", type=int, default=4096)
-    ap.add_argument("--what", default="all", help="decode | prefill | prefill32k | moe | w4 | spec | spec65k | batch32k | prefix | hybrid | tp | ep | replica | all")
+    ap.add_argument("--what", default="all", help="decode | prefill | prefill32k | moe | w4 | spec | spec65k | batch32k | prefix | hybrid | tp | ep | pp | replica | all")
     ap.add_argument("--kv-cache", default="bf16")
     ap.add_argument("--int8-head", action="store_true")
     ap.add_argument("--prefill-backend", default="auto")
@@ -240,6 +240,13 @@ def main():
             tpx[f"decode_{mode}"] = TP.bench_decode(cfg, mode, args.depth, steps, warm)
             tpx[f"prefill_{mode}"] = TP.bench_prefill(cfg, mode, args.prefill_len)
         tpx["fused_ops"] = TP.bench_fused_ops(cfg, args.prefill_len, peaks=load_peaks())
+        # the 8-request serving case of the 27B configuration: 32,768-token prompts into an int8 KV cache, then the
+        # eight requests decode together at that depth (the sharded model against itself on one GPU first)
+        tpx["self_check_small_dense_int8kv"] = TPC.self_check(TPC.widen_for(preset("small-dense"), world), ("fused",), 200,
+                                                              kv_dtype="int8")
+        tpx["prefill_32k_int8kv_fused"] = TP.bench_prefill(cfg, "fused", 32768, reps=2, kv_dtype="int8")
+        tpx["decode8_depth32k_int8kv_fused"] = TP.bench_decode(cfg, "fused", 32768, steps, warm, rows=args.tp_rows,
+                                                               kv_dtype="int8")
         return tpx
 
     def replica_extra():
@@ -306,6 +313,13 @@ def main():
         guarded("tp", tp_extra, multi_rank=True)
     if world > 1 and args.what in ("all", "ep"):
         guarded("ep", ep_extra, multi_rank=True)
+    if world == 2 and args.what in ("all", "pp"):
+        def pp_extra():
+            # the two GPUs as pipeline stages of one 27B model: the 32,768-token prompt pass and decode behind it
+            from b200serve.models.config import preset
+            from b200serve.parallel import pp as PP
+            return PP.bench_pp(preset(args.model), 32768, min(args.steps, 32), max(args.warmup, 3))
+        guarded("pp2", pp_extra, multi_rank=True)
     if world > 1 and args.what in ("all", "replica"):
         guarded("replica", replica_extra, multi_rank=True)
     clocks = sampler.stop()

@@ -202,7 +202,7 @@ def bench_decode(cfg: ModelConfig, mode: str, depth: int, steps: int, warmup: in
     return out
 
 
-def bench_prefill(cfg: ModelConfig, mode: str, n: int, reps: int = 4) -> dict:
+def bench_prefill(cfg: ModelConfig, mode: str, n: int, reps: int = 4, kv_dtype: str = "bf16") -> dict:
     """Whole prompt passes of ``n`` tokens through ``Engine.prefill``; ms is the max over ranks."""
     import torch.distributed as dist
     from ..ops import lib as K
@@ -210,7 +210,8 @@ def bench_prefill(cfg: ModelConfig, mode: str, n: int, reps: int = 4) -> dict:
     rank = dist.get_rank() if dist.is_initialized() else 0
     dev = torch.device("cuda", torch.cuda.current_device())
     w = random_weights(cfg, device=dev, seed=0, exact=False) if world == 1 else random_shard(cfg, rank, world, dev)
-    eng = make_engine(w, mode=mode, max_seqs=1, max_len=n + 64, use_graphs=False, prefill_backend="bf16-resident")
+    eng = make_engine(w, mode=mode, max_seqs=1, max_len=n + 64, use_graphs=False, prefill_backend="bf16-resident",
+                      kv_dtype=kv_dtype)
     g = torch.Generator().manual_seed(1)
     ids = torch.randint(0, cfg.vocab, (n,), generator=g).tolist()
     for _ in range(3):
@@ -231,7 +232,7 @@ def bench_prefill(cfg: ModelConfig, mode: str, n: int, reps: int = 4) -> dict:
     eng.close()
     del eng, w
     torch.cuda.empty_cache()
-    return {"ms": ms, "tokens": n, "tokens_per_s": n / (ms / 1e3), "launches": launches}
+    return {"ms": ms, "tokens": n, "tokens_per_s": n / (ms / 1e3), "launches": launches, "kv_cache": kv_dtype}
 
 
 def bench_fused_ops(cfg: ModelConfig, c: int = 4096, reps: int = 20, peaks: Optional[dict] = None) -> dict:

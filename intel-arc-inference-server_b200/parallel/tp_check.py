@@ -28,7 +28,7 @@ def widen_for(cfg, world: int):
     return cfg
 
 
-def self_check(cfg, modes=("fused", "nccl"), prompt_len: int = 40) -> dict:
+def self_check(cfg, modes=("fused", "nccl"), prompt_len: int = 40, kv_dtype: str = "bf16") -> dict:
     """The sharded model against the same model on one GPU (every rank computes the one-GPU answer itself): logits of
     the prompt's last position, 12 teacher-forced decode steps, and bit-equal tokens and residual rows on all ranks.
     Returns ``{mode: {...,"ok": bool}}``; call it on every rank of an initialised process group."""
@@ -44,7 +44,7 @@ def self_check(cfg, modes=("fused", "nccl"), prompt_len: int = 40) -> dict:
     full = random_weights(cfg, device=dev, seed=0)
     g = torch.Generator().manual_seed(5)
     prompt = torch.randint(0, cfg.vocab, (prompt_len,), generator=g).tolist()
-    one = Engine(full, max_seqs=1, max_len=prompt_len + 216, use_graphs=False)
+    one = Engine(full, max_seqs=1, max_len=prompt_len + 216, use_graphs=False, kv_dtype=kv_dtype)
     first = one.prefill(0, prompt)
     ref_logits = one.model.buf.logits[one.last_prefill_row].clone()
     ref_toks = [first]
@@ -53,7 +53,8 @@ def self_check(cfg, modes=("fused", "nccl"), prompt_len: int = 40) -> dict:
     shard = TP.shard_weights(full, rank, world, dev)
     per = (cfg.vocab + world - 1) // world
     for mode in modes:
-        eng = TP.make_engine(shard, mode=mode, max_seqs=1, max_len=prompt_len + 216, use_graphs=(mode == "fused"))
+        eng = TP.make_engine(shard, mode=mode, max_seqs=1, max_len=prompt_len + 216, use_graphs=(mode == "fused"),
+                             kv_dtype=kv_dtype)
         t0 = eng.prefill(0, prompt)
         lg = eng.model.buf.logits[eng.last_prefill_row]
         want = ref_logits[rank * per: rank * per + lg.numel()]
@@ -96,6 +97,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=4)
     ap.add_argument("--rows", type=int, default=1)
     ap.add_argument("--modes", default="fused,nccl")
+    ap.add_argument("--kv-cache", default="bf16", help="bf16 | int8 (the check then runs both engines with an int8 KV cache)")
     ap.add_argument("--prefill", type=int, default=0, help="time prompt passes of this many tokens")
     ap.add_argument("--ops", type=int, default=0, help="time the fused GEMM+collective kernels alone on a chunk of this many rows")
     ap.add_argument("--pp", action="store_true", help="pipeline check: the ranks are stages; tokens must equal the one-GPU run")
@@ -124,7 +126,7 @@ def main():
         return float(t)
 
     if args.check:
-        chk = self_check(cfg, args.modes.split(","), args.prompt)
+        chk = self_check(cfg, args.modes.split(","), args.prompt, kv_dtype=args.kv_cache)
         ok = ok and all(v["ok"] for v in chk.values())
         report.update(chk)
     if args.pp:
@@ -132,15 +134,25 @@ def main():
         full = random_weights(cfg, device=dev, seed=0)
         g = torch.Generator().manual_seed(5)
         prompt = torch.randint(0, cfg.vocab, (args.prompt,), generator=g).tolist()
-        one = Engine(full, max_seqs=1, max_len=args.prompt + 64, use_graphs=False, prefill_backend="rows")
-        want = one.generate(prompt, 12)
+        # a long prompt takes the tcgen05 prompt kernels on both sides (chunks of 128 so that several are in flight)
+        long_prompt = args.prompt > 64
+        one = Engine(full, max_seqs=1, max_len=args.prompt + 64, use_graphs=False,
+                     prefill_backend="auto" if long_prompt else "rows")
+        one.reset(0)
+        first = one.prefill(0, prompt, chunk=128 if long_prompt else None)
+        one.decode_begin([0], [first])
+        want = [first] + [one.decode_step()[0] for _ in range(11)]
         a, b = PP.split_layers(cfg.n_layers, world)[rank]
         eng = PP.PipelineEngine(PP.stage_weights(full, a, b), rank, world, max_seqs=1, max_len=args.prompt + 64)
-        got = eng.generate(prompt, 12)
+        eng.reset(0)
+        first = eng.prefill(0, prompt, chunk=128 if long_prompt else None)
+        eng.decode_begin([0], [first])
+        got = [first] + [eng.decode_step()[0] for _ in range(11)]
         K.check_status()
         good = got == want
         ok = ok and good
-        report["pp"] = {"stages": world, "layers": [a, b], "tokens_equal": good, "sent_bytes": eng.sent_bytes}
+        report["pp"] = {"stages": world, "layers": [a, b], "tokens_equal": good, "sent_bytes": eng.sent_bytes,
+                        "tokens": got, "want": want}
     if args.bench:
         for mode in args.modes.split(","):
             report[f"bench_{mode}"] = TP.bench_decode(cfg, mode, args.depth, args.steps, args.warmup, args.rows)

@@ -50,6 +50,7 @@ class TpPrefillRunner(PrefillRunner):
         self.own = torch.zeros(self.rows_cap, h, dtype=torch.bfloat16, device=self.dev)   # this rank's residual rows
         self.done = torch.zeros(self.tpr, dtype=torch.int32, device=self.dev)
         self.ag_epoch = 0
+        self._kv16 = None     # int8 KV cache: bf16 K / V of the request being ingested, all local layers (see run)
 
     def _fold(self, nsrc: int, arrivals: int, norm_w, c: int):
         K.rs_fold(self.rs, arrivals, nsrc, self.done, self.own, norm_w, self.cfg.rms_eps, self.xw, self.cfg.hidden,
@@ -72,13 +73,20 @@ class TpPrefillRunner(PrefillRunner):
         bt_row = eng.block_table[slot]
         xg = self.x_full[:c]
         for li, lw in enumerate(layers):
-            kc, vc, ks, vs = eng.kv.layer(li)
             qkv = self.qkv[:c]
             G.gemm_tp(xg, self._w_bf16(lw.qkv), qkv, G.EPI_F32, ag_cnt=self.xw.flags, ag_expect=128 * self.ag_epoch)
-            K.rope_append(qkv, 0, 1, c, None, eng.block_table, eng.max_blocks, m.cos_t, m.sin_t, cfg.n_q_heads,
-                          cfg.n_kv_heads, cfg.head_dim, self.q, kc, vc, ks, vs, eng.kv.kv_int8, req=slot, pos0=pos0)
-            K.attn_prefill(self.q, kc, vc, bt_row, self.attn, c, pos0, cfg.n_q_heads, cfg.n_kv_heads, cfg.head_dim,
-                           eng.kv.num_pages, eng.max_blocks, m.scale, window=m._window(li))
+            if self._kv16 is None:
+                kc, vc, ks, vs = eng.kv.layer(li)
+                K.rope_append(qkv, 0, 1, c, None, eng.block_table, eng.max_blocks, m.cos_t, m.sin_t, cfg.n_q_heads,
+                              cfg.n_kv_heads, cfg.head_dim, self.q, kc, vc, ks, vs, False, req=slot, pos0=pos0)
+                K.attn_prefill(self.q, kc, vc, bt_row, self.attn, c, pos0, cfg.n_q_heads, cfg.n_kv_heads, cfg.head_dim,
+                               eng.kv.num_pages, eng.max_blocks, m.scale, window=m._window(li))
+            else:       # the bf16 scratch of this request: identity page table, request 0
+                k16, v16, tab16 = self._kv16
+                K.rope_append(qkv, 0, 1, c, None, tab16, tab16.shape[1], m.cos_t, m.sin_t, cfg.n_q_heads,
+                              cfg.n_kv_heads, cfg.head_dim, self.q, k16[li], v16[li], None, None, False, req=0, pos0=pos0)
+                K.attn_prefill(self.q, k16[li], v16[li], tab16[0], self.attn, c, pos0, cfg.n_q_heads, cfg.n_kv_heads,
+                               cfg.head_dim, k16.shape[1], tab16.shape[1], m.scale, window=m._window(li))
             arr = G.gemm_tp(self.attn[:c], self._w_bf16(lw.o), None, G.EPI_RS_PUSH, rs=self.rs, rs_tpr=self.tpr)
             self._fold(w, arr, lw.post_norm, c)
             act = self.act[:c, : cfg.ffn]
@@ -95,8 +103,12 @@ class TpPrefillRunner(PrefillRunner):
         chunk = min(chunk or self.max_chunk, self.max_chunk)
         start = eng.seq_len[slot]
         n = len(ids)
+        if eng.kv.kv_int8:
+            self._int8_begin(slot, start, n)
         for c0 in range(0, n, chunk):
             self.chunk(slot, ids[c0: c0 + chunk], start + c0)
+        if eng.kv.kv_int8:
+            self._int8_end(slot, start, n)
         last = (n - 1) % chunk
         # the last fold pushed final_norm(residual) of every token: wait for the last token's tile, then the head
         K.wire_wait(self.xw.flags[last // 128:], 128 * self.ag_epoch)
@@ -111,8 +123,43 @@ class TpPrefillRunner(PrefillRunner):
         eng.last_prefill_row = 0
         return eng._read_out(1)[0]
 
+    # ------------------------------------------------------------------ int8 KV cache
+    # The prompt attention kernel reads bf16 pages.  With an int8 cache the request's K / V of ALL local layers are
+    # kept in a bf16 scratch while it is ingested (a rank holds n_kv_heads / world heads: 4 GB for 32,768 positions of
+    # the 27B shape at two ranks) and quantised into the cache afterwards; positions the slot already holds are
+    # dequantised into the scratch first.  The chunk walk stays chunk-major, so the fused collectives are unchanged.
+    def _int8_begin(self, slot: int, start: int, n: int):
+        eng, cfg = self.eng, self.cfg
+        total = start + n
+        eng._ensure_pages(slot, total)
+        blocks = (total + 15) // 16
+        sc = self._kv16
+        if sc is None or sc[0].shape[1] < blocks + 1:
+            cap = max(blocks, eng.max_blocks) + 1
+            shape = (len(eng.model.w.layers), cap, cfg.n_kv_heads, cfg.page_size, cfg.head_dim)
+            self._kv16 = None
+            sc = (torch.zeros(shape, dtype=torch.bfloat16, device=self.dev),
+                  torch.zeros(shape, dtype=torch.bfloat16, device=self.dev),
+                  torch.arange(1, cap + 1, dtype=torch.int32, device=self.dev).clamp_(max=cap - 1).view(1, cap))
+        self._kv16 = sc
+        if start > 0:
+            k16, v16, tab16 = sc
+            tab8 = eng.block_table[slot]
+            for li in range(k16.shape[0]):
+                k8, v8, ks, vs = eng.kv.layer(li)
+                K.kv_convert(k16[li], v16[li], tab16[0], k8, v8, ks, vs, tab8, 0, start, cfg.n_kv_heads, cfg.head_dim, False)
+
+    def _int8_end(self, slot: int, start: int, n: int):
+        eng, cfg = self.eng, self.cfg
+        k16, v16, tab16 = self._kv16
+        tab8 = eng.block_table[slot]
+        for li in range(k16.shape[0]):
+            k8, v8, ks, vs = eng.kv.layer(li)
+            K.kv_convert(k16[li], v16[li], tab16[0], k8, v8, ks, vs, tab8, start, n, cfg.n_kv_heads, cfg.head_dim, True)
+
     def close(self):
         self.x_full = None
+        self._kv16 = None
         self.rs.close()
         self.xw.close()
 

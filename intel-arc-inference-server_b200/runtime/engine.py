@@ -326,7 +326,9 @@ class Engine:
             return False
         if self.cfg.n_gdn_layers and (self.kv.kv_int8 or self.tp is not None or self.model.nccl is not None):
             return False        # hybrid models: the layer-major int8-KV pass and the parallel runners know no GDN layers
-        ok = self.cfg.head_dim == 128 and (not self.kv.kv_int8 or (self.tp is None and self.model.nccl is None))
+        # an int8 KV cache: the one-GPU runner's layer-major pass, or the tensor-parallel runner's bf16 scratch of
+        # the request; the NCCL comparison build has neither
+        ok = self.cfg.head_dim == 128 and (not self.kv.kv_int8 or self.model.nccl is None)
         if not ok and self.prefill_backend != "auto":
             raise ValueError(f"prefill backend {self.prefill_backend!r} needs head_dim 128 (and a bf16 KV cache under "
                              "tensor parallelism)")
