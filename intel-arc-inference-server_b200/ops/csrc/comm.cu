@@ -332,7 +332,7 @@ extern "C" int b2_allreduce_rows(const float* x, float* out, int M, int N, const
 extern "C" int b2_rs_fold(const void* land, int* rs_cnt, int* done, int rs_expect, int nsrc, void* resid,
                           const float* norm_w, float eps, const void* x_table, int world, int rank, int H, int tpr, int c,
                           void* stream) {
-  if (H % 8 || world < 1 || world > kMaxRanks || nsrc > world || tpr < 1) return -1;
+  if (H % 8 || world < 1 || world > kMaxRanks || nsrc > kMaxRanks || tpr < 1) return -1;   // (nsrc > world: a loop-back test with several landing slots)
   RsFoldParams p;
   p.land = (const __nv_bfloat16*)land; p.rs_cnt = rs_cnt; p.done = done; p.rs_expect = rs_expect; p.nsrc = nsrc;
   p.resid = (__nv_bfloat16*)resid; p.norm_w = norm_w; p.eps = eps; p.x_table = (const unsigned long long*)x_table;

@@ -46,6 +46,47 @@ def test_gemv_w4_matches_fp32(m, n, k):
     assert (got - ref).abs().max() <= 2e-3 * ref.abs().max() + 1e-4
 
 
+@pytest.mark.parametrize("m", [1, 4])
+def test_gemv_w4_outlier_activations(m):
+    """A few activations hundreds of times larger than the rest (the massive-activation channels of real models): the
+    kernel re-quantises each 64-k group of a row to 15-bit integers against the GROUP's maximum, so an outlier may cost
+    precision only inside its own group.  Checked per output against the fp32 product of the same bf16 inputs, with a
+    tolerance scaled by each row's own |x| . |w| bound rather than by the largest output."""
+    k_ = K()
+    torch.manual_seed(11 + m)
+    n, k = 768, 2048
+    w = torch.randn(n, k) * 0.02
+    q, s = Q.quantize_rtn(w)
+    w4b = Q.to_w4b(q, s).cuda()
+    wd = Q.dequant(q, s)
+    x = torch.randn(m, k)
+    x[:, 5] = 300.0          # one massive channel in group 0
+    x[:, 1031] = -450.0      # another in group 16
+    x[0, 64:128] = 0.0       # an all-zero group
+    x = x.to(torch.bfloat16)
+    splits = k_.gemv_splits(n, k)
+    out = torch.full((splits, m, n), float("nan"), device="cuda")
+    k_.gemv_w4(w4b, x.cuda(), out, m, n, k, splits)
+    torch.cuda.synchronize()
+    k_.check_status()
+    got = out.sum(0).cpu()
+    ref = x.float() @ wd.t()
+    assert torch.isfinite(got).all()
+    # error budget per group: |w| . (group max |x|) * 64 / 2^14 (half a quantisation step of every element)
+    xg = x.float().abs().view(m, k // 64, 64).amax(dim=2)                       # [m][groups]
+    wg = wd.abs().view(n, k // 64, 64).sum(dim=2)                               # [n][groups]
+    bound = (xg @ wg.t()) / 16383.0 * 0.5 + 1e-5 * ref.abs()                    # [m][n]
+    assert ((got - ref).abs() <= bound + 1e-4).all(), float(((got - ref).abs() / (bound + 1e-4)).max())
+    # and the groups without an outlier keep their own precision: zero the outlier channels, the rest must agree tightly
+    x2 = x.clone()
+    x2[:, 5] = 0
+    x2[:, 1031] = 0
+    out2 = torch.zeros(splits, m, n, device="cuda")
+    k_.gemv_w4(w4b, x2.cuda(), out2, m, n, k, splits)
+    ref2 = x2.float() @ wd.t()
+    assert (out2.sum(0).cpu() - ref2).abs().max() <= 2e-3 * ref2.abs().max() + 1e-4
+
+
 def test_gemv_w4_rows_do_not_depend_on_m():
     """Property R: a row's bits are the same whether it runs alone or among other rows."""
     k_ = K()

@@ -17,6 +17,19 @@ def K():
     return lib
 
 
+def _rowwise_close(got, ref, cos_min=0.9995, tile=32, tile_tol=0.03):
+    """Per-row cosine and per-32-column-piece error against the piece's own scale: a wrong piece of small values does
+    not hide behind the tensor's largest element."""
+    cos = torch.nn.functional.cosine_similarity(got.float(), ref.float(), dim=1)
+    assert float(cos.min()) > cos_min, float(cos.min())
+    m, n = ref.shape
+    n32 = n // tile * tile
+    g = got.float()[:, :n32].reshape(m, n32 // tile, tile)
+    r = ref.float()[:, :n32].reshape(m, n32 // tile, tile)
+    scale = r.abs().amax(dim=2).clamp_min(float(ref.abs().mean()))
+    assert float(((g - r).abs().amax(dim=2) / scale).max()) < tile_tol
+
+
 @pytest.mark.parametrize("m,n,k,bn", [(128, 256, 64, 256), (128, 128, 64, 128), (256, 512, 256, 256),
                                       (200, 384, 192, 128), (4096, 1024, 512, 256), (77, 264, 128, 0),
                                       (1000, 5120, 1024, 0)])
@@ -31,6 +44,7 @@ def test_gemm_bf16(m, n, k, bn):
     ref = a.float() @ b.float().t()
     assert torch.isfinite(c.float()).all()
     assert (c.float() - ref).abs().max() <= 1e-2 * ref.abs().max()
+    _rowwise_close(c, ref)      # every 32-column piece against its own scale, every row's direction
 
 
 def test_gemm_bf16_epilogues():
@@ -49,6 +63,7 @@ def test_gemm_bf16_epilogues():
     v = ref.reshape(m, n // 32, 2, 16)
     want = (torch.nn.functional.silu(v[:, :, 0]) * v[:, :, 1]).reshape(m, n // 2)
     assert (cs.float() - want).abs().max() <= 1e-2 * want.abs().max() + 1e-3
+    _rowwise_close(cs, want, tile=16, tile_tol=0.05)
     # residual add, in place
     r = torch.randn(m, n, device="cuda").to(torch.bfloat16)
     want = (r.float() + ref)
@@ -56,6 +71,7 @@ def test_gemm_bf16_epilogues():
     torch.cuda.synchronize()
     K().check_status()
     assert (r.float() - want).abs().max() <= 1e-2 * want.abs().max()
+    _rowwise_close(r, want)
 
 
 @pytest.mark.parametrize("m,n,k", [(128, 256, 128), (333, 640, 512), (2048, 1024, 1024)])
@@ -120,21 +136,9 @@ def test_gemm_grouped():
     for ex, r0, rn in zip(blk_e, blk_r0, blk_n):
         ref = a[r0:r0 + rn].float() @ b[ex].float().t()
         assert (c[r0:r0 + rn].float() - ref).abs().max() <= 1e-2 * ref.abs().max()
+        _rowwise_close(c[r0:r0 + rn], ref)
     # rows beyond a block's valid count are not written
     assert (c[130:256] == 0).all()
-
-
-def _rowwise_close(got, ref, cos_min=0.9995, tile=32, tile_tol=0.03):
-    """Per-row cosine and per-32-column-piece error against the piece's own scale: a wrong piece of small values does
-    not hide behind the tensor's largest element."""
-    cos = torch.nn.functional.cosine_similarity(got.float(), ref.float(), dim=1)
-    assert float(cos.min()) > cos_min, float(cos.min())
-    m, n = ref.shape
-    n32 = n // tile * tile
-    g = got.float()[:, :n32].reshape(m, n32 // tile, tile)
-    r = ref.float()[:, :n32].reshape(m, n32 // tile, tile)
-    scale = r.abs().amax(dim=2).clamp_min(float(ref.abs().mean()))
-    assert float(((g - r).abs().amax(dim=2) / scale).max()) < tile_tol
 
 
 @pytest.mark.parametrize("m,n,k,bn", [(128, 256, 64, 256), (128, 128, 128, 128), (300, 512, 256, 256),

@@ -121,3 +121,40 @@ def test_expert_parallel_decode_rows_single_rank_match_plain():
     assert err < 0.02 * scale, err        # the returned rows are bf16 where the plain path folds fp32 slices
     assert agree >= 7, agree
     ep.close()
+
+
+def test_reduce_scatter_fold_error_with_eight_sources():
+    """The owner's fold adds bf16 partial tiles from every source rank to the residual row in fp32 and rounds once.
+    One rank, eight landing slots filled by hand: the result against the fp32 sum of the UNROUNDED partials stays
+    inside the rounding of the eight bf16 partials plus the final rounding, and equals the fp32 sum of the rounded
+    partials to the last bit (fixed source order)."""
+    from b200serve.ops import lib as K
+    from b200serve.parallel.symm import Wire
+    torch.manual_seed(21)
+    nsrc, h, tpr, c = 8, 1024, 1, 100
+    rows_cap = tpr * 128
+    rs = Wire(nsrc * rows_cap * h * 2, nsrc * tpr, 0, None, torch.device("cuda"))
+    xw = Wire(rows_cap * h * 2, tpr, 0, None, torch.device("cuda"))
+    part32 = torch.randn(nsrc, rows_cap, h, device="cuda") * 0.7          # what the GEMMs would hold in fp32
+    part16 = part32.to(torch.bfloat16)
+    rs.buf.view(torch.bfloat16, 0, nsrc * rows_cap * h).copy_(part16.view(-1))
+    rs.flags.fill_(5)                                                       # every tile of every source has arrived
+    resid0 = (torch.randn(rows_cap, h, device="cuda") * 2.0).to(torch.bfloat16)
+    resid = resid0.clone()
+    norm_w = torch.ones(h, device="cuda")
+    done = torch.zeros(tpr, dtype=torch.int32, device="cuda")
+    K.rs_fold(rs, 5, nsrc, done, resid, norm_w, 1e-6, xw, h, tpr, c)
+    torch.cuda.synchronize()
+    K.check_status()
+    exact_rounded = resid0[:c].float()
+    for s_ in range(nsrc):                                                  # the kernel's order: residual, then sources 0..7
+        exact_rounded = exact_rounded + part16[s_, :c].float()
+    assert torch.equal(resid[:c], exact_rounded.to(torch.bfloat16))
+    true = resid0[:c].float() + part32[:, :c].sum(0)
+    err = (resid[:c].float() - true).abs()
+    bound = part32[:, :c].abs().sum(0) * 2.0 ** -9 + true.abs() * 2.0 ** -8 + 1e-6
+    assert (err <= bound).all()
+    rel = float(err.max() / true.abs().max())
+    assert rel < 4e-3, rel          # bf16 transport of 8 partials costs a few 1e-3 of the row's scale
+    rs.close()
+    xw.close()
