@@ -152,7 +152,8 @@ def test_reduce_scatter_fold_error_with_eight_sources():
     assert torch.equal(resid[:c], exact_rounded.to(torch.bfloat16))
     true = resid0[:c].float() + part32[:, :c].sum(0)
     err = (resid[:c].float() - true).abs()
-    bound = part32[:, :c].abs().sum(0) * 2.0 ** -9 + true.abs() * 2.0 ** -8 + 1e-6
+    # bf16 keeps 8 significant bits: unit roundoff 2^-8 for each partial and for the stored result
+    bound = part32[:, :c].abs().sum(0) * 2.0 ** -8 + (true.abs() + 0.1) * 2.0 ** -8 + 1e-6
     assert (err <= bound).all()
     rel = float(err.max() / true.abs().max())
     assert rel < 4e-3, rel          # bf16 transport of 8 partials costs a few 1e-3 of the row's scale
