@@ -36,8 +36,8 @@ using namespace b2;
 namespace {
 
 constexpr int kBlockBytes = 4352;
-constexpr int kG = 2;  // quantisation groups (W4B blocks) per ring stage
-constexpr int kStages = 8;
+constexpr int kG = 4;  // quantisation groups (W4B blocks) per ring stage: per-stage waits and hand-backs are paid per 17 KB
+constexpr int kStages = 4;
 constexpr int kStageBytes = kG * kBlockBytes;
 constexpr int kRingBytes = kStages * kStageBytes;
 constexpr int kConsumerThreads = 256;
@@ -269,6 +269,12 @@ __global__ void __launch_bounds__(kThreads, (T <= 2 ? 2 : 1)) gemv_w4_kernel(con
   const uint32_t gsB = (p.xcg * 8 * T * 8 + 127) & ~127;   // bytes of one buffer's group scales
   const uint32_t xsB = (uint32_t)p.rows * strideB;          // bytes of one buffer's rows
 
+  // One token tile (M <= 8): the eight consumer warps form two groups of four that take alternate ring stages, a warp
+  // owning 32 rows of the block as two 16-row tiles.  Two stages of a CTA (four of an SM) are then in work at a time
+  // and a warp has twice the independent MMA chains per wait; with all eight warps on every stage the loop was bound
+  // by the latency of one stage's wait -> load -> MMA -> hand-back chain, not by HBM.
+  constexpr bool kSplit = T == 1;
+  constexpr int RT = kSplit ? 2 : 1;   // row tiles per warp
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int nblk = blockIdx.x, split = blockIdx.y;
   if (p.skip_negative) {   // the ids are the previous kernel's output
@@ -283,7 +289,7 @@ __global__ void __launch_bounds__(kThreads, (T <= 2 ? 2 : 1)) gemv_w4_kernel(con
   if (tid == 0) {
     for (int i = 0; i < kStages; ++i) {
       mbar_init(full0 + 8 * i, 1);
-      mbar_init(empty0 + 8 * i, 8);
+      mbar_init(empty0 + 8 * i, kSplit ? 4 : 8);   // warps that hand a stage back
     }
     if (p.x_mode == 3) {
       for (int i = 0; i < 2; ++i) {
@@ -368,15 +374,17 @@ __global__ void __launch_bounds__(kThreads, (T <= 2 ? 2 : 1)) gemv_w4_kernel(con
 
   const uint8_t* xbase = reinterpret_cast<const uint8_t*>(p.x) + (size_t)(blockIdx.z / p.x_div) * p.x_batch_bytes;
   const int g = lane >> 2, t = lane & 3;
-  float acc[T][4];
+  float acc[T * RT][4];
 #pragma unroll
-  for (int i = 0; i < T; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+  for (int i = 0; i < T * RT; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
   bool ok = true;
+  const int wgrp = kSplit ? (warp >> 2) : 0;            // stage parity this warp serves
+  const int row16 = kSplit ? (warp & 3) * 2 : warp;     // first 16-row tile of the warp
 
   // per-thread constant offsets.  A token row beyond the staged rows aliases the last staged row:
   // column j of the MMA result depends on token j alone, and columns of absent tokens are not stored.
-  const uint32_t w_off = warp * 512 + lane * 16;
-  const uint32_t sc_off = 4096 + (warp * 16 + 2 * g) * 2;
+  const uint32_t w_off = row16 * 512 + lane * 16;
+  const uint32_t sc_off = 4096 + (row16 * 16 + 2 * g) * 2;
   uint32_t x_row[T];
 #pragma unroll
   for (int tt = 0; tt < T; ++tt) x_row[tt] = xs0 + min(tt * 8 + g, p.rows - 1) * strideB + t * 32;
@@ -438,6 +446,7 @@ __global__ void __launch_bounds__(kThreads, (T <= 2 ? 2 : 1)) gemv_w4_kernel(con
     // wait and never a deadlock.
     for (int gi = 0; gi < cg; gi += kG) {
       const int i = (c0 + gi) / kG;  // stage index since kernel start
+      if (kSplit && (i & 1) != wgrp) continue;   // the other group's stage
       const int s = i % kStages;
       if (ok) ok = mbar_wait(full0 + 8 * s, (i / kStages) & 1, ERR_GEMV_FULL_WAIT);
       if (!ok) continue;
@@ -446,12 +455,25 @@ __global__ void __launch_bounds__(kThreads, (T <= 2 ? 2 : 1)) gemv_w4_kernel(con
 #pragma unroll
       for (int tt = 0; tt < T; ++tt) xa[tt] = x_row[tt] + xb * xsB + gi * 128;
       const uint32_t gsa = gs_t + xb * gsB;
-      if (gi + 1 < cg) group_mma<T, (T <= 2 ? 2 : 1)>(acc, st, w_off, sc_off, xa, gsa + gi * 8 * T * 8);
-      else group_mma<T, 1>(acc, st, w_off, sc_off, xa, gsa + gi * 8 * T * 8);
-      if (T > 2 && gi + 1 < cg) {
+      const int ng = min(kG, cg - gi);   // groups of this stage
+      constexpr int NGq = T <= 2 ? 2 : 1;   // groups whose MMA chains are interleaved
+#pragma unroll 1
+      for (int q0 = 0; q0 < ng; q0 += NGq) {
+        if (kSplit) {
+          float (&a0)[1][4] = *reinterpret_cast<float (*)[1][4]>(&acc[0]);
+          float (&a1)[1][4] = *reinterpret_cast<float (*)[1][4]>(&acc[T]);
+          const uint32_t (&xa1)[1] = *reinterpret_cast<const uint32_t (*)[1]>(&xa[0]);
+          if (q0 + 1 < ng) {
+            group_mma<1, 2>(a0, st + q0 * kBlockBytes, w_off, sc_off, xa1, gsa + (gi + q0) * 8 * T * 8);
+            group_mma<1, 2>(a1, st + q0 * kBlockBytes, w_off + 512, sc_off + 32, xa1, gsa + (gi + q0) * 8 * T * 8);
+          } else {
+            group_mma<1, 1>(a0, st + q0 * kBlockBytes, w_off, sc_off, xa1, gsa + (gi + q0) * 8 * T * 8);
+            group_mma<1, 1>(a1, st + q0 * kBlockBytes, w_off + 512, sc_off + 32, xa1, gsa + (gi + q0) * 8 * T * 8);
+          }
+        } else if (NGq == 2 && q0 + 1 < ng) group_mma<T, NGq>(*reinterpret_cast<float (*)[T][4]>(&acc[0]), st + q0 * kBlockBytes, w_off, sc_off, xa, gsa + (gi + q0) * 8 * T * 8);
+        else group_mma<T, 1>(*reinterpret_cast<float (*)[T][4]>(&acc[0]), st + q0 * kBlockBytes, w_off, sc_off, xa, gsa + (gi + q0) * 8 * T * 8);
 #pragma unroll
-        for (int tt = 0; tt < T; ++tt) xa[tt] += 128;
-        group_mma<T, 1>(acc, st + kBlockBytes, w_off, sc_off, xa, gsa + (gi + 1) * 8 * T * 8);
+        for (int tt = 0; tt < T; ++tt) xa[tt] += 128 * NGq;
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(empty0 + 8 * s);
@@ -463,18 +485,43 @@ __global__ void __launch_bounds__(kThreads, (T <= 2 ? 2 : 1)) gemv_w4_kernel(con
   }
 
   // ---- write this split's partial sums
-  const int n_lo = nblk * 128 + warp * 16 + g, n_hi = n_lo + 8;
   float* outp = p.out + (size_t)blockIdx.z * p.out_batch + (size_t)split * p.M * p.ldo;
+  if (kSplit) {
+    // the two groups hold the sums of alternate stages of the same rows: they meet in shared memory (the ring is
+    // free now: every stage has been waited for and consumed), group 0 first, so the order of the sum is fixed
+    consumer_sync();
+    const uint32_t scr = ring + ((warp & 3) * 32 + lane) * 32;   // 8 floats per thread of a group
+    if (wgrp == 1) {
 #pragma unroll
-  for (int tt = 0; tt < T; ++tt) {
-    const int m0 = tt * 8 + 2 * t, m1 = m0 + 1;
-    if (m0 < p.M) {
-      if (n_lo < p.N) outp[(size_t)m0 * p.ldo + n_lo] = acc[tt][0];
-      if (n_hi < p.N) outp[(size_t)m0 * p.ldo + n_hi] = acc[tt][2];
+      for (int h = 0; h < RT; ++h)
+        asm volatile("st.shared.v4.f32 [%0], {%1,%2,%3,%4};" ::"r"(scr + 16 * h), "f"(acc[h][0]), "f"(acc[h][1]), "f"(acc[h][2]), "f"(acc[h][3]) : "memory");
     }
-    if (m1 < p.M) {
-      if (n_lo < p.N) outp[(size_t)m1 * p.ldo + n_lo] = acc[tt][1];
-      if (n_hi < p.N) outp[(size_t)m1 * p.ldo + n_hi] = acc[tt][3];
+    consumer_sync();
+    if (wgrp == 0) {
+#pragma unroll
+      for (int h = 0; h < RT; ++h) {
+        float4 o;
+        asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(o.x), "=f"(o.y), "=f"(o.z), "=f"(o.w) : "r"(scr + 16 * h));
+        acc[h][0] += o.x; acc[h][1] += o.y; acc[h][2] += o.z; acc[h][3] += o.w;
+      }
+    }
+  }
+#pragma unroll
+  for (int h = 0; h < RT; ++h) {
+    if (kSplit && wgrp != 0) break;
+    const int n_lo = nblk * 128 + (row16 + h) * 16 + g, n_hi = n_lo + 8;
+#pragma unroll
+    for (int tt = 0; tt < T; ++tt) {
+      const int m0 = tt * 8 + 2 * t, m1 = m0 + 1;
+      const float (&a)[4] = acc[kSplit ? h : tt];
+      if (m0 < p.M) {
+        if (n_lo < p.N) outp[(size_t)m0 * p.ldo + n_lo] = a[0];
+        if (n_hi < p.N) outp[(size_t)m0 * p.ldo + n_hi] = a[2];
+      }
+      if (m1 < p.M) {
+        if (n_lo < p.N) outp[(size_t)m1 * p.ldo + n_lo] = a[1];
+        if (n_hi < p.N) outp[(size_t)m1 * p.ldo + n_hi] = a[3];
+      }
     }
   }
   if (p.fold_tickets == nullptr) return;
@@ -613,11 +660,11 @@ int launch_t(GemvParams& p, cudaStream_t stream) {
   while (rows < p.M) rows *= 2;
   p.rows = rows;
   int xcg = (kXBudget / (rows * 2) - 8) / 64;
-  xcg &= ~1;
+  xcg &= ~(kG - 1);
   if (xcg > 160) xcg = 160;   // keeps two CTAs per SM at one staged row
-  if (p.x_mode == 3) xcg = (xcg / 2) & ~1;   // two buffers
+  if (p.x_mode == 3) xcg = (xcg / 2) & ~(kG - 1);   // two buffers
   if (xcg > p.gps) xcg = p.gps;
-  if (xcg < 2) xcg = 2;
+  if (xcg < kG) xcg = kG;
   p.xcg = xcg;
   const int nbuf = p.x_mode == 3 ? 2 : 1;
   const int smem = 128 + kRingBytes + 128 + 256 + nbuf * (((xcg * 8 * T * 8 + 127) & ~127) + rows * stride_words(xcg) * 4);
@@ -625,7 +672,9 @@ int launch_t(GemvParams& p, cudaStream_t stream) {
   int dev = 0;
   cudaGetDevice(&dev);
   if (configured[dev & 63] < smem) {
-    const int want = 128 + kRingBytes + 128 + 256 + 16384 + kXBudget + 4096;
+    int want = 128 + kRingBytes + 128 + 256 + 16384 + kXBudget + 4096;
+    if (want < smem) want = smem;   // many rows with two activation buffers of at least one stage's groups each
+    if (want > 232448) return -7;
     cudaError_t e = cudaFuncSetAttribute(gemv_w4_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, want);
     if (e != cudaSuccess) return (int)e;
     configured[dev & 63] = want;
