@@ -129,7 +129,18 @@ class Engine:
     def _ensure_pages(self, slot: int, upto_len: int):
         if upto_len > self.max_len:
             raise ValueError(f"sequence of {upto_len} positions exceeds max_len {self.max_len}")
-        changed = self.pool.ensure(slot, (upto_len + PAGE - 1) // PAGE)
+        want = (upto_len + PAGE - 1) // PAGE
+        try:
+            changed = self.pool.ensure(slot, want)
+        except MemoryError:
+            # the pool is short of pages: whoever keeps finished sessions and cached blocks on the device (the prefix
+            # store) gives some back -- cached blocks go to the host tier, idle sessions leave, least recently used
+            # first -- and the request goes on; only when that does not cover it does the request fail
+            hook = getattr(self, "on_pool_pressure", None)
+            need = want - len(self.pool.table(slot))
+            if hook is None or not hook(slot, need):
+                raise
+            changed = self.pool.ensure(slot, want)
         if changed:
             row = self.pool.table(slot)
             host = self.table_stage.begin()

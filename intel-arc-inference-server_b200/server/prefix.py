@@ -140,6 +140,11 @@ class PrefixStore:
         self.host_owner: Dict[int, int] = {}        # host slot -> node
         self.resident: Dict[int, List[int]] = {}     # engine slot -> ids whose KV the slot still holds
         self.stats = {"hits": 0, "restored_blocks": 0, "continued": 0, "spilled": 0, "evicted": 0, "inserted": 0}
+        self._ended: Dict[int, int] = {}      # slot -> when its request ended (idle sessions, for make_room)
+        self._clock = 0
+        eng = getattr(self.kv, "e", None)
+        if eng is not None:
+            eng.on_pool_pressure = self.make_room     # a request that needs pages the pool lacks asks here first
 
     # ------------------------------------------------------------------ scheduling hint
     def preferred_slot(self, ids: Sequence[int]) -> int:
@@ -159,6 +164,7 @@ class PrefixStore:
         """Leaves ``slot`` holding the longest cached prefix of ``prompt``; returns its length in tokens."""
         prompt = [int(t) for t in prompt]
         res = self.resident.pop(slot, [])
+        self._ended.pop(slot, None)
         plan = self.ix.plan(self.root, prompt, res, split_last)
         kind, matched = plan["kind"], plan["matched_tokens"]
         if kind == "continue":
@@ -220,6 +226,26 @@ class PrefixStore:
         ids = self._held(slot, ids)
         self._insert_blocks(slot, ids)
         self.resident[slot] = ids
+        self._clock += 1
+        self._ended[slot] = self._clock          # an idle session from now on: its pages may be taken back
+
+    def make_room(self, slot: int, n_pages: int) -> bool:
+        """Called when the page pool cannot give ``slot`` the ``n_pages`` more it needs (the role of the reference
+        scheduler's make_room / evict, src/server/scheduler.cc:940-1010).  First cached blocks leave the device tier
+        (to the host tier when there is one), least recently used first; then the sessions of finished requests
+        that still sit in their slots leave, oldest first: their whole blocks stay in the index (a later turn restores
+        them), the partly filled last block is dropped.  True when the pages are free afterwards."""
+        self._make_room(n_pages)
+        while self.kv.free_pages() < n_pages and self._ended:
+            victim = min((s for s in self._ended if s != slot), key=lambda s: self._ended[s], default=None)
+            if victim is None:
+                break
+            del self._ended[victim]
+            self.resident.pop(victim, None)
+            self.kv.set_slot(victim, [], 0)
+            self.stats["idle_evicted"] = self.stats.get("idle_evicted", 0) + 1
+            self._make_room(n_pages)          # the session's shared blocks are unreferenced now and may spill
+        return self.kv.free_pages() >= n_pages
 
     def _insert_blocks(self, slot: int, ids: List[int]):
         pages = self.kv.slot_pages(slot)

@@ -173,3 +173,33 @@ def test_split_last_keeps_one_more_position_out():
     assert ix.plan(root, ids, [], False)["matched_tokens"] == 32
     # split_last: the match must end before position n - 2 as well, so the second block no longer fits
     assert ix.plan(root, ids, [], True)["matched_tokens"] == 16
+
+
+def test_pool_pressure_spills_cached_blocks_then_evicts_idle_sessions():
+    """A request that needs more pages than the pool has free: cached blocks leave the device tier first, then the
+    sessions of finished requests leave their slots, least recently ended first; the running request itself and the
+    requesting slot are never touched, and a later turn of an evicted session finds its whole blocks in the index."""
+    kv = FakeKV(num_pages=24, slots=4)
+    st = PrefixStore(kv, host_gb=1e-6 * 40, block_tokens=32, device_fraction=0.9)
+    a, b = list(range(1000, 1100)), list(range(2000, 2100))        # 100 tokens each: 7 pages, 3 whole blocks
+    run(st, kv, 0, a)
+    run(st, kv, 1, b)
+    free0 = kv.free_pages()
+    assert 0 < free0 <= 24 - 14
+    # slot 2 is a running request that grows past what is free
+    c = list(range(3000, 3000 + 16 * free0))
+    st.begin(2, c)
+    kv.prefill(2, c)                                               # takes every free page
+    assert kv.free_pages() == 0
+    assert st.make_room(2, 4)
+    assert kv.free_pages() >= 4
+    assert st.stats["spilled"] + st.stats.get("idle_evicted", 0) > 0
+    assert kv.slot_pages(2) and kv.seq_len[2] == len(c)            # the running request kept everything
+    # everything idle may go when more is asked for; what cannot be covered is reported
+    assert st.make_room(2, 12)
+    assert not st.make_room(2, 100)
+    assert 0 not in st.resident and 1 not in st.resident           # both idle sessions left their slots
+    # the first session's whole blocks are still known: its next turn restores them (from the host tier here)
+    cached = st.begin(3, a + [7, 7, 7])
+    assert cached in (0, 32, 64, 96)
+    kv.check(3, a, cached)
