@@ -55,6 +55,7 @@ class StepBuffers:
         self.flag = torch.zeros(4, dtype=torch.int32, device=device)
         self.tickets = torch.zeros(max_rows * cfg.n_kv_heads, dtype=torch.int32, device=device)
         self.fold_tickets = torch.zeros((h + 127) // 128, dtype=torch.int32, device=device)
+        self.qkv_tickets = torch.zeros(max((cfg.qkv_dim + 127) // 128, 8), dtype=torch.int32, device=device)   # per head of the qkv projection
         self.ssq = torch.zeros(max_rows * ((h + 127) // 128), dtype=f32, device=device)
         kmax = max(2 * h, cfg.q_dim, cfg.ffn, cfg.expert_ffn, cfg.shared_ffn, cfg.gdn_value_dim)
         if cfg.n_gdn_layers:
@@ -170,6 +171,10 @@ class DecoderModel:
         # step against 5.1 ms for the launch-per-linear walk, whose several CTAs per SM hide the latency of the
         # fold / barrier chain between two linears better than one resident CTA per SM does
         self.use_mega = os.environ.get("B2_MEGA", "0") == "1"
+        # the qkv projection's last split CTA per head can apply RoPE and append K / V itself (bf16 cache, head size
+        # 128): one launch fewer per layer.  Measured neutral on the 27B step (4.73 vs 4.70 ms: the fold's latency
+        # replaces the small kernel's), so it is opt-in
+        self.rope_fold = os.environ.get("B2_ROPE_FOLD", "0") == "1"
         self.ep = None      # parallel.ep.EpMoe with the row form enabled: MoE layers of a decode step go through it
         self.mega_cooperative = os.environ.get("B2_MEGA_COOP", "1") != "0"
         self._mega_bufs = {}
@@ -263,6 +268,24 @@ class DecoderModel:
                         tp_mcap=self.tp.mcap if self.tp is not None else 0)
         return part, s
 
+    def _qkv_rope(self, lw: LayerWeights, m: int, ctrl, block_table, max_blocks, kc, vc, x_ready: bool):
+        """qkv projection + RoPE + KV append in one launch (the GEMV's last split CTA per head does the rest)."""
+        cfg, b = self.cfg, self.buf
+        ql = lw.qkv
+        key = (ql.n, ql.k)
+        s = self._splits.get(key)
+        if s is None:
+            s = self._splits[key] = K.gemv_splits(ql.n, ql.k)
+        part = b.part("qkv", s, ql.n)
+        x, x_mode, norm_w, aux = (b.x, 0, None, None) if x_ready else (b.resid, 2, lw.input_norm, b.ssq)
+        if m >= self.prequant_rows:
+            K.quant_x(x, m, ql.k, b.xq, b.xq_gs, x_mode=x_mode, norm_w=norm_w, norm_ssq=aux, norm_eps=cfg.rms_eps)
+            x, x_mode, norm_w, aux = b.xq, 3, None, b.xq_gs
+        K.gemv_w4_qkv_rope(ql.w4b, x, part, m, ql.k, s, x_mode=x_mode, norm_w=norm_w, norm_ssq=aux, norm_eps=cfg.rms_eps,
+                           tickets=b.qkv_tickets, q_out=b.q, cos_t=self.cos_t, sin_t=self.sin_t, ctrl=ctrl,
+                           block_table=block_table, max_blocks=max_blocks, n_q=ql.n // 128 - 2 * cfg.n_kv_heads,
+                           n_kv=cfg.n_kv_heads, k_plane=kc, v_plane=vc)
+
     def dense_layer_fused(self, lw: LayerWeights, li: int, m: int, ctrl, block_table, max_blocks, kv: KVCache,
                           x_ready: bool):
         """One dense layer in six launches: the residual folds ride in the o / down GEMVs' last CTAs and the
@@ -270,13 +293,16 @@ class DecoderModel:
         the normalised input (first layer, after the embedding kernel); otherwise ``buf.resid`` and
         ``buf.ssq`` do."""
         cfg, b = self.cfg, self.buf
-        if x_ready:
-            part, s = self._gemv("qkv", lw.qkv, b.x, m)
-        else:
-            part, s = self._gemv_fused("qkv", lw.qkv, b.resid, m, norm_w=lw.input_norm, x_mode=2)
         kc, vc, ks, vs = kv.layer(li)
-        K.rope_append(part, m * cfg.qkv_dim, s, m, ctrl, block_table, max_blocks, self.cos_t, self.sin_t,
-                      cfg.n_q_heads, cfg.n_kv_heads, cfg.head_dim, b.q, kc, vc, ks, vs, kv.kv_int8)
+        if self.rope_fold and not kv.kv_int8 and cfg.head_dim == 128 and lw.qkv.n == cfg.qkv_dim:
+            self._qkv_rope(lw, m, ctrl, block_table, max_blocks, kc, vc, x_ready)
+        else:
+            if x_ready:
+                part, s = self._gemv("qkv", lw.qkv, b.x, m)
+            else:
+                part, s = self._gemv_fused("qkv", lw.qkv, b.resid, m, norm_w=lw.input_norm, x_mode=2)
+            K.rope_append(part, m * cfg.qkv_dim, s, m, ctrl, block_table, max_blocks, self.cos_t, self.sin_t,
+                          cfg.n_q_heads, cfg.n_kv_heads, cfg.head_dim, b.q, kc, vc, ks, vs, kv.kv_int8)
         self._attention(m, ctrl, block_table, max_blocks, kv, kc, vc, ks, vs, self._window(li))
         self._gemv_fused("o", lw.o, b.attn_out, m, fold=True)
         gu, s_gu = self._gemv_fused("gate_up", lw.gate_up, b.resid, m, norm_w=lw.post_norm, x_mode=2)

@@ -36,6 +36,7 @@ using namespace b2;
 namespace {
 
 constexpr int kBlockBytes = 4352;
+constexpr int CTRL_ROW_REQ = 16, CTRL_ROW_POS = 80;   // control block words (ops/lib.py)
 constexpr int kG = 4;  // quantisation groups (W4B blocks) per ring stage: per-stage waits and hand-backs are paid per 17 KB
 constexpr int kStages = 4;
 constexpr int kStageBytes = kG * kBlockBytes;
@@ -68,6 +69,16 @@ struct GemvParams {
   const __nv_bfloat16* fold_resid_in;    // [M][N]
   __nv_bfloat16* fold_resid_out;         // [M][N] (may alias fold_resid_in)
   float* fold_ssq;                       // [M][nb]
+  // fused RoPE + KV append (the qkv projection, head size 128, bf16 cache): the last split CTA of an n-block (= one
+  // head) sums the slices in split order, rotates q / k heads and writes q rows or the row's slot of the paged cache
+  __nv_bfloat16* rope_q;                 // [M][n_q * 128], or nullptr: no such fold
+  const float* rope_cos;                 // [position][64]
+  const float* rope_sin;
+  const int* rope_ctrl;                  // control block: request and position of every row
+  const int* rope_block_table;
+  int rope_max_blocks, rope_n_q, rope_n_kv;
+  __nv_bfloat16* rope_k;                 // the layer's planes [page][n_kv][16][128]
+  __nv_bfloat16* rope_v;
   // fused RMSNorm (consumer side, x_mode 2): x = bf16(resid * rsqrt(sum(ssq) / K + eps) * norm_w)
   const float* norm_w;                   // [K]
   const float* norm_ssq;                 // [M][norm_nb]
@@ -543,6 +554,51 @@ __global__ void __launch_bounds__(kThreads, (T <= 2 ? 2 : 1)) gemv_w4_kernel(con
   __threadfence();
   const int nb_total = (p.N + 127) / 128;
   const int items = p.M * 128;
+  if (p.rope_q != nullptr) {
+    // the head's 128 columns of every row, summed in split order, meet in shared memory (the ring is free) so that
+    // column d finds its rotate-half partner d +- 64
+    for (int idx0 = 0; idx0 < items; idx0 += kConsumerThreads) {
+      const int idx = idx0 + tid;
+      if (idx < items) {
+        const int m = idx >> 7, c = idx & 127, n = nblk * 128 + c;
+        float v[16];
+#pragma unroll
+        for (int sp = 0; sp < 16; ++sp) v[sp] = sp < p.S ? __ldcg(p.out + ((size_t)sp * p.M + m) * p.ldo + n) : 0.f;
+        float x = 0.f;
+#pragma unroll
+        for (int sp = 0; sp < 16; ++sp) x += v[sp];
+        asm volatile("st.shared.f32 [%0], %1;" ::"r"(ring + idx * 4), "f"(x) : "memory");
+      }
+    }
+    consumer_sync();
+    const int head = nblk;
+    for (int idx0 = 0; idx0 < items; idx0 += kConsumerThreads) {
+      const int idx = idx0 + tid;
+      if (idx >= items) continue;
+      const int m = idx >> 7, c = idx & 127, j = c & 63;
+      float x1, x2;
+      asm volatile("ld.shared.f32 %0, [%1];" : "=f"(x1) : "r"(ring + (m * 128 + j) * 4));
+      asm volatile("ld.shared.f32 %0, [%1];" : "=f"(x2) : "r"(ring + (m * 128 + j + 64) * 4));
+      const int req = p.rope_ctrl[CTRL_ROW_REQ + m], pos = p.rope_ctrl[CTRL_ROW_POS + m];
+      float y;
+      if (head < p.rope_n_q + p.rope_n_kv) {
+        const float cs = p.rope_cos[(size_t)pos * 64 + j], sn = p.rope_sin[(size_t)pos * 64 + j];
+        y = c < 64 ? x1 * cs - x2 * sn : x2 * cs + x1 * sn;
+      } else {
+        y = c < 64 ? x1 : x2;
+      }
+      if (head < p.rope_n_q) {
+        p.rope_q[(size_t)m * p.rope_n_q * 128 + (size_t)head * 128 + c] = __float2bfloat16(y);
+      } else {
+        const bool is_v = head >= p.rope_n_q + p.rope_n_kv;
+        const int kh = head - p.rope_n_q - (is_v ? p.rope_n_kv : 0);
+        const int page = p.rope_block_table[(size_t)req * p.rope_max_blocks + (pos >> 4)];
+        __nv_bfloat16* dst = (is_v ? p.rope_v : p.rope_k) + (((size_t)page * p.rope_n_kv + kh) * 16 + (pos & 15)) * 128;
+        dst[c] = __float2bfloat16(y);
+      }
+    }
+    return;
+  }
   const bool tp = p.tp.world > 1;
   const float* land_me = nullptr;
   if (tp) {
@@ -709,7 +765,7 @@ extern "C" int b2_gemv_w4(const void* w4b, const void* x, float* out, int M, int
   p.x = x;
   p.out = out;
   p.batches = 1; p.expert_ids = nullptr; p.skip_negative = 0; p.expert_bytes = 0; p.x_div = 1; p.x_batch_bytes = 0; p.out_batch = 0;
-  p.fold_tickets = nullptr; p.fold_resid_in = nullptr; p.fold_resid_out = nullptr; p.fold_ssq = nullptr;
+  p.fold_tickets = nullptr; p.fold_resid_in = nullptr; p.fold_resid_out = nullptr; p.fold_ssq = nullptr; p.rope_q = nullptr;
   p.norm_w = nullptr; p.norm_ssq = nullptr; p.norm_nb = 0; p.norm_eps = 0.f;
   p.tp.table = nullptr; p.tp.epoch = nullptr; p.tp.world = 0; p.tp.rank = 0; p.tp_mcap = 0; p.xq_gs = nullptr;
   p.M = M; p.N = N; p.KG = K / 64; p.S = S;
@@ -746,12 +802,45 @@ extern "C" int b2_gemv_w4_fused(const void* w4b, const void* x, float* out, int 
   if (p.gps % kG != 0) p.gps += kG - p.gps % kG;
   p.ldx = ldx; p.ldo = N; p.x_mode = x_mode; p.s_in = s_in; p.x_slice = x_slice;
   p.batches = 1; p.expert_ids = nullptr; p.skip_negative = 0; p.expert_bytes = 0; p.x_div = 1; p.x_batch_bytes = 0; p.out_batch = 0;
+  p.rope_q = nullptr;
   p.fold_tickets = fold_tickets; p.fold_resid_in = (const __nv_bfloat16*)fold_resid_in;
   p.fold_resid_out = (__nv_bfloat16*)fold_resid_out; p.fold_ssq = fold_ssq;
   p.norm_w = norm_w; p.norm_ssq = norm_ssq; p.norm_nb = K / 128; p.norm_eps = norm_eps;
   p.tp.table = (const unsigned long long*)tp_table; p.tp.epoch = tp_epoch; p.tp.world = tp_world; p.tp.rank = tp_rank;
   p.tp_mcap = tp_mcap;
   p.xq_gs = reinterpret_cast<const uint32_t*>(norm_ssq);   // x_mode 3: the group scales ride in the norm_ssq slot
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (M <= 8) return launch_t<1>(p, st);
+  if (M <= 16) return launch_t<2>(p, st);
+  if (M <= 32) return launch_t<4>(p, st);
+  return launch_t<8>(p, st);
+}
+
+// The qkv projection with the RoPE / KV-append fold: heads of 128 dims, bf16 cache planes of the layer.  x_mode 0
+// (normalised rows), 2 (residual rows + RMSNorm) or 3 (pre-quantised rows, group scales in norm_ssq).
+extern "C" int b2_gemv_w4_qkv_rope(const void* w4b, const void* x, float* out, int M, int K, int S, int ldx, int x_mode,
+                                   const float* norm_w, const float* norm_ssq, float norm_eps, int* tickets, void* q_out,
+                                   const float* cos_t, const float* sin_t, const int* ctrl, const int* block_table,
+                                   int max_blocks, int n_q, int n_kv, void* k_plane, void* v_plane, void* stream) {
+  if (M < 1 || M > 64 || K % 64 != 0 || S < 1 || S > 16 || !tickets || !q_out || n_q < 1 || n_kv < 1) return -1;
+  if (x_mode == 2 && (K % 128 != 0 || !norm_w || !norm_ssq)) return -2;
+  if (x_mode == 3 && !norm_ssq) return -2;
+  GemvParams p;
+  p.w = reinterpret_cast<const uint8_t*>(w4b);
+  p.x = x;
+  p.out = out;
+  p.M = M; p.N = (n_q + 2 * n_kv) * 128; p.KG = K / 64; p.S = S;
+  p.gps = (p.KG + S - 1) / S;
+  if (p.gps % kG != 0) p.gps += kG - p.gps % kG;
+  p.ldx = ldx; p.ldo = p.N; p.x_mode = x_mode; p.s_in = 1; p.x_slice = 0;
+  p.batches = 1; p.expert_ids = nullptr; p.skip_negative = 0; p.expert_bytes = 0; p.x_div = 1; p.x_batch_bytes = 0; p.out_batch = 0;
+  p.fold_tickets = tickets; p.fold_resid_in = nullptr; p.fold_resid_out = nullptr; p.fold_ssq = nullptr;
+  p.norm_w = norm_w; p.norm_ssq = norm_ssq; p.norm_nb = K / 128; p.norm_eps = norm_eps;
+  p.tp.table = nullptr; p.tp.epoch = nullptr; p.tp.world = 0; p.tp.rank = 0; p.tp_mcap = 0;
+  p.xq_gs = reinterpret_cast<const uint32_t*>(norm_ssq);
+  p.rope_q = (__nv_bfloat16*)q_out; p.rope_cos = cos_t; p.rope_sin = sin_t; p.rope_ctrl = ctrl;
+  p.rope_block_table = block_table; p.rope_max_blocks = max_blocks; p.rope_n_q = n_q; p.rope_n_kv = n_kv;
+  p.rope_k = (__nv_bfloat16*)k_plane; p.rope_v = (__nv_bfloat16*)v_plane;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   if (M <= 8) return launch_t<1>(p, st);
   if (M <= 16) return launch_t<2>(p, st);
@@ -775,7 +864,7 @@ static int gemv_w4_experts_impl(const void* w4b_stack, long long expert_bytes, c
   p.ldx = ldx; p.ldo = N; p.x_mode = x_mode; p.s_in = s_in; p.x_slice = x_slice;
   p.batches = batches; p.expert_ids = expert_ids; p.expert_bytes = expert_bytes; p.x_div = x_div; p.skip_negative = skip_negative;
   p.x_batch_bytes = x_batch_bytes; p.out_batch = (long long)S * N;
-  p.fold_tickets = nullptr; p.fold_resid_in = nullptr; p.fold_resid_out = nullptr; p.fold_ssq = nullptr;
+  p.fold_tickets = nullptr; p.fold_resid_in = nullptr; p.fold_resid_out = nullptr; p.fold_ssq = nullptr; p.rope_q = nullptr;
   p.norm_w = nullptr; p.norm_ssq = nullptr; p.norm_nb = 0; p.norm_eps = 0.f;
   p.tp.table = nullptr; p.tp.epoch = nullptr; p.tp.world = 0; p.tp.rank = 0; p.tp_mcap = 0; p.xq_gs = nullptr;
   return launch_t<1>(p, reinterpret_cast<cudaStream_t>(stream));

@@ -167,6 +167,16 @@ def gemv_w4_fused(w4b, x, out, m, n, k, splits, *, x_mode=0, s_in=1, x_slice=0, 
     _check(rc, "gemv_w4_fused")
 
 
+def gemv_w4_qkv_rope(w4b, x, out, m, k, splits, *, x_mode, norm_w, norm_ssq, norm_eps, tickets, q_out, cos_t, sin_t, ctrl,
+                     block_table, max_blocks, n_q, n_kv, k_plane, v_plane):
+    """The qkv projection whose last split CTA per head also sums the slices, applies RoPE and writes the q rows / the
+    rows' slots of the paged bf16 cache (head size 128): the separate RoPE + append launch disappears."""
+    rc = lib().b2_gemv_w4_qkv_rope(_p(w4b), _p(x), _p(out), m, k, splits, k, x_mode, _p(norm_w), _p(norm_ssq),
+                                   ctypes.c_float(norm_eps), _p(tickets), _p(q_out), _p(cos_t), _p(sin_t), _p(ctrl),
+                                   _p(block_table), max_blocks, n_q, n_kv, _p(k_plane), _p(v_plane), _stream())
+    _check(rc, "gemv_w4_qkv_rope")
+
+
 def quant_slots(m: int) -> int:
     """Token slots per 64-k group in ``xq_gs`` for ``m`` rows: 8 per row tile of the GEMV (8, 16, 32 or 64)."""
     return 8 if m <= 8 else (16 if m <= 16 else (32 if m <= 32 else 64))

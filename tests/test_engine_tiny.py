@@ -148,3 +148,22 @@ def test_kv_snapshot_roundtrip_continues_identically():
     b = [eng.forward_rows([Row(1, 48, first)])[0]]
     b.append(eng.forward_rows([Row(1, 49, b[0])])[0])
     assert a == b
+
+
+@pytest.mark.gpu
+def test_qkv_gemv_with_rope_and_kv_append_fold_matches_separate_kernel():
+    """The qkv projection whose last split CTA per head applies RoPE and writes q / the KV slots itself, against the
+    same engine with the separate RoPE + append launch: same tokens, same logits bit for bit (same sums, same order)."""
+    from b200serve.models.config import small_dense
+    from b200serve.models.weights import random_weights
+    from b200serve.runtime.engine import Engine
+    cfg = small_dense()
+    w = _to_cuda(random_weights(cfg, seed=0))
+    g = torch.Generator().manual_seed(0)
+    prompt = torch.randint(0, cfg.vocab, (90,), generator=g).tolist()
+    a = Engine(w, max_seqs=1, max_len=512, use_graphs=False)
+    b = Engine(w, max_seqs=1, max_len=512, use_graphs=False)
+    b.model.rope_fold = True
+    ta, tb = a.generate(prompt, 16), b.generate(prompt, 16)
+    assert ta == tb
+    assert torch.equal(a.logits(1), b.logits(1))
