@@ -21,7 +21,7 @@ STEP_BUFFERS: Dict[str, Tuple[str, bool, bool]] = {
     "resid": ("step", False, False), "x": ("step", False, False), "q": ("step", False, False),
     "attn_out": ("step", False, False), "o_part": ("step", False, False), "ml_part": ("step", False, False),
     "logits": ("step", False, False), "cand_val": ("step", False, False), "cand_idx": ("step", False, False),
-    "flag": ("step", False, False), "tickets": ("step", False, False), "fold_tickets": ("step", False, False),
+    "flag": ("step", False, False), "tickets": ("step", False, False), "fold_tickets": ("step", False, False), "qkv_tickets": ("step", False, False),
     "ssq": ("step", False, False), "xq": ("step", False, False), "xq_gs": ("step", False, False),
     "gdn_act": ("step", False, False), "gdn_out": ("step", False, False),
 }
