@@ -55,6 +55,8 @@ struct AttnRowsParams {
   int M, n_q, n_kv, gqa, nsplit, max_blocks;
   int nbuf;        // 1: one K / V tile pair; 2: the next batch of keys is fetched while this one is multiplied
   int window;      // > 0: a row attends to its last `window` positions only (sliding-window layers)
+  int block;       // 1: the rows of a group form a block that attends to ALL of the group's positions (a block
+                   //    drafter's rows see one another, before and after: no causal mask inside the block)
   int one_slice;   // 1: never cut a batch's keys over idle warps (a row's bits then do not depend on the group's size)
   int span_pages;  // > 0: every split covers this many pages whatever the context (a row's bits then do not depend
                    // on which rows share its CTA); 0: the group's context is cut into nsplit equal parts
@@ -131,7 +133,7 @@ __device__ __forceinline__ void attn_rows_body(const AttnRowsParams& p, uint8_t*
     const int qr = rg * 16 + g + 8 * hf;
     const bool ok = qr < QR;
     const int m = z + (ok ? qr / p.gqa : 0), h = ok ? qr % p.gqa : 0;
-    ctx[hf] = ok ? s_pos[m] + 1 : 0;
+    ctx[hf] = ok ? (p.block ? ctx_max : s_pos[m] + 1) : 0;
     wlo[hf] = p.window > 0 ? ctx[hf] - p.window : 0;
     const __nv_bfloat16* qp = p.q + (size_t)m * p.n_q * D + (size_t)(kh * p.gqa + h) * D;
 #pragma unroll
@@ -533,6 +535,8 @@ extern "C" int b2_attn_rows(const void* q, const void* k_cache, const void* v_ca
   p.scale_log2 = scale * 1.4426950408889634f;
   p.span_pages = span_pages;
   p.window = window > 0 ? window : 0;
+  p.block = window == -1 ? 1 : 0;          // window -1: non-causal block rows (they must form one group)
+  if (p.block && M * (n_q / n_kv) > 64) return -5;
   p.one_slice = span_pages > 0 ? 1 : 0;   // fixed spans promise bits that do not depend on the group
   if (span_pages > 0 && (long)span_pages * nsplit < max_blocks) return -2;  // fixed spans must cover the longest sequence
   // Two CTAs per SM, each with one batch in flight, hide the copies as well as one CTA that prefetches (measured

@@ -17,7 +17,7 @@ import torch
 from . import build as _build
 
 _lib: Optional[ctypes.CDLL] = None
-_UNITS = ("gemv", "decode", "gemm", "attn", "attnrows", "moe", "comm", "ep", "spec", "sampler", "gdn", "mega")
+_UNITS = ("gemv", "decode", "gemm", "attn", "attnrows", "moe", "comm", "ep", "spec", "sampler", "gdn", "mega", "dflash")
 
 # Control block layout (int32 words) -- mirrors decode_ops.cu
 CTRL_N_ROWS = 0
@@ -274,7 +274,8 @@ def attn_rows(q, k_cache, v_cache, block_table, ctrl, o_part, ml_part, out, tick
               max_blocks, scale, span_pages: int = 0, k_scale=None, v_scale=None, kv_int8: bool = False, window: int = 0):
     """Decode / verify attention that serves consecutive rows of one request together on the tensor cores
     (bf16 or int8 KV, head size 128); same split-KV partial buffers and in-kernel merge as ``attn_decode``.
-    ``window`` > 0: every row attends to its last ``window`` positions only."""
+    ``window`` > 0: every row attends to its last ``window`` positions only; ``window`` = -1: the rows are a block whose
+    rows all attend to every position up to the block's last one (no causal mask inside the block)."""
     rc = lib().b2_attn_rows(_p(q), _p(k_cache), _p(v_cache), _p(k_scale), _p(v_scale), 1 if kv_int8 else 0,
                             _p(block_table), _p(ctrl), _p(o_part), _p(ml_part),
                             _p(out), _p(tickets), m, n_q, n_kv, d, nsplit, max_blocks, ctypes.c_float(scale), span_pages,
