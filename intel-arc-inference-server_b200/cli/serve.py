@@ -65,7 +65,8 @@ def main(argv=None):
     adapter = EngineAdapter(engine, eos_ids=eos or (2,))
     if spec in ("mtp", "dflash", "dflash-lookup"):
         from ..runtime.spec import SpecAdapter
-        adapter = SpecAdapter(adapter, spec, f.spec_max, f.draft_model, f.draft_vocab, f.draft_vocab_ids)
+        adapter = SpecAdapter(adapter, spec, f.spec_max, f.draft_model, f.draft_vocab, f.draft_vocab_ids,
+                              candidate_head_int8=f.candidate_head_int8)
     prefix = None
     if f.prefix_cache_gb != "0" and not hybrid:
         from ..server.prefix import PrefixStore

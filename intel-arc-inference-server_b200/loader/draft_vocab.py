@@ -53,9 +53,19 @@ def read_ranked_ids(path: str) -> List[int]:
 class DraftVocab:
     """The gathered head rows and the map from a position in V' back to the token id."""
 
-    def __init__(self, lm_head: torch.Tensor, ids: Sequence[int]):
+    def __init__(self, lm_head: torch.Tensor, ids: Sequence[int], int8: bool = False):
+        """``int8``: keep the gathered rows as int8 with one scale per row -- a candidate head at half the bytes, whose
+        best candidates a block drafter then scores exactly against the bf16 rows (the reference's candidate head is
+        an int4 / 2-bit copy of its int8 head: src/loader/dflash_loader.h:24-75)."""
         self.ids = torch.as_tensor(list(ids), dtype=torch.int64, device=lm_head.device)
         self.head = lm_head.index_select(0, self.ids).contiguous()
+        self.head_i8 = None
+        self.exact_rows = not int8      # the logits of ``head`` are the target head's own
+        if int8:
+            wf = self.head.float()
+            sc = wf.abs().amax(dim=1).clamp_min(1e-12) / 127.0
+            self.head_i8 = (torch.round(wf / sc[:, None]).clamp_(-127, 127).to(torch.int8).contiguous(), sc.contiguous())
+            self.head = None
         self.ids32 = self.ids.to(torch.int32)
         self.size = int(self.ids.numel())
 

@@ -161,6 +161,7 @@ class DecoderModel:
         # CTA of the GEMV (whose prologue repeats the rows' work per 128 output columns)
         self.prequant_rows = 3
         self.attn_rows_min = int(os.environ.get("B2_ATTN_ROWS_MIN", "1"))
+        self.block_rows = False      # set by a block drafter around its layers: flagged rows attend non-causally
         self.attn_merge_inkernel_rows = int(os.environ.get("B2_ATTN_MERGE_INKERNEL_ROWS", "0"))
         # fixed KV split spans make a row's attention bits independent of the rows it is verified with (speculation
         # then reproduces plain decoding exactly); off, the splits adapt to the context (fastest at any depth)
@@ -203,7 +204,9 @@ class DecoderModel:
         """Split-KV attention of the step's rows into ``buf.attn_out``.  Head size 128 (bf16 or int8 KV) goes to the
         tensor-core kernel that serves a request's consecutive rows together; the rest to the per-row kernel."""
         cfg, b = self.cfg, self.buf
-        if m >= self.attn_rows_min and cfg.head_dim == 128 and self.nsplit_attn <= 64 and cfg.gqa <= 16:
+        if window == -1 and (cfg.head_dim != 128 or self.nsplit_attn > 64 or cfg.gqa > 16):
+            raise NotImplementedError("block rows need the multi-row attention kernel (head size 128)")
+        if (m >= self.attn_rows_min or window == -1) and cfg.head_dim == 128 and self.nsplit_attn <= 64 and cfg.gqa <= 16:
             inkernel = m <= self.attn_merge_inkernel_rows    # few rows: the last split CTA merges; many: a merge launch
             K.attn_rows(b.q, kc, vc, block_table, ctrl, b.o_part, b.ml_part, b.attn_out, b.tickets if inkernel else None,
                         m, cfg.n_q_heads,
@@ -230,7 +233,9 @@ class DecoderModel:
         return self._gemv("gdn_out", g.out_proj, b.gdn_out, m)
 
     def _window(self, li: int) -> int:
-        return self.cfg.window_of(li) if li < self.cfg.n_layers else 0   # draft-head layers: the whole context
+        if li < self.cfg.n_layers:
+            return self.cfg.window_of(li)
+        return -1 if self.block_rows else 0    # draft-head layers: the whole context; -1: block rows as flagged
 
     def attention_block(self, lw: LayerWeights, li: int, m: int, ctrl, block_table, max_blocks, kv: KVCache):
         cfg, b = self.cfg, self.buf

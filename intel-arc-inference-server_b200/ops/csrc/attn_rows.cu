@@ -31,7 +31,7 @@ using namespace b2;
 
 namespace {
 
-constexpr int CTRL_ROW_REQ = 16, CTRL_ROW_POS = 80;
+constexpr int CTRL_ROW_REQ = 16, CTRL_ROW_POS = 80, CTRL_ROW_BLOCK = 336;
 constexpr int D = 128;
 constexpr int KB = 128;          // keys per batch
 constexpr int HALFB = KB * 128;  // one tile half: 128 keys x 64 dims (128-byte rows, TMA 128-byte swizzle)
@@ -55,8 +55,9 @@ struct AttnRowsParams {
   int M, n_q, n_kv, gqa, nsplit, max_blocks;
   int nbuf;        // 1: one K / V tile pair; 2: the next batch of keys is fetched while this one is multiplied
   int window;      // > 0: a row attends to its last `window` positions only (sliding-window layers)
-  int block;       // 1: the rows of a group form a block that attends to ALL of the group's positions (a block
-                   //    drafter's rows see one another, before and after: no causal mask inside the block)
+  int block;       // 1: a row whose CTRL_ROW_BLOCK word is set attends to ALL positions of its group, those after it
+                   //    too (a block drafter's rows see one another: no causal mask inside the block); the group's
+                   //    other rows stay causal
   int one_slice;   // 1: never cut a batch's keys over idle warps (a row's bits then do not depend on the group's size)
   int span_pages;  // > 0: every split covers this many pages whatever the context (a row's bits then do not depend
                    // on which rows share its CTA); 0: the group's context is cut into nsplit equal parts
@@ -133,7 +134,7 @@ __device__ __forceinline__ void attn_rows_body(const AttnRowsParams& p, uint8_t*
     const int qr = rg * 16 + g + 8 * hf;
     const bool ok = qr < QR;
     const int m = z + (ok ? qr / p.gqa : 0), h = ok ? qr % p.gqa : 0;
-    ctx[hf] = ok ? (p.block ? ctx_max : s_pos[m] + 1) : 0;
+    ctx[hf] = ok ? (s_pos[m] < 0 ? ctx_max : s_pos[m] + 1) : 0;
     wlo[hf] = p.window > 0 ? ctx[hf] - p.window : 0;
     const __nv_bfloat16* qp = p.q + (size_t)m * p.n_q * D + (size_t)(kh * p.gqa + h) * D;
 #pragma unroll
@@ -440,6 +441,7 @@ __global__ void __launch_bounds__(kThreads, 2) attn_rows_kernel(const __grid_con
     s_req[tid] = tid < p.M ? p.ctrl[CTRL_ROW_REQ + tid] : -1;
     s_pos[tid] = tid < p.M ? p.ctrl[CTRL_ROW_POS + tid] : 0;
   }
+  const bool blk = p.block && tid < p.M && p.ctrl[CTRL_ROW_BLOCK + tid] != 0;
   __syncthreads();
   const int req = s_req[z];
   int gs = z;
@@ -451,6 +453,13 @@ __global__ void __launch_bounds__(kThreads, 2) attn_rows_kernel(const __grid_con
   const int QR = rows * p.gqa;
   int ctx_max = 0;
   for (int r = 0; r < rows; ++r) ctx_max = max(ctx_max, s_pos[z + r] + 1);
+  if (p.block) {           // a block row sees every position of its REQUEST's rows in this step, also those a
+                           // sibling CTA serves; its position becomes -1: "all of these keys" for the body
+    for (int r = gs; r < p.M && s_req[r] == req; ++r) ctx_max = max(ctx_max, s_pos[r] + 1);
+    __syncthreads();
+    if (blk) s_pos[tid] = -1;
+    __syncthreads();
+  }
   if (QR <= 16 && !p.one_slice)
     attn_rows_body<I8, 4>(p, smem_raw, s_pos, &s_last, s_bt, req, rows, QR, ctx_max);
   else if (QR <= 32 && !p.one_slice)
@@ -535,8 +544,7 @@ extern "C" int b2_attn_rows(const void* q, const void* k_cache, const void* v_ca
   p.scale_log2 = scale * 1.4426950408889634f;
   p.span_pages = span_pages;
   p.window = window > 0 ? window : 0;
-  p.block = window == -1 ? 1 : 0;          // window -1: non-causal block rows (they must form one group)
-  if (p.block && M * (n_q / n_kv) > 64) return -5;
+  p.block = window == -1 ? 1 : 0;          // window -1: rows flagged in the control block are non-causal block rows
   p.one_slice = span_pages > 0 ? 1 : 0;   // fixed spans promise bits that do not depend on the group
   if (span_pages > 0 && (long)span_pages * nsplit < max_blocks) return -2;  // fixed spans must cover the longest sequence
   // Two CTAs per SM, each with one batch in flight, hide the copies as well as one CTA that prefetches (measured

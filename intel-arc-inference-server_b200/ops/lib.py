@@ -26,6 +26,7 @@ CTRL_ROW_POS = 80
 CTRL_CUR_TOKEN = 144
 CTRL_OUT_TOKEN = 208
 CTRL_OUT_VALUE = 272
+CTRL_ROW_BLOCK = 336     # [64] 1: the row attends to every position of its request's rows (block drafter)
 CTRL_WORDS = 512
 MAX_ROWS = 64
 

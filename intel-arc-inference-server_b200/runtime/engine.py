@@ -32,6 +32,7 @@ class Row:
     slot: int
     pos: int
     token: int
+    block: int = 0      # 1: a block drafter's row, which attends to all positions of its request's rows in the step
 
 
 class Engine:
@@ -155,6 +156,7 @@ class Engine:
             c[K.CTRL_ROW_REQ + i] = r.slot
             c[K.CTRL_ROW_POS + i] = r.pos
             c[K.CTRL_CUR_TOKEN + i] = r.token
+            c[K.CTRL_ROW_BLOCK + i] = r.block
         self._one_request = all(r.slot == rows[0].slot and r.pos == rows[0].pos + i for i, r in enumerate(rows))
         self.ctrl_stage.push(self.ctrl)
 

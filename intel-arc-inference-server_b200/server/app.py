@@ -247,12 +247,26 @@ class Server:
 
     def _decode(self, a):
         rows = {}
+        ask = {}       # slot -> (pending, k, temperature, seed): drafts the engine's head makes, all slots in one call
         for slot, n in zip(a["slots"], a["rows"]):
             s = self.by_slot.get(slot)
             if s is None or s.finished or s.pending is None:
                 continue
             drafts = self._draft(s, self._draft_budget(s, n - 1)) if n > 1 else []
+            if isinstance(drafts, int):       # the engine's draft head is to make this many
+                sampled = self.o.spec != "mtp" and not s.req.greedy and s.req.repetition_penalty == 1.0
+                seed = (s.rng_seed * 1000003 + len(s.out_ids)) & 0x7FFFFFFF
+                ask[slot] = (s.pending, drafts, s.req.temperature if sampled else 0.0, seed)
+                drafts = []
             rows[slot] = [s.pending] + drafts
+        s_q = {}
+        if ask:
+            many = getattr(self.engine, "draft_many", None)
+            made = many(ask) if many is not None else {sl: self.engine.draft(sl, rq[0], rq[1]) for sl, rq in ask.items()}
+            for slot, drafts in made.items():
+                rows[slot] = rows[slot] + [int(t) for t in drafts]
+                if ask[slot][2] > 0 and hasattr(self.engine, "draft_q"):
+                    s_q[slot] = self.engine.draft_q(slot)
         if not rows:
             return
         try:
@@ -272,8 +286,14 @@ class Server:
             elif drafts:
                 p_rows = np.stack([self.engine.logits(slot, i) for i in range(len(toks))])
                 seed = (s.rng_seed * 1000003 + len(s.out_ids)) & 0xFFFFFFFFFFFFFFFF
-                acc, nxt = H.accept_point_mass(p_rows, drafts, self.engine.vocab_size, s.req.temperature,
-                                               s.req.top_k, s.req.top_p, seed)
+                q = s_q.get(slot)
+                if q is not None:
+                    # the drafts were drawn from a sparse q (a block drafter's candidates): the lossless rule for it
+                    acc, nxt = H.accept_sparse(p_rows, q[0][: len(drafts)], q[1][: len(drafts)], drafts,
+                                               self.engine.vocab_size, s.req.temperature, s.req.top_k, s.req.top_p, seed)
+                else:
+                    acc, nxt = H.accept_point_mass(p_rows, drafts, self.engine.vocab_size, s.req.temperature,
+                                                   s.req.top_k, s.req.top_p, seed)
             else:
                 acc, nxt = 0, (self._sample(s) if host_rule else out[0])
             self._observe_drafts(s, len(drafts), acc)
@@ -333,7 +353,8 @@ class Server:
             except Exception as e:  # noqa: BLE001
                 sys.stderr.write(f"engine recovery failed: {e}\n")
 
-    def _draft(self, s: Session, k: int) -> List[int]:
+    def _draft(self, s: Session, k: int):
+        """The step's drafts for ``s`` (a list), or how many the engine's draft head should make (an int)."""
         if k <= 0:
             return []
         room = s.req.max_tokens - len(s.out_ids) - 1
@@ -354,7 +375,7 @@ class Server:
                     s.copy_step = True
                     return drafts
         if self.o.spec in ("mtp", "dflash", "dflash-lookup") and hasattr(self.engine, "draft"):
-            return list(self.engine.draft(s.slot, s.pending, min(k, room)))     # a learned draft head on the engine side
+            return min(k, room)     # a learned draft head on the engine side
         if self.o.spec not in ("lookup", "dflash-lookup"):
             return []
         return list(self._lookup(s).propose(min(k, room), 2))

@@ -136,9 +136,10 @@ def test_select_argmax_and_keyed_gumbel_is_reproducible():
     assert other != chosen.cpu().tolist()
 
 
-def test_block_rows_attend_to_the_whole_block():
-    """Rows of one request served as a block (window = -1): every row sees every position up to the block's last one,
-    against fp32 softmax attention without a causal mask inside the block."""
+@pytest.mark.parametrize("causal_rows", [0, 2])
+def test_block_rows_attend_to_the_whole_block(causal_rows):
+    """Rows flagged as block rows (window = -1) see every position up to the block's last one; the rows before them stay
+    causal -- against fp32 softmax attention with that mask."""
     k_ = K()
     torch.manual_seed(4)
     n_q, n_kv, d, rows, ctx0, nsplit = 8, 2, 128, 6, 70, 4
@@ -152,6 +153,7 @@ def test_block_rows_attend_to_the_whole_block():
     ctrl[k_.CTRL_N_ROWS] = rows
     for i in range(rows):
         ctrl[k_.CTRL_ROW_REQ + i], ctrl[k_.CTRL_ROW_POS + i] = 0, ctx0 + i
+        ctrl[k_.CTRL_ROW_BLOCK + i] = 1 if i >= causal_rows else 0
     ctrl = ctrl.cuda()
     o_part = torch.zeros(rows * n_q * nsplit * d, device="cuda")
     ml = torch.zeros(rows * n_q * nsplit * 2, device="cuda")
@@ -163,8 +165,11 @@ def test_block_rows_attend_to_the_whole_block():
     kf = kc.float().permute(1, 0, 2, 3).reshape(n_kv, pages * 16, d)[:, :total]
     vf = vc.float().permute(1, 0, 2, 3).reshape(n_kv, pages * 16, d)[:, :total]
     qf = q.float().view(rows, n_q, d)
+    seen = torch.tensor([total if i >= causal_rows else ctx0 + i + 1 for i in range(rows)], device="cuda")
+    mask = torch.arange(total, device="cuda")[None, :] < seen[:, None]
     ref = torch.zeros(rows, n_q, d, device="cuda")
     for h in range(n_q):
-        s = (qf[:, h] @ kf[h // gqa].t()) * d ** -0.5          # every row over ALL `total` keys
+        s = (qf[:, h] @ kf[h // gqa].t()) * d ** -0.5
+        s = s.masked_fill(~mask, float("-inf"))
         ref[:, h] = torch.softmax(s, dim=-1) @ vf[h // gqa]
     assert (out.float().view(rows, n_q, d) - ref).abs().max() < 2e-2 * ref.abs().max() + 2e-3
