@@ -52,6 +52,12 @@ class NameView:
             raise KeyError(f"checkpoint has no tensor {name}")
         return self.st.get(self.map[name], self.copy)
 
+    def shape(self, name):
+        return self.st.shape(self.map[name])
+
+    def dtype(self, name) -> str:
+        return self.st.dtype(self.map[name])
+
 
 class _LinearSrc:
     """One quantised (or bf16) linear of the checkpoint: ``q`` uint8 [K][N] + scales, or a dense weight."""
@@ -68,7 +74,11 @@ class _LinearSrc:
             self.scales = sc if qc.group_size == 64 else Q.expand_group128(sc)
             self.dense = None
         elif view.has(prefix + ".weight"):
-            self.dense = view.get(prefix + ".weight").float()   # an excluded module: quantise on the host (RTN)
+            # an excluded module or an unquantised drafter (bf16, or int8 with one scale per output row): quantise on
+            # the host (RTN)
+            self.dense = view.get(prefix + ".weight").float()
+            if view.has(prefix + ".weight_scale"):
+                self.dense = self.dense * view.get(prefix + ".weight_scale").float().reshape(-1, 1)
             self.q, self.scales = Q.quantize_rtn(self.dense)
         else:
             raise KeyError(f"checkpoint has neither {prefix}.qweight nor {prefix}.weight")
@@ -230,32 +240,91 @@ def load(snapshot: str, device="cuda", mtp: bool = True, int8_head: bool = False
     return w
 
 
+def _drafter_linears(cfg: ModelConfig, prefix: str, n_layers: int):
+    """(name, out features, in features) of every linear a draft head's snapshot must hold."""
+    h = cfg.hidden
+    out = [(prefix + "fc", h, 2 * h)]
+    for i in range(n_layers):
+        p = f"{prefix}layers.{i}"
+        out += [(p + ".self_attn.q_proj", cfg.q_dim, h), (p + ".self_attn.k_proj", cfg.kv_dim, h),
+                (p + ".self_attn.v_proj", cfg.kv_dim, h), (p + ".self_attn.o_proj", h, cfg.q_dim),
+                (p + ".mlp.gate_proj", cfg.ffn, h), (p + ".mlp.up_proj", cfg.ffn, h), (p + ".mlp.down_proj", h, cfg.ffn)]
+    return out
+
+
+def check_drafter(st, cfg: ModelConfig, prefix: str, n_layers: int, group_size: int = 64) -> List[str]:
+    """Everything wrong with a drafter snapshot's tensors, by name: missing tensors, element types and shapes that do
+    not fit the configuration -- read from the file headers only, before any weight is touched (the reference checks
+    its drafter checkpoint the same way: src/loader/dflash_loader.h:24-53).  An empty list: the snapshot loads."""
+    bad: List[str] = []
+
+    def want(name, dtypes, shape):
+        if not st.has(name):
+            bad.append(f"{name}: missing")
+            return
+        dt, sh = st.dtype(name), tuple(st.shape(name))
+        if dt not in dtypes:
+            bad.append(f"{name}: element type {dt}, expected one of {sorted(dtypes)}")
+        if shape is not None and sh != tuple(shape):
+            bad.append(f"{name}: shape {list(sh)}, expected {list(shape)}")
+
+    fl = {"BF16", "F16", "F32"}
+    h = cfg.hidden
+    for nm in ("pre_fc_norm_embedding.weight", "pre_fc_norm_hidden.weight", "norm.weight"):
+        want(prefix + nm, fl, (h,))
+    for i in range(n_layers):
+        want(f"{prefix}layers.{i}.input_layernorm.weight", fl, (h,))
+        want(f"{prefix}layers.{i}.post_attention_layernorm.weight", fl, (h,))
+    for name, n, k in _drafter_linears(cfg, prefix, n_layers):
+        if st.has(name + ".qweight"):
+            want(name + ".qweight", {"I32"}, (k // 8, n))
+            want(name + ".scales", {"F16", "BF16"}, (k // group_size, n))
+        elif st.has(name + ".weight_scale"):
+            want(name + ".weight", {"I8"}, (n, k))
+            want(name + ".weight_scale", {"F32", "F16", "BF16"}, None)
+        else:
+            want(name + ".weight", fl, (n, k))
+    return bad
+
+
 def load_drafter(snapshot: str, device="cuda", report=sys.stderr) -> MtpWeights:
     """A draft head from its own snapshot (``--draft-model``): the front (``fc`` over [norm(embed) ‖ norm(hidden)],
-    the two pre-norms), its decoder layers and its output norm, in the GPTQ layout of the main checkpoint.  Tensor
-    names may carry the prefix ``mtp.`` (a head cut out of a main checkpoint), ``drafter.`` or none.  The
-    reference loads its DFlash drafter the same way (src/loader/loader.cc:521 load_mtp, docs/13-loader.md)."""
+    the two pre-norms), its decoder layers and its output norm.  Linears come as int4 (the GPTQ layout of the main
+    checkpoint), dense bf16 / fp16, or int8 with a scale per output row; the last two are quantised to int4 g64 on the
+    host.  Tensor names may carry the prefix ``mtp.`` (a head cut out of a main checkpoint), ``drafter.`` or none.
+    ``mask_token_id`` of ``config.json`` names the token whose embedding row stands for "not drafted yet" in a block.
+    The snapshot's tensors are checked against the configuration before anything is read; one error lists every
+    problem.  The reference: src/loader/dflash_loader.h:24-75, src/loader/loader.cc:521 load_mtp."""
     snap = resolve_snapshot(snapshot)
     with open(os.path.join(snap, "config.json")) as f:
         hf = json.load(f)
     if "text_config" in hf:
-        hf = {**hf["text_config"], "quantization_config": hf.get("quantization_config", hf["text_config"].get("quantization_config"))}
+        hf = {**hf["text_config"], "quantization_config": hf.get("quantization_config", hf["text_config"].get("quantization_config")),
+              "mask_token_id": hf.get("mask_token_id", hf["text_config"].get("mask_token_id"))}
     cfg = ModelConfig.from_hf_config(hf)
-    qc = QuantConfig.parse(hf)
+    # an unquantised drafter has no quantization_config: its linears take the host quantiser's group size
+    qc = QuantConfig.parse(hf) if hf.get("quantization_config") else QuantConfig("none", 4, 64, True, False)
     st = SafetensorsSet(snap)
     view = NameView(st, copy=torch.device(device).type == "cpu")
-    prefix = next((p for p in ("mtp.", "drafter.", "") if view.has(p + "fc.qweight") or view.has(p + "fc.weight")), None)
+    prefix = next((p for p in ("mtp.", "drafter.", "")
+                   if any(view.has(p + "fc" + sfx) for sfx in (".qweight", ".weight"))), None)
     if prefix is None:
-        raise KeyError(f"{snap}: no draft head found (fc.qweight under mtp., drafter. or no prefix)")
+        raise KeyError(f"{snap}: no draft head found (fc.qweight or fc.weight under mtp., drafter. or no prefix)")
     n_layers = 0
     while view.has(f"{prefix}layers.{n_layers}.input_layernorm.weight"):
         n_layers += 1
+    bad = check_drafter(view, cfg, prefix, n_layers, qc.group_size)
+    if bad:
+        raise ValueError(f"{snap}: the draft head does not fit its configuration:\n  " + "\n  ".join(bad))
     fc = _LinearSrc(view, prefix + "fc", qc)
     head = MtpWeights(view.get(prefix + "pre_fc_norm_embedding.weight").float().to(device),
                       view.get(prefix + "pre_fc_norm_hidden.weight").float().to(device),
                       _ql(fc.q, fc.scales, device),
                       [_load_layer(view, cfg, f"{prefix}layers.{i}", qc, device, (0, 1)) for i in range(n_layers)],
                       view.get(prefix + "norm.weight").float().to(device))
+    mt = hf.get("mask_token_id")
+    head.mask_token = int(mt) if mt is not None and 0 <= int(mt) < cfg.vocab else None
     if report is not None:
-        report.write(f"load: draft head with {n_layers} layer(s) from {snap}\n")
+        fmt = "int4" if view.has(prefix + "fc.qweight") else ("int8" if view.has(prefix + "fc.weight_scale") else "dense")
+        report.write(f"load: draft head with {n_layers} layer(s) ({fmt} linears) from {snap}\n")
     return head

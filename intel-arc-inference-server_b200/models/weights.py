@@ -110,6 +110,7 @@ class MtpWeights:
     fc: QLinear                    # [hidden][2*hidden]
     layers: List[LayerWeights]
     norm: torch.Tensor
+    mask_token: Optional[int] = None    # a block drafter's "not drafted yet" token (default: the last vocabulary id)
 
 
 @dataclass

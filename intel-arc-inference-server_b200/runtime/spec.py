@@ -64,6 +64,8 @@ class DraftHead:
         self.kv0 = cfg.n_layers if kv_layer0 is None else kv_layer0
         if engine.kv.n_layers < self.kv0 + len(head.layers):
             raise ValueError("the engine's KV cache has no layers for the draft head (extra_kv_layers)")
+        if mask_token is None:
+            mask_token = getattr(head, "mask_token", None)
         self.mask_token = cfg.vocab - 1 if mask_token is None else mask_token
         dev = engine.device
         self.xcat = torch.zeros(engine.max_rows, 2 * cfg.hidden, dtype=torch.bfloat16, device=dev)

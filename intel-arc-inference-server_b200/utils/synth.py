@@ -116,3 +116,39 @@ def write_checkpoint(w: ModelWeights, path: str, shards: int = 2, g_idx: bool = 
     with open(os.path.join(path, "config.json"), "w") as f:
         json.dump(hf, f, indent=1)
     return path
+
+
+def write_drafter(head, cfg: ModelConfig, path: str, fmt: str = "int4", prefix: str = "drafter.",
+                  mask_token_id: int = -1) -> str:
+    """Writes a draft head (front, decoder layers, norm) as a snapshot of its own in one of the formats a drafter
+    ships in: ``int4`` (GPTQ g64, as the main checkpoint), ``bf16`` (dense ``.weight`` [out][in]) or ``int8``
+    (``.weight`` int8 [out][in] + ``.weight_scale`` fp32 [out])."""
+    os.makedirs(path, exist_ok=True)
+    t: Dict[str, torch.Tensor] = {}
+    t[prefix + "pre_fc_norm_embedding.weight"] = head.pre_norm_embed.cpu().to(torch.bfloat16)
+    t[prefix + "pre_fc_norm_hidden.weight"] = head.pre_norm_hidden.cpu().to(torch.bfloat16)
+    t[prefix + "norm.weight"] = head.norm.cpu().to(torch.bfloat16)
+    _emit_linear(t, prefix + "fc", *Q.from_w4b(head.fc.w4b.cpu(), head.fc.n), False)
+    for i, lw in enumerate(head.layers):
+        _emit_layer(t, cfg, f"{prefix}layers.{i}", lw, False)
+    if fmt != "int4":
+        for name in [n[: -len(".qweight")] for n in list(t) if n.endswith(".qweight")]:
+            q = Q.unpack_gptq(t.pop(name + ".qweight"))
+            sc = t.pop(name + ".scales")
+            t.pop(name + ".qzeros")
+            dense = ((q.float() - 8.0) * sc.float().repeat_interleave(64, dim=0)).t().contiguous()     # [out][in]
+            if fmt == "bf16":
+                t[name + ".weight"] = dense.to(torch.bfloat16)
+            else:
+                s8 = dense.abs().amax(dim=1).clamp_min(1e-12) / 127.0
+                t[name + ".weight"] = torch.round(dense / s8[:, None]).clamp_(-127, 127).to(torch.int8)
+                t[name + ".weight_scale"] = s8.float()
+    save_file(t, os.path.join(path, "model.safetensors"), {"format": "pt"})
+    hf = cfg.to_hf_config()
+    if fmt != "int4":
+        hf.pop("quantization_config", None)
+    if mask_token_id >= 0:
+        hf["mask_token_id"] = mask_token_id
+    with open(os.path.join(path, "config.json"), "w") as f:
+        json.dump(hf, f, indent=1)
+    return path

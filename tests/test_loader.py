@@ -164,3 +164,49 @@ def test_hybrid_checkpoint_round_trip(tmp_path):
             assert torch.equal(getattr(a.gdn, f), getattr(b.gdn, f)), f
     ids = torch.arange(12) % cfg.vocab
     assert torch.equal(OracleModel(got).forward(ids), OracleModel(w).forward(ids))
+
+
+@pytest.mark.parametrize("fmt", ["int4", "bf16", "int8"])
+def test_drafter_snapshot_formats(tmp_path, fmt):
+    """A block drafter's snapshot loads from int4 (GPTQ), dense bf16 and int8-with-row-scales linears; the unquantised
+    forms are quantised on the host and stay close to the original; the mask token comes from config.json."""
+    from b200serve.loader.loader import load_drafter
+    from b200serve.runtime.spec import random_drafter
+    from b200serve.utils.synth import write_drafter
+    cfg = tiny_dense()
+    head = random_drafter(cfg, "cpu", seed=3, layers=2)
+    snap = write_drafter(head, cfg, str(tmp_path / fmt), fmt=fmt, mask_token_id=cfg.vocab - 2)
+    got = load_drafter(snap, device="cpu", report=None)
+    assert len(got.layers) == 2 and got.mask_token == cfg.vocab - 2
+    pairs = [(head.fc, got.fc)] + [(a.qkv, b.qkv) for a, b in zip(head.layers, got.layers)] + \
+            [(a.down, b.down) for a, b in zip(head.layers, got.layers)]
+    for a, b in pairs:
+        qa, sa = Q.from_w4b(a.w4b, a.n)
+        qb, sb = Q.from_w4b(b.w4b, b.n)
+        da = (qa.float() - 8) * sa.float().repeat_interleave(64, dim=0)
+        db = (qb.float() - 8) * sb.float().repeat_interleave(64, dim=0)
+        if fmt == "int4":
+            assert torch.equal(qa, qb) and torch.equal(sa, sb)
+        else:   # one more rounding (bf16 or int8) and a second round-to-nearest int4
+            assert (da - db).abs().max() <= 0.6 * sa.float().max()
+
+
+def test_drafter_snapshot_check_lists_every_problem(tmp_path):
+    from b200serve.loader.loader import load_drafter
+    from b200serve.runtime.spec import random_drafter
+    from b200serve.utils.synth import write_drafter
+    cfg = tiny_dense()
+    head = random_drafter(cfg, "cpu", seed=3, layers=1)
+    snap = write_drafter(head, cfg, str(tmp_path / "d"), fmt="bf16")
+    st = SafetensorsSet(snap)
+    t = {n: st.get(n) for n in st.names()}
+    del t["drafter.norm.weight"]
+    t["drafter.layers.0.mlp.down_proj.weight"] = t["drafter.layers.0.mlp.down_proj.weight"][:, :-64].contiguous()
+    t["drafter.fc.weight"] = t["drafter.fc.weight"].to(torch.int32)
+    save_file(t, os.path.join(snap, "model.safetensors"), {"format": "pt"})
+    with pytest.raises(ValueError) as e:
+        load_drafter(snap, device="cpu", report=None)
+    msg = str(e.value)
+    assert "drafter.norm.weight: missing" in msg
+    assert "drafter.layers.0.mlp.down_proj.weight: shape" in msg
+    assert "drafter.fc.weight: element type I32" in msg

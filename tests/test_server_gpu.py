@@ -78,5 +78,16 @@ def test_completions_match_engine_greedy(spec, prefix):
             assert res["usage"]["completion_tokens"] == 20
             if prefix and attempt == 1:
                 assert res["usage"]["prompt_tokens_details"]["cached_tokens"] >= 64
+        if spec == "dflash":
+            # sampled requests: the block drafter draws its drafts from 16 candidates per row and the server applies
+            # the sparse-q accept rule; the same seed gives the same text
+            texts = []
+            for _ in range(2):
+                status, res = post(srv.port, "/v1/completions", dict(body, temperature=0.8, seed=5))
+                assert status == 200, res
+                assert res["usage"]["completion_tokens"] == 20
+                texts.append(res["choices"][0].get("token_ids") or res["choices"][0]["text"])
+            assert texts[0] == texts[1]
+            assert adapter.stats["drafted"] > 0
     finally:
         srv.stop()
