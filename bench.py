@@ -298,7 +298,7 @@ def main():
         from b200serve.utils.benchlib import run_spec_bench
         # the same loop behind a 65,536-token context (its prompt pass runs first, draft heads included)
         guarded("spec_after_65536", lambda: run_spec_bench(args, barrier, iters=8, depth=65536,
-                                                           cases=(("mtp", 3, (3,), 0), ("dflash", 7, (7,), 0))))
+                                                           cases=(("mtp", 3, (3,), 0), ("dflash", 15, (7,), 0))))
     if args.what == "batch32k" or (args.what == "all" and world == 1):
         from b200serve.utils.benchlib import run_batch_after_long_prompt
         guarded("decode_8req_after_32k_int8kv", lambda: run_batch_after_long_prompt(args, barrier))

@@ -113,8 +113,8 @@ def run_prefill_bench(args, barrier, model: str, backend: str, n: int = 0, warm:
 def run_spec_bench(args, barrier, iters: int = 12, depth: int = 0, cases=None) -> dict:
     """Draft-and-verify iterations on the 27B shape with FORCED acceptance lengths, so that the step time does
     not depend on what random-init heads happen to propose: an MTP head (1 layer, draft depth 3) and a
-    DFlash-style block drafter (2 layers, 7 drafts in one block pass), each verified in one trunk step of
-    k + 1 rows.  tokens/s = (accepted + 1) / iteration time (draft + verify, host control included)."""
+    DFlash-style block drafter (2 layers; the pending token and 15 mask rows form one 16-token block whose rows attend
+    to one another, 16 candidates per row, picked on the device), each verified in one trunk step of k + 1 rows.  tokens/s = (accepted + 1) / iteration time (draft + verify, host control included)."""
     import dataclasses
     import time
     from ..runtime.spec import SpecAdapter
@@ -126,7 +126,7 @@ def run_spec_bench(args, barrier, iters: int = 12, depth: int = 0, cases=None) -
     out = {"depth": depth}
     g = torch.Generator().manual_seed(0)
     ids = torch.randint(0, cfg.vocab - 1, (depth,), generator=g).tolist()
-    for kind, k, accepts, dv in (cases or (("mtp", 3, (0, 3), 0), ("mtp", 3, (3,), 32768), ("dflash", 7, (0, 3, 7), 0))):
+    for kind, k, accepts, dv in (cases or (("mtp", 3, (0, 3), 0), ("mtp", 3, (3,), 32768), ("dflash", 15, (0, 3, 7), 0))):
         eng = Engine(weights, max_seqs=1, max_len=depth + 64 * (iters + 4) + 64, extra_kv_layers=2)
         ad = SpecAdapter(EngineAdapter(eng), kind, k, draft_vocab=dv)
         pending = ad.prefill(0, ids)
