@@ -37,6 +37,7 @@ enum : unsigned int {
   ERR_ATTN_WAIT = 0x301,
   ERR_MOE_WAIT = 0x401,
   ERR_COMM_FLAG_WAIT = 0x501,
+  ERR_GDN_WAIT = 0x601,
   ERR_BAD_ARG = 0x901,
 };
 

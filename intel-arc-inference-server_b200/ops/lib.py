@@ -310,6 +310,21 @@ def gdn_chunk(act, m, n, n_k, n_v, head_dim, slot, a_log, dt_bias, norm_w, eps, 
                               ctypes.c_float(eps), _p(state), _p(out), _stream()), "gdn_chunk")
 
 
+def gdn_wy_block_bytes() -> int:
+    """Workspace bytes the chunked scan needs per (64-row chunk, value head)."""
+    return int(lib().b2_gdn_wy_block_bytes())
+
+
+def gdn_chunk_wy(act, m, n, n_k, n_v, head_dim, slot, a_log, dt_bias, norm_w, eps, state, out, ws):
+    """``gdn_chunk`` with the recurrence in its chunked form on the tensor cores: per 64-row chunk the rows' deltas come
+    from a triangular solve that does not involve the state (all chunks in parallel), and the scan over the chunks
+    is four small matrix products per chunk and value head.  ``ws``: uint8 workspace of
+    ``ceil(m / 64) * n_v * gdn_wy_block_bytes()`` bytes."""
+    _check(lib().b2_gdn_chunk_wy(_p(act), m, n, n_k, n_v, head_dim, slot, _p(a_log), _p(dt_bias), _p(norm_w),
+                                 ctypes.c_float(eps), _p(state), _p(out), _p(ws),
+                                 ctypes.c_longlong(ws.numel() * ws.element_size()), _stream()), "gdn_chunk_wy")
+
+
 def sample_rows(logits, m, n_valid, temperature, top_k, top_p, seed, token, status, penalty=None, hist=None,
                 hist_len=None, kept=None):
     """One token per row of ``logits`` [m][ld] by the host sampler's rule (temperature, top-k, top-p, optional

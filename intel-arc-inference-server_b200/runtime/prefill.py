@@ -17,6 +17,8 @@ Weight forms for the GEMMs:
 """
 from __future__ import annotations
 
+import os
+
 from typing import List, Optional
 
 import torch
@@ -96,6 +98,11 @@ class PrefillRunner:
             self.gdn_proj = torch.empty(c, cfg.gdn_proj_dim, dtype=f32, device=self.dev)
             self.gdn_act = torch.empty(c, cfg.gdn_proj_dim, dtype=f32, device=self.dev)
             self.gdn_out = torch.empty(c, cfg.gdn_value_dim, dtype=bf, device=self.dev)
+            # the chunked scan's operand images, one block per (64-row chunk, value head); B2_GDN_WY=0: sequential scan
+            self.gdn_ws = None
+            if os.environ.get("B2_GDN_WY", "1") == "1" and cfg.gdn_head_dim == 128:
+                self.gdn_ws = torch.empty(((c + 63) // 64) * cfg.gdn_v_heads * K.gdn_wy_block_bytes(), dtype=torch.uint8,
+                                          device=self.dev)
         self.ids_stage = Staged((max_chunk,), torch.int64)   # ring of pinned buffers: the host runs a chunk ahead of the copies
         self.ids_dev = torch.empty(max_chunk, dtype=torch.int64, device=self.dev)
         self._slab: Optional[torch.Tensor] = None
@@ -161,8 +168,12 @@ class PrefillRunner:
             phase("gdn_scan")
             K.gdn_conv(self.gdn_proj, 1, c, n, cfg.gdn_conv_channels, None, g.conv_w, eng.kv.gdn_conv[gi],
                        self.gdn_act, slot=slot)
-            K.gdn_chunk(self.gdn_act, c, n, cfg.gdn_k_heads, cfg.gdn_v_heads, cfg.gdn_head_dim, slot, g.a_log,
-                        g.dt_bias, g.norm_w, cfg.rms_eps, eng.kv.gdn_state[gi], self.gdn_out)
+            if self.gdn_ws is not None and c >= 64:
+                K.gdn_chunk_wy(self.gdn_act, c, n, cfg.gdn_k_heads, cfg.gdn_v_heads, cfg.gdn_head_dim, slot, g.a_log,
+                               g.dt_bias, g.norm_w, cfg.rms_eps, eng.kv.gdn_state[gi], self.gdn_out, self.gdn_ws)
+            else:
+                K.gdn_chunk(self.gdn_act, c, n, cfg.gdn_k_heads, cfg.gdn_v_heads, cfg.gdn_head_dim, slot, g.a_log,
+                            g.dt_bias, g.norm_w, cfg.rms_eps, eng.kv.gdn_state[gi], self.gdn_out)
             phase("gdn_out")
             self.linear(g.out_proj, self.gdn_out[:c], resid, G.EPI_RESID_ADD, resid=resid)
         else:

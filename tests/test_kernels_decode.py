@@ -538,3 +538,65 @@ def test_gdn_conv_and_step_match_fp32():
     assert torch.equal(conv_a, conv_b)
     assert (st_a - st_b).abs().max() < 1e-4 * st_a.abs().max()
     assert (out_a.float() - out_b.float()).abs().max() < 0.01 * out_a.float().abs().max() + 1e-3
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("m,seed", [(200, 3), (64, 4), (1000, 5)])
+def test_gdn_chunked_scan_on_tensor_cores_matches_recurrence(m, seed):
+    """The chunked (WY) form of the gated delta rule -- triangular solve per 64-row chunk, state walked chunk by chunk
+    with tensor-core products -- against the row-by-row recurrence in float64 torch, and against the sequential scan
+    kernel: read-out rows, final state; a partial last chunk and a non-zero starting state included."""
+    import torch.nn.functional as F
+    k_ = K()
+    torch.manual_seed(seed)
+    n_k, n_v, dh = 2, 4, 128
+    kd, vd = n_k * dh, n_v * dh
+    n = 2 * kd + 2 * vd + 2 * n_v
+    dev = "cuda"
+    act0 = torch.randn(m, n, device=dev) * 0.8          # what gdn_conv leaves: q | k | v | z | b | a
+    act0[:, 2 * kd + 2 * vd + n_v:] = torch.randn(m, n_v, device=dev) * 1.5 - 1.0     # a: decay factors from ~0.3 to ~1
+    state0 = torch.randn(2, n_v, dh, dh, device=dev) * 0.1
+    a_log = torch.log(torch.rand(n_v, device=dev) * 2 + 0.2)
+    dt_bias, norm_w = torch.randn(n_v, device=dev) * 0.5, 1 + 0.1 * torch.randn(dh, device=dev)
+    eps = 1e-6
+    # float64 reference, row by row
+    f = act0.double()
+    q, k = f[:, :kd].view(m, n_k, dh), f[:, kd:2 * kd].view(m, n_k, dh)
+    v, z = f[:, 2 * kd:2 * kd + vd].view(m, n_v, dh), f[:, 2 * kd + vd:2 * kd + 2 * vd].view(m, n_v, dh)
+    b, a = f[:, 2 * kd + 2 * vd:2 * kd + 2 * vd + n_v], f[:, 2 * kd + 2 * vd + n_v:]
+    q = q * torch.rsqrt((q * q).sum(-1, keepdim=True) + 1e-6) * dh ** -0.5
+    k = k * torch.rsqrt((k * k).sum(-1, keepdim=True) + 1e-6)
+    q, k = q.repeat_interleave(n_v // n_k, 1), k.repeat_interleave(n_v // n_k, 1)
+    decay = torch.exp(-torch.exp(a_log.double()) * F.softplus(a + dt_bias.double()))
+    beta = torch.sigmoid(b)
+    S = state0[1].double().clone()
+    o_ref = torch.zeros(m, n_v, dh, dtype=torch.float64, device=dev)
+    for i in range(m):
+        S = S * decay[i][:, None, None]
+        delta = (v[i] - torch.einsum("hij,hi->hj", S, k[i])) * beta[i][:, None]
+        S = S + torch.einsum("hi,hj->hij", k[i], delta)
+        o_ref[i] = torch.einsum("hij,hi->hj", S, q[i])
+    ref = (o_ref * torch.rsqrt((o_ref * o_ref).mean(-1, keepdim=True) + eps) * norm_w.double() * F.silu(z)).reshape(m, vd)
+    # the two kernels
+    outs, states, raws = [], [], []
+    for wy in (False, True):
+        act, st = act0.clone(), state0.clone()
+        out = torch.zeros(m, vd, dtype=torch.bfloat16, device=dev)
+        if wy:
+            ws = torch.zeros(((m + 63) // 64) * n_v * k_.gdn_wy_block_bytes(), dtype=torch.uint8, device=dev)
+            k_.gdn_chunk_wy(act, m, n, n_k, n_v, dh, 1, a_log, dt_bias, norm_w, eps, st, out, ws)
+        else:
+            k_.gdn_chunk(act, m, n, n_k, n_v, dh, 1, a_log, dt_bias, norm_w, eps, st, out)
+        torch.cuda.synchronize()
+        k_.check_status()
+        outs.append(out.float())
+        states.append(st)
+        raws.append(act[:, 2 * kd:2 * kd + vd].clone())
+    o_scale = float(o_ref.abs().max())
+    for name, raw, st, out in (("scan", raws[0], states[0], outs[0]), ("wy", raws[1], states[1], outs[1])):
+        assert torch.equal(st[0], state0[0]), name                                  # the other slot is untouched
+        e_o = float((raw.double().view(m, n_v, dh) - o_ref).abs().max())
+        e_s = float((st[1].double() - S).abs().max())
+        assert e_o < (2e-5 if name == "scan" else 4e-3) * o_scale + 1e-6, (name, e_o, o_scale)
+        assert e_s < (2e-5 if name == "scan" else 4e-3) * float(S.abs().max()), (name, e_s)
+        assert float((out.double() - ref).abs().max()) < 0.02 * float(ref.abs().max()) + 1e-3, name
