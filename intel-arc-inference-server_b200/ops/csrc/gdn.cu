@@ -156,12 +156,12 @@ __global__ void __launch_bounds__(DH) gdn_step_kernel(const GdnStepParams p) {
 
 // ---- prompt chunks: the same layer as three kernels, so that everything that does not depend on the state runs
 // in parallel over the chunk's rows and the sequential scan is left with two 128-long loops per row.
-//   gdn_prep_kernel  grid (rows, n_k + 1): L2-normalises q and k of a key head in place (q also scaled); the last
-//                    block of a row turns b, a into beta and the decay factor in place;
+//   gdn_prep_kernel  a warp per (row, key head): L2-normalises q and k of a key head in place (q also scaled); the last
+//                    warp of a row turns b, a into beta and the decay factor in place;
 //   gdn_scan_kernel  grid (n_v): walks the rows in order; thread j owns state column j; the row's q / k reach the
 //                    threads through a double-buffered shared-memory copy (one barrier per row), the next row's
 //                    operands are fetched while this row's loops run; the raw read-out replaces v in place;
-//   gdn_gate_kernel  grid (rows, n_v): RMS norm of the read-out, weight, SiLU(z) gate, bf16 store.
+//   gdn_gate_kernel  a warp per (row, value head): RMS norm of the read-out, weight, SiLU(z) gate, bf16 store.
 struct GdnChunkParams {
   float* act;   // [M][N]
   int M, N, n_k, n_v;
@@ -174,20 +174,26 @@ struct GdnChunkParams {
   __nv_bfloat16* out;
 };
 
-__global__ void __launch_bounds__(DH) gdn_prep_kernel(const GdnChunkParams p) {
-  __shared__ float red[4];
+// one warp per (row, key head) -- or per row for the gates; lanes hold four consecutive elements
+__global__ void __launch_bounds__(256) gdn_prep_kernel(const GdnChunkParams p) {
   pdl_wait();
   pdl_launch_dependents();
-  const int m = blockIdx.x, y = blockIdx.y, j = threadIdx.x;
+  const int wid = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  const int m = wid / (p.n_k + 1), y = wid % (p.n_k + 1);
+  if (m >= p.M) return;
   const int kd = p.n_k * DH, vd = p.n_v * DH;
   float* a = p.act + (size_t)m * p.N;
   if (y < p.n_k) {
-    const float qv = a[y * DH + j], kv = a[kd + y * DH + j];
-    const float qn = block_sum_128(qv * qv, red), kn = block_sum_128(kv * kv, red);
-    a[y * DH + j] = qv * rsqrtf(qn + 1e-6f) * 0.08838834764831845f;
-    a[kd + y * DH + j] = kv * rsqrtf(kn + 1e-6f);
+    float4* qp = reinterpret_cast<float4*>(a + y * DH) + lane;
+    float4* kp = reinterpret_cast<float4*>(a + kd + y * DH) + lane;
+    float4 q = *qp, k = *kp;
+    const float qn = warp_sum(q.x * q.x + q.y * q.y + q.z * q.z + q.w * q.w);
+    const float kn = warp_sum(k.x * k.x + k.y * k.y + k.z * k.z + k.w * k.w);
+    const float qs = rsqrtf(qn + 1e-6f) * 0.08838834764831845f, ks = rsqrtf(kn + 1e-6f);
+    *qp = make_float4(q.x * qs, q.y * qs, q.z * qs, q.w * qs);
+    *kp = make_float4(k.x * ks, k.y * ks, k.z * ks, k.w * ks);
   } else {
-    for (int h = j; h < p.n_v; h += DH) {
+    for (int h = lane; h < p.n_v; h += 32) {
       const float bb = a[2 * kd + 2 * vd + h], sp_in = a[2 * kd + 2 * vd + p.n_v + h] + p.dt_bias[h];
       const float softplus = sp_in > 20.f ? sp_in : log1pf(__expf(sp_in));
       a[2 * kd + 2 * vd + h] = 1.f / (1.f + __expf(-bb));
@@ -244,18 +250,24 @@ __global__ void __launch_bounds__(DH) gdn_scan_kernel(const GdnChunkParams p) {
   for (int i = 0; i < DH; ++i) sp[(size_t)i * DH] = S[i];
 }
 
-__global__ void __launch_bounds__(DH) gdn_gate_kernel(const GdnChunkParams p) {
-  __shared__ float red[4];
+// one warp per (row, value head)
+__global__ void __launch_bounds__(256) gdn_gate_kernel(const GdnChunkParams p) {
   pdl_wait();
   pdl_launch_dependents();
-  const int m = blockIdx.x, h = blockIdx.y, j = threadIdx.x;
+  const int wid = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  const int m = wid / p.n_v, h = wid % p.n_v;
+  if (m >= p.M) return;
   const int kd = p.n_k * DH, vd = p.n_v * DH;
   const float* a = p.act + (size_t)m * p.N;
-  const float o = a[2 * kd + h * DH + j], zj = a[2 * kd + vd + h * DH + j];
-  const float ms = block_sum_128(o * o, red) * (1.f / DH);
-  p.out[(size_t)m * vd + h * DH + j] = __float2bfloat16(o * rsqrtf(ms + p.eps) * p.norm_w[j] * (zj / (1.f + __expf(-zj))));
+  const float4 o = reinterpret_cast<const float4*>(a + 2 * kd + h * DH)[lane];
+  const float4 z = reinterpret_cast<const float4*>(a + 2 * kd + vd + h * DH)[lane];
+  const float4 w = reinterpret_cast<const float4*>(p.norm_w)[lane];
+  const float r = rsqrtf(warp_sum(o.x * o.x + o.y * o.y + o.z * o.z + o.w * o.w) * (1.f / DH) + p.eps);
+  uint2 packed;
+  packed.x = pack_bf16(o.x * r * w.x * silu(z.x), o.y * r * w.y * silu(z.y));
+  packed.y = pack_bf16(o.z * r * w.z * silu(z.z), o.w * r * w.w * silu(z.w));
+  reinterpret_cast<uint2*>(p.out + (size_t)m * vd + h * DH)[lane] = packed;
 }
-
 
 // ---------------------------------------------------------------------------------------------------------------
 // Chunked form of the same recurrence on the tensor cores (the role of the reference's
@@ -270,7 +282,7 @@ __global__ void __launch_bounds__(DH) gdn_gate_kernel(const GdnChunkParams p) {
 //                     limbs where the triangular solve amplifies errors), the solve by forward substitution in
 //                     fp32 (thread = one column of [Wk | Wv], its 64 values in registers), and the operand images
 //                     of the scan, padded for conflict-free ldmatrix, in a workspace block per (chunk, head);
-// gdn_wy_scan_kernel  grid (n_v): walks the chunks; warp w owns 16 value columns of the state, S^T[16][128] fp32 in
+// gdn_wy_scan_kernel  grid (n_v, 2), four warps: walks the chunks; a warp owns 16 value columns of the state, S^T[16][128] fp32 in
 //                     MMA accumulator registers for the whole walk.  Every product is written with the value
 //                     dimension as M, so accumulators turn into the next product's A operand in registers
 //                     (S^T -> A of S^T Wk^T and S^T Qg^T; U^T -> A of U^T P^T and U^T Kg) and the warps never
@@ -348,17 +360,27 @@ __global__ void __launch_bounds__(256, 2) gdn_wy_prep_kernel(const GdnWyParams p
     bet[s0] = b0;
     bet[s1] = b1;
   }
-  for (int i = tid; i < WY_C * DH; i += 256) {
-    const int s = i >> 7, col = i & 127;
-    float kv = 0.f, qv = 0.f;
-    if (s < valid) {
-      kv = a0[(size_t)s * p.N + kd + hk * DH + col];
-      qv = a0[(size_t)s * p.N + hk * DH + col];
+  // rows of K and Q into shared memory as bf16 limbs; 16 rows' loads are in flight per thread at a time
+  {
+    const int col = tid & 127, sh = tid >> 7;      // this thread: column col of rows sh, sh + 2, ...
+#pragma unroll
+    for (int s0 = 0; s0 < WY_C; s0 += 32) {
+      float kv[16], qv[16];
+#pragma unroll
+      for (int u = 0; u < 16; ++u) {
+        const int s = s0 + 2 * u + sh;
+        kv[u] = s < valid ? a0[(size_t)s * p.N + kd + hk * DH + col] : 0.f;
+        qv[u] = s < valid ? a0[(size_t)s * p.N + hk * DH + col] : 0.f;
+      }
+#pragma unroll
+      for (int u = 0; u < 16; ++u) {
+        const int s = s0 + 2 * u + sh;
+        const __nv_bfloat16 kh = __float2bfloat16(kv[u]);
+        Khi[s * WY_LDK + col] = kh;
+        Klo[s * WY_LDK + col] = __float2bfloat16(kv[u] - __bfloat162float(kh));
+        Qhi[s * WY_LDK + col] = __float2bfloat16(qv[u]);
+      }
     }
-    const __nv_bfloat16 kh = __float2bfloat16(kv);
-    Khi[s * WY_LDK + col] = kh;
-    Klo[s * WY_LDK + col] = __float2bfloat16(kv - __bfloat162float(kh));
-    Qhi[s * WY_LDK + col] = __float2bfloat16(qv);
   }
   __syncthreads();
   // ---- K K^T (three limb products) and Q K^T (two): warp = (16-row tile, half of the columns)
@@ -444,15 +466,31 @@ __global__ void __launch_bounds__(256, 2) gdn_wy_prep_kernel(const GdnWyParams p
   }
   // Qg = gamma_s q_s (from the fp32 rows)
   __nv_bfloat16* Qg = reinterpret_cast<__nv_bfloat16*>(blk + WY_OFF_QG);
-  for (int i = tid; i < WY_C * DH; i += 256) {
-    const int s = i >> 7, col = i & 127;
-    const float qv = s < valid ? a0[(size_t)s * p.N + hk * DH + col] : 0.f;
-    Qg[s * WY_LDK + col] = __float2bfloat16(qv * __expf(lg[s]));
+  {
+    const int col = tid & 127, sh = tid >> 7;
+#pragma unroll
+    for (int s0 = 0; s0 < WY_C; s0 += 32) {
+      float qv[16];
+#pragma unroll
+      for (int u = 0; u < 16; ++u) {
+        const int s = s0 + 2 * u + sh;
+        qv[u] = s < valid ? a0[(size_t)s * p.N + hk * DH + col] : 0.f;
+      }
+#pragma unroll
+      for (int u = 0; u < 16; ++u) {
+        const int s = s0 + 2 * u + sh;
+        Qg[s * WY_LDK + col] = __float2bfloat16(qv[u] * __expf(lg[s]));
+      }
+    }
   }
   if (tid == 0) *reinterpret_cast<float*>(blk + WY_OFF_GC) = __expf(lg[WY_C - 1]);
 }
 
-constexpr int WYB_SMEM = 2 * WY_BLOCK + 64;
+// the scan's stage: the block's images up to Wv^T, this CTA's half of Wv^T (64 value columns), gamma_63
+constexpr int WYB_WV_HALF = (DH / 2) * WY_LDV * 4;
+constexpr int WYB_STAGE = WY_OFF_WVT + WYB_WV_HALF + 16;
+constexpr int WYB_SMEM = 2 * WYB_STAGE + 64;
+static_assert(WYB_STAGE % 128 == 0 || WYB_STAGE % 16 == 0, "stages start on 16-byte boundaries");
 
 // hi and lo bf16 limbs of a pair of fp32 values (x = hi + lo to about 16 bits)
 __device__ __forceinline__ void split2(float x, float y, uint32_t& hi, uint32_t& lo) {
@@ -460,11 +498,11 @@ __device__ __forceinline__ void split2(float x, float y, uint32_t& hi, uint32_t&
   lo = pack_bf16(x - bf16_lo(hi), y - bf16_hi(hi));
 }
 
-__global__ void __launch_bounds__(256, 1) gdn_wy_scan_kernel(const GdnWyParams p) {
+__global__ void __launch_bounds__(128, 1) gdn_wy_scan_kernel(const GdnWyParams p) {
   extern __shared__ __align__(128) uint8_t wy_smem[];
   const uint32_t stage0 = smem_u32(wy_smem);
-  const uint32_t bar0 = stage0 + 2 * WY_BLOCK;
-  const int h = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const uint32_t bar0 = stage0 + 2 * WYB_STAGE;
+  const int h = blockIdx.x, half = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, t = lane & 3;
   const int kd = p.n_k * DH;
   const uint8_t* ws = p.ws + (size_t)h * WY_BLOCK;
@@ -477,17 +515,21 @@ __global__ void __launch_bounds__(256, 1) gdn_wy_scan_kernel(const GdnWyParams p
   __syncthreads();
   pdl_wait();             // the workspace is the previous kernel's output
   pdl_launch_dependents();
-  if (tid == 0) {
-    for (int c = 0; c < min(2, p.chunks); ++c) {
-      mbar_expect_tx(bar0 + 8 * c, WY_BLOCK);
-      bulk_g2s(stage0 + c * WY_BLOCK, ws + c * ws_step, WY_BLOCK, bar0 + 8 * c);
-    }
-  }
+  auto fetch = [&](int c, int b) {   // three pieces of chunk c's block into stage b
+    const uint32_t dst = stage0 + b * WYB_STAGE, bar = bar0 + 8 * b;
+    const uint8_t* src = ws + (size_t)c * ws_step;
+    mbar_expect_tx(bar, WYB_STAGE);
+    bulk_g2s(dst, src, WY_OFF_WVT, bar);
+    bulk_g2s(dst + WY_OFF_WVT, src + WY_OFF_WVT + half * WYB_WV_HALF, WYB_WV_HALF, bar);
+    bulk_g2s(dst + WY_OFF_WVT + WYB_WV_HALF, src + WY_OFF_GC, 16, bar);
+  };
+  if (tid == 0)
+    for (int c = 0; c < min(2, p.chunks); ++c) fetch(c, c);
   // ---- S^T[dv][dk] of this warp's 16 value columns as accumulator tiles: st[j] covers dk 8j .. 8j+7;
   // [0], [1]: row dv0 = 16 warp + g, columns 8j + 2t, +1;  [2], [3]: row dv0 + 8
   float st[16][4];
   float* sp = p.state + ((size_t)p.slot * p.n_v + h) * DH * DH;
-  const int dv0 = 16 * warp + g;
+  const int dvl = 16 * warp + g, dv0 = 64 * half + dvl;     // row within this CTA's half, and within the head
 #pragma unroll
   for (int j = 0; j < 16; ++j) {
     const int dk = 8 * j + 2 * t;
@@ -499,7 +541,7 @@ __global__ void __launch_bounds__(256, 1) gdn_wy_scan_kernel(const GdnWyParams p
   bool ok = true;
   for (int c = 0; c < p.chunks; ++c) {
     const int b = c & 1;
-    const uint32_t sb = stage0 + b * WY_BLOCK;
+    const uint32_t sb = stage0 + b * WYB_STAGE;
     ok = mbar_wait(bar0 + 8 * b, (c >> 1) & 1, ERR_GDN_WAIT);
     if (!__syncthreads_and(ok)) {
       // a copy gave up: wait (bounded) for the other stage's copy, which may still be in flight, and leave the
@@ -526,19 +568,18 @@ __global__ void __launch_bounds__(256, 1) gdn_wy_scan_kernel(const GdnWyParams p
         for (int u = 0; u < 2; ++u) {
           mma_bf16_16816(r1[2 * jj + u], ah[0], ah[1], ah[2], ah[3], bw[2 * u], bw[2 * u + 1]);
           mma_bf16_16816(r1[2 * jj + u], al[0], al[1], al[2], al[3], bw[2 * u], bw[2 * u + 1]);
-          mma_bf16_16816(r2[2 * jj + u], ah[0], ah[1], ah[2], ah[3], bq[2 * u], bq[2 * u + 1]);
-          mma_bf16_16816(r2[2 * jj + u], al[0], al[1], al[2], al[3], bq[2 * u], bq[2 * u + 1]);
+          mma_bf16_16816(r2[2 * jj + u], ah[0], ah[1], ah[2], ah[3], bq[2 * u], bq[2 * u + 1]);   // read-out only: one limb
         }
       }
     }
     // ---- U^T = Wv^T - R1^T, as A operand limbs over the chunk's rows (4 k-steps of 16)
     uint32_t uh[4][4], ul[4][4];
     {
-      const float* wv = reinterpret_cast<const float*>(wy_smem + b * WY_BLOCK + WY_OFF_WVT);
+      const float* wv = reinterpret_cast<const float*>(wy_smem + b * WYB_STAGE + WY_OFF_WVT);
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
-        const float2 v0 = *reinterpret_cast<const float2*>(wv + dv0 * WY_LDV + 8 * j + 2 * t);
-        const float2 v1 = *reinterpret_cast<const float2*>(wv + (dv0 + 8) * WY_LDV + 8 * j + 2 * t);
+        const float2 v0 = *reinterpret_cast<const float2*>(wv + dvl * WY_LDV + 8 * j + 2 * t);
+        const float2 v1 = *reinterpret_cast<const float2*>(wv + (dvl + 8) * WY_LDV + 8 * j + 2 * t);
         const float u0 = v0.x - r1[j][0], u1 = v0.y - r1[j][1], u2 = v1.x - r1[j][2], u3 = v1.y - r1[j][3];
         // tile j is the k-half (j & 1) of k-step j >> 1: regs 0, 1 (rows g, g + 8) or 2, 3
         split2(u0, u1, uh[j >> 1][2 * (j & 1)], ul[j >> 1][2 * (j & 1)]);
@@ -555,7 +596,6 @@ __global__ void __launch_bounds__(256, 1) gdn_wy_scan_kernel(const GdnWyParams p
 #pragma unroll
         for (int u = 0; u < 2; ++u) {
           mma_bf16_16816(r2[2 * jj + u], uh[kk][0], uh[kk][1], uh[kk][2], uh[kk][3], bp[2 * u], bp[2 * u + 1]);
-          mma_bf16_16816(r2[2 * jj + u], ul[kk][0], ul[kk][1], ul[kk][2], ul[kk][3], bp[2 * u], bp[2 * u + 1]);
         }
       }
     {   // the raw read-out takes v's place in the rows (as the sequential scan leaves it)
@@ -576,7 +616,7 @@ __global__ void __launch_bounds__(256, 1) gdn_wy_scan_kernel(const GdnWyParams p
     }
     // ---- S^T <- gamma_63 S^T + U^T Kg  (B[k = row s][n = dk] from Kg^T [dk][s])
     {
-      const float gc = *reinterpret_cast<const float*>(wy_smem + b * WY_BLOCK + WY_OFF_GC);
+      const float gc = *reinterpret_cast<const float*>(wy_smem + b * WYB_STAGE + WY_OFF_WVT + WYB_WV_HALF);
 #pragma unroll
       for (int j = 0; j < 16; ++j) {
         st[j][0] *= gc; st[j][1] *= gc; st[j][2] *= gc; st[j][3] *= gc;
@@ -595,10 +635,7 @@ __global__ void __launch_bounds__(256, 1) gdn_wy_scan_kernel(const GdnWyParams p
         }
     }
     __syncthreads();     // every warp is done with this stage: the chunk after the next one may land in it
-    if (tid == 0 && c + 2 < p.chunks) {
-      mbar_expect_tx(bar0 + 8 * b, WY_BLOCK);
-      bulk_g2s(sb, ws + (size_t)(c + 2) * ws_step, WY_BLOCK, bar0 + 8 * b);
-    }
+    if (tid == 0 && c + 2 < p.chunks) fetch(c + 2, b);
   }
   if (!ok) {
     // a copy gave up: wait (bounded) for what may still be in flight, leave the state as it was
@@ -621,13 +658,14 @@ __global__ void __launch_bounds__(256, 1) gdn_wy_scan_kernel(const GdnWyParams p
 extern "C" int b2_gdn_chunk(float* act, int M, int N, int n_k, int n_v, int head_dim, int slot, const float* a_log,
                             const float* dt_bias, const float* norm_w, float eps, float* state, void* out, void* stream) {
   if (head_dim != DH || M < 1 || slot < 0 || n_k < 1 || n_v % n_k != 0 || N != 2 * n_k * DH + 2 * n_v * DH + 2 * n_v) return -1;
+  if (N % 4) return -1;   // rows are read in 16-byte pieces
   GdnChunkParams p{act, M, N, n_k, n_v, slot, a_log, dt_bias, norm_w, eps, state, (__nv_bfloat16*)out};
   cudaStream_t st = (cudaStream_t)stream;
-  int rc = b2_launch(gdn_prep_kernel, dim3(M, n_k + 1), dim3(DH), 0, st, true, p);
+  int rc = b2_launch(gdn_prep_kernel, dim3((M * (n_k + 1) + 7) / 8), dim3(256), 0, st, true, p);
   if (rc) return rc;
   rc = b2_launch(gdn_scan_kernel, dim3(n_v), dim3(DH), 0, st, true, p);
   if (rc) return rc;
-  return b2_launch(gdn_gate_kernel, dim3(M, n_v), dim3(DH), 0, st, true, p);
+  return b2_launch(gdn_gate_kernel, dim3((M * n_v + 7) / 8), dim3(256), 0, st, true, p);
 }
 
 // act [M][N] from the projection's split-K partials; the first conv_ch columns go through the 4-tap causal
@@ -656,6 +694,7 @@ extern "C" int b2_gdn_chunk_wy(float* act, int M, int N, int n_k, int n_v, int h
                                const float* dt_bias, const float* norm_w, float eps, float* state, void* out, void* ws,
                                long long ws_bytes, void* stream) {
   if (head_dim != DH || M < 1 || slot < 0 || n_k < 1 || n_v % n_k != 0 || N != 2 * n_k * DH + 2 * n_v * DH + 2 * n_v) return -1;
+  if (N % 4) return -1;   // rows are read in 16-byte pieces
   const int chunks = (M + WY_C - 1) / WY_C;
   if (!ws || ((uintptr_t)ws & 15) || (long long)chunks * n_v * WY_BLOCK > ws_bytes) return -2;
   static bool configured = false;
@@ -668,13 +707,13 @@ extern "C" int b2_gdn_chunk_wy(float* act, int M, int N, int n_k, int n_v, int h
   GdnChunkParams p{act, M, N, n_k, n_v, slot, a_log, dt_bias, norm_w, eps, state, (__nv_bfloat16*)out};
   GdnWyParams w{act, M, N, n_k, n_v, slot, chunks, (uint8_t*)ws, state};
   cudaStream_t st = (cudaStream_t)stream;
-  int rc = b2_launch(gdn_prep_kernel, dim3(M, n_k + 1), dim3(DH), 0, st, true, p);
+  int rc = b2_launch(gdn_prep_kernel, dim3((M * (n_k + 1) + 7) / 8), dim3(256), 0, st, true, p);
   if (rc) return rc;
   rc = b2_launch(gdn_wy_prep_kernel, dim3(chunks, n_v), dim3(256), WYA_SMEM, st, true, w);
   if (rc) return rc;
-  rc = b2_launch(gdn_wy_scan_kernel, dim3(n_v), dim3(256), WYB_SMEM, st, true, w);
+  rc = b2_launch(gdn_wy_scan_kernel, dim3(n_v, 2), dim3(128), WYB_SMEM, st, true, w);
   if (rc) return rc;
-  return b2_launch(gdn_gate_kernel, dim3(M, n_v), dim3(DH), 0, st, true, p);
+  return b2_launch(gdn_gate_kernel, dim3((M * n_v + 7) / 8), dim3(256), 0, st, true, p);
 }
 
 B2_DEFINE_STATUS(gdn)
