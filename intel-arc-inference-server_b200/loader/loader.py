@@ -165,12 +165,32 @@ def _load_gdn_layer(view: NameView, cfg: ModelConfig, prefix: str, qc: QuantConf
 def _load_ffn(lw: LayerWeights, view: NameView, cfg: ModelConfig, prefix: str, qc: QuantConfig, device, tp):
     rank, world = tp
 
-    def mlp(p, ffn):
-        g, u, d = (_LinearSrc(view, f"{p}.{n}_proj", qc) for n in ("gate", "up", "down"))
+    def has_linear(name):
+        return view.has(name + ".qweight") or view.has(name + ".weight")
+
+    def mlp(p, ffn, fused=None):
+        """``fused``: the per-expert form the layer uses (decided from expert 0, required of every expert): separate
+        ``gate_proj`` / ``up_proj``, or one ``gate_up_proj`` whose first half of output columns is gate (the
+        reference reads both: src/loader/moe.h:29-57)."""
+        is_fused = has_linear(f"{p}.gate_up_proj")
+        if fused is not None and is_fused != fused:
+            raise ValueError(f"{p}: mixed expert forms in one layer (gate_up_proj next to gate_proj / up_proj)")
+        d = _LinearSrc(view, f"{p}.down_proj", qc)
+        if is_fused:
+            both = _LinearSrc(view, f"{p}.gate_up_proj", qc)
+            if both.n != 2 * ffn:
+                raise ValueError(f"{p}.gate_up_proj: {both.n} output columns, expected {2 * ffn}")
+            g = u = None
+            gc = lambda lo, hi: _cols(both, lo, hi)
+            uc = lambda lo, hi: _cols(both, ffn + lo, ffn + hi)
+        else:
+            g, u = (_LinearSrc(view, f"{p}.{n}_proj", qc) for n in ("gate", "up"))
+            gc = lambda lo, hi: _cols(g, lo, hi)
+            uc = lambda lo, hi: _cols(u, lo, hi)
         if ffn % (16 * world):
             raise ValueError(f"tensor parallel {world} does not divide FFN {ffn} into runs of 16")
         lo, hi = rank * ffn // world, (rank + 1) * ffn // world
-        gu = _interleave_cols(_cols(g, lo, hi), _cols(u, lo, hi))
+        gu = _interleave_cols(gc(lo, hi), uc(lo, hi))
         if (lo % 64) or (hi % 64):
             raise ValueError(f"tensor parallel {world}: FFN slice {lo}:{hi} is not a whole number of groups")
         return _ql(*gu, device), _ql(d.q[lo:hi], d.scales[lo // 64: hi // 64], device)
@@ -178,8 +198,9 @@ def _load_ffn(lw: LayerWeights, view: NameView, cfg: ModelConfig, prefix: str, q
     if cfg.is_moe:
         lw.router = view.get(prefix + ".mlp.gate.weight").to(torch.bfloat16).to(device)
         lw.experts = []
+        fused = has_linear(f"{prefix}.mlp.experts.0.gate_up_proj")
         for e in range(cfg.n_experts):
-            gu, dn = mlp(f"{prefix}.mlp.experts.{e}", cfg.expert_ffn)
+            gu, dn = mlp(f"{prefix}.mlp.experts.{e}", cfg.expert_ffn, fused)
             lw.experts.append(ExpertWeights(gu, dn))
         lw.experts_gate_up_w4b = torch.stack([x.gate_up.w4b for x in lw.experts]).contiguous()
         lw.experts_down_w4b = torch.stack([x.down.w4b for x in lw.experts]).contiguous()

@@ -39,7 +39,7 @@ def _split_gate_up(ql: QLinear):
             (qv[:, :, 1].reshape(k, -1), sv[:, :, 1].reshape(s.shape[0], -1)))
 
 
-def _emit_layer(out, cfg: ModelConfig, prefix: str, lw: LayerWeights, g_idx: bool):
+def _emit_layer(out, cfg: ModelConfig, prefix: str, lw: LayerWeights, g_idx: bool, fused_experts: bool = False):
     out[prefix + ".input_layernorm.weight"] = lw.input_norm.cpu().to(torch.bfloat16)
     out[prefix + ".post_attention_layernorm.weight"] = lw.post_norm.cpu().to(torch.bfloat16)
     if lw.gdn is not None:
@@ -68,7 +68,13 @@ def _emit_layer(out, cfg: ModelConfig, prefix: str, lw: LayerWeights, g_idx: boo
     if lw.experts is not None:
         out[prefix + ".mlp.gate.weight"] = lw.router.cpu()
         for e, ex in enumerate(lw.experts):
-            mlp(f"{prefix}.mlp.experts.{e}", ex.gate_up, ex.down)
+            if fused_experts:     # one gate_up_proj per expert: gate columns first, then up
+                (gq, gs), (uq, us) = _split_gate_up(ex.gate_up)
+                p = f"{prefix}.mlp.experts.{e}"
+                _emit_linear(out, p + ".gate_up_proj", torch.cat([gq, uq], dim=1), torch.cat([gs, us], dim=1), g_idx)
+                _emit_linear(out, p + ".down_proj", *Q.from_w4b(ex.down.w4b.cpu(), ex.down.n), g_idx)
+            else:
+                mlp(f"{prefix}.mlp.experts.{e}", ex.gate_up, ex.down)
         if lw.shared is not None:
             mlp(prefix + ".mlp.shared_expert", lw.shared.gate_up, lw.shared.down)
             out[prefix + ".mlp.shared_expert_gate.weight"] = lw.shared_gate.cpu()
@@ -77,7 +83,7 @@ def _emit_layer(out, cfg: ModelConfig, prefix: str, lw: LayerWeights, g_idx: boo
 
 
 def write_checkpoint(w: ModelWeights, path: str, shards: int = 2, g_idx: bool = False, wrapper_prefix: bool = False,
-                     quant_method: str = "gptq") -> str:
+                     quant_method: str = "gptq", fused_experts: bool = False) -> str:
     """Writes ``w`` as a snapshot directory and returns it.  Norm weights are stored in bf16 (as real
     checkpoints do), so ``w``'s norms should be bf16-representable for a bit-exact round trip."""
     os.makedirs(path, exist_ok=True)
@@ -85,7 +91,7 @@ def write_checkpoint(w: ModelWeights, path: str, shards: int = 2, g_idx: bool = 
     tensors: Dict[str, torch.Tensor] = {"model.embed_tokens.weight": w.embed.cpu(), "lm_head.weight": w.lm_head.cpu(),
                                         "model.norm.weight": w.final_norm.cpu().to(torch.bfloat16)}
     for i, lw in enumerate(w.layers):
-        _emit_layer(tensors, cfg, f"model.layers.{i}", lw, g_idx)
+        _emit_layer(tensors, cfg, f"model.layers.{i}", lw, g_idx, fused_experts)
     if w.mtp is not None:
         m = w.mtp
         tensors["mtp.pre_fc_norm_embedding.weight"] = m.pre_norm_embed.cpu().to(torch.bfloat16)

@@ -27,8 +27,8 @@ def _bf16_norms(w):
     return w
 
 
-@pytest.mark.parametrize("make,kw", [(tiny_dense, {}), (tiny_moe, {}), (tiny_dense, {"g_idx": True, "wrapper_prefix": True,
-                                                                                         "quant_method": "auto-round"})])
+@pytest.mark.parametrize("make,kw", [(tiny_dense, {}), (tiny_moe, {}), (tiny_moe, {"fused_experts": True}),
+                                     (tiny_dense, {"g_idx": True, "wrapper_prefix": True, "quant_method": "auto-round"})])
 def test_checkpoint_round_trip(tmp_path, make, kw):
     cfg = make()
     if not cfg.is_moe:
@@ -210,3 +210,27 @@ def test_drafter_snapshot_check_lists_every_problem(tmp_path):
     assert "drafter.norm.weight: missing" in msg
     assert "drafter.layers.0.mlp.down_proj.weight: shape" in msg
     assert "drafter.fc.weight: element type I32" in msg
+
+
+def test_mixed_expert_forms_in_a_layer_are_refused(tmp_path):
+    """Experts of one layer come either all as gate_proj / up_proj or all as one gate_up_proj; a mix names the expert."""
+    cfg = tiny_moe()
+    w = _bf16_norms(random_weights(cfg, seed=6))
+    snap = write_checkpoint(w, str(tmp_path / "snap"), shards=1, fused_experts=True)
+    st = SafetensorsSet(snap)
+    t = {n: st.get(n) for n in st.names()}
+    p = "model.layers.0.mlp.experts.1"
+    both = Q.unpack_gptq(t[p + ".gate_up_proj.qweight"])
+    half = both.shape[1] // 2
+    for name, cols in (("gate_proj", slice(0, half)), ("up_proj", slice(half, 2 * half))):
+        t[f"{p}.{name}.qweight"] = Q.pack_gptq(both[:, cols].contiguous())
+        t[f"{p}.{name}.scales"] = t[p + ".gate_up_proj.scales"][:, cols].contiguous()
+        t[f"{p}.{name}.qzeros"] = t[p + ".gate_up_proj.qzeros"][:, : half // 8].contiguous()
+    for sfx in (".qweight", ".scales", ".qzeros"):
+        del t[p + ".gate_up_proj" + sfx]
+    fname = [f for f in os.listdir(snap) if f.endswith(".safetensors")][0]
+    save_file(t, os.path.join(snap, fname), {"format": "pt"})
+    with open(os.path.join(snap, "model.safetensors.index.json"), "w") as f:
+        json.dump({"metadata": {}, "weight_map": {n: fname for n in t}}, f)
+    with pytest.raises(ValueError, match="experts.1: mixed expert forms"):
+        load(snap, device="cpu", report=None)
