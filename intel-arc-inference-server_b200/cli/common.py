@@ -114,16 +114,27 @@ def build_rank_engine(f, par: str) -> int:
     ctl = dist.new_group(backend="gloo", timeout=datetime.timedelta(days=7))     # control plane: host objects only
     plane = L.ControlPlane(ctl)
     kind, deg = L.parse_parallel(par)
+    spec = "off"
     dev = torch.device("cuda", local)
     max_len = 4096 if f.max_len == "auto" else int(f.max_len)
     kw = dict(max_seqs=f.max_num_seqs, max_len=max_len, kv_dtype=f.kv_cache, int8_head=f.int8_head)
     if kind == "replica":
         engine = Engine(load_model(f.model, dev, f.seed, f.int8_head), **kw)
     elif kind == "tp":
+        import dataclasses
+        want_mtp = f.spec == "mtp"
+        if f.spec not in ("auto", "off", "mtp"):
+            raise SystemExit("--parallel tpN serves with --spec mtp or without a draft head")
         if f.model in PRESETS:
-            w = TP.random_shard(preset(f.model), rank, world, dev, f.seed)
+            cfg = preset(f.model)
+            w = TP.random_shard(dataclasses.replace(cfg, mtp_layers=1) if want_mtp else cfg, rank, world, dev, f.seed)
         else:
             w = load_model(f.model, dev, f.seed, f.int8_head, tp=(rank, world))
+        if f.spec in ("auto", "mtp") and w.mtp is not None:
+            spec = "mtp"
+            kw["extra_kv_layers"] = len(w.mtp.layers)
+        elif want_mtp:
+            raise SystemExit("--spec mtp needs a checkpoint with an MTP head")
         engine = TP.make_engine(w, mode="fused", **kw)
     elif kind == "pp":
         from ..parallel import pp as PP
@@ -139,16 +150,20 @@ def build_rank_engine(f, par: str) -> int:
     else:
         raise SystemExit("--parallel ep serves through the expert-parallel prompt pass only: use tpN, ppN or replica")
     adapter = EngineAdapter(engine, eos_ids=(2,))
+    if spec == "mtp":       # every rank carries its slice of the draft head and drafts in lockstep
+        from ..runtime.spec import SpecAdapter
+        adapter = SpecAdapter(adapter, "mtp", f.spec_max)
     if rank != 0:
         n = L.serve_replica_worker(adapter, plane) if kind == "replica" else L.follow_lockstep(adapter, plane)
         sys.stderr.write(f"rank {rank}: {n} commands\n")
         return 0
     from ..server.app import Server, ServerOptions
     from ..server.chat_template import ChatTemplate
-    front = L.ReplicaRouter(adapter, plane) if kind == "replica" else L.LockstepLeader(adapter, plane)
+    front = L.ReplicaRouter(adapter, plane) if kind == "replica" else L.lockstep_leader(adapter, plane)
     tok = find_tokenizer(f.model)
     template = ChatTemplate.from_snapshot(f.model) if f.model not in PRESETS else ChatTemplate()
-    opts = ServerOptions(model_name=engine.cfg.name, log_requests=f.log_requests, spec="off", spec_max=0,
+    opts = ServerOptions(model_name=engine.cfg.name, log_requests=f.log_requests, spec=spec,
+                         spec_max=f.spec_max if spec != "off" else 0,
                          tool_format=f.tool_format, prefix_split_last=f.prefix_split_last)
     srv = Server(front, tok, template, opts, host=f.host, port=f.port)
     sys.stderr.write(f"serving {engine.cfg.name} ({par}, {world} GPUs) on http://{f.host}:{srv.port}/v1\n")

@@ -252,7 +252,9 @@ class DecoderModel:
         return self._gemv("down", lw.down, gu, m, x_mode=1, s_in=s_gu, x_slice=m * 2 * cfg.ffn)
 
     def _gemv_fused(self, name: str, ql: QLinear, x, m: int, norm_w=None, fold: bool = False, x_mode=0, s_in=1,
-                    x_slice=0):
+                    x_slice=0, tp_fold: bool = True):
+        """``tp_fold`` False: a linear every rank holds whole (a draft head's front) folds locally, without the
+        ranks' all-reduce."""
         key = (ql.n, ql.k)
         s = self._splits.get(key)
         if s is None:
@@ -269,7 +271,8 @@ class DecoderModel:
                         norm_w=norm_w, norm_ssq=xq_gs if xq_gs is not None else (b.ssq if norm_w is not None else None),
                         norm_eps=self.cfg.rms_eps,
                         fold_tickets=b.fold_tickets if fold else None, fold_resid=b.resid if fold else None,
-                        fold_ssq=b.ssq if fold else None, tp=self.tp.fold if (fold and self.tp is not None) else None,
+                        fold_ssq=b.ssq if fold else None,
+                        tp=self.tp.fold if (fold and tp_fold and self.tp is not None) else None,
                         tp_mcap=self.tp.mcap if self.tp is not None else 0)
         return part, s
 

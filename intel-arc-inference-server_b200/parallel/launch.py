@@ -104,6 +104,29 @@ class LockstepLeader(EngineIface):
         self.plane.broadcast((SHUTDOWN, ()))
 
 
+class LockstepSpecLeader(LockstepLeader):
+    """The leader of a group whose engines carry a draft head: every rank drafts (the head's layers are sliced like the
+    trunk's and its chained rows meet in the same kernels); the drafts the leader returns reach the followers again as
+    the verify step's rows."""
+
+    def draft(self, slot, pending, k, temperature=0.0, seed=0):
+        return self._all("draft", int(slot), int(pending), int(k), float(temperature), int(seed))
+
+    def draft_many(self, reqs):
+        return self._all("draft_many", {int(s): tuple(r) for s, r in reqs.items()})
+
+    def draft_q(self, slot):
+        return self.e.draft_q(slot)
+
+    @property
+    def stats(self):
+        return self.e.stats
+
+
+def lockstep_leader(engine: EngineIface, plane: ControlPlane) -> LockstepLeader:
+    return LockstepSpecLeader(engine, plane) if hasattr(engine, "draft_many") else LockstepLeader(engine, plane)
+
+
 def follow_lockstep(engine: EngineIface, plane: ControlPlane) -> int:
     """Follower loop of a lock-step group; returns the number of commands executed."""
     n = 0

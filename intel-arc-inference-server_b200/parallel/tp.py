@@ -89,7 +89,14 @@ def shard_weights(full: ModelWeights, rank: int, world: int, device=None) -> Mod
     per = (cfg.vocab + world - 1) // world
     head = full.lm_head[rank * per: min(cfg.vocab, (rank + 1) * per)].to(device).contiguous()
     layers = [shard_layer(lw, cfg, rank, world, device) for lw in full.layers]
-    return ModelWeights(local, full.embed.to(device), head, full.final_norm.to(device), layers)
+    out = ModelWeights(local, full.embed.to(device), head, full.final_norm.to(device), layers)
+    if full.mtp is not None:      # the draft head: its layers are sliced like the trunk's, its front is held whole
+        from ..models.weights import MtpWeights
+        t = full.mtp
+        out.mtp = MtpWeights(t.pre_norm_embed.to(device), t.pre_norm_hidden.to(device),
+                             QLinear(t.fc.w4b.to(device), t.fc.n, t.fc.k),
+                             [shard_layer(lw, cfg, rank, world, device) for lw in t.layers], t.norm.to(device))
+    return out
 
 
 def random_shard(cfg: ModelConfig, rank: int, world: int, device, seed: int = 0) -> ModelWeights:

@@ -87,6 +87,63 @@ def self_check(cfg, modes=("fused", "nccl"), prompt_len: int = 40, kv_dtype: str
     return report
 
 
+def spec_check(cfg, prompt_len: int = 40, new_tokens: int = 24, k: int = 3) -> dict:
+    """Speculative decoding with an MTP head under tensor parallelism: every rank carries its slice of the head
+    (layers sliced like the trunk's, the front held whole) and drafts in lockstep; greedy drafts + verify + accept must
+    give the tokens of the same sharded engine decoding plainly, on every rank (the reference's tp_mtp_test.cc)."""
+    import dataclasses
+    import torch.distributed as dist
+    from ..models.weights import random_weights
+    from ..native import host as H
+    from ..ops import lib as K
+    from ..runtime.spec import SpecAdapter
+    from ..server.adapter import EngineAdapter
+    from . import tp as TP
+    world = dist.get_world_size() if dist.is_initialized() else 1
+    rank = dist.get_rank() if dist.is_initialized() else 0
+    dev = torch.device("cuda", torch.cuda.current_device())
+    cfg = dataclasses.replace(cfg, mtp_layers=1)
+    full = random_weights(cfg, device=dev, seed=0)
+    g = torch.Generator().manual_seed(6)
+    prompt = torch.randint(0, cfg.vocab, (prompt_len,), generator=g).tolist()
+    shard = TP.shard_weights(full, rank, world, dev)
+    max_len = prompt_len + new_tokens + 64
+    plain = TP.make_engine(shard, mode="fused", max_seqs=1, max_len=max_len)
+    plain.model.attn_fixed_spans = True       # the spec engine's setting: a row's bits must not depend on its company
+    plain.graphs.clear()
+    want = plain.generate(prompt, new_tokens)
+    if hasattr(plain, "close"):
+        plain.close()
+    del plain
+    eng = TP.make_engine(shard, mode="fused", max_seqs=1, max_len=max_len, extra_kv_layers=1)
+    ad = SpecAdapter(EngineAdapter(eng), "mtp", k)
+    pending = ad.prefill(0, prompt)
+    got, iters, accepted = [pending], 0, 0
+    while len(got) < new_tokens:
+        drafts = ad.draft(0, pending, k)
+        out = ad.step({0: [pending] + drafts})[0]
+        acc, nxt = H.accept_greedy(out, drafts)
+        if acc < len(drafts):
+            ad.truncate(0, ad.length(0) - (len(drafts) - acc))
+        got += drafts[:acc] + [nxt]
+        pending = nxt
+        iters += 1
+        accepted += acc
+    K.check_status()
+    tt = torch.tensor(got[:new_tokens], device=dev, dtype=torch.int64)
+    all_t = [torch.empty_like(tt) for _ in range(world)]
+    if world > 1:
+        dist.all_gather(all_t, tt)
+    else:
+        all_t = [tt]
+    same = all(bool((x == all_t[0]).all()) for x in all_t)
+    good = got[:new_tokens] == want[:new_tokens] and same and ad.stats["drafted"] >= iters
+    if hasattr(eng, "close"):
+        eng.close()
+    return {"tokens_equal_plain": got[:new_tokens] == want[:new_tokens], "ranks_same_tokens": same, "iterations": iters,
+            "drafted": ad.stats["drafted"], "accepted": accepted, "prompt": prompt_len, "ok": good}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--model", default="small-dense")
@@ -102,6 +159,7 @@ def main():
     ap.add_argument("--ops", type=int, default=0, help="time the fused GEMM+collective kernels alone on a chunk of this many rows")
     ap.add_argument("--pp", action="store_true", help="pipeline check: the ranks are stages; tokens must equal the one-GPU run")
     ap.add_argument("--prompt", type=int, default=40, help="prompt length of --check (> 64 takes the GEMM path)")
+    ap.add_argument("--spec", action="store_true", help="MTP drafts + verify under tensor parallelism equal plain decoding")
     args = ap.parse_args()
 
     import torch.distributed as dist
@@ -129,6 +187,10 @@ def main():
         chk = self_check(cfg, args.modes.split(","), args.prompt, kv_dtype=args.kv_cache)
         ok = ok and all(v["ok"] for v in chk.values())
         report.update(chk)
+    if args.spec:
+        sc = spec_check(widen_for(cfg, world), args.prompt)
+        ok = ok and sc["ok"]
+        report["spec_mtp"] = sc
     if args.pp:
         from . import pp as PP
         full = random_weights(cfg, device=dev, seed=0)

@@ -34,6 +34,7 @@ class TpPrefillRunner(PrefillRunner):
     def __init__(self, engine, group=None, max_chunk: int = 4096):
         import torch.distributed as dist
         super().__init__(engine, max_chunk)
+        self.group = group
         if self.backend not in ("bf16", "bf16-resident"):
             raise ValueError("the tensor-parallel prompt pass runs the bf16 GEMMs")
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
@@ -95,8 +96,22 @@ class TpPrefillRunner(PrefillRunner):
             arr = G.gemm_tp(act, self._w_bf16(lw.down), None, G.EPI_RS_PUSH, rs=self.rs, rs_tpr=self.tpr)
             nxt = layers[li + 1].input_norm if li + 1 < len(layers) else m.w.final_norm
             self._fold(w, arr, nxt, c)
+        hook = getattr(eng, "on_chunk_hidden", None)
+        if hook is not None:
+            # a draft head ingests the prompt from the trunk's hidden rows: every rank holds the rows it owns, so the
+            # ranks exchange them (one all-gather per chunk) and each runs the head over the whole chunk, in row steps
+            hook(None, slot, ids, pos0, self._gather_resid(c))
         eng.seq_len[slot] = max(eng.seq_len[slot], pos0 + c)
         return c
+
+    def _gather_resid(self, c: int) -> torch.Tensor:
+        import torch.distributed as dist
+        if self.world == 1:
+            return self.own[:c]
+        if getattr(self, "_resid_all", None) is None:
+            self._resid_all = torch.empty(self.world * self.rows_cap, self.cfg.hidden, dtype=torch.bfloat16, device=self.dev)
+        dist.all_gather_into_tensor(self._resid_all, self.own, group=self.group)
+        return self._resid_all[:c]
 
     def run(self, slot: int, ids: List[int], chunk: Optional[int] = None) -> int:
         eng, cfg, m = self.eng, self.cfg, self.eng.model

@@ -17,6 +17,7 @@ Rows the head wrote beyond the accepted length are overwritten by the next catch
 """
 from __future__ import annotations
 
+import os
 from typing import Dict, List, Optional, Sequence
 
 import numpy as np
@@ -82,6 +83,7 @@ class DraftHead:
         self.df_val = torch.zeros(engine.max_rows, nk, dtype=torch.float32, device=dev)
         self.df_chosen = torch.zeros(engine.max_rows, dtype=torch.int32, device=dev)
         self.df_host = None          # pinned (candidates, scores) of the last pass, read on demand
+        self.fused_layers = os.environ.get("B2_HEAD_FUSED", "1") == "1"    # 0: the head's layers walk unfused
         self.graphs = {}
         self.prev_last: Dict[int, torch.Tensor] = {}    # last hidden of the previous prompt chunk, per slot
         engine.on_chunk_hidden = self._ingest_chunk
@@ -98,14 +100,24 @@ class DraftHead:
         h = cfg.hidden
         K.draft_front(m.w.embed, eng.ctrl, cfg.vocab, self.hid_in, head.pre_norm_embed, head.pre_norm_hidden,
                       cfg.rms_eps, n, h, self.xcat, b.flag)
-        part, s = m._gemv("head_fc", head.fc, self.xcat, n)
-        # residual stream of the head = the fc output (the split-K slices folded onto zero rows)
-        K.resid_norm(1, n, h, head.norm, cfg.rms_eps, b.resid, None, resid_in=self.zero_rows, part=part,
-                     part_slice=n * h, splits=s)
+        dense = all(lw.gate_up is not None and lw.gdn is None for lw in head.layers)
         m.block_rows = block         # rows flagged in the control block attend to the whole block (no causal mask)
         try:
-            pend = m.layers_walk(head.layers, n, eng.ctrl, eng.block_table, eng.max_blocks, eng.kv,
-                                 first_from_embed=False, kv_layer0=self.kv0)
+            if m.fused and dense and h % 128 == 0 and self.fused_layers:
+                # the front's GEMV folds its split-K slices onto zero rows and leaves the rows' sums of squares: the
+                # head's layers then run as the trunk's do (six launches each, tensor-parallel folds included); the
+                # front itself is held whole by every rank
+                b.resid[:n].copy_(self.zero_rows[:n])
+                m._gemv_fused("head_fc", head.fc, self.xcat, n, fold=True, tp_fold=False)
+                pend = m.layers_walk(head.layers, n, eng.ctrl, eng.block_table, eng.max_blocks, eng.kv,
+                                     first_from_embed=False, kv_layer0=self.kv0, resid_ready=True)
+            else:
+                part, s = m._gemv("head_fc", head.fc, self.xcat, n)
+                # residual stream of the head = the fc output (the split-K slices folded onto zero rows)
+                K.resid_norm(1, n, h, head.norm, cfg.rms_eps, b.resid, None, resid_in=self.zero_rows, part=part,
+                             part_slice=n * h, splits=s)
+                pend = m.layers_walk(head.layers, n, eng.ctrl, eng.block_table, eng.max_blocks, eng.kv,
+                                     first_from_embed=False, kv_layer0=self.kv0)
         finally:
             m.block_rows = False
         if self.kind == "dflash":
