@@ -235,11 +235,14 @@ def main():
         steps, warm = min(args.steps, 32), max(args.warmup, 3)
         tpx = {"world": world, "parallelism": f"tp{world}"}
         tpx["self_check_small_dense"] = TPC.self_check(TPC.widen_for(preset("small-dense"), world), ("fused", "nccl"), 200)
+        tpx["spec_mtp_check_small_dense"] = TPC.spec_check(TPC.widen_for(preset("small-dense"), world), 200)
         tpx["decode8_nccl"] = TP.bench_decode(cfg, "nccl", args.depth, steps, warm, rows=args.tp_rows, kv_dtype=args.kv_cache)
         for mode in ("fused", "nccl"):
             tpx[f"decode_{mode}"] = TP.bench_decode(cfg, mode, args.depth, steps, warm)
             tpx[f"prefill_{mode}"] = TP.bench_prefill(cfg, mode, args.prefill_len)
         tpx["fused_ops"] = TP.bench_fused_ops(cfg, args.prefill_len, peaks=load_peaks())
+        # speculative decoding under tensor parallelism: the MTP head sliced over the ranks, forced acceptance
+        tpx["spec_mtp_k3_accept4_fused"] = TP.bench_spec_mtp(cfg, min(args.depth, 4096))
         # the 8-request serving case of the 27B configuration: 32,768-token prompts into an int8 KV cache, then the
         # eight requests decode together at that depth (the sharded model against itself on one GPU first)
         tpx["self_check_small_dense_int8kv"] = TPC.self_check(TPC.widen_for(preset("small-dense"), world), ("fused",), 200,

@@ -209,6 +209,50 @@ def bench_decode(cfg: ModelConfig, mode: str, depth: int, steps: int, warmup: in
     return out
 
 
+def bench_spec_mtp(cfg: ModelConfig, depth: int, iters: int = 12, k: int = 3, accept: int = 3) -> dict:
+    """Draft-and-verify iterations with an MTP head under tensor parallelism (fused wires), FORCED acceptance so the
+    time does not depend on what a random-init head proposes: prompt pass of ``depth`` tokens (the head ingests it from
+    the gathered hidden rows), then ``iters`` iterations of k chained drafts + one verify step of k + 1 rows on every
+    rank in lockstep.  Device time, max over ranks; tokens/s = (accept + 1) / iteration."""
+    import torch.distributed as dist
+    from ..ops import lib as K
+    from ..runtime.spec import SpecAdapter
+    from ..server.adapter import EngineAdapter
+    world = dist.get_world_size() if dist.is_initialized() else 1
+    rank = dist.get_rank() if dist.is_initialized() else 0
+    dev = torch.device("cuda", torch.cuda.current_device())
+    w = random_shard(dataclasses.replace(cfg, mtp_layers=1), rank, world, dev)
+    eng = make_engine(w, mode="fused", max_seqs=1, max_len=depth + (k + 1) * (iters + 8) + 64, extra_kv_layers=1)
+    ad = SpecAdapter(EngineAdapter(eng), "mtp", k)
+    g = torch.Generator().manual_seed(0)
+    ids = torch.randint(0, cfg.vocab - 1, (depth,), generator=g).tolist()
+    pending = ad.prefill(0, ids)
+
+    def iteration(pending):
+        drafts = ad.draft(0, pending, k)
+        res = ad.step({0: [pending] + drafts})[0]
+        keep = min(accept, len(drafts))
+        if keep < len(drafts):
+            ad.truncate(0, ad.length(0) - (len(drafts) - keep))
+        return res[keep]
+
+    for _ in range(3):
+        pending = iteration(pending)
+    _sync_all()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        pending = iteration(pending)
+    e1.record()
+    _sync_all()
+    ms = _max_over_ranks(e0.elapsed_time(e1) / iters, dev)
+    K.check_status()
+    if hasattr(eng, "close"):
+        eng.close()
+    return {"world": world, "depth": depth, "k": k, "accepted": accept, "ms_per_iteration": ms,
+            "tokens_per_s": (accept + 1) / ms * 1e3, "rows_verified": k + 1}
+
+
 def bench_prefill(cfg: ModelConfig, mode: str, n: int, reps: int = 4, kv_dtype: str = "bf16") -> dict:
     """Whole prompt passes of ``n`` tokens through ``Engine.prefill``; ms is the max over ranks."""
     import torch.distributed as dist
