@@ -123,8 +123,8 @@ def build_rank_engine(f, par: str) -> int:
     elif kind == "tp":
         import dataclasses
         want_mtp = f.spec == "mtp"
-        if f.spec not in ("auto", "off", "mtp"):
-            raise SystemExit("--parallel tpN serves with --spec mtp or without a draft head")
+        if f.spec not in ("auto", "off", "mtp", "dflash"):
+            raise SystemExit("--parallel tpN serves with --spec mtp, --spec dflash or without a draft head")
         if f.model in PRESETS:
             cfg = preset(f.model)
             w = TP.random_shard(dataclasses.replace(cfg, mtp_layers=1) if want_mtp else cfg, rank, world, dev, f.seed)
@@ -135,6 +135,9 @@ def build_rank_engine(f, par: str) -> int:
             kw["extra_kv_layers"] = len(w.mtp.layers)
         elif want_mtp:
             raise SystemExit("--spec mtp needs a checkpoint with an MTP head")
+        elif f.spec == "dflash":
+            spec = "dflash"
+            kw["extra_kv_layers"] = 2
         engine = TP.make_engine(w, mode="fused", **kw)
     elif kind == "pp":
         from ..parallel import pp as PP
@@ -150,9 +153,9 @@ def build_rank_engine(f, par: str) -> int:
     else:
         raise SystemExit("--parallel ep serves through the expert-parallel prompt pass only: use tpN, ppN or replica")
     adapter = EngineAdapter(engine, eos_ids=(2,))
-    if spec == "mtp":       # every rank carries its slice of the draft head and drafts in lockstep
+    if spec != "off":       # every rank carries its slice of the draft head and drafts in lockstep
         from ..runtime.spec import SpecAdapter
-        adapter = SpecAdapter(adapter, "mtp", f.spec_max)
+        adapter = SpecAdapter(adapter, spec, f.spec_max, f.draft_model)
     if rank != 0:
         n = L.serve_replica_worker(adapter, plane) if kind == "replica" else L.follow_lockstep(adapter, plane)
         sys.stderr.write(f"rank {rank}: {n} commands\n")

@@ -308,14 +308,15 @@ def check_drafter(st, cfg: ModelConfig, prefix: str, n_layers: int, group_size: 
     return bad
 
 
-def load_drafter(snapshot: str, device="cuda", report=sys.stderr) -> MtpWeights:
+def load_drafter(snapshot: str, device="cuda", report=sys.stderr, tp: Tuple[int, int] = (0, 1)) -> MtpWeights:
     """A draft head from its own snapshot (``--draft-model``): the front (``fc`` over [norm(embed) ‖ norm(hidden)],
     the two pre-norms), its decoder layers and its output norm.  Linears come as int4 (the GPTQ layout of the main
     checkpoint), dense bf16 / fp16, or int8 with a scale per output row; the last two are quantised to int4 g64 on the
     host.  Tensor names may carry the prefix ``mtp.`` (a head cut out of a main checkpoint), ``drafter.`` or none.
     ``mask_token_id`` of ``config.json`` names the token whose embedding row stands for "not drafted yet" in a block.
     The snapshot's tensors are checked against the configuration before anything is read; one error lists every
-    problem.  The reference: src/loader/dflash_loader.h:24-75, src/loader/loader.cc:521 load_mtp."""
+    problem.  ``tp`` = (rank, world): the layers are sliced like the trunk's (the reference splits its drafter for two
+    cards: src/loader/dflash_tp_split.h), the front and the norms are held whole.  The reference: src/loader/dflash_loader.h:24-75, src/loader/loader.cc:521 load_mtp."""
     snap = resolve_snapshot(snapshot)
     with open(os.path.join(snap, "config.json")) as f:
         hf = json.load(f)
@@ -341,7 +342,7 @@ def load_drafter(snapshot: str, device="cuda", report=sys.stderr) -> MtpWeights:
     head = MtpWeights(view.get(prefix + "pre_fc_norm_embedding.weight").float().to(device),
                       view.get(prefix + "pre_fc_norm_hidden.weight").float().to(device),
                       _ql(fc.q, fc.scales, device),
-                      [_load_layer(view, cfg, f"{prefix}layers.{i}", qc, device, (0, 1)) for i in range(n_layers)],
+                      [_load_layer(view, cfg, f"{prefix}layers.{i}", qc, device, tp) for i in range(n_layers)],
                       view.get(prefix + "norm.weight").float().to(device))
     mt = hf.get("mask_token_id")
     head.mask_token = int(mt) if mt is not None and 0 <= int(mt) < cfg.vocab else None

@@ -110,7 +110,7 @@ class TpWires:
         import torch.distributed as dist
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
-        self.mcap, self.hidden = mcap, hidden
+        self.mcap, self.hidden, self.group = mcap, hidden, group
         nb = (hidden + 127) // 128
         w = self.world
         self.fold = Wire(2 * w * mcap * hidden * 4, 2 * w * nb, nb, group, device)

@@ -87,10 +87,12 @@ def self_check(cfg, modes=("fused", "nccl"), prompt_len: int = 40, kv_dtype: str
     return report
 
 
-def spec_check(cfg, prompt_len: int = 40, new_tokens: int = 24, k: int = 3) -> dict:
+def spec_check(cfg, prompt_len: int = 40, new_tokens: int = 24, k: int = 3, kind: str = "mtp") -> dict:
     """Speculative decoding with an MTP head under tensor parallelism: every rank carries its slice of the head
     (layers sliced like the trunk's, the front held whole) and drafts in lockstep; greedy drafts + verify + accept must
-    give the tokens of the same sharded engine decoding plainly, on every rank (the reference's tp_mtp_test.cc)."""
+    give the tokens of the same sharded engine decoding plainly, on every rank (the reference's tp_mtp_test.cc).
+    ``kind`` "dflash": a block drafter instead -- every rank finds the candidates of its vocabulary slice, the ranks
+    merge them, and all must pick the same drafts."""
     import dataclasses
     import torch.distributed as dist
     from ..models.weights import random_weights
@@ -115,12 +117,17 @@ def spec_check(cfg, prompt_len: int = 40, new_tokens: int = 24, k: int = 3) -> d
     if hasattr(plain, "close"):
         plain.close()
     del plain
-    eng = TP.make_engine(shard, mode="fused", max_seqs=1, max_len=max_len, extra_kv_layers=1)
-    ad = SpecAdapter(EngineAdapter(eng), "mtp", k)
+    eng = TP.make_engine(shard, mode="fused", max_seqs=1, max_len=max_len, extra_kv_layers=2)
+    ad = SpecAdapter(EngineAdapter(eng), kind, k)
     pending = ad.prefill(0, prompt)
-    got, iters, accepted = [pending], 0, 0
+    got, iters, accepted, same_drafts = [pending], 0, 0, True
     while len(got) < new_tokens:
         drafts = ad.draft(0, pending, k)
+        if world > 1:      # every rank proposes the same tokens
+            dt = torch.tensor(drafts + [0] * (k - len(drafts)), device=dev, dtype=torch.int64)
+            all_d = [torch.empty_like(dt) for _ in range(world)]
+            dist.all_gather(all_d, dt)
+            same_drafts = same_drafts and all(bool((x == all_d[0]).all()) for x in all_d)
         out = ad.step({0: [pending] + drafts})[0]
         acc, nxt = H.accept_greedy(out, drafts)
         if acc < len(drafts):
@@ -137,10 +144,11 @@ def spec_check(cfg, prompt_len: int = 40, new_tokens: int = 24, k: int = 3) -> d
     else:
         all_t = [tt]
     same = all(bool((x == all_t[0]).all()) for x in all_t)
-    good = got[:new_tokens] == want[:new_tokens] and same and ad.stats["drafted"] >= iters
+    good = got[:new_tokens] == want[:new_tokens] and same and same_drafts and ad.stats["drafted"] >= iters
     if hasattr(eng, "close"):
         eng.close()
-    return {"tokens_equal_plain": got[:new_tokens] == want[:new_tokens], "ranks_same_tokens": same, "iterations": iters,
+    return {"kind": kind, "tokens_equal_plain": got[:new_tokens] == want[:new_tokens], "ranks_same_tokens": same,
+            "ranks_same_drafts": same_drafts, "iterations": iters,
             "drafted": ad.stats["drafted"], "accepted": accepted, "prompt": prompt_len, "ok": good}
 
 
@@ -188,9 +196,10 @@ def main():
         ok = ok and all(v["ok"] for v in chk.values())
         report.update(chk)
     if args.spec:
-        sc = spec_check(widen_for(cfg, world), args.prompt)
-        ok = ok and sc["ok"]
-        report["spec_mtp"] = sc
+        for kind in ("mtp", "dflash"):
+            sc = spec_check(widen_for(cfg, world), args.prompt, kind=kind)
+            ok = ok and sc["ok"]
+            report["spec_" + kind] = sc
     if args.pp:
         from . import pp as PP
         full = random_weights(cfg, device=dev, seed=0)

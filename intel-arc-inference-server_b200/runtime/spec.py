@@ -171,11 +171,36 @@ class DraftHead:
             else:
                 K.head_gemv(m.w.lm_head, b.x, b.logits, n, nv, h, b.cand_val, b.cand_idx)
             DF.topk(b.logits, n, nv, nv, DF_CANDIDATES, self.df_cand0, self.df_val0)
+        if m.tp is not None or m.nccl is not None:
+            return          # a vocabulary slice per rank: the ranks' candidates are merged after the pass (_merge_ranks)
         if exact:
             self.df_cand[:n].copy_(self.df_cand0[:n])
             self.df_val[:n].copy_(self.df_val0[:n])
         else:
             DF.rerank(m.w.lm_head, b.x, n, m.head_rows, self.df_cand0, DF_CANDIDATES, DF_CANDIDATES, self.df_cand, self.df_val)
+
+    def _merge_ranks(self, n: int):
+        """Tensor parallelism: every rank holds the 16 best of its vocabulary slice; the ranks exchange them (one small
+        all-gather) and each keeps the 16 best of all, larger score first and the lower id among equals -- the same
+        list on every rank (the reference merges its two halves' candidates on the host:
+        src/runtime/dflash/tp_dflash_drafter.h)."""
+        import torch.distributed as dist
+        m = self.eng.model
+        world = m.tp.world if m.tp is not None else m.nccl[1]
+        group = getattr(m.tp, "group", None) if m.tp is not None else m.nccl[2]
+        off = m.vocab_offset if m.tp is not None else m.vocab_offset_nccl
+        ids = self.df_cand0[:n].to(torch.int64)
+        ids = torch.where(ids == DF.NO_IDX, ids, ids + off)
+        mine = torch.stack([ids, self.df_val0[:n].view(torch.int32).to(torch.int64)], dim=0).contiguous()     # [2][n][16]
+        every = torch.empty((world,) + tuple(mine.shape), dtype=torch.int64, device=mine.device)
+        dist.all_gather_into_tensor(every, mine, group=group)
+        all_ids = every[:, 0].permute(1, 0, 2).reshape(n, -1)
+        all_val = every[:, 1].permute(1, 0, 2).reshape(n, -1).to(torch.int32).view(torch.float32)
+        by_id = torch.sort(all_ids, dim=1, stable=True)
+        val = torch.gather(all_val, 1, by_id.indices)
+        by_val = torch.sort(val, dim=1, descending=True, stable=True)       # equal scores stay in id order
+        self.df_val[:n].copy_(by_val.values[:, :DF_CANDIDATES])
+        self.df_cand[:n].copy_(torch.gather(by_id.values, 1, by_val.indices)[:, :DF_CANDIDATES].to(torch.int32))
 
     def _pick(self, row0: int, n: int, temperature: float, seed: int):
         """One token per row out of its candidates into the control block's output words: the best one, or at a
@@ -225,6 +250,8 @@ class DraftHead:
         if chain < 0:
             self._run(n, False, any(r.block for r in rows))
             if self.kind == "dflash":
+                if eng.model.tp is not None or eng.model.nccl is not None:
+                    self._merge_ranks(n)
                 for row0, cnt, temperature, seed in (picks or [(0, n, 0.0, 0)]):
                     self._pick(row0, cnt, temperature, seed)
                 self.df_host = None
@@ -295,12 +322,17 @@ class SpecAdapter:
                 raise ValueError("--spec mtp needs a checkpoint with an MTP head")
             head, kind = w.mtp, "mtp"
         else:
-            if isinstance(draft_model, str):      # a drafter snapshot (--draft-model)
+            if isinstance(draft_model, str):      # a drafter snapshot (--draft-model); sliced under tensor parallelism
                 from ..loader.loader import load_drafter
-                draft_model = load_drafter(draft_model, self.e.device)
+                tpw = self.e.model.tp
+                draft_model = load_drafter(draft_model, self.e.device,
+                                           tp=(tpw.rank, tpw.world) if tpw is not None else (0, 1))
             head = draft_model if isinstance(draft_model, MtpWeights) else random_drafter(self.e.cfg, self.e.device)
             kind = "dflash"
         dv = None
+        sharded = self.e.model.tp is not None or self.e.model.nccl is not None
+        if draft_vocab and draft_vocab < self.e.cfg.vocab and sharded:
+            raise ValueError("a reduced draft vocabulary is not sliced for tensor parallelism")
         if draft_vocab and draft_vocab < self.e.cfg.vocab:
             from ..loader.draft_vocab import DraftVocab, build_draft_vocab, read_ranked_ids
             ranked = read_ranked_ids(draft_vocab_ids) if draft_vocab_ids else None
