@@ -2,38 +2,25 @@
 //
 //   O[r] = softmax( q[r] . K[0 .. pos(r)]^T / sqrt(D) ) V[0 .. pos(r)]      pos(r) = pos0 + r
 //
-// Stands where the reference has pf_flash_attn / pf_flash_merge (src/kernels/prefill/
-// pf_flash_attn.cl).  One CTA owns 128 query rows of one query head and walks the keys in tiles
-// of 128 (8 pages of 16 tokens); the K and V tiles of the head's KV group are fetched page by page
-// with 2-D TMA (box = 16 keys x 64 dims, 128-byte swizzle) straight from the page pool through the
-// sequence's block table, double buffered.
-//   warp 0     TMA producer (Q once, then K / V tiles)
-//   warp 1     MMA issuer: S = Q K^T (M 128, N 128, K 16 x 8) into one of two TMEM score buffers, issued one
-//              tile AHEAD of O += P V, so the tensor pipe computes the next scores while the softmax threads
-//              work; V is an MN-major operand (the cache keeps keys as rows, which is what P V needs along K);
-//              O accumulates in TMEM over all key tiles
-//   warps 2-9  two threads per query row (64 of the 128 key columns each; maxima and sums meet in shared memory): one tcgen05.ld pass of the S row into registers, causal mask,
-//              softmax in fp32 with exp2 against a lazily updated reference maximum, P written to shared
-//              memory as bf16 in the swizzled K-major layout; when a row's maximum moves by more than 2^6 the
-//              row's accumulator is rescaled in place in TMEM before the next P V is issued
-// All mbarrier waits are bounded (common.cuh); on a failed wait every role leaves its loop and the
-// CTA still meets at the final barrier and frees its tensor memory.
+// Stands where the reference has pf_flash_attn / pf_flash_merge (src/kernels/prefill/pf_flash_attn.cl; its pair form
+// shares K / V between two query tiles the same way).  One CTA owns TWO query tiles (256 rows) of one query head and
+// walks the keys in tiles of 64 (4 pages of 16 tokens); the K and V tiles of the head's KV group are fetched page by
+// page with 2-D TMA (box = 16 keys x 64 dims, 128-byte swizzle) straight from the page pool through the sequence's
+// block table, double buffered.  Scores S = Q K^T (M 128, N 64) and the output O += P V (M 128, N 128; V is an
+// MN-major operand: the cache keeps keys as rows, which is what P V needs along K) live in tensor memory; the
+// softmax runs in fp32 with exp2 against a lazily updated reference maximum (a row's accumulator is rescaled in
+// place in TMEM only when its maximum moved by more than 2^6); P goes through shared memory as bf16 in the swizzled
+// K-major layout.  The roles, the buffers and what was measured to set their numbers are described at the kernel.
+// All mbarrier waits are bounded (common.cuh); on a failed wait every role leaves its loop and the CTA still meets
+// at the final barrier and frees its tensor memory.
 #include "common.cuh"
-
-#include <cstdlib>
 
 using namespace b2;
 
 namespace {
 
 constexpr int D = 128;
-constexpr int BQ = 128;   // query rows per CTA
-constexpr int BK = 128;   // keys per tile
-constexpr int kThreads = 320;   // TMA warp, MMA warp, two softmax warpgroups (each takes half of a row's columns)
-constexpr int Q_BYTES = BQ * D * 2;       // 32 KB: [2 d-blocks][128 rows][64]
-constexpr int KV_BYTES = BK * D * 2;      // 32 KB each for K and V
-constexpr int P_BYTES = BQ * BK * 2;      // 32 KB: [2 key-blocks][128 rows][64]
-constexpr int SMEM = Q_BYTES + 2 * 2 * KV_BYTES + 2 * P_BYTES + 1024 + 256 + 2 * 128 * 4;   // 231,680 of 232,448 bytes
+constexpr int BQ = 128;   // rows of a query tile
 
 struct AttnPfParams {
   const int* block_table;  // this sequence's page table
@@ -46,19 +33,6 @@ struct AttnPfParams {
   __nv_bfloat16* out;  // [C][n_q * D]
 };
 
-// smem descriptor for the MN-major V operand: rows are keys (128 B = 64 dims, 128-byte swizzle),
-// 8-key groups are 1024 B apart (stride byte offset); the next block of 64 dims is a whole tile
-// half away (leading byte offset).
-__device__ __forceinline__ uint64_t make_desc_v(uint32_t smem_addr) {
-  uint64_t d = 0;
-  d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);
-  d |= (uint64_t)((BK * 128) >> 4) << 16;
-  d |= (uint64_t)(1024 >> 4) << 32;
-  d |= (uint64_t)1 << 46;
-  d |= (uint64_t)2 << 61;
-  return d;
-}
-
 #ifdef B2_ATTN_PROF
 // measurement build: cycles per phase, summed over tiles and CTAs by one softmax thread and the MMA thread
 __device__ unsigned long long g_attn_prof[16];
@@ -69,326 +43,11 @@ __device__ unsigned long long g_attn_prof[16];
 #define APROF_ADD(i, a, b)
 #endif
 
-__global__ void __launch_bounds__(kThreads, 1)
-attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-                    const __grid_constant__ CUtensorMap map_v, const AttnPfParams p) {
-  extern __shared__ uint8_t smem_raw[];
-  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  const uint32_t q_s = base, kv_s = base + Q_BYTES, p_s = kv_s + 4 * KV_BYTES, bars = p_s + 2 * P_BYTES;
-  // barriers: q_full, k_full[2], v_full[2], k_empty[2], v_empty[2], s_full[2], s_free[2], p_full, o_done[2]
-  const uint32_t b_qfull = bars, b_kfull = bars + 8, b_vfull = bars + 24, b_kempty = bars + 40, b_vempty = bars + 56,
-                 b_sfull = bars + 72, b_sfree = bars + 88, b_pfull = bars + 104, b_odone = bars + 112;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_raw + (bars + 128 - smem_u32(smem_raw)));
-
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int qt = gridDim.x - 1 - blockIdx.x;  // heavy (late) tiles first
-  const int head = blockIdx.y, kh = head / (p.n_q / p.n_kv);
-  const int row0 = qt * BQ;
-  const int last_pos = p.pos0 + min(row0 + BQ, p.C) - 1;
-  const int t0 = p.window > 0 ? max(0, p.pos0 + row0 - p.window + 1) / BK : 0;   // first key tile any row of the CTA needs
-  const int n_tiles = last_pos / BK + 1 - t0;
-
-  if (threadIdx.x == 0) {
-    mbar_init(b_qfull, 1);
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(b_kfull + 8 * i, 1);
-      mbar_init(b_vfull + 8 * i, 1);
-      mbar_init(b_kempty + 8 * i, 1);
-      mbar_init(b_vempty + 8 * i, 1);
-      mbar_init(b_sfull + 8 * i, 1);
-      mbar_init(b_sfree + 8 * i, 256);
-    }
-    mbar_init(b_pfull, 256);
-    mbar_init(b_odone, 1);
-    mbar_init(b_odone + 8, 1);
-    mbar_fence_init();
-  }
-  if (warp == 1) {
-    tmem_alloc(smem_u32(tmem_slot), 512);
-    tmem_relinquish();
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem_base = *tmem_slot;
-  const uint32_t t_s = tmem_base, t_o = tmem_base + 256;  // S double buffered (2 x 128 columns), O accumulator
-
-  if (warp == 0) {
-    if (lane == 0) {
-      prefetch_tmap(&map_q);
-      prefetch_tmap(&map_k);
-      prefetch_tmap(&map_v);
-      mbar_expect_tx(b_qfull, Q_BYTES);
-      tma_load_2d(q_s, &map_q, head * D, row0, b_qfull);
-      tma_load_2d(q_s + BQ * 128, &map_q, head * D + 64, row0, b_qfull);
-      bool ok = true;
-      int issued = 0;
-      for (int i = 0; i < n_tiles && ok; ++i) {
-        const int s = i & 1;
-        const uint32_t k_s = kv_s + s * 2 * KV_BYTES, v_s = k_s + KV_BYTES;
-        // Always 8 pages: table entries past the sequence point at pages that hold finite data (page 0
-        // is the never-allocated zero page), and those keys are masked out; an unfilled tile half
-        // could hold NaN bit patterns, and 0 * NaN in P V would poison the row.
-        constexpr int n_pages = 8;
-        // the tile's page numbers in one batch of independent loads (one at a time, each TMA would wait a
-        // full memory latency for its coordinate)
-        int rowc[n_pages];
-#pragma unroll
-        for (int pg = 0; pg < n_pages; ++pg) {
-          const int page = ((t0 + i) * 8 + pg < p.max_blocks) ? __ldg(p.block_table + (t0 + i) * 8 + pg) : 0;
-          rowc[pg] = (page * p.n_kv + kh) * 16;
-        }
-        if (i >= 2) ok = mbar_wait(b_kempty + 8 * s, ((i >> 1) - 1) & 1, ERR_ATTN_WAIT);
-        if (!ok) break;
-        mbar_expect_tx(b_kfull + 8 * s, n_pages * 4096);
-#pragma unroll
-        for (int pg = 0; pg < n_pages; ++pg) {
-          tma_load_2d(k_s + pg * 2048, &map_k, 0, rowc[pg], b_kfull + 8 * s);
-          tma_load_2d(k_s + BK * 128 + pg * 2048, &map_k, 64, rowc[pg], b_kfull + 8 * s);
-        }
-        if (i >= 2) ok = mbar_wait(b_vempty + 8 * s, ((i >> 1) - 1) & 1, ERR_ATTN_WAIT);
-        if (!ok) {
-          mbar_wait(b_kfull + 8 * s, (i >> 1) & 1, ERR_ATTN_WAIT);  // drain the K copies just issued
-          break;
-        }
-        mbar_expect_tx(b_vfull + 8 * s, n_pages * 4096);
-#pragma unroll
-        for (int pg = 0; pg < n_pages; ++pg) {
-          tma_load_2d(v_s + pg * 2048, &map_v, 0, rowc[pg], b_vfull + 8 * s);
-          tma_load_2d(v_s + BK * 128 + pg * 2048, &map_v, 64, rowc[pg], b_vfull + 8 * s);
-        }
-        issued = i + 1;
-      }
-      if (!ok) {
-        for (int i = max(0, issued - 2); i < issued; ++i) {
-          mbar_wait(b_kfull + 8 * (i & 1), (i >> 1) & 1, ERR_ATTN_WAIT);
-          mbar_wait(b_vfull + 8 * (i & 1), (i >> 1) & 1, ERR_ATTN_WAIT);
-        }
-      }
-    }
-  } else if (warp == 1) {
-    if (lane == 0) {
-      constexpr uint32_t idesc_qk = make_idesc(1, 1, BQ, BK);
-      constexpr uint32_t idesc_pv = make_idesc(1, 1, BQ, D) | (1u << 16);  // B (V) is MN-major
-      bool ok = mbar_wait(b_qfull, 0, ERR_ATTN_WAIT);
-      // S(j) = Q K(j)^T into S buffer j & 1; issued one tile ahead of the P V product so that the tensor pipe
-      // works on the next scores while the softmax threads are busy with the current ones
-      auto issue_qk = [&](int j) -> bool {
-        const int s = j & 1;
-        if (!mbar_wait(b_kfull + 8 * s, (j >> 1) & 1, ERR_ATTN_WAIT)) return false;
-        if (j >= 2 && !mbar_wait(b_sfree + 8 * s, ((j >> 1) - 1) & 1, ERR_ATTN_WAIT)) return false;
-        tc_fence_after();
-        const uint32_t k_s = kv_s + s * 2 * KV_BYTES;
-#pragma unroll
-        for (int k = 0; k < 8; ++k) {  // 8 x 16 dims; dims 64.. live in the second 16 KB block
-          const uint32_t off = (k >> 2) * (BQ * 128) + (k & 3) * 32;
-          umma_f16(t_s + s * BK, make_desc_sw128(q_s + off), make_desc_sw128(k_s + off), idesc_qk, k != 0);
-        }
-        tc_commit(b_sfull + 8 * s);
-        tc_commit(b_kempty + 8 * s);
-        return true;
-      };
-      if (ok) ok = issue_qk(0);
-      for (int i = 0; i < n_tiles && ok; ++i) {
-        const int s = i & 1;
-        APROF_T(m0);
-        if (i + 1 < n_tiles) ok = issue_qk(i + 1);
-        if (!ok) break;
-        APROF_T(m1);
-        // O += P(i) V(i) once the softmax threads have written P (and rescaled O where the maximum moved)
-        ok = mbar_wait(b_pfull, i & 1, ERR_ATTN_WAIT);
-        APROF_T(m2);
-        if (ok) ok = mbar_wait(b_vfull + 8 * s, (i >> 1) & 1, ERR_ATTN_WAIT);
-        if (!ok) break;
-        APROF_T(m3);
-        APROF_ADD(8, m0, m1); APROF_ADD(9, m1, m2); APROF_ADD(10, m2, m3); APROF_ADD(11, m0, m0 + 1);
-        tc_fence_after();
-        const uint32_t v_s = kv_s + s * 2 * KV_BYTES + KV_BYTES;
-#pragma unroll
-        for (int k = 0; k < 8; ++k) {  // 8 x 16 keys; keys 64.. of P live in its second 16 KB block
-          const uint32_t p_off = (k >> 2) * (BQ * 128) + (k & 3) * 32;
-          umma_f16(t_o, make_desc_sw128(p_s + s * P_BYTES + p_off), make_desc_v(v_s + k * 16 * 128), idesc_pv, (i | k) != 0);
-        }
-        tc_commit(b_odone + 8 * s);
-        tc_commit(b_vempty + 8 * s);
-      }
-    }
-  } else {
-    // ---------------------------------------------------------- softmax: one thread per query row
-    // The output accumulates in tensor memory over all key tiles.  A row's reference maximum moves only when
-    // the tile's maximum exceeds it by more than kLazy (in log2 units); then the row's accumulator is rescaled
-    // in place (tcgen05.ld / st) before the next P V product is issued.  P and the running sum use the same
-    // reference, so the result is exact; P stays below 2^kLazy.
-    constexpr float kLazy = 6.f;
-    const int quarter = warp & 3;         // TMEM lane quarter this warp may touch
-    const int half = (warp - 2) >> 2;     // which 64 of the row's 128 columns: the threads of a pair share a row
-    const int r = quarter * 32 + lane;
-    const int qpos = p.pos0 + row0 + r;
-    const int qlo = p.window > 0 ? qpos - p.window + 1 : 0;   // the row's keys: qlo <= key <= qpos
-    const bool row_ok = row0 + r < p.C;
-    const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
-    const uint32_t xch = bars + 256;      // float [2][128]: the halves exchange their row maxima / sums here
-    float mref = -INFINITY, l = 0.f;
-    bool ok = true;
-    // Both passes over a tile are loops over 32-column pieces that are NOT unrolled: with few warps per
-    // scheduler there is nobody to hide instruction fetches behind, so the loop body has to stay resident.
-    // After a failed wait a thread skips its work but still meets its partner at the named barrier.
-    for (int i = 0; i < n_tiles; ++i) {
-      const int sb = i & 1;
-      APROF_T(t0_);
-      if (ok) ok = mbar_wait(b_sfull + 8 * sb, (i >> 1) & 1, ERR_ATTN_WAIT);
-      tc_fence_after();
-      APROF_T(t1_);
-      const int key0 = (t0 + i) * BK;
-      // only tiles that reach past the CTA's first row, or below the window of its last row, need the mask
-      const bool diag = key0 + BK - 1 > p.pos0 + row0 || (p.window > 0 && key0 < p.pos0 + row0 + BQ - p.window);
-      // pass 1: the maximum of this thread's 64 columns (raw scores: the scale is positive)
-      float tmax = -INFINITY;
-      if (ok) {
-#pragma unroll 1
-        for (int c = 2 * half; c < 2 * half + 2; ++c) {
-          uint32_t v[32];
-          B2_TMEM_LD_32(t_s + sb * BK + lane_addr + c * 32, v);
-          tmem_ld_wait();
-          if (diag) {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              const int kj = key0 + c * 32 + j;
-              tmax = fmaxf(tmax, (kj <= qpos && kj >= qlo) ? __uint_as_float(v[j]) : -INFINITY);
-            }
-          } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) tmax = fmaxf(tmax, __uint_as_float(v[j]));
-          }
-        }
-      }
-      APROF_T(t2_);
-      asm volatile("st.shared.f32 [%0], %1;" ::"r"(xch + (half * 128 + r) * 4), "f"(tmax) : "memory");
-      asm volatile("bar.sync 2, 256;" ::: "memory");
-      float other;
-      asm volatile("ld.shared.f32 %0, [%1];" : "=f"(other) : "r"(xch + ((half ^ 1) * 128 + r) * 4));
-      asm volatile("bar.sync 2, 256;" ::: "memory");   // the slot is free for the next tile
-      APROF_T(t3_);
-      tmax = fmaxf(tmax, other) * p.scale_log2;
-      float alpha = 1.f;
-      if (tmax > mref + kLazy || (mref == -INFINITY && tmax > -INFINITY)) {
-        alpha = exp2f(mref - tmax);  // 0 when this is the row's first finite maximum
-        mref = tmax;
-      }
-      const float nmref = (mref == -INFINITY) ? 0.f : -mref;
-      // P is double buffered: P(i - 2) V(i - 2) must be done before its buffer is overwritten (long done in
-      // steady state); only a row whose reference moved must also wait for P(i - 1) V(i - 1) before it
-      // rescales the accumulator -- so the softmax of tile i + 1 normally overlaps the P V of tile i
-      if (i >= 2 && ok) ok = mbar_wait(b_odone + 8 * sb, ((i >> 1) - 1) & 1, ERR_ATTN_WAIT);
-      if (i > 0) {
-        const bool resc = __any_sync(0xffffffffu, alpha != 1.f);
-        if (ok && resc) ok = mbar_wait(b_odone + 8 * (sb ^ 1), ((i - 1) >> 1) & 1, ERR_ATTN_WAIT);
-        tc_fence_after();
-        if (ok && resc) {
-#pragma unroll 1
-          for (int c = 2 * half; c < 2 * half + 2; ++c) {   // this thread's half of the row's accumulator
-            uint32_t v[32];
-            B2_TMEM_LD_32(t_o + lane_addr + c * 32, v);
-            tmem_ld_wait();
-#pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) * alpha);
-            B2_TMEM_ST_32(t_o + lane_addr + c * 32, v);
-          }
-          tmem_st_wait();
-        }
-      }
-      APROF_T(t4_);
-      // pass 2: P = 2^(s * scale - m) as bf16 into shared memory (swizzled, K-major over keys), row sum in fp32
-      float lsum = 0.f;
-      if (ok) {
-#pragma unroll 1
-        for (int c = 2 * half; c < 2 * half + 2; ++c) {
-          uint32_t v[32];
-          B2_TMEM_LD_32(t_s + sb * BK + lane_addr + c * 32, v);
-          tmem_ld_wait();
-          uint32_t pk[16];
-#pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            float e0, e1;
-            asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e0) : "f"(fmaf(__uint_as_float(v[2 * j]), p.scale_log2, nmref)));
-            asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e1) : "f"(fmaf(__uint_as_float(v[2 * j + 1]), p.scale_log2, nmref)));
-            if (diag) {
-              const int k0 = key0 + c * 32 + 2 * j;
-              e0 = (k0 <= qpos && k0 >= qlo) ? e0 : 0.f;
-              e1 = (k0 + 1 <= qpos && k0 + 1 >= qlo) ? e1 : 0.f;
-            }
-            lsum += e0 + e1;
-            pk[j] = pack_bf16(e0, e1);
-          }
-          const uint32_t rowb = p_s + sb * P_BYTES + (c >> 1) * (BQ * 128) + r * 128;
-#pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            const int chunk = ((c & 1) * 4 + q) ^ (r & 7);
-            asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(rowb + chunk * 16), "r"(pk[4 * q]),
-                         "r"(pk[4 * q + 1]), "r"(pk[4 * q + 2]), "r"(pk[4 * q + 3])
-                         : "memory");
-          }
-        }
-      }
-      l = l * alpha + lsum;   // this half's share of the row sum; the halves are added at the end
-      APROF_T(t5_);
-      if (ok) {
-        tc_fence_before();
-        mbar_arrive(b_sfree + 8 * sb);  // both passes over the scores are done: the buffer may take tile i + 2
-        fence_proxy_async_smem();       // P was written with generic stores, the MMA reads it through the async proxy
-        mbar_arrive(b_pfull);
-      }
-#ifdef B2_ATTN_PROF
-      if (warp == 2 && lane == 0) {
-        APROF_T(t6_);
-        APROF_ADD(0, t0_, t1_); APROF_ADD(1, t1_, t2_); APROF_ADD(2, t2_, t3_); APROF_ADD(3, t3_, t4_);
-        APROF_ADD(4, t4_, t5_); APROF_ADD(5, t5_, t6_); APROF_ADD(6, t0_, t0_ + 1);
-      }
-#endif
-    }
-    // the row sum: both halves
-    asm volatile("st.shared.f32 [%0], %1;" ::"r"(xch + (half * 128 + r) * 4), "f"(l) : "memory");
-    asm volatile("bar.sync 2, 256;" ::: "memory");
-    float lo;
-    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(lo) : "r"(xch + ((half ^ 1) * 128 + r) * 4));
-    l += lo;
-    // the last product (and, accumulating in issue order, every product before it)
-    if (ok) ok = mbar_wait(b_odone + 8 * ((n_tiles - 1) & 1), ((n_tiles - 1) >> 1) & 1, ERR_ATTN_WAIT);
-    if (ok) {
-      tc_fence_after();
-      const float inv = l > 0.f ? 1.f / l : 0.f;
-      __nv_bfloat16* dst = p.out + (size_t)(row0 + r) * (p.n_q * D) + head * D;
-#pragma unroll 1
-      for (int c = 2 * half; c < 2 * half + 2; ++c) {
-        uint32_t v[32];
-        B2_TMEM_LD_32(t_o + lane_addr + c * 32, v);
-        tmem_ld_wait();
-        if (row_ok) {
-#pragma unroll
-          for (int j = 0; j < 4; ++j)
-            *reinterpret_cast<uint4*>(dst + c * 32 + 8 * j) = make_uint4(
-                pack_bf16(__uint_as_float(v[8 * j]) * inv, __uint_as_float(v[8 * j + 1]) * inv),
-                pack_bf16(__uint_as_float(v[8 * j + 2]) * inv, __uint_as_float(v[8 * j + 3]) * inv),
-                pack_bf16(__uint_as_float(v[8 * j + 4]) * inv, __uint_as_float(v[8 * j + 5]) * inv),
-                pack_bf16(__uint_as_float(v[8 * j + 6]) * inv, __uint_as_float(v[8 * j + 7]) * inv));
-        }
-      }
-      tc_fence_before();
-    }
-  }
-  tc_fence_before();
-  __syncthreads();
-  if (warp == 1) {
-    tc_fence_after();
-    tmem_dealloc(tmem_base, 512);
-  }
-}
-
 // ---------------------------------------------------------------------------------------------------------------
-// Pair form: one CTA owns TWO query tiles of one head (rows row0 .. row0 + 255) and walks the keys in tiles of 64.
+// One CTA owns TWO query tiles of one head (rows row0 .. row0 + 255) and walks the keys in tiles of 64.
 // The two tiles share every K / V tile that comes in (half the L2 traffic per score), and each has its own softmax
-// warpgroup -- one thread per query row, the row's 64 scores read from tensor memory ONCE into registers -- so while
-// one group works on its scores the tensor pipe runs the other tile's products:
+// threads -- two per query row, a row's scores read from tensor memory ONCE into registers -- so while one group works
+// on its scores the tensor pipe runs the other tile's products:
 //     S0(i+1) = Q0 K(i+1)^T   after  O0 += P0(i) V(i),      S1(i+1) = Q1 K(i+1)^T   after  O1 += P1(i) V(i)
 // Score buffers are double buffered per tile and handed back as soon as they are in registers, so the tensor pipe
 // never waits for a softmax to END before it starts the next scores.  Tensor memory: 4 x 64 score columns + 2 x 128
@@ -406,7 +65,9 @@ constexpr int KV2_BYTES = BK2 * D * 2;            // 16 KB per K or V tile: [2 d
 constexpr int P2_BYTES = BQ * BK2 * 2;            // 16 KB: [128 rows][64 keys]
 constexpr int SMEM2 = Q2_BYTES + 4 * KV2_BYTES + 4 * P2_BYTES + 1024 + 256 + 2 * 2 * 2 * 128 * 4;   // + barriers + exchange slots
 
-__device__ __forceinline__ uint64_t make_desc_v2(uint32_t smem_addr) {     // as make_desc_v for 64-key tiles
+// smem descriptor for the MN-major V operand: rows are keys (128 B = 64 dims, 128-byte swizzle), 8-key groups are
+// 1024 B apart (stride byte offset); the next block of 64 dims is a whole tile half away (leading byte offset).
+__device__ __forceinline__ uint64_t make_desc_v2(uint32_t smem_addr) {
   uint64_t d = 0;
   d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);
   d |= (uint64_t)((BK2 * 128) >> 4) << 16;
@@ -832,17 +493,10 @@ extern "C" int b2_attn_prefill(const void* q, const void* k_cache, const void* v
   rc = make_map_bf16(&mv, v_cache, (uint64_t)num_pages * n_kv * 16, D, 16);
   if (rc) return rc;
   static bool configured[64] = {};
-  static int form = -1;     // B2_ATTN_PAIR=0: one query tile per CTA (the earlier form, kept for comparison)
-  if (form < 0) {
-    const char* e = getenv("B2_ATTN_PAIR");
-    form = (e && e[0] == '0') ? 0 : 1;
-  }
   int dev = 0;
   cudaGetDevice(&dev);
   if (!configured[dev & 63]) {
-    cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
-    if (e == cudaSuccess)
-      e = cudaFuncSetAttribute(attn_prefill_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM2);
+    cudaError_t e = cudaFuncSetAttribute(attn_prefill_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM2);
     if (e != cudaSuccess) return (int)e;
     configured[dev & 63] = true;
   }
@@ -850,13 +504,8 @@ extern "C" int b2_attn_prefill(const void* q, const void* k_cache, const void* v
   p.block_table = block_table; p.n_q = n_q; p.n_kv = n_kv; p.C = C; p.pos0 = pos0; p.max_blocks = max_blocks;
   p.scale_log2 = scale * 1.4426950408889634f; p.out = (__nv_bfloat16*)out;
   p.window = window > 0 ? window : 0;
-  if (form == 1) {
-    dim3 grid((C + 2 * BQ - 1) / (2 * BQ), n_q);
-    attn_prefill_pair_kernel<<<grid, kThreads2, SMEM2, (cudaStream_t)stream>>>(mq, mk, mv, p);
-    return (int)cudaGetLastError();
-  }
-  dim3 grid((C + BQ - 1) / BQ, n_q);
-  attn_prefill_kernel<<<grid, kThreads, SMEM, (cudaStream_t)stream>>>(mq, mk, mv, p);
+  dim3 grid((C + 2 * BQ - 1) / (2 * BQ), n_q);
+  attn_prefill_pair_kernel<<<grid, kThreads2, SMEM2, (cudaStream_t)stream>>>(mq, mk, mv, p);
   return (int)cudaGetLastError();
 }
 
