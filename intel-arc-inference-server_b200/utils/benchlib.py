@@ -126,7 +126,7 @@ def run_spec_bench(args, barrier, iters: int = 12, depth: int = 0, cases=None) -
     out = {"depth": depth}
     g = torch.Generator().manual_seed(0)
     ids = torch.randint(0, cfg.vocab - 1, (depth,), generator=g).tolist()
-    for kind, k, accepts, dv in (cases or (("mtp", 3, (0, 3), 0), ("mtp", 3, (3,), 32768), ("dflash", 15, (0, 3, 7), 0))):
+    for kind, k, accepts, dv in (cases or (("mtp", 3, (0, 3), 0), ("mtp", 3, (3,), 32768), ("dflash", 7, (7,), 0), ("dflash", 15, (0, 3, 7), 0))):
         eng = Engine(weights, max_seqs=1, max_len=depth + 64 * (iters + 4) + 64, extra_kv_layers=2)
         ad = SpecAdapter(EngineAdapter(eng), kind, k, draft_vocab=dv)
         pending = ad.prefill(0, ids)
