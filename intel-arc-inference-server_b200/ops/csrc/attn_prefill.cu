@@ -62,8 +62,8 @@ constexpr int kThreads2 = 608;    // TMA warp, MMA warp of tile 0, 2 tiles x 2 c
 constexpr int kMmaWarp1 = 18;
 constexpr int Q2_BYTES = 2 * BQ * D * 2;          // two query tiles, each [2 d-blocks][128 rows][64]
 constexpr int KV2_BYTES = BK2 * D * 2;            // 16 KB per K or V tile: [2 d-blocks][64 keys][64]
-constexpr int P2_BYTES = BQ * BK2 * 2;            // 16 KB: [128 rows][64 keys]
-constexpr int SMEM2 = Q2_BYTES + 4 * KV2_BYTES + 4 * P2_BYTES + 1024 + 256 + 2 * 2 * 2 * 128 * 4;   // + barriers + exchange slots
+constexpr int KVS = 4;                            // K / V ring depth (tiles in flight)
+constexpr int SMEM2 = Q2_BYTES + 2 * KVS * KV2_BYTES + 1024 + 256 + 2 * 2 * 2 * 128 * 4;   // + alignment, barriers, exchange slots
 
 // smem descriptor for the MN-major V operand: rows are keys (128 B = 64 dims, 128-byte swizzle), 8-key groups are
 // 1024 B apart (stride byte offset); the next block of 64 dims is a whole tile half away (leading byte offset).
@@ -82,16 +82,16 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                          const __grid_constant__ CUtensorMap map_v, const AttnPfParams p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  const uint32_t q_s = base, k_s0 = base + Q2_BYTES, v_s0 = k_s0 + 2 * KV2_BYTES, p_s0 = v_s0 + 2 * KV2_BYTES,
-                 bars = p_s0 + 4 * P2_BYTES;
-  // barriers (8 bytes each): q_full; k_full[2], k_empty[2], v_full[2], v_empty[2]; per tile w: s_full[w][2],
-  // s_free[w][2], p_full[w], o_done[w][2]
-  const uint32_t b_qfull = bars, b_kfull = bars + 8, b_kempty = bars + 24, b_vfull = bars + 40, b_vempty = bars + 56;
-  auto b_sfull = [&](int w, int b) { return bars + 72 + (w * 2 + b) * 8; };
-  auto b_sfree = [&](int w, int b) { return bars + 104 + (w * 2 + b) * 8; };
-  auto b_pfull = [&](int w) { return bars + 136 + w * 8; };
-  auto b_odone = [&](int w, int b) { return bars + 152 + (w * 2 + b) * 8; };
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_raw + (bars + 192 - smem_u32(smem_raw)));
+  const uint32_t q_s = base, k_s0 = base + Q2_BYTES, v_s0 = k_s0 + KVS * KV2_BYTES, bars = v_s0 + KVS * KV2_BYTES;
+  // barriers (8 bytes each): q_full; k_full, k_empty, v_full, v_empty [KVS each]; per tile w: s_full[w][2],
+  // p_full[w], o_done[w][2]
+  const uint32_t b_qfull = bars, b_kfull = bars + 8, b_kempty = b_kfull + 8 * KVS, b_vfull = b_kempty + 8 * KVS,
+                 b_vempty = b_vfull + 8 * KVS;
+  auto b_sfull = [&](int w, int b) { return bars + 136 + (w * 2 + b) * 8; };
+  auto b_pfull = [&](int w) { return bars + 168 + w * 8; };
+  auto b_odone = [&](int w, int b) { return bars + 184 + (w * 2 + b) * 8; };
+  static_assert(8 + 4 * 8 * KVS <= 136, "the ring's barriers end where the tiles' begin");
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_raw + (bars + 224 - smem_u32(smem_raw)));
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int qt = gridDim.x - 1 - blockIdx.x;   // heavy (late) pairs first
@@ -106,7 +106,7 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
 
   if (threadIdx.x == 0) {
     mbar_init(b_qfull, 1);
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < KVS; ++i) {
       mbar_init(b_kfull + 8 * i, 1);
       mbar_init(b_kempty + 8 * i, 2);     // one arrival per issuing thread
       mbar_init(b_vfull + 8 * i, 1);
@@ -115,7 +115,6 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     for (int w = 0; w < 2; ++w) {
       for (int b = 0; b < 2; ++b) {
         mbar_init(b_sfull(w, b), 1);
-        mbar_init(b_sfree(w, b), 256);
         mbar_init(b_odone(w, b), 1);
       }
       mbar_init(b_pfull(w), 256);
@@ -147,7 +146,7 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
       bool ok = true;
       int issued = 0;
       for (int i = 0; i < n_all && ok; ++i) {
-        const int s = i & 1;
+        const int s = i % KVS, ph = (i / KVS) & 1;
         const uint32_t k_s = k_s0 + s * KV2_BYTES, v_s = v_s0 + s * KV2_BYTES;
         // Always 4 pages: table entries past the sequence point at pages that hold finite data (page 0 is the
         // never-allocated zero page) and those keys are masked out; an unfilled part of a tile could hold NaN bit
@@ -160,7 +159,7 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
           const int page = pi < p.max_blocks ? __ldg(p.block_table + pi) : 0;
           rowc[pg] = (page * p.n_kv + kh) * 16;
         }
-        if (i >= 2) ok = mbar_wait(b_kempty + 8 * s, ((i >> 1) - 1) & 1, ERR_ATTN_WAIT);
+        if (i >= KVS) ok = mbar_wait(b_kempty + 8 * s, ph ^ 1, ERR_ATTN_WAIT);
         if (!ok) break;
         mbar_expect_tx(b_kfull + 8 * s, KV2_BYTES);
 #pragma unroll
@@ -168,9 +167,9 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
           tma_load_2d(k_s + pg * 2048, &map_k, 0, rowc[pg], b_kfull + 8 * s);
           tma_load_2d(k_s + BK2 * 128 + pg * 2048, &map_k, 64, rowc[pg], b_kfull + 8 * s);
         }
-        if (i >= 2) ok = mbar_wait(b_vempty + 8 * s, ((i >> 1) - 1) & 1, ERR_ATTN_WAIT);
+        if (i >= KVS) ok = mbar_wait(b_vempty + 8 * s, ph ^ 1, ERR_ATTN_WAIT);
         if (!ok) {
-          mbar_wait(b_kfull + 8 * s, (i >> 1) & 1, ERR_ATTN_WAIT);  // drain the K copies just issued
+          mbar_wait(b_kfull + 8 * s, ph, ERR_ATTN_WAIT);  // drain the K copies just issued
           break;
         }
         mbar_expect_tx(b_vfull + 8 * s, KV2_BYTES);
@@ -182,9 +181,9 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         issued = i + 1;
       }
       if (!ok) {
-        for (int i = max(0, issued - 2); i < issued; ++i) {
-          mbar_wait(b_kfull + 8 * (i & 1), (i >> 1) & 1, ERR_ATTN_WAIT);
-          mbar_wait(b_vfull + 8 * (i & 1), (i >> 1) & 1, ERR_ATTN_WAIT);
+        for (int i = max(0, issued - KVS); i < issued; ++i) {
+          mbar_wait(b_kfull + 8 * (i % KVS), (i / KVS) & 1, ERR_ATTN_WAIT);
+          mbar_wait(b_vfull + 8 * (i % KVS), (i / KVS) & 1, ERR_ATTN_WAIT);
         }
       }
     }
@@ -202,34 +201,32 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
       // low word is (address >> 4) plus the leading-offset field, so an operand piece is one integer add away.
       const uint32_t hi_k = (uint32_t)(make_desc_sw128(0) >> 32), hi_v = (uint32_t)(make_desc_v2(0) >> 32);
       const uint32_t ql = (uint32_t)make_desc_sw128(q_s + w * (BQ * D * 2));
-      const uint32_t k_lo0 = (uint32_t)make_desc_sw128(k_s0), k_lo1 = (uint32_t)make_desc_sw128(k_s0 + KV2_BYTES);
-      const uint32_t v_lo0 = (uint32_t)make_desc_v2(v_s0), v_lo1 = (uint32_t)make_desc_v2(v_s0 + KV2_BYTES);
-      const uint32_t p_lo0 = (uint32_t)make_desc_sw128(p_s0 + (w * 2) * P2_BYTES),
-                     p_lo1 = (uint32_t)make_desc_sw128(p_s0 + (w * 2 + 1) * P2_BYTES);
+      const uint32_t k_lo0 = (uint32_t)make_desc_sw128(k_s0), v_lo0 = (uint32_t)make_desc_v2(v_s0);   // ring stage 0; a stage is KV2_BYTES >> 4 further
       const uint32_t to = t_o(w);
       auto issue_qk = [&](int j) -> bool {
-        const int s = j & 1;
-        if (!mbar_wait(b_kfull + 8 * s, (j >> 1) & 1, ERR_ATTN_WAIT)) return false;
-        if (j >= 2 && !mbar_wait(b_sfree(w, s), ((j >> 1) - 1) & 1, ERR_ATTN_WAIT)) return false;
+        const int s = j & 1, ks = j % KVS;
+        if (!mbar_wait(b_kfull + 8 * ks, (j / KVS) & 1, ERR_ATTN_WAIT)) return false;
+        // the buffer's first 32 columns hold P(j - 2) until that tile's P V product has read them
+        if (j >= 2 && !mbar_wait(b_odone(w, s), ((j >> 1) - 1) & 1, ERR_ATTN_WAIT)) return false;
         tc_fence_after();
-        const uint32_t kl = s ? k_lo1 : k_lo0, ts = t_s(w, s);
+        const uint32_t kl = k_lo0 + ks * (KV2_BYTES >> 4), ts = t_s(w, s);
 #pragma unroll
         for (int k = 0; k < 8; ++k)   // 8 x 16 dims; dims 64.. live in the operands' second block
           umma_f16_w(ts, ql + (((k >> 2) * (BQ * 128) + (k & 3) * 32) >> 4), hi_k,
                      kl + (((k >> 2) * (BK2 * 128) + (k & 3) * 32) >> 4), hi_k, idesc_qk, k != 0);
         tc_commit(b_sfull(w, s));
-        tc_commit(b_kempty + 8 * s);
+        tc_commit(b_kempty + 8 * ks);
         return true;
       };
       if (ok && nt > 0) ok = issue_qk(0);
       for (int i = 0; i < n_all && ok; ++i) {
-        const int s = i & 1;
+        const int s = i & 1, ks = i % KVS, kph = (i / KVS) & 1;
         if (i >= nt) {
           // the other tile still has key tiles: hand this thread's share of their buffers back as they arrive
-          ok = mbar_wait(b_kfull + 8 * s, (i >> 1) & 1, ERR_ATTN_WAIT);
-          if (ok) mbar_arrive(b_kempty + 8 * s);
-          if (ok) ok = mbar_wait(b_vfull + 8 * s, (i >> 1) & 1, ERR_ATTN_WAIT);
-          if (ok) mbar_arrive(b_vempty + 8 * s);
+          ok = mbar_wait(b_kfull + 8 * ks, kph, ERR_ATTN_WAIT);
+          if (ok) mbar_arrive(b_kempty + 8 * ks);
+          if (ok) ok = mbar_wait(b_vfull + 8 * ks, kph, ERR_ATTN_WAIT);
+          if (ok) mbar_arrive(b_vempty + 8 * ks);
           continue;
         }
         // the tile's NEXT scores first (their buffer was handed back when the tile's threads had tile i - 1 in
@@ -241,17 +238,17 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         // O_w += P_w(i) V(i) once the tile's softmax threads have written P (and rescaled O where a maximum moved)
         ok = mbar_wait(b_pfull(w), i & 1, ERR_ATTN_WAIT);
         APROF_T(m2);
-        if (ok) ok = mbar_wait(b_vfull + 8 * s, (i >> 1) & 1, ERR_ATTN_WAIT);
+        if (ok) ok = mbar_wait(b_vfull + 8 * ks, kph, ERR_ATTN_WAIT);
         if (!ok) break;
         APROF_T(m3);
         APROF_ADD(8, m0, m1); APROF_ADD(9, m1, m2); APROF_ADD(10, m2, m3); APROF_ADD(11, m0, m0 + 1);
         tc_fence_after();
-        const uint32_t vl = s ? v_lo1 : v_lo0, pl = s ? p_lo1 : p_lo0;
+        const uint32_t vl = v_lo0 + ks * (KV2_BYTES >> 4), tp = t_s(w, s);
 #pragma unroll
-        for (int k = 0; k < 4; ++k)   // 4 x 16 keys
-          umma_f16_w(to, pl + ((k * 32) >> 4), hi_k, vl + ((k * 16 * 128) >> 4), hi_v, idesc_pv, (i | k) != 0);
+        for (int k = 0; k < 4; ++k)   // 4 x 16 keys: P comes from tensor memory, 8 columns (16 bf16) per step
+          umma_f16_ts_w(to, tp + 8 * k, vl + ((k * 16 * 128) >> 4), hi_v, idesc_pv, (i | k) != 0);
         tc_commit(b_odone(w, s));
-        tc_commit(b_vempty + 8 * s);
+        tc_commit(b_vempty + 8 * ks);
       }
     }
   } else {
@@ -287,8 +284,6 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
       if (ok) {
         B2_TMEM_LD_32(t_s(w, sb) + lane_addr + half * 32, v);
         tmem_ld_wait();
-        tc_fence_before();
-        mbar_arrive(b_sfree(w, sb));
       } else {
 #pragma unroll
         for (int j = 0; j < 32; ++j) v[j] = 0xff800000u;
@@ -326,7 +321,6 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
       const float nmref = (mref == -INFINITY) ? 0.f : -mref;
       // P is double buffered: P(i - 2) V(i - 2) must be done before its buffer is overwritten (long done in steady
       // state); only a row whose reference moved must also wait for P(i - 1) V(i - 1) before it rescales the accumulator
-      if (i >= 2 && ok) ok = mbar_wait(b_odone(w, sb), ((i >> 1) - 1) & 1, ERR_ATTN_WAIT);
       if (i > 0) {
         const bool resc = __any_sync(0xffffffffu, alpha != 1.f);
         if (ok && resc) ok = mbar_wait(b_odone(w, sb ^ 1), ((i - 1) >> 1) & 1, ERR_ATTN_WAIT);
@@ -369,14 +363,16 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         pk[j] = pack_bf16(e0, e1);
       }
       if (ok) {
-        const uint32_t rowb = p_s0 + (w * 2 + sb) * P2_BYTES + r * 128;
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          const int chunk = (half * 4 + q) ^ (r & 7);
-          asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(rowb + chunk * 16), "r"(pk[4 * q]),
-                       "r"(pk[4 * q + 1]), "r"(pk[4 * q + 2]), "r"(pk[4 * q + 3])
-                       : "memory");
-        }
+        // P goes back into tensor memory, over the first 32 columns of the score buffer it came from (both halves
+        // of the row have their scores in registers: they met at the barrier above): 16 packed columns per thread,
+        // the A operand of P V without a trip through shared memory
+        asm volatile(
+            "tcgen05.st.sync.aligned.32x32b.x16.b32 [%16], {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15};" ::"r"(pk[0]),
+            "r"(pk[1]), "r"(pk[2]), "r"(pk[3]), "r"(pk[4]), "r"(pk[5]), "r"(pk[6]), "r"(pk[7]), "r"(pk[8]), "r"(pk[9]),
+            "r"(pk[10]), "r"(pk[11]), "r"(pk[12]), "r"(pk[13]), "r"(pk[14]), "r"(pk[15]),
+            "r"(t_s(w, sb) + lane_addr + half * 16)
+            : "memory");
+        tmem_st_wait();
       }
       {
         float a0, a1, a2, a3;
@@ -386,7 +382,7 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
       }
       APROF_T(t5_);
       if (ok) {
-        fence_proxy_async_smem();       // P was written with generic stores, the MMA reads it through the async proxy
+        tc_fence_before();
         mbar_arrive(b_pfull(w));
       }
 #ifdef B2_ATTN_PROF
