@@ -41,13 +41,14 @@ class _RowScratch:
         e, k, h, i = cfg.n_experts, cfg.top_k, cfg.hidden, cfg.expert_ffn
         self.ld = (e + (1 if cfg.shared_ffn else 0) + 7) // 8 * 8
         self.logits = torch.zeros(mr, self.ld, dtype=torch.float32, device=dev)
-        self.topk_idx = torch.zeros(mr * k, dtype=torch.int32, device=dev)
-        self.topk_w = torch.zeros(mr * k, dtype=torch.float32, device=dev)
+        self.topk_idx = torch.zeros(mr * (k + 1), dtype=torch.int32, device=dev)      # + the shared expert's slot
+        self.topk_w = torch.zeros(mr * (k + 1), dtype=torch.float32, device=dev)
         self.s_gu = K.gemv_splits(2 * i, h)
         self.s_dn = K.gemv_splits(h, i)
-        self.part_gu = torch.zeros(mr * k * self.s_gu * 2 * i, dtype=torch.float32, device=dev)
-        self.part_dn = torch.zeros(mr * k * self.s_dn * h, dtype=torch.float32, device=dev)
+        self.part_gu = torch.zeros(mr * (k + 1) * self.s_gu * 2 * i, dtype=torch.float32, device=dev)
+        self.part_dn = torch.zeros(mr * (k + 1) * self.s_dn * h, dtype=torch.float32, device=dev)
         self.out = torch.zeros(mr * h, dtype=torch.float32, device=dev)
+        self.ticket = torch.zeros(1, dtype=torch.int32, device=dev)
 
 
 def moe_block_rows(model, lw: LayerWeights, m: int):
@@ -58,10 +59,25 @@ def moe_block_rows(model, lw: LayerWeights, m: int):
         sc = model._moe_rows = _RowScratch(model)
     e, k, h, i = cfg.n_experts, cfg.top_k, cfg.hidden, cfg.expert_ffn
     rc = router_cat(lw, cfg)
-    K.head_gemv(rc, b.x, sc.logits, m, rc.shape[0], h)
-    M.route(sc.logits, sc.ld, m, e, k, sc.topk_idx, sc.topk_w)
     gu_bytes = lw.experts_gate_up_w4b[0].numel()
     dn_bytes = lw.experts_down_w4b[0].numel()
+    if lw.shared is None or (cfg.shared_ffn == i and lw.shared.gate_up.w4b.numel() == gu_bytes):
+        # Four launches: router logits + routing (one kernel, the shared expert becomes slot k of every row with
+        # weight sigmoid(gate)), the two batched int4 GEMVs over k (+ 1) slots per row -- the shared expert's weights
+        # ride along as an alternative tensor for its slot id -- and the weighted sum.
+        ks = k + (1 if lw.shared is not None else 0)
+        M.router_rows(rc, b.x, sc.logits, m, e + (1 if lw.shared_gate is not None else 0), h, sc.ld, e, k,
+                      lw.shared is not None, lw.shared_gate is not None, sc.topk_idx, sc.topk_w, sc.ticket)
+        alt_gu = lw.shared.gate_up.w4b if lw.shared is not None else None
+        alt_dn = lw.shared.down.w4b if lw.shared is not None else None
+        M.gemv_experts(lw.experts_gate_up_w4b, gu_bytes, sc.topk_idx, m * ks, b.x, ks, h * 2, sc.part_gu, 2 * i, h, sc.s_gu, h,
+                       alt_w=alt_gu, alt_id=e)
+        M.gemv_experts(lw.experts_down_w4b, dn_bytes, sc.topk_idx, m * ks, sc.part_gu, 1, sc.s_gu * 2 * i * 4, sc.part_dn,
+                       h, i, sc.s_dn, 2 * i, x_mode=1, s_in=sc.s_gu, x_slice=2 * i, alt_w=alt_dn, alt_id=e)
+        M.combine_rows(sc.part_dn, sc.s_dn, m, ks, h, sc.topk_w, None, 0, None, sc.ld, sc.out)
+        return sc.out, 1
+    K.head_gemv(rc, b.x, sc.logits, m, rc.shape[0], h)
+    M.route(sc.logits, sc.ld, m, e, k, sc.topk_idx, sc.topk_w)
     M.gemv_experts(lw.experts_gate_up_w4b, gu_bytes, sc.topk_idx, m * k, b.x, k, h * 2, sc.part_gu, 2 * i, h, sc.s_gu, h)
     M.gemv_experts(lw.experts_down_w4b, dn_bytes, sc.topk_idx, m * k, sc.part_gu, 1, sc.s_gu * 2 * i * 4, sc.part_dn,
                    h, i, sc.s_dn, 2 * i, x_mode=1, s_in=sc.s_gu, x_slice=2 * i)

@@ -60,6 +60,8 @@ struct GemvParams {
   const int* expert_ids;     // [batches] or nullptr
   int skip_negative;         // batched form: a batch whose expert id is negative does nothing (its CTAs leave at once)
   long long expert_bytes;    // bytes between experts' W4B tensors
+  const uint8_t* alt_w;      // batched form: a batch whose expert id is alt_id reads these weights instead of the stack's
+  int alt_id;                //   (the shared expert as one more slot of a row: same shapes, its own tensor)
   int x_div;                 // batch b reads activations of batch b / x_div
   long long x_batch_bytes;   // bytes between activation batches
   long long out_batch;       // floats between output batches
@@ -318,7 +320,11 @@ __global__ void __launch_bounds__(kThreads, (T <= 2 ? 2 : 1)) gemv_w4_kernel(con
       // the expert ids come from the routing kernel before this one: in the batched form the producer
       // has to wait for it too (the dense form streams weights that depend on nothing)
       if (p.expert_ids) pdl_wait();
-      const uint8_t* wbase = p.expert_ids ? p.w + (size_t)p.expert_ids[blockIdx.z] * p.expert_bytes : p.w;
+      const uint8_t* wbase = p.w;
+      if (p.expert_ids) {
+        const int eid = p.expert_ids[blockIdx.z];
+        wbase = (p.alt_w && eid == p.alt_id) ? p.alt_w : p.w + (size_t)eid * p.expert_bytes;
+      }
       const uint8_t* src = wbase + ((size_t)nblk * p.KG + gbeg) * kBlockBytes;
       bool ok = true;
       int issued = 0;
@@ -852,9 +858,12 @@ extern "C" int b2_gemv_w4_qkv_rope(const void* w4b, const void* x, float* out, i
 // equally shaped W4B tensors, reads the activations of batch b / x_div and writes out[b][S][N].
 static int gemv_w4_experts_impl(const void* w4b_stack, long long expert_bytes, const int* expert_ids, int batches,
                                 const void* x, int x_div, long long x_batch_bytes, float* out, int N, int K, int S,
-                                int ldx, int x_mode, int s_in, long long x_slice, int skip_negative, void* stream) {
+                                int ldx, int x_mode, int s_in, long long x_slice, int skip_negative, void* stream,
+                                const void* alt_w = nullptr, int alt_id = -1) {
   if (batches < 1 || batches > 65535 || K % 64 != 0 || S < 1 || x_div < 1) return -1;
   GemvParams p;
+  p.alt_w = reinterpret_cast<const uint8_t*>(alt_w);
+  p.alt_id = alt_id;
   p.w = reinterpret_cast<const uint8_t*>(w4b_stack);
   p.x = x;
   p.out = out;
@@ -882,6 +891,16 @@ extern "C" int b2_gemv_w4_experts_sparse(const void* w4b_stack, long long expert
                                          int ldx, int x_mode, int s_in, long long x_slice, void* stream) {
   return gemv_w4_experts_impl(w4b_stack, expert_bytes, expert_ids, batches, x, x_div, x_batch_bytes, out, N, K, S, ldx, x_mode,
                               s_in, x_slice, 1, stream);
+}
+
+// The same with one more weight tensor outside the stack: batches whose id is alt_id read alt_w (the shared expert
+// as slot k of every row).
+extern "C" int b2_gemv_w4_experts_alt(const void* w4b_stack, long long expert_bytes, const int* expert_ids, int batches,
+                                      const void* x, int x_div, long long x_batch_bytes, float* out, int N, int K, int S,
+                                      int ldx, int x_mode, int s_in, long long x_slice, const void* alt_w, int alt_id,
+                                      void* stream) {
+  return gemv_w4_experts_impl(w4b_stack, expert_bytes, expert_ids, batches, x, x_div, x_batch_bytes, out, N, K, S, ldx, x_mode,
+                              s_in, x_slice, 0, stream, alt_w, alt_id);
 }
 
 // Quantise activation rows for x_mode 3.  Input modes as the GEMV's (0 bf16 rows, 1 SiLU*up of fp32 slices,

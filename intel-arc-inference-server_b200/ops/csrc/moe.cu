@@ -20,29 +20,23 @@ namespace {
 
 // ---------------------------------------------------------------- route: one warp per token
 // logits fp32 [T][ld], the first E columns are the experts (E <= 512).  topk_idx int32 [T][k], topk_w fp32 [T][k].
-__global__ void __launch_bounds__(256) moe_route_kernel(const float* __restrict__ logits, int ld, int T, int E, int k,
-                                                        int* __restrict__ topk_idx, float* __restrict__ topk_w) {
-  pdl_wait();
-  pdl_launch_dependents();
-  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
-  if (warp >= T) return;
+// One row's routing by a whole warp: softmax over E logits, top-k by repeated arg-max (ties to the lower id), weights
+// renormalised over the chosen k.  `stride` >= k entries per row in topk_idx / topk_w.
+__device__ __forceinline__ void route_row(const float* __restrict__ lrow, int E, int k, int* __restrict__ idx_out,
+                                          float* __restrict__ w_out, int lane) {
   constexpr int PER = 16;  // experts per lane (E <= 512)
   float v[PER];
   float mx = -INFINITY;
 #pragma unroll
   for (int i = 0; i < PER; ++i) {
     const int e = lane + 32 * i;
-    v[i] = e < E ? logits[(size_t)warp * ld + e] : -INFINITY;
+    v[i] = e < E ? __ldcg(lrow + e) : -INFINITY;
     mx = fmaxf(mx, v[i]);
   }
   mx = warp_max(mx);
-  float z = 0.f;
 #pragma unroll
-  for (int i = 0; i < PER; ++i) {
+  for (int i = 0; i < PER; ++i)
     v[i] = (lane + 32 * i) < E ? __expf(v[i] - mx) : -1.f;  // probabilities (unnormalised); -1 marks "taken / absent"
-    if (v[i] > 0.f) z += v[i];
-  }
-  z = warp_sum(z);
   float wsum = 0.f;
   float myw = 0.f;
   int myid = 0;
@@ -66,10 +60,90 @@ __global__ void __launch_bounds__(256) moe_route_kernel(const float* __restrict_
     if (lane == r) { myw = bv; myid = bi; }
   }
   if (lane < k) {
-    topk_idx[(size_t)warp * k + lane] = myid;
-    topk_w[(size_t)warp * k + lane] = myw / wsum;  // softmax normaliser cancels: p_i / sum p_topk
+    idx_out[lane] = myid;
+    w_out[lane] = myw / wsum;  // softmax normaliser cancels: p_i / sum p_topk
   }
-  (void)z;
+}
+
+__global__ void __launch_bounds__(256) moe_route_kernel(const float* __restrict__ logits, int ld, int T, int E, int k,
+                                                        int* __restrict__ topk_idx, float* __restrict__ topk_w) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  if (warp >= T) return;
+  route_row(logits + (size_t)warp * ld, E, k, topk_idx + (size_t)warp * k, topk_w + (size_t)warp * k, lane);
+}
+
+// ---------------------------------------------------------------- decode rows: router logits + routing in one launch
+// logits[m][r] = x[m] . W[r] for the R router rows (E experts, then the shared expert's gate row when there is one):
+// a warp per router row, eight token rows per pass over the weights.  The CTA that finishes last (a ticket) then
+// routes every token row.  With `shared_slot` each row gets one more slot: expert id E (the shared expert, see the
+// batched GEMV's alt weights) with weight sigmoid(gate logit), or 1 without a gate row.
+struct RouterRowsParams {
+  const __nv_bfloat16* w;   // [R][H]
+  const __nv_bfloat16* x;   // [M][H]
+  float* logits;            // [M][ld]
+  int M, R, H, ld, E, k;
+  int shared_slot, has_gate;
+  int* topk_idx;            // [M][k + shared_slot]
+  float* topk_w;
+  int* ticket;              // one zeroed word; left zero
+};
+
+__global__ void __launch_bounds__(256) moe_router_rows_kernel(const RouterRowsParams p) {
+  __shared__ int s_last;
+  pdl_wait();
+  pdl_launch_dependents();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int r = blockIdx.x * 8 + warp;
+  if (r < p.R) {
+    const uint4* wr = reinterpret_cast<const uint4*>(p.w + (size_t)r * p.H);
+    for (int m0 = 0; m0 < p.M; m0 += 8) {
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      for (int c = lane; c < p.H / 8; c += 32) {
+        const uint4 wv = __ldg(wr + c);
+        const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
+#pragma unroll
+        for (int mm = 0; mm < 8; ++mm) {
+          if (m0 + mm < p.M) {
+            const uint4 xv = __ldg(reinterpret_cast<const uint4*>(p.x + (size_t)(m0 + mm) * p.H) + c);
+            const uint32_t xx[4] = {xv.x, xv.y, xv.z, xv.w};
+            float a = acc[mm];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              a = fmaf(bf16_lo(ww[j]), bf16_lo(xx[j]), a);
+              a = fmaf(bf16_hi(ww[j]), bf16_hi(xx[j]), a);
+            }
+            acc[mm] = a;
+          }
+        }
+      }
+#pragma unroll
+      for (int mm = 0; mm < 8; ++mm) {
+        const float v = warp_sum(acc[mm]);
+        if (lane == 0 && m0 + mm < p.M) p.logits[(size_t)(m0 + mm) * p.ld + r] = v;
+      }
+    }
+  }
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int t = atomicAdd(p.ticket, 1);
+    s_last = t == (int)gridDim.x - 1;
+    if (s_last) *p.ticket = 0;
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  const int stride = p.k + p.shared_slot;
+  for (int m = warp; m < p.M; m += 8) {
+    const float* lrow = p.logits + (size_t)m * p.ld;
+    route_row(lrow, p.E, p.k, p.topk_idx + (size_t)m * stride, p.topk_w + (size_t)m * stride, lane);
+    if (p.shared_slot && lane == 0) {
+      p.topk_idx[(size_t)m * stride + p.k] = p.E;
+      p.topk_w[(size_t)m * stride + p.k] = p.has_gate ? 1.f / (1.f + __expf(-__ldcg(lrow + p.E))) : 1.f;
+    }
+  }
 }
 
 // ---------------------------------------------------------------- count + rank
@@ -159,9 +233,11 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const __nv_bfloat16* _
   }
 }
 
-// ---------------------------------------------------------------- combine (decode rows): one CTA per row
+// ---------------------------------------------------------------- combine (decode rows): a thread per (row, column)
 // Folds the split-K slices of the batched expert GEMVs: part is [batch = M * k (+ M shared)][S][H] fp32,
-// written as out[0][m][H] fp32 (one slice) for the next residual fold.
+// written as out[0][m][H] fp32 (one slice) for the next residual fold.  Grid (M, H / 256): a thread's k * S loads
+// are independent, so the kernel is one memory latency long (one CTA per row looping over the columns took 75 us
+// for a 2048-wide row).
 __global__ void __launch_bounds__(256) moe_combine_rows_kernel(const float* __restrict__ part, int S, int M, int k, int H,
                                                                const float* __restrict__ topk_w,
                                                                const float* __restrict__ shared_part, int S_sh,
@@ -172,8 +248,9 @@ __global__ void __launch_bounds__(256) moe_combine_rows_kernel(const float* __re
   const int m = blockIdx.x;
   float g = 0.f;
   if (shared_part) g = gate_logit ? 1.f / (1.f + __expf(-gate_logit[(size_t)m * gate_ld])) : 1.f;
-  for (int j = threadIdx.x; j < H; j += blockDim.x) {
+  for (int j = blockIdx.y * blockDim.x + threadIdx.x; j < H; j += gridDim.y * blockDim.x) {
     float acc = 0.f;
+#pragma unroll 4
     for (int s = 0; s < k; ++s) {
       const float* p = part + ((size_t)(m * k + s) * S) * H + j;
       float v = 0.f;
@@ -198,6 +275,15 @@ extern "C" int b2_moe_route(const float* logits, int ld, int T, int E, int k, in
   const int blocks = (T * 32 + 255) / 256;
   return b2_launch(moe_route_kernel, dim3(blocks), dim3(256), 0, (cudaStream_t)stream, true, logits, ld, T, E, k,
                    topk_idx, topk_w);
+}
+
+extern "C" int b2_moe_router_rows(const void* w, const void* x, float* logits, int M, int R, int H, int ld, int E, int k,
+                                  int shared_slot, int has_gate, int* topk_idx, float* topk_w, int* ticket,
+                                  void* stream) {
+  if (E > 512 || k > 32 || k < 1 || H % 8 || M < 1 || R < E + (has_gate ? 1 : 0) || ld < R) return -1;
+  RouterRowsParams p{(const __nv_bfloat16*)w, (const __nv_bfloat16*)x, logits, M, R, H, ld, E, k, shared_slot, has_gate,
+                     topk_idx, topk_w, ticket};
+  return b2_launch(moe_router_rows_kernel, dim3((R + 7) / 8), dim3(256), 0, (cudaStream_t)stream, true, p);
 }
 
 // counts must hold E zeros on entry (the caller clears it on the stream).
@@ -239,8 +325,8 @@ extern "C" int b2_moe_combine(const void* y, const int* row_of, const float* top
 extern "C" int b2_moe_combine_rows(const float* part, int S, int M, int k, int H, const float* topk_w,
                                    const float* shared_part, int S_sh, const float* gate_logit, int gate_ld, float* out,
                                    void* stream) {
-  return b2_launch(moe_combine_rows_kernel, dim3(M), dim3(256), 0, (cudaStream_t)stream, true, part, S, M, k, H, topk_w,
-                   shared_part, S_sh, gate_logit, gate_ld, out);
+  return b2_launch(moe_combine_rows_kernel, dim3(M, (H + 255) / 256), dim3(256), 0, (cudaStream_t)stream, true, part, S, M,
+                   k, H, topk_w, shared_part, S_sh, gate_logit, gate_ld, out);
 }
 
 B2_DEFINE_STATUS(moe)

@@ -42,10 +42,25 @@ def combine_rows(part, s, m, k, h, topk_w, shared_part, s_sh, gate_logit, gate_l
                                          K._p(gate_logit), gate_ld, K._p(out), K._stream()), "moe_combine_rows")
 
 
+def router_rows(w, x, logits, m, r, h, ld, e, k, shared_slot, has_gate, topk_idx, topk_w, ticket):
+    """Decode rows: router logits (``r`` rows of ``w``: the experts, then the shared expert's gate row) and the
+    routing of every row in one launch.  ``shared_slot``: each row gets slot k = (expert id ``e``, sigmoid(gate logit)
+    or 1), so ``topk_idx`` / ``topk_w`` hold k + 1 entries per row.  ``ticket``: one zeroed int32 word."""
+    K._check(K.lib().b2_moe_router_rows(K._p(w), K._p(x), K._p(logits), m, r, h, ld, e, k, int(shared_slot), int(has_gate),
+                                        K._p(topk_idx), K._p(topk_w), K._p(ticket), K._stream()), "moe_router_rows")
+
+
 def gemv_experts(w4b_stack, expert_bytes, expert_ids, batches, x, x_div, x_batch_bytes, out, n, k, splits, ldx,
-                 x_mode=0, s_in=1, x_slice=0, sparse=False):
+                 x_mode=0, s_in=1, x_slice=0, sparse=False, alt_w=None, alt_id=-1):
     """One row per batch against the W4B weights of expert ``expert_ids[b]``; ``out`` is ``[b][splits][n]``.
-    ``sparse``: batches whose id is negative are skipped (their output rows are left as they are)."""
+    ``sparse``: batches whose id is negative are skipped (their output rows are left as they are).  ``alt_w``: batches
+    whose id is ``alt_id`` read this tensor instead of the stack (the shared expert as one more slot of a row)."""
+    if alt_w is not None:
+        rc = K.lib().b2_gemv_w4_experts_alt(K._p(w4b_stack), ctypes.c_longlong(expert_bytes), K._p(expert_ids), batches,
+                                            K._p(x), x_div, ctypes.c_longlong(x_batch_bytes), K._p(out), n, k, splits, ldx,
+                                            x_mode, s_in, ctypes.c_longlong(x_slice), K._p(alt_w), alt_id, K._stream())
+        K._check(rc, "gemv_w4_experts_alt")
+        return
     fn = K.lib().b2_gemv_w4_experts_sparse if sparse else K.lib().b2_gemv_w4_experts
     rc = fn(K._p(w4b_stack), ctypes.c_longlong(expert_bytes), K._p(expert_ids), batches,
                                     K._p(x), x_div, ctypes.c_longlong(x_batch_bytes), K._p(out), n, k, splits, ldx,
