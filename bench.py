@@ -203,6 +203,16 @@ def main():
     if args.what in ("all", "moe") and one_gpu_sections:
         extra["moe_prefill"] = run_prefill_bench(args, barrier, model="moe-35b-a3b", backend=args.prefill_backend)
         release()
+
+        def moe_decode():
+            # one request decoding on the 35B-A3B shape (3B active parameters per token), timed like the headline
+            import copy
+            a = copy.copy(args)
+            a.model, a.windows = "moe-35b-a3b", 3
+            r = run_decode_bench(a, barrier)
+            return {"ms_per_step": r["ms_per_step"], "tokens_per_s": 1e3 / r["ms_per_step"],
+                    "e2e_tokens_per_s": 1e3 / r["e2e_ms_per_step"], "depth": a.depth, "config": r["config"]}
+        guarded("moe_decode", moe_decode)
     if world == 1 and args.what in ("all", "prefill", "moe", "w4"):
         # the prompt pass that keeps ONLY the int4 weights resident: the GEMM expands W4B blocks inside its shared-memory tiles
         if args.what != "moe":

@@ -316,6 +316,38 @@ class DecoderModel:
         gu, s_gu = self._gemv_fused("gate_up", lw.gate_up, b.resid, m, norm_w=lw.post_norm, x_mode=2)
         self._gemv_fused("down", lw.down, gu, m, fold=True, x_mode=1, s_in=s_gu, x_slice=m * 2 * cfg.ffn)
 
+    def moe_layer_fused(self, lw: LayerWeights, li: int, m: int, ctrl, block_table, max_blocks, kv: KVCache, x_ready: bool):
+        """One mixture-of-experts layer in ten launches (eleven unfused): the input RMSNorm rides in the qkv GEMV's
+        staging, the attention branch's residual fold in the o GEMV's last CTAs, and the experts' weighted sum is
+        added to the residual rows by the combine kernel, which also leaves the sums of squares the next layer's
+        qkv GEMV normalises with.  ``x_ready`` as in ``dense_layer_fused``."""
+        from . import moe as _moe
+        cfg, b = self.cfg, self.buf
+        kc, vc, ks, vs = kv.layer(li)
+        if self.rope_fold and not kv.kv_int8 and cfg.head_dim == 128 and lw.qkv.n == cfg.qkv_dim:
+            self._qkv_rope(lw, m, ctrl, block_table, max_blocks, kc, vc, x_ready)
+        else:
+            if x_ready:
+                part, s = self._gemv("qkv", lw.qkv, b.x, m)
+            else:
+                part, s = self._gemv_fused("qkv", lw.qkv, b.resid, m, norm_w=lw.input_norm, x_mode=2)
+            K.rope_append(part, m * cfg.qkv_dim, s, m, ctrl, block_table, max_blocks, self.cos_t, self.sin_t,
+                          cfg.n_q_heads, cfg.n_kv_heads, cfg.head_dim, b.q, kc, vc, ks, vs, kv.kv_int8)
+        self._attention(m, ctrl, block_table, max_blocks, kv, kc, vc, ks, vs, self._window(li))
+        self._gemv_fused("o", lw.o, b.attn_out, m, fold=True)
+        # the experts and the router read normalised rows
+        K.resid_norm(1, m, cfg.hidden, lw.post_norm, cfg.rms_eps, b.resid, b.x, resid_in=b.resid, splits=0)
+        _moe.moe_block_rows(self, lw, m, fold=True)
+
+    def _moe_fusable(self, layers: List[LayerWeights]) -> bool:
+        cfg = self.cfg
+        if not self.fused or self.tp is not None or self.nccl is not None or self.ep is not None or cfg.hidden % 128:
+            return False
+        return all(lw.experts_gate_up_w4b is not None and lw.gdn is None and lw.qkv is not None and
+                   (lw.shared is None or (cfg.shared_ffn == cfg.expert_ffn and
+                                          lw.shared.gate_up.w4b.numel() == lw.experts_gate_up_w4b[0].numel()))
+                   for lw in layers)
+
     # ------------------------------------------------------------------ whole-step kernel
     def mega_plan(self, layers: List[LayerWeights], m: int, kv: KVCache):
         """The schedule of the whole-step kernel for ``m`` rows, or None when this step is outside what it covers:
@@ -407,6 +439,12 @@ class DecoderModel:
                          vocab=cfg.vocab, flag=b.flag)
             for i, lw in enumerate(layers):
                 self.dense_layer_fused(lw, kv_layer0 + i, m, ctrl, block_table, max_blocks, kv, x_ready=(i == 0))
+            return None, 0      # the residual stream is already folded
+        if first_from_embed and self._moe_fusable(layers):
+            K.resid_norm(0, m, h, layers[0].input_norm, cfg.rms_eps, b.resid, b.x, embed=self.w.embed, ctrl=ctrl,
+                         vocab=cfg.vocab, flag=b.flag)
+            for i, lw in enumerate(layers):
+                self.moe_layer_fused(lw, kv_layer0 + i, m, ctrl, block_table, max_blocks, kv, x_ready=(i == 0))
             return None, 0      # the residual stream is already folded
         if self.tp is not None:
             raise NotImplementedError("tensor parallel decode covers dense models whose hidden size is a multiple of 128")

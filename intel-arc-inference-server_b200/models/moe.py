@@ -51,8 +51,9 @@ class _RowScratch:
         self.ticket = torch.zeros(1, dtype=torch.int32, device=dev)
 
 
-def moe_block_rows(model, lw: LayerWeights, m: int):
-    """Returns (partials, splits) of the MoE branch for the next residual fold."""
+def moe_block_rows(model, lw: LayerWeights, m: int, fold: bool = False):
+    """Returns (partials, splits) of the MoE branch for the next residual fold.  ``fold``: the weighted sum is added
+    to ``buf.resid`` in place and ``buf.ssq`` gets the rows' sums of squares (returns ``(None, 0)``)."""
     cfg, b = model.cfg, model.buf
     sc = getattr(model, "_moe_rows", None)
     if sc is None:
@@ -74,8 +75,14 @@ def moe_block_rows(model, lw: LayerWeights, m: int):
                        alt_w=alt_gu, alt_id=e)
         M.gemv_experts(lw.experts_down_w4b, dn_bytes, sc.topk_idx, m * ks, sc.part_gu, 1, sc.s_gu * 2 * i * 4, sc.part_dn,
                        h, i, sc.s_dn, 2 * i, x_mode=1, s_in=sc.s_gu, x_slice=2 * i, alt_w=alt_dn, alt_id=e)
+        if fold:
+            M.combine_rows(sc.part_dn, sc.s_dn, m, ks, h, sc.topk_w, None, 0, None, sc.ld, sc.out, fold_resid=b.resid,
+                           fold_ssq=b.ssq)
+            return None, 0
         M.combine_rows(sc.part_dn, sc.s_dn, m, ks, h, sc.topk_w, None, 0, None, sc.ld, sc.out)
         return sc.out, 1
+    if fold:
+        raise NotImplementedError("the folding combine covers a shared expert of the routed experts' shape")
     K.head_gemv(rc, b.x, sc.logits, m, rc.shape[0], h)
     M.route(sc.logits, sc.ld, m, e, k, sc.topk_idx, sc.topk_w)
     M.gemv_experts(lw.experts_gate_up_w4b, gu_bytes, sc.topk_idx, m * k, b.x, k, h * 2, sc.part_gu, 2 * i, h, sc.s_gu, h)

@@ -242,14 +242,17 @@ __global__ void __launch_bounds__(256) moe_combine_rows_kernel(const float* __re
                                                                const float* __restrict__ topk_w,
                                                                const float* __restrict__ shared_part, int S_sh,
                                                                const float* __restrict__ gate_logit, int gate_ld,
-                                                               float* __restrict__ out) {
+                                                               float* __restrict__ out, __nv_bfloat16* fold_resid,
+                                                               float* __restrict__ fold_ssq) {
+  __shared__ float s_ss[8];
   pdl_wait();
   pdl_launch_dependents();
   const int m = blockIdx.x;
   float g = 0.f;
   if (shared_part) g = gate_logit ? 1.f / (1.f + __expf(-gate_logit[(size_t)m * gate_ld])) : 1.f;
-  for (int j = blockIdx.y * blockDim.x + threadIdx.x; j < H; j += gridDim.y * blockDim.x) {
-    float acc = 0.f;
+  const int j = blockIdx.y * blockDim.x + threadIdx.x;
+  float acc = 0.f;
+  if (j < H) {
 #pragma unroll 4
     for (int s = 0; s < k; ++s) {
       const float* p = part + ((size_t)(m * k + s) * S) * H + j;
@@ -263,7 +266,29 @@ __global__ void __launch_bounds__(256) moe_combine_rows_kernel(const float* __re
       for (int q = 0; q < S_sh; ++q) v += p[(size_t)q * M * H];
       acc = fmaf(g, v, acc);
     }
-    out[(size_t)m * H + j] = acc;
+  }
+  if (!fold_resid) {
+    if (j < H) out[(size_t)m * H + j] = acc;
+    return;
+  }
+  // Fold form: the row's residual stream takes the sum in place (bf16) and every 128-column block's sum of squares
+  // of the ROUNDED values is left for the next layer's fused RMSNorm -- the arithmetic and the order of the four
+  // 32-column partial sums are those of the GEMV's fold epilogue.
+  float rf = 0.f;
+  if (j < H) {
+    const __nv_bfloat16 rb = __float2bfloat16(__bfloat162float(fold_resid[(size_t)m * H + j]) + acc);
+    fold_resid[(size_t)m * H + j] = rb;
+    rf = __bfloat162float(rb);
+  }
+  const float ss = warp_sum(rf * rf);
+  if ((threadIdx.x & 31) == 0) s_ss[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  if (threadIdx.x < 2) {
+    const int nb = blockIdx.y * 2 + threadIdx.x;
+    if (nb * 128 < H) {
+      const float* q = s_ss + 4 * threadIdx.x;
+      fold_ssq[(size_t)m * ((H + 127) / 128) + nb] = ((q[0] + q[1]) + q[2]) + q[3];
+    }
   }
 }
 
@@ -324,9 +349,10 @@ extern "C" int b2_moe_combine(const void* y, const int* row_of, const float* top
 
 extern "C" int b2_moe_combine_rows(const float* part, int S, int M, int k, int H, const float* topk_w,
                                    const float* shared_part, int S_sh, const float* gate_logit, int gate_ld, float* out,
-                                   void* stream) {
+                                   void* fold_resid, float* fold_ssq, void* stream) {
+  if (fold_resid && (!fold_ssq || H % 128)) return -1;
   return b2_launch(moe_combine_rows_kernel, dim3(M, (H + 255) / 256), dim3(256), 0, (cudaStream_t)stream, true, part, S, M,
-                   k, H, topk_w, shared_part, S_sh, gate_logit, gate_ld, out);
+                   k, H, topk_w, shared_part, S_sh, gate_logit, gate_ld, out, (__nv_bfloat16*)fold_resid, fold_ssq);
 }
 
 B2_DEFINE_STATUS(moe)

@@ -37,9 +37,13 @@ def combine(y, row_of, topk_w, t, k, h, shared_y, gate_logit, gate_ld, resid, ou
                                     gate_ld, K._p(resid), K._p(out), K._stream()), "moe_combine")
 
 
-def combine_rows(part, s, m, k, h, topk_w, shared_part, s_sh, gate_logit, gate_ld, out):
+def combine_rows(part, s, m, k, h, topk_w, shared_part, s_sh, gate_logit, gate_ld, out, fold_resid=None, fold_ssq=None):
+    """Weighted sum of a row's slots (split-K slices folded).  ``fold_resid`` / ``fold_ssq``: add the sum to the bf16
+    residual rows in place and leave the per-128-column sums of squares for the next fused RMSNorm, instead of
+    writing ``out``."""
     K._check(K.lib().b2_moe_combine_rows(K._p(part), s, m, k, h, K._p(topk_w), K._p(shared_part), s_sh,
-                                         K._p(gate_logit), gate_ld, K._p(out), K._stream()), "moe_combine_rows")
+                                         K._p(gate_logit), gate_ld, K._p(out), K._p(fold_resid), K._p(fold_ssq),
+                                         K._stream()), "moe_combine_rows")
 
 
 def router_rows(w, x, logits, m, r, h, ld, e, k, shared_slot, has_gate, topk_idx, topk_w, ticket):

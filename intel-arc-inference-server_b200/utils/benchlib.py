@@ -72,7 +72,8 @@ def run_decode_bench(args, barrier) -> dict:
         "h2d": K.CTRL_WORDS * 4, "d2h": K.CTRL_WORDS * 4, "launches": launches,
         "config": {"model": cfg.name, "global_batch": 1, "seq_len": args.depth, "parallelism": "replica",
                    "kv_cache": args.kv_cache, "lm_head": "int8" if args.int8_head else "bf16",
-                   "weights": "W4A16 int4 g64, random init", "l2": "inputs larger than L2 (12.7 GB of weights per step)",
+                   "weights": "W4A16 int4 g64, random init",
+                   "l2": f"inputs larger than L2 ({w_bytes / 1e9:.1f} GB of weights per step)",
                    "bytes_per_step": w_bytes + kv_bytes, "windows_ms_per_step": [round(x, 4) for x in win_ms],
                    "launches_per_step": eng.launches(1, True),
                    "achieved_GBps": (w_bytes + kv_bytes) / (ms / 1e3) / 1e9},
