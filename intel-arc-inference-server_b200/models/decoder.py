@@ -316,6 +316,24 @@ class DecoderModel:
         gu, s_gu = self._gemv_fused("gate_up", lw.gate_up, b.resid, m, norm_w=lw.post_norm, x_mode=2)
         self._gemv_fused("down", lw.down, gu, m, fold=True, x_mode=1, s_in=s_gu, x_slice=m * 2 * cfg.ffn)
 
+    def gdn_layer_fused(self, lw: LayerWeights, li: int, m: int, ctrl, kv: KVCache, x_ready: bool):
+        """A gated delta-net layer with a dense FFN in six launches: projection GEMV (input RMSNorm in its staging),
+        convolution + SiLU, recurrent step, output projection (residual fold in its last CTAs), gate||up (post norm in
+        its staging), down (fold).  ``x_ready`` as in ``dense_layer_fused``."""
+        cfg, b, g = self.cfg, self.buf, lw.gdn
+        gi = cfg.gdn_index(li)
+        if x_ready:
+            part, s = self._gemv("gdn_in", g.in_proj, b.x, m)
+        else:
+            part, s = self._gemv_fused("gdn_in", g.in_proj, b.resid, m, norm_w=lw.input_norm, x_mode=2)
+        n = cfg.gdn_proj_dim
+        K.gdn_conv(part, s, m, n, cfg.gdn_conv_channels, ctrl, g.conv_w, kv.gdn_conv[gi], b.gdn_act)
+        K.gdn_step(b.gdn_act, m, n, cfg.gdn_k_heads, cfg.gdn_v_heads, cfg.gdn_head_dim, ctrl, g.a_log, g.dt_bias,
+                   g.norm_w, cfg.rms_eps, kv.gdn_state[gi], b.gdn_out)
+        self._gemv_fused("gdn_out", g.out_proj, b.gdn_out, m, fold=True)
+        gu, s_gu = self._gemv_fused("gate_up", lw.gate_up, b.resid, m, norm_w=lw.post_norm, x_mode=2)
+        self._gemv_fused("down", lw.down, gu, m, fold=True, x_mode=1, s_in=s_gu, x_slice=m * 2 * cfg.ffn)
+
     def moe_layer_fused(self, lw: LayerWeights, li: int, m: int, ctrl, block_table, max_blocks, kv: KVCache, x_ready: bool):
         """One mixture-of-experts layer in ten launches (eleven unfused): the input RMSNorm rides in the qkv GEMV's
         staging, the attention branch's residual fold in the o GEMV's last CTAs, and the experts' weighted sum is
@@ -440,6 +458,18 @@ class DecoderModel:
             for i, lw in enumerate(layers):
                 self.dense_layer_fused(lw, kv_layer0 + i, m, ctrl, block_table, max_blocks, kv, x_ready=(i == 0))
             return None, 0      # the residual stream is already folded
+        if (self.fused and first_from_embed and self.tp is None and self.nccl is None and h % 128 == 0 and
+                any(lw.gdn is not None for lw in layers) and all(lw.gate_up is not None for lw in layers) and
+                cfg.gdn_value_dim % 64 == 0):
+            # hybrid model: gated delta-net layers and attention layers, both on their fused forms
+            K.resid_norm(0, m, h, layers[0].input_norm, cfg.rms_eps, b.resid, b.x, embed=self.w.embed, ctrl=ctrl,
+                         vocab=cfg.vocab, flag=b.flag)
+            for i, lw in enumerate(layers):
+                if lw.gdn is not None:
+                    self.gdn_layer_fused(lw, kv_layer0 + i, m, ctrl, kv, x_ready=(i == 0))
+                else:
+                    self.dense_layer_fused(lw, kv_layer0 + i, m, ctrl, block_table, max_blocks, kv, x_ready=(i == 0))
+            return None, 0
         if first_from_embed and self._moe_fusable(layers):
             K.resid_norm(0, m, h, layers[0].input_norm, cfg.rms_eps, b.resid, b.x, embed=self.w.embed, ctrl=ctrl,
                          vocab=cfg.vocab, flag=b.flag)
