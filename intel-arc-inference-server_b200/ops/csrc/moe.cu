@@ -98,30 +98,42 @@ __global__ void __launch_bounds__(256) moe_router_rows_kernel(const RouterRowsPa
   const int r = blockIdx.x * 8 + warp;
   if (r < p.R) {
     const uint4* wr = reinterpret_cast<const uint4*>(p.w + (size_t)r * p.H);
+    const int chunks = p.H / 8;                 // 16-byte pieces of a row; a lane takes every 32nd
     for (int m0 = 0; m0 < p.M; m0 += 8) {
+      const int mt = min(8, p.M - m0);
       float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-      for (int c = lane; c < p.H / 8; c += 32) {
-        const uint4 wv = __ldg(wr + c);
-        const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
+      for (int c0 = lane; c0 < chunks; c0 += 32 * 8) {
+        // eight pieces of the router row in flight, then the token rows against them
+        uint4 wv[8];
 #pragma unroll
-        for (int mm = 0; mm < 8; ++mm) {
-          if (m0 + mm < p.M) {
-            const uint4 xv = __ldg(reinterpret_cast<const uint4*>(p.x + (size_t)(m0 + mm) * p.H) + c);
-            const uint32_t xx[4] = {xv.x, xv.y, xv.z, xv.w};
-            float a = acc[mm];
+        for (int u = 0; u < 8; ++u) {
+          const int c = c0 + 32 * u;
+          wv[u] = c < chunks ? __ldg(wr + c) : make_uint4(0, 0, 0, 0);
+        }
+        for (int mm = 0; mm < mt; ++mm) {
+          const uint4* xr = reinterpret_cast<const uint4*>(p.x + (size_t)(m0 + mm) * p.H);
+          uint4 xv[8];
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {
+            const int c = c0 + 32 * u;
+            xv[u] = c < chunks ? __ldg(xr + c) : make_uint4(0, 0, 0, 0);
+          }
+          float a = 0.f, b = 0.f;
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {
+            const uint32_t ww[4] = {wv[u].x, wv[u].y, wv[u].z, wv[u].w}, xx[4] = {xv[u].x, xv[u].y, xv[u].z, xv[u].w};
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
               a = fmaf(bf16_lo(ww[j]), bf16_lo(xx[j]), a);
-              a = fmaf(bf16_hi(ww[j]), bf16_hi(xx[j]), a);
+              b = fmaf(bf16_hi(ww[j]), bf16_hi(xx[j]), b);
             }
-            acc[mm] = a;
           }
+          acc[mm] += a + b;
         }
       }
-#pragma unroll
-      for (int mm = 0; mm < 8; ++mm) {
+      for (int mm = 0; mm < mt; ++mm) {
         const float v = warp_sum(acc[mm]);
-        if (lane == 0 && m0 + mm < p.M) p.logits[(size_t)(m0 + mm) * p.ld + r] = v;
+        if (lane == 0) p.logits[(size_t)(m0 + mm) * p.ld + r] = v;
       }
     }
   }
@@ -253,12 +265,31 @@ __global__ void __launch_bounds__(256) moe_combine_rows_kernel(const float* __re
   const int j = blockIdx.y * blockDim.x + threadIdx.x;
   float acc = 0.f;
   if (j < H) {
-#pragma unroll 4
-    for (int s = 0; s < k; ++s) {
-      const float* p = part + ((size_t)(m * k + s) * S) * H + j;
-      float v = 0.f;
-      for (int q = 0; q < S; ++q) v += p[(size_t)q * H];
-      acc = fmaf(topk_w[m * k + s], v, acc);
+    // every load of the row's slots goes out before the first is used (up to 12 slots x 4 slices a pass)
+    for (int s0 = 0; s0 < k; s0 += 12) {
+      float v[12][4], w[12];
+#pragma unroll
+      for (int u = 0; u < 12; ++u) {
+        const int s = s0 + u;
+        w[u] = s < k ? topk_w[m * k + s] : 0.f;
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+          v[u][q] = (s < k && q < S) ? part[((size_t)(m * k + s) * S + q) * H + j] : 0.f;
+      }
+#pragma unroll
+      for (int u = 0; u < 12; ++u) {
+        float t = v[u][0];
+#pragma unroll
+        for (int q = 1; q < 4; ++q) t += v[u][q];      // slices in order; absent ones add 0
+        acc = fmaf(w[u], t, acc);
+      }
+    }
+    if (S > 4) {   // more slices than a pass holds: the rest, slot by slot
+      for (int s = 0; s < k; ++s) {
+        float t = 0.f;
+        for (int q = 4; q < S; ++q) t += part[((size_t)(m * k + s) * S + q) * H + j];
+        acc = fmaf(topk_w[m * k + s], t, acc);
+      }
     }
     if (shared_part) {
       const float* p = shared_part + (size_t)m * H + j;  // shared expert: [S_sh][M][H]
