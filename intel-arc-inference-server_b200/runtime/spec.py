@@ -316,6 +316,11 @@ class SpecAdapter:
         self.inner = inner
         self.e: Engine = inner.e
         self.spec, self.k_max = spec, spec_max
+        if self.e.cfg.is_moe:
+            # never validated: the one run of a draft head over a mixture-of-experts trunk ended in an illegal memory
+            # access, so the combination is refused until its cause is found
+            raise NotImplementedError("draft heads (--spec mtp / dflash) are not available for mixture-of-experts models; "
+                                      "use --spec lookup or --spec off")
         w = self.e.model.w
         if spec == "mtp":
             if w.mtp is None:
