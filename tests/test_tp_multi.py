@@ -34,3 +34,18 @@ def test_tp_decode_matches_one_gpu(world):
     for mode in ("fused", "nccl"):
         assert rep[mode]["ok"], rep
         assert rep[mode]["ranks_same_tokens"] and rep[mode]["ranks_same_residual"]
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("prompt", [40, 600])
+def test_draft_heads_under_tensor_parallelism(prompt):
+    """MTP chain and block drafter with the head sliced over two ranks: greedy drafts + verify + accept give the tokens
+    of the same sharded engine decoding plainly; every rank proposes the same drafts (the block drafter merges the
+    candidates of the ranks' vocabulary slices).  The longer prompt goes through the fused prompt pass, whose hidden
+    rows are gathered for the head's ingestion."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    rep = _run(2, ["--model", "small-dense", "--spec", "--prompt", str(prompt)])
+    for kind in ("spec_mtp", "spec_dflash"):
+        assert rep[kind]["ok"], rep
+        assert rep[kind]["tokens_equal_plain"] and rep[kind]["ranks_same_tokens"] and rep[kind]["ranks_same_drafts"]
