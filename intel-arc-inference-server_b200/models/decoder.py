@@ -161,6 +161,7 @@ class DecoderModel:
         # CTA of the GEMV (whose prologue repeats the rows' work per 128 output columns)
         self.prequant_rows = 3
         self.attn_rows_min = int(os.environ.get("B2_ATTN_ROWS_MIN", "1"))
+        self.rows_one_request = False    # set by the engine around a step whose rows are one request's, consecutive
         self.block_rows = False      # set by a block drafter around its layers: flagged rows attend non-causally
         self.attn_merge_inkernel_rows = int(os.environ.get("B2_ATTN_MERGE_INKERNEL_ROWS", "0"))
         # fixed KV split spans make a row's attention bits independent of the rows it is verified with (speculation
@@ -212,7 +213,7 @@ class DecoderModel:
                         m, cfg.n_q_heads,
                         cfg.n_kv_heads, cfg.head_dim, self.nsplit_attn, max_blocks, self.scale,
                         span_pages=(max_blocks + self.nsplit_attn - 1) // self.nsplit_attn if self.attn_fixed_spans else 0,
-                        k_scale=ks, v_scale=vs, kv_int8=kv.kv_int8, window=window)
+                        k_scale=ks, v_scale=vs, kv_int8=kv.kv_int8, window=window, one_request=self.rows_one_request and m > 1)
         else:
             if window > 0:
                 raise NotImplementedError("sliding-window layers need the multi-row attention kernel (head size 128)")
@@ -442,6 +443,7 @@ class DecoderModel:
         h = cfg.hidden
         pend = None
         embedded = False
+        self.rows_one_request = bool(one_request)     # the attention launch then counts row groups, not rows
         if self.fused and resid_ready and all(lw.gate_up is not None and lw.gdn is None for lw in layers) and h % 128 == 0:
             for i, lw in enumerate(layers):
                 self.dense_layer_fused(lw, kv_layer0 + i, m, ctrl, block_table, max_blocks, kv, x_ready=False)

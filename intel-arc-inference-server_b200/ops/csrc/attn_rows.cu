@@ -55,6 +55,8 @@ struct AttnRowsParams {
   int M, n_q, n_kv, gqa, nsplit, max_blocks;
   int nbuf;        // 1: one K / V tile pair; 2: the next batch of keys is fetched while this one is multiplied
   int window;      // > 0: a row attends to its last `window` positions only (sliding-window layers)
+  int one_group;   // 1: the host knows that all rows belong to one request at consecutive positions: grid.z counts
+                   //    groups of rmax rows, not rows (no CTAs that only find out they are not a group's leader)
   int block;       // 1: a row whose CTRL_ROW_BLOCK word is set attends to ALL positions of its group, those after it
                    //    too (a block drafter's rows see one another: no causal mask inside the block); the group's
                    //    other rows stay causal
@@ -81,7 +83,7 @@ __device__ __forceinline__ uint32_t tile_off(int row, int d) {
 // NKS: key slices per batch (1, 2 or 4); the four warps are NKS slices x (4 / NKS) groups of 16 query rows.
 template <bool I8, int NKS>
 __device__ __forceinline__ void attn_rows_body(const AttnRowsParams& p, uint8_t* smem_raw, const int* s_pos, int* s_last_p, int* s_bt,
-                                               const int req, const int rows, const int QR, const int ctx_max) {
+                                               const int req, const int rows, const int QR, const int ctx_max, const int z) {
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;   // the swizzle pattern repeats every 1024 bytes
   // bf16 form: nbuf pairs of operand tiles.  int8 form: one pair of operand tiles, nbuf pairs of staged int8 rows.
   const int ntile = I8 ? 1 : p.nbuf;
@@ -94,7 +96,7 @@ __device__ __forceinline__ void attn_rows_body(const AttnRowsParams& p, uint8_t*
   constexpr int KW = KB / NKS;              // keys per warp and batch
   constexpr int KS = KW > kPassKeys ? kPassKeys : KW;   // keys per pass over the warp's slice
   constexpr int NJ = KS / 8;                // n8 tiles of keys per pass
-  const int kh = blockIdx.x, split = blockIdx.y, z = blockIdx.z;
+  const int kh = blockIdx.x, split = blockIdx.y;   // z: the group's first row
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
   const int rg = warp % NRG, ksl = warp / NRG;
   const int total_pages = (ctx_max + 15) >> 4;
@@ -427,7 +429,7 @@ template <bool I8>
 __global__ void __launch_bounds__(kThreads, 2) attn_rows_kernel(const __grid_constant__ AttnRowsParams p) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ int s_last;
-  const int z = blockIdx.z, tid = threadIdx.x;
+  const int z = p.one_group ? blockIdx.z * min(kMaxRows, 64 / p.gqa) : blockIdx.z, tid = threadIdx.x;
   if (tid == 0) {   // the descriptors are launch parameters: their fetch overlaps the wait for the previous kernel
     prefetch_tmap(&p.k_map);
     prefetch_tmap(&p.v_map);
@@ -461,11 +463,11 @@ __global__ void __launch_bounds__(kThreads, 2) attn_rows_kernel(const __grid_con
     __syncthreads();
   }
   if (QR <= 16 && !p.one_slice)
-    attn_rows_body<I8, 4>(p, smem_raw, s_pos, &s_last, s_bt, req, rows, QR, ctx_max);
+    attn_rows_body<I8, 4>(p, smem_raw, s_pos, &s_last, s_bt, req, rows, QR, ctx_max, z);
   else if (QR <= 32 && !p.one_slice)
-    attn_rows_body<I8, 2>(p, smem_raw, s_pos, &s_last, s_bt, req, rows, QR, ctx_max);
+    attn_rows_body<I8, 2>(p, smem_raw, s_pos, &s_last, s_bt, req, rows, QR, ctx_max, z);
   else
-    attn_rows_body<I8, 1>(p, smem_raw, s_pos, &s_last, s_bt, req, rows, QR, ctx_max);
+    attn_rows_body<I8, 1>(p, smem_raw, s_pos, &s_last, s_bt, req, rows, QR, ctx_max, z);
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -529,7 +531,7 @@ extern "C" int b2_attn_rows(const void* q, const void* k_cache, const void* v_ca
                             const float* v_scale, int kv_int8, const int* block_table,
                             const int* ctrl, float* o_part, float* ml_part, void* out, int* tickets, int M, int n_q,
                             int n_kv, int D_, int nsplit, int max_blocks, float scale, int span_pages, int num_pages,
-                            int window, void* stream) {
+                            int window, int one_group, void* stream) {
   if (D_ != D || nsplit < 1 || nsplit > 64 || n_q % n_kv != 0 || n_q / n_kv > 16 || M > 64 || num_pages < 1) return -1;
   if (((uintptr_t)k_cache | (uintptr_t)v_cache) & 15) return -4;
   AttnRowsParams p;
@@ -551,7 +553,10 @@ extern "C" int b2_attn_rows(const void* q, const void* k_cache, const void* v_ca
   // at depth 32768: 1.10 against 1.12 ms for 8 layers); the second tile pair pays only when the grid leaves SMs
   // with a single CTA and a split holds several batches.  B2_ATTN_NBUF=1|2 overrides.
   const int pages_per_split = span_pages > 0 ? span_pages : (max_blocks + nsplit - 1) / nsplit;
-  p.nbuf = (pages_per_split * 16 > 2 * KB && n_kv * nsplit * M <= 148) ? 2 : 1;
+  const int rmax = min(kMaxRows, 64 / (n_q / n_kv));
+  const int gz = one_group ? (M + rmax - 1) / rmax : M;     // grid.z: groups, or rows that find their group themselves
+  p.one_group = one_group ? 1 : 0;
+  p.nbuf = (pages_per_split * 16 > 2 * KB && n_kv * nsplit * gz <= 148) ? 2 : 1;
   static const int nbuf_env = [] { const char* e = getenv("B2_ATTN_NBUF"); return e ? atoi(e) : 0; }();
   if (nbuf_env == 1 || nbuf_env == 2) p.nbuf = nbuf_env;
   const int smem = 1024 + (kv_int8 ? 1 : p.nbuf) * 2 * TILEB + 64 + (kv_int8 ? p.nbuf * 2 * KB * D : 0);
@@ -566,8 +571,8 @@ extern "C" int b2_attn_rows(const void* q, const void* k_cache, const void* v_ca
     configured[dev & 63] = 1;
   }
   if (kv_int8)
-    return b2_launch(attn_rows_kernel<true>, dim3(n_kv, nsplit, M), dim3(kThreads), smem, (cudaStream_t)stream, true, p);
-  return b2_launch(attn_rows_kernel<false>, dim3(n_kv, nsplit, M), dim3(kThreads), smem, (cudaStream_t)stream, true, p);
+    return b2_launch(attn_rows_kernel<true>, dim3(n_kv, nsplit, gz), dim3(kThreads), smem, (cudaStream_t)stream, true, p);
+  return b2_launch(attn_rows_kernel<false>, dim3(n_kv, nsplit, gz), dim3(kThreads), smem, (cudaStream_t)stream, true, p);
 }
 
 B2_DEFINE_STATUS(attnrows)

@@ -469,6 +469,13 @@ def test_attn_rows_int8_kv_matches_per_row_kernel():
     k_.check_status()
     err = (out.float() - ref.float()).abs().max()
     assert err <= 2e-2 * ref.float().abs().max() + 2e-3, float(err)
+    # the same rows launched as ONE request's group (a CTA column per group of rows instead of one per row): same bits
+    out1 = torch.full_like(ref, float("nan"))
+    k_.attn_rows(q, k8, v8, table, ctrl, o_part, ml, out1, None, m, n_q, n_kv, d, nsplit, max_blocks, d ** -0.5,
+                 k_scale=ks, v_scale=vs, kv_int8=True, one_request=True)
+    torch.cuda.synchronize()
+    k_.check_status()
+    assert torch.equal(out1, out)
 
 
 @pytest.mark.gpu
