@@ -72,7 +72,7 @@ def test_tokenizer_parity_over_the_reference_corpus(tmp_path):
     """Every line of the reference's tokenizer parity corpus (10,240 cases: prose, code, numbers, scripts, whitespace
     runs) through both libraries, with a vocabulary trained on part of that corpus and the pre-tokeniser pattern
     read from the reference's own tokenizer file.  (The reference's expected ids belong to a full vocabulary that is
-    not on this machine, so the library it wraps is the judge.)"""
+    not available here, so the library it wraps decides what is right.)"""
     import json
     corpus = os.path.join(REF_TOK_DIR, "tokenizer", "corpus.txt")
     tokjson = os.path.join(REF_TOK_DIR, "model", "qwen4exp-q38tok", "tokenizer.json")
