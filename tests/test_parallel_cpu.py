@@ -66,6 +66,47 @@ def _sharded(rank, world, port, q):
         q.put(("follower", n))
 
 
+def _lockstep_spec(rank, world, port, q):
+    """An engine with a draft head behind the lock-step leader: drafts are made on every rank."""
+    sys.path.insert(0, ROOT)
+    from b200serve.parallel import launch as L
+    from b200serve.server.iface import MockEngine
+    _init(rank, world, port)
+    plane = L.ControlPlane()
+
+    class Drafting(MockEngine):
+        def __init__(self, **kw):
+            super().__init__(**kw)
+            self.draft_calls = []
+            self.stats = {"drafted": 0}
+
+        def draft_many(self, reqs):
+            self.draft_calls.append(dict(reqs))
+            out = {s: [(r[0] + 1 + j) % self.vocab_size for j in range(r[1])] for s, r in reqs.items()}
+            self.stats["drafted"] += sum(len(v) for v in out.values())
+            return out
+
+        def draft(self, slot, pending, k, temperature=0.0, seed=0):
+            return self.draft_many({slot: (pending, k, temperature, seed)})[slot]
+
+        def draft_q(self, slot):
+            return None
+
+    eng = Drafting(vocab_size=259, max_seqs=2)
+    if rank == 0:
+        lead = L.lockstep_leader(eng, plane)
+        assert isinstance(lead, L.LockstepSpecLeader)
+        plain = L.lockstep_leader(MockEngine(vocab_size=259, max_seqs=2), plane)
+        first = lead.prefill(0, [5, 6, 7])
+        d1 = lead.draft(0, first, 3)
+        d2 = lead.draft_many({0: (first, 2, 0.5, 9)})
+        lead.shutdown()
+        q.put(("leader", d1, d2, not hasattr(plain, "draft_many"), lead.stats["drafted"], lead.draft_q(0)))
+    else:
+        n = L.follow_lockstep(eng, plane)
+        q.put(("follower", n, eng.draft_calls, eng.stats["drafted"]))
+
+
 def _replica(rank, world, port, q):
     sys.path.insert(0, ROOT)
     from b200serve.parallel import launch as L
@@ -106,6 +147,17 @@ def test_lockstep_followers_execute_every_leader_call():
     _, n, flen, fseq = res["follower"]
     assert n == 3 and flen == length == 3          # prefill, step, truncate reached the follower
     assert fseq == [5, 6, 7]
+
+
+def test_lockstep_leader_with_a_draft_head_drafts_on_every_rank():
+    res = _spawn(_lockstep_spec, port=29704)
+    _, d1, d2, plain_has_none, drafted, q0 = res["leader"]
+    _, n, calls, fdrafted = res["follower"]
+    assert len(d1) == 3 and list(d2) == [0] and len(d2[0]) == 2
+    assert plain_has_none and q0 is None            # an engine without a head gets the plain leader
+    assert n == 3 and len(calls) == 2               # prefill + two draft calls reached the follower
+    assert calls[0][0][1] == 3 and calls[1][0][1:] == (2, 0.5, 9)
+    assert drafted == fdrafted == 5
 
 
 def test_lockstep_leader_assembles_full_vocabulary_row_from_shards():
