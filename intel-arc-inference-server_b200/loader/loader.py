@@ -139,22 +139,44 @@ def _load_layer(view: NameView, cfg: ModelConfig, prefix: str, qc: QuantConfig, 
 
 
 def _load_gdn_layer(view: NameView, cfg: ModelConfig, prefix: str, qc: QuantConfig, device, tp) -> LayerWeights:
-    """A gated delta-net layer: ``linear_attn.in_proj_qkvz`` (columns [ q | k | v | z ], heads in order) and
-    ``linear_attn.in_proj_ba`` ([ b | a ]) are fused into one projection; ``conv1d.weight`` is [channels][1][4]."""
+    """A gated delta-net layer: ``linear_attn.in_proj_qkvz`` (columns [ q | k | v | z ], heads in order) and the
+    gate projection are fused into one projection; ``conv1d.weight`` is [channels][1][4].  The gate projection comes
+    as one ``in_proj_ba`` ([ b | a ]) or as two tensors ``in_proj_b`` and ``in_proj_a``, int4 or unquantised (exports
+    differ: some exclude a / b from quantisation, some quantise them like every other linear); an unquantised one is
+    quantised on the host.  Every GDN layer of a checkpoint must use the form and the kind of the first one -- a later
+    layer in the other form is refused by name (the reference's rule: src/loader/ab.h:13-21)."""
     from ..models.weights import GdnWeights
     if tp[1] != 1:
         raise ValueError("gated delta-net layers are not sliced for tensor parallelism")
     p = prefix + ".linear_attn"
-    qkvz, ba = _LinearSrc(view, p + ".in_proj_qkvz", qc), _LinearSrc(view, p + ".in_proj_ba", qc)
-    if qkvz.n != 2 * cfg.gdn_key_dim + 2 * cfg.gdn_value_dim or ba.n != 2 * cfg.gdn_v_heads:
-        raise ValueError(f"{p}: projection widths {qkvz.n} / {ba.n} do not match the configured heads")
+    qkvz = _LinearSrc(view, p + ".in_proj_qkvz", qc)
+    split = not (view.has(p + ".in_proj_ba.qweight") or view.has(p + ".in_proj_ba.weight"))
+    first_name = p + (".in_proj_b" if split else ".in_proj_ba")
+    form = ("split" if split else "fused", "int4" if view.has(first_name + ".qweight") else "dense")
+    seen = getattr(view, "_gdn_gate_form", None)
+    if seen is None:
+        view._gdn_gate_form = (form, p)
+    elif seen[0] != form:
+        raise ValueError(f"{p}: gate projection is {form[0]} / {form[1]}, but {seen[1]} has it {seen[0][0]} / {seen[0][1]}: "
+                         "a checkpoint keeps one form for all gated delta-net layers")
+    if split:
+        pb, pa = _LinearSrc(view, p + ".in_proj_b", qc), _LinearSrc(view, p + ".in_proj_a", qc)
+        if pb.n != cfg.gdn_v_heads or pa.n != cfg.gdn_v_heads:
+            raise ValueError(f"{p}: in_proj_b / in_proj_a have {pb.n} / {pa.n} columns, expected {cfg.gdn_v_heads} each")
+        ba_cols = _fuse_cols([_cols(pb, 0, pb.n), _cols(pa, 0, pa.n)])
+        ba_n = pb.n + pa.n
+    else:
+        ba = _LinearSrc(view, p + ".in_proj_ba", qc)
+        ba_cols, ba_n = _cols(ba, 0, ba.n), ba.n
+    if qkvz.n != 2 * cfg.gdn_key_dim + 2 * cfg.gdn_value_dim or ba_n != 2 * cfg.gdn_v_heads:
+        raise ValueError(f"{p}: projection widths {qkvz.n} / {ba_n} do not match the configured heads")
     out = _LinearSrc(view, p + ".out_proj", qc)
     conv = view.get(p + ".conv1d.weight").float().reshape(cfg.gdn_conv_channels, 4)
     lw = LayerWeights(
         input_norm=view.get(prefix + ".input_layernorm.weight").float().to(device),
         post_norm=view.get(prefix + ".post_attention_layernorm.weight").float().to(device), qkv=None, o=None)
     lw.gdn = GdnWeights(
-        in_proj=_ql(*_fuse_cols([_cols(qkvz, 0, qkvz.n), _cols(ba, 0, ba.n)]), device),
+        in_proj=_ql(*_fuse_cols([_cols(qkvz, 0, qkvz.n), ba_cols]), device),
         conv_w=conv.contiguous().to(device), a_log=view.get(p + ".A_log").float().to(device),
         dt_bias=view.get(p + ".dt_bias").float().to(device), norm_w=view.get(p + ".norm.weight").float().to(device),
         out_proj=_ql(out.q, out.scales, device))

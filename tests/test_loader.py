@@ -234,3 +234,46 @@ def test_mixed_expert_forms_in_a_layer_are_refused(tmp_path):
         json.dump({"metadata": {}, "weight_map": {n: fname for n in t}}, f)
     with pytest.raises(ValueError, match="experts.1: mixed expert forms"):
         load(snap, device="cpu", report=None)
+
+
+def test_gdn_gate_projection_forms(tmp_path):
+    """The gate projection of gated delta-net layers as two tensors (in_proj_b, in_proj_a) loads to the same fused
+    projection as in_proj_ba; a checkpoint that mixes the forms is refused by name."""
+    from b200serve.models.config import preset
+    cfg = preset("small-hybrid")
+    w = _bf16_norms(random_weights(cfg, seed=8))
+    snap = write_checkpoint(w, str(tmp_path / "snap"), shards=1)
+    fname = [f for f in os.listdir(snap) if f.endswith(".safetensors")][0]
+    st = SafetensorsSet(snap)
+    base = {n: st.get(n) for n in st.names()}
+    nv = cfg.gdn_v_heads
+
+    def split(t, layer):
+        p = f"model.layers.{layer}.linear_attn"
+        q = Q.unpack_gptq(t[p + ".in_proj_ba.qweight"])
+        sc = t[p + ".in_proj_ba.scales"]
+        for name, cols in (("in_proj_b", slice(0, nv)), ("in_proj_a", slice(nv, 2 * nv))):
+            t[f"{p}.{name}.qweight"] = Q.pack_gptq(q[:, cols].contiguous())
+            t[f"{p}.{name}.scales"] = sc[:, cols].contiguous()
+            t[f"{p}.{name}.qzeros"] = Q.make_qzeros(q.shape[0], nv)
+        for sfx in (".qweight", ".scales", ".qzeros"):
+            del t[p + ".in_proj_ba" + sfx]
+
+    def write(t):
+        save_file(t, os.path.join(snap, fname), {"format": "pt"})
+        with open(os.path.join(snap, "model.safetensors.index.json"), "w") as f:
+            json.dump({"metadata": {}, "weight_map": {n: fname for n in t}}, f)
+
+    t = dict(base)
+    for layer in (0, 2):
+        split(t, layer)
+    write(t)
+    got = load(snap, device="cpu", report=None)
+    for a, b in zip(got.layers, w.layers):
+        if b.gdn is not None:
+            assert torch.equal(a.gdn.in_proj.w4b, b.gdn.in_proj.w4b)
+    t = dict(base)
+    split(t, 2)            # layer 0 keeps in_proj_ba
+    write(t)
+    with pytest.raises(ValueError, match="layers.2.linear_attn: gate projection is split"):
+        load(snap, device="cpu", report=None)
