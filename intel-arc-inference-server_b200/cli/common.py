@@ -53,6 +53,23 @@ def peek_config(spec: str):
     return ModelConfig.from_hf_config(hf)
 
 
+def chat_format_for(spec: str):
+    """The chat format of a snapshot, from ``config.json``'s ``model_type`` (None for presets and for every model
+    type that reads as the default format, which then follows ``--tool-format``)."""
+    if spec in PRESETS:
+        return None
+    import json
+    from ..loader.snapshot import resolve_snapshot
+    from ..server.chat_format import ChatFormat
+    try:
+        with open(os.path.join(resolve_snapshot(spec), "config.json")) as f:
+            hf = json.load(f)
+    except OSError:
+        return None
+    fmt = ChatFormat.for_model_type(hf.get("model_type") or hf.get("text_config", {}).get("model_type"))
+    return fmt if fmt.kind != "qwen" else None
+
+
 def parallel_auto(cfg, n_gpus: int, mem_bytes: int, max_seqs: int = 1, kv_dtype: str = "bf16", int8_head: bool = False,
                   min_len: int = 8192) -> str:
     """What ``--parallel auto`` means: one GPU when the model and ``min_len`` positions per sequence fit on it (a
@@ -167,7 +184,8 @@ def build_rank_engine(f, par: str) -> int:
     template = ChatTemplate.from_snapshot(f.model) if f.model not in PRESETS else ChatTemplate()
     opts = ServerOptions(model_name=engine.cfg.name, log_requests=f.log_requests, spec=spec,
                          spec_max=f.spec_max if spec != "off" else 0,
-                         tool_format=f.tool_format, prefix_split_last=f.prefix_split_last)
+                         tool_format=f.tool_format, prefix_split_last=f.prefix_split_last,
+                         chat_format=chat_format_for(f.model))
     srv = Server(front, tok, template, opts, host=f.host, port=f.port)
     sys.stderr.write(f"serving {engine.cfg.name} ({par}, {world} GPUs) on http://{f.host}:{srv.port}/v1\n")
     signal.signal(signal.SIGINT, lambda *_: setattr(srv, "_stop", True))

@@ -72,7 +72,8 @@ def main(argv=None):
         from ..server.prefix import PrefixStore
         prefix = PrefixStore(engine, f.prefix_cache_gb)
     opts = ServerOptions(model_name=cfg.name, log_requests=f.log_requests, spec=spec, spec_max=f.spec_max,
-                         tool_format=f.tool_format, prefix_split_last=f.prefix_split_last)
+                         tool_format=f.tool_format, prefix_split_last=f.prefix_split_last,
+                         chat_format=common.chat_format_for(f.model))
     srv = Server(adapter, tok, template, opts, host=f.host, port=f.port, prefix=prefix)
     sys.stderr.write(f"serving {cfg.name} on http://{f.host}:{srv.port}/v1 (spec {spec}, {f.max_num_seqs} slots, "
                      f"context {mp.max_len})\n")

@@ -36,6 +36,7 @@ class ServerOptions:
     prefill_chunk: int = 4096
     row_budget: int = 64
     tool_format: str = "qwen_xml"
+    chat_format: Optional[object] = None     # server.chat_format.ChatFormat; None: the Qwen format with ``tool_format``
     log_requests: Optional[str] = None
     spec: str = "off"                 # off | lookup | mtp | dflash (drafting is done by the engine adapter)
     spec_max: int = 3
@@ -138,10 +139,15 @@ class Server:
             req = H.parse_request(r["body"].decode("utf-8", "replace"), chat)
         except ValueError as e:
             return self._error(hid, 400, str(e))
+        fmt = self.o.chat_format
         try:
             thinking = False
             if chat:
-                prompt = self.template.render(req.messages, req.tools, True, **(req.template_kwargs or {}))
+                messages, kwargs = req.messages, (req.template_kwargs or {})
+                if fmt is not None:
+                    fmt.check_template_kwargs(kwargs)
+                    messages, kwargs = fmt.template_messages(messages), fmt.request_template_kwargs(kwargs)
+                prompt = self.template.render(messages, req.tools, True, **kwargs)
                 thinking = self.template.thinking_opened(prompt)
                 ids = self.tok.encode(prompt)
             else:
@@ -158,7 +164,12 @@ class Server:
                     created=int(time.time()), t0=time.time())
         s.rng_seed = req.seed if req.has_seed else int.from_bytes(os.urandom(6), "little")
         s.streamer = self.tok.streamer()
-        s.parser = H.OutputStream(thinking, req.tools, self.o.tool_format) if chat else None
+        tool_format = fmt.tool_format if fmt is not None else self.o.tool_format
+        if chat and fmt is not None and fmt.reasoning_in_output:
+            from .chat_format import OutputOpening
+            s.parser = OutputOpening(lambda opened, tools=req.tools, tf=tool_format: H.OutputStream(opened, tools, tf))
+        else:
+            s.parser = H.OutputStream(thinking, req.tools, tool_format) if chat else None
         s.stopper = H.StopMatcher(list(req.stop))
         req.max_tokens = max_new
         preferred = self.prefix.preferred_slot(ids) if self.prefix else -1

@@ -270,3 +270,38 @@ def test_client_that_leaves_while_queued_is_cleaned_up(server):
     while time.time() < deadline and (srv.sessions or srv.http.active() > 0):
         time.sleep(0.02)
     assert not srv.sessions and srv.http.active() == 0
+
+
+def test_chat_format_kolibri_reads_kwargs_joins_parts_and_keys_reasoning_on_the_output():
+    """The per-model chat format: template kwargs are checked (a bad reasoning_effort is a 400), list contents reach
+    the template as one string, tool calls are hermes JSON, and reasoning is recognised from a <think> the MODEL
+    emits -- also when the tag arrives split over several pieces."""
+    from b200serve.native import host as H
+    from b200serve.server.chat_format import ChatFormat, OutputOpening
+    fmt = ChatFormat.for_model_type("kolibri1")
+    assert fmt.kind == "kolibri" and fmt.tool_format == "hermes" and fmt.reasoning_in_output
+    assert ChatFormat.for_model_type("qwen3_5_moe").kind == "qwen" and ChatFormat.for_model_type(None).tool_format == "qwen_xml"
+    msgs = [{"role": "user", "content": [{"type": "text", "text": "a"}, {"type": "text", "text": "b"}]},
+            {"role": "assistant", "content": "c"}]
+    assert fmt.template_messages(msgs)[0]["content"] == "a\nb" and fmt.template_messages(msgs)[1]["content"] == "c"
+    assert ChatFormat("qwen").template_messages(msgs) is msgs
+    fmt.check_template_kwargs({"reasoning_effort": "xhigh", "preserve_thinking": True})
+    for bad in ({"reasoning_effort": "extreme"}, {"preserve_thinking": "yes"}):
+        with pytest.raises(ValueError):
+            fmt.check_template_kwargs(bad)
+    assert fmt.request_template_kwargs({"reasoning_effort": "low", "x": 1}) == {"reasoning_effort": "low", "x": 1}
+    assert ChatFormat("qwen").request_template_kwargs({"reasoning_effort": "low", "enable_thinking": False}) == {"enable_thinking": False}
+
+    def run(pieces):
+        p = OutputOpening(lambda opened: H.OutputStream(opened, None, "hermes"))
+        out = []
+        for piece in pieces:
+            out += p.push(piece)
+        out += p.finish()
+        r = "".join(d["text"] for d in out if d["kind"] == "reasoning")
+        c = "".join(d["text"] for d in out if d["kind"] == "content")
+        return r, c
+    assert run(["<th", "ink>", "plan it", "</think>", "answer"]) == ("plan it", "answer")
+    assert run(["  <think>x</think>y"]) == ("x", "y")
+    assert run(["<thin", "g> is not a tag"]) == ("", "<thing> is not a tag")
+    assert run(["<th"]) == ("", "<th")
