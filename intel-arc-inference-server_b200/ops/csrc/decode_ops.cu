@@ -664,6 +664,123 @@ __global__ void __launch_bounds__(256) head_gemv_kernel(const HeadParams<WT> p, 
   }
 }
 
+// The bf16 head on the tensor cores, up to 16 activation rows per pass over the weights: the FMA form above is bound
+// by fp32 issue from 5 rows up (8 rows take twice the time the bytes need), and a 16-row verify step read the head
+// twice.  64 threads = 2 warps, 32 weight rows per warp, 64 per CTA (the arg-max candidate count stays
+// ceil(N / 64)).  mma.m16n8k16 with the activations as A and the weight rows as B; a dot product does not care in
+// which order its k terms are taken, so a lane loads 8 consecutive k of its weight row (and of its two activation
+// rows) as one 16-byte vector and feeds the words to two MMAs in matching slots -- no transposes.
+// With the vectors of a step held in registers (92 per thread) 16 warps fit an SM and the kernel waits on memory
+// latency; so the loads are cp.async into a ring of six stages in shared memory in which every lane owns its slots
+// (it reads back only what it copied: no barrier, no bank conflict) and five stages per warp are in flight: 72 KB per
+// CTA, three CTAs per SM, 120 KB of weights on their way per SM.
+// Every row count runs this kernel, so a row's logits do not depend on how many rows share the step.
+constexpr int kHeadStages = 6, kHeadVecs = 12;   // per stage and lane: 2 x 4 weight vectors, 2 x 2 activation vectors
+constexpr int kHeadSmem = 2 * kHeadStages * kHeadVecs * 512;
+
+__global__ void __launch_bounds__(64) head_gemv_mma_kernel(const HeadParams<__nv_bfloat16> p, int m0) {
+  constexpr int NG = 4, KU = 2, NW = 2;
+  extern __shared__ __align__(16) unsigned char head_smem[];
+  __shared__ float sv[NW][16];
+  __shared__ int si[NW][16];
+  pdl_wait();
+  pdl_launch_dependents();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  const int row0 = blockIdx.x * 64 + warp * 8 * NG;
+  const __nv_bfloat16* wp[NG];
+#pragma unroll
+  for (int i = 0; i < NG; ++i) wp[i] = p.w + (size_t)min(row0 + 8 * i + g, p.N - 1) * p.K + t * 8;
+  const __nv_bfloat16* xa = p.x + (size_t)min(m0 + g, p.M - 1) * p.K + t * 8;
+  const __nv_bfloat16* xb = p.x + (size_t)min(m0 + 8 + g, p.M - 1) * p.K + t * 8;
+  // this lane's slots: stage s, vector v at ring + ((s * kHeadVecs + v) * 32 + lane) * 16
+  unsigned char* ring = head_smem + (size_t)warp * kHeadStages * kHeadVecs * 512 + lane * 16;
+  const uint32_t ring_s = (uint32_t)__cvta_generic_to_shared(ring);
+  const int steps = p.K / (32 * KU);
+  auto issue = [&](int step) {
+    if (step < steps) {
+      const int k = step * 32 * KU;
+      const uint32_t dst = ring_s + (step % kHeadStages) * kHeadVecs * 512;
+#pragma unroll
+      for (int u = 0; u < KU; ++u) {
+#pragma unroll
+        for (int i = 0; i < NG; ++i)
+          asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + (u * NG + i) * 512), "l"(wp[i] + k + 32 * u)
+                       : "memory");
+        asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(dst + (KU * NG + 2 * u) * 512), "l"(xa + k + 32 * u)
+                     : "memory");
+        asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(dst + (KU * NG + 2 * u + 1) * 512),
+                     "l"(xb + k + 32 * u)
+                     : "memory");
+      }
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");   // an empty group past the end keeps the count uniform
+  };
+  float acc[NG][4];
+#pragma unroll
+  for (int i = 0; i < NG; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+#pragma unroll
+  for (int s0 = 0; s0 < kHeadStages; ++s0) issue(s0);
+  for (int step = 0; step < steps; ++step) {
+    asm volatile("cp.async.wait_group %0;" ::"n"(kHeadStages - 1) : "memory");
+    const uint4* st = reinterpret_cast<const uint4*>(ring + (size_t)(step % kHeadStages) * kHeadVecs * 512);
+#pragma unroll
+    for (int u = 0; u < KU; ++u) {
+      const uint4 av = st[(KU * NG + 2 * u) * 32], bv = st[(KU * NG + 2 * u + 1) * 32];
+#pragma unroll
+      for (int i = 0; i < NG; ++i) {
+        const uint4 wv = st[(u * NG + i) * 32];
+        mma_bf16_16816(acc[i], av.x, bv.x, av.y, bv.y, wv.x, wv.y);
+        mma_bf16_16816(acc[i], av.z, bv.z, av.w, bv.w, wv.z, wv.w);
+      }
+    }
+    issue(step + kHeadStages);   // into the stage just read: its values sit in MMA operands by now
+  }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+  // c[0], c[1]: activation row g, weight rows 2t, 2t + 1 of the group; c[2], c[3]: activation row g + 8
+  float best[2] = {-INFINITY, -INFINITY};
+  int besti[2] = {0x7fffffff, 0x7fffffff};
+#pragma unroll
+  for (int grp = 0; grp < NG; ++grp) {
+    const float* c = acc[grp];
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const int n = row0 + grp * 8 + 2 * t + j;
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int m = m0 + g + 8 * h;
+        const float v = c[2 * h + j];
+        if (n < p.N && m < p.M) {
+          p.out[(size_t)m * p.ldo + n] = v;
+          if (n < p.n_valid && v > best[h]) { best[h] = v; besti[h] = n; }   // n ascends: ties keep the lower id
+        }
+      }
+    }
+  }
+  if (!p.cand_val) return;
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+#pragma unroll
+    for (int d = 1; d <= 2; d <<= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best[h], d);
+      const int oi = __shfl_xor_sync(0xffffffffu, besti[h], d);
+      if (ov > best[h] || (ov == best[h] && oi < besti[h])) { best[h] = ov; besti[h] = oi; }
+    }
+    if (t == 0) { sv[warp][g + 8 * h] = best[h]; si[warp][g + 8 * h] = besti[h]; }
+  }
+  __syncthreads();
+  if (threadIdx.x < 16 && m0 + threadIdx.x < p.M) {
+    const int m = threadIdx.x;
+    float b = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int w = 0; w < NW; ++w)
+      if (sv[w][m] > b) { b = sv[w][m]; bi = si[w][m]; }   // warps ascend in n
+    p.cand_val[(size_t)(m0 + m) * gridDim.x + blockIdx.x] = b;
+    p.cand_idx[(size_t)(m0 + m) * gridDim.x + blockIdx.x] = bi;
+  }
+}
+
 // grid M, 256 threads: reduce the candidates; ties -> lower id; write control block.
 __global__ void __launch_bounds__(256) argmax_finish_kernel(const float* cand_val, const int* cand_idx, int ncand,
                                                             int* ctrl, int advance) {
@@ -830,6 +947,21 @@ template <typename WT>
 static int head_launch(const HeadParams<WT>& p, cudaStream_t st) {
   const int rows_per_cta = 64;
   dim3 grid((p.N + rows_per_cta - 1) / rows_per_cta);
+  if constexpr (sizeof(WT) == 2) {
+    if (p.K % 64 == 0) {
+      static bool configured = false;
+      if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(head_gemv_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kHeadSmem);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+      }
+      for (int m0 = 0; m0 < p.M; m0 += 16) {
+        int rc = b2_launch(head_gemv_mma_kernel, grid, dim3(64), kHeadSmem, st, true, p, m0);
+        if (rc) return rc;
+      }
+      return 0;
+    }
+  }
   // up to 8 rows per pass over the weights (the rows share every weight vector a lane loads)
   for (int m0 = 0; m0 < p.M; m0 += 8) {
     const int mt = min(8, p.M - m0);

@@ -8,10 +8,9 @@
 // not built).  One comparator everywhere: the larger value wins, an equal value goes to the lower id, NaN never
 // wins, ids at or above `used` are never candidates; absent candidates are (-inf, kNoIdx).
 //
-// B200 form: a row of logits (up to ~250k floats = 1 MB) is L2-resident right after the head GEMV wrote it, so the
-// top-K is one pass per row: 512 threads keep their own sorted K-lists over a strided slice (registers), then K
-// rounds of a block-wide arg-max over the lists' heads (warp shuffles + one shared-memory step) pop the winners in
-// order.  The rerank is one warp per candidate streaming that head row (bf16, 10 KB at hidden 5120) against the
+// B200 form: a row of logits (up to ~250k floats = 1 MB) is L2-resident right after the head GEMV wrote it.  The
+// top-K is two launches: a warp per ~1k-entry slice keeps its best 16 as a list sorted across its lanes (ballot +
+// shuffle-up per insertion), then one CTA per row runs the same routine over the slices' lists.  The rerank is one warp per candidate streaming that head row (bf16, 10 KB at hidden 5120) against the
 // drafter's hidden row in shared memory.
 #include "common.cuh"
 
@@ -22,7 +21,7 @@ namespace {
 constexpr int kTopMax = 16;
 constexpr unsigned kNoIdx = 0x7fffffffu;
 constexpr int kThreads = 1024;     // rerank: 32 warps, one candidate each per round
-constexpr int kTopThreads = 512;   // top-K: the private lists want 32 registers of a thread's 128
+constexpr int kTopThreads = 256;   // top-K of whole rows: 8 warps
 
 __device__ __forceinline__ bool better(float a, unsigned ai, float b, unsigned bi) {
   // NaN never wins: a comparison with NaN is false, and a NaN `b` loses to any real `a`
@@ -32,105 +31,117 @@ __device__ __forceinline__ bool better(float a, unsigned ai, float b, unsigned b
 }
 
 struct TopkParams {
-  const float* logits;   // [rows][ld]
+  const float* logits;   // [rows][ld]; second stage: the warps' partial values, [rows][n]
+  const unsigned* in_ids;   // second stage: the partial entries' indices (nullptr: the position is the index)
   int ld, n, used, k;
+  int lists;             // first stage: warps (= partial lists of kTopMax pairs) per row
   const int* id_table;   // draft vocabulary: index -> real id (ascending), or nullptr
   float out_mult, softcap;
-  unsigned* cand;        // [rows][k] real ids
+  unsigned* cand;        // [rows][k] real ids        (first stage: [rows][lists][kTopMax] indices)
   float* value;          // [rows][k]
 };
 
-// grid rows, 512 threads
-__global__ void __launch_bounds__(kTopThreads) df_topk_kernel(const TopkParams p) {
-  __shared__ float s_v[32];
-  __shared__ unsigned s_i[32];
+// the partial lists of one launch pair: rows x lists x kTopMax pairs, part of the library's image so that a call
+// allocates nothing (calls on one stream follow one another; two streams must not run the top-K at once)
+constexpr int kPartRows = 64, kPartLists = 128;
+__device__ float g_part_val[kPartRows * kPartLists * kTopMax];
+__device__ unsigned g_part_id[kPartRows * kPartLists * kTopMax];
+
+// A warp's running best-32 of the entries [lo, hi) it scans, kept sorted ACROSS the lanes (lane j holds rank j): a
+// batch of 32 entries per load, a ballot of those that beat rank K - 1, and per survivor one ballot (its place), one
+// shuffle-up (the ranks behind it move) -- about ten instructions, against the ~150 of a bubble through a private
+// register list, and no block-wide round per output.  After warm-up a survivor is rare (K ln(n / K) in n entries).
+// `x`/`xi` may point to global or shared memory; an entry whose index is kNoIdx is absent.
+__device__ __forceinline__ void warp_topk_scan(const float* x, const unsigned* xi, int lo, int hi, int K, float& lv,
+                                               unsigned& li) {
+  const int lane = threadIdx.x & 31;
+  lv = -INFINITY;
+  li = kNoIdx;
+  for (int i0 = lo; i0 < hi; i0 += 128) {
+    float a4[4];
+    unsigned i4[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int i = i0 + u * 32 + lane;
+      a4[u] = i < hi ? x[i] : -INFINITY;
+      i4[u] = i < hi ? (xi ? xi[i] : (unsigned)i) : kNoIdx;
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const float tv = __shfl_sync(0xffffffffu, lv, K - 1);
+      const unsigned ti = __shfl_sync(0xffffffffu, li, K - 1);
+      unsigned mask = __ballot_sync(0xffffffffu, i4[u] != kNoIdx && better(a4[u], i4[u], tv, ti));
+      while (mask) {
+        const int src = __ffs(mask) - 1;
+        mask &= mask - 1;
+        const float cv = __shfl_sync(0xffffffffu, a4[u], src);
+        const unsigned ci = __shfl_sync(0xffffffffu, i4[u], src);
+        const int pos = __popc(__ballot_sync(0xffffffffu, better(lv, li, cv, ci)));   // the ranks that stay ahead
+        const float pv = __shfl_up_sync(0xffffffffu, lv, 1);
+        const unsigned pi = __shfl_up_sync(0xffffffffu, li, 1);
+        if (lane == pos) {
+          lv = cv;
+          li = ci;
+        } else if (lane > pos) {
+          lv = pv;
+          li = pi;
+        }
+      }
+    }
+  }
+}
+
+// first stage: grid (ceil(lists / 4), rows), 128 threads; warp = one slice of the row -> its kTopMax best, raw
+__global__ void __launch_bounds__(128) df_topk_part_kernel(const TopkParams p) {
   pdl_wait();
   pdl_launch_dependents();
-  const int row = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const float* x = p.logits + (size_t)row * p.ld;
-  float v[kTopMax];
-  unsigned id[kTopMax];
-#pragma unroll
-  for (int i = 0; i < kTopMax; ++i) {
-    v[i] = -INFINITY;
-    id[i] = kNoIdx;
-  }
+  const int row = blockIdx.y, lane = threadIdx.x & 31, list = blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (list >= p.lists) return;
   const int lim = min(p.n, p.used);
-  for (int i = tid; i < lim; i += kTopThreads) {
-    const float a = x[i];
-    if (!better(a, (unsigned)i, v[kTopMax - 1], id[kTopMax - 1])) continue;
-    // insertion into the sorted private list (K <= 16: a short unrolled bubble, all in registers)
-    float cv = a;
-    unsigned ci = (unsigned)i;
-#pragma unroll
-    for (int s = 0; s < kTopMax; ++s) {
-      if (better(cv, ci, v[s], id[s])) {
-        const float tv = v[s];
-        const unsigned ti = id[s];
-        v[s] = cv;
-        id[s] = ci;
-        cv = tv;
-        ci = ti;
-      }
-    }
+  const int per = (lim + p.lists - 1) / p.lists;
+  float lv;
+  unsigned li;
+  warp_topk_scan(p.logits + (size_t)row * p.ld, nullptr, list * per, min(lim, (list + 1) * per), kTopMax, lv, li);
+  if (lane < kTopMax) {
+    p.value[((size_t)row * p.lists + list) * kTopMax + lane] = lv;
+    p.cand[((size_t)row * p.lists + list) * kTopMax + lane] = li;
   }
-  // K rounds: the block-wide best of the lists' heads; its owner pops
-  for (int r = 0; r < p.k; ++r) {
-    float bv = v[0];
-    unsigned bi = id[0];
-#pragma unroll
-    for (int d = 16; d > 0; d >>= 1) {
-      const float ov = __shfl_xor_sync(0xffffffffu, bv, d);
-      const unsigned oi = __shfl_xor_sync(0xffffffffu, bi, d);
-      if (better(ov, oi, bv, bi)) {
-        bv = ov;
-        bi = oi;
-      }
+}
+
+// whole rows (a short row, or the second stage over the partial lists): grid rows, 256 threads = 8 warps over
+// eighths of the row, their lists through shared memory, warp 0 over those
+__global__ void __launch_bounds__(kTopThreads) df_topk_kernel(const TopkParams p) {
+  __shared__ float s_v[kTopThreads / 32 * kTopMax];
+  __shared__ unsigned s_i[kTopThreads / 32 * kTopMax];
+  pdl_wait();
+  pdl_launch_dependents();
+  const int row = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const unsigned* xi = p.in_ids ? p.in_ids + (size_t)row * p.ld : nullptr;
+  const int lim = xi ? p.n : min(p.n, p.used);
+  constexpr int W = kTopThreads / 32;
+  const int per = (lim + W - 1) / W;
+  float lv;
+  unsigned li;
+  warp_topk_scan(p.logits + (size_t)row * p.ld, xi, warp * per, min(lim, (warp + 1) * per), kTopMax, lv, li);
+  if (lane < kTopMax) {
+    s_v[warp * kTopMax + lane] = lv;
+    s_i[warp * kTopMax + lane] = li;
+  }
+  __syncthreads();
+  if (warp != 0) return;
+  warp_topk_scan(s_v, s_i, 0, W * kTopMax, p.k, lv, li);
+  if (lane < p.k) {
+    float out = lv;
+    unsigned real = li;
+    if (li == kNoIdx) {
+      out = -INFINITY;
+    } else {
+      out *= p.out_mult;
+      if (p.softcap > 0.f) out = p.softcap * tanhf(out / p.softcap);
+      if (p.id_table) real = (unsigned)p.id_table[li];
     }
-    if (lane == 0) {
-      s_v[warp] = bv;
-      s_i[warp] = bi;
-    }
-    __syncthreads();
-    if (warp == 0) {
-      float wv = lane < kTopThreads / 32 ? s_v[lane] : -INFINITY;
-      unsigned wi = lane < kTopThreads / 32 ? s_i[lane] : kNoIdx;
-#pragma unroll
-      for (int d = 16; d > 0; d >>= 1) {
-        const float ov = __shfl_xor_sync(0xffffffffu, wv, d);
-        const unsigned oi = __shfl_xor_sync(0xffffffffu, wi, d);
-        if (better(ov, oi, wv, wi)) {
-          wv = ov;
-          wi = oi;
-        }
-      }
-      if (lane == 0) {
-        float out = wv;
-        unsigned real = wi;
-        if (wi != kNoIdx) {
-          out *= p.out_mult;
-          if (p.softcap > 0.f) out = p.softcap * tanhf(out / p.softcap);
-          if (p.id_table) real = (unsigned)p.id_table[wi];
-        } else {
-          out = -INFINITY;
-        }
-        p.cand[(size_t)row * p.k + r] = real;
-        p.value[(size_t)row * p.k + r] = out;
-        s_i[0] = wi;   // the winner's index: its owner pops
-      }
-    }
-    __syncthreads();
-    const unsigned win = s_i[0];
-    if (win != kNoIdx && id[0] == win) {
-#pragma unroll
-      for (int s = 0; s + 1 < kTopMax; ++s) {
-        v[s] = v[s + 1];
-        id[s] = id[s + 1];
-      }
-      v[kTopMax - 1] = -INFINITY;
-      id[kTopMax - 1] = kNoIdx;
-    }
-    __syncthreads();
+    p.cand[(size_t)row * p.k + lane] = real;
+    p.value[(size_t)row * p.k + lane] = out;
   }
 }
 
@@ -277,9 +288,36 @@ extern "C" int b2_df_topk(const float* logits, int rows, int ld, int n, int used
                           float softcap, unsigned* cand, float* value, void* stream) {
   if (rows < 1 || k < 1 || k > kTopMax || n < 1 || n > ld) return -1;
   TopkParams p;
-  p.logits = logits; p.ld = ld; p.n = n; p.used = used; p.k = k; p.id_table = id_table; p.out_mult = out_mult;
-  p.softcap = softcap; p.cand = cand; p.value = value;
-  return b2_launch(df_topk_kernel, dim3(rows), dim3(kTopThreads), 0, (cudaStream_t)stream, true, p);
+  p.used = used; p.k = k; p.id_table = id_table; p.out_mult = out_mult; p.softcap = softcap; p.in_ids = nullptr;
+  p.lists = 0;
+  const int lim = n < used ? n : used;
+  int lists = lim / 1024;   // a warp per ~1k entries and more: enough warps to fill the GPU from a handful of rows
+  if (lists > kPartLists) lists = kPartLists;
+  static float* pv = nullptr;   // one device per process
+  static unsigned* pi = nullptr;
+  if (lists >= 16 && (!pv || !pi)) {
+    if (cudaGetSymbolAddress((void**)&pv, g_part_val) != cudaSuccess) return -3;
+    if (cudaGetSymbolAddress((void**)&pi, g_part_id) != cudaSuccess) return -3;
+  }
+  for (int r0 = 0; r0 < rows; r0 += kPartRows) {
+    const int nr = rows - r0 < kPartRows ? rows - r0 : kPartRows;
+    p.logits = logits + (size_t)r0 * ld; p.ld = ld; p.n = n;
+    p.cand = cand + (size_t)r0 * k; p.value = value + (size_t)r0 * k;
+    if (lists < 16) {
+      int rc = b2_launch(df_topk_kernel, dim3(nr), dim3(kTopThreads), 0, (cudaStream_t)stream, true, p);
+      if (rc) return rc;
+      continue;
+    }
+    TopkParams a = p;
+    a.lists = lists; a.cand = pi; a.value = pv;
+    int rc = b2_launch(df_topk_part_kernel, dim3((lists + 3) / 4, nr), dim3(128), 0, (cudaStream_t)stream, true, a);
+    if (rc) return rc;
+    TopkParams b = p;
+    b.logits = pv; b.in_ids = pi; b.ld = lists * kTopMax; b.n = lists * kTopMax;
+    rc = b2_launch(df_topk_kernel, dim3(nr), dim3(kTopThreads), 0, (cudaStream_t)stream, true, b);
+    if (rc) return rc;
+  }
+  return 0;
 }
 
 extern "C" int b2_df_rerank(const void* head, const void* x, long long ldx, int rows, int H, int used, const unsigned* ids,

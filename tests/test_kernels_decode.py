@@ -225,11 +225,11 @@ def test_rope_append_and_attention(n_q, n_kv, d, kv_int8):
     assert (got - ref).abs().max() < (0.04 if kv_int8 else 0.02) * ref.abs().max() + 1e-3
 
 
-@pytest.mark.parametrize("int8", [False, True])
-def test_head_gemv_and_argmax(int8):
+@pytest.mark.parametrize("int8,m", [(False, 6), (True, 6), (False, 1), (False, 16), (False, 19)])
+def test_head_gemv_and_argmax(int8, m):
     k_ = K()
     torch.manual_seed(9)
-    m, n, kdim = 6, 1000, 512
+    n, kdim = 1000, 512
     w = (torch.randn(n, kdim) * 0.05).to(torch.bfloat16)
     x = torch.randn(m, kdim).to(torch.bfloat16)
     # force a tie between ids 17 and 600 on row 0: identical weight rows

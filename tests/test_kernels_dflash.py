@@ -33,10 +33,10 @@ def _ref_topk(row, used, k, table=None, mult=1.0, cap=0.0):
     return out
 
 
-@pytest.mark.parametrize("n,used,k", [(151936, 151800, 16), (4096, 4096, 16), (1000, 7, 16), (32768, 32768, 4)])
-def test_topk_order_ties_nan_and_padding(n, used, k):
+@pytest.mark.parametrize("n,used,k,rows", [(151936, 151800, 16, 3), (4096, 4096, 16, 3), (1000, 7, 16, 3), (32768, 32768, 4, 3),
+                                           (248320, 248320, 16, 15), (40000, 39000, 16, 70)])
+def test_topk_order_ties_nan_and_padding(n, used, k, rows):
     torch.manual_seed(n + k)
-    rows = 3
     x = torch.randn(rows, n)
     x[0, 5] = x[0, 900 % n] = 7.5          # a tie at the top: the lower index first
     x[1, 3] = float("nan")
