@@ -221,8 +221,16 @@ __device__ __forceinline__ void attn_rows_body(const AttnRowsParams& p, uint8_t*
             uint32_t o[8];
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-              o[2 * j] = pack_bf16((float)(int8_t)(ww[j] & 0xff) * sc, (float)(int8_t)((ww[j] >> 8) & 0xff) * sc);
-              o[2 * j + 1] = pack_bf16((float)(int8_t)((ww[j] >> 16) & 0xff) * sc, (float)(int8_t)(ww[j] >> 24) * sc);
+              // int8 -> fp32 without the conversion unit (a quarter-rate pipe that capped this loop): the byte, biased
+              // to 0..255, dropped into the mantissa of 2^23 is 8388608 + u, and subtracting 8388736 leaves the signed
+              // value exactly -- the same floats as (float)(int8_t), so the same products
+              const uint32_t u = ww[j] ^ 0x80808080u;
+              const float f0 = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7540)) - 8388736.f;
+              const float f1 = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7541)) - 8388736.f;
+              const float f2 = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7542)) - 8388736.f;
+              const float f3 = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7543)) - 8388736.f;
+              o[2 * j] = pack_bf16(f0 * sc, f1 * sc);
+              o[2 * j + 1] = pack_bf16(f2 * sc, f3 * sc);
             }
             asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst + tile_off(tid, 16 * i)), "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3]) : "memory");
             asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst + tile_off(tid, 16 * i + 8)), "r"(o[4]), "r"(o[5]), "r"(o[6]), "r"(o[7]) : "memory");
