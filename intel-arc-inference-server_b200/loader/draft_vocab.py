@@ -50,6 +50,18 @@ def read_ranked_ids(path: str) -> List[int]:
     return out
 
 
+def int8_rows(w: torch.Tensor, rows_per_pass: int = 16384):
+    """``w`` [n][k] as (int8 rows, fp32 scale per row), symmetric, the row's largest magnitude at 127."""
+    q = torch.empty(w.shape, dtype=torch.int8, device=w.device)
+    sc = torch.empty(w.shape[0], dtype=torch.float32, device=w.device)
+    for r0 in range(0, w.shape[0], rows_per_pass):
+        wf = w[r0: r0 + rows_per_pass].float()
+        s = wf.abs().amax(dim=1).clamp_min(1e-12) / 127.0
+        q[r0: r0 + rows_per_pass] = torch.round(wf / s[:, None]).clamp_(-127, 127).to(torch.int8)
+        sc[r0: r0 + rows_per_pass] = s
+    return q.contiguous(), sc.contiguous()
+
+
 class DraftVocab:
     """The gathered head rows and the map from a position in V' back to the token id."""
 
@@ -62,9 +74,7 @@ class DraftVocab:
         self.head_i8 = None
         self.exact_rows = not int8      # the logits of ``head`` are the target head's own
         if int8:
-            wf = self.head.float()
-            sc = wf.abs().amax(dim=1).clamp_min(1e-12) / 127.0
-            self.head_i8 = (torch.round(wf / sc[:, None]).clamp_(-127, 127).to(torch.int8).contiguous(), sc.contiguous())
+            self.head_i8 = int8_rows(self.head)
             self.head = None
         self.ids32 = self.ids.to(torch.int32)
         self.size = int(self.ids.numel())

@@ -622,10 +622,13 @@ __global__ void __launch_bounds__(256) head_gemv_kernel(const HeadParams<WT> p, 
           } else {
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-              a = fmaf((float)(int8_t)(ww[j] & 0xff), xf[4 * j], a);
-              a = fmaf((float)(int8_t)((ww[j] >> 8) & 0xff), xf[4 * j + 1], a);
-              a = fmaf((float)(int8_t)((ww[j] >> 16) & 0xff), xf[4 * j + 2], a);
-              a = fmaf((float)(int8_t)(ww[j] >> 24), xf[4 * j + 3], a);
+              // int8 -> fp32 by a byte permute into the mantissa of 2^23 and one subtraction (exact; the integer
+              // conversion unit is a quarter-rate pipe and capped this loop below the memory rate)
+              const uint32_t u = ww[j] ^ 0x80808080u;
+              a = fmaf(__uint_as_float(__byte_perm(u, 0x4B000000u, 0x7540)) - 8388736.f, xf[4 * j], a);
+              a = fmaf(__uint_as_float(__byte_perm(u, 0x4B000000u, 0x7541)) - 8388736.f, xf[4 * j + 1], a);
+              a = fmaf(__uint_as_float(__byte_perm(u, 0x4B000000u, 0x7542)) - 8388736.f, xf[4 * j + 2], a);
+              a = fmaf(__uint_as_float(__byte_perm(u, 0x4B000000u, 0x7543)) - 8388736.f, xf[4 * j + 3], a);
             }
           }
           acc[r][m] = a;
