@@ -159,7 +159,7 @@ class DecoderModel:
         self._splits = {}
         # from this many rows up the activations are quantised once by their own kernel instead of in every
         # CTA of the GEMV (whose prologue repeats the rows' work per 128 output columns)
-        self.prequant_rows = 3
+        self.prequant_rows = int(os.environ.get("B2_PREQUANT_ROWS", "3"))
         self.attn_rows_min = int(os.environ.get("B2_ATTN_ROWS_MIN", "1"))
         self.rows_one_request = False    # set by the engine around a step whose rows are one request's, consecutive
         self.block_rows = False      # set by a block drafter around its layers: flagged rows attend non-causally

@@ -84,7 +84,8 @@ struct GemmParams {
 };
 
 constexpr int kW4Block = 4352;     // one W4B block: 128 rows x 64 k of nibbles (4096 B) + 128 fp16 scales
-constexpr int kDequantWarps = 8;   // W4 form: warps that expand the blocks into the B tile
+constexpr int kDequantWarps = 16;  // W4 form: warps that expand the blocks into the B tile (one 16-byte vector per thread and
+                                   // stage at BN = 256: eight warps left a third of the issue slots empty on dependent chains)
 
 template <int BN, bool W4 = false>
 struct Cfg {
@@ -231,11 +232,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       }
     }
   } else if (W4 && warp >= 6) {
-    // ------------------------------------------------------------ W4 expansion (warps 6..13)
+    // ------------------------------------------------------------ W4 expansion (warps 6 .. 6 + kDequantWarps - 1)
     // One 16-byte vector of a W4B block holds rows g and g + 8 of a 16-row tile, 64 k: low nibbles are k 4t..4t+3 of a
     // 32-k step, high nibbles k + 16 (the operand order of the decode GEMV).  Each vector becomes sixteen 8-byte
     // pieces of the B tile: row r at r * 128 bytes, 16-byte chunk (k / 8) XOR (r mod 8) -- the 128-byte swizzle.
-    const int dt = threadIdx.x - 6 * 32;   // 0 .. 255
+    const int dt = threadIdx.x - 6 * 32;   // 0 .. 32 * kDequantWarps - 1
     int it = 0;
     bool ok = true;
     for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
@@ -257,21 +258,30 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           const __half2 sh = *reinterpret_cast<const __half2*>(&sc2);
           const float s_lo = __low2float(sh), s_hi = __high2float(sh);
           const uint32_t wa[4] = {wv.x, wv.y, wv.z, wv.w};
+          uint64_t sc2x[2], off2;
+          asm("mov.b64 %0, {%1, %1};" : "=l"(sc2x[0]) : "f"(s_lo));
+          asm("mov.b64 %0, {%1, %1};" : "=l"(sc2x[1]) : "f"(s_hi));
+          asm("mov.b64 %0, {%1, %1};" : "=l"(off2) : "f"(-8388616.f));
 #pragma unroll
           for (int c = 0; c < 4; ++c) {
             const int row = b * 128 + j * 16 + g + 8 * (c & 1);
-            const float sc = (c & 1) ? s_hi : s_lo;
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
               const uint32_t x = (wa[c] >> (4 * e)) & 0x0F0F0F0Fu;
-              // bytes -> floats through the 2^23 trick: 0x4B0000qq is 8388608 + q, so (q - 8) * s = f * s - 8388616 * s
-              const float f0 = __uint_as_float(__byte_perm(x, 0x4B000000u, 0x7440));
-              const float f1 = __uint_as_float(__byte_perm(x, 0x4B000000u, 0x7441));
-              const float f2 = __uint_as_float(__byte_perm(x, 0x4B000000u, 0x7442));
-              const float f3 = __uint_as_float(__byte_perm(x, 0x4B000000u, 0x7443));
-              const float off = -8388616.f;
-              const uint32_t p01 = pack_bf16((f0 + off) * sc, (f1 + off) * sc);
-              const uint32_t p23 = pack_bf16((f2 + off) * sc, (f3 + off) * sc);
+              // bytes -> floats through the 2^23 trick: 0x4B0000qq is 8388608 + q; q - 8 (exact) and the product with
+              // the scale run as packed pairs (add.f32x2 / mul.f32x2), the same floats as the scalar form
+              uint64_t f01, f23;
+              asm("mov.b64 %0, {%1, %2};" : "=l"(f01) : "r"(__byte_perm(x, 0x4B000000u, 0x7440)), "r"(__byte_perm(x, 0x4B000000u, 0x7441)));
+              asm("mov.b64 %0, {%1, %2};" : "=l"(f23) : "r"(__byte_perm(x, 0x4B000000u, 0x7442)), "r"(__byte_perm(x, 0x4B000000u, 0x7443)));
+              asm("add.rn.f32x2 %0, %0, %1;" : "+l"(f01) : "l"(off2));
+              asm("add.rn.f32x2 %0, %0, %1;" : "+l"(f23) : "l"(off2));
+              asm("mul.rn.f32x2 %0, %0, %1;" : "+l"(f01) : "l"(sc2x[c & 1]));
+              asm("mul.rn.f32x2 %0, %0, %1;" : "+l"(f23) : "l"(sc2x[c & 1]));
+              float g0, g1, g2, g3;
+              asm("mov.b64 {%0, %1}, %2;" : "=f"(g0), "=f"(g1) : "l"(f01));
+              asm("mov.b64 {%0, %1}, %2;" : "=f"(g2), "=f"(g3) : "l"(f23));
+              const uint32_t p01 = pack_bf16(g0, g1);
+              const uint32_t p23 = pack_bf16(g2, g3);
               const int k0 = 32 * (c >> 1) + 16 * e + 4 * tq;
               const uint32_t dst = sb + row * 128 + ((((uint32_t)k0 >> 3) ^ ((uint32_t)row & 7u)) << 4) + (k0 & 7) * 2;
               asm volatile("st.shared.v2.u32 [%0], {%1, %2};" ::"r"(dst), "r"(p01), "r"(p23) : "memory");

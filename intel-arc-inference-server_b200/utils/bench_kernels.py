@@ -124,8 +124,9 @@ if __name__ == "__main__":
         from ..runtime.engine import Engine
         cfg = replace(preset("dense-27b"), n_layers=2)
         ntok = int(sys.argv[2]) if len(sys.argv) > 2 else 2048
+        backend = sys.argv[3] if len(sys.argv) > 3 else "bf16-resident"     # or int8 | w4
         eng = Engine(random_weights(cfg, device="cuda", seed=0, exact=False), max_seqs=1, max_len=ntok + 64, use_graphs=False,
-                     prefill_backend="bf16-resident")
+                     prefill_backend=backend)
         ids = torch.randint(0, cfg.vocab, (ntok,)).tolist()
         for _ in range(2):
             eng.reset(0)
@@ -159,6 +160,18 @@ if __name__ == "__main__":
             meng.reset(0)
             mrun.run(0, ids)
         torch.cuda.synchronize()
+        K.check_status()
+    elif what == "sampler-one":  # the device sampler on a few rows of 27B-vocabulary logits (temperature, top-k, top-p)
+        m, n = (int(sys.argv[2]) if len(sys.argv) > 2 else 8), 151936
+        logits = torch.randn(m, n, device="cuda") * 3
+        f32, i32 = torch.float32, torch.int32
+        temp = torch.full((m,), 0.8, dtype=f32, device="cuda")
+        top_k = torch.full((m,), 40, dtype=i32, device="cuda")
+        top_p = torch.full((m,), 0.95, dtype=f32, device="cuda")
+        seed = torch.arange(m, dtype=torch.int64, device="cuda") + 1234
+        tok, status = torch.zeros(m, dtype=i32, device="cuda"), torch.zeros(m, dtype=i32, device="cuda")
+        ms = time_ms(lambda: K.sample_rows(logits, m, n, temp, top_k, top_p, seed, tok, status), iters=5)
+        print(f"sample_rows {m} rows x {n} logits: {ms * 1e3:.1f} us per launch; tokens {tok.tolist()} status {status.tolist()}")
         K.check_status()
     elif what == "gemv-graph":  # back-to-back launches inside a CUDA graph
         bench_gemv((1, 4, 8), graph=True)
