@@ -225,6 +225,29 @@ def test_rope_append_and_attention(n_q, n_kv, d, kv_int8):
     assert (got - ref).abs().max() < (0.04 if kv_int8 else 0.02) * ref.abs().max() + 1e-3
 
 
+def test_head_logits_do_not_depend_on_the_rows_that_share_the_pass():
+    """A row's logits are the same bits alone, among 8 rows and among 19 (two passes): verify rows reproduce
+    single-row decoding through near-ties."""
+    k_ = K()
+    torch.manual_seed(21)
+    n, kdim = 1500, 1024
+    w = (torch.randn(n, kdim) * 0.05).to(torch.bfloat16).cuda()
+    x = torch.randn(19, kdim).to(torch.bfloat16).cuda()
+    ncand = k_.head_ncand(n)
+    outs = {}
+    for m in (1, 8, 19):
+        out = torch.zeros(m, n, device="cuda")
+        cv = torch.zeros(m * ncand, device="cuda")
+        ci = torch.zeros(m * ncand, dtype=torch.int32, device="cuda")
+        k_.head_gemv(w, x[:m].contiguous(), out, m, n, kdim, cv, ci)
+        outs[m] = out
+    torch.cuda.synchronize()
+    k_.check_status()
+    assert torch.equal(outs[1][0], outs[8][0]) and torch.equal(outs[8], outs[19][:8])
+    ref = x.float() @ w.float().t()
+    assert (outs[19] - ref).abs().max() < 2e-3 * ref.abs().max()
+
+
 @pytest.mark.parametrize("int8,m", [(False, 6), (True, 6), (False, 1), (False, 16), (False, 19)])
 def test_head_gemv_and_argmax(int8, m):
     k_ = K()
