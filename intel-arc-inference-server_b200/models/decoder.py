@@ -160,6 +160,7 @@ class DecoderModel:
         # from this many rows up the activations are quantised once by their own kernel instead of in every
         # CTA of the GEMV (whose prologue repeats the rows' work per 128 output columns)
         self.prequant_rows = int(os.environ.get("B2_PREQUANT_ROWS", "3"))
+        self.merge_quant = os.environ.get("B2_MERGE_QUANT", "1") == "1"   # the attention merge writes the o projection's quantised rows
         self.attn_rows_min = int(os.environ.get("B2_ATTN_ROWS_MIN", "1"))
         self.rows_one_request = False    # set by the engine around a step whose rows are one request's, consecutive
         self.block_rows = False      # set by a block drafter around its layers: flagged rows attend non-causally
@@ -201,7 +202,8 @@ class DecoderModel:
             K.gemv_w4(ql.w4b, x, part, m, ql.n, ql.k, s, x_mode=x_mode, s_in=s_in, x_slice=x_slice)
         return part, s
 
-    def _attention(self, m: int, ctrl, block_table, max_blocks, kv: KVCache, kc, vc, ks, vs, window: int = 0):
+    def _attention(self, m: int, ctrl, block_table, max_blocks, kv: KVCache, kc, vc, ks, vs, window: int = 0,
+                   quant_out: bool = False) -> bool:
         """Split-KV attention of the step's rows into ``buf.attn_out``.  Head size 128 (bf16 or int8 KV) goes to the
         tensor-core kernel that serves a request's consecutive rows together; the rest to the per-row kernel."""
         cfg, b = self.cfg, self.buf
@@ -209,17 +211,22 @@ class DecoderModel:
             raise NotImplementedError("block rows need the multi-row attention kernel (head size 128)")
         if (m >= self.attn_rows_min or window == -1) and cfg.head_dim == 128 and self.nsplit_attn <= 64 and cfg.gqa <= 16:
             inkernel = m <= self.attn_merge_inkernel_rows    # few rows: the last split CTA merges; many: a merge launch
+            # ``quant_out``: the caller's next launch is the o projection on pre-quantised rows; the merge writes them
+            quant = quant_out and not inkernel and m >= self.prequant_rows and self.merge_quant
             K.attn_rows(b.q, kc, vc, block_table, ctrl, b.o_part, b.ml_part, b.attn_out, b.tickets if inkernel else None,
                         m, cfg.n_q_heads,
                         cfg.n_kv_heads, cfg.head_dim, self.nsplit_attn, max_blocks, self.scale,
                         span_pages=(max_blocks + self.nsplit_attn - 1) // self.nsplit_attn if self.attn_fixed_spans else 0,
-                        k_scale=ks, v_scale=vs, kv_int8=kv.kv_int8, window=window, one_request=self.rows_one_request and m > 1)
+                        k_scale=ks, v_scale=vs, kv_int8=kv.kv_int8, window=window, one_request=self.rows_one_request and m > 1,
+                        xq=b.xq if quant else None, xq_gs=b.xq_gs if quant else None)
+            return quant
         else:
             if window > 0:
                 raise NotImplementedError("sliding-window layers need the multi-row attention kernel (head size 128)")
             K.attn_decode(b.q, kc, vc, block_table, ctrl, b.o_part, b.ml_part, b.attn_out, m, cfg.n_q_heads,
                           cfg.n_kv_heads, cfg.head_dim, self.nsplit_attn, max_blocks, self.scale, ks, vs, kv.kv_int8,
                           tickets=b.tickets)
+        return False
 
     def gdn_block(self, lw: LayerWeights, li: int, m: int, ctrl, kv: KVCache):
         """A gated delta-net layer's mixer for the step's rows: projection GEMV, convolution + SiLU, the recurrent
@@ -253,7 +260,7 @@ class DecoderModel:
         return self._gemv("down", lw.down, gu, m, x_mode=1, s_in=s_gu, x_slice=m * 2 * cfg.ffn)
 
     def _gemv_fused(self, name: str, ql: QLinear, x, m: int, norm_w=None, fold: bool = False, x_mode=0, s_in=1,
-                    x_slice=0, tp_fold: bool = True):
+                    x_slice=0, tp_fold: bool = True, prequantised: bool = False):
         """``tp_fold`` False: a linear every rank holds whole (a draft head's front) folds locally, without the
         ranks' all-reduce."""
         key = (ql.n, ql.k)
@@ -262,7 +269,9 @@ class DecoderModel:
             s = self._splits[key] = K.gemv_splits(ql.n, ql.k)
         b = self.buf
         part = b.part(name, s, ql.n)
-        if m >= self.prequant_rows:
+        if prequantised:        # ``buf.xq`` / ``buf.xq_gs`` already hold these rows (written by the attention merge)
+            x, x_mode, norm_w, xq_gs = b.xq, 3, None, b.xq_gs
+        elif m >= self.prequant_rows:
             K.quant_x(x, m, ql.k, b.xq, b.xq_gs, x_mode=x_mode, s_in=s_in, x_slice=x_slice, norm_w=norm_w,
                       norm_ssq=b.ssq if norm_w is not None else None, norm_eps=self.cfg.rms_eps)
             x, x_mode, norm_w, xq_gs = b.xq, 3, None, b.xq_gs
@@ -312,8 +321,9 @@ class DecoderModel:
                 part, s = self._gemv_fused("qkv", lw.qkv, b.resid, m, norm_w=lw.input_norm, x_mode=2)
             K.rope_append(part, m * cfg.qkv_dim, s, m, ctrl, block_table, max_blocks, self.cos_t, self.sin_t,
                           cfg.n_q_heads, cfg.n_kv_heads, cfg.head_dim, b.q, kc, vc, ks, vs, kv.kv_int8)
-        self._attention(m, ctrl, block_table, max_blocks, kv, kc, vc, ks, vs, self._window(li))
-        self._gemv_fused("o", lw.o, b.attn_out, m, fold=True)
+        q8 = self._attention(m, ctrl, block_table, max_blocks, kv, kc, vc, ks, vs, self._window(li),
+                             quant_out=lw.o.k == cfg.n_q_heads * 128)
+        self._gemv_fused("o", lw.o, b.attn_out, m, fold=True, prequantised=q8)
         gu, s_gu = self._gemv_fused("gate_up", lw.gate_up, b.resid, m, norm_w=lw.post_norm, x_mode=2)
         self._gemv_fused("down", lw.down, gu, m, fold=True, x_mode=1, s_in=s_gu, x_slice=m * 2 * cfg.ffn)
 
@@ -352,8 +362,9 @@ class DecoderModel:
                 part, s = self._gemv_fused("qkv", lw.qkv, b.resid, m, norm_w=lw.input_norm, x_mode=2)
             K.rope_append(part, m * cfg.qkv_dim, s, m, ctrl, block_table, max_blocks, self.cos_t, self.sin_t,
                           cfg.n_q_heads, cfg.n_kv_heads, cfg.head_dim, b.q, kc, vc, ks, vs, kv.kv_int8)
-        self._attention(m, ctrl, block_table, max_blocks, kv, kc, vc, ks, vs, self._window(li))
-        self._gemv_fused("o", lw.o, b.attn_out, m, fold=True)
+        q8 = self._attention(m, ctrl, block_table, max_blocks, kv, kc, vc, ks, vs, self._window(li),
+                             quant_out=lw.o.k == cfg.n_q_heads * 128)
+        self._gemv_fused("o", lw.o, b.attn_out, m, fold=True, prequantised=q8)
         # the experts and the router read normalised rows
         K.resid_norm(1, m, cfg.hidden, lw.post_norm, cfg.rms_eps, b.resid, b.x, resid_in=b.resid, splits=0)
         _moe.moe_block_rows(self, lw, m, fold=True)

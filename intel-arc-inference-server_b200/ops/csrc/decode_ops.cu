@@ -504,14 +504,18 @@ __global__ void __launch_bounds__(256) attn_decode_kernel(const AttnDecParams p)
   }
 }
 
-// grid (n_q, M), D threads
+// grid (n_q, M), D threads.  xq != nullptr (D = 128): the head's 128 outputs, as rounded to bf16, also leave as the two
+// quantised 64-k groups the o projection's integer GEMV reads (the work of quant_x_kernel on this row slice, same
+// bits), which saves that launch in a step of several rows.
 __global__ void attn_merge_kernel(const float* o_part, const float* ml_part, __nv_bfloat16* out, int n_q, int nsplit,
-                                  int D) {
+                                  int D, uint8_t* xq, uint32_t* xq_gs, int gs_rows) {
   __shared__ float cw[64];
+  __shared__ __align__(16) __nv_bfloat16 srow[128];
   pdl_wait();
   pdl_launch_dependents();
   const int h = blockIdx.x, m = blockIdx.y, d = threadIdx.x;
   const size_t base = ((size_t)m * n_q + h) * nsplit;
+  float merged;
   if (nsplit <= 64) {
     // weights of the splits once per CTA (one lane per split), then every thread's loads are independent
     if (d < 32) {
@@ -539,9 +543,8 @@ __global__ void attn_merge_kernel(const float* o_part, const float* ml_part, __n
 #pragma unroll
       for (int u = 0; u < 32; ++u) o = fmaf(v0[u], 32 + u < nsplit ? cw[32 + u] : 0.f, o);
     }
-    out[((size_t)m * n_q + h) * D + d] = __float2bfloat16(o);
-    return;
-  }
+    merged = o;
+  } else {
   float mm = -INFINITY;
   for (int s = 0; s < nsplit; ++s) mm = fmaxf(mm, ml_part[(base + s) * 2]);
   float lt = 0.f, o = 0.f;
@@ -551,7 +554,30 @@ __global__ void attn_merge_kernel(const float* o_part, const float* ml_part, __n
     lt += ml_part[(base + s) * 2 + 1] * c;
     o += o_part[(base + s) * D + d] * c;
   }
-  out[((size_t)m * n_q + h) * D + d] = __float2bfloat16(lt > 0.f ? o / lt : 0.f);
+  merged = lt > 0.f ? o / lt : 0.f;
+  }
+  const __nv_bfloat16 ob = __float2bfloat16(merged);
+  out[((size_t)m * n_q + h) * D + d] = ob;
+  if (xq) {
+    srow[d] = ob;
+    __syncthreads();
+    if (d < 32) {   // lanes 0..15 hold the head's sixteen 16-byte vectors; every lane of the warp calls the quantiser
+      const uint4 val = d < 16 ? reinterpret_cast<const uint4*>(srow)[d] : make_uint4(0, 0, 0, 0);
+      const StagedVec sv = stage_quant(val);
+      if (d < 16) {
+        const int KG = n_q * 2, group = h * 2 + (d >> 3), vq = d & 7;
+        uint32_t* dst = reinterpret_cast<uint32_t*>(xq + ((size_t)m * KG + group) * 128) + stage_word(vq);
+        dst[0] = sv.w[0];
+        dst[4] = sv.w[1];
+        dst[8] = sv.w[2];
+        dst[12] = sv.w[3];
+        if (vq == 0) {
+          xq_gs[((size_t)group * gs_rows + m) * 2] = __float_as_uint(sv.scale);
+          xq_gs[((size_t)group * gs_rows + m) * 2 + 1] = (uint32_t)sv.m8sum;
+        }
+      }
+    }
+  }
 }
 
 // ------------------------------------------------------------------ gemv_bf16 / gemv_i8 (lm_head, router)
@@ -926,7 +952,7 @@ extern "C" int b2_attn_decode(const void* q, const void* k_cache, const void* v_
   else return -2;
   if (rc || tickets) return rc;
   return b2_launch(attn_merge_kernel, dim3(n_q, M), dim3(D), 0, st, true, (const float*)o_part, (const float*)ml_part,
-                   (__nv_bfloat16*)out, n_q, nsplit, D);
+                   (__nv_bfloat16*)out, n_q, nsplit, D, (uint8_t*)nullptr, (uint32_t*)nullptr, 0);
 }
 
 extern "C" int b2_kv_convert(void* k16, void* v16, const int* table16, void* k8, void* v8, float* ks, float* vs,
@@ -943,7 +969,16 @@ extern "C" int b2_kv_convert(void* k16, void* v16, const int* table16, void* k8,
 extern "C" int b2_attn_merge(const float* o_part, const float* ml_part, void* out, int M, int n_q, int nsplit, int D,
                              void* stream) {
   return b2_launch(attn_merge_kernel, dim3(n_q, M), dim3(D), 0, (cudaStream_t)stream, true, o_part, ml_part,
-                   (__nv_bfloat16*)out, n_q, nsplit, D);
+                   (__nv_bfloat16*)out, n_q, nsplit, D, (uint8_t*)nullptr, (uint32_t*)nullptr, 0);
+}
+
+// The merge that also writes the rows' quantised form for the o projection (head size 128; xq [M][n_q * 2][128 B],
+// xq_gs [n_q * 2][gs_rows] {scale, -8 sum}: the layout of b2_quant_x for K = n_q * 128).
+extern "C" int b2_attn_merge_quant(const float* o_part, const float* ml_part, void* out, int M, int n_q, int nsplit, int D,
+                                   void* xq, void* xq_gs, int gs_rows, void* stream) {
+  if (D != 128 || !xq || !xq_gs || gs_rows < M) return -1;
+  return b2_launch(attn_merge_kernel, dim3(n_q, M), dim3(D), 0, (cudaStream_t)stream, true, o_part, ml_part,
+                   (__nv_bfloat16*)out, n_q, nsplit, D, (uint8_t*)xq, (uint32_t*)xq_gs, gs_rows);
 }
 
 template <typename WT>
@@ -1050,7 +1085,7 @@ extern "C" int b2_attn_decode_static(const void* q, const void* k_cache, const v
   else rc = attn_decode_dispatch<64>(n_q / n_kv, p, grid, st);
   if (rc) return rc;
   return b2_launch(attn_merge_kernel, dim3(n_q, M), dim3(D), 0, st, true, (const float*)o_part, (const float*)ml_part,
-                   (__nv_bfloat16*)out, n_q, nsplit, D);
+                   (__nv_bfloat16*)out, n_q, nsplit, D, (uint8_t*)nullptr, (uint32_t*)nullptr, 0);
 }
 
 B2_DEFINE_STATUS(decode)

@@ -218,53 +218,9 @@ __device__ __forceinline__ uint4 stage_load(const GemvParams& p, const uint8_t* 
   return val;
 }
 
-// Quantises a group's 64 activations (as rounded to bf16) to 15-bit integers with one scale,
-// X = rint(x * 16383 / amax) = 128 X_hi + X_lo with X_hi in [-128, 127] and X_lo in [0, 127].  The eight
-// lanes that hold a group (one 16-byte vector each) share amax and sum(X) by shuffles; every lane of the
-// warp must call this.  w[0..3] = high limbs of k 0..3, low limbs of k 0..3, high of k 4..7, low of k 4..7.
-struct StagedVec {
-  uint32_t w[4];
-  float scale;
-  int m8sum;  // -8 sum(X) of the whole group
-};
-__device__ __forceinline__ StagedVec stage_quant(uint4 val) {
-  float xf[8] = {bf16_lo(val.x), bf16_hi(val.x), bf16_lo(val.y), bf16_hi(val.y),
-                 bf16_lo(val.z), bf16_hi(val.z), bf16_lo(val.w), bf16_hi(val.w)};
-  float amax = 0.f;
-#pragma unroll
-  for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(xf[i]));
-  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
-  const bool live = amax > 0.f && amax < 3.0e38f;
-  const float inv = live ? 16383.f / amax : 0.f;
-  int X[8], sumX = 0;
-#pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    X[i] = __float2int_rn(xf[i] * inv);
-    sumX += X[i];
-  }
-  sumX += __shfl_xor_sync(0xffffffffu, sumX, 1);
-  sumX += __shfl_xor_sync(0xffffffffu, sumX, 2);
-  sumX += __shfl_xor_sync(0xffffffffu, sumX, 4);
-  StagedVec o;
-  o.w[0] = o.w[1] = o.w[2] = o.w[3] = 0;
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    o.w[0] |= (uint32_t)((X[i] >> 7) & 0xff) << (8 * i);
-    o.w[1] |= (uint32_t)(X[i] & 127) << (8 * i);
-    o.w[2] |= (uint32_t)((X[i + 4] >> 7) & 0xff) << (8 * i);
-    o.w[3] |= (uint32_t)(X[i + 4] & 127) << (8 * i);
-  }
-  o.scale = live ? amax / 16383.f : 0.f;
-  o.m8sum = -8 * sumX;
-  return o;
-}
-// Word index inside a group's 32 words where vector vq (k = 8 vq .. 8 vq + 7) puts its first word: 32-k step
-// vq >> 2, operand register (vq & 3) >> 1, lanes t = 2 (vq & 1) and + 1.  Lane t's words sit at
-// t * 8 + limb * 4 + step * 2 + register, so the main loop reads a limb's four words with one 16-byte load;
-// the vector's four words go to +0 (high, k 0..3), +4 (low), +8 (high, k 4..7), +12 (low).
-__device__ __forceinline__ int stage_word(int vq) { return (vq & 1) * 16 + (vq >> 2) * 2 + ((vq & 3) >> 1); }
+// StagedVec / stage_quant / stage_word (the quantiser of one 16-byte vector and its place in a group) live in
+// common.cuh: the attention merge uses them too.
+
 
 template <int T>
 __global__ void __launch_bounds__(kThreads, (T <= 2 ? 2 : 1)) gemv_w4_kernel(const GemvParams p) {

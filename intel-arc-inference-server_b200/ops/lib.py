@@ -273,20 +273,26 @@ def attn_decode(q, k_cache, v_cache, block_table, ctrl, o_part, ml_part, out, m,
 
 def attn_rows(q, k_cache, v_cache, block_table, ctrl, o_part, ml_part, out, tickets, m, n_q, n_kv, d, nsplit,
               max_blocks, scale, span_pages: int = 0, k_scale=None, v_scale=None, kv_int8: bool = False, window: int = 0,
-              one_request: bool = False):
+              one_request: bool = False, xq=None, xq_gs=None):
     """Decode / verify attention that serves consecutive rows of one request together on the tensor cores
     (bf16 or int8 KV, head size 128); same split-KV partial buffers and in-kernel merge as ``attn_decode``.
     ``window`` > 0: every row attends to its last ``window`` positions only; ``window`` = -1: the rows are a block whose
     rows all attend to every position up to the block's last one (no causal mask inside the block).
     ``one_request``: the caller knows that all ``m`` rows are one request's, at consecutive positions; the launch then
-    has one CTA column per group of rows instead of one per row (most of which would leave at once)."""
+    has one CTA column per group of rows instead of one per row (most of which would leave at once).
+    ``xq`` / ``xq_gs`` (with ``tickets=None``): the merge also writes the rows in the quantised form of ``quant_x`` for
+    K = n_q * d, so that the o projection's GEMV can read them without that launch."""
     rc = lib().b2_attn_rows(_p(q), _p(k_cache), _p(v_cache), _p(k_scale), _p(v_scale), 1 if kv_int8 else 0,
                             _p(block_table), _p(ctrl), _p(o_part), _p(ml_part),
                             _p(out), _p(tickets), m, n_q, n_kv, d, nsplit, max_blocks, ctypes.c_float(scale), span_pages,
                             k_cache.numel() // (n_kv * 16 * d), window, 1 if one_request else 0, _stream())
     _check(rc, "attn_rows")
     if tickets is None:     # many rows: the merge is its own launch, one CTA per row and head
-        rc = lib().b2_attn_merge(_p(o_part), _p(ml_part), _p(out), m, n_q, nsplit, d, _stream())
+        if xq is not None:
+            rc = lib().b2_attn_merge_quant(_p(o_part), _p(ml_part), _p(out), m, n_q, nsplit, d, _p(xq), _p(xq_gs),
+                                           quant_slots(m), _stream())
+        else:
+            rc = lib().b2_attn_merge(_p(o_part), _p(ml_part), _p(out), m, n_q, nsplit, d, _stream())
         _check(rc, "attn_merge")
 
 

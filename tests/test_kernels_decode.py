@@ -630,3 +630,37 @@ def test_gdn_chunked_scan_on_tensor_cores_matches_recurrence(m, seed):
         assert e_o < (2e-5 if name == "scan" else 4e-3) * o_scale + 1e-6, (name, e_o, o_scale)
         assert e_s < (2e-5 if name == "scan" else 4e-3) * float(S.abs().max()), (name, e_s)
         assert float((out.double() - ref).abs().max()) < 0.02 * float(ref.abs().max()) + 1e-3, name
+
+
+@pytest.mark.parametrize("m,nsplit", [(4, 8), (13, 37)])
+def test_attention_merge_writes_the_same_quantised_rows_as_the_quantiser(m, nsplit):
+    """The merge's optional second output is quant_x of its own bf16 rows, bit for bit (limbs, scales, sums)."""
+    k_ = K()
+    torch.manual_seed(5 + m)
+    n_q, d = 10, 128
+    o_part = torch.randn(m * n_q * nsplit * d, device="cuda")
+    ml = torch.empty(m * n_q * nsplit, 2, device="cuda")
+    ml[:, 0] = torch.randn(m * n_q * nsplit, device="cuda") * 3
+    ml[:, 1] = torch.rand(m * n_q * nsplit, device="cuda") + 0.5
+    ml[5, 0] = float("-inf")                  # a split without keys
+    kdim = n_q * d
+    slots = k_.quant_slots(m)
+
+    def bufs():
+        return (torch.zeros(m * (kdim // 64) * 128, dtype=torch.uint8, device="cuda"),
+                torch.zeros(slots * (kdim // 64) * 2, dtype=torch.int32, device="cuda"))
+    out_a = torch.zeros(m, kdim, dtype=torch.bfloat16, device="cuda")
+    out_b = torch.zeros_like(out_a)
+    xq_a, gs_a = bufs()
+    xq_b, gs_b = bufs()
+    L, P, S = k_.lib(), k_._p, k_._stream
+    assert L.b2_attn_merge(P(o_part), P(ml), P(out_a), m, n_q, nsplit, d, S()) == 0
+    k_.quant_x(out_a, m, kdim, xq_a, gs_a)
+    assert L.b2_attn_merge_quant(P(o_part), P(ml), P(out_b), m, n_q, nsplit, d, P(xq_b), P(gs_b), slots, S()) == 0
+    torch.cuda.synchronize()
+    k_.check_status()
+    assert torch.equal(out_a, out_b)
+    assert torch.equal(xq_a, xq_b)
+    g_a = gs_a.view(kdim // 64, slots, 2)[:, :m]
+    g_b = gs_b.view(kdim // 64, slots, 2)[:, :m]
+    assert torch.equal(g_a, g_b)
