@@ -987,11 +987,13 @@ static int head_launch(const HeadParams<WT>& p, cudaStream_t st) {
   dim3 grid((p.N + rows_per_cta - 1) / rows_per_cta);
   if constexpr (sizeof(WT) == 2) {
     if (p.K % 64 == 0) {
-      static bool configured = false;
-      if (!configured) {
+      static bool configured[64] = {};   // per device: the attribute belongs to the device's copy of the kernel
+      int dev = 0;
+      cudaGetDevice(&dev);
+      if (!configured[dev & 63]) {
         cudaError_t e = cudaFuncSetAttribute(head_gemv_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kHeadSmem);
         if (e != cudaSuccess) return (int)e;
-        configured = true;
+        configured[dev & 63] = true;
       }
       for (int m0 = 0; m0 < p.M; m0 += 16) {
         int rc = b2_launch(head_gemv_mma_kernel, grid, dim3(64), kHeadSmem, st, true, p, m0);

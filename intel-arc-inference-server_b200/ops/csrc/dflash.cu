@@ -293,8 +293,12 @@ extern "C" int b2_df_topk(const float* logits, int rows, int ld, int n, int used
   const int lim = n < used ? n : used;
   int lists = lim / 1024;   // a warp per ~1k entries and more: enough warps to fill the GPU from a handful of rows
   if (lists > kPartLists) lists = kPartLists;
-  static float* pv = nullptr;   // one device per process
-  static unsigned* pi = nullptr;
+  static float* pvs[64] = {};   // per device: each has its own copy of the arrays
+  static unsigned* pis[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  float*& pv = pvs[dev & 63];
+  unsigned*& pi = pis[dev & 63];
   if (lists >= 16 && (!pv || !pi)) {
     if (cudaGetSymbolAddress((void**)&pv, g_part_val) != cudaSuccess) return -3;
     if (cudaGetSymbolAddress((void**)&pi, g_part_id) != cudaSuccess) return -3;
