@@ -1,10 +1,13 @@
 """Small decode workload for kernel profiling: a few layers of a named shape at a given depth.
 
     python -m b200serve.utils.profile_decode --model dense-27b --layers 4 --depth 4096 --steps 3
+    python -m b200serve.utils.profile_decode --model dense-27b --layers 2 --depth 1024 --steps 2 --rows 16 --spec dflash
 
 The KV cache is filled with random values up to ``depth`` (no prompt pass), so a
 capture sees only the decode-step kernels.  Runs eagerly (no CUDA graph) so every
-launch appears under its own name in a launch list.
+launch appears under its own name in a launch list.  ``--spec mtp|dflash``: the steps are
+draft-and-verify iterations of a random-init head (``--rows`` - 1 drafts, one verify step of
+``--rows`` rows) after a real prompt pass of ``depth`` tokens, which the head ingests.
 """
 from __future__ import annotations
 
